@@ -1,0 +1,347 @@
+/* silvann_b200.h — the C boundary of the B200 (sm_100a) attention silicon family for SiLVANN.
+ *
+ * One shared library, libsilvann_nvidia_b200.so, is loaded by an unmodified SiLVANN engine the way it loads any
+ * silicon family: it looks up the single entry `silvann_silicon_family_get`, asks for ABI version 9 and receives a
+ * table of per-package "door" tables — plain C function pointers over raw device addresses and sizes.  Everything in
+ * the first half of this header restates that contract so that the library and its tests build without the engine's
+ * sources; the field order and every signature must stay byte-compatible with the engine's own headers:
+ *
+ *   family table            engine/src/packages/sys/contracts/abi/silicon_family.cuh:33-59
+ *   sys doors (31)          engine/src/packages/sys/contracts/abi/gpu.cuh:46-77 (meaning of each: :79-150)
+ *   nn doors (137)          engine/src/packages/nn/contracts/abi/gpu.cuh:93-240
+ *   by-value door structs   engine/src/packages/nn/contracts/abi/gpu.cuh:13-61
+ *   the exported symbol     engine/src/silicon_families/entry.cuh:68-80
+ *
+ * The second half declares what the door ABI cannot express — bf16 element type, the paged KV pool with its page
+ * table and pinned host tier, a one-call fused decode / causal prefill / DeltaNet, counters — as ordinary exported C
+ * functions named `silvann_b200_*`.  They have no `__` in their names, so the engine's "one entry point and nothing
+ * else of ours" build gate (engine/scripts/build_silicon_families.sh:73-79 counts only `<prefix>__` names) still holds.
+ *
+ * Conventions shared by every entry point: pointers named `*_dev` or passed to a door are device addresses of the
+ * device bound to the calling thread; a "half" is 16 raw bits (IEEE fp16, or bf16 where a dtype argument says so);
+ * all accumulation is fp32; nothing here throws, aborts or allocates behind the caller's back unless it says so. */
+#ifndef SILVANN_B200_H
+#define SILVANN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+#include <stdbool.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef uint16_t sv_h16;      /* 16 raw bits of an fp16 (door ABI) or bf16 (extension, by dtype) value */
+typedef uint8_t  sv_u8;
+typedef uint32_t sv_u32;
+typedef uint64_t sv_u64;
+typedef unsigned int sv_fault; /* a worker's device-resident fault word; doors OR a four-letter code into it */
+
+/* ---- constants of the engine's contract ------------------------------------------------------------------ */
+#define SILVANN_B200_ABI_VERSION     9u            /* silicon_family.cuh:31 */
+#define SILVANN_B200_FAMILY_ID       310u          /* a free roster slot above nvidia_cuda12 (300); ids < 1024 */
+#define SILVANN_B200_FAMILY_NAME     "nvidia_b200"
+#define SILVANN_B200_PACKAGES        7u            /* sys, nn, and five model packages with empty door tables */
+#define SILVANN_B200_FAULT_OVERFLOW  0x4E504F56u   /* "NPOV": an fp32 result did not fit a half (primitives.cuh:57) */
+#define SILVANN_B200_RESIDUAL_FLOATS(head_dim) ((head_dim) + 2u)  /* per head: m, l, acc[head_dim] (kernels.cuh:1186) */
+#define SILVANN_B200_GATE_SILU       0u            /* deltanet.cuh:14-15 */
+#define SILVANN_B200_GATE_SIGMOID    1u
+
+/* ---- by-value structs some doors take (layout only; this family does not implement those doors) ----------- */
+typedef struct sv_tq_groups     { sv_u64 codes[12], luts[12], rows[12], d[12], out_at[12], count; } sv_tq_groups;
+typedef struct sv_expert_groups { sv_u64 codes[12], luts[12], out_rows[12], d[12], out_at[12], pairs_at[12], pairs[12], count; } sv_expert_groups;
+typedef struct sv_vector_parts  { sv_u64 at[8], count; } sv_vector_parts;
+
+/* ---- package 0: sys doors — memory, copies, queues, devices (sys/contracts/abi/gpu.cuh:46-77) ------------- */
+#define SILVANN_B200_SYS_DOORS(D) \
+    D( 0, bool,     memory_allocate,                 (void** at, size_t bytes)) \
+    D( 1, void,     memory_free,                     (void* at)) \
+    D( 2, bool,     memory_zerofill,                 (void* at, size_t bytes)) \
+    D( 3, bool,     memory_read,                     (void* to, const void* from, size_t bytes)) \
+    D( 4, bool,     memory_write,                    (void* to, const void* from, size_t bytes)) \
+    D( 5, bool,     compute_completed,               (void)) \
+    D( 6, bool,     side_open,                       (void** channel)) \
+    D( 7, void,     side_close,                      (void* channel)) \
+    D( 8, bool,     side_memory_read,                (void* to, const void* from, size_t bytes, void* channel)) \
+    D( 9, bool,     side_memory_write,               (void* to, const void* from, size_t bytes, void* channel)) \
+    D(10, bool,     memory_allocate_host_ram_mapped, (void** at, void** card_at, size_t bytes)) \
+    D(11, void,     memory_free_host_ram,            (void* at)) \
+    D(12, uint32_t, device_count,                    (void)) \
+    D(13, uint32_t, bind_device,                     (uint32_t index)) \
+    D(14, uint32_t, bound_device,                    (void)) \
+    D(15, bool,     memory_register_host,            (void* at, size_t bytes, void** card_at)) \
+    D(16, void,     memory_unregister_host,          (void* at)) \
+    D(17, bool,     file_open,                       (const char* path, uint64_t* handle)) \
+    D(18, void,     file_close,                      (uint64_t handle)) \
+    D(19, bool,     file_read,                       (uint64_t handle, uint64_t offset, uint64_t bytes, void* to)) \
+    D(20, bool,     memory_map_file,                 (void* at, size_t bytes, uint64_t handle, uint64_t offset)) \
+    D(21, bool,     memory_prefetch,                 (const void* at, size_t bytes)) \
+    D(22, bool,     peer_access,                     (uint32_t other)) \
+    D(23, bool,     mark_open,                       (void** mark)) \
+    D(24, void,     mark_close,                      (void* mark)) \
+    D(25, bool,     mark_record,                     (void* mark)) \
+    D(26, bool,     mark_wait,                       (void* mark)) \
+    D(27, bool,     side_memory_write_queued,        (void* to, const void* from, size_t bytes, void* channel)) \
+    D(28, bool,     side_memory_read_queued,         (void* to, const void* from, size_t bytes, void* channel)) \
+    D(29, bool,     side_mark_record,                (void* mark, void* channel)) \
+    D(30, bool,     mark_reached,                    (void* mark))
+
+#define SILVANN_B200_FIELD_SYS(IDX, RET, NAME, PARAMS) RET (*NAME) PARAMS;
+typedef struct silvann_b200_sys_doors {
+    uint32_t size;                       /* sizeof(this) as the library was built: 256 */
+    SILVANN_B200_SYS_DOORS(SILVANN_B200_FIELD_SYS)
+} silvann_b200_sys_doors;
+
+/* ---- package 1: nn doors, in the engine's append-only order (nn/contracts/abi/gpu.cuh:93-230) ------------- *
+ * Every door returns void, enqueues work on the bound device's default queue and returns.  This family answers the
+ * attention and Gated-DeltaNet rows (25, 26, 28-31, 34, 61, 62, 66, 95-98, 133) with its own sm_100a kernels; the
+ * other rows are present, never null, and refuse: they print one line, and the device's next `compute_completed`
+ * answers false once, which the engine raises as the fault "SEWK" (nvidia_cuda12/sys.cuh:41-61 does the same for a
+ * launch the runtime refused). */
+#define SILVANN_B200_NN_DOORS(D) \
+    D(  0, vector_zero, (sv_h16* v, sv_u64 n)) \
+    D(  1, vector_exp, (sv_h16* o, const sv_h16* x, sv_u64 n, sv_fault* over)) \
+    D(  2, vector_softplus, (sv_h16* o, const sv_h16* x, sv_u64 n, sv_fault* over)) \
+    D(  3, vector_scale, (sv_h16* o, const sv_h16* x, sv_u64 n, float factor, sv_fault* over)) \
+    D(  4, vector_add, (sv_h16* z, const sv_h16* x, const sv_h16* y, sv_u64 n, sv_fault* over)) \
+    D(  5, vector_pointwise_mul, (sv_h16* z, const sv_h16* x, const sv_h16* y, sv_u64 n, sv_fault* over)) \
+    D(  6, rmsnorm, (sv_h16* o, const sv_h16* x, const sv_h16* w, sv_u64 n, float eps, sv_fault* over)) \
+    D(  7, vector_l2norm, (sv_h16* o, const sv_h16* x, sv_u64 n, sv_fault* over)) \
+    D(  8, softmax, (sv_h16* o, const sv_h16* x, sv_u64 n, sv_fault* over)) \
+    D(  9, sigmoid, (sv_h16* o, const sv_h16* x, sv_u64 n, sv_fault* over)) \
+    D( 10, vector_scale_at, (sv_h16* o, const sv_h16* x, const sv_h16* a, sv_u64 which, sv_u64 n, sv_fault* over)) \
+    D( 11, matrix_transpose, (sv_h16* d, const sv_h16* s, sv_u64 rows, sv_u64 cols)) \
+    D( 12, matrix_matvec_transposed, (sv_h16* out, const sv_h16* W, const sv_h16* x, sv_u64 rows, sv_u64 cols, sv_fault* over)) \
+    D( 13, argmax, (sv_u64* out, sv_u64 stamp, const sv_h16* x, sv_u64 n)) \
+    D( 14, vector_dot_product, (sv_u64* out, sv_u64 stamp, const sv_h16* a, const sv_h16* b, sv_u64 n)) \
+    D( 15, vector_at, (sv_u64* out, sv_u64 stamp, const sv_h16* x, sv_u64 i)) \
+    D( 16, swiglu_combine, (sv_h16* o, const sv_h16* g, const sv_h16* u, sv_u64 n, sv_fault* over)) \
+    D( 17, deltanet_rank_1_update, (float* S, const sv_h16* k, const sv_h16* d, float g, sv_u64 k_dim, sv_u64 v_dim)) \
+    D( 18, deltanet_readout, (sv_h16* o, const float* S, const sv_h16* x, sv_u64 k_dim, sv_u64 v_dim, sv_fault* over)) \
+    D( 19, deltanet_conv_step, (sv_h16* o, sv_h16* s, const sv_h16* w, const sv_h16* x, sv_u64 ch, sv_fault* over)) \
+    D( 20, expert_multiply_fp16, (sv_h16* out, const sv_h16* W, const sv_h16* x, sv_u64 rows, sv_u64 cols, sv_fault* over)) \
+    D( 21, turboquant_decode, (sv_h16* out, const sv_u8* weights, sv_u64 w_room, const sv_u8* luts, sv_u64 l_room, sv_u64 d, sv_u64 rows, sv_u64 cols, sv_fault* over)) \
+    D( 22, turboquant_gemv, (sv_h16* out, const sv_u8* weights, sv_u64 w_room, const sv_u8* luts, sv_u64 l_room, const sv_h16* x, sv_u64 d, sv_u64 rows, sv_u64 cols, sv_fault* over)) \
+    D( 23, hadamard_rotate, (sv_h16* out, const sv_h16* in, const sv_h16* sign, sv_u64 n, sv_fault* over)) \
+    D( 24, rope, (sv_h16* o, const sv_h16* x, const float* cs, sv_u64 heads, sv_u64 head_dim, sv_fault* over)) \
+    D( 25, attention_scores, (float* p, const sv_h16* q, const sv_h16* k, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 length)) \
+    D( 26, attention_mix, (sv_h16* o, const float* p, const sv_h16* v, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 length, sv_fault* over)) \
+    D( 27, rope_angles, (float* cs, sv_u64 position, float theta, sv_u64 head_dim)) \
+    D( 28, attention_weights, (float* p, float* res, const sv_h16* q, const sv_h16* k, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 length)) \
+    D( 29, attention_residual_mix, (float* res, const float* p, const sv_h16* v, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 length)) \
+    D( 30, attention_merge, (float* into, const float* a, const float* b, sv_u64 q_heads, sv_u64 head_dim)) \
+    D( 31, attention_finish, (sv_h16* o, const float* res, sv_u64 q_heads, sv_u64 head_dim, sv_fault* over)) \
+    D( 32, vector_top_k, (sv_u64* values, sv_u64 stride, sv_h16* weights, const sv_h16* x, sv_u64 n, sv_u64 k)) \
+    D( 33, turboquant_gemv_int8, (sv_h16* out, const sv_u8* weights, sv_u64 w_room, const sv_u8* luts, sv_u64 l_room, const sv_h16* x, sv_u64 d, sv_u64 rows, sv_u64 cols, sv_fault* over)) \
+    D( 34, deltanet_step, (float* S, const sv_h16* conved, const sv_h16* z, const sv_h16* beta, const sv_h16* g, const sv_h16* w, sv_h16* out, sv_u64 k_heads, sv_u64 v_heads, sv_u64 head_dim, sv_fault* over)) \
+    D( 35, turboquant_gemv_groups, (sv_h16* out, sv_tq_groups g, const sv_h16* x, sv_u64 cols, sv_fault* over)) \
+    D( 36, turboquant_gemv_groups_sum, (sv_h16* out, sv_tq_groups g, const sv_h16* x, const sv_h16* w, const sv_h16* residual, sv_u64 rows, sv_u64 cols, sv_fault* over)) \
+    D( 37, turboquant_gemv_groups_int8, (sv_h16* out, sv_tq_groups g, const sv_h16* x, sv_u64 cols, sv_fault* over)) \
+    D( 38, turboquant_gemv_groups_sum_int8, (sv_h16* out, sv_tq_groups g, const sv_h16* x, const sv_h16* w, const sv_h16* residual, sv_u64 rows, sv_u64 cols, sv_fault* over)) \
+    D( 39, swiglu_pairs, (sv_h16* o, const sv_h16* gu, sv_u64 pairs, sv_u64 n, sv_fault* over)) \
+    D( 40, expert_rows, (sv_h16* out, const sv_u8* weights, sv_u64 w_room, const sv_u8* luts, sv_u64 l_room, const sv_h16* x, const sv_u32* rows, sv_u64 count, sv_u64 d, sv_u64 out_rows, sv_u64 cols, sv_fault* over)) \
+    D( 41, expert_rows_sum, (float* acc, const sv_u8* weights, sv_u64 w_room, const sv_u8* luts, sv_u64 l_room, const sv_h16* x, const sv_u32* rows, const sv_h16* w, sv_u64 count, sv_u64 d, sv_u64 out_rows, sv_u64 cols)) \
+    D( 42, expert_groups, (sv_h16* out, sv_expert_groups g, const sv_h16* x, const sv_u32* rows, sv_u64 cols, sv_fault* over)) \
+    D( 43, expert_rows_finish, (sv_h16* out, float* acc, const sv_h16* residual, sv_u64 n, sv_fault* over)) \
+    D( 44, expert_rows_reduce, (sv_h16* out, float* acc, const sv_h16* residual, sv_u64 n, sv_u64 k, sv_u64 cols, sv_fault* over)) \
+    D( 45, rmsnorm_rows, (sv_h16* o, const sv_h16* x, const sv_h16* w, sv_u64 n, sv_u64 rows, sv_u64 x_stride, sv_u64 o_stride, float eps, sv_fault* over)) \
+    D( 46, rope_rows, (sv_h16* o, const sv_h16* x, const float* cs, sv_u64 rows, sv_u64 heads, sv_u64 head_stride, sv_u64 row_stride, sv_u64 rot, sv_fault* over)) \
+    D( 47, rope_angles_rows, (float* cs, sv_u64 first, float theta, sv_u64 head_dim, sv_u64 rows)) \
+    D( 48, rope_angles_mrope_rows, (float* cs, const sv_u32* positions, float theta, sv_u64 head_dim, sv_u64 rows, sv_u64 sections)) \
+    D( 49, rope_angles_axial_rows, (float* cs, const sv_u32* positions, float theta, sv_u64 head_dim, sv_u64 rows)) \
+    D( 50, layernorm_rows, (sv_h16* o, const sv_h16* x, const sv_h16* w, const sv_h16* b, sv_u64 n, sv_u64 rows, sv_u64 x_stride, sv_u64 o_stride, float eps, sv_fault* over)) \
+    D( 51, vector_bias_rows, (sv_h16* o, const sv_h16* x, const sv_h16* b, sv_u64 n, sv_u64 rows, sv_fault* over)) \
+    D( 52, vector_gelu, (sv_h16* o, const sv_h16* x, sv_u64 n, sv_u64 exact, sv_fault* over)) \
+    D( 53, attention_set, (sv_h16* o, const sv_h16* qkv, sv_u64 rows, sv_u64 heads, sv_u64 head_dim, sv_fault* over)) \
+    D( 54, attention_limits, (sv_h16* o, const sv_h16* q, const sv_h16* k, const sv_h16* v, const sv_u32* limits, sv_u64 rows, sv_u64 heads, sv_u64 head_dim, sv_u64 q_stride, sv_u64 kv_stride, sv_fault* over)) \
+    D( 55, vector_gated_add_rows, (sv_h16* o, const sv_h16* x, const sv_h16* y, const sv_h16* g, sv_u64 n, sv_u64 rows, sv_fault* over)) \
+    D( 56, vector_tanh, (sv_h16* o, const sv_h16* x, sv_u64 n, sv_fault* over)) \
+    D( 57, vector_silu, (sv_h16* o, const sv_h16* x, sv_u64 n, sv_fault* over)) \
+    D( 58, unfold_rows, (sv_h16* o, const sv_h16* x, sv_u64 H, sv_u64 W, sv_u64 C, sv_u64 kh, sv_u64 kw, sv_u64 stride, sv_u64 pad_top, sv_u64 pad_left, sv_u64 up, sv_u64 Wo, sv_u64 r0, sv_u64 rows)) \
+    D( 59, depth_to_space_rows, (sv_h16* o, const sv_h16* x, sv_u64 H, sv_u64 W, sv_u64 C, sv_u64 f)) \
+    D( 60, hadamard_ladder_rows, (sv_h16* out, const sv_h16* in, const sv_h16* sign, sv_u64 cols, sv_u64 rows, sv_fault* over)) \
+    D( 61, attention_causal_scores, (float* p, const sv_h16* q, const sv_h16* k, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 first, sv_u64 rows)) \
+    D( 62, attention_causal_mix, (sv_h16* o, const float* p, const sv_h16* v, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 first, sv_u64 rows, sv_fault* over)) \
+    D( 63, attention_gate_rows, (sv_h16* o, const sv_h16* att, const sv_h16* qg, sv_u64 heads, sv_u64 head_dim, sv_fault* over)) \
+    D( 64, deltanet_gates_rows, (sv_h16* beta, sv_h16* g, const sv_h16* a, const sv_h16* b, const sv_h16* a_log, const sv_h16* dt_bias, sv_u64 heads, sv_u64 rows, sv_fault* over)) \
+    D( 65, deltanet_conv_steps, (sv_h16* o, sv_h16* s, const sv_h16* w, const sv_h16* x, sv_u64 ch, sv_u64 rows, sv_fault* over)) \
+    D( 66, deltanet_steps, (float* S, const sv_h16* conved, const sv_h16* z, const sv_h16* beta, const sv_h16* g, const sv_h16* w, sv_h16* out, sv_u64 k_heads, sv_u64 v_heads, sv_u64 head_dim, sv_u64 rows, sv_fault* over)) \
+    D( 67, hadamard_blocks, (sv_h16* out, const sv_h16* in, const sv_h16* sign, sv_u64 n, sv_u64 block, sv_u64 inverse, sv_fault* over)) \
+    D( 68, turboquant_encode_rows, (sv_u8* codes, sv_h16* scales, const sv_h16* x, sv_u64 rows, sv_u64 cols, sv_u64 d, sv_fault* over)) \
+    D( 69, attention_weights_tq, (float* p, float* res, const sv_h16* q, const sv_u8* codes, const sv_h16* scales, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 length, sv_u64 d)) \
+    D( 70, attention_residual_mix_tq, (float* res, const float* p, const sv_u8* codes, const sv_h16* scales, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 length, sv_u64 d)) \
+    D( 71, hyper_logits, (float* lg, const sv_h16* streams, const sv_h16* fn, sv_u64 hidden, sv_u64 mult, float norm_eps)) \
+    D( 72, hyper_pre, (sv_h16* out, float* mix, const sv_h16* streams, const sv_h16* base, const sv_h16* scale, sv_u64 hidden, sv_u64 mult, sv_u64 iters, float eps, sv_fault* over)) \
+    D( 73, hyper_post, (sv_h16* out, const sv_h16* streams, const sv_h16* y, const float* mix, sv_u64 hidden, sv_u64 mult, sv_fault* over)) \
+    D( 74, kda_step, (float* S, const sv_h16* conved, const sv_h16* f, const sv_h16* b, const sv_h16* dt, const sv_h16* a_log, const sv_h16* gate, const sv_h16* w, sv_h16* out, sv_u64 heads, sv_u64 head_dim, float lower, float eps, sv_fault* over)) \
+    D( 75, vector_top_k_biased, (sv_u64* values, sv_u64 stride, sv_h16* weights, const sv_h16* x, const sv_h16* bias, sv_u64 n, sv_u64 k, float scale)) \
+    D( 76, swiglu_clamped, (sv_h16* act, const sv_h16* gu, sv_u64 pairs, sv_u64 n, float limit, sv_fault* over)) \
+    D( 77, attention_absorb, (sv_h16* out, const sv_h16* q, const sv_h16* W, sv_u64 heads, sv_u64 nope, sv_u64 latent, sv_u64 stride, float scale, sv_fault* over)) \
+    D( 78, attention_expand, (sv_h16* out, const sv_h16* o, const sv_h16* W, sv_u64 heads, sv_u64 width, sv_u64 latent, sv_u64 stride, sv_u64 offset, sv_fault* over)) \
+    D( 79, index_layernorm, (sv_h16* o, const sv_h16* x, const sv_h16* w, const sv_h16* b, sv_u64 n, float eps, sv_fault* over)) \
+    D( 80, index_pool, (sv_h16* pooled, const sv_h16* keys, const sv_h16* gates, const sv_h16* ape, sv_u64 first, sv_u64 pools, sv_u64 dim, sv_u64 kpool, sv_fault* over)) \
+    D( 81, index_scores, (float* scores, const sv_h16* q, const sv_h16* w, const sv_h16* pooled, sv_u64 heads, sv_u64 dim, sv_u64 pools, float scale)) \
+    D( 82, index_select, (sv_u32* index, sv_u32* count, const float* scores, sv_u64 pools, sv_u64 k, sv_u64 kpool, sv_u64 tail_first, sv_u64 tail)) \
+    D( 83, index_gather, (sv_h16* out, const sv_h16* src, const sv_u32* index, sv_u64 n, sv_u64 row)) \
+    D( 84, index_blocks, (float* out, const float* scores, sv_u64 pools, sv_u64 block)) \
+    D( 85, vector_copy, (sv_h16* out, const sv_h16* in, sv_u64 n)) \
+    D( 86, hyper_logits_rows, (float* lg, const sv_h16* streams, const sv_h16* fn, sv_u64 hidden, sv_u64 mult, float norm_eps, sv_u64 rows, sv_u64 lg_stride)) \
+    D( 87, hyper_pre_rows, (sv_h16* out, float* mix, const sv_h16* streams, const sv_h16* base, const sv_h16* scale, sv_u64 hidden, sv_u64 mult, sv_u64 iters, float eps, sv_u64 rows, sv_u64 mix_stride, sv_fault* over)) \
+    D( 88, hyper_post_rows, (sv_h16* out, const sv_h16* streams, const sv_h16* y, const float* mix, sv_u64 hidden, sv_u64 mult, sv_u64 rows, sv_u64 mix_stride, sv_fault* over)) \
+    D( 89, kda_steps, (float* S, const sv_h16* conved, const sv_h16* f, const sv_h16* b, const sv_h16* dt, const sv_h16* a_log, const sv_h16* gate, const sv_h16* w, sv_h16* out, sv_u64 heads, sv_u64 head_dim, float lower, float eps, sv_u64 rows, sv_fault* over)) \
+    D( 90, expert_groups_int8, (sv_h16* out, sv_expert_groups g, const sv_h16* x, const sv_u32* rows, sv_u64 cols, sv_fault* over)) \
+    D( 91, expert_rows_sum_int8, (float* acc, const sv_u8* weights, sv_u64 w_room, const sv_u8* luts, sv_u64 l_room, const sv_h16* x, const sv_u32* rows, const sv_h16* w, sv_u64 count, sv_u64 d, sv_u64 out_rows, sv_u64 cols)) \
+    D( 92, rank1_dots, (float* s, const sv_h16* v, const sv_u32* which, const sv_h16* x, const sv_h16* w, const sv_u32* w_at, sv_u64 n, sv_u64 cols, sv_u64 x_stride, sv_u64 w_stride)) \
+    D( 93, rank1_add, (sv_h16* out, const sv_h16* r, const float* s, sv_u64 n, sv_u64 per, sv_u64 rows, sv_u64 out_stride, sv_fault* over)) \
+    D( 94, rank1_spread, (float* acc, const sv_h16* r, const float* s, const sv_u32* row_of, sv_u64 n, sv_u64 rows, sv_u64 row_stride)) \
+    D( 95, attention_scores_grouped, (float* p, const sv_h16* q, const sv_h16* k, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 length)) \
+    D( 96, attention_softmax_rows, (float* p, sv_u64 rows, sv_u64 length)) \
+    D( 97, attention_causal_scores_grouped, (float* p, const sv_h16* q, const sv_h16* k, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 first, sv_u64 rows)) \
+    D( 98, attention_causal_softmax, (float* p, sv_u64 q_heads, sv_u64 first, sv_u64 rows)) \
+    D( 99, vector_penalize, (sv_h16* x, sv_u64 n, const sv_u64* ids, sv_u64 stride, sv_u64 count, float penalty, sv_fault* over)) \
+    D(100, vector_draw, (sv_u64* out, sv_u64 stamp, const sv_h16* w, sv_u64 k, float top_p, sv_u64 seed, sv_u64 pos)) \
+    D(101, attention_weights_rows, (float* p, float* res, const sv_h16* q, const sv_h16* k, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 first, sv_u64 rows)) \
+    D(102, attention_residual_mix_rows, (float* res, const float* p, const sv_h16* v, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 first, sv_u64 rows)) \
+    D(103, attention_weights_tq_rows, (float* p, float* res, const sv_h16* q, const sv_u8* codes, const sv_h16* scales, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 length, sv_u64 d, sv_u64 rows)) \
+    D(104, attention_residual_mix_tq_rows, (float* res, const float* p, const sv_u8* codes, const sv_h16* scales, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 length, sv_u64 d, sv_u64 rows)) \
+    D(105, vector_sum, (sv_h16* out, sv_vector_parts parts, sv_u64 n, sv_fault* over)) \
+    D(106, rope_interleaved, (sv_h16* o, const sv_h16* x, const float* cs, sv_u64 heads, sv_u64 head_stride, sv_u64 rot, sv_u64 inverse, sv_fault* over)) \
+    D(107, attention_softmax_sink, (float* p, const sv_h16* sink, sv_u64 rows, sv_u64 length)) \
+    D(108, hyper_collapse_fp32, (float* out, const float* mix, const float* streams, sv_u64 hidden, sv_u64 mult)) \
+    D(109, vector_top_k_scored, (sv_u64* values, sv_u64 stride, sv_h16* weights, const sv_h16* x, const sv_h16* bias, sv_u64 n, sv_u64 k, float scale, sv_u64 score)) \
+    D(110, engram_gate_fp32, (float* streams, const sv_h16* kv, const sv_h16* w, sv_u64 hidden, sv_u64 mult, float eps)) \
+    D(111, turboquant_gemv_groups_n, (sv_h16* out, sv_tq_groups g, const sv_h16* x, sv_u64 cols, sv_u64 n, sv_u64 out_stride, sv_fault* over)) \
+    D(112, rmsnorm_rotate, (sv_h16* rot, sv_h16* o, const sv_h16* x, const sv_h16* w, const sv_h16* sign, sv_u64 n, float eps, sv_fault* over)) \
+    D(113, hyper_logits_fp32, (float* lg, const float* streams, const sv_h16* fn, sv_u64 hidden, sv_u64 mult, float norm_eps)) \
+    D(114, hyper_pre_fp32, (float* out, float* mix, const float* streams, const sv_h16* base, const sv_h16* scale, sv_u64 hidden, sv_u64 mult, sv_u64 iters, float eps)) \
+    D(115, hyper_post_fp32, (float* out, const float* streams, const sv_h16* y, const float* mix, sv_u64 hidden, sv_u64 mult)) \
+    D(116, rmsnorm_fp32, (sv_h16* o, const float* x, const sv_h16* w, sv_u64 n, float eps, sv_fault* over)) \
+    D(117, vector_widen, (float* out, const sv_h16* x, sv_u64 n)) \
+    D(118, vector_copy_rows, (sv_h16* out, sv_u64 out_row, const sv_h16* in, sv_u64 in_row, sv_u64 width, sv_u64 rows)) \
+    D(119, expert_multiply_fp16_rows, (sv_h16* out, const sv_h16* W, const sv_h16* x, sv_u64 rows, sv_u64 cols, sv_u64 n, sv_fault* over)) \
+    D(120, vector_top_k_biased_rows, (sv_u64* values, sv_u64 stride, sv_u64 values_row, sv_h16* weights, sv_u64 weights_row, const sv_h16* x, const sv_h16* bias, sv_u64 n, sv_u64 k, float scale, sv_u64 rows)) \
+    D(121, attention_absorb_rows, (sv_h16* out, const sv_h16* q, const sv_h16* W, sv_u64 heads, sv_u64 nope, sv_u64 latent, sv_u64 stride, float scale, sv_u64 rows, sv_fault* over)) \
+    D(122, attention_expand_rows, (sv_h16* out, const sv_h16* o, const sv_h16* W, sv_u64 heads, sv_u64 width, sv_u64 latent, sv_u64 stride, sv_u64 offset, sv_u64 rows, sv_fault* over)) \
+    D(123, kda_decays, (float* eg, const sv_h16* f, const sv_h16* dt, const sv_h16* a_log, sv_u64 heads, sv_u64 head_dim, float lower, sv_u64 rows)) \
+    D(124, kda_steps_decayed, (float* S, const sv_h16* conved, const float* eg, const sv_h16* b, const sv_h16* gate, const sv_h16* w, sv_h16* out, sv_u64 heads, sv_u64 head_dim, float eps, sv_u64 rows, sv_fault* over)) \
+    D(125, index_scores_rows, (float* scores, sv_u64 scores_row, const sv_h16* q, const sv_h16* w, const sv_h16* pooled, sv_u64 heads, sv_u64 dim, sv_u64 len0, sv_u64 kpool, sv_u64 rows, float scale)) \
+    D(126, index_select_rows, (sv_u32* index, sv_u64 index_row, sv_u32* counts, const float* scores, sv_u64 scores_row, sv_u64 k, sv_u64 kpool, sv_u64 len0, sv_u64 rows)) \
+    D(127, index_gather_rows, (sv_h16* out, sv_u64 out_row, const sv_h16* src, const sv_u32* index, sv_u64 index_row, const sv_u32* counts, sv_u64 most, sv_u64 row, sv_u64 rows)) \
+    D(128, attention_scores_grouped_rows, (float* p, sv_u64 p_row, const sv_h16* q, sv_u64 q_row, const sv_h16* k, sv_u64 k_row, const sv_u32* lens, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 most, sv_u64 rows)) \
+    D(129, attention_softmax_lens, (float* p, sv_u64 p_row, const sv_u32* lens, sv_u64 heads, sv_u64 rows)) \
+    D(130, attention_mix_rows, (sv_h16* o, sv_u64 o_row, const float* p, sv_u64 p_row, const sv_h16* v, sv_u64 v_row, const sv_u32* lens, sv_u64 q_heads, sv_u64 kv_heads, sv_u64 head_dim, sv_u64 rows, sv_fault* over)) \
+    D(131, vector_top_k_rows, (sv_u64* values, sv_u64 stride, sv_u64 values_row, sv_h16* weights, sv_u64 weights_row, const sv_h16* x, sv_u64 n, sv_u64 k, sv_u64 rows)) \
+    D(132, expert_pairs_rows, (sv_u32* pairs, sv_u64 n, sv_u64 x_step, sv_u64 x_at, sv_u64 out_step, sv_u64 out_at)) \
+    D(133, deltanet_steps_gate, (float* S, const sv_h16* conved, const sv_h16* z, const sv_h16* beta, const sv_h16* g, const sv_h16* w, sv_h16* out, sv_u64 k_heads, sv_u64 v_heads, sv_u64 head_dim, sv_u64 rows, unsigned int gate, sv_fault* over)) \
+    D(134, rmsnorm_fp32_rows, (sv_h16* o, const float* x, const sv_h16* w, sv_u64 n, sv_u64 rows, sv_u64 period, float eps, sv_fault* over)) \
+    D(135, gated_rank, (sv_h16* rot, sv_h16* act, const sv_h16* a, const sv_h16* sign, sv_u64 rank, float scale, sv_fault* over)) \
+    D(136, gated_mean, (sv_h16* into, sv_h16* inj, const sv_h16* gt, const sv_h16* an, const sv_h16* ij, sv_u64 hidden, sv_u64 streams, float mean, sv_fault* over))
+
+#define SILVANN_B200_FIELD_NN(IDX, NAME, PARAMS) void (*NAME) PARAMS;
+typedef struct silvann_b200_nn_doors {
+    uint32_t size;                       /* sizeof(this) as the library was built: 1104 */
+    SILVANN_B200_NN_DOORS(SILVANN_B200_FIELD_NN)
+} silvann_b200_nn_doors;
+
+/* ---- packages 2..6: model packages whose door tables are a size word only (the ai_<model> packages, contracts/abi/gpu.cuh) */
+typedef struct silvann_b200_empty_doors { uint32_t size; } silvann_b200_empty_doors;
+
+/* ---- the family table and the one symbol the engine binds (silicon_family.cuh:48-59, entry.cuh:68-80) ------ */
+typedef struct silvann_b200_family {
+    uint32_t            abi_version;     /* 9 */
+    uint32_t            size;            /* sizeof(this) */
+    uint32_t            id;              /* SILVANN_B200_FAMILY_ID */
+    uint32_t            package_count;   /* 7 */
+    const char*         name;            /* "nvidia_b200" */
+    const void* const*  package_doors;   /* [package id] -> that package's door table */
+} silvann_b200_family;
+
+/* Answers the family table when `abi_version` is 9 and a null pointer otherwise. */
+const silvann_b200_family* silvann_silicon_family_get(uint32_t abi_version);
+
+/* ================================================================================================================
+ * Extension entry points — what the door ABI cannot say.
+ *
+ * Every function returns SILVANN_B200_OK or an error code and leaves a one-line message for
+ * silvann_b200_last_error() (per thread).  `stream` is a cudaStream_t passed as void*, null meaning the bound
+ * device's default queue.  `dtype` selects how 16-bit operands are read and results rounded.  `over` is a device
+ * fault word (may be null): a finite result that does not fit the 16-bit type ORs SILVANN_B200_FAULT_OVERFLOW there.
+ * Unless a function says otherwise it only enqueues work and does not wait for the device.
+ * ================================================================================================================ */
+#define SILVANN_B200_DTYPE_FP16 0
+#define SILVANN_B200_DTYPE_BF16 1
+
+#define SILVANN_B200_OK          0
+#define SILVANN_B200_E_ARGUMENT  1   /* a shape, size or address the kernels cannot take; nothing was enqueued */
+#define SILVANN_B200_E_CUDA      2   /* the CUDA runtime refused an allocation, copy or launch */
+#define SILVANN_B200_E_TIMEOUT   3   /* a bounded device-side wait ran out; see silvann_b200_device_status */
+#define SILVANN_B200_E_STATE     4   /* an object used before it was prepared, or after it was destroyed */
+
+/* Indexes into the counter array of silvann_b200_counters_read. */
+#define SILVANN_B200_COUNTER_FUSED_DECODE    0   /* attention_scores + attention_mix answered by one kernel */
+#define SILVANN_B200_COUNTER_FUSED_RESIDUAL  1   /* attention_weights + attention_residual_mix answered by one kernel */
+#define SILVANN_B200_COUNTER_FUSED_PREFILL   2   /* the three causal doors answered by one kernel */
+#define SILVANN_B200_COUNTER_FLUSHED         3   /* a deferred door that had to run as worded */
+#define SILVANN_B200_COUNTER_REFUSED         4   /* refused doors and refused launches */
+#define SILVANN_B200_COUNTER_DELTANET        5   /* DeltaNet door calls */
+#define SILVANN_B200_COUNTER_LAUNCHES        6   /* kernels of this library launched, all paths */
+#define SILVANN_B200_COUNTER_EXT_CALLS       7   /* silvann_b200_* compute entry points called */
+#define SILVANN_B200_COUNTERS                8
+
+const char* silvann_b200_last_error(void);
+/* Copies min(n, SILVANN_B200_COUNTERS) process-wide counters into out; reset != 0 zeroes them afterwards. */
+int silvann_b200_counters_read(uint64_t* out, uint32_t n, int reset);
+/* Waits for the bound device's default queue, then answers its status word: 0, or "B2TO" (0x4232544F) when a kernel
+ * gave up on a bounded wait.  clear != 0 zeroes the word. */
+int silvann_b200_device_status(uint32_t* word, int clear);
+
+/* Fused split-KV decode of one query position over a contiguous cache — the work of attention_scores +
+ * attention_mix (kernels.cuh:1133-1164), or of attention_weights + attention_residual_mix (:1189-1241) when `res`
+ * is given.  q [q_heads][head_dim]; k, v [length][kv_heads][head_dim]; o [q_heads][head_dim] (may be null);
+ * res [q_heads][head_dim + 2] fp32 = (m, l, acc) per head, unnormalised (may be null).  nsplit 0 lets the library
+ * choose how many blocks share a kv head.  Uses the bound device's split scratch: calls on different streams of one
+ * device must not overlap. */
+int silvann_b200_decode(void* o, float* res, const void* q, const void* k, const void* v, uint64_t q_heads,
+                        uint64_t kv_heads, uint64_t head_dim, uint64_t length, uint32_t nsplit, int dtype,
+                        sv_fault* over, void* stream);
+
+/* Two residuals into one, and a residual into 16-bit output — attention_merge / attention_finish with a dtype. */
+int silvann_b200_merge(float* into, const float* a, const float* b, uint64_t q_heads, uint64_t head_dim, void* stream);
+int silvann_b200_finish(void* o, const float* res, uint64_t q_heads, uint64_t head_dim, int dtype, sv_fault* over, void* stream);
+
+/* Batched decode over a paged KV pool.  The pool is [pages][page_positions][kv_heads][head_dim] for K and the same
+ * for V; sequence s owns pages page_table[s][0 .. ceil(len_s / page_positions)) in order.  A plan turns the host's
+ * view of the sequence lengths into a balanced device work list (and owns the split scratch), once per decoding step;
+ * every layer of that step then calls silvann_b200_paged_decode with it.  page_positions must be a multiple of 64. */
+typedef struct silvann_b200_plan silvann_b200_plan;
+int silvann_b200_plan_create(silvann_b200_plan** plan);
+int silvann_b200_plan_destroy(silvann_b200_plan* plan);
+/* seq_lens is a HOST array; the call copies what it needs before it returns (it waits for `stream` when it has to
+ * grow its buffers).  blocks_target 0 = a few waves of the device's SMs. */
+int silvann_b200_plan_decode(silvann_b200_plan* plan, const int32_t* seq_lens, uint32_t seqs, uint32_t q_heads,
+                             uint32_t kv_heads, uint32_t head_dim, uint32_t blocks_target, void* stream);
+/* What the last plan_decode produced: thread blocks, scratch slots, and the positions summed over sequences. */
+int silvann_b200_plan_info(const silvann_b200_plan* plan, uint32_t* blocks, uint32_t* slots, uint64_t* positions);
+/* q, o [seqs][q_heads][head_dim]; res [seqs][q_heads][head_dim + 2] or null; page_table is a DEVICE array
+ * [seqs][table_stride] of int32 page numbers. */
+int silvann_b200_paged_decode(silvann_b200_plan* plan, void* o, float* res, const void* q, const void* k_pool,
+                              const void* v_pool, uint64_t pool_pages, uint32_t page_positions,
+                              const int32_t* page_table, uint32_t table_stride, int dtype, sv_fault* over, void* stream);
+
+/* Causal grouped-query prefill in one kernel — attention_causal_scores_grouped + attention_causal_softmax +
+ * attention_causal_mix (kernels.cuh:1028-1081, 2051-2060): row r is position first + r and attends cache rows
+ * 0..first+r.  q, o [rows][q_heads][head_dim]; k, v [first + rows][kv_heads][head_dim]. */
+int silvann_b200_prefill(void* o, const void* q, const void* k, const void* v, uint64_t q_heads, uint64_t kv_heads,
+                         uint64_t head_dim, uint64_t first, uint64_t rows, int dtype, sv_fault* over, void* stream);
+
+/* Gated DeltaNet over `rows` positions of `seqs` independent sequences (deltanet_steps_gate, kernels.cuh:650-718,
+ * 2131-2165, with a dtype and a batch).  S [seqs][v_heads][d][d] fp32 in place; conved [seqs][rows][(2·k_heads +
+ * v_heads)·d]; z, out [seqs][rows][v_heads·d]; beta, g [seqs][rows][v_heads]; w [d]. */
+int silvann_b200_deltanet(float* S, const void* conved, const void* z, const void* beta, const void* g, const void* w,
+                          void* out, uint64_t k_heads, uint64_t v_heads, uint64_t head_dim, uint64_t rows,
+                          uint32_t seqs, uint32_t gate, int dtype, sv_fault* over, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SILVANN_B200_H */

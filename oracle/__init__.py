@@ -1,0 +1,248 @@
+"""The checker — TEST INFRASTRUCTURE, NOT PRODUCT.
+
+Two CPU witnesses of the attention / Gated-DeltaNet door arithmetic, both driven with numpy arrays:
+
+  * `port`       the plain-C restatement in silvann_oracle.c (fp16 and bf16), always available after oracle/build.py;
+  * `reference`  the reference's own CPU silicon family (x86_avx2, fp16 only), compiled unmodified from the reference
+                 tree into oracle/_ref/ where that tree is mounted; None elsewhere unless an earlier build travelled.
+
+Only tests/, __graft_entry__.smoke() and bench.py's cpu_baseline / --impl reference legs may import this package.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+FP16, BF16 = 0, 1
+
+
+# ---- 16-bit helpers (numpy has no bf16) -------------------------------------------------------------------------
+
+def to_bits(x: np.ndarray, dtype: int) -> np.ndarray:
+    """fp32 array -> uint16 bit patterns of fp16 (dtype 0) or bf16 (dtype 1), round to nearest even."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    if dtype == FP16:
+        return x.astype(np.float16).view(np.uint16)
+    u = x.view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def from_bits(b: np.ndarray, dtype: int) -> np.ndarray:
+    b = np.ascontiguousarray(b, dtype=np.uint16)
+    if dtype == FP16:
+        return b.view(np.float16).astype(np.float32)
+    return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+def fp16_exact_bf16(x: np.ndarray) -> np.ndarray:
+    """Rounds to bf16 and flushes |x| < 2^-17 to zero, so every value is exactly representable in fp16 as well: the
+    reference (fp16 only) and a bf16 kernel then see the same real numbers."""
+    y = from_bits(to_bits(x, BF16), BF16)
+    y[np.abs(y) < 2.0 ** -17] = 0.0
+    y = np.clip(y, -65504.0, 65504.0)
+    assert np.array_equal(y.astype(np.float16).astype(np.float32), y)
+    return y
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+# ---- the C restatement -------------------------------------------------------------------------------------------
+
+class Port:
+    def __init__(self):
+        so = HERE / "liboracle.so"
+        if not so.exists():
+            from . import build
+            build.build_port()
+        self.lib = C.CDLL(str(so))
+        u64, vp, i32 = C.c_uint64, C.c_void_p, C.c_int
+        sig = {
+            "oracle_attention_scores": [vp, vp, vp, u64, u64, u64, u64, i32],
+            "oracle_attention_scores_grouped": [vp, vp, vp, u64, u64, u64, u64, i32],
+            "oracle_attention_softmax_rows": [vp, u64, u64],
+            "oracle_attention_mix": [vp, vp, vp, u64, u64, u64, u64, i32, vp],
+            "oracle_attention_weights": [vp, vp, vp, vp, u64, u64, u64, u64, i32],
+            "oracle_attention_residual_mix": [vp, vp, vp, u64, u64, u64, u64, i32],
+            "oracle_attention_merge": [vp, vp, vp, u64, u64],
+            "oracle_attention_finish": [vp, vp, u64, u64, i32, vp],
+            "oracle_attention_causal_scores_grouped": [vp, vp, vp, u64, u64, u64, u64, u64, i32],
+            "oracle_attention_causal_softmax": [vp, u64, u64, u64],
+            "oracle_attention_causal_mix": [vp, vp, vp, u64, u64, u64, u64, u64, i32, vp],
+            "oracle_prefill": [vp, vp, vp, vp, vp, u64, u64, u64, u64, u64, i32, vp],
+            "oracle_deltanet_steps": [vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, C.c_uint, i32, vp],
+        }
+        for name, args in sig.items():
+            fn = getattr(self.lib, name)
+            fn.argtypes, fn.restype = args, None
+
+    # one query position ------------------------------------------------------------------------------------------
+    def scores(self, q, k, qh, kvh, d, length, dtype=FP16):
+        p = np.empty((qh, length), np.float32)
+        self.lib.oracle_attention_scores(_p(p), _p(q), _p(k), qh, kvh, d, length, dtype)
+        return p
+
+    def mix(self, p, v, qh, kvh, d, length, dtype=FP16):
+        o = np.empty((qh, d), np.uint16)
+        over = np.zeros(1, np.uint32)
+        self.lib.oracle_attention_mix(_p(o), _p(p), _p(v), qh, kvh, d, length, dtype, _p(over))
+        return o, int(over[0])
+
+    def residual(self, q, k, v, qh, kvh, d, length, dtype=FP16):
+        """(m, l, acc) per head, [qh][d + 2] fp32: attention_weights then attention_residual_mix."""
+        p = np.empty((qh, length), np.float32)
+        res = np.zeros((qh, d + 2), np.float32)
+        self.lib.oracle_attention_weights(_p(p), _p(res), _p(q), _p(k), qh, kvh, d, length, dtype)
+        self.lib.oracle_attention_residual_mix(_p(res), _p(p), _p(v), qh, kvh, d, length, dtype)
+        return res
+
+    def merge(self, a, b, qh, d):
+        out = np.empty_like(a)
+        self.lib.oracle_attention_merge(_p(out), _p(a), _p(b), qh, d)
+        return out
+
+    def finish(self, res, qh, d, dtype=FP16):
+        o = np.empty((qh, d), np.uint16)
+        over = np.zeros(1, np.uint32)
+        self.lib.oracle_attention_finish(_p(o), _p(res), qh, d, dtype, _p(over))
+        return o, int(over[0])
+
+    def decode(self, q, k, v, qh, kvh, d, length, dtype=FP16):
+        """attention_scores + attention_mix.  Answers (o bits, fp32 value before rounding)."""
+        res = self.residual(q, k, v, qh, kvh, d, length, dtype)
+        p = self.scores(q, k, qh, kvh, d, length, dtype)
+        o, _ = self.mix(p, v, qh, kvh, d, length, dtype)
+        return o, res[:, 2:] / res[:, 1:2]
+
+    # a prompt's rows -------------------------------------------------------------------------------------------
+    def causal_three_doors(self, q, k, v, qh, kvh, d, first, rows, dtype=FP16):
+        span = first + rows
+        p = np.zeros((rows * qh, span), np.float32)
+        o = np.empty((rows, qh, d), np.uint16)
+        over = np.zeros(1, np.uint32)
+        self.lib.oracle_attention_causal_scores_grouped(_p(p), _p(q), _p(k), qh, kvh, d, first, rows, dtype)
+        self.lib.oracle_attention_causal_softmax(_p(p), qh, first, rows)
+        self.lib.oracle_attention_causal_mix(_p(o), _p(p), _p(v), qh, kvh, d, first, rows, dtype, _p(over))
+        return o
+
+    def prefill(self, q, k, v, qh, kvh, d, first, rows, dtype=FP16):
+        o = np.empty((rows, qh, d), np.uint16)
+        o32 = np.empty((rows, qh, d), np.float32)
+        over = np.zeros(1, np.uint32)
+        self.lib.oracle_prefill(_p(o), _p(o32), _p(q), _p(k), _p(v), qh, kvh, d, first, rows, dtype, _p(over))
+        return o, o32
+
+    # Gated DeltaNet ------------------------------------------------------------------------------------------------
+    def deltanet(self, S, conved, z, beta, g, w, kh, vh, d, rows, gate=0, dtype=FP16):
+        """Updates S in place; answers out [rows][vh*d] bits."""
+        out = np.empty((rows, vh * d), np.uint16)
+        over = np.zeros(1, np.uint32)
+        self.lib.oracle_deltanet_steps(_p(S), _p(conved), _p(z), _p(beta), _p(g), _p(w), _p(out), kh, vh, d, rows, gate, dtype, _p(over))
+        return out
+
+
+# ---- the reference's own CPU family --------------------------------------------------------------------------------
+
+class Reference:
+    """Door calls into the reference's x86_avx2 family; a CPU family's "device" addresses are host addresses."""
+
+    def __init__(self, path: Path):
+        from silvann_b200.abi import Family
+        os.environ.setdefault("SILVANN_CPU_AVX512", "0")     # pin the AVX2 bodies so runs are comparable across hosts
+        self.family = Family(path)
+        self.nn = self.family.nn
+        self.family.sys.bind_device(0)
+        self.over = np.zeros(4, np.uint32)
+
+    def wait(self):
+        self.family.sys.compute_completed()
+
+    def scores(self, q, k, qh, kvh, d, length):
+        p = np.empty((qh, length), np.float32)
+        self.nn.attention_scores(_p(p), _p(q), _p(k), qh, kvh, d, length)
+        self.wait()
+        return p
+
+    def decode(self, q, k, v, qh, kvh, d, length, p=None):
+        p = np.empty((qh, length), np.float32) if p is None else p
+        o = np.empty((qh, d), np.uint16)
+        self.nn.attention_scores(_p(p), _p(q), _p(k), qh, kvh, d, length)
+        self.nn.attention_mix(_p(o), _p(p), _p(v), qh, kvh, d, length, _p(self.over))
+        self.wait()
+        return o
+
+    def residual(self, q, k, v, qh, kvh, d, length, p=None):
+        p = np.empty((qh, length), np.float32) if p is None else p
+        res = np.zeros((qh, d + 2), np.float32)
+        self.nn.attention_weights(_p(p), _p(res), _p(q), _p(k), qh, kvh, d, length)
+        self.nn.attention_residual_mix(_p(res), _p(p), _p(v), qh, kvh, d, length)
+        self.wait()
+        return res
+
+    def merge(self, a, b, qh, d):
+        out = np.empty_like(a)
+        self.nn.attention_merge(_p(out), _p(a), _p(b), qh, d)
+        self.wait()
+        return out
+
+    def finish(self, res, qh, d):
+        o = np.empty((qh, d), np.uint16)
+        self.nn.attention_finish(_p(o), _p(res), qh, d, _p(self.over))
+        self.wait()
+        return o
+
+    def causal(self, q, k, v, qh, kvh, d, first, rows, p=None):
+        """One chunk of rows through the three causal doors, as the runtime drives them (<= 256 rows a call)."""
+        span = first + rows
+        p = np.empty((rows * qh, span), np.float32) if p is None else p
+        o = np.empty((rows, qh, d), np.uint16)
+        self.nn.attention_causal_scores_grouped(_p(p), _p(q), _p(k), qh, kvh, d, first, rows)
+        self.nn.attention_causal_softmax(_p(p), qh, first, rows)
+        self.nn.attention_causal_mix(_p(o), _p(p), _p(v), qh, kvh, d, first, rows, _p(self.over))
+        self.wait()
+        return o
+
+    def prefill(self, q, k, v, qh, kvh, d, rows, chunk=256):
+        o = np.empty((rows, qh, d), np.uint16)
+        p = np.empty(chunk * qh * rows, np.float32)
+        for first in range(0, rows, chunk):
+            n = min(chunk, rows - first)
+            o[first:first + n] = self.causal(q[first:first + n], k, v, qh, kvh, d, first, n, p)
+        return o
+
+    def deltanet(self, S, conved, z, beta, g, w, kh, vh, d, rows, gate=0):
+        out = np.empty((rows, vh * d), np.uint16)
+        if rows == 1 and gate == 0:
+            self.nn.deltanet_step(_p(S), _p(conved), _p(z), _p(beta), _p(g), _p(w), _p(out), kh, vh, d, _p(self.over))
+        else:
+            self.nn.deltanet_steps_gate(_p(S), _p(conved), _p(z), _p(beta), _p(g), _p(w), _p(out), kh, vh, d, rows, gate, _p(self.over))
+        self.wait()
+        return out
+
+
+_port = None
+_reference = None
+_reference_tried = False
+
+
+def port() -> Port:
+    global _port
+    if _port is None:
+        _port = Port()
+    return _port
+
+
+def reference() -> Reference | None:
+    global _reference, _reference_tried
+    if not _reference_tried:
+        _reference_tried = True
+        from . import build
+        so = build.build_reference()
+        if so is not None and so.exists():
+            _reference = Reference(so)
+    return _reference

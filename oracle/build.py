@@ -1,0 +1,51 @@
+"""Builds the checker: the C restatement (liboracle.so, next to this file) and — only where the reference tree is
+mounted — the reference's own CPU silicon family, compiled from its sources where they lie, into oracle/_ref/.
+
+TEST INFRASTRUCTURE.  The reference family is built with the reference's own recipe for it (one translation unit that
+includes silicon_families/x86_avx2/unit.cuh; g++ -O3 -mavx2 -mfma -mf16c, engine/scripts/build_silicon_families.sh:
+196-201 of that tree); no reference source is copied anywhere.  oracle/_ref/ is git-ignored and still travels to a GPU
+box with the rest of the working tree, where the reference tree itself does not exist.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+import tempfile
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+PORT = HERE / "liboracle.so"
+REF_DIR = HERE / "_ref"
+REF = REF_DIR / "libsilvann_x86_avx2.so"
+REFERENCE_TREE = Path(os.environ.get("SILVANN_REFERENCE", "/root/reference"))
+
+
+def build_port(force: bool = False) -> Path:
+    src = HERE / "silvann_oracle.c"
+    if force or not PORT.exists() or PORT.stat().st_mtime < src.stat().st_mtime:
+        cmd = ["gcc", "-O2", "-mavx2", "-mfma", "-ffp-contract=off", "-fopenmp", "-fPIC", "-shared", str(src), "-lm", "-o", str(PORT)]
+        subprocess.run(cmd, check=True)
+    return PORT
+
+
+def build_reference(force: bool = False) -> Path | None:
+    """The reference CPU family, or None when its sources are not on this machine and no earlier build is present."""
+    unit = REFERENCE_TREE / "engine" / "src" / "silicon_families" / "x86_avx2" / "unit.cuh"
+    if not unit.exists():
+        return REF if REF.exists() else None
+    if REF.exists() and not force:
+        return REF
+    REF_DIR.mkdir(exist_ok=True)
+    with tempfile.TemporaryDirectory() as tmp:
+        tu = Path(tmp) / "x86_avx2.cpp"
+        tu.write_text('#include "silicon_families/x86_avx2/unit.cuh"\n')
+        cmd = ["g++", "-O3", "-mavx2", "-mfma", "-mf16c", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+               "-I", str(REFERENCE_TREE / "engine" / "src"), str(tu), "-lpthread", "-o", str(REF)]
+        subprocess.run(cmd, check=True)
+    return REF
+
+
+if __name__ == "__main__":
+    print(build_port(force="-f" in sys.argv))
+    print(build_reference(force="-f" in sys.argv))

@@ -1,0 +1,264 @@
+/* silvann_oracle.c — TEST INFRASTRUCTURE, NOT PRODUCT.  A plain-C, CPU restatement of the arithmetic of SiLVANN's
+ * attention and Gated-DeltaNet doors, used only as the checker in tests/, in __graft_entry__.smoke() and as the
+ * `cpu_baseline` of bench.py when the reference's own CPU family could not be built.  Nothing in silvann_b200/ may
+ * call it.
+ *
+ * Each function names the reference body it restates (paths under engine/src/ of the reference tree).  The loops are
+ * serial in the order the reference's one-lane host build would take; dtype 0 reads and rounds IEEE fp16 (the only
+ * type the reference has), dtype 1 reads and rounds bf16 (this library's extension).  Parity is pinned against the
+ * reference's own x86_avx2 family: tests/golden/ holds outputs of that family, produced in a container that had the
+ * reference sources, by tests/golden/make_golden.py. */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define ORACLE_FAULT_OVERFLOW 0x4E504F56u   /* packages/nn/contracts/objects/primitives.cuh:57 */
+
+/* ---- 16-bit conversions --------------------------------------------------------------------------------------- */
+
+static float f16_to_f32(uint16_t h) {                      /* packages/nn/gpu/kernels/kernels.cuh:2733-2759 */
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    const int exp = (h >> 10) & 31;
+    const uint32_t man = h & 0x3FFu;
+    if (exp == 31) { union { uint32_t u; float f; } c; c.u = sign | 0x7F800000u | (man << 13); return c.f; }
+    float v = exp == 0 ? ldexpf((float)man, -24) : ldexpf((float)(man | 0x400u), exp - 25);
+    return sign ? -v : v;
+}
+static uint16_t f32_to_f16(float f, int* over) {           /* kernels.cuh:2766-2808: RNE; a finite value that does not fit flags */
+    union { float f; uint32_t u; } c; c.f = f;
+    const uint32_t sign = (c.u >> 16) & 0x8000u, e = (c.u >> 23) & 0xFFu;
+    uint32_t m = c.u & 0x7FFFFFu;
+    if (e == 0xFFu) return (uint16_t)(sign | 0x7C00u | (m ? ((m >> 13) | 0x200u) : 0u));
+    int he = (int)e - 112;
+    if (he >= 31) { if (over) *over = 1; return (uint16_t)(sign | 0x7C00u); }
+    if (he > 0) {
+        uint32_t mh = m >> 13; const uint32_t rem = m & 0x1FFFu;
+        if (rem > 0x1000u || (rem == 0x1000u && (mh & 1u))) {
+            if (++mh == 0x400u) { mh = 0; if (++he >= 31) { if (over) *over = 1; return (uint16_t)(sign | 0x7C00u); } }
+        }
+        return (uint16_t)(sign | ((uint32_t)he << 10) | mh);
+    }
+    if (he < -10) return (uint16_t)sign;
+    m |= 0x800000u;
+    const uint32_t shift = (uint32_t)(14 - he), half = 1u << (shift - 1);
+    uint32_t mh = m >> shift; const uint32_t rem = m & ((1u << shift) - 1u);
+    if (rem > half || (rem == half && (mh & 1u))) ++mh;
+    return (uint16_t)(sign | mh);
+}
+static float bf16_to_f32(uint16_t h) { union { uint32_t u; float f; } c; c.u = (uint32_t)h << 16; return c.f; }
+static uint16_t f32_to_bf16(float f, int* over) {
+    union { float f; uint32_t u; } c; c.f = f;
+    if ((c.u & 0x7F800000u) == 0x7F800000u) return (uint16_t)((c.u >> 16) | ((c.u & 0xFFFFu) ? 0x40u : 0u));
+    const uint32_t r = c.u + 0x7FFFu + ((c.u >> 16) & 1u);
+    if ((r & 0x7F800000u) == 0x7F800000u && over) *over = 1;
+    return (uint16_t)(r >> 16);
+}
+static inline float ld16(uint16_t h, int dtype) { return dtype ? bf16_to_f32(h) : f16_to_f32(h); }
+static inline uint16_t st16(float f, int dtype, int* over) { return dtype ? f32_to_bf16(f, over) : f32_to_f16(f, over); }
+
+uint16_t oracle_f32_to_f16(float f) { return f32_to_f16(f, 0); }
+float oracle_f16_to_f32(uint16_t h) { return f16_to_f32(h); }
+uint16_t oracle_f32_to_bf16(float f) { return f32_to_bf16(f, 0); }
+
+/* ---- one query position ------------------------------------------------------------------------------------------ */
+
+/* scaled scores of one head: dot over head_dim in element order, times 1/sqrt(head_dim) (kernels.cuh:894-905) */
+static void head_scores(float* ph, const uint16_t* qh, const uint16_t* kh, uint64_t row, uint64_t d, uint64_t len, int dt) {
+    const float scale = 1.0f / sqrtf((float)d);
+    for (uint64_t t = 0; t < len; ++t) {
+        float dot = 0.0f;
+        for (uint64_t e = 0; e < d; ++e) dot += ld16(qh[e], dt) * ld16(kh[t * row + e], dt);
+        ph[t] = dot * scale;
+    }
+}
+/* in place: exp(x - max), optionally over the sum (kernels.cuh:906-914, 1085-1099) */
+static void head_softmax(float* ph, uint64_t len, int normalise, float* top_out, float* sum_out) {
+    float top = -INFINITY, sum = 0.0f;
+    for (uint64_t t = 0; t < len; ++t) if (ph[t] > top) top = ph[t];
+    for (uint64_t t = 0; t < len; ++t) { ph[t] = expf(ph[t] - top); sum += ph[t]; }
+    if (normalise) { const float inv = 1.0f / sum; for (uint64_t t = 0; t < len; ++t) ph[t] *= inv; }
+    if (top_out) *top_out = top;
+    if (sum_out) *sum_out = sum;
+}
+
+/* attention_scores: p[h][t] = softmax_t(q_h · k_{t, h/group} / sqrt(d))  (kernels.cuh:1133-1141) */
+void oracle_attention_scores(float* p, const uint16_t* q, const uint16_t* k, uint64_t qh, uint64_t kvh, uint64_t d, uint64_t len, int dt) {
+    const uint64_t group = qh / kvh, row = kvh * d;
+    for (uint64_t h = 0; h < qh; ++h) {
+        head_scores(p + h * len, q + h * d, k + (h / group) * d, row, d, len, dt);
+        head_softmax(p + h * len, len, 1, 0, 0);
+    }
+}
+/* attention_scores_grouped: the same without the softmax (kernels.cuh:931-952) */
+void oracle_attention_scores_grouped(float* p, const uint16_t* q, const uint16_t* k, uint64_t qh, uint64_t kvh, uint64_t d, uint64_t len, int dt) {
+    const uint64_t group = qh / kvh, row = kvh * d;
+    for (uint64_t h = 0; h < qh; ++h) head_scores(p + h * len, q + h * d, k + (h / group) * d, row, d, len, dt);
+}
+/* attention_softmax_rows (kernels.cuh:1085-1101) */
+void oracle_attention_softmax_rows(float* p, uint64_t rows, uint64_t len) {
+    for (uint64_t r = 0; r < rows; ++r) head_softmax(p + r * len, len, 1, 0, 0);
+}
+/* attention_mix: o[h][e] = half(sum_t p[h][t] · v[t][h/group][e]), positions in order (kernels.cuh:1144-1164) */
+void oracle_attention_mix(uint16_t* o, const float* p, const uint16_t* v, uint64_t qh, uint64_t kvh, uint64_t d, uint64_t len, int dt, unsigned* over) {
+    const uint64_t group = qh / kvh, row = kvh * d;
+    int hit = 0;
+    for (uint64_t h = 0; h < qh; ++h)
+        for (uint64_t e = 0; e < d; ++e) {
+            float sum = 0.0f;
+            for (uint64_t t = 0; t < len; ++t) sum += p[h * len + t] * ld16(v[t * row + (h / group) * d + e], dt);
+            o[h * d + e] = st16(sum, dt, &hit);
+        }
+    if (hit && over) *over = ORACLE_FAULT_OVERFLOW;
+}
+/* attention_weights: unnormalised e^(s-m) into p; m and l into res[h][0..1]  (kernels.cuh:1189-1222) */
+void oracle_attention_weights(float* p, float* res, const uint16_t* q, const uint16_t* k, uint64_t qh, uint64_t kvh, uint64_t d, uint64_t len, int dt) {
+    const uint64_t group = qh / kvh, row = kvh * d;
+    for (uint64_t h = 0; h < qh; ++h) {
+        head_scores(p + h * len, q + h * d, k + (h / group) * d, row, d, len, dt);
+        head_softmax(p + h * len, len, 0, &res[h * (d + 2)], &res[h * (d + 2) + 1]);
+    }
+}
+/* attention_residual_mix: acc into res[h][2..]  (kernels.cuh:1225-1241) */
+void oracle_attention_residual_mix(float* res, const float* p, const uint16_t* v, uint64_t qh, uint64_t kvh, uint64_t d, uint64_t len, int dt) {
+    const uint64_t group = qh / kvh, row = kvh * d;
+    for (uint64_t h = 0; h < qh; ++h)
+        for (uint64_t e = 0; e < d; ++e) {
+            float sum = 0.0f;
+            for (uint64_t t = 0; t < len; ++t) sum += p[h * len + t] * ld16(v[t * row + (h / group) * d + e], dt);
+            res[h * (d + 2) + 2 + e] = sum;
+        }
+}
+/* attention_merge: both scaled to the common maximum, then added; `into` may be a or b (kernels.cuh:1243-1255) */
+void oracle_attention_merge(float* into, const float* a, const float* b, uint64_t qh, uint64_t d) {
+    const uint64_t w = d + 2;
+    for (uint64_t h = 0; h < qh; ++h) {
+        const float ma = a[h * w], la = a[h * w + 1], mb = b[h * w], lb = b[h * w + 1];
+        const float m = ma > mb ? ma : mb, fa = expf(ma - m), fb = expf(mb - m);
+        for (uint64_t e = 0; e < d; ++e) into[h * w + 2 + e] = a[h * w + 2 + e] * fa + b[h * w + 2 + e] * fb;
+        into[h * w] = m;
+        into[h * w + 1] = la * fa + lb * fb;
+    }
+}
+/* attention_finish: half(acc / l)  (kernels.cuh:1258-1267) */
+void oracle_attention_finish(uint16_t* o, const float* res, uint64_t qh, uint64_t d, int dt, unsigned* over) {
+    const uint64_t w = d + 2;
+    int hit = 0;
+    for (uint64_t i = 0; i < qh * d; ++i) o[i] = st16(res[(i / d) * w + 2 + i % d] / res[(i / d) * w + 1], dt, &hit);
+    if (hit && over) *over = ORACLE_FAULT_OVERFLOW;
+}
+
+/* ---- a prompt's rows ------------------------------------------------------------------------------------------------ */
+
+/* attention_causal_scores_grouped: row r (position first + r), head h over cache rows 0..first+r, unnormalised, at
+ * p + (r·qh + h)·(first + rows)  (kernels.cuh:1028-1062; per-element order of nn__attention__zzprivate_dots, :975-995) */
+void oracle_attention_causal_scores_grouped(float* p, const uint16_t* q, const uint16_t* k, uint64_t qh, uint64_t kvh, uint64_t d, uint64_t first, uint64_t rows, int dt) {
+    const uint64_t group = qh / kvh, row = kvh * d, span = first + rows;
+    for (uint64_t i = 0; i < rows * qh; ++i) {
+        const uint64_t r = i / qh, h = i % qh;
+        head_scores(p + i * span, q + i * d, k + (h / group) * d, row, d, first + r + 1, dt);
+    }
+}
+/* attention_causal_softmax (kernels.cuh:1066-1081) */
+void oracle_attention_causal_softmax(float* p, uint64_t qh, uint64_t first, uint64_t rows) {
+    const uint64_t span = first + rows;
+    for (uint64_t i = 0; i < rows * qh; ++i) head_softmax(p + i * span, first + i / qh + 1, 1, 0, 0);
+}
+/* attention_causal_mix (kernels.cuh:2051-2060) */
+void oracle_attention_causal_mix(uint16_t* o, const float* p, const uint16_t* v, uint64_t qh, uint64_t kvh, uint64_t d, uint64_t first, uint64_t rows, int dt, unsigned* over) {
+    const uint64_t group = qh / kvh, row = kvh * d, span = first + rows;
+    int hit = 0;
+    for (uint64_t i = 0; i < rows * qh; ++i) {
+        const uint64_t r = i / qh, h = i % qh, len = first + r + 1;
+        for (uint64_t e = 0; e < d; ++e) {
+            float sum = 0.0f;
+            for (uint64_t t = 0; t < len; ++t) sum += p[i * span + t] * ld16(v[t * row + (h / group) * d + e], dt);
+            o[i * d + e] = st16(sum, dt, &hit);
+        }
+    }
+    if (hit && over) *over = ORACLE_FAULT_OVERFLOW;
+}
+/* The three causal doors for a run of rows without the rows·(first+rows) buffer: one row's weights at a time.  Also
+ * answers the fp32 value before rounding (o32, may be null).  Same arithmetic and order as the three above. */
+void oracle_prefill(uint16_t* o, float* o32, const uint16_t* q, const uint16_t* k, const uint16_t* v, uint64_t qh, uint64_t kvh, uint64_t d,
+                    uint64_t first, uint64_t rows, int dt, unsigned* over) {
+    const uint64_t group = qh / kvh, row = kvh * d;
+    int hit = 0;
+#pragma omp parallel for schedule(dynamic, 4) reduction(| : hit)
+    for (int64_t i = 0; i < (int64_t)(rows * qh); ++i) {
+        const uint64_t r = (uint64_t)i / qh, h = (uint64_t)i % qh, len = first + r + 1;
+        float* ph = (float*)malloc(len * sizeof(float));
+        head_scores(ph, q + (uint64_t)i * d, k + (h / group) * d, row, d, len, dt);
+        head_softmax(ph, len, 1, 0, 0);
+        for (uint64_t e = 0; e < d; ++e) {
+            float sum = 0.0f;
+            for (uint64_t t = 0; t < len; ++t) sum += ph[t] * ld16(v[t * row + (h / group) * d + e], dt);
+            int one = 0;
+            o[(uint64_t)i * d + e] = st16(sum, dt, &one);
+            hit |= one;
+            if (o32) o32[(uint64_t)i * d + e] = sum;
+        }
+        free(ph);
+    }
+    if (hit && over) *over = ORACLE_FAULT_OVERFLOW;
+}
+
+/* ---- Gated DeltaNet -------------------------------------------------------------------------------------------------- */
+
+/* One value head, one position (nn__deltanet__zzprivate_step_head, kernels.cuh:650-691). */
+static void deltanet_head(float* S, const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* z, float beta, float g,
+                          const uint16_t* w, uint16_t* out, uint64_t d, unsigned gate, int dt, int* hit) {
+    float qq = 0.0f, kk = 0.0f;
+    for (uint64_t i = 0; i < d; ++i) { const float qi = ld16(q[i], dt), ki = ld16(k[i], dt); qq += qi * qi; kk += ki * ki; }
+    const float inv_q = 1.0f / sqrtf(qq + 1e-6f) / sqrtf((float)d), inv_k = 1.0f / sqrtf(kk + 1e-6f), decay = expf(g);
+    float oo = 0.0f;
+    for (uint64_t j = 0; j < d; ++j) {
+        float kv = 0.0f;
+        for (uint64_t i = 0; i < d; ++i) kv += S[i * d + j] * ld16(k[i], dt);
+        const float delta = (ld16(v[j], dt) - decay * kv * inv_k) * beta;
+        float o = 0.0f;
+        for (uint64_t i = 0; i < d; ++i) {
+            const float s = decay * S[i * d + j] + ld16(k[i], dt) * inv_k * delta;
+            S[i * d + j] = s;
+            o += s * ld16(q[i], dt);
+        }
+        out[j] = st16(o * inv_q, dt, hit);                 /* the read-out is rounded before its norm */
+        const float oj = ld16(out[j], dt);
+        oo += oj * oj;
+    }
+    const float scale = 1.0f / sqrtf(oo / (float)d + 1e-6f);
+    for (uint64_t j = 0; j < d; ++j) {
+        const float zr = ld16(z[j], dt), zc = zr < -88.0f ? -88.0f : (zr > 88.0f ? 88.0f : zr);
+        const float gz = gate == 1u ? 1.0f / (1.0f + expf(-zc)) : zc / (1.0f + expf(-zc));
+        out[j] = st16(ld16(out[j], dt) * scale * ld16(w[j], dt) * gz, dt, hit);
+    }
+}
+/* deltanet_steps_gate (kernels.cuh:2131-2165); rows = 1 and gate = 0 is deltanet_step (:707-718).
+ * conved row = q heads, k heads, v heads; value head h reads key head h / (vh / kh). */
+void oracle_deltanet_steps(float* S, const uint16_t* conved, const uint16_t* z, const uint16_t* beta, const uint16_t* g, const uint16_t* w,
+                           uint16_t* out, uint64_t kh, uint64_t vh, uint64_t d, uint64_t rows, unsigned gate, int dt, unsigned* over) {
+    const uint64_t rep = vh / kh, ch = (2 * kh + vh) * d, vd = vh * d;
+    int hit = 0;
+#pragma omp parallel for schedule(static) reduction(| : hit)
+    for (int64_t h = 0; h < (int64_t)vh; ++h)
+        for (uint64_t t = 0; t < rows; ++t) {
+            const uint16_t* c = conved + t * ch;
+            int one = 0;
+            deltanet_head(S + (uint64_t)h * d * d, c + ((uint64_t)h / rep) * d, c + kh * d + ((uint64_t)h / rep) * d, c + 2 * kh * d + (uint64_t)h * d,
+                          z + t * vd + (uint64_t)h * d, ld16(beta[t * vh + (uint64_t)h], dt), ld16(g[t * vh + (uint64_t)h], dt), w,
+                          out + t * vd + (uint64_t)h * d, d, gate, dt, &one);
+            hit |= one;
+        }
+    if (hit && over) *over = ORACLE_FAULT_OVERFLOW;
+}
+
+/* vector_sum: parts added in the order given, one rounding (kernels.cuh:117-126) */
+void oracle_vector_sum(uint16_t* out, const uint16_t* const* parts, uint64_t count, uint64_t n, int dt, unsigned* over) {
+    int hit = 0;
+    for (uint64_t i = 0; i < n; ++i) {
+        float s = 0.0f;
+        for (uint64_t k = 0; k < count; ++k) s += ld16(parts[k][i], dt);
+        out[i] = st16(s, dt, &hit);
+    }
+    if (hit && over) *over = ORACLE_FAULT_OVERFLOW;
+}

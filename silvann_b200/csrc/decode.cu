@@ -1,0 +1,484 @@
+/* decode.cu — split-KV grouped-query decode attention for sm_100a.
+ *
+ * Replaces, in one launch, the reference's two-door decode: `attention_scores` (scores + softmax into an fp32 buffer,
+ * engine/src/packages/nn/gpu/kernels/kernels.cuh:894-915,1133-1141) followed by `attention_mix` (:1144-1164), and
+ * equally the range-residual pair `attention_weights` + `attention_residual_mix` (:1186-1241) with the split merge
+ * `attention_merge` (:1243-1255) and `attention_finish` (:1258-1267).  The fp32 weights buffer is never materialised.
+ *
+ * Shape of the work.  The cache is [position][kv_head][head_dim] 16-bit; query head h reads kv head h / group.  A
+ * block owns one kv head's slice of KV tiles (64 positions each) for up to 8 or 16 query heads of its group, streams
+ * K and V through a ring of TMA-filled shared-memory stages (128-byte swizzle, one 64-column box per 128 bytes of a
+ * row), and keeps an online softmax in registers.  Heads are the N dimension of the warp MMAs (S^T = K·Q^T and
+ * O^T = V^T·P^T), so a group of 8 heads wastes nothing and K/V bytes are read from HBM exactly once per group.
+ * One extra warp does nothing but issue TMA loads.  Partials (m, l, acc) of the splits of a group meet in scratch in
+ * the reference's residual layout; the block that arrives last (an atomic ticket, no spinning) merges them in split
+ * order — so the result does not depend on which block was last — and writes the answer.
+ *
+ * Algorithmic bytes: 2 · positions · kv_heads · head_dim · 2 per pass (K and V once); everything else is O(heads). */
+#include "common.cuh"
+#include "kernels.h"
+#include "tensormap.cuh"
+#include <stdio.h>
+
+namespace sv {
+
+static constexpr int BT = SV_DECODE_TILE;  /* positions per tile */
+static constexpr int NW = 4;               /* consumer warps; each owns 16 positions of a tile */
+
+template <int D> struct DecodeCfg {
+    static constexpr int BOXES = D / 64;                 /* 64-column (128-byte) boxes per row */
+    static constexpr int BOX_BYTES = BT * 128;
+    static constexpr int K_BYTES = BOXES * BOX_BYTES;
+    static constexpr int STAGE_BYTES = 2 * K_BYTES;      /* K then V */
+    static constexpr int STAGES = (D == 64) ? 8 : (D == 128) ? 6 : 3;
+};
+
+struct DecodeParams {
+    void* o;
+    float* res;
+    const uint16_t* q;
+    float* partials;
+    unsigned int* tickets;
+    const DecodeItem* items;
+    const int32_t* page_table;
+    const int32_t* seq_lens;
+    unsigned int* over;
+    unsigned int* status;
+    uint32_t table_stride, page_pos;
+    uint32_t q_heads, kv_heads, group;
+    uint32_t length, nsplit, head_blocks, heads_per_block;
+    uint32_t slot_floats;
+    float scale_log2;
+};
+
+template <int D, int DT, int NHT>
+__global__ void __launch_bounds__((NW + 1) * 32, 1)
+decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+              const DecodeParams P) {
+    using Cfg = DecodeCfg<D>;
+    using E = Elem<DT>;
+    constexpr int HPB = 8 * NHT;            /* heads per block */
+    constexpr int KS = D / 16;              /* k-steps of the score product = m-tiles of the value product */
+    constexpr bool QREG = !(NHT == 2 && D >= 256);
+    constexpr int Q_BYTES = Cfg::BOXES * HPB * 128;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* stage_base = smem;
+    uint8_t* q_base = smem + Cfg::STAGES * Cfg::STAGE_BYTES;
+    uint64_t* full = (uint64_t*)(q_base + Q_BYTES);
+    uint64_t* empty = full + Cfg::STAGES;
+    volatile uint32_t* abort_flag = (volatile uint32_t*)(empty + Cfg::STAGES);
+    uint32_t* ticket_s = (uint32_t*)abort_flag + 1;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    /* ---- which work is this block's ---- */
+    int seq, kvh, head0, heads, tile_begin, tile_end, split, nsplit, slot_base, slot_stride, ticket;
+    if (P.items) {
+        const DecodeItem it = P.items[blockIdx.x];
+        seq = it.seq; kvh = it.kvh; head0 = it.head0; heads = it.heads; tile_begin = it.tile_begin; tile_end = it.tile_end;
+        split = it.split; nsplit = it.nsplit; slot_base = it.slot_base; slot_stride = 1; ticket = it.ticket;
+    } else {
+        const int hb = blockIdx.x % P.head_blocks, rest = blockIdx.x / P.head_blocks;
+        kvh = rest % P.kv_heads; split = rest / P.kv_heads; nsplit = P.nsplit; seq = 0;
+        head0 = kvh * P.group + hb * P.heads_per_block;
+        heads = min((int)P.heads_per_block, (int)P.group - hb * (int)P.heads_per_block);
+        const int tiles = (P.length + BT - 1) / BT, chunk = (tiles + nsplit - 1) / nsplit;
+        tile_begin = split * chunk; tile_end = min(tiles, tile_begin + chunk);
+        slot_base = kvh * P.head_blocks + hb; slot_stride = P.kv_heads * P.head_blocks; ticket = slot_base;
+    }
+    const int len = P.seq_lens ? P.seq_lens[seq] : (int)P.length;
+    const int nt = max(tile_end - tile_begin, 0);
+
+    if (tid == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NW); }
+        *abort_flag = 0u;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    /* per-thread softmax state for the 2·NHT heads this lane's accumulator columns belong to (log2 units) */
+    float m_run[NHT][2], l_run[NHT][2];
+    float oacc[NHT][KS][4];
+#pragma unroll
+    for (int n = 0; n < NHT; ++n) {
+        m_run[n][0] = m_run[n][1] = -INFINITY; l_run[n][0] = l_run[n][1] = 0.f;
+#pragma unroll
+        for (int k = 0; k < KS; ++k) { oacc[n][k][0] = oacc[n][k][1] = oacc[n][k][2] = oacc[n][k][3] = 0.f; }
+    }
+
+    if (warp == NW) {
+        /* ---- producer: one lane issues every TMA load of this block ---- */
+        if (lane == 0 && nt > 0) {
+            tma_prefetch_desc(&kmap); tma_prefetch_desc(&vmap);
+            const uint64_t pol = l2_policy_evict_first();
+            const int32_t* pt = P.page_table ? P.page_table + (size_t)seq * P.table_stride : nullptr;
+            for (int it = 0; it < nt; ++it) {
+                const int s = it % Cfg::STAGES;
+                if (it >= Cfg::STAGES && !mbar_wait(&empty[s], ((it / Cfg::STAGES) - 1) & 1, abort_flag, P.status)) break;
+                const int pos0 = (tile_begin + it) * BT;
+                int32_t y = pos0;
+                if (pt) y = pt[pos0 / (int)P.page_pos] * (int)P.page_pos + pos0 % (int)P.page_pos;
+                uint8_t* st = stage_base + s * Cfg::STAGE_BYTES;
+                mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+#pragma unroll
+                for (int c = 0; c < Cfg::BOXES; ++c)
+                    tma_load_2d_hint(st + c * Cfg::BOX_BYTES, &kmap, &full[s], kvh * D + c * 64, y, pol);
+#pragma unroll
+                for (int c = 0; c < Cfg::BOXES; ++c)
+                    tma_load_2d_hint(st + Cfg::K_BYTES + c * Cfg::BOX_BYTES, &vmap, &full[s], kvh * D + c * 64, y, pol);
+            }
+        }
+    } else {
+        /* ---- consumers: stage the query heads (zero rows past `heads`), then walk the tiles ---- */
+        const uint16_t* qsrc = P.q + ((size_t)seq * P.q_heads + head0) * D;
+        for (int i = tid; i < HPB * (D / 8); i += NW * 32) {
+            const int r = i / (D / 8), j = i % (D / 8);
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (r < heads) val = *reinterpret_cast<const uint4*>(qsrc + (size_t)r * D + j * 8);
+            *reinterpret_cast<uint4*>(q_base + (j / 8) * (HPB * 128) + swz128(r, j % 8)) = val;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+
+        uint32_t qf[QREG ? NHT : 1][QREG ? KS : 1][2];
+        const uint32_t q_u32 = smem_u32(q_base);
+        auto load_qfrag = [&](int n, int kk, uint32_t& b0, uint32_t& b1) {
+            /* B fragment of Q^T for heads n*8..n*8+7, columns kk*16..+15: two 8x8 blocks (chunks 2kk, 2kk+1) */
+            const int chunk = 2 * kk + ((lane >> 3) & 1), row = n * 8 + (lane & 7);
+            uint32_t r0, r1, r2, r3;
+            ldsm_x4(q_u32 + (chunk / 8) * (HPB * 128) + swz128(row, chunk % 8), r0, r1, r2, r3);
+            b0 = r0; b1 = r1; (void)r2; (void)r3;
+        };
+        if (QREG) {
+#pragma unroll
+            for (int n = 0; n < NHT; ++n)
+#pragma unroll
+                for (int kk = 0; kk < KS; ++kk) load_qfrag(n, kk, qf[n][kk][0], qf[n][kk][1]);
+        }
+
+        const int r_lo = lane >> 2;                 /* accumulator row (position or value column) of c0/c1 */
+        for (int it = 0; it < nt; ++it) {
+            const int s = it % Cfg::STAGES;
+            if (!mbar_wait(&full[s], (it / Cfg::STAGES) & 1, abort_flag, P.status)) break;
+            const uint32_t kst = smem_u32(stage_base + s * Cfg::STAGE_BYTES), vst = kst + Cfg::K_BYTES;
+            const int pos0 = (tile_begin + it) * BT + warp * 16;
+
+            /* rows of V past the sequence end may hold anything (a pool page's tail): make them zero so that a
+             * zero weight times a NaN cannot reach the accumulator */
+            if (pos0 + 16 > len) {
+                for (int i = lane; i < 16 * (D / 8); i += 32) {
+                    const int r = i / (D / 8), j = i % (D / 8);
+                    if (pos0 + r >= len)
+                        *reinterpret_cast<uint4*>(stage_base + s * Cfg::STAGE_BYTES + Cfg::K_BYTES + (j / 8) * Cfg::BOX_BYTES +
+                                                  swz128(warp * 16 + r, j % 8)) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                __syncwarp();
+            }
+
+            /* S^T[16 positions][heads] = K_tile · Q^T, two interleaved accumulators per head tile */
+            float sa[NHT][4], sb[NHT][4];
+#pragma unroll
+            for (int n = 0; n < NHT; ++n) { sa[n][0] = sa[n][1] = sa[n][2] = sa[n][3] = 0.f; sb[n][0] = sb[n][1] = sb[n][2] = sb[n][3] = 0.f; }
+#pragma unroll
+            for (int kk = 0; kk < KS; ++kk) {
+                const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, chunk = 2 * kk + (lane >> 4);
+                uint32_t a0, a1, a2, a3;
+                ldsm_x4(kst + (chunk / 8) * Cfg::BOX_BYTES + swz128(row, chunk % 8), a0, a1, a2, a3);
+#pragma unroll
+                for (int n = 0; n < NHT; ++n) {
+                    uint32_t b0, b1;
+                    if (QREG) { b0 = qf[n][kk][0]; b1 = qf[n][kk][1]; } else load_qfrag(n, kk, b0, b1);
+                    if (kk & 1) mma16816<DT>(sb[n], a0, a1, a2, a3, b0, b1);
+                    else        mma16816<DT>(sa[n], a0, a1, a2, a3, b0, b1);
+                }
+            }
+
+            /* online softmax over positions (accumulator rows), per head (accumulator columns) */
+            uint32_t pb0[NHT], pb1[NHT];
+            const bool v0 = pos0 + r_lo < len, v1 = pos0 + r_lo + 8 < len;
+#pragma unroll
+            for (int n = 0; n < NHT; ++n) {
+                float t0 = v0 ? (sa[n][0] + sb[n][0]) * P.scale_log2 : -INFINITY;   /* pos r_lo,   head A */
+                float t1 = v0 ? (sa[n][1] + sb[n][1]) * P.scale_log2 : -INFINITY;   /* pos r_lo,   head B */
+                float t2 = v1 ? (sa[n][2] + sb[n][2]) * P.scale_log2 : -INFINITY;   /* pos r_lo+8, head A */
+                float t3 = v1 ? (sa[n][3] + sb[n][3]) * P.scale_log2 : -INFINITY;   /* pos r_lo+8, head B */
+                float ma = fmaxf(t0, t2), mb = fmaxf(t1, t3);
+#pragma unroll
+                for (int x = 4; x < 32; x <<= 1) {
+                    ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, x));
+                    mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, x));
+                }
+                const float na = fmaxf(m_run[n][0], ma), nb = fmaxf(m_run[n][1], mb);
+                const float ua = (na == -INFINITY) ? 0.f : na, ub = (nb == -INFINITY) ? 0.f : nb;
+                const float fa = fast_exp2(m_run[n][0] - ua), fb = fast_exp2(m_run[n][1] - ub);
+                m_run[n][0] = na; m_run[n][1] = nb;
+                const uint32_t w0 = E::pack2(fast_exp2(t0 - ua), fast_exp2(t1 - ub));
+                const uint32_t w1 = E::pack2(fast_exp2(t2 - ua), fast_exp2(t3 - ub));
+                /* the row sum uses the weights as rounded for the MMA, so weights and normaliser stay consistent */
+                const float2 f0 = E::unpack2(w0), f1 = E::unpack2(w1);
+                l_run[n][0] = l_run[n][0] * fa + f0.x + f1.x;
+                l_run[n][1] = l_run[n][1] * fb + f0.y + f1.y;
+                if (__any_sync(0xffffffffu, fa != 1.f || fb != 1.f)) {
+#pragma unroll
+                    for (int k = 0; k < KS; ++k) { oacc[n][k][0] *= fa; oacc[n][k][2] *= fa; oacc[n][k][1] *= fb; oacc[n][k][3] *= fb; }
+                }
+                pb0[n] = movm_t(w0); pb1[n] = movm_t(w1);
+            }
+
+            /* O^T[value column][head] += V_tile^T · P^T */
+#pragma unroll
+            for (int mt = 0; mt < KS; ++mt) {
+                const int j = lane >> 3, row = warp * 16 + (lane & 7) + (j >> 1) * 8, chunk = 2 * mt + (j & 1);
+                uint32_t a0, a1, a2, a3;
+                ldsm_x4_t(vst + (chunk / 8) * Cfg::BOX_BYTES + swz128(row, chunk % 8), a0, a1, a2, a3);
+#pragma unroll
+                for (int n = 0; n < NHT; ++n) mma16816<DT>(oacc[n][mt], a0, a1, a2, a3, pb0[n], pb1[n]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+        /* the lanes that share a head column hold disjoint positions: fold their sums */
+#pragma unroll
+        for (int n = 0; n < NHT; ++n)
+#pragma unroll
+            for (int x = 4; x < 32; x <<= 1) {
+                l_run[n][0] += __shfl_xor_sync(0xffffffffu, l_run[n][0], x);
+                l_run[n][1] += __shfl_xor_sync(0xffffffffu, l_run[n][1], x);
+            }
+    }
+
+    /* ---- fold the four warps' partials through shared memory (the stage ring is free now) ---- */
+    __syncthreads();
+    float* wm = (float*)stage_base;                   /* [NW][HPB] */
+    float* wl = wm + NW * HPB;                        /* [NW][HPB] */
+    float* wo = wl + NW * HPB;                        /* [NW][HPB][D] */
+    if (warp < NW) {
+        const int r_lo = lane >> 2, c2 = (lane & 3) * 2;
+#pragma unroll
+        for (int n = 0; n < NHT; ++n) {
+            const int ha = n * 8 + c2;
+            if (r_lo == 0) {
+                wm[warp * HPB + ha] = m_run[n][0]; wm[warp * HPB + ha + 1] = m_run[n][1];
+                wl[warp * HPB + ha] = l_run[n][0]; wl[warp * HPB + ha + 1] = l_run[n][1];
+            }
+#pragma unroll
+            for (int k = 0; k < KS; ++k) {
+                float* base = wo + (size_t)(warp * HPB) * D + k * 16 + r_lo;
+                base[(ha) * D] = oacc[n][k][0];
+                base[(ha + 1) * D] = oacc[n][k][1];
+                base[(ha) * D + 8] = oacc[n][k][2];
+                base[(ha + 1) * D + 8] = oacc[n][k][3];
+            }
+        }
+    }
+    __syncthreads();
+
+    const uint32_t SF = P.slot_floats;                /* floats per head in scratch: D + 2 */
+    const bool single = (nsplit == 1);
+    float* my_slot = P.partials + (size_t)(slot_base + split * slot_stride) * HPB * SF;
+    bool hit = false;
+    for (int i = tid; i < heads * D; i += (NW + 1) * 32) {
+        const int h = i / D, e = i % D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) m = fmaxf(m, wm[w * HPB + h]);
+        float acc = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float mw = wm[w * HPB + h];
+            if (mw != -INFINITY) { const float f = fast_exp2(mw - m); acc += wo[(size_t)(w * HPB + h) * D + e] * f; l += wl[w * HPB + h] * f; }
+        }
+        if (single) {
+            const size_t hq = (size_t)seq * P.q_heads + head0 + h;
+            if (P.o) ((uint16_t*)P.o)[hq * D + e] = E::from_float(acc / l, hit);
+            if (P.res) {
+                float* r = P.res + hq * (D + 2);
+                r[2 + e] = acc;
+                if (e == 0) { r[0] = m * SV_LN2; r[1] = l; }
+            }
+        } else {
+            float* r = my_slot + (size_t)h * SF;
+            r[2 + e] = acc;
+            if (e == 0) { r[0] = m; r[1] = l; }
+        }
+    }
+    if (single) {
+        if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
+        return;
+    }
+
+    /* ---- arrive; the last block of the group merges all splits in split order ---- */
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) *ticket_s = atomicAdd(&P.tickets[ticket], 1u);
+    __syncthreads();
+    if (*ticket_s != (uint32_t)(nsplit - 1)) return;
+    __threadfence();
+    for (int i = tid; i < heads * D; i += (NW + 1) * 32) {
+        const int h = i / D, e = i % D;
+        float m = -INFINITY;
+        for (int s = 0; s < nsplit; ++s)
+            m = fmaxf(m, __ldcg(P.partials + ((size_t)(slot_base + s * slot_stride) * HPB + h) * SF));
+        float acc = 0.f, l = 0.f;
+        for (int s = 0; s < nsplit; ++s) {
+            const float* r = P.partials + ((size_t)(slot_base + s * slot_stride) * HPB + h) * SF;
+            const float ms = __ldcg(r);
+            if (ms != -INFINITY) { const float f = fast_exp2(ms - m); acc += __ldcg(r + 2 + e) * f; l += __ldcg(r + 1) * f; }
+        }
+        const size_t hq = (size_t)seq * P.q_heads + head0 + h;
+        if (P.o) ((uint16_t*)P.o)[hq * D + e] = E::from_float(acc / l, hit);
+        if (P.res) {
+            float* r = P.res + hq * (D + 2);
+            r[2 + e] = acc;
+            if (e == 0) { r[0] = m * SV_LN2; r[1] = l; }
+        }
+    }
+    if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
+    if (tid == 0) P.tickets[ticket] = 0u;             /* ready for the next launch */
+}
+
+/* ---------------------------------------------------------------------------------------------------------- */
+/* host side                                                                                                    */
+
+static constexpr int DEVICES_MAX = 64;
+static DecodeScratch g_scratch[DEVICES_MAX];
+static unsigned int* g_status[DEVICES_MAX];
+static uint32_t g_sms[DEVICES_MAX];
+
+uint32_t device_sm_count() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= DEVICES_MAX) return 148u;
+    if (g_sms[d] == 0u) {
+        int n = 0;
+        g_sms[d] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) == cudaSuccess && n > 0) ? (uint32_t)n : 148u;
+    }
+    return g_sms[d];
+}
+
+unsigned int* device_status_word() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= DEVICES_MAX) return nullptr;
+    if (!g_status[d]) {
+        unsigned int* p = nullptr;
+        if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
+        if (cudaMemset(p, 0, 256) != cudaSuccess) { cudaFree(p); return nullptr; }
+        g_status[d] = p;
+    }
+    return g_status[d];
+}
+
+cudaError_t decode_device_scratch(DecodeScratch* out) {
+    int d = 0;
+    cudaError_t e = cudaGetDevice(&d);
+    if (e != cudaSuccess) return e;
+    if (d < 0 || d >= DEVICES_MAX) return cudaErrorInvalidDevice;
+    DecodeScratch& s = g_scratch[d];
+    if (!s.partials) {
+        const uint32_t slot_floats = 256 + 2;
+        const size_t bytes = (size_t)SV_DECODE_MAX_SLOTS * 16 * slot_floats * sizeof(float);
+        float* p = nullptr; unsigned int* t = nullptr;
+        if ((e = cudaMalloc(&p, bytes)) != cudaSuccess) return e;
+        if ((e = cudaMalloc(&t, SV_DECODE_MAX_TICKETS * sizeof(unsigned int))) != cudaSuccess) { cudaFree(p); return e; }
+        if ((e = cudaMemset(t, 0, SV_DECODE_MAX_TICKETS * sizeof(unsigned int))) != cudaSuccess) { cudaFree(p); cudaFree(t); return e; }
+        s.partials = p; s.tickets = t; s.slots = SV_DECODE_MAX_SLOTS; s.tickets_n = SV_DECODE_MAX_TICKETS; s.slot_floats = slot_floats;
+    }
+    *out = s;
+    return cudaSuccess;
+}
+
+static inline uint32_t heads_per_block_for(uint32_t group) { return group <= 8u ? 8u : 16u; }
+
+bool decode_fits(const DecodeCall& c) {
+    if (c.head_dim != 64 && c.head_dim != 128 && c.head_dim != 256) return false;
+    if (c.kv_heads == 0 || c.q_heads % c.kv_heads != 0) return false;
+    if (c.q_heads / c.kv_heads > 64) return false;
+    if (((uintptr_t)c.q | (uintptr_t)c.k | (uintptr_t)c.v) & 15u) return false;
+    if ((c.kv_heads * c.head_dim * 2u) % 16u != 0) return false;
+    if (c.kv_rows == 0 || c.kv_rows > 0x7FFFFFFFull) return false;
+    if (c.page_table && (c.page_pos == 0 || c.page_pos % BT != 0)) return false;
+    return encode_tiled_fn() != nullptr;
+}
+
+void decode_auto_split(uint32_t length, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim, uint32_t sms,
+                       uint32_t* nsplit, uint32_t* head_blocks) {
+    (void)head_dim;
+    const uint32_t group = q_heads / kv_heads, hpb = heads_per_block_for(group), hb = (group + hpb - 1) / hpb;
+    const uint32_t tiles = (length + BT - 1) / BT, lanes = kv_heads * hb;
+    /* one wave of blocks when the cache is short, up to four when each block still gets a long run of tiles */
+    uint32_t want = sms / lanes;
+    if (want < 1u) want = 1u;
+    if (tiles / want >= 32u) want *= 4u; else if (tiles / want >= 16u) want *= 2u;
+    uint32_t ns = want < tiles ? want : tiles;
+    if (ns < 1u) ns = 1u;
+    const uint32_t chunk = (tiles + ns - 1) / ns;
+    ns = (tiles + chunk - 1) / chunk;                       /* no empty split */
+    while (ns * lanes > SV_DECODE_MAX_SLOTS && ns > 1u) --ns;
+    *nsplit = ns; *head_blocks = hb;
+}
+
+template <int D, int DT, int NHT>
+static cudaError_t launch_one(const CUtensorMap& km, const CUtensorMap& vm, const DecodeParams& P, uint32_t blocks,
+                              cudaStream_t st) {
+    using Cfg = DecodeCfg<D>;
+    const size_t smem = 1024 + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES + Cfg::BOXES * 8 * NHT * 128 + 2 * Cfg::STAGES * 8 + 64;
+    static bool attr_set[DEVICES_MAX] = {};
+    int d = 0; cudaGetDevice(&d);
+    if (d >= 0 && d < DEVICES_MAX && !attr_set[d]) {
+        cudaError_t e = cudaFuncSetAttribute(decode_kernel<D, DT, NHT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        attr_set[d] = true;
+    }
+    decode_kernel<D, DT, NHT><<<blocks, (NW + 1) * 32, smem, st>>>(km, vm, P);
+    note_launch(1);
+    return cudaGetLastError();
+}
+
+cudaError_t decode_launch(const DecodeCall& c) {
+    const uint32_t group = c.q_heads / c.kv_heads, hpb = heads_per_block_for(group), hb = (group + hpb - 1) / hpb;
+    CUtensorMap km, vm;
+    const uint64_t cols = (uint64_t)c.kv_heads * c.head_dim, stride = cols * 2u;
+    const bool bf = c.dtype == SV_DTYPE_BF16;
+    if (!make_map_2d_sw128(&km, c.k, cols, c.kv_rows, stride, 64u, BT, bf)) return cudaErrorInvalidValue;
+    if (!make_map_2d_sw128(&vm, c.v, cols, c.kv_rows, stride, 64u, BT, bf)) return cudaErrorInvalidValue;
+
+    DecodeParams P;
+    P.o = c.o; P.res = c.res; P.q = (const uint16_t*)c.q;
+    P.partials = c.scratch.partials; P.tickets = c.scratch.tickets; P.items = c.items;
+    P.page_table = c.page_table; P.seq_lens = c.seq_lens; P.over = c.over; P.status = device_status_word();
+    P.table_stride = c.table_stride; P.page_pos = c.page_pos;
+    P.q_heads = c.q_heads; P.kv_heads = c.kv_heads; P.group = group;
+    P.length = c.length; P.head_blocks = hb; P.heads_per_block = hpb;
+    P.slot_floats = c.head_dim + 2u;
+    P.scale_log2 = (1.0f / sqrtf((float)c.head_dim)) * SV_LOG2E;
+    uint32_t blocks;
+    if (c.items) { blocks = c.n_items; P.nsplit = 0; }
+    else {
+        uint32_t ns = c.nsplit, hb2 = hb;
+        if (ns == 0) decode_auto_split(c.length, c.q_heads, c.kv_heads, c.head_dim, device_sm_count(), &ns, &hb2);
+        const uint32_t tiles = (c.length + BT - 1) / BT;
+        if (ns > tiles) ns = tiles;
+        const uint32_t chunk = (tiles + ns - 1) / ns;
+        ns = (tiles + chunk - 1) / chunk;
+        if ((uint64_t)ns * c.kv_heads * hb > c.scratch.slots || (uint64_t)c.kv_heads * hb > c.scratch.tickets_n) return cudaErrorInvalidValue;
+        P.nsplit = ns; blocks = ns * c.kv_heads * hb;
+    }
+    if (blocks == 0) return cudaSuccess;
+    if ((size_t)hpb * P.slot_floats > (size_t)16 * c.scratch.slot_floats) return cudaErrorInvalidValue;
+
+#define SV_DECODE_CASE(DD, TT, NN) return launch_one<DD, TT, NN>(km, vm, P, blocks, c.stream)
+    const int nht = hpb == 8 ? 1 : 2;
+    if (c.dtype == SV_DTYPE_FP16) {
+        if (c.head_dim == 64)  { if (nht == 1) SV_DECODE_CASE(64, SV_DTYPE_FP16, 1);  else SV_DECODE_CASE(64, SV_DTYPE_FP16, 2); }
+        if (c.head_dim == 128) { if (nht == 1) SV_DECODE_CASE(128, SV_DTYPE_FP16, 1); else SV_DECODE_CASE(128, SV_DTYPE_FP16, 2); }
+        if (c.head_dim == 256) { if (nht == 1) SV_DECODE_CASE(256, SV_DTYPE_FP16, 1); else SV_DECODE_CASE(256, SV_DTYPE_FP16, 2); }
+    } else {
+        if (c.head_dim == 64)  { if (nht == 1) SV_DECODE_CASE(64, SV_DTYPE_BF16, 1);  else SV_DECODE_CASE(64, SV_DTYPE_BF16, 2); }
+        if (c.head_dim == 128) { if (nht == 1) SV_DECODE_CASE(128, SV_DTYPE_BF16, 1); else SV_DECODE_CASE(128, SV_DTYPE_BF16, 2); }
+        if (c.head_dim == 256) { if (nht == 1) SV_DECODE_CASE(256, SV_DTYPE_BF16, 1); else SV_DECODE_CASE(256, SV_DTYPE_BF16, 2); }
+    }
+#undef SV_DECODE_CASE
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace sv

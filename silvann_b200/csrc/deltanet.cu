@@ -1,0 +1,222 @@
+/* deltanet.cu — Gated DeltaNet: the recurrent state update for one position (decode) and for a run of positions.
+ *
+ * The doors this answers: `deltanet_step`, `deltanet_steps`, `deltanet_steps_gate`
+ * (engine/src/packages/nn/contracts/abi/gpu.cuh:128,160,227); the arithmetic is the reference's
+ * nn__deltanet__zzprivate_step_head (engine/src/packages/nn/gpu/kernels/kernels.cuh:650-691): per value head h with
+ * key head h / (v_heads / k_heads), per position,
+ *     kn = k / sqrt(|k|^2 + 1e-6)      qs = q / sqrt(|q|^2 + 1e-6) / sqrt(d)      decay = exp(g)
+ *     delta = (v - decay · S^T kn) · beta            S <- decay · S + kn delta^T            o = half(S^T qs)
+ *     out = half(o · rsqrt(mean(o^2) + 1e-6) · w · gate(z))          gate = silu or sigmoid, z clamped to ±88
+ * with S[key i][value j] fp32, updated in place.
+ *
+ * Mapping.  The columns j of a head's state never interact inside the recurrence, so a head is cut into blocks of 32
+ * columns and every (sequence, head, column block) is an independent thread block: 4 blocks a head at d = 128, which
+ * puts 128 blocks on the card for one sequence of 32 heads where a block per head would light 32 SMs.  A thread owns
+ * one column's d/4 consecutive keys, keeps that slice of S in registers across all positions of the call, and the
+ * state crosses HBM exactly once in and once out.  Two block barriers a position.  The read-out's RMS norm needs the
+ * whole head, so the loop leaves the rounded read-out in `out` and each block's sum of squares in scratch; a second,
+ * elementwise kernel norms and gates.  Scratch: positions · v_heads · (d/32) floats per sequence.
+ *
+ * Algorithmic bytes a position (decode, state round trip): 2·v_heads·d²·4 + inputs (see bench). */
+#include "common.cuh"
+#include "kernels_deltanet.h"
+#include "kernels.h"
+
+namespace sv {
+
+static constexpr int DN_COLS = 32;     /* state columns per block */
+static constexpr int DN_RG = 4;        /* row groups: threads sharing a column */
+static constexpr int DN_THREADS = DN_COLS * DN_RG;
+
+struct DeltaParams {
+    float* S;
+    const uint16_t *conved, *z, *beta, *g, *w;
+    uint16_t* out;
+    float* ss;                 /* scratch [seqs][rows][v_heads][d/32] */
+    unsigned int* over;
+    uint32_t k_heads, v_heads, seqs;
+    uint64_t rows;
+    int gate;
+};
+
+template <int D, int DT>
+__global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaParams P) {
+    using E = Elem<DT>;
+    constexpr int CB = D / DN_COLS;            /* column blocks per head */
+    constexpr int R = D / DN_RG;               /* keys per thread */
+    const int tid = threadIdx.x, rg = tid / DN_COLS, c = tid % DN_COLS;
+    const int cb = blockIdx.x % CB, h = (blockIdx.x / CB) % P.v_heads, b = blockIdx.x / (CB * P.v_heads);
+    const int rep = P.v_heads / P.k_heads, kh = h / rep;
+    const int j = cb * DN_COLS + c;            /* this thread's value column */
+    const uint64_t ch = (uint64_t)(2 * P.k_heads + P.v_heads) * D, vd = (uint64_t)P.v_heads * D;
+
+    __shared__ __align__(16) float qk[2][2][D];   /* [buffer][q|k][i] as fp32 */
+    __shared__ float red1[DN_RG][DN_COLS + 2];     /* first fold, per row group: S^T k partials, then |q|^2 and |k|^2 */
+    __shared__ float red2[DN_RG][DN_COLS];         /* second fold: read-out partials */
+
+    float* Sh = P.S + ((uint64_t)b * P.v_heads + h) * D * D;
+    float s[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) s[i] = Sh[(uint64_t)(rg * R + i) * D + j];
+
+    const uint16_t* cv = P.conved + (uint64_t)b * P.rows * ch;
+    const uint16_t* bb = P.beta + (uint64_t)b * P.rows * P.v_heads;
+    const uint16_t* gg = P.g + (uint64_t)b * P.rows * P.v_heads;
+    uint16_t* oo = P.out + (uint64_t)b * P.rows * vd;
+    float* ss = P.ss + (uint64_t)b * P.rows * P.v_heads * CB;
+
+    /* stage position 0's q and k */
+    for (int i = tid; i < 2 * D; i += DN_THREADS) {
+        const int which = i / D, e = i % D;
+        qk[0][which][e] = E::to_float(cv[(which == 0 ? kh * D : (P.k_heads + kh) * D) + e]);
+    }
+    __syncthreads();
+
+    const float inv_sqrt_d = 1.0f / sqrtf((float)D);
+    bool hit = false;
+    for (uint64_t t = 0; t < P.rows; ++t) {
+        const int buf = (int)(t & 1);
+        const uint16_t* row = cv + t * ch;
+        /* this position's scalars and value, and the next position's q,k into the other buffer */
+        const float vj = E::to_float(row[(uint64_t)2 * P.k_heads * D + (uint64_t)h * D + j]);
+        const float beta = E::to_float(bb[t * P.v_heads + h]);
+        const float decay = expf(E::to_float(gg[t * P.v_heads + h]));
+        if (t + 1 < P.rows) {
+            const uint16_t* nrow = row + ch;
+            for (int i = tid; i < 2 * D; i += DN_THREADS) {
+                const int which = i / D, e = i % D;
+                qk[buf ^ 1][which][e] = E::to_float(nrow[(which == 0 ? kh * D : (P.k_heads + kh) * D) + e]);
+            }
+        }
+        const float* qv = qk[buf][0] + rg * R;
+        const float* kv_ = qk[buf][1] + rg * R;
+        float kvp = 0.f, qq = 0.f, kk = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; i += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kv_ + i);
+            const float4 q4 = *reinterpret_cast<const float4*>(qv + i);
+            kvp += s[i] * k4.x + s[i + 1] * k4.y + s[i + 2] * k4.z + s[i + 3] * k4.w;
+            kk += k4.x * k4.x + k4.y * k4.y + k4.z * k4.z + k4.w * k4.w;
+            qq += q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w;
+        }
+        red1[rg][c] = kvp;
+        if (c == 0) { red1[rg][DN_COLS] = qq; red1[rg][DN_COLS + 1] = kk; }
+        __syncthreads();
+        float kvsum = 0.f, qsum = 0.f, ksum = 0.f;
+#pragma unroll
+        for (int r = 0; r < DN_RG; ++r) { kvsum += red1[r][c]; qsum += red1[r][DN_COLS]; ksum += red1[r][DN_COLS + 1]; }
+        const float inv_k = 1.0f / sqrtf(ksum + 1e-6f);
+        const float inv_q = 1.0f / sqrtf(qsum + 1e-6f) * inv_sqrt_d;
+        const float delta = (vj - decay * kvsum * inv_k) * beta;
+        const float kd = inv_k * delta;
+        float op = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; i += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kv_ + i);
+            const float4 q4 = *reinterpret_cast<const float4*>(qv + i);
+            s[i]     = decay * s[i]     + k4.x * kd; op += s[i]     * q4.x;
+            s[i + 1] = decay * s[i + 1] + k4.y * kd; op += s[i + 1] * q4.y;
+            s[i + 2] = decay * s[i + 2] + k4.z * kd; op += s[i + 2] * q4.z;
+            s[i + 3] = decay * s[i + 3] + k4.w * kd; op += s[i + 3] * q4.w;
+        }
+        red2[rg][c] = op;
+        __syncthreads();
+        if (rg == 0) {
+            const float o = (red2[0][c] + red2[1][c] + red2[2][c] + red2[3][c]) * inv_q;
+            const uint16_t oh = E::from_float(o, hit);
+            oo[t * vd + (uint64_t)h * D + j] = oh;
+            float sq = E::to_float(oh); sq *= sq;
+            for (int x = 16; x > 0; x >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, x);
+            if (c == 0) ss[(t * P.v_heads + h) * CB + cb] = sq;
+        }
+        /* Two barriers a position are enough because the folds use separate arrays: red1 is rewritten after this
+         * position's second barrier, which follows every read of it; red2 is rewritten after the next position's first
+         * barrier, which the readers above reach only after reading; qk[buf] is rewritten by the next position's
+         * prefetch, after the second barrier that follows its last read. */
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i) Sh[(uint64_t)(rg * R + i) * D + j] = s[i];
+    if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
+}
+
+/* out <- half(out · rsqrt(mean(out^2) + 1e-6) · w · gate(z)), the head's sum of squares read from the blocks' parts. */
+template <int D, int DT>
+__global__ void __launch_bounds__(256) deltanet_norm_kernel(uint16_t* out, const float* ss, const uint16_t* z, const uint16_t* w,
+                                                            uint64_t heads_total, int gate, unsigned int* over) {
+    using E = Elem<DT>;
+    constexpr int CB = D / DN_COLS;
+    bool hit = false;
+    const uint64_t n = heads_total * D;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t hh = i / D; const int e = (int)(i % D);
+        float sum = 0.f;
+#pragma unroll
+        for (int k = 0; k < CB; ++k) sum += ss[hh * CB + k];
+        const float scale = 1.0f / sqrtf(sum / (float)D + 1e-6f);
+        const float zr = E::to_float(z[i]);
+        const float zc = zr < -88.0f ? -88.0f : (zr > 88.0f ? 88.0f : zr);
+        const float sg = 1.0f / (1.0f + expf(-zc));
+        const float gz = gate == 1 ? sg : zc * sg;
+        out[i] = E::from_float(E::to_float(out[i]) * scale * E::to_float(w[e]) * gz, hit);
+    }
+    if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
+}
+
+/* ---------------------------------------------------------------------------------------------------------- */
+
+static float* g_ss[64];
+static size_t g_ss_floats[64];
+
+static cudaError_t ss_scratch(size_t floats, float** out) {
+    int d = 0;
+    cudaError_t e = cudaGetDevice(&d);
+    if (e != cudaSuccess) return e;
+    if (d < 0 || d >= 64) return cudaErrorInvalidDevice;
+    if (g_ss_floats[d] < floats) {
+        /* grow-only; the old block is released once the queue that may still read it has drained */
+        if (g_ss[d]) { if ((e = cudaDeviceSynchronize()) != cudaSuccess) return e; cudaFree(g_ss[d]); g_ss[d] = nullptr; g_ss_floats[d] = 0; }
+        size_t want = floats < (1u << 20) ? (1u << 20) : floats;
+        if ((e = cudaMalloc(&g_ss[d], want * sizeof(float))) != cudaSuccess) return e;
+        g_ss_floats[d] = want;
+    }
+    *out = g_ss[d];
+    return cudaSuccess;
+}
+
+bool deltanet_fits(const DeltaCall& c) {
+    if (c.head_dim != 64 && c.head_dim != 128 && c.head_dim != 256) return false;
+    if (c.k_heads == 0 || c.v_heads % c.k_heads != 0) return false;
+    return ((uintptr_t)c.S & 3u) == 0;
+}
+
+template <int D, int DT>
+static cudaError_t launch_dn(const DeltaCall& c, float* ss) {
+    DeltaParams P;
+    P.S = c.S; P.conved = c.conved; P.z = c.z; P.beta = c.beta; P.g = c.g; P.w = c.w; P.out = c.out; P.ss = ss; P.over = c.over;
+    P.k_heads = c.k_heads; P.v_heads = c.v_heads; P.seqs = c.seqs; P.rows = c.rows; P.gate = c.gate;
+    const unsigned blocks = c.seqs * c.v_heads * (D / DN_COLS);
+    deltanet_steps_kernel<D, DT><<<blocks, DN_THREADS, 0, c.stream>>>(P);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    const uint64_t heads_total = (uint64_t)c.seqs * c.rows * c.v_heads;
+    /* z and out are laid out [seq][row][head][d], so one flat pass covers every sequence */
+    uint64_t nb = (heads_total * D + 255) / 256; if (nb > 148 * 16) nb = 148 * 16;
+    deltanet_norm_kernel<D, DT><<<(unsigned)nb, 256, 0, c.stream>>>(c.out, ss, c.z, c.w, heads_total, c.gate, c.over);
+    note_launch(2);
+    return cudaGetLastError();
+}
+
+cudaError_t deltanet_launch(const DeltaCall& c) {
+    if (c.rows == 0 || c.seqs == 0) return cudaSuccess;
+    float* ss = nullptr;
+    cudaError_t e = ss_scratch((size_t)c.seqs * c.rows * c.v_heads * (c.head_dim / DN_COLS), &ss);
+    if (e != cudaSuccess) return e;
+#define SV_DN(DD) (c.dtype == SV_DTYPE_BF16 ? launch_dn<DD, SV_DTYPE_BF16>(c, ss) : launch_dn<DD, SV_DTYPE_FP16>(c, ss))
+    if (c.head_dim == 64) return SV_DN(64);
+    if (c.head_dim == 128) return SV_DN(128);
+    if (c.head_dim == 256) return SV_DN(256);
+#undef SV_DN
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace sv

@@ -1,0 +1,417 @@
+/* family.cu — the silicon-family face of the library: the one exported entry, the seven door tables, the sys doors
+ * over the CUDA runtime, and the nn doors with deferred-pair fusion.
+ *
+ * What the engine expects of a family is restated in include/silvann_b200.h.  Behaviour that mirrors the reference's
+ * CUDA family (engine/src/silicon_families/nvidia_cuda12/sys.cuh, nn.cuh):
+ *   - the device a call acts on is the one the CALLING THREAD bound with bind_device; only sm_100 cards are counted;
+ *   - every door enqueues on that device's legacy default stream and returns, so memory_read / memory_write (plain
+ *     cudaMemcpy) and compute_completed order against door work exactly as they do there;
+ *   - a launch the runtime refuses is remembered per device; the next compute_completed on it answers false once.
+ *
+ * Deferred pairs.  The contract splits attention over two or three doors with an fp32 weights buffer between them.
+ * Here the first door of a pair only records its arguments (per device); when the matching second door arrives next,
+ * one fused kernel runs and the buffer is never written.  Any other door — including every sys door that could make
+ * the buffer observable — first runs the recorded door for real, so a program that reads the weights still finds
+ * them.  SILVANN_B200_FUSE=0 turns the deferral off (each door then runs as worded). */
+#include "../../include/silvann_b200.h"
+#include "common.cuh"
+#include "kernels.h"
+#include "kernels_deltanet.h"
+#include <cuda_runtime.h>
+#include <mutex>
+#include <atomic>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <fcntl.h>
+#include <unistd.h>
+
+namespace svf {
+
+static constexpr int DEVICES_MAX = 64;
+
+/* ---- counters (read through silvann_b200_counters_read) ---- */
+std::atomic<uint64_t> g_counters[SILVANN_B200_COUNTERS];
+static inline void bump(int which) { g_counters[which].fetch_add(1, std::memory_order_relaxed); }
+
+/* ---- refused launches, per device ---- */
+static volatile unsigned int g_refused[DEVICES_MAX];
+static int current_device() { int d = -1; return (cudaGetDevice(&d) == cudaSuccess) ? d : -1; }
+void launch_refused(const char* door, cudaError_t e) {
+    const int d = current_device();
+    fprintf(stderr, "silvann nvidia_b200: %s was refused on device %d: %s\n", door, d, e == cudaSuccess ? "not answered by this family" : cudaGetErrorString(e));
+    if (e != cudaSuccess) (void)cudaGetLastError();
+    if (d >= 0 && d < DEVICES_MAX) g_refused[d] = 1u;
+    bump(SILVANN_B200_COUNTER_REFUSED);
+}
+}  // namespace svf
+namespace sv { void note_launch(uint32_t kernels) { svf::g_counters[SILVANN_B200_COUNTER_LAUNCHES].fetch_add(kernels, std::memory_order_relaxed); } }
+namespace svf {
+static inline void check(const char* door, cudaError_t e) { if (e != cudaSuccess) launch_refused(door, e); }
+
+static bool fuse_enabled() {
+    static const bool on = []() { const char* v = getenv("SILVANN_B200_FUSE"); return !(v && v[0] == '0'); }();
+    return on;
+}
+
+/* ---- the deferred first door of a pair, per device ---- */
+enum PendingKind { NONE = 0, SCORES, WEIGHTS, CAUSAL_RAW, CAUSAL_SOFT };
+struct Pending {
+    int kind;
+    float* p; float* res; const uint16_t* q; const uint16_t* k;
+    uint64_t qh, kvh, d, length, first, rows;
+};
+static Pending g_pending[DEVICES_MAX];
+static std::mutex g_pending_lock[DEVICES_MAX];
+
+/* Runs the recorded door as the contract words it.  Called with the device's lock held. */
+static void run_pending_locked(Pending& pd) {
+    const Pending x = pd;
+    pd.kind = NONE;
+    switch (x.kind) {
+        case SCORES:      check("attention_scores", sv::scores_launch(x.p, x.q, x.k, x.qh, x.kvh, x.d, x.length, 0, nullptr, 0)); break;
+        case WEIGHTS:     check("attention_weights", sv::scores_launch(x.p, x.q, x.k, x.qh, x.kvh, x.d, x.length, 1, x.res, 0)); break;
+        case CAUSAL_RAW:  check("attention_causal_scores_grouped", sv::causal_scores_launch(x.p, x.q, x.k, x.qh, x.kvh, x.d, x.first, x.rows, false, 0)); break;
+        case CAUSAL_SOFT: check("attention_causal_softmax", sv::causal_scores_launch(x.p, x.q, x.k, x.qh, x.kvh, x.d, x.first, x.rows, true, 0)); break;
+        default: return;
+    }
+    bump(SILVANN_B200_COUNTER_FLUSHED);
+}
+void flush() {
+    const int d = current_device();
+    if (d < 0 || d >= DEVICES_MAX) return;
+    if (g_pending[d].kind == NONE) return;
+    std::lock_guard<std::mutex> hold(g_pending_lock[d]);
+    run_pending_locked(g_pending[d]);
+}
+
+/* ================================================================================================================ */
+/* sys doors                                                                                                        */
+
+static bool takes(int ordinal) {
+    int major = 0, minor = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, ordinal) != cudaSuccess) return false;
+    if (cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, ordinal) != cudaSuccess) return false;
+    return major == 10 && minor == 0;              /* the library carries sm_100a code only */
+}
+static int shown() { int n = 0; return (cudaGetDeviceCount(&n) == cudaSuccess && n > 0) ? n : 0; }
+static int ordinal_of(uint32_t index) {
+    uint32_t mine = 0u;
+    for (int o = 0; o < shown(); ++o) { if (!takes(o)) continue; if (mine++ == index) return o; }
+    return -1;
+}
+
+static bool s_memory_allocate(void** at, size_t bytes) {
+    size_t free_b = 0, total_b = 0;
+    if (bytes >= ((size_t)1 << 20) && cudaMemGetInfo(&free_b, &total_b) == cudaSuccess && bytes > free_b) return false;
+    return cudaMalloc(at, bytes) == cudaSuccess;
+}
+static void s_memory_free(void* at) { flush(); if (at) (void)cudaFree(at); }
+static bool s_memory_zerofill(void* at, size_t bytes) { flush(); return cudaMemset(at, 0, bytes) == cudaSuccess; }
+static bool s_memory_read(void* to, const void* from, size_t bytes) { flush(); return cudaMemcpy(to, from, bytes, cudaMemcpyDeviceToHost) == cudaSuccess; }
+static bool s_memory_write(void* to, const void* from, size_t bytes) { flush(); return cudaMemcpy(to, from, bytes, cudaMemcpyHostToDevice) == cudaSuccess; }
+static bool s_compute_completed(void) {
+    flush();
+    const bool waited = cudaStreamSynchronize(0) == cudaSuccess;
+    const int d = current_device();
+    if (d >= 0 && d < DEVICES_MAX && g_refused[d] != 0u) { g_refused[d] = 0u; return false; }
+    return waited;
+}
+static bool s_side_open(void** channel) { return cudaStreamCreateWithFlags((cudaStream_t*)channel, cudaStreamNonBlocking) == cudaSuccess; }
+static void s_side_close(void* channel) { if (channel) (void)cudaStreamDestroy((cudaStream_t)channel); }
+static bool s_side_memory_read(void* to, const void* from, size_t bytes, void* ch) {
+    return cudaMemcpyAsync(to, from, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)ch) == cudaSuccess && cudaStreamSynchronize((cudaStream_t)ch) == cudaSuccess;
+}
+static bool s_side_memory_write(void* to, const void* from, size_t bytes, void* ch) {
+    return cudaMemcpyAsync(to, from, bytes, cudaMemcpyHostToDevice, (cudaStream_t)ch) == cudaSuccess && cudaStreamSynchronize((cudaStream_t)ch) == cudaSuccess;
+}
+static bool s_memory_allocate_host_ram_mapped(void** at, void** card_at, size_t bytes) {
+    if (cudaHostAlloc(at, bytes, cudaHostAllocMapped) != cudaSuccess) return false;
+    if (cudaHostGetDevicePointer(card_at, *at, 0) == cudaSuccess) return true;
+    (void)cudaFreeHost(*at); *at = nullptr;
+    return false;
+}
+static void s_memory_free_host_ram(void* at) { if (at) (void)cudaFreeHost(at); }
+static uint32_t s_device_count(void) { uint32_t n = 0u; for (int o = 0; o < shown(); ++o) if (takes(o)) ++n; return n; }
+static uint32_t s_bind_device(uint32_t index) { const int o = ordinal_of(index); return (o >= 0 && cudaSetDevice(o) == cudaSuccess) ? 1u : 0u; }
+static uint32_t s_bound_device(void) {
+    const int d = current_device();
+    if (d < 0 || !takes(d)) return 0xFFFFFFFFu;
+    uint32_t mine = 0u;
+    for (int o = 0; o < d; ++o) if (takes(o)) ++mine;
+    return mine;
+}
+static bool s_memory_register_host(void* at, size_t bytes, void** card_at) {
+    if (cudaHostRegister(at, bytes, cudaHostRegisterMapped) != cudaSuccess) return false;
+    if (cudaHostGetDevicePointer(card_at, at, 0) == cudaSuccess) return true;
+    (void)cudaHostUnregister(at);
+    return false;
+}
+static void s_memory_unregister_host(void* at) { if (at) (void)cudaHostUnregister(at); }
+/* Files: a handle is the descriptor plus one (never zero); a read goes through a bounce buffer and memory_write,
+ * as engine/src/packages/sys/cpu/silicon/file.cuh does for every card family. */
+static bool s_file_open(const char* path, uint64_t* handle) {
+    if (!path || !handle) return false;
+    const int fd = open(path, O_RDONLY);
+    if (fd < 0) return false;
+    *handle = (uint64_t)(uint32_t)fd + 1ull;
+    return true;
+}
+static void s_file_close(uint64_t handle) { if (handle) (void)close((int)(uint32_t)handle - 1); }
+static bool s_file_read(uint64_t handle, uint64_t offset, uint64_t bytes, void* to) {
+    if (!handle || (!to && bytes)) return false;
+    const size_t piece = bytes < ((size_t)8 << 20) ? (size_t)bytes : ((size_t)8 << 20);
+    if (piece == 0) return true;
+    char* bounce = (char*)malloc(piece);
+    if (!bounce) return false;
+    bool ok = true;
+    for (uint64_t done = 0; ok && done < bytes; ) {
+        const size_t n = (size_t)(bytes - done < piece ? bytes - done : piece);
+        size_t got = 0;
+        while (ok && got < n) {
+            const ssize_t r = pread((int)(uint32_t)handle - 1, bounce + got, n - got, (off_t)(offset + done + got));
+            if (r <= 0) ok = false; else got += (size_t)r;
+        }
+        ok = ok && s_memory_write((char*)to + done, bounce, n);
+        done += n;
+    }
+    free(bounce);
+    return ok;
+}
+static bool s_memory_map_file(void*, size_t, uint64_t, uint64_t) { return false; }    /* a card's memory is not the machine's */
+static bool s_memory_prefetch(const void*, size_t) { return true; }                    /* device memory is never paged out */
+static bool s_peer_access(uint32_t other) {
+    const int here = current_device(), there = ordinal_of(other);
+    if (here < 0 || there < 0) return false;
+    if (here == there) return true;
+    int can = 0;
+    if (cudaDeviceCanAccessPeer(&can, here, there) != cudaSuccess || !can) return false;
+    const cudaError_t on = cudaDeviceEnablePeerAccess(there, 0);
+    if (on == cudaErrorPeerAccessAlreadyEnabled) { (void)cudaGetLastError(); return true; }
+    return on == cudaSuccess;
+}
+static bool s_mark_open(void** mark) { return cudaEventCreateWithFlags((cudaEvent_t*)mark, cudaEventDisableTiming) == cudaSuccess; }
+static void s_mark_close(void* mark) { if (mark) (void)cudaEventDestroy((cudaEvent_t)mark); }
+static bool s_mark_record(void* mark) { flush(); return cudaEventRecord((cudaEvent_t)mark, 0) == cudaSuccess; }
+static bool s_mark_wait(void* mark) { return cudaStreamWaitEvent(0, (cudaEvent_t)mark, 0) == cudaSuccess; }
+static bool s_side_memory_write_queued(void* to, const void* from, size_t bytes, void* ch) { return cudaMemcpyAsync(to, from, bytes, cudaMemcpyHostToDevice, (cudaStream_t)ch) == cudaSuccess; }
+static bool s_side_memory_read_queued(void* to, const void* from, size_t bytes, void* ch) { return cudaMemcpyAsync(to, from, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)ch) == cudaSuccess; }
+static bool s_side_mark_record(void* mark, void* ch) { return cudaEventRecord((cudaEvent_t)mark, (cudaStream_t)ch) == cudaSuccess; }
+static bool s_mark_reached(void* mark) { return cudaEventSynchronize((cudaEvent_t)mark) == cudaSuccess; }
+
+/* ================================================================================================================ */
+/* nn doors: first every row as a refusal, then the rows this family answers                                        */
+
+#define SVF_STUB(IDX, NAME, PARAMS) static void stub_##NAME PARAMS { flush(); launch_refused(#NAME, cudaSuccess); }
+SILVANN_B200_NN_DOORS(SVF_STUB)
+#undef SVF_STUB
+
+static sv::DecodeCall decode_call_for(const Pending& x, void* o, float* res, const uint16_t* v, unsigned int* over) {
+    sv::DecodeCall c;
+    memset(&c, 0, sizeof c);
+    c.o = o; c.res = res; c.q = x.q; c.k = x.k; c.v = v; c.kv_rows = x.length;
+    c.seqs = 1; c.q_heads = (uint32_t)x.qh; c.kv_heads = (uint32_t)x.kvh; c.head_dim = (uint32_t)x.d; c.length = (uint32_t)x.length;
+    c.dtype = SV_DTYPE_FP16; c.over = over; c.stream = 0;
+    return c;
+}
+static bool small_enough(uint64_t qh, uint64_t kvh, uint64_t d, uint64_t length) {
+    return qh && kvh && d && length && qh < (1u << 16) && kvh < (1u << 16) && d <= 1024 && length < 0x7FFFFFFFull;
+}
+
+static void d_attention_scores(float* p, const sv_h16* q, const sv_h16* k, sv_u64 qh, sv_u64 kvh, sv_u64 d, sv_u64 length) {
+    flush();
+    const int dev = current_device();
+    if (fuse_enabled() && dev >= 0 && dev < DEVICES_MAX && small_enough(qh, kvh, d, length)) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        g_pending[dev] = Pending{SCORES, p, nullptr, q, k, qh, kvh, d, length, 0, 0};
+        return;
+    }
+    check("attention_scores", sv::scores_launch(p, q, k, qh, kvh, d, length, 0, nullptr, 0));
+}
+static void d_attention_mix(sv_h16* o, const float* p, const sv_h16* v, sv_u64 qh, sv_u64 kvh, sv_u64 d, sv_u64 length, sv_fault* over) {
+    const int dev = current_device();
+    if (dev >= 0 && dev < DEVICES_MAX) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        Pending& x = g_pending[dev];
+        if (x.kind == SCORES && x.p == p && x.qh == qh && x.kvh == kvh && x.d == d && x.length == length) {
+            sv::DecodeCall c = decode_call_for(x, o, nullptr, v, over);
+            if (sv::decode_fits(c) && sv::decode_device_scratch(&c.scratch) == cudaSuccess) {
+                x.kind = NONE;
+                check("attention_scores+attention_mix", sv::decode_launch(c));
+                bump(SILVANN_B200_COUNTER_FUSED_DECODE);
+                return;
+            }
+        }
+        run_pending_locked(x);
+    }
+    check("attention_mix", sv::mix_launch(o, nullptr, p, v, qh, kvh, d, length, over, 0));
+}
+static void d_attention_weights(float* p, float* res, const sv_h16* q, const sv_h16* k, sv_u64 qh, sv_u64 kvh, sv_u64 d, sv_u64 length) {
+    flush();
+    const int dev = current_device();
+    if (fuse_enabled() && dev >= 0 && dev < DEVICES_MAX && small_enough(qh, kvh, d, length)) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        g_pending[dev] = Pending{WEIGHTS, p, res, q, k, qh, kvh, d, length, 0, 0};
+        return;
+    }
+    check("attention_weights", sv::scores_launch(p, q, k, qh, kvh, d, length, 1, res, 0));
+}
+static void d_attention_residual_mix(float* res, const float* p, const sv_h16* v, sv_u64 qh, sv_u64 kvh, sv_u64 d, sv_u64 length) {
+    const int dev = current_device();
+    if (dev >= 0 && dev < DEVICES_MAX) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        Pending& x = g_pending[dev];
+        if (x.kind == WEIGHTS && x.p == p && x.res == res && x.qh == qh && x.kvh == kvh && x.d == d && x.length == length) {
+            sv::DecodeCall c = decode_call_for(x, nullptr, res, v, nullptr);
+            if (sv::decode_fits(c) && sv::decode_device_scratch(&c.scratch) == cudaSuccess) {
+                x.kind = NONE;
+                check("attention_weights+attention_residual_mix", sv::decode_launch(c));
+                bump(SILVANN_B200_COUNTER_FUSED_RESIDUAL);
+                return;
+            }
+        }
+        run_pending_locked(x);
+    }
+    check("attention_residual_mix", sv::mix_launch(nullptr, res, p, v, qh, kvh, d, length, nullptr, 0));
+}
+static void d_attention_merge(float* into, const float* a, const float* b, sv_u64 qh, sv_u64 d) {
+    flush();
+    check("attention_merge", sv::merge_launch(into, a, b, qh, d, 0));
+}
+static void d_attention_finish(sv_h16* o, const float* res, sv_u64 qh, sv_u64 d, sv_fault* over) {
+    flush();
+    check("attention_finish", sv::finish_launch(o, res, qh, d, over, SV_DTYPE_FP16, 0));
+}
+static void d_attention_scores_grouped(float* p, const sv_h16* q, const sv_h16* k, sv_u64 qh, sv_u64 kvh, sv_u64 d, sv_u64 length) {
+    flush();
+    check("attention_scores_grouped", sv::scores_launch(p, q, k, qh, kvh, d, length, 2, nullptr, 0));
+}
+static void d_attention_softmax_rows(float* p, sv_u64 rows, sv_u64 length) {
+    flush();
+    check("attention_softmax_rows", sv::softmax_rows_launch(p, rows, length, 0));
+}
+static void d_attention_causal_scores(float* p, const sv_h16* q, const sv_h16* k, sv_u64 qh, sv_u64 kvh, sv_u64 d, sv_u64 first, sv_u64 rows) {
+    flush();
+    const int dev = current_device();
+    if (fuse_enabled() && dev >= 0 && dev < DEVICES_MAX && small_enough(qh, kvh, d, first + rows)) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        g_pending[dev] = Pending{CAUSAL_SOFT, p, nullptr, q, k, qh, kvh, d, 0, first, rows};
+        return;
+    }
+    check("attention_causal_scores", sv::causal_scores_launch(p, q, k, qh, kvh, d, first, rows, true, 0));
+}
+static void d_attention_causal_scores_grouped(float* p, const sv_h16* q, const sv_h16* k, sv_u64 qh, sv_u64 kvh, sv_u64 d, sv_u64 first, sv_u64 rows) {
+    flush();
+    const int dev = current_device();
+    if (fuse_enabled() && dev >= 0 && dev < DEVICES_MAX && small_enough(qh, kvh, d, first + rows)) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        g_pending[dev] = Pending{CAUSAL_RAW, p, nullptr, q, k, qh, kvh, d, 0, first, rows};
+        return;
+    }
+    check("attention_causal_scores_grouped", sv::causal_scores_launch(p, q, k, qh, kvh, d, first, rows, false, 0));
+}
+static void d_attention_causal_softmax(float* p, sv_u64 qh, sv_u64 first, sv_u64 rows) {
+    const int dev = current_device();
+    if (dev >= 0 && dev < DEVICES_MAX) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        Pending& x = g_pending[dev];
+        if (x.kind == CAUSAL_RAW && x.p == p && x.qh == qh && x.first == first && x.rows == rows) { x.kind = CAUSAL_SOFT; return; }
+        run_pending_locked(x);
+    }
+    check("attention_causal_softmax", sv::causal_softmax_launch(p, qh, first, rows, 0));
+}
+static void d_attention_causal_mix(sv_h16* o, const float* p, const sv_h16* v, sv_u64 qh, sv_u64 kvh, sv_u64 d, sv_u64 first, sv_u64 rows, sv_fault* over) {
+    const int dev = current_device();
+    if (dev >= 0 && dev < DEVICES_MAX) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        Pending& x = g_pending[dev];
+        if (x.kind == CAUSAL_SOFT && x.p == p && x.qh == qh && x.kvh == kvh && x.d == d && x.first == first && x.rows == rows) {
+            sv::PrefillCall c;
+            memset(&c, 0, sizeof c);
+            c.o = o; c.q = x.q; c.k = x.k; c.v = v; c.q_heads = (uint32_t)qh; c.kv_heads = (uint32_t)kvh; c.head_dim = (uint32_t)d;
+            c.first = first; c.rows = rows; c.dtype = SV_DTYPE_FP16; c.over = over; c.stream = 0;
+            if (sv::prefill_fits(c)) {
+                x.kind = NONE;
+                check("attention_causal_scores+softmax+mix", sv::prefill_launch(c));
+                bump(SILVANN_B200_COUNTER_FUSED_PREFILL);
+                return;
+            }
+        }
+        run_pending_locked(x);
+    }
+    check("attention_causal_mix", sv::causal_mix_launch(o, p, v, qh, kvh, d, first, rows, over, 0));
+}
+static void deltanet_door(const char* name, float* S, const sv_h16* conved, const sv_h16* z, const sv_h16* beta, const sv_h16* g, const sv_h16* w,
+                          sv_h16* out, sv_u64 kh, sv_u64 vh, sv_u64 d, sv_u64 rows, unsigned gate, sv_fault* over) {
+    flush();
+    sv::DeltaCall c;
+    memset(&c, 0, sizeof c);
+    c.S = S; c.conved = conved; c.z = z; c.beta = beta; c.g = g; c.w = w; c.out = out;
+    c.k_heads = (uint32_t)kh; c.v_heads = (uint32_t)vh; c.head_dim = (uint32_t)d; c.seqs = 1; c.rows = rows;
+    c.gate = (int)gate; c.dtype = SV_DTYPE_FP16; c.over = over; c.stream = 0;
+    if (!sv::deltanet_fits(c)) { launch_refused(name, cudaSuccess); return; }
+    check(name, sv::deltanet_launch(c));
+    bump(SILVANN_B200_COUNTER_DELTANET);
+}
+static void d_deltanet_step(float* S, const sv_h16* conved, const sv_h16* z, const sv_h16* beta, const sv_h16* g, const sv_h16* w, sv_h16* out,
+                            sv_u64 kh, sv_u64 vh, sv_u64 d, sv_fault* over) {
+    deltanet_door("deltanet_step", S, conved, z, beta, g, w, out, kh, vh, d, 1, SILVANN_B200_GATE_SILU, over);
+}
+static void d_deltanet_steps(float* S, const sv_h16* conved, const sv_h16* z, const sv_h16* beta, const sv_h16* g, const sv_h16* w, sv_h16* out,
+                             sv_u64 kh, sv_u64 vh, sv_u64 d, sv_u64 rows, sv_fault* over) {
+    deltanet_door("deltanet_steps", S, conved, z, beta, g, w, out, kh, vh, d, rows, SILVANN_B200_GATE_SILU, over);
+}
+static void d_deltanet_steps_gate(float* S, const sv_h16* conved, const sv_h16* z, const sv_h16* beta, const sv_h16* g, const sv_h16* w, sv_h16* out,
+                                  sv_u64 kh, sv_u64 vh, sv_u64 d, sv_u64 rows, unsigned int gate, sv_fault* over) {
+    deltanet_door("deltanet_steps_gate", S, conved, z, beta, g, w, out, kh, vh, d, rows, gate, over);
+}
+static void d_vector_sum(sv_h16* out, sv_vector_parts parts, sv_u64 n, sv_fault* over) {
+    flush();
+    check("vector_sum", sv::vector_sum_launch(out, parts.at, parts.count, n, over, 0));
+}
+
+/* ================================================================================================================ */
+/* tables and the entry                                                                                             */
+
+#define SVF_SYS_FILL(IDX, RET, NAME, PARAMS) s_##NAME,
+static silvann_b200_sys_doors g_sys = {(uint32_t)sizeof(silvann_b200_sys_doors), SILVANN_B200_SYS_DOORS(SVF_SYS_FILL)};
+#undef SVF_SYS_FILL
+#define SVF_NN_FILL(IDX, NAME, PARAMS) stub_##NAME,
+static silvann_b200_nn_doors g_nn = {(uint32_t)sizeof(silvann_b200_nn_doors), SILVANN_B200_NN_DOORS(SVF_NN_FILL)};
+#undef SVF_NN_FILL
+static const silvann_b200_empty_doors g_empty = {(uint32_t)sizeof(silvann_b200_empty_doors)};
+static const void* const g_packages[SILVANN_B200_PACKAGES] = {&g_sys, &g_nn, &g_empty, &g_empty, &g_empty, &g_empty, &g_empty};
+static const silvann_b200_family g_family = {SILVANN_B200_ABI_VERSION, (uint32_t)sizeof(silvann_b200_family), SILVANN_B200_FAMILY_ID,
+                                             SILVANN_B200_PACKAGES, SILVANN_B200_FAMILY_NAME, g_packages};
+
+static void install_doors() {
+    g_nn.attention_scores = d_attention_scores;
+    g_nn.attention_mix = d_attention_mix;
+    g_nn.attention_weights = d_attention_weights;
+    g_nn.attention_residual_mix = d_attention_residual_mix;
+    g_nn.attention_merge = d_attention_merge;
+    g_nn.attention_finish = d_attention_finish;
+    g_nn.attention_scores_grouped = d_attention_scores_grouped;
+    g_nn.attention_softmax_rows = d_attention_softmax_rows;
+    g_nn.attention_causal_scores = d_attention_causal_scores;
+    g_nn.attention_causal_scores_grouped = d_attention_causal_scores_grouped;
+    g_nn.attention_causal_softmax = d_attention_causal_softmax;
+    g_nn.attention_causal_mix = d_attention_causal_mix;
+    g_nn.deltanet_step = d_deltanet_step;
+    g_nn.deltanet_steps = d_deltanet_steps;
+    g_nn.deltanet_steps_gate = d_deltanet_steps_gate;
+    g_nn.vector_sum = d_vector_sum;
+}
+
+}  // namespace svf
+
+static_assert(sizeof(silvann_b200_sys_doors) == 256, "sys door table must be 4 + 31 pointers, padded: 256 bytes");
+static_assert(sizeof(silvann_b200_nn_doors) == 1104, "nn door table must be 4 + 137 pointers, padded: 1104 bytes");
+static_assert(sizeof(sv_tq_groups) == 488 && sizeof(sv_expert_groups) == 680 && sizeof(sv_vector_parts) == 72, "by-value door structs");
+
+extern "C" __attribute__((visibility("default")))
+const silvann_b200_family* silvann_silicon_family_get(uint32_t abi_version) {
+    static std::once_flag once;
+    std::call_once(once, svf::install_doors);
+    return abi_version == SILVANN_B200_ABI_VERSION ? &svf::g_family : nullptr;
+}

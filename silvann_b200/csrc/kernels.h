@@ -1,0 +1,100 @@
+/* kernels.h — host-side launchers of this library's kernels; the doors (family.cu) and the `silvann_b200_*`
+ * entry points (ext.cu) are thin callers of these.  Every launcher validates nothing the caller has not already
+ * validated except what only it can know (kernel fit), enqueues on the given stream and returns the runtime's error.
+ * None of them synchronises the device. */
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sv {
+
+/* ---- split-KV decode (decode.cu) ------------------------------------------------------------------------ */
+
+/* One unit of decode work: query heads [head0, head0+heads) of sequence `seq`, all sharing kv head `kvh`, over KV
+ * tiles [tile_begin, tile_end) of 64 positions.  Split `split` of `nsplit` for that (seq, head block); the partial
+ * of split s is written to scratch slot `slot_base + s`, and `ticket` indexes the arrival counter of the group. */
+struct DecodeItem {
+    int32_t seq, kvh, head0, heads;
+    int32_t tile_begin, tile_end, split, nsplit;
+    int32_t slot_base, ticket, pad0, pad1;
+};
+
+#define SV_DECODE_TILE 64          /* positions per KV tile */
+#define SV_DECODE_MAX_SLOTS 2048   /* scratch partial slots per device (per plan) */
+#define SV_DECODE_MAX_TICKETS 8192
+
+struct DecodeScratch {
+    float* partials;        /* [slots][16][head_dim_max + 2] fp32 */
+    unsigned int* tickets;  /* zero between launches: the last block of a group resets its ticket */
+    uint32_t slots, tickets_n, slot_floats;
+};
+
+struct DecodeCall {
+    void* o;                 /* [seqs][q_heads][head_dim] 16-bit, or null */
+    float* res;              /* [seqs][q_heads][head_dim + 2] fp32 (m, l, acc), or null */
+    const void* q;           /* [seqs][q_heads][head_dim] 16-bit */
+    const void* k;           /* contiguous: [length][kv_heads][head_dim]; paged: pool [pages][page_pos][kv_heads][head_dim] */
+    const void* v;
+    uint64_t kv_rows;        /* rows the K/V maps span: length (contiguous) or pages * page_pos (paged) */
+    const int32_t* page_table;  /* device [seqs][table_stride], or null for a contiguous cache */
+    uint32_t table_stride, page_pos;
+    const int32_t* seq_lens;    /* device [seqs] (paged), or null: every sequence is `length` long */
+    const DecodeItem* items;    /* device work list, `n_items` long, or null for one sequence split evenly */
+    uint32_t n_items;
+    uint32_t seqs, q_heads, kv_heads, head_dim, length;
+    uint32_t nsplit;            /* with items == null: 0 = choose */
+    int dtype;                  /* SV_DTYPE_* */
+    unsigned int* over;         /* device fault word or null */
+    DecodeScratch scratch;
+    cudaStream_t stream;
+};
+
+/* Whether the TMA kernel can take these shapes and addresses (head_dim 64/128/256, 16-byte aligned q/k/v, rows a
+ * multiple of 16 bytes, whole query groups of at most 64 heads on a kv head). */
+bool decode_fits(const DecodeCall& c);
+/* Blocks the launch will use and scratch slots it needs, for a one-sequence call with items == null. */
+void decode_auto_split(uint32_t length, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim, uint32_t sms,
+                       uint32_t* nsplit, uint32_t* head_blocks);
+cudaError_t decode_launch(const DecodeCall& c);
+/* Per-device scratch for calls that bring none (the doors): allocated once on first use, kept until exit. */
+cudaError_t decode_device_scratch(DecodeScratch* out);
+uint32_t device_sm_count();
+void note_launch(uint32_t kernels);    /* adds to the library's launch counter (family.cu) */
+unsigned int* device_status_word();   /* device address of the bound device's status word (allocated on first use) */
+
+/* ---- contract-faithful attention doors, any shape (attn_doors.cu) ------------------------------------------- */
+cudaError_t scores_launch(float* p, const uint16_t* q, const uint16_t* k, uint64_t qh, uint64_t kvh, uint64_t d,
+                          uint64_t length, int mode /*0 softmax, 1 weights+res, 2 raw grouped*/, float* res,
+                          cudaStream_t st);
+cudaError_t softmax_rows_launch(float* p, uint64_t rows, uint64_t length, cudaStream_t st);
+cudaError_t mix_launch(uint16_t* o, float* res, const float* p, const uint16_t* v, uint64_t qh, uint64_t kvh,
+                       uint64_t d, uint64_t length, unsigned int* over, cudaStream_t st);
+cudaError_t merge_launch(float* into, const float* a, const float* b, uint64_t qh, uint64_t d, cudaStream_t st);
+cudaError_t finish_launch(uint16_t* o, const float* res, uint64_t qh, uint64_t d, unsigned int* over, int dtype,
+                          cudaStream_t st);
+cudaError_t causal_scores_launch(float* p, const uint16_t* q, const uint16_t* k, uint64_t qh, uint64_t kvh, uint64_t d,
+                                 uint64_t first, uint64_t rows, bool softmax, cudaStream_t st);
+cudaError_t causal_softmax_launch(float* p, uint64_t qh, uint64_t first, uint64_t rows, cudaStream_t st);
+cudaError_t causal_mix_launch(uint16_t* o, const float* p, const uint16_t* v, uint64_t qh, uint64_t kvh, uint64_t d,
+                              uint64_t first, uint64_t rows, unsigned int* over, cudaStream_t st);
+cudaError_t vector_sum_launch(uint16_t* out, const uint64_t* parts, uint64_t count, uint64_t n, unsigned int* over,
+                              cudaStream_t st);
+
+}  // namespace sv
+
+/* ---- causal GQA prefill on tcgen05 / TMEM (prefill.cu) ------------------------------------------------------- */
+namespace sv {
+struct PrefillCall {
+    void* o;                  /* [rows][q_heads][head_dim] 16-bit */
+    const void* q;            /* [rows][q_heads][head_dim] */
+    const void* k;            /* [first + rows][kv_heads][head_dim] */
+    const void* v;
+    uint32_t q_heads, kv_heads, head_dim;
+    uint64_t first, rows;     /* row r is position first + r and attends cache rows 0..first+r */
+    int dtype;
+    unsigned int* over;
+    cudaStream_t stream;
+};
+bool prefill_fits(const PrefillCall& c);
+cudaError_t prefill_launch(const PrefillCall& c);
+}  // namespace sv
