@@ -1,0 +1,480 @@
+#!/usr/bin/env python
+"""bench.py — the decode-attention benchmark of the B200 attention silicon family.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+           bench.py --gpus N --steps K --warmup W
+
+Headline (one JSON line on rank 0): `decode attn KV GB/s` on BASELINE configuration 3 — batched paged decode of 32
+sequences with lengths uniform in [1,024, 100,000], 16 query heads on 2 kv heads, head_dim 256, bf16, 256-position
+pages in a randomly permuted pool, int32 page table.  A step is one pass of the fused paged-decode kernel over the
+whole batch.  Each GPU holds its own batch (sequences are independent: no collective on the data path), so N GPUs
+process N batches: weak scaling.
+
+  value        all ranks' KV bytes per step / the slowest rank's device time per step (CUDA events), inputs resident
+  e2e          the same metric with, inside every timed step, the host-side plan, the upload of the step's inputs
+               (queries and each sequence's newest K/V row, from pinned host memory through the family's memory_write
+               door) and the read-back of the outputs (memory_read door)
+  roofline     algorithmic KV bytes per launch / mean launch duration, against the measured HBM copy bandwidth
+  cpu_baseline the reference's own CPU family (oracle/_ref) on this host's cores, on a stated sample of the workload
+  others       the remaining configurations (1, 2, 4, 5), each with its own roofline fraction, single GPU
+
+The KV pool of a step is 3.3 GB, far larger than the 126 MB L2, so no L2 flush is needed between iterations.
+Synthetic data: pools are filled on the device with seeded N(0,1) values (there is no dataset for this path).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC, UNIT = "decode attn KV GB/s", "GB/s"
+WORKLOAD = "config3: batched paged decode, 32 seqs U[1024,100000], 16q/2kv heads, head_dim 256, bf16, 256-pos pages"
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while a timed region runs."""
+    REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
+               0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.stop_flag, self.max_mhz = [], set(), threading.Event(), None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+        self.thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                mask = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(self.nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit and name != "gpu_idle":
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.05)
+
+    def __enter__(self):
+        if self.nv:
+            self.thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self.stop_flag.set()
+        if self.nv:
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unsampled"]}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def device_index() -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except Exception:
+            return local
+    return local
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------------------------------
+
+def time_loop(torch, fn, steps, warmup):
+    """Mean milliseconds per call of fn over `steps` calls after `warmup`, CUDA events on the current (default) stream."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+class PagedWorkload:
+    """Configuration 3 resident on the current device."""
+
+    def __init__(self, torch, seed_shift=0):
+        from silvann_b200 import ext, workloads
+        self.torch, self.ext = torch, ext
+        L = self.layout = workloads.config3_layout()
+        self.seqs = len(L.seq_lens)
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(1003 + seed_shift)
+        shape = (L.pool_pages, workloads.PAGE_POSITIONS, L.kv_heads, L.head_dim)
+        self.k_pool = torch.randn(shape, generator=gen, device="cuda", dtype=torch.bfloat16)
+        self.v_pool = torch.randn(shape, generator=gen, device="cuda", dtype=torch.bfloat16)
+        self.q = torch.randn((self.seqs, L.q_heads, L.head_dim), generator=gen, device="cuda", dtype=torch.bfloat16)
+        self.table = torch.from_numpy(np.maximum(L.page_table, 0)).cuda()
+        self.out = torch.zeros((self.seqs, L.q_heads, L.head_dim), device="cuda", dtype=torch.bfloat16)
+        self.plan = ext.Plan()
+        self.plan.plan(L.seq_lens, L.q_heads, L.kv_heads, L.head_dim)
+        self.page_positions = workloads.PAGE_POSITIONS
+        self.kv_bytes = L.kv_bytes
+
+    def step(self):
+        L = self.layout
+        self.plan.decode(self.out, None, self.q, self.k_pool, self.v_pool, L.pool_pages, self.page_positions, self.table,
+                         L.page_table.shape[1], self.ext.BF16)
+
+
+class EndToEnd:
+    """A decoding step as a caller with host buffers sees it: plan, upload this step's inputs, decode, read back."""
+
+    def __init__(self, torch, wl: PagedWorkload, fam):
+        import ctypes as C
+        self.C, self.wl, self.fam, self.torch = C, wl, fam, torch
+        L = wl.layout
+        row = L.kv_heads * L.head_dim
+        self.q_bytes = wl.seqs * L.q_heads * L.head_dim * 2
+        self.row_bytes = row * 2
+        self.o_bytes = self.q_bytes
+        n = self.q_bytes + 2 * wl.seqs * self.row_bytes + self.o_bytes
+        host, card = C.c_void_p(), C.c_void_p()
+        assert fam.sys.memory_allocate_host_ram_mapped(C.byref(host), C.byref(card), n), "pinned host buffer"
+        self.host = host
+        buf = np.ctypeslib.as_array(C.cast(host, C.POINTER(C.c_uint16)), shape=(n // 2,))
+        rng = np.random.default_rng(3)
+        buf[:] = (rng.standard_normal(n // 2).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+        self.h_q = host.value
+        self.h_rows = host.value + self.q_bytes
+        self.h_out = self.h_rows + 2 * wl.seqs * self.row_bytes
+        self.rows_dev = torch.zeros((2, wl.seqs, row), device="cuda", dtype=torch.bfloat16)
+        self.h2d = self.q_bytes + 2 * wl.seqs * self.row_bytes
+        self.d2h = self.o_bytes
+
+    def step(self):
+        wl, sysd, L = self.wl, self.fam.sys, self.wl.layout
+        wl.plan.plan(L.seq_lens, L.q_heads, L.kv_heads, L.head_dim)
+        sysd.memory_write(wl.q.data_ptr(), self.h_q, self.q_bytes)
+        sysd.memory_write(self.rows_dev.data_ptr(), self.h_rows, 2 * wl.seqs * self.row_bytes)
+        wl.plan.append(wl.k_pool, wl.v_pool, self.rows_dev[0], self.rows_dev[1], wl.page_positions, wl.table, L.page_table.shape[1])
+        wl.step()
+        sysd.memory_read(self.h_out, wl.out.data_ptr(), self.o_bytes)
+
+    def close(self):
+        self.fam.sys.memory_free_host_ram(self.host)
+
+
+def cpu_baseline_paged(wl: PagedWorkload, budget_s=20.0):
+    """The reference's CPU family over a bounded sample of configuration 3: whole sequences, gathered from the pools
+    to the contiguous planes its doors take, attention_scores + attention_mix each.  Answers (GB/s, cores, sample)."""
+    import oracle
+    R = oracle.reference()
+    kind = "reference" if R is not None else "port"
+    P = None if R is not None else oracle.port()
+    L = wl.layout
+    torch = wl.torch
+    order = np.argsort(L.seq_lens)[::-1]
+    picked, positions = [], 0
+    for s in order[:8]:
+        picked.append(int(s)); positions += int(L.seq_lens[s])
+        if kind == "port" and positions > 20000:
+            break
+    planes = []
+    for s in picked:
+        n = int(L.seq_lens[s])
+        pages = torch.from_numpy(L.page_table[s, :(n + wl.page_positions - 1) // wl.page_positions].astype(np.int64)).cuda()
+        ks = wl.k_pool[pages].reshape(-1, L.kv_heads, L.head_dim)[:n].to(torch.float16).cpu().numpy().view(np.uint16)
+        vs = wl.v_pool[pages].reshape(-1, L.kv_heads, L.head_dim)[:n].to(torch.float16).cpu().numpy().view(np.uint16)
+        qs = wl.q[s].to(torch.float16).cpu().numpy().view(np.uint16)
+        planes.append((qs, ks, vs, n))
+    pbuf = np.empty(L.q_heads * int(L.seq_lens.max()), np.float32)
+    best, t_all = None, time.time()
+    for _ in range(5):
+        t0 = time.perf_counter()
+        for qs, ks, vs, n in planes:
+            if R is not None:
+                R.decode(qs, ks, vs, L.q_heads, L.kv_heads, L.head_dim, n, pbuf[:L.q_heads * n].reshape(L.q_heads, n))
+            else:
+                P.decode(qs, ks, vs, L.q_heads, L.kv_heads, L.head_dim, n, 0)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+        if time.time() - t_all > budget_s:
+            break
+    nbytes = positions * 2 * L.kv_heads * L.head_dim * 2
+    cores = (os.cpu_count() or 1) if R is not None else 1
+    return {"value": nbytes / best / 1e9, "unit": UNIT, "cores": cores, "kind": kind,
+            "sample": f"{len(picked)} longest sequences of the batch ({positions} positions, {nbytes / 1e6:.0f} MB of KV), fp16 copies, best of <=5 passes; SILVANN_CPU_AVX512=0"}
+
+
+def other_workloads(torch, fam, pk, steps, warmup):
+    """Configurations 1, 4 and 5 (and 2 when the prefill kernel fits), each timed alone on one GPU."""
+    from silvann_b200 import ext, workloads
+    out = {}
+    hbm = pk["hbm_gbs"]
+    gen = torch.Generator(device="cuda"); gen.manual_seed(77)
+
+    # configuration 1 through the two doors, cycling 64 distinct caches (1.07 GB) so that nothing stays in L2
+    qh, kvh, d, L = 16, 4, 128, 8192
+    copies = 64
+    k = torch.randn((copies, L, kvh, d), generator=gen, device="cuda", dtype=torch.float16)
+    v = torch.randn((copies, L, kvh, d), generator=gen, device="cuda", dtype=torch.float16)
+    q = torch.randn((qh, d), generator=gen, device="cuda", dtype=torch.float16)
+    p = torch.zeros((qh, L), device="cuda", dtype=torch.float32)
+    o = torch.zeros((qh, d), device="cuda", dtype=torch.float16)
+    state = {"i": 0}
+
+    def door_pair():
+        i = state["i"] = (state["i"] + 1) % copies
+        fam.nn.attention_scores(p.data_ptr(), q.data_ptr(), k[i].data_ptr(), qh, kvh, d, L)
+        fam.nn.attention_mix(o.data_ptr(), p.data_ptr(), v[i].data_ptr(), qh, kvh, d, L, None)
+    ms = time_loop(torch, door_pair, max(steps * 20, 200), max(warmup * 5, 20))
+    nbytes = 2 * L * kvh * d * 2
+    out["config1_decode_doors"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms, "frac_hbm": nbytes / ms / 1e6 / hbm,
+                                   "note": "attention_scores+attention_mix door pair, fp16, 16.8 MB of KV a call, 64 caches cycled"}
+    del k, v
+
+    # configuration 4 on one GPU, everything in HBM (537 MB a pass)
+    qh, kvh, d, L = 32, 4, 128, 262144
+    k = torch.randn((L, kvh, d), generator=gen, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn((L, kvh, d), generator=gen, device="cuda", dtype=torch.bfloat16)
+    q = torch.randn((qh, d), generator=gen, device="cuda", dtype=torch.bfloat16)
+    o = torch.zeros((qh, d), device="cuda", dtype=torch.bfloat16)
+    ms = time_loop(torch, lambda: ext.decode(o, None, q, k, v, qh, kvh, d, L, ext.BF16), max(steps, 20), max(warmup, 3))
+    nbytes = 2 * L * kvh * d * 2
+    out["config4_long_context_1gpu_resident"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms, "frac_hbm": nbytes / ms / 1e6 / hbm,
+                                                 "note": "262,144 positions, 32q/4kv, d128, bf16, all KV in HBM"}
+    del k, v
+
+    # configuration 5: recurrent decode steps (batched so that state traffic is real) and the prompt
+    heads, d = 32, 128
+    for seqs, tag in ((1, "config5_deltanet_decode_1seq"), (64, "config5_deltanet_decode_64seq")):
+        S = torch.zeros((seqs, heads, d, d), device="cuda", dtype=torch.float32)
+        conved = torch.randn((seqs, 1, 3 * heads * d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.1
+        z = torch.randn((seqs, 1, heads * d), generator=gen, device="cuda", dtype=torch.bfloat16)
+        beta = torch.rand((seqs, 1, heads), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        g = (-torch.rand((seqs, 1, heads), generator=gen, device="cuda", dtype=torch.float32)).to(torch.bfloat16)
+        w = torch.ones(d, device="cuda", dtype=torch.bfloat16)
+        o = torch.zeros((seqs, 1, heads * d), device="cuda", dtype=torch.bfloat16)
+        ms = time_loop(torch, lambda: ext.deltanet(S, conved, z, beta, g, w, o, heads, heads, d, 1, seqs, 0, ext.BF16), max(steps * 10, 100), 10)
+        nbytes = seqs * (2 * heads * d * d * 4 + 3 * heads * d * 2 + 2 * heads * d * 2 + 2 * heads * 2 + d * 2)
+        out[tag] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_step": ms, "frac_hbm": nbytes / ms / 1e6 / hbm,
+                    "note": f"{seqs} sequence(s) x 32 heads x 128x128 fp32 state, read and written once a step"
+                            + (" (2 MiB of state: stays in L2 between steps)" if seqs == 1 else "")}
+    T = 8192
+    S = torch.zeros((1, heads, d, d), device="cuda", dtype=torch.float32)
+    conved = torch.randn((T, 3 * heads * d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.1
+    z = torch.randn((T, heads * d), generator=gen, device="cuda", dtype=torch.bfloat16)
+    beta = torch.rand((T, heads), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    g = (-torch.rand((T, heads), generator=gen, device="cuda", dtype=torch.float32)).to(torch.bfloat16)
+    o = torch.zeros((T, heads * d), device="cuda", dtype=torch.bfloat16)
+    ms = time_loop(torch, lambda: ext.deltanet(S, conved, z, beta, g, w, o, heads, heads, d, T, 1, 0, ext.BF16), 3, 1)
+    nbytes = T * (3 * heads * d * 2 + 2 * heads * d * 2 + 4 * heads) + 2 * heads * d * d * 4
+    out["config5_deltanet_prefill_8192"] = {"value": T / ms * 1e3, "unit": "positions/s", "ms": ms, "frac_hbm": nbytes / ms / 1e6 / hbm,
+                                            "tflops": 7.0 * d * d * heads * T / ms / 1e9,
+                                            "note": "one sequence, 8,192 positions, recurrence walked position by position"}
+
+    # configuration 2: causal prefill
+    qh, kvh, d, T = 16, 2, 256, 4096
+    q = torch.randn((T, qh, d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.5
+    k = torch.randn((T, kvh, d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.5
+    v = torch.randn((T, kvh, d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.5
+    o = torch.zeros((T, qh, d), device="cuda", dtype=torch.bfloat16)
+    try:
+        ms = time_loop(torch, lambda: ext.prefill(o, q, k, v, qh, kvh, d, 0, T, ext.BF16), max(steps, 20), max(warmup, 3))
+        flops = 4.0 * qh * d * T * (T + 1) / 2
+        out["config2_causal_prefill"] = {"value": flops / ms / 1e9, "unit": "TFLOP/s", "ms_per_call": ms, "frac_bf16_burst": flops / ms / 1e9 / pk["bf16_tflops"],
+                                         "note": "4,096 rows, 16q/2kv, d256, bf16, one fused kernel"}
+    except ext.B200Error as e:
+        out["config2_causal_prefill"] = {"value": None, "unit": "TFLOP/s", "note": f"fused prefill not available: {e}"}
+    return out
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this library has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import silvann_b200
+    from silvann_b200 import ext
+    fam = silvann_b200.family()
+    assert fam.sys.bind_device(local) == 1, "the family does not take this device (needs sm_100)"
+    pk = peaks()
+
+    wl = PagedWorkload(torch, seed_shift=rank)
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- value: K steps, inputs resident ----
+    for _ in range(warmup):
+        wl.step()
+    barrier()
+    c0 = ext.counters()["launches"]
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    with ClockSampler(device_index()) as clocks:
+        barrier()
+        ev[0].record()
+        for i in range(steps):
+            wl.step()
+            ev[i + 1].record()
+        barrier()
+    launches = ext.counters()["launches"] - c0
+    total_ms = ev[0].elapsed_time(ev[steps])
+    per_launch_ms = float(np.mean([ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]))
+    t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / steps
+    status = ext.device_status()
+
+    # ---- e2e: host buffers, copies inside the timed region ----
+    e2e = EndToEnd(torch, wl, fam)
+    for _ in range(2):
+        e2e.step()
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    e_steps = max(3, min(steps, 20))
+    t0.record()
+    for _ in range(e_steps):
+        e2e.step()
+    t1.record()
+    barrier()
+    te = torch.tensor([t0.elapsed_time(t1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ms = float(te.item()) / e_steps
+
+    kv_all = wl.kv_bytes * world
+    line = {
+        "metric": METRIC, "value": kv_all / ms_step / 1e6, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "positions_per_gpu": wl.layout.positions, "kv_bytes_per_gpu_step": wl.kv_bytes,
+                   "l2": "inputs (3.3 GB a step) larger than L2; no flush needed", "sharding": "one independent batch per GPU, no collective"},
+        "e2e": {"value": kv_all / e2e_ms / 1e6, "unit": UNIT, "h2d_bytes_per_step": e2e.h2d, "d2h_bytes_per_step": e2e.d2h, "ms_per_step": e2e_ms,
+                "note": "plan + upload of queries and each sequence's newest K/V row (pinned host memory, memory_write door) + row append into the pool + decode + memory_read of outputs; the KV pool is the path's resident state"},
+        "gpu_launches": int(launches),
+        "clocks": clocks.summary(),
+        "device_status": status,
+    }
+    if rank == 0:
+        achieved = wl.kv_bytes / per_launch_ms / 1e6
+        line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+                            "traffic": TRAFFIC_BYTES_PER_LAUNCH, "peak_source": pk["source"], "kernel": "sv::decode_kernel<256, bf16, 1>",
+                            "algorithmic_bytes_per_launch": wl.kv_bytes}
+        if world == 1:
+            line["cpu_baseline"] = cpu_baseline_paged(wl)
+            if not args.no_others:
+                line["others"] = other_workloads(torch, fam, pk, steps, warmup)
+    e2e.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the ncu capture summarised
+# under profiles/ (scaled to a full launch by positions); None until a capture exists.
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# reference arm: the reference's own CPU implementation of the path on this host's cores
+# ---------------------------------------------------------------------------------------------------------------------
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    from silvann_b200 import workloads
+    R = oracle.reference()
+    kind = "reference" if R is not None else "port"
+    P = None if R is not None else oracle.port()
+    L = workloads.config3_layout()
+    order = np.argsort(L.seq_lens)[::-1][: (8 if R is not None else 1)]
+    rng = np.random.default_rng(1003)
+    planes, positions = [], 0
+    for s in order:
+        n = int(L.seq_lens[s]) if R is not None else 4096
+        positions += n
+        mk = lambda shape: rng.standard_normal(shape, dtype=np.float32).astype(np.float16).view(np.uint16)
+        planes.append((mk((L.q_heads, L.head_dim)), mk((n, L.kv_heads, L.head_dim)), mk((n, L.kv_heads, L.head_dim)), n))
+    pbuf = np.empty(L.q_heads * max(p[3] for p in planes), np.float32)
+
+    def step():
+        for qs, ks, vs, n in planes:
+            if R is not None:
+                R.decode(qs, ks, vs, L.q_heads, L.kv_heads, L.head_dim, n, pbuf[:L.q_heads * n].reshape(L.q_heads, n))
+            else:
+                P.decode(qs, ks, vs, L.q_heads, L.kv_heads, L.head_dim, n, 0)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    ms = (time.perf_counter() - t0) * 1e3 / steps
+    nbytes = positions * 2 * L.kv_heads * L.head_dim * 2
+    cores = (os.cpu_count() or 1) if R is not None else 1
+    value = nbytes / ms / 1e6
+    sample = f"{len(planes)} sequences of the batch ({positions} positions, {nbytes / 1e6:.0f} MB of KV a step), fp16, attention_scores + attention_mix per sequence on the host's cores"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps, "warmup": warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate over fp16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-others", action="store_true", help="skip the secondary configurations (faster; used under profilers)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

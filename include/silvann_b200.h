@@ -328,6 +328,13 @@ int silvann_b200_paged_decode(silvann_b200_plan* plan, void* o, float* res, cons
                               const void* v_pool, uint64_t pool_pages, uint32_t page_positions,
                               const int32_t* page_table, uint32_t table_stride, int dtype, sv_fault* over, void* stream);
 
+/* Writes each sequence's newest K and V row into its place in the pools: sequence s's row goes to position
+ * len_s - 1 (the lengths of the last plan_decode), i.e. page page_table[s][(len_s-1) / page_positions].  k_rows and
+ * v_rows are DEVICE arrays [seqs][kv_heads][head_dim] of 16-bit elements.  This is the pool-side half of what the
+ * engine's mixer does when it projects k and v "straight into the cache row" (ai_qwen_3 mixer__abi.cuh:229-239). */
+int silvann_b200_paged_append(silvann_b200_plan* plan, void* k_pool, void* v_pool, const void* k_rows, const void* v_rows,
+                              uint32_t page_positions, const int32_t* page_table, uint32_t table_stride, void* stream);
+
 /* Causal grouped-query prefill in one kernel — attention_causal_scores_grouped + attention_causal_softmax +
  * attention_causal_mix (kernels.cuh:1028-1081, 2051-2060): row r is position first + r and attends cache rows
  * 0..first+r.  q, o [rows][q_heads][head_dim]; k, v [first + rows][kv_heads][head_dim]. */

@@ -258,6 +258,34 @@ SV_EXPORT int silvann_b200_paged_decode(silvann_b200_plan* p, void* o, float* re
     return e == cudaSuccess ? SILVANN_B200_OK : cuda_fail("paged_decode: launch", e);
 }
 
+__global__ void __launch_bounds__(128) paged_append_kernel(uint4* k_pool, uint4* v_pool, const uint4* k_rows, const uint4* v_rows,
+                                                           const int32_t* lens, const int32_t* table, uint32_t table_stride,
+                                                           uint32_t page_pos, uint32_t row_vec) {
+    const uint32_t s = blockIdx.x;
+    const int32_t pos = lens[s] - 1;
+    if (pos < 0) return;
+    const size_t at = ((size_t)table[(size_t)s * table_stride + pos / page_pos] * page_pos + pos % page_pos) * row_vec;
+    for (uint32_t i = threadIdx.x; i < row_vec; i += blockDim.x) {
+        k_pool[at + i] = k_rows[(size_t)s * row_vec + i];
+        v_pool[at + i] = v_rows[(size_t)s * row_vec + i];
+    }
+}
+
+SV_EXPORT int silvann_b200_paged_append(silvann_b200_plan* p, void* k_pool, void* v_pool, const void* k_rows, const void* v_rows,
+                                        uint32_t page_positions, const int32_t* page_table, uint32_t table_stride, void* stream) {
+    called();
+    if (!p || !p->ready) return fail(SILVANN_B200_E_STATE, "paged_append: plan_decode has not run");
+    if (!k_pool || !v_pool || !k_rows || !v_rows || !page_table || page_positions == 0) return fail(SILVANN_B200_E_ARGUMENT, "paged_append: a null operand");
+    const uint32_t row_bytes = p->kv_heads * p->head_dim * 2u;
+    if (row_bytes % 16u || (((uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)k_rows | (uintptr_t)v_rows) & 15u))
+        return fail(SILVANN_B200_E_ARGUMENT, "paged_append: rows and pools must be 16-byte aligned");
+    paged_append_kernel<<<p->seqs, 128, 0, (cudaStream_t)stream>>>((uint4*)k_pool, (uint4*)v_pool, (const uint4*)k_rows, (const uint4*)v_rows,
+                                                                  p->lens_dev, page_table, table_stride, page_positions, row_bytes / 16u);
+    sv::note_launch(1);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? SILVANN_B200_OK : cuda_fail("paged_append: launch", e);
+}
+
 /* ---------------------------------------------------------------------------------------------------------- */
 
 SV_EXPORT int silvann_b200_prefill(void* o, const void* q, const void* k, const void* v, uint64_t q_heads, uint64_t kv_heads, uint64_t head_dim,

@@ -1,0 +1,141 @@
+"""ctypes bindings of the `silvann_b200_*` entry points (include/silvann_b200.h, second half).
+
+Arguments that are device buffers may be torch tensors (their data_ptr() is used), integers (raw device addresses) or
+None.  Every call raises B200Error with the library's own message when it answers anything but SILVANN_B200_OK.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import library_path
+
+FP16, BF16 = 0, 1
+OK, E_ARGUMENT, E_CUDA, E_TIMEOUT, E_STATE = 0, 1, 2, 3, 4
+COUNTERS = ("fused_decode", "fused_residual", "fused_prefill", "flushed", "refused", "deltanet", "launches", "ext_calls")
+EXPORTS = (
+    "silvann_silicon_family_get", "silvann_b200_last_error", "silvann_b200_counters_read", "silvann_b200_device_status",
+    "silvann_b200_decode", "silvann_b200_merge", "silvann_b200_finish", "silvann_b200_plan_create",
+    "silvann_b200_plan_destroy", "silvann_b200_plan_decode", "silvann_b200_plan_info", "silvann_b200_paged_decode", "silvann_b200_paged_append",
+    "silvann_b200_prefill", "silvann_b200_deltanet",
+)
+
+
+class B200Error(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"silvann_b200 error {code}: {message}")
+        self.code = code
+
+
+def addr(x) -> int | None:
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    return x.data_ptr()
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        L = C.CDLL(str(library_path()), mode=C.RTLD_LOCAL)
+        vp, u64, u32, i32 = C.c_void_p, C.c_uint64, C.c_uint32, C.c_int
+        L.silvann_b200_last_error.restype = C.c_char_p
+        sigs = {
+            "silvann_b200_counters_read": [vp, u32, i32],
+            "silvann_b200_device_status": [vp, i32],
+            "silvann_b200_decode": [vp, vp, vp, vp, vp, u64, u64, u64, u64, u32, i32, vp, vp],
+            "silvann_b200_merge": [vp, vp, vp, u64, u64, vp],
+            "silvann_b200_finish": [vp, vp, u64, u64, i32, vp, vp],
+            "silvann_b200_plan_create": [vp],
+            "silvann_b200_plan_destroy": [vp],
+            "silvann_b200_plan_decode": [vp, vp, u32, u32, u32, u32, u32, vp],
+            "silvann_b200_plan_info": [vp, vp, vp, vp],
+            "silvann_b200_paged_decode": [vp, vp, vp, vp, vp, vp, u64, u32, vp, u32, i32, vp, vp],
+            "silvann_b200_paged_append": [vp, vp, vp, vp, vp, u32, vp, u32, vp],
+            "silvann_b200_prefill": [vp, vp, vp, vp, u64, u64, u64, u64, u64, i32, vp, vp],
+            "silvann_b200_deltanet": [vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u32, u32, i32, vp, vp],
+        }
+        for name, args in sigs.items():
+            fn = getattr(L, name)
+            fn.argtypes, fn.restype = args, i32
+        _lib = L
+    return _lib
+
+
+def _check(code: int):
+    if code != OK:
+        raise B200Error(code, lib().silvann_b200_last_error().decode())
+
+
+def counters(reset: bool = False) -> dict:
+    out = (C.c_uint64 * len(COUNTERS))()
+    _check(lib().silvann_b200_counters_read(out, len(COUNTERS), int(reset)))
+    return dict(zip(COUNTERS, out))
+
+
+def device_status(clear: bool = True) -> int:
+    w = C.c_uint32(0)
+    _check(lib().silvann_b200_device_status(C.byref(w), int(clear)))
+    return w.value
+
+
+def decode(o, res, q, k, v, q_heads, kv_heads, head_dim, length, dtype=FP16, nsplit=0, over=None, stream=None):
+    _check(lib().silvann_b200_decode(addr(o), addr(res), addr(q), addr(k), addr(v), q_heads, kv_heads, head_dim, length,
+                                     nsplit, dtype, addr(over), stream))
+
+
+def merge(into, a, b, q_heads, head_dim, stream=None):
+    _check(lib().silvann_b200_merge(addr(into), addr(a), addr(b), q_heads, head_dim, stream))
+
+
+def finish(o, res, q_heads, head_dim, dtype=FP16, over=None, stream=None):
+    _check(lib().silvann_b200_finish(addr(o), addr(res), q_heads, head_dim, dtype, addr(over), stream))
+
+
+class Plan:
+    """A paged-decode plan (work list + split scratch) on the current device."""
+
+    def __init__(self):
+        self.handle = C.c_void_p()
+        _check(lib().silvann_b200_plan_create(C.byref(self.handle)))
+
+    def close(self):
+        if self.handle:
+            lib().silvann_b200_plan_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def plan(self, seq_lens, q_heads, kv_heads, head_dim, blocks_target=0, stream=None):
+        arr = (C.c_int32 * len(seq_lens))(*[int(x) for x in seq_lens])
+        _check(lib().silvann_b200_plan_decode(self.handle, arr, len(seq_lens), q_heads, kv_heads, head_dim, blocks_target, stream))
+
+    def info(self) -> dict:
+        b, s, p = C.c_uint32(), C.c_uint32(), C.c_uint64()
+        _check(lib().silvann_b200_plan_info(self.handle, C.byref(b), C.byref(s), C.byref(p)))
+        return {"blocks": b.value, "slots": s.value, "positions": p.value}
+
+    def decode(self, o, res, q, k_pool, v_pool, pool_pages, page_positions, page_table, table_stride, dtype=FP16, over=None, stream=None):
+        _check(lib().silvann_b200_paged_decode(self.handle, addr(o), addr(res), addr(q), addr(k_pool), addr(v_pool), pool_pages,
+                                               page_positions, addr(page_table), table_stride, dtype, addr(over), stream))
+
+
+    def append(self, k_pool, v_pool, k_rows, v_rows, page_positions, page_table, table_stride, stream=None):
+        _check(lib().silvann_b200_paged_append(self.handle, addr(k_pool), addr(v_pool), addr(k_rows), addr(v_rows), page_positions,
+                                               addr(page_table), table_stride, stream))
+
+
+def prefill(o, q, k, v, q_heads, kv_heads, head_dim, first, rows, dtype=FP16, over=None, stream=None):
+    _check(lib().silvann_b200_prefill(addr(o), addr(q), addr(k), addr(v), q_heads, kv_heads, head_dim, first, rows, dtype, addr(over), stream))
+
+
+def deltanet(S, conved, z, beta, g, w, out, k_heads, v_heads, head_dim, rows, seqs=1, gate=0, dtype=FP16, over=None, stream=None):
+    _check(lib().silvann_b200_deltanet(addr(S), addr(conved), addr(z), addr(beta), addr(g), addr(w), addr(out), k_heads, v_heads,
+                                       head_dim, rows, seqs, gate, dtype, addr(over), stream))

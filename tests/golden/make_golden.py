@@ -1,0 +1,76 @@
+"""Generates tests/golden/reference_x86_avx2.npz: outputs of the REFERENCE's own CPU silicon family (x86_avx2, built
+unmodified by oracle/build.py from the mounted reference tree) on small seeded inputs, for every door on the hot path.
+
+Run where the reference tree is mounted:  python tests/golden/make_golden.py
+The fixtures travel with the repository; the reference tree does not.  Inputs are stored as bit patterns, so the
+fixture does not depend on how this script's numpy rounds.
+"""
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+
+import oracle  # noqa: E402
+from oracle import to_bits  # noqa: E402
+
+
+def main():
+    R = oracle.reference()
+    if R is None:
+        raise SystemExit("the reference tree is not mounted and oracle/_ref holds no earlier build")
+    rng = np.random.default_rng(20260901)
+    out = {}
+
+    def bits(shape, scale=1.0):
+        return to_bits(rng.standard_normal(shape, dtype=np.float32) * np.float32(scale), 0)
+
+    # one query position: decode, residual over two ranges, merge, finish
+    for tag, (qh, kvh, d, L) in {"dec_a": (8, 2, 64, 200), "dec_b": (8, 2, 128, 150), "dec_c": (4, 4, 32, 17), "dec_d": (6, 1, 96, 70)}.items():
+        q, k, v = bits((qh, d)), bits((L, kvh, d)), bits((L, kvh, d))
+        out[f"{tag}_shape"] = np.array([qh, kvh, d, L])
+        out[f"{tag}_q"], out[f"{tag}_k"], out[f"{tag}_v"] = q, k, v
+        out[f"{tag}_p"] = R.scores(q, k, qh, kvh, d, L)
+        out[f"{tag}_o"] = R.decode(q, k, v, qh, kvh, d, L)
+        cut = L // 3
+        ra = R.residual(q, k[:cut], v[:cut], qh, kvh, d, cut)
+        rb = R.residual(q, np.ascontiguousarray(k[cut:]), np.ascontiguousarray(v[cut:]), qh, kvh, d, L - cut)
+        rm = R.merge(ra, rb, qh, d)
+        out[f"{tag}_cut"] = np.array([cut])
+        out[f"{tag}_res_a"], out[f"{tag}_res_b"], out[f"{tag}_res_m"] = ra, rb, rm
+        out[f"{tag}_o_merged"] = R.finish(rm, qh, d)
+
+    # a prompt's rows through the three causal doors
+    for tag, (qh, kvh, d, first, rows) in {"cau_a": (8, 2, 64, 0, 24), "cau_b": (4, 1, 128, 9, 7)}.items():
+        q, k, v = bits((rows, qh, d), 0.5), bits((first + rows, kvh, d), 0.5), bits((first + rows, kvh, d), 0.5)
+        out[f"{tag}_shape"] = np.array([qh, kvh, d, first, rows])
+        out[f"{tag}_q"], out[f"{tag}_k"], out[f"{tag}_v"] = q, k, v
+        out[f"{tag}_o"] = R.causal(q, k, v, qh, kvh, d, first, rows)
+
+    # Gated DeltaNet: a run of rows then one more step, both gates
+    for tag, (kh, vh, d, rows, gate) in {"dn_a": (1, 2, 64, 6, 0), "dn_b": (1, 1, 128, 3, 1)}.items():
+        conved = bits((rows + 1, (2 * kh + vh) * d))
+        z = bits((rows + 1, vh * d))
+        beta = to_bits(1.0 / (1.0 + np.exp(-rng.standard_normal((rows + 1, vh), dtype=np.float32))), 0)
+        g = to_bits(-np.log1p(np.exp(rng.standard_normal((rows + 1, vh), dtype=np.float32))), 0)
+        w = bits((d,))
+        S = (rng.standard_normal((vh, d, d), dtype=np.float32) * 0.05).astype(np.float32)
+        out[f"{tag}_shape"] = np.array([kh, vh, d, rows, gate])
+        for name, arr in (("conved", conved), ("z", z), ("beta", beta), ("g", g), ("w", w), ("S0", S.copy())):
+            out[f"{tag}_{name}"] = arr
+        o_rows = R.deltanet(S, conved[:rows], z[:rows], beta[:rows], g[:rows], w, kh, vh, d, rows, gate)
+        out[f"{tag}_S_rows"], out[f"{tag}_o_rows"] = S.copy(), o_rows
+        o_step = R.deltanet(S, conved[rows:], z[rows:], beta[rows:], g[rows:], w, kh, vh, d, 1, gate)
+        out[f"{tag}_S_step"], out[f"{tag}_o_step"] = S.copy(), o_step
+
+    path = Path(__file__).with_name("reference_x86_avx2.npz")
+    np.savez_compressed(path, **out)
+    print(path, path.stat().st_size, "bytes,", len(out), "arrays")
+
+
+if __name__ == "__main__":
+    main()

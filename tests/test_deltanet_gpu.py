@@ -1,0 +1,84 @@
+"""Gated DeltaNet on a B200 against the reference's CPU family (fp16 doors) and the restatement (bf16 extension).
+Bars: fp32 state within 1e-3 relative of its largest magnitude, 16-bit outputs within 2e-3."""
+import numpy as np
+import pytest
+
+from oracle import from_bits
+from silvann_b200 import ext, verbs, workloads
+from util import dev, host_bits
+
+pytestmark = pytest.mark.gpu
+
+
+def check(S_got, S_want, o_got, o_want, dtype, what):
+    assert np.abs(S_got - S_want).max() <= 1e-3 * max(np.abs(S_want).max(), 1e-6), what
+    assert np.abs(from_bits(o_got, dtype) - from_bits(o_want, dtype)).max() <= 2e-3 + (0 if dtype == 0 else 2.0 ** -8 * np.abs(from_bits(o_want, dtype)).max()), what
+
+
+@pytest.mark.parametrize("tag", ["dn_a", "dn_b"])
+def test_golden_rows_then_step_through_the_doors(cuda, fam, golden, tag):
+    kh, vh, d, rows, gate = (int(x) for x in golden[f"{tag}_shape"])
+    V = verbs.Verbs(fam)
+    conved, z, beta, g, w = (golden[f"{tag}_{n}"] for n in ("conved", "z", "beta", "g", "w"))
+    S = dev(cuda, golden[f"{tag}_S0"])
+    out = cuda.zeros((rows, vh * d), dtype=cuda.int16, device="cuda")
+    V.deltanet_rows(S, dev(cuda, conved[:rows]), dev(cuda, z[:rows]), dev(cuda, beta[:rows]), dev(cuda, g[:rows]), dev(cuda, w), out, kh, vh, d, rows, gate)
+    assert fam.sys.compute_completed()
+    check(S.cpu().numpy(), golden[f"{tag}_S_rows"], host_bits(out), golden[f"{tag}_o_rows"], 0, f"{tag} rows")
+    out1 = cuda.zeros((1, vh * d), dtype=cuda.int16, device="cuda")
+    V.deltanet_step(S, dev(cuda, conved[rows:]), dev(cuda, z[rows:]), dev(cuda, beta[rows:]), dev(cuda, g[rows:]), dev(cuda, w), out1, kh, vh, d, gate)
+    assert fam.sys.compute_completed()
+    check(S.cpu().numpy(), golden[f"{tag}_S_step"], host_bits(out1), golden[f"{tag}_o_step"], 0, f"{tag} step")
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_config5_shape_shortened(cuda, port, reference, dtype):
+    """32 heads of 128, a prompt of 256 rows then 8 single steps — the benchmark's shape with a shorter prompt."""
+    w = workloads.config5(rows=264, dtype=dtype)
+    kh = vh = 32; d = 128; T = 256
+    S_want = np.zeros((vh, d, d), np.float32)
+    use_ref = reference is not None and dtype == 0
+    run = (lambda S, lo, hi: reference.deltanet(S, w.conved[lo:hi], w.z[lo:hi], w.beta[lo:hi], w.g[lo:hi], w.w, kh, vh, d, hi - lo)) if use_ref else \
+          (lambda S, lo, hi: port.deltanet(S, np.ascontiguousarray(w.conved[lo:hi]), np.ascontiguousarray(w.z[lo:hi]), np.ascontiguousarray(w.beta[lo:hi]),
+                                           np.ascontiguousarray(w.g[lo:hi]), w.w, kh, vh, d, hi - lo, 0, dtype))
+    o_want = [run(S_want, 0, T)] + [run(S_want, T + i, T + i + 1) for i in range(8)]
+    S = cuda.zeros((vh, d, d), dtype=cuda.float32, device="cuda")
+    tc, tz, tb, tg, tw = (dev(cuda, x) for x in (w.conved, w.z, w.beta, w.g, w.w))
+    out = cuda.zeros((264, vh * d), dtype=cuda.int16, device="cuda")
+    ch = (2 * kh + vh) * d
+    ext.deltanet(S, tc, tz, tb, tg, tw, out, kh, vh, d, T, 1, 0, dtype)
+    for i in range(8):
+        r = T + i
+        ext.deltanet(S, tc.data_ptr() + 2 * r * ch, tz.data_ptr() + 2 * r * vh * d, tb.data_ptr() + 2 * r * vh, tg.data_ptr() + 2 * r * vh,
+                     tw, out.data_ptr() + 2 * r * vh * d, kh, vh, d, 1, 1, 0, dtype)
+    cuda.cuda.synchronize()
+    got = host_bits(out)
+    check(S.cpu().numpy(), S_want, got[:T], o_want[0], dtype, "prompt")
+    for i in range(8):
+        check(S.cpu().numpy(), S_want, got[T + i:T + i + 1], o_want[1 + i], dtype, f"step {i}")
+
+
+def test_batched_sequences_equal_one_at_a_time(cuda):
+    """Size-independent property: a batch of independent sequences gives bit-for-bit what each gives alone."""
+    kh, vh, d, rows, B = 2, 4, 128, 5, 3
+    rng = np.random.default_rng(2)
+    def r16(a): return dev(cuda, a.astype(np.float16).view(np.uint16))
+    def rnd(*s): return rng.standard_normal(s, dtype=np.float32) * 0.5
+    conved, z = r16(rnd(B, rows, (2 * kh + vh) * d)), r16(rnd(B, rows, vh * d))
+    beta, g, w = r16(np.abs(rnd(B, rows, vh))), r16(-np.abs(rnd(B, rows, vh))), r16(rnd(d))
+    S0 = cuda.from_numpy(rng.standard_normal((B, vh, d, d), dtype=np.float32) * 0.1).cuda()
+    Sb, ob = S0.clone(), cuda.zeros((B, rows, vh * d), dtype=cuda.int16, device="cuda")
+    ext.deltanet(Sb, conved, z, beta, g, w, ob, kh, vh, d, rows, B, 1, 0)
+    for b in range(B):
+        S1, o1 = S0[b].clone(), cuda.zeros((rows, vh * d), dtype=cuda.int16, device="cuda")
+        ext.deltanet(S1, conved[b].contiguous(), z[b].contiguous(), beta[b].contiguous(), g[b].contiguous(), w, o1, kh, vh, d, rows, 1, 1, 0)
+        cuda.cuda.synchronize()
+        assert cuda.equal(S1, Sb[b]) and cuda.equal(o1, ob[b])
+
+
+def test_unfit_shapes_are_refused(cuda):
+    t = cuda.zeros(4096, dtype=cuda.float32, device="cuda")
+    with pytest.raises(ext.B200Error):
+        ext.deltanet(t, t, t, t, t, t, t, 1, 1, 48, 1)
+    with pytest.raises(ext.B200Error):
+        ext.deltanet(t, t, t, t, t, t, t, 3, 4, 64, 1)

@@ -1,0 +1,115 @@
+"""Pins the checker itself: the C restatement against outputs of the reference's own CPU family (tests/golden/, and
+live where oracle/_ref is present) and against fp64 numpy."""
+import numpy as np
+import pytest
+
+import oracle
+from oracle import from_bits, to_bits
+
+DEC = ["dec_a", "dec_b", "dec_c", "dec_d"]
+
+
+@pytest.mark.parametrize("tag", DEC)
+def test_decode_matches_reference_golden(golden, port, tag):
+    qh, kvh, d, L = (int(x) for x in golden[f"{tag}_shape"])
+    q, k, v = golden[f"{tag}_q"], golden[f"{tag}_k"], golden[f"{tag}_v"]
+    p = port.scores(q, k, qh, kvh, d, L)
+    np.testing.assert_allclose(p, golden[f"{tag}_p"], rtol=2e-5, atol=1e-7)
+    o, _ = port.mix(p, v, qh, kvh, d, L)
+    # fp16 outputs: identical up to one unit in the last place where summation order differs
+    assert np.abs(from_bits(o, 0) - from_bits(golden[f"{tag}_o"], 0)).max() <= 2.0 ** -10 * max(1.0, np.abs(from_bits(o, 0)).max())
+
+
+@pytest.mark.parametrize("tag", DEC)
+def test_residual_merge_finish_match_reference_golden(golden, port, tag):
+    qh, kvh, d, L = (int(x) for x in golden[f"{tag}_shape"])
+    q, k, v = golden[f"{tag}_q"], golden[f"{tag}_k"], golden[f"{tag}_v"]
+    cut = int(golden[f"{tag}_cut"][0])
+    ra = port.residual(q, np.ascontiguousarray(k[:cut]), np.ascontiguousarray(v[:cut]), qh, kvh, d, cut)
+    rb = port.residual(q, np.ascontiguousarray(k[cut:]), np.ascontiguousarray(v[cut:]), qh, kvh, d, L - cut)
+    np.testing.assert_allclose(ra, golden[f"{tag}_res_a"], rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(rb, golden[f"{tag}_res_b"], rtol=1e-4, atol=1e-5)
+    rm = port.merge(ra, rb, qh, d)
+    np.testing.assert_allclose(rm, golden[f"{tag}_res_m"], rtol=1e-4, atol=1e-5)
+    o, _ = port.finish(rm, qh, d)
+    want = from_bits(golden[f"{tag}_o_merged"], 0)
+    assert np.abs(from_bits(o, 0) - want).max() <= 2.0 ** -10 * max(1.0, np.abs(want).max())
+    # and the merged answer is the one-call answer (the reference's exactness claim, kernels.cuh:1180-1184)
+    assert np.abs(want - from_bits(golden[f"{tag}_o"], 0)).max() <= 2e-3
+
+
+@pytest.mark.parametrize("tag", ["cau_a", "cau_b"])
+def test_causal_matches_reference_golden(golden, port, tag):
+    qh, kvh, d, first, rows = (int(x) for x in golden[f"{tag}_shape"])
+    q, k, v = golden[f"{tag}_q"], golden[f"{tag}_k"], golden[f"{tag}_v"]
+    want = from_bits(golden[f"{tag}_o"], 0)
+    three = port.causal_three_doors(q, k, v, qh, kvh, d, first, rows)
+    fused, o32 = port.prefill(q, k, v, qh, kvh, d, first, rows)
+    assert np.array_equal(three, fused)
+    assert np.abs(from_bits(fused, 0) - want).max() <= 2.0 ** -10 * max(1.0, np.abs(want).max())
+    assert np.abs(o32 - want).max() <= 1e-3
+
+
+@pytest.mark.parametrize("tag", ["dn_a", "dn_b"])
+def test_deltanet_matches_reference_golden(golden, port, tag):
+    kh, vh, d, rows, gate = (int(x) for x in golden[f"{tag}_shape"])
+    conved, z, beta, g, w = (golden[f"{tag}_{n}"] for n in ("conved", "z", "beta", "g", "w"))
+    S = golden[f"{tag}_S0"].copy()
+    o_rows = port.deltanet(S, conved[:rows], z[:rows], beta[:rows], g[:rows], w, kh, vh, d, rows, gate)
+    ref_S = golden[f"{tag}_S_rows"]
+    assert np.abs(S - ref_S).max() <= 1e-3 * np.abs(ref_S).max()
+    assert np.abs(from_bits(o_rows, 0) - from_bits(golden[f"{tag}_o_rows"], 0)).max() <= 2e-3
+    o_step = port.deltanet(S, np.ascontiguousarray(conved[rows:]), np.ascontiguousarray(z[rows:]), np.ascontiguousarray(beta[rows:]),
+                           np.ascontiguousarray(g[rows:]), w, kh, vh, d, 1, gate)
+    assert np.abs(S - golden[f"{tag}_S_step"]).max() <= 1e-3 * np.abs(golden[f"{tag}_S_step"]).max()
+    assert np.abs(from_bits(o_step, 0) - from_bits(golden[f"{tag}_o_step"], 0)).max() <= 2e-3
+
+
+def test_decode_against_fp64(port):
+    rng = np.random.default_rng(7)
+    qh, kvh, d, L = 8, 2, 64, 257
+    q, k, v = (to_bits(rng.standard_normal(s, dtype=np.float32), 0) for s in ((qh, d), (L, kvh, d), (L, kvh, d)))
+    _, o32 = port.decode(q, k, v, qh, kvh, d, L)
+    qf, kf, vf = (from_bits(x, 0).astype(np.float64) for x in (q, k, v))
+    want = np.zeros((qh, d))
+    for h in range(qh):
+        s = kf[:, h // (qh // kvh), :] @ qf[h] / np.sqrt(d)
+        w = np.exp(s - s.max())
+        want[h] = (w / w.sum()) @ vf[:, h // (qh // kvh), :]
+    assert np.abs(o32 - want).max() < 1e-5
+
+
+def test_bf16_inputs_are_fp16_exact_and_port_agrees_across_dtypes(port):
+    """The bridge used for every bf16 configuration: the same real numbers, read as fp16 by the reference and as bf16 by
+    the kernels, give the same fp32 result in the restatement."""
+    rng = np.random.default_rng(11)
+    qh, kvh, d, L = 8, 1, 64, 100
+    vals = [oracle.fp16_exact_bf16(rng.standard_normal(s, dtype=np.float32)) for s in ((qh, d), (L, kvh, d), (L, kvh, d))]
+    as16 = [to_bits(x, 0) for x in vals]
+    asbf = [to_bits(x, 1) for x in vals]
+    for a, b, x in zip(as16, asbf, vals):
+        assert np.array_equal(from_bits(a, 0), x) and np.array_equal(from_bits(b, 1), x)
+    _, o16 = port.decode(*as16, qh, kvh, d, L, 0)
+    _, obf = port.decode(*asbf, qh, kvh, d, L, 1)
+    assert np.array_equal(o16, obf)
+
+
+def test_half_conversion_edges(port):
+    lib = port.lib
+    import ctypes as C
+    lib.oracle_f32_to_f16.restype, lib.oracle_f32_to_f16.argtypes = C.c_uint16, [C.c_float]
+    lib.oracle_f16_to_f32.restype, lib.oracle_f16_to_f32.argtypes = C.c_float, [C.c_uint16]
+    for x in [0.0, -0.0, 1.0, 65504.0, 65520.0, 1e-8, 6e-8, 6.1e-5, -3.14159, 0.1, 2049.0, 2051.0]:
+        want = np.float32(x).astype(np.float16)
+        got = lib.oracle_f32_to_f16(x)
+        assert got == int(want.view(np.uint16)) or (np.isinf(want) and got & 0x7FFF == 0x7C00), x
+    for h in [0, 1, 0x03FF, 0x0400, 0x3C00, 0x7BFF, 0x8001, 0xFBFF]:
+        assert lib.oracle_f16_to_f32(h) == float(np.array([h], np.uint16).view(np.float16)[0])
+
+
+def test_live_reference_agrees_with_golden(golden, reference):
+    if reference is None:
+        pytest.skip("oracle/_ref holds no reference family on this machine")
+    qh, kvh, d, L = (int(x) for x in golden["dec_a_shape"])
+    o = reference.decode(golden["dec_a_q"], golden["dec_a_k"], golden["dec_a_v"], qh, kvh, d, L)
+    assert np.array_equal(o, golden["dec_a_o"])
