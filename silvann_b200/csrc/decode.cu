@@ -315,23 +315,51 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     __syncthreads();
     if (*ticket_s != (uint32_t)(nsplit - 1)) return;
     __threadfence();
-    for (int i = tid; i < heads * D; i += (NW + 1) * 32) {
-        const int h = i / D, e = i % D;
+    /* first the per-(head, split) factors e^(m_s - m) and the merged l, a warp a head, lanes across splits ... */
+    float* fac = (float*)stage_base;                  /* [heads][nsplit] */
+    float* mh = fac + HPB * nsplit;                   /* [heads] merged m (log2 units), then merged l */
+    float* lh = mh + HPB;
+    for (int h = warp; h < heads; h += NW + 1) {
         float m = -INFINITY;
-        for (int s = 0; s < nsplit; ++s)
+        for (int s = lane; s < nsplit; s += 32)
             m = fmaxf(m, __ldcg(P.partials + ((size_t)(slot_base + s * slot_stride) * HPB + h) * SF));
-        float acc = 0.f, l = 0.f;
-        for (int s = 0; s < nsplit; ++s) {
+        for (int x = 16; x > 0; x >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, x));
+        float l = 0.f;
+        for (int s = lane; s < nsplit; s += 32) {
             const float* r = P.partials + ((size_t)(slot_base + s * slot_stride) * HPB + h) * SF;
             const float ms = __ldcg(r);
-            if (ms != -INFINITY) { const float f = fast_exp2(ms - m); acc += __ldcg(r + 2 + e) * f; l += __ldcg(r + 1) * f; }
+            const float f = (ms == -INFINITY) ? 0.f : fast_exp2(ms - m);
+            fac[h * nsplit + s] = f;
+            l += __ldcg(r + 1) * f;
         }
+        for (int x = 16; x > 0; x >>= 1) l += __shfl_xor_sync(0xffffffffu, l, x);
+        if (lane == 0) { mh[h] = m; lh[h] = l; }
+    }
+    __syncthreads();
+    /* ... then each output element: the splits' accumulators in split order, neighbouring threads neighbouring
+     * elements, so every load is a coalesced read of what the other blocks left in L2 */
+    for (int i = tid; i < heads * D; i += (NW + 1) * 32) {
+        const int h = i / D, e = i % D;
+        const float* r = P.partials + ((size_t)slot_base * HPB + h) * SF + 2 + e;
+        const size_t step = (size_t)slot_stride * HPB * SF;
+        const float* f = fac + h * nsplit;
+        float acc = 0.f;
+        int s = 0;
+        for (; s + 8 <= nsplit; s += 8) {
+            float x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) x[u] = __ldcg(r + (size_t)(s + u) * step);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc += x[u] * f[s + u];
+        }
+        for (; s < nsplit; ++s) acc += __ldcg(r + (size_t)s * step) * f[s];
+        const float m = mh[h], l = lh[h];
         const size_t hq = (size_t)seq * P.q_heads + head0 + h;
         if (P.o) ((uint16_t*)P.o)[hq * D + e] = E::from_float(acc / l, hit);
         if (P.res) {
-            float* r = P.res + hq * (D + 2);
-            r[2 + e] = acc;
-            if (e == 0) { r[0] = m * SV_LN2; r[1] = l; }
+            float* ro = P.res + hq * (D + 2);
+            ro[2 + e] = acc;
+            if (e == 0) { ro[0] = m * SV_LN2; ro[1] = l; }
         }
     }
     if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
@@ -408,11 +436,12 @@ void decode_auto_split(uint32_t length, uint32_t q_heads, uint32_t kv_heads, uin
     /* one wave of blocks when the cache is short, up to four when each block still gets a long run of tiles */
     uint32_t want = sms / lanes;
     if (want < 1u) want = 1u;
-    if (tiles / want >= 32u) want *= 4u; else if (tiles / want >= 16u) want *= 2u;
+    if (tiles / want >= 64u) want *= 2u;
     uint32_t ns = want < tiles ? want : tiles;
     if (ns < 1u) ns = 1u;
     const uint32_t chunk = (tiles + ns - 1) / ns;
     ns = (tiles + chunk - 1) / chunk;                       /* no empty split */
+    if (ns > 1024u) ns = 1024u;                                /* the merge keeps heads x splits factors in shared memory */
     while (ns * lanes > SV_DECODE_MAX_SLOTS && ns > 1u) --ns;
     *nsplit = ns; *head_blocks = hb;
 }
@@ -458,6 +487,7 @@ cudaError_t decode_launch(const DecodeCall& c) {
         if (ns == 0) decode_auto_split(c.length, c.q_heads, c.kv_heads, c.head_dim, device_sm_count(), &ns, &hb2);
         const uint32_t tiles = (c.length + BT - 1) / BT;
         if (ns > tiles) ns = tiles;
+        if (ns > 1024u) ns = 1024u;
         const uint32_t chunk = (tiles + ns - 1) / ns;
         ns = (tiles + chunk - 1) / chunk;
         if ((uint64_t)ns * c.kv_heads * hb > c.scratch.slots || (uint64_t)c.kv_heads * hb > c.scratch.tickets_n) return cudaErrorInvalidValue;

@@ -65,10 +65,22 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
     uint16_t* oo = P.out + (uint64_t)b * P.rows * vd;
     float* ss = P.ss + (uint64_t)b * P.rows * P.v_heads * CB;
 
-    /* stage position 0's q and k */
-    for (int i = tid; i < 2 * D; i += DN_THREADS) {
+    /* Inputs run one position ahead in registers so that no global-load latency sits on the serial path: during
+     * position t the thread already holds position t's value/beta/g and position t+1's q,k elements (both loaded during
+     * t-1); it parks the q,k elements in the other shared buffer and issues the loads for t+1 and t+2. */
+    constexpr int NQ = (2 * D + DN_THREADS - 1) / DN_THREADS;      /* q,k elements this thread stages per position */
+    /* raw bits are kept until use: converting at load time would stall the thread on the load */
+    auto qk_src = [&](const uint16_t* row, int i) -> uint16_t {
         const int which = i / D, e = i % D;
-        qk[0][which][e] = E::to_float(cv[(which == 0 ? kh * D : (P.k_heads + kh) * D) + e]);
+        return row[(which == 0 ? kh * D : (P.k_heads + kh) * D) + e];
+    };
+    for (int i = tid; i < 2 * D; i += DN_THREADS) (&qk[0][0][0])[i] = E::to_float(qk_src(cv, i));
+    uint16_t n_v = cv[(uint64_t)2 * P.k_heads * D + (uint64_t)h * D + j], n_beta = bb[h], n_g = gg[h];
+    uint16_t n_qk[NQ];
+#pragma unroll
+    for (int u = 0; u < NQ; ++u) {
+        const int i = tid + u * DN_THREADS;
+        n_qk[u] = (P.rows > 1 && i < 2 * D) ? qk_src(cv + ch, i) : (uint16_t)0;
     }
     __syncthreads();
 
@@ -76,16 +88,23 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
     bool hit = false;
     for (uint64_t t = 0; t < P.rows; ++t) {
         const int buf = (int)(t & 1);
-        const uint16_t* row = cv + t * ch;
-        /* this position's scalars and value, and the next position's q,k into the other buffer */
-        const float vj = E::to_float(row[(uint64_t)2 * P.k_heads * D + (uint64_t)h * D + j]);
-        const float beta = E::to_float(bb[t * P.v_heads + h]);
-        const float decay = expf(E::to_float(gg[t * P.v_heads + h]));
+        const float vj = E::to_float(n_v), beta = E::to_float(n_beta), decay = expf(E::to_float(n_g));
         if (t + 1 < P.rows) {
-            const uint16_t* nrow = row + ch;
-            for (int i = tid; i < 2 * D; i += DN_THREADS) {
-                const int which = i / D, e = i % D;
-                qk[buf ^ 1][which][e] = E::to_float(nrow[(which == 0 ? kh * D : (P.k_heads + kh) * D) + e]);
+#pragma unroll
+            for (int u = 0; u < NQ; ++u) {
+                const int i = tid + u * DN_THREADS;
+                if (i < 2 * D) (&qk[buf ^ 1][0][0])[i] = E::to_float(n_qk[u]);
+            }
+            const uint16_t* nrow = cv + (t + 1) * ch;
+            n_v = nrow[(uint64_t)2 * P.k_heads * D + (uint64_t)h * D + j];
+            n_beta = bb[(t + 1) * P.v_heads + h];
+            n_g = gg[(t + 1) * P.v_heads + h];
+            if (t + 2 < P.rows) {
+#pragma unroll
+                for (int u = 0; u < NQ; ++u) {
+                    const int i = tid + u * DN_THREADS;
+                    if (i < 2 * D) n_qk[u] = qk_src(nrow + ch, i);
+                }
             }
         }
         const float* qv = qk[buf][0] + rg * R;

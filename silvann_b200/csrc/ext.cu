@@ -155,6 +155,7 @@ SV_EXPORT int silvann_b200_plan_decode(silvann_b200_plan* p, const int32_t* seq_
     for (uint32_t s = 0; s < seqs; ++s) {
         const uint32_t tiles = ((uint32_t)seq_lens[s] + SV_DECODE_TILE - 1) / SV_DECODE_TILE;
         uint32_t ns = (uint32_t)((tiles + chunk - 1) / chunk);
+        if (ns > 1024u) ns = 1024u;
         const uint32_t per = (tiles + ns - 1) / ns;
         ns = (tiles + per - 1) / per;
         for (uint32_t g = 0; g < kv_heads; ++g)

@@ -12,7 +12,10 @@ pytestmark = pytest.mark.gpu
 
 def check(S_got, S_want, o_got, o_want, dtype, what):
     assert np.abs(S_got - S_want).max() <= 1e-3 * max(np.abs(S_want).max(), 1e-6), what
-    assert np.abs(from_bits(o_got, dtype) - from_bits(o_want, dtype)).max() <= 2e-3 + (0 if dtype == 0 else 2.0 ** -8 * np.abs(from_bits(o_want, dtype)).max()), what
+    # 2e-3, or two units in the last place of the 16-bit type where that is larger: the read-out is rounded to 16 bits
+    # once before its norm and once after (kernels.cuh:677-688), and a summation-order tie can flip either rounding
+    want = from_bits(o_want, dtype)
+    assert (np.abs(from_bits(o_got, dtype) - want) <= np.maximum(2e-3, (2.0 ** -9 if dtype == 0 else 2.0 ** -6) * np.abs(want))).all(), what
 
 
 @pytest.mark.parametrize("tag", ["dn_a", "dn_b"])
