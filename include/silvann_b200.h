@@ -39,8 +39,12 @@ typedef unsigned int sv_fault; /* a worker's device-resident fault word; doors O
 
 /* ---- constants of the engine's contract ------------------------------------------------------------------ */
 #define SILVANN_B200_ABI_VERSION     9u            /* silicon_family.cuh:31 */
+#ifndef SILVANN_B200_FAMILY_ID                     /* both may be given at build time to answer to another roster name */
 #define SILVANN_B200_FAMILY_ID       310u          /* a free roster slot above nvidia_cuda12 (300); ids < 1024 */
+#endif
+#ifndef SILVANN_B200_FAMILY_NAME
 #define SILVANN_B200_FAMILY_NAME     "nvidia_b200"
+#endif
 #define SILVANN_B200_PACKAGES        7u            /* sys, nn, and five model packages with empty door tables */
 #define SILVANN_B200_FAULT_OVERFLOW  0x4E504F56u   /* "NPOV": an fp32 result did not fit a half (primitives.cuh:57) */
 #define SILVANN_B200_RESIDUAL_FLOATS(head_dim) ((head_dim) + 2u)  /* per head: m, l, acc[head_dim] (kernels.cuh:1186) */
