@@ -309,6 +309,25 @@ int silvann_b200_decode(void* o, float* res, const void* q, const void* k, const
                         uint64_t kv_heads, uint64_t head_dim, uint64_t length, uint32_t nsplit, int dtype,
                         sv_fault* over, void* stream);
 
+/* The same decode for callers that must not cause an allocation.  It has no counterpart in the reference: the
+ * reference's doors never own memory, because the engine carves every buffer from pools it sized at boot — and that is
+ * exactly the kind of caller this is for.  A host that has committed all of the card's memory up front, or that is
+ * recording its work into a stream capture, cannot afford a library that reaches for cudaMalloc on first use (the call
+ * may fail, and it stalls the device while it waits for it to go idle).  Here the split-KV scratch is a fixed array
+ * inside the library image (about 5 MB on every device that loads the library, until the process ends), so:
+ *   - nothing is allocated or freed, by this call or on its behalf;
+ *   - work that needs more than 304 scratch slots (splits x kv_heads x head blocks of 8 or 16 query heads) is refused
+ *     with a message; nsplit 0 chooses a split count that fits;
+ *   - all calls on a device share that one array: calls that overlap in time on a device race with each other, so
+ *     keep them on one stream or otherwise serialised; tickets are re-zeroed on `stream` before each launch;
+ *   - the first call on each device looks up the array's device address; make that first call before any stream
+ *     capture begins.
+ * Operands and results are silvann_b200_decode's.  Returns 0, 1 (refused: shapes, alignment or size) or 2 (the CUDA
+ * runtime refused); a one-line reason is written to `message` (may be null) — this entry keeps no error state. */
+int silvann_b200_decode_noalloc(void* o, float* res, const void* q, const void* k, const void* v, uint64_t q_heads,
+                                uint64_t kv_heads, uint64_t head_dim, uint64_t length, uint32_t nsplit, int dtype,
+                                sv_fault* over, void* stream, char* message, uint32_t message_bytes);
+
 /* Two residuals into one, and a residual into 16-bit output — attention_merge / attention_finish with a dtype. */
 int silvann_b200_merge(float* into, const float* a, const float* b, uint64_t q_heads, uint64_t head_dim, void* stream);
 int silvann_b200_finish(void* o, const float* res, uint64_t q_heads, uint64_t head_dim, int dtype, sv_fault* over, void* stream);

@@ -19,6 +19,7 @@
 #include "kernels.h"
 #include "tensormap.cuh"
 #include <stdio.h>
+#include <string.h>
 
 namespace sv {
 
@@ -512,3 +513,144 @@ cudaError_t decode_launch(const DecodeCall& c) {
 }
 
 }  // namespace sv
+
+namespace sv {
+
+/* ================================================================================================================ */
+/* A decode entry point that allocates nothing                                                                        */
+/*
+ * Who needs it.  SiLVANN sizes its buffer pools from the card's free memory when a machine boots and from then on
+ * expects every byte to be spoken for: a door that discovers, on its first call in the middle of a turn, that it wants
+ * a few more megabytes may be told there are none left — or may stall the whole device, because cudaMalloc waits for
+ * the device to go idle.  Hosts that replay work from a captured stream are in the same position: an allocation is not
+ * something a capture can contain.  For those callers the split-KV decode is offered once more with its scratch
+ * (split partials, arrival tickets and the status word) living in a fixed array that is part of the library image
+ * itself, so the kernel's scratch exists as soon as the library is loaded on a device and no call ever asks the
+ * runtime for memory.
+ *
+ * The price is a ceiling and a shared array.  The array is SV_STATIC_SLOTS partial slots (about 5 MB); every device
+ * that loads the library carries it until the process ends.  A call whose (splits x kv heads x head blocks) does not
+ * fit is refused with a message, never truncated.  Every call on a device uses the same array and finds whatever the
+ * previous call left: the tickets are cleared on the caller's stream before each launch (the partials need no
+ * clearing: each split writes its slot before anyone reads it), and two calls that overlap in time on one device —
+ * different streams, different threads — would race on it.  Serialise them.
+ *
+ * The array's name means something different on the two sides of the compiler: device code can name `g_static_scratch`
+ * directly, but in host code the same identifier is only a handle for the runtime — passing it to a kernel would hand
+ * the kernel a host address.  So the host asks the runtime where the array lives on the CURRENT device
+ * (cudaGetSymbolAddress), once per device, and passes that address to the kernel.  That lookup happens in the first
+ * call on each device; make that first call outside any stream capture. */
+
+#define SV_STATIC_SLOTS 304u                        /* two waves of 148 blocks, and a little */
+#define SV_STATIC_TICKETS 256u
+#define SV_STATIC_SLOT_FLOATS (16u * (256u + 2u))   /* a slot: up to 16 heads of (m, l, acc[256]) */
+#define SV_STATIC_FLOATS (SV_STATIC_SLOTS * SV_STATIC_SLOT_FLOATS)
+
+static __device__ __align__(256) float g_static_scratch[SV_STATIC_FLOATS + SV_STATIC_TICKETS + 64];
+
+struct StaticScratch { float* base; bool ready; };
+static StaticScratch g_static[DEVICES_MAX];
+
+/* The device address of the array on the current device, looked up once per device. */
+static cudaError_t static_scratch_address(float** out) {
+    int d = 0;
+    cudaError_t e = cudaGetDevice(&d);
+    if (e != cudaSuccess) return e;
+    if (d < 0 || d >= DEVICES_MAX) return cudaErrorInvalidDevice;
+    if (!g_static[d].ready) {
+        void* ptr = nullptr;
+        if ((e = cudaGetSymbolAddress(&ptr, g_static_scratch)) != cudaSuccess) return e;
+        g_static[d].base = (float*)ptr;
+        g_static[d].ready = true;
+    }
+    *out = g_static[d].base;
+    return cudaSuccess;
+}
+
+/* 0 ok · 1 the shapes are outside the kernel's fit · 2 the work does not fit the fixed scratch · 3 the runtime refused;
+ * `detail` receives the runtime's error or the slots that would have been needed. */
+int decode_launch_static(const DecodeCall& c0, uint32_t* detail) {
+    DecodeCall c = c0;
+    c.items = nullptr; c.page_table = nullptr; c.seq_lens = nullptr; c.seqs = 1; c.kv_rows = c.length;
+    if (!decode_fits(c)) return 1;
+    const uint32_t group = c.q_heads / c.kv_heads, hpb = heads_per_block_for(group), hb = (group + hpb - 1) / hpb;
+    const uint32_t lanes = c.kv_heads * hb, tiles = (c.length + BT - 1) / BT;
+    if (lanes > SV_STATIC_TICKETS || lanes > SV_STATIC_SLOTS) { *detail = lanes; return 2; }
+    uint32_t ns = c.nsplit, hb2 = hb;
+    if (ns == 0) {
+        decode_auto_split(c.length, c.q_heads, c.kv_heads, c.head_dim, device_sm_count(), &ns, &hb2);
+        if (ns * lanes > SV_STATIC_SLOTS) ns = SV_STATIC_SLOTS / lanes;      /* fewer, longer splits still fit */
+    }
+    if (ns > tiles) ns = tiles;
+    if (ns < 1u) ns = 1u;
+    const uint32_t chunk = (tiles + ns - 1) / ns;
+    ns = (tiles + chunk - 1) / chunk;
+    if (ns > 1024u || (uint64_t)ns * lanes > SV_STATIC_SLOTS) { *detail = ns * lanes; return 2; }
+
+    float* base = nullptr;
+    cudaError_t e = static_scratch_address(&base);
+    if (e != cudaSuccess) { *detail = (uint32_t)e; return 3; }
+    unsigned int* tickets = (unsigned int*)(base + SV_STATIC_FLOATS);
+    unsigned int* status = tickets + SV_STATIC_TICKETS;
+    /* whatever an earlier call left in the tickets (a launch that failed half way, say) must not count as arrivals */
+    if ((e = cudaMemsetAsync(tickets, 0, SV_STATIC_TICKETS * sizeof(unsigned int), c.stream)) != cudaSuccess) { *detail = (uint32_t)e; return 3; }
+
+    CUtensorMap km, vm;
+    const uint64_t cols = (uint64_t)c.kv_heads * c.head_dim, stride = cols * 2u;
+    const bool bf = c.dtype == SV_DTYPE_BF16;
+    if (!make_map_2d_sw128(&km, c.k, cols, c.kv_rows, stride, 64u, BT, bf) || !make_map_2d_sw128(&vm, c.v, cols, c.kv_rows, stride, 64u, BT, bf)) {
+        *detail = (uint32_t)cudaErrorInvalidValue; return 3;
+    }
+    DecodeParams P;
+    P.o = c.o; P.res = c.res; P.q = (const uint16_t*)c.q;
+    P.partials = base; P.tickets = tickets; P.items = nullptr; P.page_table = nullptr; P.seq_lens = nullptr;
+    P.over = c.over; P.status = status;
+    P.table_stride = 0; P.page_pos = 0;
+    P.q_heads = c.q_heads; P.kv_heads = c.kv_heads; P.group = group;
+    P.length = c.length; P.nsplit = ns; P.head_blocks = hb; P.heads_per_block = hpb;
+    P.slot_floats = c.head_dim + 2u;
+    P.scale_log2 = (1.0f / sqrtf((float)c.head_dim)) * SV_LOG2E;
+    const uint32_t blocks = ns * lanes;
+    const int nht = hpb == 8 ? 1 : 2;
+    e = cudaErrorInvalidValue;
+#define SV_STATIC_CASE(DD, TT) e = (nht == 1) ? launch_one<DD, TT, 1>(km, vm, P, blocks, c.stream) : launch_one<DD, TT, 2>(km, vm, P, blocks, c.stream)
+    if (c.dtype == SV_DTYPE_FP16) {
+        if (c.head_dim == 64) SV_STATIC_CASE(64, SV_DTYPE_FP16); else if (c.head_dim == 128) SV_STATIC_CASE(128, SV_DTYPE_FP16); else SV_STATIC_CASE(256, SV_DTYPE_FP16);
+    } else {
+        if (c.head_dim == 64) SV_STATIC_CASE(64, SV_DTYPE_BF16); else if (c.head_dim == 128) SV_STATIC_CASE(128, SV_DTYPE_BF16); else SV_STATIC_CASE(256, SV_DTYPE_BF16);
+    }
+#undef SV_STATIC_CASE
+    if (e != cudaSuccess) { *detail = (uint32_t)e; return 3; }
+    return 0;
+}
+
+}  // namespace sv
+
+/* Declared in include/silvann_b200.h.  It lives in this file because the scratch array does: only a translation unit
+ * that defines a __device__ array can ask the runtime for its address. */
+extern "C" __attribute__((visibility("default")))
+int silvann_b200_decode_noalloc(void* o, float* res, const void* q, const void* k, const void* v, uint64_t q_heads, uint64_t kv_heads,
+                                uint64_t head_dim, uint64_t length, uint32_t nsplit, int dtype, unsigned int* over, void* stream,
+                                char* message, uint32_t message_bytes) {
+    auto say = [&](const char* fmt, unsigned long long a, unsigned long long b) {
+        if (message && message_bytes) snprintf(message, message_bytes, fmt, a, b);
+    };
+    if (message && message_bytes) message[0] = 0;
+    if (!q || !k || !v || (!o && !res)) { say("decode_noalloc: a null operand", 0, 0); return 1; }
+    if (dtype != SV_DTYPE_FP16 && dtype != SV_DTYPE_BF16) { say("decode_noalloc: dtype %llu", (unsigned long long)dtype, 0); return 1; }
+    if (q_heads == 0 || kv_heads == 0 || q_heads % kv_heads != 0 || q_heads > 65535) { say("decode_noalloc: %llu query heads do not divide over %llu kv heads", q_heads, kv_heads); return 1; }
+    if (length == 0 || length > 0x7FFFFFFFull) { say("decode_noalloc: length %llu", length, 0); return 1; }
+    sv::DecodeCall c;
+    memset(&c, 0, sizeof c);
+    c.o = o; c.res = res; c.q = q; c.k = k; c.v = v;
+    c.q_heads = (uint32_t)q_heads; c.kv_heads = (uint32_t)kv_heads; c.head_dim = (uint32_t)head_dim; c.length = (uint32_t)length;
+    c.nsplit = nsplit; c.dtype = dtype; c.over = over; c.stream = (cudaStream_t)stream;
+    uint32_t detail = 0;
+    switch (sv::decode_launch_static(c, &detail)) {
+        case 0: return 0;
+        case 1: say("decode_noalloc: head_dim %llu, a group of %llu heads, or an operand's alignment is outside the kernel's fit", head_dim, q_heads / kv_heads); return 1;
+        case 2: say("decode_noalloc: this call needs %llu scratch slots and the fixed scratch holds %llu; use fewer splits or silvann_b200_decode", detail, (unsigned long long)SV_STATIC_SLOTS); return 1;
+        default: say("decode_noalloc: the CUDA runtime answered error %llu", detail, 0); (void)cudaGetLastError(); return 2;
+    }
+}
+

@@ -14,7 +14,7 @@ OK, E_ARGUMENT, E_CUDA, E_TIMEOUT, E_STATE = 0, 1, 2, 3, 4
 COUNTERS = ("fused_decode", "fused_residual", "fused_prefill", "flushed", "refused", "deltanet", "launches", "ext_calls")
 EXPORTS = (
     "silvann_silicon_family_get", "silvann_b200_last_error", "silvann_b200_counters_read", "silvann_b200_device_status",
-    "silvann_b200_decode", "silvann_b200_merge", "silvann_b200_finish", "silvann_b200_plan_create",
+    "silvann_b200_decode", "silvann_b200_decode_noalloc", "silvann_b200_merge", "silvann_b200_finish", "silvann_b200_plan_create",
     "silvann_b200_plan_destroy", "silvann_b200_plan_decode", "silvann_b200_plan_info", "silvann_b200_paged_decode", "silvann_b200_paged_append",
     "silvann_b200_prefill", "silvann_b200_deltanet",
 )
@@ -47,6 +47,7 @@ def lib():
             "silvann_b200_counters_read": [vp, u32, i32],
             "silvann_b200_device_status": [vp, i32],
             "silvann_b200_decode": [vp, vp, vp, vp, vp, u64, u64, u64, u64, u32, i32, vp, vp],
+            "silvann_b200_decode_noalloc": [vp, vp, vp, vp, vp, u64, u64, u64, u64, u32, i32, vp, vp, C.c_char_p, u32],
             "silvann_b200_merge": [vp, vp, vp, u64, u64, vp],
             "silvann_b200_finish": [vp, vp, u64, u64, i32, vp, vp],
             "silvann_b200_plan_create": [vp],
@@ -85,6 +86,16 @@ def device_status(clear: bool = True) -> int:
 def decode(o, res, q, k, v, q_heads, kv_heads, head_dim, length, dtype=FP16, nsplit=0, over=None, stream=None):
     _check(lib().silvann_b200_decode(addr(o), addr(res), addr(q), addr(k), addr(v), q_heads, kv_heads, head_dim, length,
                                      nsplit, dtype, addr(over), stream))
+
+
+def decode_noalloc(o, res, q, k, v, q_heads, kv_heads, head_dim, length, dtype=FP16, nsplit=0, over=None, stream=None):
+    """silvann_b200_decode_noalloc: the same decode with its scratch in a fixed array inside the library, for callers
+    that cannot let a library allocate.  Raises B200Error with the entry point's own message when it refuses."""
+    msg = C.create_string_buffer(256)
+    code = lib().silvann_b200_decode_noalloc(addr(o), addr(res), addr(q), addr(k), addr(v), q_heads, kv_heads, head_dim, length,
+                                             nsplit, dtype, addr(over), stream, msg, 256)
+    if code != OK:
+        raise B200Error(code, msg.value.decode())
 
 
 def merge(into, a, b, q_heads, head_dim, stream=None):
