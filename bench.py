@@ -392,7 +392,7 @@ def run_ours(args):
     if rank == 0:
         achieved = wl.kv_bytes / per_launch_ms / 1e6
         line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
-                            "traffic": TRAFFIC_BYTES_PER_LAUNCH, "peak_source": pk["source"], "kernel": "sv::decode_kernel<256, bf16, 1>",
+                            "traffic": int(wl.kv_bytes * TRAFFIC_PER_ALGORITHMIC_BYTE), "peak_source": pk["source"], "kernel": "sv::decode_kernel<256, bf16, 1>",
                             "algorithmic_bytes_per_launch": wl.kv_bytes}
         if world == 1:
             line["cpu_baseline"] = cpu_baseline_paged(wl)
@@ -406,9 +406,10 @@ def run_ours(args):
         print(json.dumps(line))
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the ncu capture summarised
-# under profiles/ (scaled to a full launch by positions); None until a capture exists.
-TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel: the ncu capture of the same kernel on
+# a smaller batch (profiles/decode_kernel_paged_small.md: 374.9 MB of traffic for 369.0 MB of algorithmic bytes, ratio
+# 1.016) scaled to the full launch by positions — traffic is one pass over K and V, so it grows in proportion.
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.016
 
 
 # ---------------------------------------------------------------------------------------------------------------------
@@ -462,6 +463,66 @@ def run_reference(args):
     }))
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# small single-kernel cases, sized for a profiler capture (a few hundred MB on the device, a handful of launches)
+# ---------------------------------------------------------------------------------------------------------------------
+
+def run_case(args):
+    import torch
+    import silvann_b200
+    from silvann_b200 import ext, workloads
+    torch.cuda.set_device(0)
+    fam = silvann_b200.family()
+    assert fam.sys.bind_device(0) == 1
+    gen = torch.Generator(device="cuda"); gen.manual_seed(5)
+    name, steps = args.case, args.steps
+    if name == "paged_small":
+        # configuration 3's shape with 8 sequences of up to 40,000 positions: ~0.3 GB of KV a launch, larger than L2
+        L = workloads.config3_layout(seqs=8, lo=8000, hi=40000)
+        shape = (L.pool_pages, workloads.PAGE_POSITIONS, L.kv_heads, L.head_dim)
+        kp = torch.randn(shape, generator=gen, device="cuda", dtype=torch.bfloat16)
+        vp = torch.randn(shape, generator=gen, device="cuda", dtype=torch.bfloat16)
+        q = torch.randn((8, L.q_heads, L.head_dim), generator=gen, device="cuda", dtype=torch.bfloat16)
+        o = torch.zeros_like(q)
+        table = torch.from_numpy(np.maximum(L.page_table, 0)).cuda()
+        plan = ext.Plan(); plan.plan(L.seq_lens, L.q_heads, L.kv_heads, L.head_dim)
+        fn = lambda: plan.decode(o, None, q, kp, vp, L.pool_pages, workloads.PAGE_POSITIONS, table, L.page_table.shape[1], ext.BF16)
+        work, unit = L.kv_bytes, "bytes"
+    elif name == "long_small":
+        # configuration 4's shape (32q/4kv, d128, bf16), 131,072 positions: 268 MB of KV a launch
+        qh, kvh, d, n = 32, 4, 128, 131072
+        k = torch.randn((n, kvh, d), generator=gen, device="cuda", dtype=torch.bfloat16)
+        v = torch.randn((n, kvh, d), generator=gen, device="cuda", dtype=torch.bfloat16)
+        q = torch.randn((qh, d), generator=gen, device="cuda", dtype=torch.bfloat16)
+        o = torch.zeros_like(q)
+        fn = lambda: ext.decode(o, None, q, k, v, qh, kvh, d, n, ext.BF16)
+        work, unit = 2 * n * kvh * d * 2, "bytes"
+    elif name == "deltanet_64":
+        heads, d, seqs = 32, 128, 64
+        S = torch.zeros((seqs, heads, d, d), device="cuda", dtype=torch.float32)
+        conved = torch.randn((seqs, 1, 3 * heads * d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.1
+        z = torch.randn((seqs, 1, heads * d), generator=gen, device="cuda", dtype=torch.bfloat16)
+        beta = torch.rand((seqs, 1, heads), generator=gen, device="cuda").to(torch.bfloat16)
+        g = (-torch.rand((seqs, 1, heads), generator=gen, device="cuda")).to(torch.bfloat16)
+        w = torch.ones(d, device="cuda", dtype=torch.bfloat16)
+        o = torch.zeros((seqs, 1, heads * d), device="cuda", dtype=torch.bfloat16)
+        fn = lambda: ext.deltanet(S, conved, z, beta, g, w, o, heads, heads, d, 1, seqs, 0, ext.BF16)
+        work, unit = seqs * (2 * heads * d * d * 4 + 3 * heads * d * 2 + 2 * heads * d * 2 + 2 * heads * 2 + d * 2), "bytes"
+    elif name == "prefill_small":
+        qh, kvh, d, T = 16, 2, 256, 2048
+        q = torch.randn((T, qh, d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.5
+        k = torch.randn((T, kvh, d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.5
+        v = torch.randn((T, kvh, d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.5
+        o = torch.zeros_like(q)
+        fn = lambda: ext.prefill(o, q, k, v, qh, kvh, d, 0, T, ext.BF16)
+        work, unit = 4.0 * qh * d * T * (T + 1) / 2, "flop"
+    else:
+        raise SystemExit(f"unknown case {name}")
+    ms = time_loop(torch, fn, steps, 1)
+    print(json.dumps({"case": name, "steps": steps, "ms_per_launch": ms, "work_per_launch": work, "work_unit": unit,
+                      "rate": work / ms / 1e6, "rate_unit": "GB/s" if unit == "bytes" else "GFLOP/s", "device_status": ext.device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -469,8 +530,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the secondary configurations (faster; used under profilers)")
+    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, deltanet_64, prefill_small)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
