@@ -1,6 +1,375 @@
-/* prefill.cu — placeholder until the tcgen05 kernel lands: nothing fits, so callers take the three-door path. */
+/* prefill.cu — causal grouped-query prefill attention on the 5th-generation tensor cores (tcgen05, TMEM), sm_100a.
+ *
+ * One kernel replaces the reference's three prompt doors — attention_causal_scores_grouped, attention_causal_softmax,
+ * attention_causal_mix (engine/src/packages/nn/gpu/kernels/kernels.cuh:1028-1081, 2051-2060) — and never writes the
+ * rows x (first + rows) fp32 weights buffer they pass between them.  Row r of the call is position first + r and attends
+ * cache rows 0 .. first + r; query head h reads kv head h / (q_heads / kv_heads).
+ *
+ * A block owns 128 query rows of one head.  Roles: warp 0 issues TMA loads (Q once, then a ring of K and V tiles of 64
+ * keys, 128-byte swizzle); one thread of warp 1 issues the MMAs — S = Q·K^T into one of two TMEM buffers (M 128, N 64,
+ * K = head_dim in steps of 16) and O += P·V (M 128, N = head_dim, K 64) with the accumulator O resident in TMEM for
+ * the whole row block; warps 2-5 (one thread per query row, its row of S read straight from TMEM with tcgen05.ld, so
+ * row max and row sum need no shuffles) run the online softmax, write P as 16-bit into a swizzled shared tile for the
+ * second MMA, rescale O in TMEM only when a row's maximum has grown by more than 2^8 (the reference maximum is otherwise
+ * kept, which is exact: every weight and the normaliser are relative to the same reference), and finally divide and
+ * store.  S for tile j+1 is issued before the softmax of tile j has finished, so the tensor pipe and the softmax overlap.
+ *
+ * Every mbarrier wait is bounded; a wait that runs out raises the block's abort flag, ORs "B2TO" into the device status
+ * word, and every role falls through to the common exit, where TMEM is released.  No multicast, no cluster.
+ *
+ * Algorithmic flops: 4 · q_heads · head_dim · rows·(rows+1)/2 (+ first·rows terms) — QK^T and PV, 2 flop a MAC. */
+#include "common.cuh"
 #include "kernels.h"
+#include "tensormap.cuh"
+
 namespace sv {
-bool prefill_fits(const PrefillCall&) { return false; }
-cudaError_t prefill_launch(const PrefillCall&) { return cudaErrorNotSupported; }
+
+static constexpr int PF_BM = 128;      /* query rows per block */
+static constexpr int PF_BN = 64;       /* keys per tile */
+static constexpr int PF_THREADS = 192; /* warp 0 TMA, warp 1 MMA, warps 2-5 softmax */
+
+/* ---- tcgen05 wrappers ---------------------------------------------------------------------------------------- */
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+/* D[tmem] (+)= A[smem desc] · B[smem desc], 16-bit inputs, fp32 accumulate; accumulate == 0 overwrites D. */
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+/* 32 consecutive fp32 columns of this thread's TMEM lane. */
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+          "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+          "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+          "r"(r[30]), "r"(r[31]) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+/* Shared-memory matrix descriptor, 128-byte swizzle: start address, leading and stride byte offsets in 16-byte units,
+ * descriptor version 1 (bit 46), layout type SWIZZLE_128B = 2 (bits 61-63). */
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+/* Instruction descriptor for kind::f16: fp32 accumulator, A and B of the given 16-bit format, A K-major, B K-major or
+ * MN-major, N >> 3 at bit 17, M >> 4 at bit 24. */
+__host__ __device__ constexpr uint32_t idesc_f16(int bf16, int b_mn_major, int m, int n) {
+    return (1u << 4) | ((uint32_t)bf16 << 7) | ((uint32_t)bf16 << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+template <int D> struct PrefillCfg {
+    static constexpr int BOXES = D / 64;
+    static constexpr int Q_BYTES = PF_BM * D * 2;
+    static constexpr int KV_TILE_BYTES = PF_BN * D * 2;              /* one K or one V tile */
+    static constexpr int KV_BOX_BYTES = PF_BN * 128;
+    static constexpr int Q_BOX_BYTES = PF_BM * 128;
+    static constexpr int STAGES = (D >= 256) ? 2 : 4;
+    static constexpr int P_BYTES = PF_BM * PF_BN * 2;
+    static constexpr int TMEM_COLS = (D + 2 * PF_BN <= 256) ? 256 : 512;
+    static constexpr size_t SMEM = 1024 + Q_BYTES + 2 * STAGES * KV_TILE_BYTES + P_BYTES + 256;
+};
+
+struct PrefillParams {
+    uint16_t* o;
+    unsigned int* over;
+    unsigned int* status;
+    uint32_t q_heads, kv_heads, group;
+    uint32_t first, rows, q_tiles;
+    float scale_log2;
+};
+
+template <int D, int DT>
+__global__ void __launch_bounds__(PF_THREADS, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+               const __grid_constant__ CUtensorMap vmap, const PrefillParams P) {
+    using Cfg = PrefillCfg<D>;
+    using E = Elem<DT>;
+    constexpr int ST = Cfg::STAGES;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_s = smem;
+    uint8_t* k_s = q_s + Cfg::Q_BYTES;
+    uint8_t* v_s = k_s + ST * Cfg::KV_TILE_BYTES;
+    uint8_t* p_s = v_s + ST * Cfg::KV_TILE_BYTES;
+    uint64_t* bars = (uint64_t*)(p_s + Cfg::P_BYTES);
+    uint64_t* q_full = bars;                 /* 1 */
+    uint64_t* k_full = bars + 1;             /* ST */
+    uint64_t* v_full = k_full + ST;          /* ST */
+    uint64_t* k_empty = v_full + ST;         /* ST: the S MMA that read the stage has completed */
+    uint64_t* pv_done = k_empty + ST;        /* ST: the PV MMA of the stage's tile has completed (V stage and P free) */
+    uint64_t* s_full = pv_done + ST;         /* 2 */
+    uint64_t* s_free = s_full + 2;           /* 2 */
+    uint64_t* p_full = s_free + 2;           /* 1 */
+    uint32_t* tmem_slot = (uint32_t*)(p_full + 1);
+    volatile uint32_t* abort_flag = (volatile uint32_t*)(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int qt = (int)P.q_tiles - 1 - (int)(blockIdx.x / P.q_heads);       /* heaviest row blocks first */
+    const int h = blockIdx.x % P.q_heads, g = h / P.group;
+    const int row0 = qt * PF_BM;
+    const int keys_total = (int)(P.first + P.rows);
+    int last_key = (int)P.first + row0 + PF_BM - 1;                          /* the last row's own position */
+    if (last_key > keys_total - 1) last_key = keys_total - 1;
+    const int nt = last_key / PF_BN + 1;                                     /* KV tiles this row block walks */
+
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < ST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&pv_done[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_free[b], 4); }
+        mbar_init(p_full, 4);
+        *abort_flag = 0u;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t t_o = tmem;                       /* columns [0, D): the output accumulator */
+    const uint32_t t_s0 = tmem + D;                  /* two score buffers of PF_BN columns */
+
+    if (warp == 0) {
+        /* ---------------- TMA producer ---------------- */
+        if (lane == 0) {
+            tma_prefetch_desc(&qmap); tma_prefetch_desc(&kmap); tma_prefetch_desc(&vmap);
+            mbar_expect_tx(q_full, Cfg::Q_BYTES);
+#pragma unroll
+            for (int c = 0; c < Cfg::BOXES; ++c) tma_load_2d(q_s + c * Cfg::Q_BOX_BYTES, &qmap, q_full, h * D + c * 64, row0);
+            for (int j = 0; j < nt; ++j) {
+                const int s = j % ST, use = j / ST;
+                if (use > 0 && !mbar_wait(&k_empty[s], (use - 1) & 1, abort_flag, P.status)) break;
+                mbar_expect_tx(&k_full[s], Cfg::KV_TILE_BYTES);
+#pragma unroll
+                for (int c = 0; c < Cfg::BOXES; ++c)
+                    tma_load_2d(k_s + s * Cfg::KV_TILE_BYTES + c * Cfg::KV_BOX_BYTES, &kmap, &k_full[s], g * D + c * 64, j * PF_BN);
+                if (use > 0 && !mbar_wait(&pv_done[s], (use - 1) & 1, abort_flag, P.status)) break;
+                mbar_expect_tx(&v_full[s], Cfg::KV_TILE_BYTES);
+#pragma unroll
+                for (int c = 0; c < Cfg::BOXES; ++c)
+                    tma_load_2d(v_s + s * Cfg::KV_TILE_BYTES + c * Cfg::KV_BOX_BYTES, &vmap, &v_full[s], g * D + c * 64, j * PF_BN);
+            }
+        }
+    } else if (warp == 1) {
+        /* ---------------- MMA issuer ---------------- */
+        if (lane == 0) {
+            constexpr uint32_t IDESC_S = idesc_f16(DT == SV_DTYPE_BF16, 0, PF_BM, PF_BN);
+            constexpr uint32_t IDESC_O = idesc_f16(DT == SV_DTYPE_BF16, 1, PF_BM, D);
+            const uint32_t q_a = smem_u32(q_s), k_a = smem_u32(k_s), v_a = smem_u32(v_s), p_a = smem_u32(p_s);
+            bool ok = mbar_wait(q_full, 0, abort_flag, P.status);
+            auto issue_s = [&](int j) -> bool {
+                const int s = j % ST, b = j & 1;
+                if (!mbar_wait(&k_full[s], (j / ST) & 1, abort_flag, P.status)) return false;
+                if (j >= 2 && !mbar_wait(&s_free[b], ((j - 2) >> 1) & 1, abort_flag, P.status)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint64_t ad = smem_desc_sw128(q_a + (kk / 4) * Cfg::Q_BOX_BYTES + (kk % 4) * 32, 16, 1024);
+                    const uint64_t bd = smem_desc_sw128(k_a + s * Cfg::KV_TILE_BYTES + (kk / 4) * Cfg::KV_BOX_BYTES + (kk % 4) * 32, 16, 1024);
+                    tc_mma(t_s0 + b * PF_BN, ad, bd, IDESC_S, kk > 0 ? 1u : 0u);
+                }
+                tc_commit(&k_empty[s]);
+                tc_commit(&s_full[b]);
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int j = 0; ok && j < nt; ++j) {
+                if (j + 1 < nt && !issue_s(j + 1)) { ok = false; break; }
+                const int s = j % ST;
+                if (!mbar_wait(p_full, j & 1, abort_flag, P.status)) break;
+                if (!mbar_wait(&v_full[s], (j / ST) & 1, abort_flag, P.status)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < PF_BN / 16; ++kk) {
+                    const uint64_t ad = smem_desc_sw128(p_a + kk * 32, 16, 1024);
+                    /* V is [key][value column]: MN-major for B; 64-column groups are a box apart (LBO), 8-key groups
+                     * 1024 bytes apart (SBO); sixteen keys a step */
+                    const uint64_t bd = smem_desc_sw128(v_a + s * Cfg::KV_TILE_BYTES + kk * 2048, Cfg::KV_BOX_BYTES, 1024);
+                    tc_mma(t_o, ad, bd, IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                tc_commit(&pv_done[s]);
+            }
+        }
+    } else {
+        /* ---------------- softmax, correction, epilogue: one thread per query row ---------------- */
+        const int quad = warp & 3;                                  /* the TMEM lanes this warp may touch */
+        const int r = quad * 32 + lane;                             /* row within the block */
+        const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+        const int pos = (int)P.first + row0 + r;                    /* this row's position: keys 0..pos */
+        float m_ref = -INFINITY, l = 0.f;
+        bool alive = true;
+        for (int j = 0; j < nt; ++j) {
+            const int b = j & 1;
+            /* the TMEM loads below are warp-collective: the warp leaves the loop together or not at all */
+            if (!__all_sync(0xffffffffu, mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag, P.status))) { alive = false; break; }
+            tc_fence_after();
+            uint32_t sv[2][32];
+            tmem_ld32(t_s0 + b * PF_BN + lane_off, sv[0]);
+            tmem_ld32(t_s0 + b * PF_BN + 32 + lane_off, sv[1]);
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_free[b]);
+
+            const int key0 = j * PF_BN;
+            const bool diag = key0 + PF_BN - 1 > pos;               /* some keys of this tile lie past the row's position */
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+                float x = __uint_as_float(sv[c >> 5][c & 31]) * P.scale_log2;
+                if (diag && key0 + c > pos) x = -INFINITY;
+                sv[c >> 5][c & 31] = __float_as_uint(x);
+                mx = fmaxf(mx, x);
+            }
+            /* keep the reference maximum unless this tile's exceeds it by more than 8 (weights then stay <= 2^8) */
+            float f = 1.f;
+            const bool grow = (mx > m_ref + 8.f) || (m_ref == -INFINITY && mx != -INFINITY);
+            if (grow) { f = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - mx); m_ref = mx; }
+            const float mu = (m_ref == -INFINITY) ? 0.f : m_ref;
+            uint32_t pk[32];
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 64; c += 2) {
+                const float p0 = fast_exp2(__uint_as_float(sv[c >> 5][c & 31]) - mu);
+                const float p1 = fast_exp2(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]) - mu);
+                const uint32_t w = E::pack2(p0, p1);
+                const float2 back = E::unpack2(w);                  /* the normaliser sums what the MMA will see */
+                sum += back.x + back.y;
+                pk[c >> 1] = w;
+            }
+            l = l * f + sum;
+
+            /* O must not be touched, and P not overwritten, while the previous PV MMA may still be running */
+            if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) % ST], ((j - 1) / ST) & 1, abort_flag, P.status))) { alive = false; break; }
+            if (j > 0 && __any_sync(0xffffffffu, f != 1.f)) {
+                tc_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t ov[32];
+                    tmem_ld32(t_o + c0 + lane_off, ov);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * f);
+                    tmem_st32(t_o + c0 + lane_off, ov);
+                }
+                tmem_wait_st();
+                tc_fence_before();
+            }
+            /* P row r, 64 keys = 8 chunks of 16 bytes, in the 128-byte-swizzled K-major tile the MMA descriptor names */
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+                *reinterpret_cast<uint4*>(p_s + swz128(r, ch)) = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+        }
+        /* epilogue: O / l, rounded, to global — a row is contiguous in the output */
+        if (alive && __all_sync(0xffffffffu, mbar_wait(&pv_done[(nt - 1) % ST], ((nt - 1) / ST) & 1, abort_flag, P.status))) {
+            tc_fence_after();
+            const float inv = 1.0f / l;
+            const int grow_ = row0 + r;
+            bool hit = false;
+            uint16_t* orow = P.o + ((size_t)grow_ * P.q_heads + h) * D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t ov[32];
+                tmem_ld32(t_o + c0 + lane_off, ov);
+                tmem_wait_ld();
+                if (grow_ < (int)P.rows) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const uint16_t lo = E::from_float(__uint_as_float(ov[c + 2 * u]) * inv, hit);
+                            const uint16_t hi = E::from_float(__uint_as_float(ov[c + 2 * u + 1]) * inv, hit);
+                            w[u] = (uint32_t)lo | ((uint32_t)hi << 16);
+                        }
+                        *reinterpret_cast<uint4*>(orow + c0 + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+            if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
+            tc_fence_before();
+        }
+    }
+
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, Cfg::TMEM_COLS); }
+}
+
+/* ---------------------------------------------------------------------------------------------------------- */
+
+bool prefill_fits(const PrefillCall& c) {
+    if (c.head_dim != 64 && c.head_dim != 128 && c.head_dim != 256) return false;
+    if (c.kv_heads == 0 || c.q_heads % c.kv_heads != 0) return false;
+    if (((uintptr_t)c.q | (uintptr_t)c.k | (uintptr_t)c.v | (uintptr_t)c.o) & 15u) return false;
+    if (c.rows == 0 || c.first + c.rows > 0x7FFFFF00ull) return false;
+    if ((uint64_t)((c.rows + PF_BM - 1) / PF_BM) * c.q_heads > 0x7FFFFFFFull) return false;
+    return encode_tiled_fn() != nullptr;
+}
+
+template <int D, int DT>
+static cudaError_t launch_prefill(const PrefillCall& c) {
+    using Cfg = PrefillCfg<D>;
+    const bool bf = DT == SV_DTYPE_BF16;
+    CUtensorMap qm, km, vm;
+    const uint64_t qcols = (uint64_t)c.q_heads * D, kcols = (uint64_t)c.kv_heads * D;
+    if (!make_map_2d_sw128(&qm, c.q, qcols, c.rows, qcols * 2, 64u, PF_BM, bf)) return cudaErrorInvalidValue;
+    if (!make_map_2d_sw128(&km, c.k, kcols, c.first + c.rows, kcols * 2, 64u, PF_BN, bf)) return cudaErrorInvalidValue;
+    if (!make_map_2d_sw128(&vm, c.v, kcols, c.first + c.rows, kcols * 2, 64u, PF_BN, bf)) return cudaErrorInvalidValue;
+    PrefillParams P;
+    P.o = (uint16_t*)c.o; P.over = c.over; P.status = device_status_word();
+    P.q_heads = c.q_heads; P.kv_heads = c.kv_heads; P.group = c.q_heads / c.kv_heads;
+    P.first = (uint32_t)c.first; P.rows = (uint32_t)c.rows; P.q_tiles = (uint32_t)((c.rows + PF_BM - 1) / PF_BM);
+    P.scale_log2 = (1.0f / sqrtf((float)D)) * SV_LOG2E;
+    static bool attr_set[64] = {};
+    int d = 0; cudaGetDevice(&d);
+    if (d >= 0 && d < 64 && !attr_set[d]) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_kernel<D, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
+        if (e != cudaSuccess) return e;
+        attr_set[d] = true;
+    }
+    prefill_kernel<D, DT><<<P.q_tiles * c.q_heads, PF_THREADS, Cfg::SMEM, c.stream>>>(qm, km, vm, P);
+    note_launch(1);
+    return cudaGetLastError();
+}
+
+cudaError_t prefill_launch(const PrefillCall& c) {
+#define SV_PF(DD) (c.dtype == SV_DTYPE_BF16 ? launch_prefill<DD, SV_DTYPE_BF16>(c) : launch_prefill<DD, SV_DTYPE_FP16>(c))
+    if (c.head_dim == 64) return SV_PF(64);
+    if (c.head_dim == 128) return SV_PF(128);
+    if (c.head_dim == 256) return SV_PF(256);
+#undef SV_PF
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace sv
