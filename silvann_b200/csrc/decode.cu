@@ -23,15 +23,16 @@
 
 namespace sv {
 
-static constexpr int BT = SV_DECODE_TILE;  /* positions per tile */
-static constexpr int NW = 4;               /* consumer warps; each owns 16 positions of a tile */
-
+/* Consumer warps a block, each owning 16 positions of a tile: 4 at head_dim 256 (tiles of 64 positions, 64 KB a stage),
+ * 8 at head_dim 128 and 64 (tiles of 128 positions), so that the per-tile softmax work keeps pace with a stage's bytes. */
 template <int D> struct DecodeCfg {
+    static constexpr int NW = (D >= 256) ? 4 : 8;
+    static constexpr int BT = 16 * NW;                   /* positions per tile */
     static constexpr int BOXES = D / 64;                 /* 64-column (128-byte) boxes per row */
     static constexpr int BOX_BYTES = BT * 128;
     static constexpr int K_BYTES = BOXES * BOX_BYTES;
     static constexpr int STAGE_BYTES = 2 * K_BYTES;      /* K then V */
-    static constexpr int STAGES = (D == 64) ? 8 : (D == 128) ? 6 : 3;
+    static constexpr int STAGES = (D == 64) ? 6 : 3;     /* 192 KB in flight per SM */
 };
 
 struct DecodeParams {
@@ -53,14 +54,15 @@ struct DecodeParams {
 };
 
 template <int D, int DT, int NHT>
-__global__ void __launch_bounds__((NW + 1) * 32, 1)
+__global__ void __launch_bounds__((DecodeCfg<D>::NW + 1) * 32, 1)
 decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
               const DecodeParams P) {
     using Cfg = DecodeCfg<D>;
     using E = Elem<DT>;
+    constexpr int NW = Cfg::NW, BT = Cfg::BT;
     constexpr int HPB = 8 * NHT;            /* heads per block */
     constexpr int KS = D / 16;              /* k-steps of the score product = m-tiles of the value product */
-    constexpr bool QREG = !(NHT == 2 && D >= 256);
+    constexpr bool QREG = !(NHT == 2 && D >= 128);   /* 16 heads at head_dim >= 128: query fragments are re-read from shared memory */
     constexpr int Q_BYTES = Cfg::BOXES * HPB * 128;
 
     extern __shared__ uint8_t smem_raw[];
@@ -425,13 +427,13 @@ bool decode_fits(const DecodeCall& c) {
     if (((uintptr_t)c.q | (uintptr_t)c.k | (uintptr_t)c.v) & 15u) return false;
     if ((c.kv_heads * c.head_dim * 2u) % 16u != 0) return false;
     if (c.kv_rows == 0 || c.kv_rows > 0x7FFFFFFFull) return false;
-    if (c.page_table && (c.page_pos == 0 || c.page_pos % BT != 0)) return false;
+    if (c.page_table && (c.page_pos == 0 || c.page_pos % decode_tile_positions(c.head_dim) != 0)) return false;
     return encode_tiled_fn() != nullptr;
 }
 
 void decode_auto_split(uint32_t length, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim, uint32_t sms,
                        uint32_t* nsplit, uint32_t* head_blocks) {
-    (void)head_dim;
+    const uint32_t BT = decode_tile_positions(head_dim);
     const uint32_t group = q_heads / kv_heads, hpb = heads_per_block_for(group), hb = (group + hpb - 1) / hpb;
     const uint32_t tiles = (length + BT - 1) / BT, lanes = kv_heads * hb;
     /* one wave of blocks when the cache is short, up to four when each block still gets a long run of tiles */
@@ -459,7 +461,7 @@ static cudaError_t launch_one(const CUtensorMap& km, const CUtensorMap& vm, cons
         if (e != cudaSuccess) return e;
         attr_set[d] = true;
     }
-    decode_kernel<D, DT, NHT><<<blocks, (NW + 1) * 32, smem, st>>>(km, vm, P);
+    decode_kernel<D, DT, NHT><<<blocks, (Cfg::NW + 1) * 32, smem, st>>>(km, vm, P);
     note_launch(1);
     return cudaGetLastError();
 }
@@ -467,6 +469,7 @@ static cudaError_t launch_one(const CUtensorMap& km, const CUtensorMap& vm, cons
 cudaError_t decode_launch(const DecodeCall& c) {
     const uint32_t group = c.q_heads / c.kv_heads, hpb = heads_per_block_for(group), hb = (group + hpb - 1) / hpb;
     CUtensorMap km, vm;
+    const uint32_t BT = decode_tile_positions(c.head_dim);
     const uint64_t cols = (uint64_t)c.kv_heads * c.head_dim, stride = cols * 2u;
     const bool bf = c.dtype == SV_DTYPE_BF16;
     if (!make_map_2d_sw128(&km, c.k, cols, c.kv_rows, stride, 64u, BT, bf)) return cudaErrorInvalidValue;
@@ -574,6 +577,7 @@ int decode_launch_static(const DecodeCall& c0, uint32_t* detail) {
     c.items = nullptr; c.page_table = nullptr; c.seq_lens = nullptr; c.seqs = 1; c.kv_rows = c.length;
     if (!decode_fits(c)) return 1;
     const uint32_t group = c.q_heads / c.kv_heads, hpb = heads_per_block_for(group), hb = (group + hpb - 1) / hpb;
+    const uint32_t BT = decode_tile_positions(c.head_dim);
     const uint32_t lanes = c.kv_heads * hb, tiles = (c.length + BT - 1) / BT;
     if (lanes > SV_STATIC_TICKETS || lanes > SV_STATIC_SLOTS) { *detail = lanes; return 2; }
     uint32_t ns = c.nsplit, hb2 = hb;

@@ -140,10 +140,11 @@ SV_EXPORT int silvann_b200_plan_decode(silvann_b200_plan* p, const int32_t* seq_
     if (head_dim != 64 && head_dim != 128 && head_dim != 256) return fail(SILVANN_B200_E_ARGUMENT, "plan_decode: head_dim %u", head_dim);
     cudaStream_t st = (cudaStream_t)stream;
     const uint32_t group = q_heads / kv_heads, hpb = group <= 8 ? 8u : 16u, hb = (group + hpb - 1) / hpb, lanes = kv_heads * hb;
+    const uint32_t TILE = sv::decode_tile_positions(head_dim);
     uint64_t tiles_total = 0, positions = 0;
     for (uint32_t s = 0; s < seqs; ++s) {
         if (seq_lens[s] <= 0) return fail(SILVANN_B200_E_ARGUMENT, "plan_decode: sequence %u has length %d", s, seq_lens[s]);
-        tiles_total += ((uint64_t)seq_lens[s] + SV_DECODE_TILE - 1) / SV_DECODE_TILE;
+        tiles_total += ((uint64_t)seq_lens[s] + TILE - 1) / TILE;
         positions += (uint64_t)seq_lens[s];
     }
     if (blocks_target == 0) blocks_target = sv::device_sm_count() * 4u;
@@ -153,7 +154,7 @@ SV_EXPORT int silvann_b200_plan_decode(silvann_b200_plan* p, const int32_t* seq_
     std::vector<sv::DecodeItem> items;
     uint32_t slots = 0, tickets = 0;
     for (uint32_t s = 0; s < seqs; ++s) {
-        const uint32_t tiles = ((uint32_t)seq_lens[s] + SV_DECODE_TILE - 1) / SV_DECODE_TILE;
+        const uint32_t tiles = ((uint32_t)seq_lens[s] + TILE - 1) / TILE;
         uint32_t ns = (uint32_t)((tiles + chunk - 1) / chunk);
         if (ns > 1024u) ns = 1024u;
         const uint32_t per = (tiles + ns - 1) / ns;
@@ -246,7 +247,7 @@ SV_EXPORT int silvann_b200_paged_decode(silvann_b200_plan* p, void* o, float* re
     if (!p || !p->ready) return fail(SILVANN_B200_E_STATE, "paged_decode: plan_decode has not run");
     if (!q || !k_pool || !v_pool || !page_table || (!o && !res)) return fail(SILVANN_B200_E_ARGUMENT, "paged_decode: a null operand");
     if (!dtype_ok(dtype)) return fail(SILVANN_B200_E_ARGUMENT, "paged_decode: dtype %d", dtype);
-    if (page_positions == 0 || page_positions % SV_DECODE_TILE != 0) return fail(SILVANN_B200_E_ARGUMENT, "paged_decode: page of %u positions is not a multiple of %d", page_positions, SV_DECODE_TILE);
+    if (page_positions == 0 || page_positions % sv::decode_tile_positions(p->head_dim) != 0) return fail(SILVANN_B200_E_ARGUMENT, "paged_decode: page of %u positions is not a multiple of %u", page_positions, sv::decode_tile_positions(p->head_dim));
     if (pool_pages == 0 || pool_pages * page_positions > 0x7FFFFFFFull) return fail(SILVANN_B200_E_ARGUMENT, "paged_decode: pool of %llu pages", (unsigned long long)pool_pages);
     sv::DecodeCall c;
     memset(&c, 0, sizeof c);

@@ -11,7 +11,7 @@ namespace sv {
 /* ---- split-KV decode (decode.cu) ------------------------------------------------------------------------ */
 
 /* One unit of decode work: query heads [head0, head0+heads) of sequence `seq`, all sharing kv head `kvh`, over KV
- * tiles [tile_begin, tile_end) of 64 positions.  Split `split` of `nsplit` for that (seq, head block); the partial
+ * tiles [tile_begin, tile_end) of decode_tile_positions(head_dim) positions.  Split `split` of `nsplit` for that (seq, head block); the partial
  * of split s is written to scratch slot `slot_base + s`, and `ticket` indexes the arrival counter of the group. */
 struct DecodeItem {
     int32_t seq, kvh, head0, heads;
@@ -19,7 +19,8 @@ struct DecodeItem {
     int32_t slot_base, ticket, pad0, pad1;
 };
 
-#define SV_DECODE_TILE 64          /* positions per KV tile */
+/* Positions per KV tile of the decode kernel: 64 at head_dim 256, 128 at head_dim 128 and 64. */
+inline uint32_t decode_tile_positions(uint32_t head_dim) { return head_dim >= 256u ? 64u : 128u; }
 #define SV_DECODE_MAX_SLOTS 2048   /* scratch partial slots per device (per plan) */
 #define SV_DECODE_MAX_TICKETS 8192
 

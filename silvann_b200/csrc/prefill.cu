@@ -26,7 +26,7 @@ namespace sv {
 
 static constexpr int PF_BM = 128;      /* query rows per block */
 static constexpr int PF_BN = 64;       /* keys per tile */
-static constexpr int PF_THREADS = 192; /* warp 0 TMA, warp 1 MMA, warps 2-5 softmax */
+static constexpr int PF_THREADS = 320; /* warp 0 TMA, warp 1 MMA, warps 2-9 softmax (two per TMEM lane quadrant) */
 
 /* ---- tcgen05 wrappers ---------------------------------------------------------------------------------------- */
 
@@ -94,7 +94,7 @@ template <int D> struct PrefillCfg {
     static constexpr int STAGES = (D >= 256) ? 2 : 4;
     static constexpr int P_BYTES = PF_BM * PF_BN * 2;
     static constexpr int TMEM_COLS = (D + 2 * PF_BN <= 256) ? 256 : 512;
-    static constexpr size_t SMEM = 1024 + Q_BYTES + 2 * STAGES * KV_TILE_BYTES + P_BYTES + 256;
+    static constexpr size_t SMEM = 1024 + Q_BYTES + 2 * STAGES * KV_TILE_BYTES + P_BYTES + 256 + 6 * PF_BM * 4;
 };
 
 struct PrefillParams {
@@ -129,8 +129,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     uint64_t* s_full = pv_done + ST;         /* 2 */
     uint64_t* s_free = s_full + 2;           /* 2 */
     uint64_t* p_full = s_free + 2;           /* 1 */
-    uint32_t* tmem_slot = (uint32_t*)(p_full + 1);
+    uint64_t* xbar = p_full + 1;             /* 4: the two softmax warps of a lane quadrant meet here once a tile */
+    uint32_t* tmem_slot = (uint32_t*)(xbar + 4);
     volatile uint32_t* abort_flag = (volatile uint32_t*)(tmem_slot + 1);
+    float* xch = (float*)(p_s + Cfg::P_BYTES + 256);         /* [6][128]: half-row maxima by tile parity, then normalisers */
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int qt = (int)P.q_tiles - 1 - (int)(blockIdx.x / P.q_heads);       /* heaviest row blocks first */
@@ -144,8 +146,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     if (tid == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < ST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&pv_done[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_free[b], 4); }
-        mbar_init(p_full, 4);
+        for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_free[b], 8); }
+        mbar_init(p_full, 8);
+        for (int x = 0; x < 4; ++x) mbar_init(&xbar[x], 2);
         *abort_flag = 0u;
         mbar_fence_init();
     }
@@ -219,8 +222,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             }
         }
     } else {
-        /* ---------------- softmax, correction, epilogue: one thread per query row ---------------- */
-        const int quad = warp & 3;                                  /* the TMEM lanes this warp may touch */
+        /* ---------------- softmax, correction, epilogue ----------------
+         * Eight warps: a warp may touch only the 32 TMEM lanes of its quadrant (warp id mod 4), so two warps share each
+         * quadrant and split every row's 64 scores in halves of 32 columns.  The two threads of a row exchange their
+         * half-row maxima through shared memory (an mbarrier per quadrant, waited for with a bound like every other wait here), keep identical reference maxima,
+         * and each carries the normaliser of its own half until the end. */
+        const int sw = warp - 2;                                    /* 0..7 */
+        const int quad = warp & 3, half = sw >> 2;
         const int r = quad * 32 + lane;                             /* row within the block */
         const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
         const int pos = (int)P.first + row0 + r;                    /* this row's position: keys 0..pos */
@@ -231,48 +239,51 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             /* the TMEM loads below are warp-collective: the warp leaves the loop together or not at all */
             if (!__all_sync(0xffffffffu, mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag, P.status))) { alive = false; break; }
             tc_fence_after();
-            uint32_t sv[2][32];
-            tmem_ld32(t_s0 + b * PF_BN + lane_off, sv[0]);
-            tmem_ld32(t_s0 + b * PF_BN + 32 + lane_off, sv[1]);
+            uint32_t sv[32];
+            tmem_ld32(t_s0 + b * PF_BN + half * 32 + lane_off, sv);
             tmem_wait_ld();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_free[b]);
 
-            const int key0 = j * PF_BN;
-            const bool diag = key0 + PF_BN - 1 > pos;               /* some keys of this tile lie past the row's position */
-            float mx = -INFINITY;
+            const int key0 = j * PF_BN + half * 32;
+            if (key0 + 31 > pos) {                                  /* keys of this half lie past the row's position */
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                float x = __uint_as_float(sv[c >> 5][c & 31]) * P.scale_log2;
-                if (diag && key0 + c > pos) x = -INFINITY;
-                sv[c >> 5][c & 31] = __float_as_uint(x);
-                mx = fmaxf(mx, x);
+                for (int c = 0; c < 32; ++c) if (key0 + c > pos) sv[c] = 0xFF800000u;   /* -inf */
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * P.scale_log2;
+            xch[(b * 2 + half) * PF_BM + r] = mx;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&xbar[quad]);
+            if (!__all_sync(0xffffffffu, mbar_wait(&xbar[quad], j & 1, abort_flag, P.status))) { alive = false; break; }
+            mx = fmaxf(mx, xch[(b * 2 + (half ^ 1)) * PF_BM + r]);
             /* keep the reference maximum unless this tile's exceeds it by more than 8 (weights then stay <= 2^8) */
             float f = 1.f;
             const bool grow = (mx > m_ref + 8.f) || (m_ref == -INFINITY && mx != -INFINITY);
             if (grow) { f = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - mx); m_ref = mx; }
             const float mu = (m_ref == -INFINITY) ? 0.f : m_ref;
-            uint32_t pk[32];
-            float sum = 0.f;
+            uint32_t pk[16];
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < 64; c += 2) {
-                const float p0 = fast_exp2(__uint_as_float(sv[c >> 5][c & 31]) - mu);
-                const float p1 = fast_exp2(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]) - mu);
+            for (int c = 0; c < 32; c += 2) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c]), P.scale_log2, -mu));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c + 1]), P.scale_log2, -mu));
                 const uint32_t w = E::pack2(p0, p1);
                 const float2 back = E::unpack2(w);                  /* the normaliser sums what the MMA will see */
-                sum += back.x + back.y;
+                sum4[(c >> 1) & 3] += back.x + back.y;
                 pk[c >> 1] = w;
             }
-            l = l * f + sum;
+            l = l * f + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
 
             /* O must not be touched, and P not overwritten, while the previous PV MMA may still be running */
             if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) % ST], ((j - 1) / ST) & 1, abort_flag, P.status))) { alive = false; break; }
             if (j > 0 && __any_sync(0xffffffffu, f != 1.f)) {
                 tc_fence_after();
 #pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 32) {
+                for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {      /* each warp of the pair half of O's columns */
                     uint32_t ov[32];
                     tmem_ld32(t_o + c0 + lane_off, ov);
                     tmem_wait_ld();
@@ -283,23 +294,28 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 tmem_wait_st();
                 tc_fence_before();
             }
-            /* P row r, 64 keys = 8 chunks of 16 bytes, in the 128-byte-swizzled K-major tile the MMA descriptor names */
+            /* P row r: this half's 32 keys = 4 chunks of 16 bytes in the 128-byte-swizzled K-major tile the MMA reads */
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch)
-                *reinterpret_cast<uint4*>(p_s + swz128(r, ch)) = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+            for (int ch = 0; ch < 4; ++ch)
+                *reinterpret_cast<uint4*>(p_s + swz128(r, half * 4 + ch)) = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
         }
-        /* epilogue: O / l, rounded, to global — a row is contiguous in the output */
+        /* epilogue: the row's normaliser is the sum of its two halves'; O / l, rounded, to global — each warp of the pair
+         * writes half of the row, which is contiguous in the output */
         if (alive && __all_sync(0xffffffffu, mbar_wait(&pv_done[(nt - 1) % ST], ((nt - 1) / ST) & 1, abort_flag, P.status))) {
             tc_fence_after();
-            const float inv = 1.0f / l;
+            xch[(4 + half) * PF_BM + r] = l;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&xbar[quad]);
+            const bool met = __all_sync(0xffffffffu, mbar_wait(&xbar[quad], nt & 1, abort_flag, P.status));
+            const float inv = met ? 1.0f / (l + xch[(4 + (half ^ 1)) * PF_BM + r]) : 0.f;
             const int grow_ = row0 + r;
             bool hit = false;
             uint16_t* orow = P.o + ((size_t)grow_ * P.q_heads + h) * D;
 #pragma unroll 1
-            for (int c0 = 0; c0 < D; c0 += 32) {
+            for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
                 uint32_t ov[32];
                 tmem_ld32(t_o + c0 + lane_off, ov);
                 tmem_wait_ld();

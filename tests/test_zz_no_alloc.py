@@ -74,7 +74,7 @@ def test_it_allocates_nothing(cuda):
 
 
 def test_explicit_splits_and_refusals(cuda):
-    qh, kvh, d, L = 16, 4, 128, 38912            # 608 tiles of 64 positions = 76 splits of 8 tiles
+    qh, kvh, d, L = 16, 4, 128, 38912            # 304 tiles of 128 positions = 76 splits of 4 tiles
     q, k, v = make(cuda, qh, kvh, d, L, 0, 9)
     want = cuda.zeros((qh, d), dtype=cuda.int16, device="cuda")
     got = cuda.zeros((qh, d), dtype=cuda.int16, device="cuda")
@@ -83,7 +83,7 @@ def test_explicit_splits_and_refusals(cuda):
     cuda.cuda.synchronize()
     assert np.array_equal(host_bits(got), host_bits(want))                    # same splits, same bits
     with pytest.raises(ext.B200Error) as e:
-        ext.decode_noalloc(got, None, q, k, v, qh, kvh, d, L, 0, nsplit=100)  # 87 splits of 7 tiles x 4 = 348 slots
+        ext.decode_noalloc(got, None, q, k, v, qh, kvh, d, L, 0, nsplit=152)  # 152 splits of 2 tiles x 4 kv heads = 608 slots
     assert e.value.code == ext.E_ARGUMENT and "304" in str(e.value)
     with pytest.raises(ext.B200Error):
         ext.decode_noalloc(got, None, q, k, v, qh, kvh, 96, L, 0)            # outside the kernel's fit
