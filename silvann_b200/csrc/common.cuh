@@ -91,6 +91,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
  * did not complete (the caller then leaves its loop and falls through to the kernel's common exit). */
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           unsigned int* status) {
+    if (mbar_try_wait(bar, parity)) return true;          /* the common case costs one try (about 100 cycles) and no loop */
     for (uint32_t i = 0; i < SV_WAIT_TRIES; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 255u && *abort_flag != 0u) return false;

@@ -26,7 +26,7 @@ namespace sv {
 
 static constexpr int PF_BM = 128;      /* query rows per block */
 static constexpr int PF_BN = 64;       /* keys per tile */
-static constexpr int PF_THREADS = 320; /* warp 0 TMA, warp 1 MMA, warps 2-9 softmax (two per TMEM lane quadrant) */
+static constexpr int PF_THREADS = 352; /* warp 0 TMA, warp 1 score MMAs, warps 2-9 softmax (two per TMEM lane quadrant), warp 10 value MMAs */
 
 /* ---- tcgen05 wrappers ---------------------------------------------------------------------------------------- */
 
@@ -49,6 +49,29 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+/* The same with the A operand in TMEM: row i of A in lane i, 16-bit elements packed two to a 32-bit column. */
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+/* The same, the B descriptor given as its two 32-bit halves so that the issuing thread can step through a tile with one
+ * integer add a step (the start-address field lives in the low half). */
+__device__ __forceinline__ void tc_mma_ts2(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 bd;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 bd, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+/* Both operands in shared memory, descriptors as halves. */
+__device__ __forceinline__ void tc_mma_ss2(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 ad, bd;\n\tsetp.ne.b32 p, %6, 0;\n\tmov.b64 ad, {%1, %2};\n\tmov.b64 bd, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], ad, bd, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
 /* 32 consecutive fp32 columns of this thread's TMEM lane. */
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -69,6 +92,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
           "r"(r[30]), "r"(r[31]) : "memory");
 }
+/* 16 consecutive 32-bit columns of this thread's TMEM lane. */
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -85,16 +115,30 @@ __host__ __device__ constexpr uint32_t idesc_f16(int bf16, int b_mn_major, int m
            ((uint32_t)(m >> 4) << 24);
 }
 
+#ifdef SV_PREFILL_TRACE
+/* Development aid, compiled only on request: block 0 leaves clock64() stamps of its softmax and MMA phases here. */
+__device__ unsigned long long g_pf_trace[2 * 128 * 8];
+#define SV_TR_S(j, k) do { if (blockIdx.x == 0 && warp == 2 && lane == 0 && (j) < 128) g_pf_trace[(j) * 8 + (k)] = clock64(); } while (0)
+#define SV_TR_M(j, k) do { if (blockIdx.x == 0 && (j) < 128) g_pf_trace[1024 + (j) * 8 + (k)] = clock64(); } while (0)
+#else
+#define SV_TR_S(j, k) do {} while (0)
+#define SV_TR_M(j, k) do {} while (0)
+#endif
+
 template <int D> struct PrefillCfg {
     static constexpr int BOXES = D / 64;
     static constexpr int Q_BYTES = PF_BM * D * 2;
+    static constexpr int Q_BOX_BYTES = PF_BM * 128;
     static constexpr int KV_TILE_BYTES = PF_BN * D * 2;              /* one K or one V tile */
     static constexpr int KV_BOX_BYTES = PF_BN * 128;
-    static constexpr int Q_BOX_BYTES = PF_BM * 128;
-    static constexpr int STAGES = (D >= 256) ? 2 : 4;
-    static constexpr int P_BYTES = PF_BM * PF_BN * 2;
-    static constexpr int TMEM_COLS = (D + 2 * PF_BN <= 256) ? 256 : 512;
-    static constexpr size_t SMEM = 1024 + Q_BYTES + 2 * STAGES * KV_TILE_BYTES + P_BYTES + 256 + 6 * PF_BM * 4;
+    static constexpr int KST = (D >= 256) ? 3 : 4;                   /* K ring: scores run two tiles ahead of the values */
+    static constexpr int VST = (D >= 256) ? 2 : 4;                   /* V ring */
+    static constexpr int NSB = 3;                                    /* score buffers in TMEM */
+    /* TMEM columns: O [0, D) fp32, then NSB score buffers of PF_BN columns whose first PF_BN/2 columns are overwritten
+     * in place by the 16-bit weights P */
+    static constexpr int T_S = D;
+    static constexpr int TMEM_COLS = (T_S + NSB * PF_BN <= 256) ? 256 : 512;
+    static constexpr size_t SMEM = 1024 + Q_BYTES + (KST + VST) * KV_TILE_BYTES + 256 + 2 * PF_BM * 4;
 };
 
 struct PrefillParams {
@@ -112,27 +156,26 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                const __grid_constant__ CUtensorMap vmap, const PrefillParams P) {
     using Cfg = PrefillCfg<D>;
     using E = Elem<DT>;
-    constexpr int ST = Cfg::STAGES;
+    constexpr int KST = Cfg::KST, VST = Cfg::VST, NSB = Cfg::NSB;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_s = smem;
     uint8_t* k_s = q_s + Cfg::Q_BYTES;
-    uint8_t* v_s = k_s + ST * Cfg::KV_TILE_BYTES;
-    uint8_t* p_s = v_s + ST * Cfg::KV_TILE_BYTES;
-    uint64_t* bars = (uint64_t*)(p_s + Cfg::P_BYTES);
-    uint64_t* q_full = bars;                 /* 1 */
-    uint64_t* k_full = bars + 1;             /* ST */
-    uint64_t* v_full = k_full + ST;          /* ST */
-    uint64_t* k_empty = v_full + ST;         /* ST: the S MMA that read the stage has completed */
-    uint64_t* pv_done = k_empty + ST;        /* ST: the PV MMA of the stage's tile has completed (V stage and P free) */
-    uint64_t* s_full = pv_done + ST;         /* 2 */
-    uint64_t* s_free = s_full + 2;           /* 2 */
-    uint64_t* p_full = s_free + 2;           /* 1 */
-    uint64_t* xbar = p_full + 1;             /* 4: the two softmax warps of a lane quadrant meet here once a tile */
+    uint8_t* v_s = k_s + KST * Cfg::KV_TILE_BYTES;
+    uint64_t* bars = (uint64_t*)(v_s + VST * Cfg::KV_TILE_BYTES);
+    uint64_t* k_full = bars;                 /* KST */
+    uint64_t* v_full = k_full + KST;         /* VST */
+    uint64_t* k_empty = v_full + VST;        /* KST: the S MMA that read the stage has completed */
+    uint64_t* pv_done = k_empty + KST;       /* VST: the PV MMA of the stage's tile has completed (V stage free, O settled) */
+    uint64_t* s_full = pv_done + VST;        /* NSB */
+    uint64_t* p_full = s_full + NSB;         /* NSB */
+    uint64_t* s_free = p_full + NSB;         /* NSB: the PV MMA that read the buffer's weights has completed */
+    uint64_t* q_full = s_free + NSB;         /* 1 */
+    uint64_t* xbar = q_full + 1;             /* 4: the two softmax warps of a lane quadrant meet here once a tile */
     uint32_t* tmem_slot = (uint32_t*)(xbar + 4);
     volatile uint32_t* abort_flag = (volatile uint32_t*)(tmem_slot + 1);
-    float* xch = (float*)(p_s + Cfg::P_BYTES + 256);         /* [6][128]: half-row maxima by tile parity, then normalisers */
+    float* xch = (float*)((uint8_t*)bars + 256);             /* [2][128]: the halves' normalisers at the end */
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int qt = (int)P.q_tiles - 1 - (int)(blockIdx.x / P.q_heads);       /* heaviest row blocks first */
@@ -144,10 +187,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     const int nt = last_key / PF_BN + 1;                                     /* KV tiles this row block walks */
 
     if (tid == 0) {
+        for (int s = 0; s < KST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+        for (int s = 0; s < VST; ++s) { mbar_init(&v_full[s], 1); mbar_init(&pv_done[s], 1); }
+        for (int b = 0; b < NSB; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 8); mbar_init(&s_free[b], 1); }
         mbar_init(q_full, 1);
-        for (int s = 0; s < ST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&pv_done[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_free[b], 8); }
-        mbar_init(p_full, 8);
         for (int x = 0; x < 4; ++x) mbar_init(&xbar[x], 2);
         *abort_flag = 0u;
         mbar_fence_init();
@@ -157,23 +200,32 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t t_o = tmem;                       /* columns [0, D): the output accumulator */
-    const uint32_t t_s0 = tmem + D;                  /* two score buffers of PF_BN columns */
+    const uint32_t t_o = tmem, t_s0 = tmem + Cfg::T_S;
 
     if (warp == 0) {
-        /* ---------------- TMA producer ---------------- */
+        /* ---------------- TMA producer: Q once, then a ring of K tiles and a ring of V tiles ---------------- */
         if (lane == 0) {
             tma_prefetch_desc(&qmap); tma_prefetch_desc(&kmap); tma_prefetch_desc(&vmap);
             mbar_expect_tx(q_full, Cfg::Q_BYTES);
 #pragma unroll
             for (int c = 0; c < Cfg::BOXES; ++c) tma_load_2d(q_s + c * Cfg::Q_BOX_BYTES, &qmap, q_full, h * D + c * 64, row0);
-            for (int j = 0; j < nt; ++j) {
-                const int s = j % ST, use = j / ST;
-                if (use > 0 && !mbar_wait(&k_empty[s], (use - 1) & 1, abort_flag, P.status)) break;
+            /* K runs ahead of V by the depth of the score pipeline: K(j + KST - VST) is requested with V(j) */
+            int jk = 0;
+            auto load_k = [&]() -> bool {
+                const int s = jk % KST, use = jk / KST;
+                if (use > 0 && !mbar_wait(&k_empty[s], (use - 1) & 1, abort_flag, P.status)) return false;
                 mbar_expect_tx(&k_full[s], Cfg::KV_TILE_BYTES);
 #pragma unroll
                 for (int c = 0; c < Cfg::BOXES; ++c)
-                    tma_load_2d(k_s + s * Cfg::KV_TILE_BYTES + c * Cfg::KV_BOX_BYTES, &kmap, &k_full[s], g * D + c * 64, j * PF_BN);
+                    tma_load_2d(k_s + s * Cfg::KV_TILE_BYTES + c * Cfg::KV_BOX_BYTES, &kmap, &k_full[s], g * D + c * 64, jk * PF_BN);
+                ++jk;
+                return true;
+            };
+            bool ok = true;
+            for (int i = 0; ok && i < KST - 1 && jk < nt; ++i) ok = load_k();
+            for (int j = 0; ok && j < nt; ++j) {
+                if (jk < nt && !load_k()) break;
+                const int s = j % VST, use = j / VST;
                 if (use > 0 && !mbar_wait(&pv_done[s], (use - 1) & 1, abort_flag, P.status)) break;
                 mbar_expect_tx(&v_full[s], Cfg::KV_TILE_BYTES);
 #pragma unroll
@@ -182,84 +234,98 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             }
         }
     } else if (warp == 1) {
-        /* ---------------- MMA issuer ---------------- */
+        /* ---------------- score MMAs: S(j) = Q · K(j)^T ----------------
+         * Two threads issue MMAs, this one the scores and one of warp 10 the values, because a thread that waits on an
+         * mbarrier (about a hundred cycles even when the phase is long complete) feeds the tensor pipe nothing meanwhile
+         * and the pipe's queue is short: with one issuer every wait is a bubble.  Scores run up to three tiles ahead
+         * (three TMEM buffers); a buffer is reused once the value MMA that read its weights has completed. */
         if (lane == 0) {
             constexpr uint32_t IDESC_S = idesc_f16(DT == SV_DTYPE_BF16, 0, PF_BM, PF_BN);
-            constexpr uint32_t IDESC_O = idesc_f16(DT == SV_DTYPE_BF16, 1, PF_BM, D);
-            const uint32_t q_a = smem_u32(q_s), k_a = smem_u32(k_s), v_a = smem_u32(v_s), p_a = smem_u32(p_s);
+            /* descriptors of stage 0; a stage further is KV_TILE_BYTES >> 4 more in the start-address field */
+            const uint64_t qd0 = smem_desc_sw128(smem_u32(q_s), 16, 1024), kd0 = smem_desc_sw128(smem_u32(k_s), 16, 1024);
+            const uint32_t qd_lo = (uint32_t)qd0, qd_hi = (uint32_t)(qd0 >> 32), kd_lo = (uint32_t)kd0, kd_hi = (uint32_t)(kd0 >> 32);
             bool ok = mbar_wait(q_full, 0, abort_flag, P.status);
-            auto issue_s = [&](int j) -> bool {
-                const int s = j % ST, b = j & 1;
-                if (!mbar_wait(&k_full[s], (j / ST) & 1, abort_flag, P.status)) return false;
-                if (j >= 2 && !mbar_wait(&s_free[b], ((j - 2) >> 1) & 1, abort_flag, P.status)) return false;
+            for (int j = 0; ok && j < nt; ++j) {
+                const int s = j % KST, b = j % NSB;
+                SV_TR_M(j, 0);
+                if (!mbar_wait(&k_full[s], (j / KST) & 1, abort_flag, P.status)) break;
+                if (j >= NSB && !mbar_wait(&s_free[b], (j / NSB - 1) & 1, abort_flag, P.status)) break;
+                SV_TR_M(j, 1);
                 tc_fence_after();
+                const uint32_t lo = kd_lo + (uint32_t)s * (Cfg::KV_TILE_BYTES >> 4), d_s = t_s0 + b * PF_BN;
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint64_t ad = smem_desc_sw128(q_a + (kk / 4) * Cfg::Q_BOX_BYTES + (kk % 4) * 32, 16, 1024);
-                    const uint64_t bd = smem_desc_sw128(k_a + s * Cfg::KV_TILE_BYTES + (kk / 4) * Cfg::KV_BOX_BYTES + (kk % 4) * 32, 16, 1024);
-                    tc_mma(t_s0 + b * PF_BN, ad, bd, IDESC_S, kk > 0 ? 1u : 0u);
-                }
+                for (int kk = 0; kk < D / 16; ++kk)      /* 16 columns a step: box kk/4, 32 bytes a step inside the 128-byte row */
+                    tc_mma_ss2(d_s, qd_lo + (kk / 4) * (Cfg::Q_BOX_BYTES >> 4) + (kk % 4) * 2, qd_hi,
+                               lo + (kk / 4) * (Cfg::KV_BOX_BYTES >> 4) + (kk % 4) * 2, kd_hi, IDESC_S, kk > 0 ? 1u : 0u);
                 tc_commit(&k_empty[s]);
                 tc_commit(&s_full[b]);
-                return true;
-            };
-            if (ok) ok = issue_s(0);
-            for (int j = 0; ok && j < nt; ++j) {
-                if (j + 1 < nt && !issue_s(j + 1)) { ok = false; break; }
-                const int s = j % ST;
-                if (!mbar_wait(p_full, j & 1, abort_flag, P.status)) break;
-                if (!mbar_wait(&v_full[s], (j / ST) & 1, abort_flag, P.status)) break;
+                SV_TR_M(j, 2);
+            }
+        }
+    } else if (warp == 10) {
+        /* ---------------- value MMAs: O += P(j) · V(j), P read from TMEM in place over the scores ---------------- */
+        if (lane == 0) {
+            constexpr uint32_t IDESC_O = idesc_f16(DT == SV_DTYPE_BF16, 1, PF_BM, D);
+            const uint64_t vd0 = smem_desc_sw128(smem_u32(v_s), Cfg::KV_BOX_BYTES, 1024);
+            const uint32_t vd_lo = (uint32_t)vd0, vd_hi = (uint32_t)(vd0 >> 32);
+            for (int j = 0; j < nt; ++j) {
+                const int s = j % VST, b = j % NSB;
+                if (!mbar_wait(&v_full[s], (j / VST) & 1, abort_flag, P.status)) break;
+                if (!mbar_wait(&p_full[b], (j / NSB) & 1, abort_flag, P.status)) break;
+                SV_TR_M(j, 3);
                 tc_fence_after();
+                /* V is [key][value column]: MN-major for B; 64-column groups are a box apart (LBO), 8-key groups
+                 * 1024 bytes apart (SBO); sixteen keys a step.  P: sixteen keys = 8 packed columns a step. */
+                const uint32_t lo = vd_lo + (uint32_t)s * (Cfg::KV_TILE_BYTES >> 4), a_p = t_s0 + b * PF_BN;
 #pragma unroll
-                for (int kk = 0; kk < PF_BN / 16; ++kk) {
-                    const uint64_t ad = smem_desc_sw128(p_a + kk * 32, 16, 1024);
-                    /* V is [key][value column]: MN-major for B; 64-column groups are a box apart (LBO), 8-key groups
-                     * 1024 bytes apart (SBO); sixteen keys a step */
-                    const uint64_t bd = smem_desc_sw128(v_a + s * Cfg::KV_TILE_BYTES + kk * 2048, Cfg::KV_BOX_BYTES, 1024);
-                    tc_mma(t_o, ad, bd, IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
-                }
+                for (int kk = 0; kk < PF_BN / 16; ++kk)
+                    tc_mma_ts2(t_o, a_p + kk * 8, lo + kk * (2048 >> 4), vd_hi, IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
                 tc_commit(&pv_done[s]);
+                tc_commit(&s_free[b]);
+                SV_TR_M(j, 4);
             }
         }
     } else {
         /* ---------------- softmax, correction, epilogue ----------------
          * Eight warps: a warp may touch only the 32 TMEM lanes of its quadrant (warp id mod 4), so two warps share each
-         * quadrant and split every row's 64 scores in halves of 32 columns.  The two threads of a row exchange their
-         * half-row maxima through shared memory (an mbarrier per quadrant, waited for with a bound like every other wait here), keep identical reference maxima,
-         * and each carries the normaliser of its own half until the end. */
+         * quadrant.  Both read a row's 64 scores (the row maximum needs them all, and reading twice is cheaper than
+         * exchanging), each turns its own 32 columns into weights, carries the normaliser of its half, and owns half of
+         * O's columns when a rescale or the final store is due. */
         const int sw = warp - 2;                                    /* 0..7 */
         const int quad = warp & 3, half = sw >> 2;
         const int r = quad * 32 + lane;                             /* row within the block */
         const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-        const int pos = (int)P.first + row0 + r;                    /* this row's position: keys 0..pos */
+        const int grow_ = row0 + r;                                 /* row of the call */
+        const int pos = (int)P.first + grow_;                       /* this row's position: keys 0..pos */
+
         float m_ref = -INFINITY, l = 0.f;
         bool alive = true;
         for (int j = 0; j < nt; ++j) {
-            const int b = j & 1;
-            /* the TMEM loads below are warp-collective: the warp leaves the loop together or not at all */
-            if (!__all_sync(0xffffffffu, mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag, P.status))) { alive = false; break; }
+            const int b = j % NSB;
+            /* the TMEM accesses below are warp-collective: the warp leaves the loop together or not at all */
+            if (!__all_sync(0xffffffffu, mbar_wait(&s_full[b], (j / NSB) & 1, abort_flag, P.status))) { alive = false; break; }
+            SV_TR_S(j, 0);
             tc_fence_after();
-            uint32_t sv[32];
-            tmem_ld32(t_s0 + b * PF_BN + half * 32 + lane_off, sv);
+            uint32_t sv[2][32];
+            tmem_ld32(t_s0 + b * PF_BN + lane_off, sv[0]);
+            tmem_ld32(t_s0 + b * PF_BN + 32 + lane_off, sv[1]);
             tmem_wait_ld();
+            /* the partner warp may overwrite these columns with its weights once it knows they have been read */
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&s_free[b]);
+            if (lane == 0) mbar_arrive(&xbar[quad]);
+            SV_TR_S(j, 1);
 
-            const int key0 = j * PF_BN + half * 32;
-            if (key0 + 31 > pos) {                                  /* keys of this half lie past the row's position */
+            const int key0 = j * PF_BN;
+            if (key0 + PF_BN - 1 > pos) {                           /* keys of this tile lie past the row's position */
 #pragma unroll
-                for (int c = 0; c < 32; ++c) if (key0 + c > pos) sv[c] = 0xFF800000u;   /* -inf */
+                for (int c = 0; c < 64; ++c) if (key0 + c > pos) sv[c >> 5][c & 31] = 0xFF800000u;   /* -inf */
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * P.scale_log2;
-            xch[(b * 2 + half) * PF_BM + r] = mx;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&xbar[quad]);
-            if (!__all_sync(0xffffffffu, mbar_wait(&xbar[quad], j & 1, abort_flag, P.status))) { alive = false; break; }
-            mx = fmaxf(mx, xch[(b * 2 + (half ^ 1)) * PF_BM + r]);
+            for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c >> 5][c & 31]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * P.scale_log2;
+            SV_TR_S(j, 2);
             /* keep the reference maximum unless this tile's exceeds it by more than 8 (weights then stay <= 2^8) */
             float f = 1.f;
             const bool grow = (mx > m_ref + 8.f) || (m_ref == -INFINITY && mx != -INFINITY);
@@ -269,18 +335,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c]), P.scale_log2, -mu));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c + 1]), P.scale_log2, -mu));
+                const float s0 = __uint_as_float(half ? sv[1][c] : sv[0][c]), s1 = __uint_as_float(half ? sv[1][c + 1] : sv[0][c + 1]);
+                const float p0 = fast_exp2(fmaf(s0, P.scale_log2, -mu));
+                const float p1 = fast_exp2(fmaf(s1, P.scale_log2, -mu));
                 const uint32_t w = E::pack2(p0, p1);
                 const float2 back = E::unpack2(w);                  /* the normaliser sums what the MMA will see */
                 sum4[(c >> 1) & 3] += back.x + back.y;
                 pk[c >> 1] = w;
             }
             l = l * f + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            SV_TR_S(j, 3);
 
-            /* O must not be touched, and P not overwritten, while the previous PV MMA may still be running */
-            if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) % ST], ((j - 1) / ST) & 1, abort_flag, P.status))) { alive = false; break; }
             if (j > 0 && __any_sync(0xffffffffu, f != 1.f)) {
+                /* O may be rescaled only between PV MMAs: the previous one must have completed, the next waits for us */
+                if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) % VST], ((j - 1) / VST) & 1, abort_flag, P.status))) { alive = false; break; }
                 tc_fence_after();
 #pragma unroll 1
                 for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {      /* each warp of the pair half of O's columns */
@@ -292,26 +360,26 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                     tmem_st32(t_o + c0 + lane_off, ov);
                 }
                 tmem_wait_st();
-                tc_fence_before();
             }
-            /* P row r: this half's 32 keys = 4 chunks of 16 bytes in the 128-byte-swizzled K-major tile the MMA reads */
-#pragma unroll
-            for (int ch = 0; ch < 4; ++ch)
-                *reinterpret_cast<uint4*>(p_s + swz128(r, half * 4 + ch)) = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-            fence_proxy_async_smem();
+            SV_TR_S(j, 4);
+            /* P over the scores, in place: 32 weights = 16 packed columns at this half's place, once the partner has read */
+            if (!__all_sync(0xffffffffu, mbar_wait(&xbar[quad], j & 1, abort_flag, P.status))) { alive = false; break; }
+            tmem_st16(t_s0 + b * PF_BN + half * 16 + lane_off, pk);
+            tmem_wait_st();
+            tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(&p_full[b]);
+            SV_TR_S(j, 5);
         }
         /* epilogue: the row's normaliser is the sum of its two halves'; O / l, rounded, to global — each warp of the pair
          * writes half of the row, which is contiguous in the output */
-        if (alive && __all_sync(0xffffffffu, mbar_wait(&pv_done[(nt - 1) % ST], ((nt - 1) / ST) & 1, abort_flag, P.status))) {
+        if (alive && __all_sync(0xffffffffu, mbar_wait(&pv_done[(nt - 1) % VST], ((nt - 1) / VST) & 1, abort_flag, P.status))) {
             tc_fence_after();
-            xch[(4 + half) * PF_BM + r] = l;
+            xch[half * PF_BM + r] = l;
             __syncwarp();
             if (lane == 0) mbar_arrive(&xbar[quad]);
             const bool met = __all_sync(0xffffffffu, mbar_wait(&xbar[quad], nt & 1, abort_flag, P.status));
-            const float inv = met ? 1.0f / (l + xch[(4 + (half ^ 1)) * PF_BM + r]) : 0.f;
-            const int grow_ = row0 + r;
+            const float inv = met ? 1.0f / (l + xch[(half ^ 1) * PF_BM + r]) : 0.f;
             bool hit = false;
             uint16_t* orow = P.o + ((size_t)grow_ * P.q_heads + h) * D;
 #pragma unroll 1
@@ -378,6 +446,12 @@ static cudaError_t launch_prefill(const PrefillCall& c) {
     note_launch(1);
     return cudaGetLastError();
 }
+
+#ifdef SV_PREFILL_TRACE
+extern "C" __attribute__((visibility("default"))) int sv_prefill_trace_read(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_pf_trace, sizeof(unsigned long long) * 2 * 128 * 8);
+}
+#endif
 
 cudaError_t prefill_launch(const PrefillCall& c) {
 #define SV_PF(DD) (c.dtype == SV_DTYPE_BF16 ? launch_prefill<DD, SV_DTYPE_BF16>(c) : launch_prefill<DD, SV_DTYPE_FP16>(c))
