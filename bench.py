@@ -314,6 +314,60 @@ def other_workloads(torch, fam, pk, steps, warmup):
     return out
 
 
+def long_context(torch, dist, rank, world, steps, pk):
+    """Configuration 4 on `world` GPUs: one sequence of 262,144 positions, 32 q heads on 4 kv heads, head_dim 128, bf16;
+    kv heads sharded over the ranks (and the range halved among the two ranks of a kv head at 8), the first 65,536
+    positions in pinned host RAM and streamed on a side stream.  Timed twice: as specified, and with every position
+    already on the card.  Answers whole-job KV GB/s from the slowest rank's device time."""
+    from silvann_b200 import ext, sharded
+    qh, kvh, d, L, HOST = 32, 4, 128, 262144, 65536
+    if world not in (1, 2, 4, 8):
+        return {"note": f"not run at {world} GPUs"}
+    shard = sharded.shard_plan(qh, kvh, L, world)[rank]
+    gen = torch.Generator(device="cuda"); gen.manual_seed(1004 + rank)
+    n, heads = shard.positions, shard.kv_heads
+    k = torch.randn((n, heads, d), generator=gen, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn((n, heads, d), generator=gen, device="cuda", dtype=torch.bfloat16)
+    q = torch.randn((shard.q_heads, d), generator=gen, device="cuda", dtype=torch.bfloat16)
+    h_len = max(0, min(HOST, shard.pos_hi) - shard.pos_lo)
+    k_host = k[:h_len].cpu().pin_memory() if h_len else None
+    v_host = v[:h_len].cpu().pin_memory() if h_len else None
+    pg = None
+    if world > kvh:                                  # every rank takes part in creating every group
+        for head in range(kvh):
+            members = [r for r in range(world) if r // (world // kvh) == head]
+            g = dist.new_group(members)
+            if rank in members:
+                pg = g
+    out = {}
+    for tag, (kh, vh, hl, kd, vd, dl) in {"tiered": (k_host, v_host, h_len, k[h_len:] if n > h_len else None, v[h_len:] if n > h_len else None, n - h_len),
+                                           "resident": (None, None, 0, k, v, n)}.items():
+        runner = sharded.LongContextRank(torch, ext, shard, d, ext.BF16, kh, vh, hl, kd, vd, dl, dist, pg, chunk_positions=8192, stages=3)
+        for _ in range(3):
+            runner.step(q)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            runner.step(q)
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / steps], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        nbytes = 2 * L * kvh * d * 2
+        out[tag] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_step": ms, "frac_hbm_of_n_gpus": nbytes / ms / 1e6 / (pk["hbm_gbs"] * world)}
+        runner.close()
+    out["tiered"]["host_tier_bytes"] = 2 * HOST * kvh * d * 2
+    out["tiered"]["host_tier_gbs"] = out["tiered"]["host_tier_bytes"] / out["tiered"]["ms_per_step"] / 1e6
+    out["note"] = ("kv heads sharded over ranks" + (", each kv head's range halved over two ranks and residuals all-gathered (NCCL) and merged" if world > kvh else ", no collective")
+                   + "; tiered: first 65,536 positions streamed from pinned host RAM each step (PCIe-bound); resident: all positions in HBM")
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -399,6 +453,12 @@ def run_ours(args):
             if not args.no_others:
                 line["others"] = other_workloads(torch, fam, pk, steps, warmup)
     e2e.close()
+    if not args.no_others:
+        del wl, e2e
+        torch.cuda.empty_cache()
+        lc = long_context(torch, dist, rank, world, max(steps, 10), pk)
+        if rank == 0:
+            line["long_context_config4"] = lc
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -358,6 +358,22 @@ int silvann_b200_paged_decode(silvann_b200_plan* plan, void* o, float* res, cons
 int silvann_b200_paged_append(silvann_b200_plan* plan, void* k_pool, void* v_pool, const void* k_rows, const void* v_rows,
                               uint32_t page_positions, const int32_t* page_table, uint32_t table_stride, void* stream);
 
+/* One query position over a two-tier cache: the oldest host_len positions in pinned host RAM (k_host, v_host are HOST
+ * addresses of [host_len][kv_heads][head_dim] planes), the next dev_len positions on the card.  The reference has no
+ * host tier; its tiered mixer attends each on-card tier into a residual and merges them (ai_qwen_3 mixer__abi.cuh:383-412),
+ * and this does the same with one more tier: host chunks of `chunk_positions` are copied by cudaMemcpyAsync on a side
+ * stream into a ring of `stages` staging buffers while `stream` attends the previous chunk; the card tier is attended
+ * first.  o [q_heads][head_dim] and/or res [q_heads][head_dim + 2] (the merged residual, for a further merge across
+ * devices).  The tier object owns the staging ring (2 * stages * chunk_positions * kv_heads * head_dim * 2 bytes). */
+typedef struct silvann_b200_tier silvann_b200_tier;
+int silvann_b200_tier_create(silvann_b200_tier** tier, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim, int dtype,
+                             uint32_t chunk_positions, uint32_t stages);
+int silvann_b200_tier_destroy(silvann_b200_tier* tier);
+int silvann_b200_tier_decode(silvann_b200_tier* tier, void* o, float* res, const void* q, const void* k_host, const void* v_host,
+                             uint64_t host_len, const void* k_dev, const void* v_dev, uint64_t dev_len, sv_fault* over, void* stream);
+/* Bytes copied host to device and chunks staged since the tier was created. */
+int silvann_b200_tier_stats(const silvann_b200_tier* tier, uint64_t* h2d_bytes, uint64_t* chunks);
+
 /* Causal grouped-query prefill in one kernel — attention_causal_scores_grouped + attention_causal_softmax +
  * attention_causal_mix (kernels.cuh:1028-1081, 2051-2060): row r is position first + r and attends cache rows
  * 0..first+r.  q, o [rows][q_heads][head_dim]; k, v [first + rows][kv_heads][head_dim]. */

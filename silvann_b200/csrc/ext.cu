@@ -24,6 +24,11 @@ static int fail(int code, const char* fmt, ...) {
     va_list ap; va_start(ap, fmt); vsnprintf(t_error, sizeof t_error, fmt, ap); va_end(ap);
     return code;
 }
+/* the same for the library's other translation units (tier.cu) */
+int sv_ext_fail(int code, const char* fmt, ...) {
+    va_list ap; va_start(ap, fmt); vsnprintf(t_error, sizeof t_error, fmt, ap); va_end(ap);
+    return code;
+}
 static int cuda_fail(const char* what, cudaError_t e) {
     (void)cudaGetLastError();
     return fail(SILVANN_B200_E_CUDA, "%s: %s", what, cudaGetErrorString(e));

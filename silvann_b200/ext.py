@@ -16,7 +16,8 @@ EXPORTS = (
     "silvann_silicon_family_get", "silvann_b200_last_error", "silvann_b200_counters_read", "silvann_b200_device_status",
     "silvann_b200_decode", "silvann_b200_decode_noalloc", "silvann_b200_merge", "silvann_b200_finish", "silvann_b200_plan_create",
     "silvann_b200_plan_destroy", "silvann_b200_plan_decode", "silvann_b200_plan_info", "silvann_b200_paged_decode", "silvann_b200_paged_append",
-    "silvann_b200_prefill", "silvann_b200_deltanet",
+    "silvann_b200_prefill", "silvann_b200_deltanet", "silvann_b200_tier_create", "silvann_b200_tier_destroy",
+    "silvann_b200_tier_decode", "silvann_b200_tier_stats",
 )
 
 
@@ -56,6 +57,10 @@ def lib():
             "silvann_b200_plan_info": [vp, vp, vp, vp],
             "silvann_b200_paged_decode": [vp, vp, vp, vp, vp, vp, u64, u32, vp, u32, i32, vp, vp],
             "silvann_b200_paged_append": [vp, vp, vp, vp, vp, u32, vp, u32, vp],
+            "silvann_b200_tier_create": [vp, u32, u32, u32, i32, u32, u32],
+            "silvann_b200_tier_destroy": [vp],
+            "silvann_b200_tier_decode": [vp, vp, vp, vp, vp, vp, u64, vp, vp, u64, vp, vp],
+            "silvann_b200_tier_stats": [vp, vp, vp],
             "silvann_b200_prefill": [vp, vp, vp, vp, u64, u64, u64, u64, u64, i32, vp, vp],
             "silvann_b200_deltanet": [vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u32, u32, i32, vp, vp],
         }
@@ -141,6 +146,34 @@ class Plan:
     def append(self, k_pool, v_pool, k_rows, v_rows, page_positions, page_table, table_stride, stream=None):
         _check(lib().silvann_b200_paged_append(self.handle, addr(k_pool), addr(v_pool), addr(k_rows), addr(v_rows), page_positions,
                                                addr(page_table), table_stride, stream))
+
+
+class Tier:
+    """Decode over a cache whose oldest positions live in pinned host RAM (see silvann_b200_tier_decode)."""
+
+    def __init__(self, q_heads, kv_heads, head_dim, dtype=FP16, chunk_positions=8192, stages=3):
+        self.handle = C.c_void_p()
+        _check(lib().silvann_b200_tier_create(C.byref(self.handle), q_heads, kv_heads, head_dim, dtype, chunk_positions, stages))
+
+    def close(self):
+        if self.handle:
+            lib().silvann_b200_tier_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def decode(self, o, res, q, k_host, v_host, host_len, k_dev, v_dev, dev_len, over=None, stream=None):
+        _check(lib().silvann_b200_tier_decode(self.handle, addr(o), addr(res), addr(q), addr(k_host), addr(v_host), host_len,
+                                              addr(k_dev), addr(v_dev), dev_len, addr(over), stream))
+
+    def stats(self) -> dict:
+        b, c = C.c_uint64(), C.c_uint64()
+        _check(lib().silvann_b200_tier_stats(self.handle, C.byref(b), C.byref(c)))
+        return {"h2d_bytes": b.value, "chunks": c.value}
 
 
 def prefill(o, q, k, v, q_heads, kv_heads, head_dim, first, rows, dtype=FP16, over=None, stream=None):

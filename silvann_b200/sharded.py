@@ -1,0 +1,129 @@
+"""One long sequence over several GPUs: which rank attends what, and how the pieces meet.
+
+The reference shards a model over cards by heads — each card gets a table with its share of the heads, and the
+attention doors never know (runtime/silvann_runtime/qwen3_5.py:112-134) — and replicates a kv head when there are more
+cards than kv heads.  Here a replicated kv head is put to work instead: the ranks that share it split its KV RANGE, each
+produces the residual (m, l, acc) of its range with the same decode kernel, and the residuals are folded with the
+reference's merge arithmetic (engine/src/packages/nn/gpu/kernels/kernels.cuh:1243-1255).  The residual is the wire
+format: q_heads_local * (head_dim + 2) floats a rank, so the exchange is one small all-gather among the ranks of a kv
+head (NCCL over NVLink on the GPUs, gloo in the CPU tests) and there is no collective at all while ranks <= kv heads.
+
+This module is host logic only: it decides shards and drives the exchange; arithmetic is the library's (ext.merge,
+ext.finish), injected so that the plumbing can be exercised without a GPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+RANGE_ALIGN = 128     # a rank's range starts on a multiple of the decode kernel's largest tile
+
+
+@dataclass
+class Shard:
+    rank: int
+    kv_head_lo: int
+    kv_head_hi: int
+    q_head_lo: int
+    q_head_hi: int
+    pos_lo: int
+    pos_hi: int
+    group: list = field(default_factory=list)   # the ranks that share these heads, in range order (len 1: no exchange)
+
+    @property
+    def kv_heads(self) -> int:
+        return self.kv_head_hi - self.kv_head_lo
+
+    @property
+    def q_heads(self) -> int:
+        return self.q_head_hi - self.q_head_lo
+
+    @property
+    def positions(self) -> int:
+        return self.pos_hi - self.pos_lo
+
+
+def shard_plan(q_heads: int, kv_heads: int, length: int, world: int) -> list[Shard]:
+    """Every rank's share of one sequence of `length` cached positions.
+
+    world <= kv_heads: whole kv heads per rank (kv_heads must divide evenly), full range, no exchange.
+    world >  kv_heads: world / kv_heads ranks per kv head, each a contiguous range of positions cut on multiples of 128.
+    """
+    if q_heads <= 0 or kv_heads <= 0 or q_heads % kv_heads or length <= 0 or world <= 0:
+        raise ValueError(f"shard_plan: {q_heads} query heads, {kv_heads} kv heads, {length} positions, {world} ranks")
+    group = q_heads // kv_heads
+    shards = []
+    if world <= kv_heads:
+        if kv_heads % world:
+            raise ValueError(f"shard_plan: {kv_heads} kv heads do not divide over {world} ranks")
+        per = kv_heads // world
+        for r in range(world):
+            shards.append(Shard(r, r * per, (r + 1) * per, r * per * group, (r + 1) * per * group, 0, length, [r]))
+        return shards
+    if world % kv_heads:
+        raise ValueError(f"shard_plan: {world} ranks do not divide over {kv_heads} kv heads")
+    parts = world // kv_heads
+    step = -(-length // parts)
+    step = -(-step // RANGE_ALIGN) * RANGE_ALIGN
+    for r in range(world):
+        head, part = divmod(r, parts)
+        lo, hi = min(part * step, length), min((part + 1) * step, length)
+        members = [head * parts + x for x in range(parts) if min(x * step, length) < min((x + 1) * step, length)]
+        shards.append(Shard(r, head, head + 1, head * group, (head + 1) * group, lo, hi, members))
+    return shards
+
+
+def fold(parts, merge):
+    """Folds residuals in the order given: ((p0 + p1) + p2) + ...; `merge(a, b)` answers the merged residual."""
+    acc = parts[0]
+    for nxt in parts[1:]:
+        acc = merge(acc, nxt)
+    return acc
+
+
+def gather_and_fold(residual, shard: Shard, dist, merge, process_group=None, empty_like=None):
+    """The residual of the whole range, on every rank of the shard's group.
+
+    `residual` is this rank's piece (a tensor the backend of `dist` can move); `dist` is torch.distributed (or anything
+    with its all_gather); ranks outside the group must not call.  Ranks fold in range order, so every rank of the group
+    computes the same bits.  A rank whose range is empty is not a member of the group.
+    """
+    if len(shard.group) == 1:
+        return residual
+    empty_like = empty_like or (lambda t: t.new_empty(t.shape))
+    pieces = [empty_like(residual) for _ in shard.group]
+    dist.all_gather(pieces, residual, group=process_group)
+    return fold(pieces, merge)
+
+
+class LongContextRank:
+    """A rank's share of the long-context decode (configuration 4): its heads, its range, its two tiers.
+
+    k_host/v_host: pinned host planes [host_len][kv_heads_local][head_dim] (this rank's positions that live in host RAM),
+    k_dev/v_dev: device planes [dev_len][kv_heads_local][head_dim].  step(q_local) answers the rank's output heads
+    [q_heads_local][head_dim] as a device tensor of 16-bit patterns.
+    """
+
+    def __init__(self, torch, ext, shard: Shard, head_dim, dtype, k_host, v_host, host_len, k_dev, v_dev, dev_len,
+                 dist=None, process_group=None, chunk_positions=8192, stages=3):
+        self.torch, self.ext, self.shard, self.d, self.dtype = torch, ext, shard, head_dim, dtype
+        self.k_host, self.v_host, self.host_len, self.k_dev, self.v_dev, self.dev_len = k_host, v_host, host_len, k_dev, v_dev, dev_len
+        self.dist, self.pg = dist, process_group
+        self.tier = ext.Tier(shard.q_heads, shard.kv_heads, head_dim, dtype, chunk_positions, stages)
+        self.res = torch.zeros((shard.q_heads, head_dim + 2), dtype=torch.float32, device="cuda")
+        self.out = torch.zeros((shard.q_heads, head_dim), dtype=torch.int16, device="cuda")
+
+    def _merge(self, a, b):
+        self.ext.merge(a, a, b, self.shard.q_heads, self.d)       # `into` may be `a`: the gathered pieces are ours to overwrite
+        return a
+
+    def step(self, q_local):
+        alone = len(self.shard.group) == 1
+        self.tier.decode(self.out if alone else None, None if alone else self.res, q_local, self.k_host, self.v_host, self.host_len,
+                         self.k_dev, self.v_dev, self.dev_len)
+        if not alone:
+            merged = gather_and_fold(self.res, self.shard, self.dist, self._merge, self.pg)
+            self.ext.finish(self.out, merged, self.shard.q_heads, self.d, self.dtype)
+        return self.out
+
+    def close(self):
+        self.tier.close()

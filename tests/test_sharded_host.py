@@ -1,0 +1,75 @@
+"""Host logic of the multi-GPU long-context path, on CPU: the shard plan, and the residual exchange + fold among the
+ranks of a kv head over a real process group (gloo, world size 2) with the checker's merge standing in for the kernel."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from silvann_b200 import sharded
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_plan_by_heads_needs_no_exchange():
+    for world in (1, 2, 4):
+        plan = sharded.shard_plan(32, 4, 262144, world)
+        assert len(plan) == world
+        assert all(len(s.group) == 1 and (s.pos_lo, s.pos_hi) == (0, 262144) for s in plan)
+        assert sorted(h for s in plan for h in range(s.kv_head_lo, s.kv_head_hi)) == [0, 1, 2, 3]
+        assert sum(s.q_heads for s in plan) == 32
+        for s in plan:
+            assert (s.q_head_lo, s.q_head_hi) == (s.kv_head_lo * 8, s.kv_head_hi * 8)
+
+
+def test_plan_splits_the_range_when_ranks_outnumber_kv_heads():
+    plan = sharded.shard_plan(32, 4, 262144, 8)
+    assert [(s.kv_head_lo, s.pos_lo, s.pos_hi) for s in plan] == [(h, p * 131072, (p + 1) * 131072) for h in range(4) for p in range(2)]
+    assert [s.group for s in plan] == [[0, 1], [0, 1], [2, 3], [2, 3], [4, 5], [4, 5], [6, 7], [6, 7]]
+    ragged = sharded.shard_plan(8, 1, 1000, 4)
+    assert [(s.pos_lo, s.pos_hi) for s in ragged] == [(0, 256), (256, 512), (512, 768), (768, 1000)]
+    tiny = sharded.shard_plan(8, 1, 200, 4)              # fewer tiles than ranks: the empty ranks are left out of the group
+    assert [(s.pos_lo, s.pos_hi) for s in tiny] == [(0, 128), (128, 200), (200, 200), (200, 200)]
+    assert tiny[0].group == [0, 1]
+
+
+def test_plan_refusals():
+    for args in [(32, 4, 100, 3), (32, 4, 100, 6), (30, 4, 100, 2), (32, 4, 0, 2)]:
+        with pytest.raises(ValueError):
+            sharded.shard_plan(*args)
+
+
+def _rank_main(rank, world, port, tmp):
+    sys.path.insert(0, str(ROOT))
+    import torch
+    import torch.distributed as dist
+    import oracle
+    from silvann_b200 import sharded as sh
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    P = oracle.port()
+    qh, kvh, d, L = 8, 1, 64, 1000
+    rng = np.random.default_rng(3)
+    q, k, v = (oracle.to_bits(rng.standard_normal(s, dtype=np.float32), 0) for s in ((qh, d), (L, kvh, d), (L, kvh, d)))
+    shard = sh.shard_plan(qh, kvh, L, world)[rank]
+    mine = P.residual(q, np.ascontiguousarray(k[shard.pos_lo:shard.pos_hi]), np.ascontiguousarray(v[shard.pos_lo:shard.pos_hi]), qh, kvh, d, shard.positions)
+    merge = lambda a, b: torch.from_numpy(P.merge(a.numpy(), b.numpy(), qh, d))
+    total = sh.gather_and_fold(torch.from_numpy(mine), shard, dist, merge)
+    o, _ = P.finish(total.numpy(), qh, d)
+    np.save(Path(tmp) / f"o{rank}.npy", o)
+    if rank == 0:
+        whole = P.residual(q, k, v, qh, kvh, d, L)
+        np.save(Path(tmp) / "want.npy", whole[:, 2:] / whole[:, 1:2])
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_exchange_and_fold_over_gloo(tmp_path):
+    import torch.multiprocessing as mp
+    port = 29500 + os.getpid() % 2000
+    mp.spawn(_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    import oracle
+    o0, o1 = np.load(tmp_path / "o0.npy"), np.load(tmp_path / "o1.npy")
+    assert np.array_equal(o0, o1)                                        # every rank of the group folds the same bits
+    assert np.abs(oracle.from_bits(o0, 0) - np.load(tmp_path / "want.npy")).max() <= 2e-3
