@@ -33,13 +33,14 @@ struct DeltaParams {
     const uint16_t *conved, *z, *beta, *g, *w;
     uint16_t* out;
     float* ss;                 /* scratch [seqs][rows][v_heads][d/32] */
+    const float4* sc;          /* with PRE: per (seq, row, value head) {1/|q|/sqrt(d), 1/|k|, e^g, beta}, made by the scalars kernel */
     unsigned int* over;
     uint32_t k_heads, v_heads, seqs;
     uint64_t rows;
     int gate;
 };
 
-template <int D, int DT>
+template <int D, int DT, bool PRE>
 __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaParams P) {
     using E = Elem<DT>;
     constexpr int CB = D / DN_COLS;            /* column blocks per head */
@@ -76,6 +77,8 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
     };
     for (int i = tid; i < 2 * D; i += DN_THREADS) (&qk[0][0][0])[i] = E::to_float(qk_src(cv, i));
     uint16_t n_v = cv[(uint64_t)2 * P.k_heads * D + (uint64_t)h * D + j], n_beta = bb[h], n_g = gg[h];
+    const float4* sc = PRE ? P.sc + (uint64_t)b * P.rows * P.v_heads + h : nullptr;
+    float4 n_sc = PRE ? sc[0] : make_float4(0.f, 0.f, 0.f, 0.f);
     uint16_t n_qk[NQ];
 #pragma unroll
     for (int u = 0; u < NQ; ++u) {
@@ -88,7 +91,9 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
     bool hit = false;
     for (uint64_t t = 0; t < P.rows; ++t) {
         const int buf = (int)(t & 1);
-        const float vj = E::to_float(n_v), beta = E::to_float(n_beta), decay = expf(E::to_float(n_g));
+        const float vj = E::to_float(n_v);
+        const float4 c_sc = n_sc;
+        const float beta = PRE ? c_sc.w : E::to_float(n_beta), decay = PRE ? c_sc.z : expf(E::to_float(n_g));
         if (t + 1 < P.rows) {
 #pragma unroll
             for (int u = 0; u < NQ; ++u) {
@@ -97,8 +102,8 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
             }
             const uint16_t* nrow = cv + (t + 1) * ch;
             n_v = nrow[(uint64_t)2 * P.k_heads * D + (uint64_t)h * D + j];
-            n_beta = bb[(t + 1) * P.v_heads + h];
-            n_g = gg[(t + 1) * P.v_heads + h];
+            if (PRE) n_sc = sc[(t + 1) * P.v_heads];
+            else { n_beta = bb[(t + 1) * P.v_heads + h]; n_g = gg[(t + 1) * P.v_heads + h]; }
             if (t + 2 < P.rows) {
 #pragma unroll
                 for (int u = 0; u < NQ; ++u) {
@@ -110,35 +115,39 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
         const float* qv = qk[buf][0] + rg * R;
         const float* kv_ = qk[buf][1] + rg * R;
         float kvp = 0.f, qq = 0.f, kk = 0.f;
+        float kv4[4] = {0.f, 0.f, 0.f, 0.f};          /* four chains instead of one: the sums are latency-bound */
 #pragma unroll
         for (int i = 0; i < R; i += 4) {
             const float4 k4 = *reinterpret_cast<const float4*>(kv_ + i);
             const float4 q4 = *reinterpret_cast<const float4*>(qv + i);
-            kvp += s[i] * k4.x + s[i + 1] * k4.y + s[i + 2] * k4.z + s[i + 3] * k4.w;
-            kk += k4.x * k4.x + k4.y * k4.y + k4.z * k4.z + k4.w * k4.w;
-            qq += q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w;
+            kv4[(i >> 2) & 3] += s[i] * k4.x + s[i + 1] * k4.y + s[i + 2] * k4.z + s[i + 3] * k4.w;
+            if (!PRE) {
+                kk += k4.x * k4.x + k4.y * k4.y + k4.z * k4.z + k4.w * k4.w;
+                qq += q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w;
+            }
         }
+        kvp = (kv4[0] + kv4[1]) + (kv4[2] + kv4[3]);
         red1[rg][c] = kvp;
-        if (c == 0) { red1[rg][DN_COLS] = qq; red1[rg][DN_COLS + 1] = kk; }
+        if (!PRE && c == 0) { red1[rg][DN_COLS] = qq; red1[rg][DN_COLS + 1] = kk; }
         __syncthreads();
         float kvsum = 0.f, qsum = 0.f, ksum = 0.f;
 #pragma unroll
-        for (int r = 0; r < DN_RG; ++r) { kvsum += red1[r][c]; qsum += red1[r][DN_COLS]; ksum += red1[r][DN_COLS + 1]; }
-        const float inv_k = 1.0f / sqrtf(ksum + 1e-6f);
-        const float inv_q = 1.0f / sqrtf(qsum + 1e-6f) * inv_sqrt_d;
+        for (int r = 0; r < DN_RG; ++r) { kvsum += red1[r][c]; if (!PRE) { qsum += red1[r][DN_COLS]; ksum += red1[r][DN_COLS + 1]; } }
+        const float inv_k = PRE ? c_sc.y : 1.0f / sqrtf(ksum + 1e-6f);
+        const float inv_q = PRE ? c_sc.x : 1.0f / sqrtf(qsum + 1e-6f) * inv_sqrt_d;
         const float delta = (vj - decay * kvsum * inv_k) * beta;
         const float kd = inv_k * delta;
-        float op = 0.f;
+        float op4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < R; i += 4) {
             const float4 k4 = *reinterpret_cast<const float4*>(kv_ + i);
             const float4 q4 = *reinterpret_cast<const float4*>(qv + i);
-            s[i]     = decay * s[i]     + k4.x * kd; op += s[i]     * q4.x;
-            s[i + 1] = decay * s[i + 1] + k4.y * kd; op += s[i + 1] * q4.y;
-            s[i + 2] = decay * s[i + 2] + k4.z * kd; op += s[i + 2] * q4.z;
-            s[i + 3] = decay * s[i + 3] + k4.w * kd; op += s[i + 3] * q4.w;
+            s[i]     = decay * s[i]     + k4.x * kd; op4[0] += s[i]     * q4.x;
+            s[i + 1] = decay * s[i + 1] + k4.y * kd; op4[1] += s[i + 1] * q4.y;
+            s[i + 2] = decay * s[i + 2] + k4.z * kd; op4[2] += s[i + 2] * q4.z;
+            s[i + 3] = decay * s[i + 3] + k4.w * kd; op4[3] += s[i + 3] * q4.w;
         }
-        red2[rg][c] = op;
+        red2[rg][c] = (op4[0] + op4[1]) + (op4[2] + op4[3]);
         __syncthreads();
         if (rg == 0) {
             const float o = (red2[0][c] + red2[1][c] + red2[2][c] + red2[3][c]) * inv_q;
@@ -156,6 +165,32 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
 #pragma unroll
     for (int i = 0; i < R; ++i) Sh[(uint64_t)(rg * R + i) * D + j] = s[i];
     if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
+}
+
+/* The per-position scalars of a run of positions, off the serial path: a warp a (sequence, position, key head) folds
+ * |q|^2 and |k|^2 and writes {1/sqrt(|q|^2 + 1e-6)/sqrt(d), 1/sqrt(|k|^2 + 1e-6), e^g, beta} for each of its value heads. */
+template <int D, int DT>
+__global__ void __launch_bounds__(128) deltanet_scalars_kernel(float4* sc, const uint16_t* conved, const uint16_t* beta, const uint16_t* g,
+                                                               uint32_t k_heads, uint32_t v_heads, uint64_t items) {
+    using E = Elem<DT>;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rep = v_heads / k_heads;
+    const uint64_t ch = (uint64_t)(2 * k_heads + v_heads) * D;
+    for (uint64_t it = (uint64_t)blockIdx.x * 4 + (threadIdx.x >> 5); it < items; it += (uint64_t)gridDim.x * 4) {
+        const uint64_t bt = it / k_heads; const uint32_t kh = (uint32_t)(it % k_heads);
+        const uint16_t* row = conved + bt * ch;
+        float qq = 0.f, kk = 0.f;
+        for (int e = lane; e < D; e += 32) {
+            const float qe = E::to_float(row[kh * D + e]), ke = E::to_float(row[(k_heads + kh) * D + e]);
+            qq += qe * qe; kk += ke * ke;
+        }
+        for (int x = 16; x > 0; x >>= 1) { qq += __shfl_xor_sync(0xffffffffu, qq, x); kk += __shfl_xor_sync(0xffffffffu, kk, x); }
+        const float inv_q = 1.0f / sqrtf(qq + 1e-6f) / sqrtf((float)D), inv_k = 1.0f / sqrtf(kk + 1e-6f);
+        for (uint32_t x = lane; x < rep; x += 32) {
+            const uint64_t hh = bt * v_heads + kh * rep + x;
+            sc[hh] = make_float4(inv_q, inv_k, expf(E::to_float(g[hh])), E::to_float(beta[hh]));
+        }
+    }
 }
 
 /* out <- half(out · rsqrt(mean(out^2) + 1e-6) · w · gate(z)), the head's sum of squares read from the blocks' parts. */
@@ -214,8 +249,22 @@ static cudaError_t launch_dn(const DeltaCall& c, float* ss) {
     P.S = c.S; P.conved = c.conved; P.z = c.z; P.beta = c.beta; P.g = c.g; P.w = c.w; P.out = c.out; P.ss = ss; P.over = c.over;
     P.k_heads = c.k_heads; P.v_heads = c.v_heads; P.seqs = c.seqs; P.rows = c.rows; P.gate = c.gate;
     const unsigned blocks = c.seqs * c.v_heads * (D / DN_COLS);
-    deltanet_steps_kernel<D, DT><<<blocks, DN_THREADS, 0, c.stream>>>(P);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e;
+    if (c.rows > 1) {
+        /* a run of positions: the norms, decays and betas of every position first, in parallel */
+        float4* sc = reinterpret_cast<float4*>(ss + (((size_t)c.seqs * c.rows * c.v_heads * (D / DN_COLS) + 3) & ~(size_t)3));
+        const uint64_t items = (uint64_t)c.seqs * c.rows * c.k_heads;
+        uint64_t nb = (items + 3) / 4; if (nb > 148 * 32) nb = 148 * 32;
+        deltanet_scalars_kernel<D, DT><<<(unsigned)nb, 128, 0, c.stream>>>(sc, c.conved, c.beta, c.g, c.k_heads, c.v_heads, items);
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        note_launch(1);
+        P.sc = sc;
+        deltanet_steps_kernel<D, DT, true><<<blocks, DN_THREADS, 0, c.stream>>>(P);
+    } else {
+        P.sc = nullptr;
+        deltanet_steps_kernel<D, DT, false><<<blocks, DN_THREADS, 0, c.stream>>>(P);
+    }
+    e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     const uint64_t heads_total = (uint64_t)c.seqs * c.rows * c.v_heads;
     /* z and out are laid out [seq][row][head][d], so one flat pass covers every sequence */
@@ -228,7 +277,8 @@ static cudaError_t launch_dn(const DeltaCall& c, float* ss) {
 cudaError_t deltanet_launch(const DeltaCall& c) {
     if (c.rows == 0 || c.seqs == 0) return cudaSuccess;
     float* ss = nullptr;
-    cudaError_t e = ss_scratch((size_t)c.seqs * c.rows * c.v_heads * (c.head_dim / DN_COLS), &ss);
+    /* per-block sums of squares, then (for a run of positions) four scalars per position and value head */
+    cudaError_t e = ss_scratch((size_t)c.seqs * c.rows * c.v_heads * (c.head_dim / DN_COLS) + 4 + (c.rows > 1 ? 4 * (size_t)c.seqs * c.rows * c.v_heads : 0), &ss);
     if (e != cudaSuccess) return e;
 #define SV_DN(DD) (c.dtype == SV_DTYPE_BF16 ? launch_dn<DD, SV_DTYPE_BF16>(c, ss) : launch_dn<DD, SV_DTYPE_FP16>(c, ss))
     if (c.head_dim == 64) return SV_DN(64);
