@@ -376,8 +376,10 @@ int silvann_b200_tier_stats(const silvann_b200_tier* tier, uint64_t* h2d_bytes, 
 
 /* Causal grouped-query prefill in one kernel — attention_causal_scores_grouped + attention_causal_softmax +
  * attention_causal_mix (kernels.cuh:1028-1081, 2051-2060): row r is position first + r and attends cache rows
- * 0..first+r.  q, o [rows][q_heads][head_dim]; k, v [first + rows][kv_heads][head_dim]. */
-int silvann_b200_prefill(void* o, const void* q, const void* k, const void* v, uint64_t q_heads, uint64_t kv_heads,
+ * 0..first+r.  q, o [rows][q_heads][head_dim]; k, v [first + rows][kv_heads][head_dim].  With `res` (may be null, as may
+ * `o`, not both) every row's heads also leave their residual (m, l, acc) at res + row·q_heads·(head_dim + 2), the
+ * answer of attention_weights_rows + attention_residual_mix_rows (nn/gpu/doors.cuh:406-431) for a later merge. */
+int silvann_b200_prefill(void* o, float* res, const void* q, const void* k, const void* v, uint64_t q_heads, uint64_t kv_heads,
                          uint64_t head_dim, uint64_t first, uint64_t rows, int dtype, sv_fault* over, void* stream);
 
 /* Gated DeltaNet over `rows` positions of `seqs` independent sequences (deltanet_steps_gate, kernels.cuh:650-718,

@@ -76,6 +76,12 @@ class Port:
             "oracle_attention_causal_mix": [vp, vp, vp, u64, u64, u64, u64, u64, i32, vp],
             "oracle_prefill": [vp, vp, vp, vp, vp, u64, u64, u64, u64, u64, i32, vp],
             "oracle_deltanet_steps": [vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, C.c_uint, i32, vp],
+            "oracle_attention_scores_grouped_rows": [vp, u64, vp, u64, vp, u64, vp, u64, u64, u64, u64, i32],
+            "oracle_attention_softmax_lens": [vp, u64, vp, u64, u64],
+            "oracle_attention_softmax_sink": [vp, vp, u64, u64],
+            "oracle_attention_mix_rows": [vp, u64, vp, u64, vp, u64, vp, u64, u64, u64, u64, i32, vp],
+            "oracle_deltanet_gates_rows": [vp, vp, vp, vp, vp, vp, u64, u64],
+            "oracle_deltanet_conv_steps": [vp, vp, vp, vp, u64, u64],
         }
         for name, args in sig.items():
             fn = getattr(self.lib, name)
@@ -146,6 +152,53 @@ class Port:
         return out
 
 
+def gathered_rows(impl, q, k, v, lens, qh, kvh, d, dtype=FP16):
+    """The per-row (gathered key set) door sequence GLM's sparse attention runs — attention_scores_grouped_rows,
+    attention_softmax_lens, attention_mix_rows (ai_z__glm_5_3 layer__abi.cuh:861-1055) — on either checker.
+    q [rows][qh][d]; k, v [rows][most][kvh][d]; lens uint32 [rows].  Answers (weights buffer, o bits)."""
+    rows, most = len(lens), k.shape[1]
+    p = np.zeros((rows, qh * most), np.float32)
+    o = np.zeros((rows, qh, d), np.uint16)
+    over = np.zeros(1, np.uint32)
+    lens = np.ascontiguousarray(lens, np.uint32)
+    if isinstance(impl, Port):
+        impl.lib.oracle_attention_scores_grouped_rows(_p(p), qh * most, _p(q), qh * d, _p(k), most * kvh * d, _p(lens), qh, kvh, d, rows, dtype)
+        impl.lib.oracle_attention_softmax_lens(_p(p), qh * most, _p(lens), qh, rows)
+        impl.lib.oracle_attention_mix_rows(_p(o), qh * d, _p(p), qh * most, _p(v), most * kvh * d, _p(lens), qh, kvh, d, rows, dtype, _p(over))
+    else:
+        impl.nn.attention_scores_grouped_rows(_p(p), qh * most, _p(q), qh * d, _p(k), most * kvh * d, _p(lens), qh, kvh, d, most, rows)
+        impl.nn.attention_softmax_lens(_p(p), qh * most, _p(lens), qh, rows)
+        impl.nn.attention_mix_rows(_p(o), qh * d, _p(p), qh * most, _p(v), most * kvh * d, _p(lens), qh, kvh, d, rows, _p(over))
+        impl.wait()
+    return p, o
+
+
+def softmax_sink(impl, scores, sink):
+    p = np.ascontiguousarray(scores, np.float32).copy()
+    rows, length = p.shape
+    if isinstance(impl, Port):
+        impl.lib.oracle_attention_softmax_sink(_p(p), _p(sink), rows, length)
+    else:
+        impl.nn.attention_softmax_sink(_p(p), _p(sink), rows, length)
+        impl.wait()
+    return p
+
+
+def deltanet_inputs(impl, a, b, a_log, dt_bias, w, x, window, heads, rows, ch):
+    """deltanet_gates_rows, then deltanet_conv_steps over `rows` rows (window updated in place)."""
+    beta, g = np.zeros((rows, heads), np.uint16), np.zeros((rows, heads), np.uint16)
+    o = np.zeros((rows, ch), np.uint16)
+    over = np.zeros(1, np.uint32)
+    if isinstance(impl, Port):
+        impl.lib.oracle_deltanet_gates_rows(_p(beta), _p(g), _p(a), _p(b), _p(a_log), _p(dt_bias), heads, rows)
+        impl.lib.oracle_deltanet_conv_steps(_p(o), _p(window), _p(w), _p(x), ch, rows)
+    else:
+        impl.nn.deltanet_gates_rows(_p(beta), _p(g), _p(a), _p(b), _p(a_log), _p(dt_bias), heads, rows, _p(over))
+        impl.nn.deltanet_conv_steps(_p(o), _p(window), _p(w), _p(x), ch, rows, _p(over))
+        impl.wait()
+    return beta, g, o
+
+
 # ---- the reference's own CPU family --------------------------------------------------------------------------------
 
 class Reference:
@@ -214,6 +267,16 @@ class Reference:
             n = min(chunk, rows - first)
             o[first:first + n] = self.causal(q[first:first + n], k, v, qh, kvh, d, first, n, p)
         return o
+
+    def residual_rows(self, q, k, v, qh, kvh, d, first, rows):
+        """attention_weights_rows + attention_residual_mix_rows: a residual a row, [rows][qh][d + 2]."""
+        span = first + rows
+        p = np.zeros((rows * qh, span), np.float32)
+        res = np.zeros((rows, qh, d + 2), np.float32)
+        self.nn.attention_weights_rows(_p(p), _p(res), _p(q), _p(k), qh, kvh, d, first, rows)
+        self.nn.attention_residual_mix_rows(_p(res), _p(p), _p(v), qh, kvh, d, first, rows)
+        self.wait()
+        return res
 
     def deltanet(self, S, conved, z, beta, g, w, kh, vh, d, rows, gate=0):
         out = np.empty((rows, vh * d), np.uint16)

@@ -262,3 +262,73 @@ void oracle_vector_sum(uint16_t* out, const uint16_t* const* parts, uint64_t cou
     }
     if (hit && over) *over = ORACLE_FAULT_OVERFLOW;
 }
+
+/* ---- the per-row (gathered key set) forms, the sink softmax, and DeltaNet's input doors ------------------------------ */
+
+/* attention_scores_grouped_rows (kernels.cuh:957-972): row u's heads at q + u·q_row, its lens[u] keys at k + u·k_row, raw
+ * scaled scores at p + u·p_row, a head's lens[u] apart */
+void oracle_attention_scores_grouped_rows(float* p, uint64_t p_row, const uint16_t* q, uint64_t q_row, const uint16_t* k, uint64_t k_row,
+                                          const uint32_t* lens, uint64_t qh, uint64_t kvh, uint64_t d, uint64_t rows, int dt) {
+    const uint64_t group = qh / kvh, row = kvh * d;
+    for (uint64_t u = 0; u < rows; ++u)
+        for (uint64_t h = 0; h < qh; ++h)
+            head_scores(p + u * p_row + h * lens[u], q + u * q_row + h * d, k + u * k_row + (h / group) * d, row, d, lens[u], dt);
+}
+/* attention_softmax_lens (kernels.cuh:1104-1110) */
+void oracle_attention_softmax_lens(float* p, uint64_t p_row, const uint32_t* lens, uint64_t heads, uint64_t rows) {
+    for (uint64_t u = 0; u < rows; ++u)
+        for (uint64_t h = 0; h < heads; ++h) head_softmax(p + u * p_row + h * lens[u], lens[u], 1, 0, 0);
+}
+/* attention_softmax_sink (kernels.cuh:1115-1131): one more term exp(sink[r]) in the sum, and in the maximum */
+void oracle_attention_softmax_sink(float* p, const uint16_t* sink, uint64_t rows, uint64_t len) {
+    for (uint64_t r = 0; r < rows; ++r) {
+        float* ph = p + r * len;
+        const float sk = f16_to_f32(sink[r]);
+        float top = sk, sum = 0.0f;
+        for (uint64_t t = 0; t < len; ++t) if (ph[t] > top) top = ph[t];
+        for (uint64_t t = 0; t < len; ++t) { ph[t] = expf(ph[t] - top); sum += ph[t]; }
+        const float inv = 1.0f / (sum + expf(sk - top));
+        for (uint64_t t = 0; t < len; ++t) ph[t] *= inv;
+    }
+}
+/* attention_mix_rows (kernels.cuh:1169-1178) */
+void oracle_attention_mix_rows(uint16_t* o, uint64_t o_row, const float* p, uint64_t p_row, const uint16_t* v, uint64_t v_row, const uint32_t* lens,
+                               uint64_t qh, uint64_t kvh, uint64_t d, uint64_t rows, int dt, unsigned* over) {
+    const uint64_t group = qh / kvh, row = kvh * d;
+    int hit = 0;
+    for (uint64_t u = 0; u < rows; ++u)
+        for (uint64_t h = 0; h < qh; ++h)
+            for (uint64_t e = 0; e < d; ++e) {
+                float sum = 0.0f;
+                for (uint64_t t = 0; t < lens[u]; ++t) sum += p[u * p_row + h * lens[u] + t] * ld16(v[u * v_row + t * row + (h / group) * d + e], dt);
+                o[u * o_row + h * d + e] = st16(sum, dt, &hit);
+            }
+    if (hit && over) *over = ORACLE_FAULT_OVERFLOW;
+}
+/* deltanet_gates_rows (kernels.cuh:2081-2101): every intermediate rounded to a half where the reference rounds it */
+void oracle_deltanet_gates_rows(uint16_t* beta, uint16_t* g, const uint16_t* a, const uint16_t* b, const uint16_t* a_log, const uint16_t* dt_bias,
+                                uint64_t heads, uint64_t rows) {
+    for (uint64_t i = 0; i < heads * rows; ++i) {
+        const uint64_t h = i % heads;
+        beta[i] = f32_to_f16(1.0f / (1.0f + expf(-f16_to_f32(b[i]))), 0);
+        const float sum = f16_to_f32(f32_to_f16(f16_to_f32(a[i]) + f16_to_f32(dt_bias[h]), 0));
+        const float mag = sum < 0.0f ? -sum : sum, top = sum > 0.0f ? sum : 0.0f;
+        const float sp = f16_to_f32(f32_to_f16(top + logf(1.0f + expf(-mag)), 0));
+        const float ea = f16_to_f32(f32_to_f16(expf(f16_to_f32(a_log[h])), 0));
+        const float prod = f16_to_f32(f32_to_f16(sp * ea, 0));
+        g[i] = f32_to_f16(prod * -1.0f, 0);
+    }
+}
+/* deltanet_conv_steps (kernels.cuh:2106-2125; rows = 1 is deltanet_conv_step, :627-645): four taps over a kept window of
+ * three and the new input, silu, then the window slides */
+void oracle_deltanet_conv_steps(uint16_t* o, uint16_t* s, const uint16_t* w, const uint16_t* x, uint64_t ch, uint64_t rows) {
+    for (uint64_t c = 0; c < ch; ++c)
+        for (uint64_t t = 0; t < rows; ++t) {
+            const uint16_t xt = x[t * ch + c];
+            float acc = 0.0f;
+            for (int k = 0; k < 3; ++k) acc += f16_to_f32(w[c * 4 + k]) * f16_to_f32(s[c * 3 + k]);
+            acc += f16_to_f32(w[c * 4 + 3]) * f16_to_f32(xt);
+            o[t * ch + c] = f32_to_f16(acc / (1.0f + expf(-acc)), 0);
+            s[c * 3] = s[c * 3 + 1]; s[c * 3 + 1] = s[c * 3 + 2]; s[c * 3 + 2] = xt;
+        }
+}

@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include "kernels_deltanet.h"
 #include "kernels.h"
+#include <stdlib.h>
 
 namespace sv {
 
@@ -274,8 +275,36 @@ static cudaError_t launch_dn(const DeltaCall& c, float* ss) {
     return cudaGetLastError();
 }
 
+template <int D, int DT>
+static cudaError_t launch_norm(const DeltaCall& c, const float* ss) {
+    const uint64_t heads_total = (uint64_t)c.seqs * c.rows * c.v_heads;
+    uint64_t nb = (heads_total * D + 255) / 256; if (nb > 148 * 16) nb = 148 * 16;
+    deltanet_norm_kernel<D, DT><<<(unsigned)nb, 256, 0, c.stream>>>(c.out, ss, c.z, c.w, heads_total, c.gate, c.over);
+    note_launch(1);
+    return cudaGetLastError();
+}
+cudaError_t deltanet_norm_launch(const DeltaCall& c, const float* ss) {
+    if (c.head_dim == 64) return c.dtype == SV_DTYPE_BF16 ? launch_norm<64, SV_DTYPE_BF16>(c, ss) : launch_norm<64, SV_DTYPE_FP16>(c, ss);
+    if (c.head_dim == 128) return c.dtype == SV_DTYPE_BF16 ? launch_norm<128, SV_DTYPE_BF16>(c, ss) : launch_norm<128, SV_DTYPE_FP16>(c, ss);
+    return cudaErrorInvalidValue;
+}
+
+static bool chunked_enabled() {
+    static const bool on = []() { const char* v = getenv("SILVANN_B200_DELTANET_CHUNKED"); return !(v && v[0] == '0'); }();
+    return on;
+}
+
 cudaError_t deltanet_launch(const DeltaCall& c) {
     if (c.rows == 0 || c.seqs == 0) return cudaSuccess;
+    if (chunked_enabled() && deltanet_chunked_fits(c)) {
+        /* a run of positions: 64 at a time */
+        const size_t ss_floats = (((size_t)c.seqs * c.rows * c.v_heads * (c.head_dim / DN_COLS)) + 3) & ~(size_t)3;
+        float* buf = nullptr;
+        cudaError_t e = ss_scratch(ss_floats + deltanet_chunked_scratch_floats(c), &buf);
+        if (e != cudaSuccess) return e;
+        if ((e = deltanet_chunked_launch(c, buf, buf + ss_floats)) != cudaSuccess) return e;
+        return deltanet_norm_launch(c, buf);
+    }
     float* ss = nullptr;
     /* per-block sums of squares, then (for a run of positions) four scalars per position and value head */
     cudaError_t e = ss_scratch((size_t)c.seqs * c.rows * c.v_heads * (c.head_dim / DN_COLS) + 4 + (c.rows > 1 ? 4 * (size_t)c.seqs * c.rows * c.v_heads : 0), &ss);

@@ -295,15 +295,15 @@ SV_EXPORT int silvann_b200_paged_append(silvann_b200_plan* p, void* k_pool, void
 
 /* ---------------------------------------------------------------------------------------------------------- */
 
-SV_EXPORT int silvann_b200_prefill(void* o, const void* q, const void* k, const void* v, uint64_t q_heads, uint64_t kv_heads, uint64_t head_dim,
+SV_EXPORT int silvann_b200_prefill(void* o, float* res, const void* q, const void* k, const void* v, uint64_t q_heads, uint64_t kv_heads, uint64_t head_dim,
                                    uint64_t first, uint64_t rows, int dtype, sv_fault* over, void* stream) {
     called();
-    if (!o || !q || !k || !v) return fail(SILVANN_B200_E_ARGUMENT, "prefill: a null operand");
+    if ((!o && !res) || !q || !k || !v) return fail(SILVANN_B200_E_ARGUMENT, "prefill: a null operand");
     if (!dtype_ok(dtype)) return fail(SILVANN_B200_E_ARGUMENT, "prefill: dtype %d", dtype);
     if (rows == 0 || kv_heads == 0 || q_heads % kv_heads != 0) return fail(SILVANN_B200_E_ARGUMENT, "prefill: rows %llu, heads %llu over %llu", (unsigned long long)rows, (unsigned long long)q_heads, (unsigned long long)kv_heads);
     sv::PrefillCall c;
     memset(&c, 0, sizeof c);
-    c.o = o; c.q = q; c.k = k; c.v = v; c.q_heads = (uint32_t)q_heads; c.kv_heads = (uint32_t)kv_heads; c.head_dim = (uint32_t)head_dim;
+    c.o = o; c.res = res; c.q = q; c.k = k; c.v = v; c.q_heads = (uint32_t)q_heads; c.kv_heads = (uint32_t)kv_heads; c.head_dim = (uint32_t)head_dim;
     c.first = first; c.rows = rows; c.dtype = dtype; c.over = over; c.stream = (cudaStream_t)stream;
     if (!sv::prefill_fits(c)) return fail(SILVANN_B200_E_ARGUMENT, "prefill: head_dim %llu or operand alignment is outside the kernel's fit", (unsigned long long)head_dim);
     cudaError_t e = sv::prefill_launch(c);

@@ -55,7 +55,7 @@ static bool fuse_enabled() {
 }
 
 /* ---- the deferred first door of a pair, per device ---- */
-enum PendingKind { NONE = 0, SCORES, WEIGHTS, CAUSAL_RAW, CAUSAL_SOFT };
+enum PendingKind { NONE = 0, SCORES, WEIGHTS, CAUSAL_RAW, CAUSAL_SOFT, WEIGHTS_ROWS };
 struct Pending {
     int kind;
     float* p; float* res; const uint16_t* q; const uint16_t* k;
@@ -73,6 +73,13 @@ static void run_pending_locked(Pending& pd) {
         case WEIGHTS:     check("attention_weights", sv::scores_launch(x.p, x.q, x.k, x.qh, x.kvh, x.d, x.length, 1, x.res, 0)); break;
         case CAUSAL_RAW:  check("attention_causal_scores_grouped", sv::causal_scores_launch(x.p, x.q, x.k, x.qh, x.kvh, x.d, x.first, x.rows, false, 0)); break;
         case CAUSAL_SOFT: check("attention_causal_softmax", sv::causal_scores_launch(x.p, x.q, x.k, x.qh, x.kvh, x.d, x.first, x.rows, true, 0)); break;
+        case WEIGHTS_ROWS: {        /* the one-row door a row, as the contract defines the many-row form (nn/gpu/doors.cuh:406-424) */
+            const uint64_t span = x.first + x.rows;
+            for (uint64_t r = 0; r < x.rows; ++r)
+                check("attention_weights_rows", sv::scores_launch(x.p + r * x.qh * span, x.q + r * x.qh * x.d, x.k, x.qh, x.kvh, x.d, x.first + r + 1, 1,
+                                                                  x.res + r * x.qh * (x.d + 2), 0));
+            break;
+        }
         default: return;
     }
     bump(SILVANN_B200_COUNTER_FLUSHED);
@@ -341,6 +348,71 @@ static void d_attention_causal_mix(sv_h16* o, const float* p, const sv_h16* v, s
     }
     check("attention_causal_mix", sv::causal_mix_launch(o, p, v, qh, kvh, d, first, rows, over, 0));
 }
+static void d_attention_weights_rows(float* p, float* res, const sv_h16* q, const sv_h16* k, sv_u64 qh, sv_u64 kvh, sv_u64 d, sv_u64 first, sv_u64 rows) {
+    flush();
+    const int dev = current_device();
+    if (dev >= 0 && dev < DEVICES_MAX && small_enough(qh, kvh, d, first + rows) && rows) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        g_pending[dev] = Pending{WEIGHTS_ROWS, p, res, q, k, qh, kvh, d, 0, first, rows};
+        if (!fuse_enabled()) run_pending_locked(g_pending[dev]);
+        return;
+    }
+    launch_refused("attention_weights_rows", cudaSuccess);
+}
+static void d_attention_residual_mix_rows(float* res, const float* p, const sv_h16* v, sv_u64 qh, sv_u64 kvh, sv_u64 d, sv_u64 first, sv_u64 rows) {
+    const int dev = current_device();
+    if (dev >= 0 && dev < DEVICES_MAX) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        Pending& x = g_pending[dev];
+        if (x.kind == WEIGHTS_ROWS && x.p == p && x.res == res && x.qh == qh && x.kvh == kvh && x.d == d && x.first == first && x.rows == rows) {
+            sv::PrefillCall c;
+            memset(&c, 0, sizeof c);
+            c.res = res; c.q = x.q; c.k = x.k; c.v = v; c.q_heads = (uint32_t)qh; c.kv_heads = (uint32_t)kvh; c.head_dim = (uint32_t)d;
+            c.first = first; c.rows = rows; c.dtype = SV_DTYPE_FP16; c.stream = 0;
+            if (sv::prefill_fits(c)) {
+                x.kind = NONE;
+                check("attention_weights_rows+attention_residual_mix_rows", sv::prefill_launch(c));
+                bump(SILVANN_B200_COUNTER_FUSED_PREFILL);
+                return;
+            }
+        }
+        run_pending_locked(x);
+    }
+    const uint64_t span = first + rows;
+    for (uint64_t r = 0; r < rows; ++r)
+        check("attention_residual_mix_rows", sv::mix_launch(nullptr, res + r * qh * (d + 2), p + r * qh * span, v, qh, kvh, d, first + r + 1, nullptr, 0));
+}
+static void d_attention_scores_grouped_rows(float* p, sv_u64 p_row, const sv_h16* q, sv_u64 q_row, const sv_h16* k, sv_u64 k_row, const sv_u32* lens,
+                                            sv_u64 qh, sv_u64 kvh, sv_u64 d, sv_u64 most, sv_u64 rows) {
+    flush(); (void)most;
+    check("attention_scores_grouped_rows", sv::scores_grouped_rows_launch(p, p_row, q, q_row, k, k_row, lens, qh, kvh, d, rows, 0));
+}
+static void d_attention_softmax_lens(float* p, sv_u64 p_row, const sv_u32* lens, sv_u64 heads, sv_u64 rows) {
+    flush();
+    check("attention_softmax_lens", sv::softmax_lens_launch(p, p_row, lens, heads, rows, 0));
+}
+static void d_attention_softmax_sink(float* p, const sv_h16* sink, sv_u64 rows, sv_u64 length) {
+    flush();
+    check("attention_softmax_sink", sv::softmax_sink_launch(p, sink, rows, length, 0));
+}
+static void d_attention_mix_rows(sv_h16* o, sv_u64 o_row, const float* p, sv_u64 p_row, const sv_h16* v, sv_u64 v_row, const sv_u32* lens,
+                                 sv_u64 qh, sv_u64 kvh, sv_u64 d, sv_u64 rows, sv_fault* over) {
+    flush();
+    check("attention_mix_rows", sv::mix_rows_launch(o, o_row, p, p_row, v, v_row, lens, qh, kvh, d, rows, over, 0));
+}
+static void d_deltanet_gates_rows(sv_h16* beta, sv_h16* g, const sv_h16* a, const sv_h16* b, const sv_h16* a_log, const sv_h16* dt_bias,
+                                  sv_u64 heads, sv_u64 rows, sv_fault* over) {
+    flush();
+    check("deltanet_gates_rows", sv::deltanet_gates_rows_launch(beta, g, a, b, a_log, dt_bias, heads, rows, over, 0));
+}
+static void d_deltanet_conv_step(sv_h16* o, sv_h16* s, const sv_h16* w, const sv_h16* x, sv_u64 ch, sv_fault* over) {
+    flush();
+    check("deltanet_conv_step", sv::deltanet_conv_steps_launch(o, s, w, x, ch, 1, over, 0));
+}
+static void d_deltanet_conv_steps(sv_h16* o, sv_h16* s, const sv_h16* w, const sv_h16* x, sv_u64 ch, sv_u64 rows, sv_fault* over) {
+    flush();
+    check("deltanet_conv_steps", sv::deltanet_conv_steps_launch(o, s, w, x, ch, rows, over, 0));
+}
 static void deltanet_door(const char* name, float* S, const sv_h16* conved, const sv_h16* z, const sv_h16* beta, const sv_h16* g, const sv_h16* w,
                           sv_h16* out, sv_u64 kh, sv_u64 vh, sv_u64 d, sv_u64 rows, unsigned gate, sv_fault* over) {
     flush();
@@ -401,6 +473,15 @@ static void install_doors() {
     g_nn.deltanet_steps = d_deltanet_steps;
     g_nn.deltanet_steps_gate = d_deltanet_steps_gate;
     g_nn.vector_sum = d_vector_sum;
+    g_nn.attention_weights_rows = d_attention_weights_rows;
+    g_nn.attention_residual_mix_rows = d_attention_residual_mix_rows;
+    g_nn.attention_scores_grouped_rows = d_attention_scores_grouped_rows;
+    g_nn.attention_softmax_lens = d_attention_softmax_lens;
+    g_nn.attention_softmax_sink = d_attention_softmax_sink;
+    g_nn.attention_mix_rows = d_attention_mix_rows;
+    g_nn.deltanet_gates_rows = d_deltanet_gates_rows;
+    g_nn.deltanet_conv_step = d_deltanet_conv_step;
+    g_nn.deltanet_conv_steps = d_deltanet_conv_steps;
 }
 
 }  // namespace svf

@@ -78,6 +78,17 @@ cudaError_t causal_scores_launch(float* p, const uint16_t* q, const uint16_t* k,
 cudaError_t causal_softmax_launch(float* p, uint64_t qh, uint64_t first, uint64_t rows, cudaStream_t st);
 cudaError_t causal_mix_launch(uint16_t* o, const float* p, const uint16_t* v, uint64_t qh, uint64_t kvh, uint64_t d,
                               uint64_t first, uint64_t rows, unsigned int* over, cudaStream_t st);
+/* ---- the doors either side of the hot kernels (more_doors.cu) ------------------------------------------------ */
+cudaError_t scores_grouped_rows_launch(float* p, uint64_t p_row, const uint16_t* q, uint64_t q_row, const uint16_t* k, uint64_t k_row,
+                                       const uint32_t* lens, uint64_t qh, uint64_t kvh, uint64_t d, uint64_t rows, cudaStream_t st);
+cudaError_t softmax_lens_launch(float* p, uint64_t p_row, const uint32_t* lens, uint64_t heads, uint64_t rows, cudaStream_t st);
+cudaError_t softmax_sink_launch(float* p, const uint16_t* sink, uint64_t rows, uint64_t length, cudaStream_t st);
+cudaError_t mix_rows_launch(uint16_t* o, uint64_t o_row, const float* p, uint64_t p_row, const uint16_t* v, uint64_t v_row, const uint32_t* lens,
+                            uint64_t qh, uint64_t kvh, uint64_t d, uint64_t rows, unsigned int* over, cudaStream_t st);
+cudaError_t deltanet_gates_rows_launch(uint16_t* beta, uint16_t* g, const uint16_t* a, const uint16_t* b, const uint16_t* a_log,
+                                       const uint16_t* dt_bias, uint64_t heads, uint64_t rows, unsigned int* over, cudaStream_t st);
+cudaError_t deltanet_conv_steps_launch(uint16_t* o, uint16_t* s, const uint16_t* w, const uint16_t* x, uint64_t ch, uint64_t rows,
+                                       unsigned int* over, cudaStream_t st);
 cudaError_t vector_sum_launch(uint16_t* out, const uint64_t* parts, uint64_t count, uint64_t n, unsigned int* over,
                               cudaStream_t st);
 
@@ -86,7 +97,8 @@ cudaError_t vector_sum_launch(uint16_t* out, const uint64_t* parts, uint64_t cou
 /* ---- causal GQA prefill on tcgen05 / TMEM (prefill.cu) ------------------------------------------------------- */
 namespace sv {
 struct PrefillCall {
-    void* o;                  /* [rows][q_heads][head_dim] 16-bit */
+    void* o;                  /* [rows][q_heads][head_dim] 16-bit, or null */
+    float* res;               /* [rows][q_heads][head_dim + 2] fp32 residuals (m, l, acc), or null */
     const void* q;            /* [rows][q_heads][head_dim] */
     const void* k;            /* [first + rows][kv_heads][head_dim] */
     const void* v;

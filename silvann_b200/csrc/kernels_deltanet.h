@@ -20,6 +20,12 @@ struct DeltaCall {
     cudaStream_t stream;
 };
 bool deltanet_fits(const DeltaCall& c);
+/* the 64-position chunked form (deltanet_chunked.cu): runs of at least 32 positions at head_dim 64 or 128 */
+bool deltanet_chunked_fits(const DeltaCall& c);
+size_t deltanet_chunked_scratch_floats(const DeltaCall& c);
+cudaError_t deltanet_chunked_launch(const DeltaCall& c, float* ss, float* prep);
+/* the read-out's norm and gate over what either form left in `out` and `ss` (deltanet.cu) */
+cudaError_t deltanet_norm_launch(const DeltaCall& c, const float* ss);
 cudaError_t deltanet_launch(const DeltaCall& c);
 
 }  // namespace sv

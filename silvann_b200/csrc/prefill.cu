@@ -143,6 +143,7 @@ template <int D> struct PrefillCfg {
 
 struct PrefillParams {
     uint16_t* o;
+    float* res;
     unsigned int* over;
     unsigned int* status;
     uint32_t q_heads, kv_heads, group;
@@ -379,15 +380,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             __syncwarp();
             if (lane == 0) mbar_arrive(&xbar[quad]);
             const bool met = __all_sync(0xffffffffu, mbar_wait(&xbar[quad], nt & 1, abort_flag, P.status));
-            const float inv = met ? 1.0f / (l + xch[(half ^ 1) * PF_BM + r]) : 0.f;
+            const float l_row = met ? l + xch[(half ^ 1) * PF_BM + r] : 0.f;
+            const float inv = met ? 1.0f / l_row : 0.f;
             bool hit = false;
             uint16_t* orow = P.o + ((size_t)grow_ * P.q_heads + h) * D;
+            /* the residual form of the answer: (m, l, acc) as attention_weights_rows + attention_residual_mix_rows leave
+             * it — m is the reference the weights were taken against (natural-log units), acc is not divided */
+            float* rrow = P.res ? P.res + ((size_t)grow_ * P.q_heads + h) * (D + 2) : nullptr;
+            if (rrow && met && half == 0 && grow_ < (int)P.rows) { rrow[0] = m_ref * SV_LN2; rrow[1] = l_row; }
 #pragma unroll 1
             for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
                 uint32_t ov[32];
                 tmem_ld32(t_o + c0 + lane_off, ov);
                 tmem_wait_ld();
-                if (grow_ < (int)P.rows) {
+                if (rrow && grow_ < (int)P.rows) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 2) *reinterpret_cast<float2*>(rrow + 2 + c0 + c) = make_float2(__uint_as_float(ov[c]), __uint_as_float(ov[c + 1]));
+                }
+                if (P.o && grow_ < (int)P.rows) {
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
                         uint32_t w[4];
@@ -416,6 +426,7 @@ bool prefill_fits(const PrefillCall& c) {
     if (c.head_dim != 64 && c.head_dim != 128 && c.head_dim != 256) return false;
     if (c.kv_heads == 0 || c.q_heads % c.kv_heads != 0) return false;
     if (((uintptr_t)c.q | (uintptr_t)c.k | (uintptr_t)c.v | (uintptr_t)c.o) & 15u) return false;
+    if ((!c.o && !c.res) || ((uintptr_t)c.res & 7u)) return false;
     if (c.rows == 0 || c.first + c.rows > 0x7FFFFF00ull) return false;
     if ((uint64_t)((c.rows + PF_BM - 1) / PF_BM) * c.q_heads > 0x7FFFFFFFull) return false;
     return encode_tiled_fn() != nullptr;
@@ -431,7 +442,7 @@ static cudaError_t launch_prefill(const PrefillCall& c) {
     if (!make_map_2d_sw128(&km, c.k, kcols, c.first + c.rows, kcols * 2, 64u, PF_BN, bf)) return cudaErrorInvalidValue;
     if (!make_map_2d_sw128(&vm, c.v, kcols, c.first + c.rows, kcols * 2, 64u, PF_BN, bf)) return cudaErrorInvalidValue;
     PrefillParams P;
-    P.o = (uint16_t*)c.o; P.over = c.over; P.status = device_status_word();
+    P.o = (uint16_t*)c.o; P.res = c.res; P.over = c.over; P.status = device_status_word();
     P.q_heads = c.q_heads; P.kv_heads = c.kv_heads; P.group = c.q_heads / c.kv_heads;
     P.first = (uint32_t)c.first; P.rows = (uint32_t)c.rows; P.q_tiles = (uint32_t)((c.rows + PF_BM - 1) / PF_BM);
     P.scale_log2 = (1.0f / sqrtf((float)D)) * SV_LOG2E;

@@ -61,7 +61,7 @@ def lib():
             "silvann_b200_tier_destroy": [vp],
             "silvann_b200_tier_decode": [vp, vp, vp, vp, vp, vp, u64, vp, vp, u64, vp, vp],
             "silvann_b200_tier_stats": [vp, vp, vp],
-            "silvann_b200_prefill": [vp, vp, vp, vp, u64, u64, u64, u64, u64, i32, vp, vp],
+            "silvann_b200_prefill": [vp, vp, vp, vp, vp, u64, u64, u64, u64, u64, i32, vp, vp],
             "silvann_b200_deltanet": [vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u32, u32, i32, vp, vp],
         }
         for name, args in sigs.items():
@@ -176,8 +176,8 @@ class Tier:
         return {"h2d_bytes": b.value, "chunks": c.value}
 
 
-def prefill(o, q, k, v, q_heads, kv_heads, head_dim, first, rows, dtype=FP16, over=None, stream=None):
-    _check(lib().silvann_b200_prefill(addr(o), addr(q), addr(k), addr(v), q_heads, kv_heads, head_dim, first, rows, dtype, addr(over), stream))
+def prefill(o, q, k, v, q_heads, kv_heads, head_dim, first, rows, dtype=FP16, over=None, stream=None, res=None):
+    _check(lib().silvann_b200_prefill(addr(o), addr(res), addr(q), addr(k), addr(v), q_heads, kv_heads, head_dim, first, rows, dtype, addr(over), stream))
 
 
 def deltanet(S, conved, z, beta, g, w, out, k_heads, v_heads, head_dim, rows, seqs=1, gate=0, dtype=FP16, over=None, stream=None):

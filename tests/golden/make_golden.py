@@ -67,6 +67,30 @@ def main():
         o_step = R.deltanet(S, conved[rows:], z[rows:], beta[rows:], g[rows:], w, kh, vh, d, 1, gate)
         out[f"{tag}_S_step"], out[f"{tag}_o_step"] = S.copy(), o_step
 
+    # a residual a row (the tiered prompt path), and the per-row gathered forms, the sink softmax, DeltaNet's input doors
+    qh, kvh, d, first, rows = 4, 2, 64, 5, 6
+    q, k, v = bits((rows, qh, d), 0.5), bits((first + rows, kvh, d), 0.5), bits((first + rows, kvh, d), 0.5)
+    out["rr_shape"] = np.array([qh, kvh, d, first, rows])
+    out["rr_q"], out["rr_k"], out["rr_v"] = q, k, v
+    out["rr_res"] = R.residual_rows(q, k, v, qh, kvh, d, first, rows)
+    qh, kvh, d, most = 8, 1, 64, 20
+    lens = np.array([20, 7, 1, 13], np.uint32)
+    q, k, v = bits((4, qh, d), 0.5), bits((4, most, kvh, d), 0.5), bits((4, most, kvh, d), 0.5)
+    p, o = oracle.gathered_rows(R, q, k, v, lens, qh, kvh, d)
+    out["gr_shape"] = np.array([qh, kvh, d, most])
+    out["gr_lens"], out["gr_q"], out["gr_k"], out["gr_v"], out["gr_p"], out["gr_o"] = lens, q, k, v, p, o
+    sc = rng.standard_normal((5, 33), dtype=np.float32) * 2
+    sink = bits((5,), 2.0)
+    out["sink_scores"], out["sink_sink"], out["sink_p"] = sc, sink, oracle.softmax_sink(R, sc, sink)
+    heads, rows, ch = 6, 5, 48
+    a, b, a_log, dt_bias = bits((rows, heads)), bits((rows, heads)), bits((heads,)), bits((heads,))
+    w, x, window = bits((ch, 4), 0.5), bits((rows, ch)), bits((ch, 3))
+    out["dni_shape"] = np.array([heads, rows, ch])
+    for name, arr in (("a", a), ("b", b), ("a_log", a_log), ("dt_bias", dt_bias), ("w", w), ("x", x), ("window0", window.copy())):
+        out[f"dni_{name}"] = arr
+    beta, g, o = oracle.deltanet_inputs(R, a, b, a_log, dt_bias, w, x, window, heads, rows, ch)
+    out["dni_beta"], out["dni_g"], out["dni_o"], out["dni_window"] = beta, g, o, window
+
     path = Path(__file__).with_name("reference_x86_avx2.npz")
     np.savez_compressed(path, **out)
     print(path, path.stat().st_size, "bytes,", len(out), "arrays")

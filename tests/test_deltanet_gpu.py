@@ -85,3 +85,23 @@ def test_unfit_shapes_are_refused(cuda):
         ext.deltanet(t, t, t, t, t, t, t, 1, 1, 48, 1)
     with pytest.raises(ext.B200Error):
         ext.deltanet(t, t, t, t, t, t, t, 3, 4, 64, 1)
+
+
+@pytest.mark.parametrize("kh,vh,d,rows,seqs,dtype", [(2, 4, 128, 100, 1, 0), (1, 2, 64, 65, 2, 1), (4, 4, 128, 32, 1, 1), (2, 2, 128, 2100, 1, 0)])
+def test_chunked_runs_match_the_recurrence(cuda, port, kh, vh, d, rows, seqs, dtype):
+    """Runs of 32 positions or more take the 64-at-a-time kernel: ragged last chunks, several sequences, a run longer
+    than one 2,048-position segment, a starting state that is not zero — against the position-at-a-time checker."""
+    rng = np.random.default_rng(rows)
+    w = workloads.config5(rows=rows * seqs, heads=vh, d=d, dtype=dtype)
+    ch = (2 * kh + vh) * d
+    conved = np.ascontiguousarray(w.conved[:, : ch] if kh == vh else np.concatenate([w.conved[:, : kh * d], w.conved[:, vh * d: vh * d + kh * d], w.conved[:, 2 * vh * d:]], axis=1))
+    S0 = (rng.standard_normal((seqs, vh, d, d), dtype=np.float32) * 0.05).astype(np.float32)
+    S_want = S0.copy()
+    o_want = np.concatenate([port.deltanet(S_want[b], np.ascontiguousarray(conved[b * rows:(b + 1) * rows]), np.ascontiguousarray(w.z[b * rows:(b + 1) * rows]),
+                                           np.ascontiguousarray(w.beta[b * rows:(b + 1) * rows]), np.ascontiguousarray(w.g[b * rows:(b + 1) * rows]), w.w,
+                                           kh, vh, d, rows, 1, dtype) for b in range(seqs)])
+    S = dev(cuda, S0)
+    out = cuda.zeros((seqs * rows, vh * d), dtype=cuda.int16, device="cuda")
+    ext.deltanet(S, dev(cuda, conved), dev(cuda, w.z), dev(cuda, w.beta), dev(cuda, w.g), dev(cuda, w.w), out, kh, vh, d, rows, seqs, 1, dtype)
+    cuda.cuda.synchronize()
+    check(S.cpu().numpy(), S_want, host_bits(out), o_want, dtype, f"chunked {rows} rows")

@@ -113,3 +113,26 @@ def test_live_reference_agrees_with_golden(golden, reference):
     qh, kvh, d, L = (int(x) for x in golden["dec_a_shape"])
     o = reference.decode(golden["dec_a_q"], golden["dec_a_k"], golden["dec_a_v"], qh, kvh, d, L)
     assert np.array_equal(o, golden["dec_a_o"])
+
+
+def test_gathered_rows_sink_and_deltanet_inputs_match_reference_golden(golden, port):
+    qh, kvh, d, most = (int(x) for x in golden["gr_shape"])
+    p, o = oracle.gathered_rows(port, golden["gr_q"], golden["gr_k"], golden["gr_v"], golden["gr_lens"], qh, kvh, d)
+    for u, n in enumerate(golden["gr_lens"]):                      # a row's weights occupy heads x its own length
+        np.testing.assert_allclose(p[u, :qh * n], golden["gr_p"][u, :qh * n], rtol=2e-5, atol=1e-7)
+    assert np.abs(from_bits(o, 0) - from_bits(golden["gr_o"], 0)).max() <= 2.0 ** -10
+    np.testing.assert_allclose(oracle.softmax_sink(port, golden["sink_scores"], golden["sink_sink"]), golden["sink_p"], rtol=2e-5, atol=1e-8)
+    heads, rows, ch = (int(x) for x in golden["dni_shape"])
+    window = golden["dni_window0"].copy()
+    beta, g, out = oracle.deltanet_inputs(port, golden["dni_a"], golden["dni_b"], golden["dni_a_log"], golden["dni_dt_bias"], golden["dni_w"],
+                                          golden["dni_x"], window, heads, rows, ch)
+    for got, want in ((beta, golden["dni_beta"]), (g, golden["dni_g"]), (out, golden["dni_o"])):
+        assert np.abs(from_bits(got, 0) - from_bits(want, 0)).max() <= 2.0 ** -10 * max(1.0, np.abs(from_bits(want, 0)).max())
+    assert np.array_equal(window, golden["dni_window"])
+
+
+def test_row_residuals_golden_stand_for_the_causal_answer(golden, port):
+    qh, kvh, d, first, rows = (int(x) for x in golden["rr_shape"])
+    res = golden["rr_res"]
+    _, want = port.prefill(golden["rr_q"], golden["rr_k"], golden["rr_v"], qh, kvh, d, first, rows)
+    np.testing.assert_allclose(res[:, :, 2:] / res[:, :, 1:2], want, rtol=0, atol=1e-5)
