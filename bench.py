@@ -568,6 +568,17 @@ def run_case(args):
         o = torch.zeros((seqs, 1, heads * d), device="cuda", dtype=torch.bfloat16)
         fn = lambda: ext.deltanet(S, conved, z, beta, g, w, o, heads, heads, d, 1, seqs, 0, ext.BF16)
         work, unit = seqs * (2 * heads * d * d * 4 + 3 * heads * d * 2 + 2 * heads * d * 2 + 2 * heads * 2 + d * 2), "bytes"
+    elif name == "deltanet_prefill":
+        heads, d, T = 32, 128, 2048
+        S = torch.zeros((1, heads, d, d), device="cuda", dtype=torch.float32)
+        conved = torch.randn((T, 3 * heads * d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.1
+        z = torch.randn((T, heads * d), generator=gen, device="cuda", dtype=torch.bfloat16)
+        beta = torch.rand((T, heads), generator=gen, device="cuda").to(torch.bfloat16)
+        g = (-torch.rand((T, heads), generator=gen, device="cuda")).to(torch.bfloat16)
+        w = torch.ones(d, device="cuda", dtype=torch.bfloat16)
+        o = torch.zeros((T, heads * d), device="cuda", dtype=torch.bfloat16)
+        fn = lambda: ext.deltanet(S, conved, z, beta, g, w, o, heads, heads, d, T, 1, 0, ext.BF16)
+        work, unit = 7.0 * d * d * heads * T, "flop"
     elif name == "prefill_small":
         qh, kvh, d, T = 16, 2, 256, 2048
         q = torch.randn((T, qh, d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.5
@@ -590,7 +601,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the secondary configurations (faster; used under profilers)")
-    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, deltanet_64, prefill_small)")
+    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, deltanet_64, deltanet_prefill, prefill_small)")
     args = ap.parse_args()
     if args.case:
         run_case(args)
