@@ -5,6 +5,11 @@ TEST INFRASTRUCTURE.  The reference family is built with the reference's own rec
 includes silicon_families/x86_avx2/unit.cuh; g++ -O3 -mavx2 -mfma -mf16c, engine/scripts/build_silicon_families.sh:
 196-201 of that tree); no reference source is copied anywhere.  oracle/_ref/ is git-ignored and still travels to a GPU
 box with the rest of the working tree, where the reference tree itself does not exist.
+
+build_engine() compiles the reference's engine (evaluator, boot, C interface and Python module) the same way, from its
+one translation unit engine/src/manifest.cu with the command its own build script uses (scripts/build.sh:25-26 of that
+tree), into oracle/_ref/ as the Python module silvann_engine_cpu.  It is there for one job: to load THIS repository's
+family into the unmodified engine and run the nn verbs through it (tests/test_engine_dropin.py).
 """
 from __future__ import annotations
 
@@ -46,6 +51,30 @@ def build_reference(force: bool = False) -> Path | None:
     return REF
 
 
+def engine_path() -> Path:
+    import sysconfig
+    return REF_DIR / ("silvann_engine_cpu" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_engine(force: bool = False) -> Path | None:
+    """The reference engine as a Python module, or None when its sources are not here and no earlier build is present."""
+    import sysconfig
+    out = engine_path()
+    unit = REFERENCE_TREE / "engine" / "src" / "manifest.cu"
+    if not unit.exists():
+        return out if out.exists() else None
+    if out.exists() and not force:
+        return out
+    import pybind11
+    REF_DIR.mkdir(exist_ok=True)
+    cmd = ["g++", "-x", "c++", "-O2", "-std=c++17", "-pthread", "-fPIC", "-shared", "-ftls-model=initial-exec", "-w",
+           "-DSILVANN_MODULE_NAME=silvann_engine_cpu", "-I", str(REFERENCE_TREE / "engine" / "src"), "-I", pybind11.get_include(),
+           "-I", sysconfig.get_path("include"), str(unit), "-o", str(out)]
+    subprocess.run(cmd, check=True)
+    return out
+
+
 if __name__ == "__main__":
     print(build_port(force="-f" in sys.argv))
     print(build_reference(force="-f" in sys.argv))
+    print(build_engine(force="-f" in sys.argv))

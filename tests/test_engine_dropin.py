@@ -1,0 +1,162 @@
+"""The drop-in claim, tested with the reference's own engine: its evaluator and its nn verbs, unmodified, load a family
+by path (engine/src/pybind.cuh:399-406), boot on it and run `(nn__attention__decode ...)`, `(nn__attention__residual ...)`,
+`(nn__attention__merge ...)`, `(nn__attention__finish ...)`, `(nn__deltanet__step ...)` and `(nn__deltanet__conv_step ...)`
+(engine/src/packages/nn/cpu/opcodes/attention__abi.cuh:120-243, deltanet__abi.cuh:55-125).
+
+Without a GPU the family is the reference's own x86_avx2, and the answers must equal, bit for bit, the same doors called
+directly — that pins the driver.  With a GPU the family is this repository's library, and the answers must be within 2e-3
+of the reference family's; the library's own counters must show that the verb's two doors ran as ONE fused launch.
+"""
+import numpy as np
+import pytest
+
+import oracle
+import oracle.build
+from oracle import FP16, to_bits
+from tests import engine_driver
+from tests.util import assert_close16
+
+QH, KVH, D, N = 16, 4, 128, 8192
+
+
+def _inputs(seed):
+    rng = np.random.default_rng(seed)
+    q = to_bits(rng.standard_normal((QH, D)).astype(np.float32) * 0.5, FP16)
+    k = to_bits(rng.standard_normal((N, KVH, D)).astype(np.float32) * 0.5, FP16)
+    v = to_bits(rng.standard_normal((N, KVH, D)).astype(np.float32) * 0.5, FP16)
+    return q, k, v
+
+
+def _u16(b, shape):
+    return np.frombuffer(b, np.uint16).reshape(shape).copy()
+
+
+def _f32(b, shape):
+    return np.frombuffer(b, np.float32).reshape(shape).copy()
+
+
+def _attention_forms(s, reference, exact):
+    q, k, v = _inputs(41)
+    qb, kb, vb = s.buffer(q.nbytes, q.tobytes()), s.buffer(k.nbytes, k.tobytes()), s.buffer(v.nbytes, v.tobytes())
+    sb = s.buffer(QH * N * 4)
+    ob = s.buffer(QH * D * 2)
+    kind, value = s.run("nn__attention__decode", qb, kb, vb, sb, ob, QH, KVH, D, 0, N)
+    assert kind == s.OBJ, "the verb answers its output buffer"
+    got = _u16(ob.read(), (QH, D))
+    want = reference.decode(q, k, v, QH, KVH, D, N)
+    if exact:
+        assert np.array_equal(got, want)
+    else:
+        assert_close16(got, oracle.from_bits(want, FP16), FP16, "decode through the engine")
+
+    # a range that does not start at zero: the verb offsets K and V by `from` rows
+    lo, hi = 1000, 5000
+    s.run("nn__attention__decode", qb, kb, vb, sb, ob, QH, KVH, D, lo, hi)
+    got = _u16(ob.read(), (QH, D))
+    want = reference.decode(q, np.ascontiguousarray(k[lo:hi]), np.ascontiguousarray(v[lo:hi]), QH, KVH, D, hi - lo)
+    if exact:
+        assert np.array_equal(got, want)
+    else:
+        assert_close16(got, oracle.from_bits(want, FP16), FP16, "decode of a range through the engine")
+
+    # two ranges as residuals, merged and finished: the tiered form (ai_qwen_3 mixer__abi.cuh:383-412)
+    ra, rb = s.buffer(QH * (D + 2) * 4), s.buffer(QH * (D + 2) * 4)
+    cut = 3000
+    s.run("nn__attention__residual", qb, kb, vb, sb, ra, QH, KVH, D, 0, cut)
+    s.run("nn__attention__residual", qb, kb, vb, sb, rb, QH, KVH, D, cut, N)
+    s.run("nn__attention__merge", ra, rb, ra, QH, D)
+    s.run("nn__attention__finish", ra, ob, QH, D)
+    got = _u16(ob.read(), (QH, D))
+    wa = reference.residual(q, np.ascontiguousarray(k[:cut]), np.ascontiguousarray(v[:cut]), QH, KVH, D, cut)
+    wb = reference.residual(q, np.ascontiguousarray(k[cut:]), np.ascontiguousarray(v[cut:]), QH, KVH, D, N - cut)
+    want = reference.finish(reference.merge(wa, wb, QH, D), QH, D)
+    if exact:
+        assert np.array_equal(got, want)
+    else:
+        assert_close16(got, oracle.from_bits(want, FP16), FP16, "residual, merge, finish through the engine")
+    s.release_buffers()
+
+
+def _deltanet_forms(s, reference, exact):
+    kh, vh, d = 4, 8, 128
+    rng = np.random.default_rng(43)
+    S0 = (rng.standard_normal((vh, d, d)) * 0.1).astype(np.float32)
+    conved = to_bits(rng.standard_normal((2 * kh + vh) * d).astype(np.float32), FP16)
+    z = to_bits(rng.standard_normal(vh * d).astype(np.float32), FP16)
+    beta = to_bits(rng.uniform(0.1, 0.9, vh).astype(np.float32), FP16)
+    g = to_bits(-rng.uniform(0.01, 0.5, vh).astype(np.float32), FP16)
+    w = to_bits((1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32), FP16)
+    for gate in (0, 1):
+        Sb = s.buffer(S0.nbytes, S0.tobytes())
+        bufs = [s.buffer(a.nbytes, a.tobytes()) for a in (conved, z, beta, g, w)]
+        out = s.buffer(vh * d * 2)
+        args = [Sb] + bufs + [out, kh, vh, d] + ([gate] if gate else [])
+        s.run("nn__deltanet__step", *args)
+        got_o, got_S = _u16(out.read(), (1, vh * d)), _f32(Sb.read(), S0.shape)
+        want_S = S0.copy()
+        want_o = reference.deltanet(want_S, conved, z, beta, g, w, kh, vh, d, 1, gate)
+        if exact:
+            assert np.array_equal(got_o, want_o) and np.array_equal(got_S, want_S)
+        else:
+            assert_close16(got_o, oracle.from_bits(want_o, FP16), FP16, f"deltanet step, gate {gate}", tol=4e-3)
+            scale = np.abs(want_S).max()
+            assert np.abs(got_S - want_S).max() <= 1e-3 * scale, "deltanet state"
+        s.release_buffers()
+
+    # the convolution step ahead of it: (nn__deltanet__conv_step w state x out channels), four taps over a window of three
+    ch = 2048
+    wc = to_bits((rng.standard_normal(ch * 4) * 0.3).astype(np.float32), FP16)
+    st = to_bits(rng.standard_normal(ch * 3).astype(np.float32), FP16)
+    x = to_bits(rng.standard_normal(ch).astype(np.float32), FP16)
+    wb, sb, xb, ob = s.buffer(wc.nbytes, wc.tobytes()), s.buffer(st.nbytes, st.tobytes()), s.buffer(x.nbytes, x.tobytes()), s.buffer(ch * 2)
+    s.run("nn__deltanet__conv_step", wb, sb, xb, ob, ch)
+    got_o, got_s = _u16(ob.read(), (ch,)), _u16(sb.read(), (ch * 3,))
+    want_o, want_s = np.empty(ch, np.uint16), st.copy()
+    reference.nn.deltanet_conv_step(oracle._p(want_o), oracle._p(want_s), oracle._p(wc), oracle._p(x), ch, oracle._p(reference.over))
+    reference.wait()
+    assert np.array_equal(got_s, want_s), "the window holds inputs, moved and not computed"
+    if exact:
+        assert np.array_equal(got_o, want_o)
+    else:
+        assert_close16(got_o, oracle.from_bits(want_o, FP16), FP16, "deltanet conv step")
+    s.release_buffers()
+
+
+@pytest.fixture(scope="module")
+def cpu_session(reference):
+    if reference is None or engine_driver.engine_module() is None:
+        pytest.skip("oracle/_ref holds no reference engine and family (built where the reference tree is mounted)")
+    s = engine_driver.Session(oracle.build.REF, "x86_avx2")
+    yield s
+    s.close()
+
+
+def test_engine_runs_reference_family(cpu_session, reference):
+    _attention_forms(cpu_session, reference, exact=True)
+    _deltanet_forms(cpu_session, reference, exact=True)
+
+
+@pytest.fixture(scope="module")
+def gpu_session(cuda):
+    import silvann_b200
+    if engine_driver.engine_module() is None:
+        pytest.fail("oracle/_ref holds no reference engine: build it where the reference tree is mounted")
+    s = engine_driver.Session(silvann_b200.library_path(), "nvidia_b200")
+    yield s
+    s.close()
+
+
+@pytest.mark.gpu
+def test_engine_runs_this_family(gpu_session, reference):
+    from silvann_b200 import ext
+    assert reference is not None
+    before = ext.counters()
+    _attention_forms(gpu_session, reference, exact=False)
+    mid = ext.counters()
+    assert mid["fused_decode"] - before["fused_decode"] == 2, "each decode verb is one fused launch"
+    assert mid["fused_residual"] - before["fused_residual"] == 2, "each residual verb is one fused launch"
+    _deltanet_forms(gpu_session, reference, exact=False)
+    after = ext.counters()
+    assert after["deltanet"] - mid["deltanet"] == 2
+    assert after["refused"] == before["refused"]
+    assert ext.device_status() == 0
