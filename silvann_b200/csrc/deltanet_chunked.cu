@@ -40,106 +40,225 @@ struct ChunkParams {
     uint32_t chunks;                     /* chunks in this segment */
 };
 
-/* ---- kernel 1: everything about a chunk that does not depend on the state ------------------------------------ */
+/* 16-byte asynchronous copies global -> shared; `bytes` of 0 writes zeros and reads nothing */
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int DT> __device__ __forceinline__ void unpack4(uint2 u, float* f) {
+    const float2 a = Elem<DT>::unpack2(u.x), b = Elem<DT>::unpack2(u.y);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+
+/* ---- kernel 1: everything about a chunk that does not depend on the state ------------------------------------
+ * A block a (sequence, chunk, KEY head), 256 threads.  The two Gram products K K^T and Q K^T belong to the key head and
+ * are made once, register-tiled (a thread owns rows ti, ti+16, ti+32, ti+48 against si, si+16, ..., so that the 16
+ * lanes that differ in si read 16 consecutive rows of shared memory); then, two value heads of the key head at a time,
+ * L is built transposed, (I + L)^-1 comes out of a right-looking substitution that lives in registers (a thread a
+ * column, 64 running rows, the loop fully unrolled so that L is read four rows at a load), and A, M and the row vectors
+ * go to scratch. */
 template <int D, int DT>
-__global__ void __launch_bounds__(128) deltanet_prep_kernel(const ChunkParams P) {
+__global__ void __launch_bounds__(256, 2) deltanet_prep_kernel(const ChunkParams P) {
     using E = Elem<DT>;
-    constexpr int LD = D + 4;
-    extern __shared__ float sm[];
+    constexpr int LD = D + 4, GL = CH + 1, TL = CH + 4, CPR = D / 8;
+    extern __shared__ __align__(16) float sm[];
     float* kf = sm;                      /* [64][LD] raw k */
     float* qf = kf + CH * LD;            /* [64][LD] raw q */
-    float* Lm = qf + CH * LD;            /* [64][65] L, then X */
-    float* Xm = Lm + CH * 65;            /* [64][65] */
-    float* vk = Xm + CH * 65;            /* inv_k[64], inv_q[64], G[64], beta[64] */
-    float* vq = vk + CH; float* vG = vq + CH; float* vb = vG + CH;
-    const int tid = threadIdx.x;
-    const uint32_t c = blockIdx.x % P.chunks, h = (blockIdx.x / P.chunks) % P.v_heads, b = blockIdx.x / (P.chunks * P.v_heads);
-    const uint32_t rep = P.v_heads / P.k_heads, kh = h / rep;
+    float* KK = qf + CH * LD;            /* [64][65] k_t . k_s, s <= t */
+    float* QK = KK + CH * GL;            /* [64][65] q_t . k_s, s <= t */
+    float* ik = QK + CH * GL;            /* 1 / |k_t| */
+    float* iq = ik + CH;                 /* 1 / |q_t| / sqrt(d) */
+    float* vb = iq + CH;                 /* [2][64] beta */
+    float* vG = vb + 2 * CH;             /* [2][64] running sums of g */
+    float* LT = sm;                      /* [2][64][TL]: L transposed, over k and q once the Gram products are done */
+    static_assert(2 * CH * TL <= 2 * CH * LD, "L transposed fits where k and q were");
+    const int tid = threadIdx.x, lane = tid & 31;
+    const uint32_t c = blockIdx.x % P.chunks, kh = (blockIdx.x / P.chunks) % P.k_heads, b = blockIdx.x / (P.chunks * P.k_heads);
+    const uint32_t rep = P.v_heads / P.k_heads;
     const uint64_t ch = (uint64_t)(2 * P.k_heads + P.v_heads) * D;
     const uint64_t t0 = P.row0 + (uint64_t)c * CH;
     const int n = (int)((P.row0 + P.seg_rows - t0) < CH ? (P.row0 + P.seg_rows - t0) : CH);
     const uint16_t* cv = P.conved + ((uint64_t)b * P.rows + t0) * ch;
 
-    for (int i = tid; i < CH * D; i += 128) {
-        const int t = i / D, e = i % D;
-        kf[t * LD + e] = t < n ? E::to_float(cv[(uint64_t)t * ch + (P.k_heads + kh) * D + e]) : 0.f;
-        qf[t * LD + e] = t < n ? E::to_float(cv[(uint64_t)t * ch + kh * D + e]) : 0.f;
+    /* k and q as fp32, with each row's sum of squares folded over the lanes that share the row */
+    for (int i = tid; i < 2 * CH * CPR; i += 256) {
+        const int which = i / (CH * CPR), r = (i / CPR) % CH, p = i % CPR;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (r < n) raw = *reinterpret_cast<const uint4*>(cv + (uint64_t)r * ch + (uint64_t)(which ? kh : P.k_heads + kh) * D + p * 8);
+        float f[8];
+        unpack4<DT>(make_uint2(raw.x, raw.y), f); unpack4<DT>(make_uint2(raw.z, raw.w), f + 4);
+        float* dst = (which ? qf : kf) + r * LD + p * 8;
+        *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(f[4], f[5], f[6], f[7]);
+        float ssq = 0.f;
+#pragma unroll
+        for (int x = 0; x < 8; ++x) ssq += f[x] * f[x];
+#pragma unroll
+        for (int x = 1; x < CPR; x <<= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, x);
+        if (p == 0) {
+            if (which) iq[r] = 1.0f / sqrtf(ssq + 1e-6f) / sqrtf((float)D);
+            else       ik[r] = 1.0f / sqrtf(ssq + 1e-6f);
+        }
     }
     __syncthreads();
-    if (tid < CH) {
-        float kk = 0.f, qq = 0.f;
-        for (int e = 0; e < D; ++e) { kk += kf[tid * LD + e] * kf[tid * LD + e]; qq += qf[tid * LD + e] * qf[tid * LD + e]; }
-        vk[tid] = 1.0f / sqrtf(kk + 1e-6f);
-        vq[tid] = 1.0f / sqrtf(qq + 1e-6f) / sqrtf((float)D);
-        const uint64_t hh = ((uint64_t)b * P.rows + t0 + tid) * P.v_heads + h;
-        vb[tid] = tid < n ? E::to_float(P.beta[hh]) : 0.f;
-        vG[tid] = tid < n ? E::to_float(P.g[hh]) : 0.f;
-    }
-    __syncthreads();
-    if (tid == 0) { float run = 0.f; for (int t = 0; t < CH; ++t) { run += vG[t]; vG[t] = run; } }   /* G_t, flat past the chunk's end */
-    __syncthreads();
-    float* out = P.prep + (((uint64_t)b * P.chunks + c) * P.v_heads + h) * PREP_FLOATS;
-    /* L (strictly lower) into shared memory, M (lower with its diagonal) straight to scratch */
-    for (int i = tid; i < CH * CH; i += 128) {
-        const int t = i / CH, s = i % CH;
-        float kk = 0.f, qk = 0.f;
-        if (s <= t && t < n) {
-            const float* ks = kf + s * LD; const float* kt = kf + t * LD; const float* qt = qf + t * LD;
-#pragma unroll 4
-            for (int e = 0; e < D; e += 4) {
-                const float4 a = *reinterpret_cast<const float4*>(ks + e), k4 = *reinterpret_cast<const float4*>(kt + e), q4 = *reinterpret_cast<const float4*>(qt + e);
-                kk += a.x * k4.x + a.y * k4.y + a.z * k4.z + a.w * k4.w;
-                qk += a.x * q4.x + a.y * q4.y + a.z * q4.z + a.w * q4.w;
+    {
+        const int ti = tid >> 4, si = tid & 15;
+        float kk[4][4] = {}, qk[4][4] = {};
+#pragma unroll 2
+        for (int e = 0; e < D; e += 4) {
+            float4 kt[4], qt[4], ks[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                kt[a] = *reinterpret_cast<const float4*>(kf + (ti + 16 * a) * LD + e);
+                qt[a] = *reinterpret_cast<const float4*>(qf + (ti + 16 * a) * LD + e);
+                ks[a] = *reinterpret_cast<const float4*>(kf + (si + 16 * a) * LD + e);
             }
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int bb = 0; bb <= a; ++bb) {       /* rows ti+16a against si+16bb: below the diagonal when a > bb */
+                    kk[a][bb] += kt[a].x * ks[bb].x + kt[a].y * ks[bb].y + kt[a].z * ks[bb].z + kt[a].w * ks[bb].w;
+                    qk[a][bb] += qt[a].x * ks[bb].x + qt[a].y * ks[bb].y + qt[a].z * ks[bb].z + qt[a].w * ks[bb].w;
+                }
         }
-        const float dec = (s <= t && t < n) ? expf(vG[t] - vG[s]) : 0.f;
-        Lm[t * 65 + s] = s < t ? vb[t] * dec * vk[t] * vk[s] * kk : 0.f;
-        out[PREP_M + i] = dec * vq[t] * vk[s] * qk;
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int bb = 0; bb <= a; ++bb) {
+                KK[(ti + 16 * a) * GL + si + 16 * bb] = kk[a][bb];
+                QK[(ti + 16 * a) * GL + si + 16 * bb] = qk[a][bb];
+            }
     }
-    __syncthreads();
-    /* X = (I + L)^-1 by forward substitution, a thread a column: X[t][c] = [t == c] - sum_{s < t} L[t][s] X[s][c] */
-    if (tid < CH) {
-        const int col = tid;
-        for (int t = 0; t < CH; ++t) {
-            float x = (t == col) ? 1.f : 0.f;
-            for (int s = col; s < t; ++s) x -= Lm[t * 65 + s] * Xm[s * 65 + col];
-            Xm[t * 65 + col] = (t >= col) ? x : 0.f;
+
+    for (uint32_t p0 = 0; p0 < rep; p0 += 2) {
+        const int nh = (int)((rep - p0) < 2u ? (rep - p0) : 2u);
+        const int hh = (tid >> 6) & 1, t = tid & 63;
+        const uint32_t h = kh * rep + p0 + hh;
+        __syncthreads();                  /* the Gram products are written; the last pass's readers are done */
+        if (tid < 128) {
+            float gsum = 0.f, be = 0.f;
+            if (hh < nh && t < n) {
+                const uint64_t at = ((uint64_t)b * P.rows + t0 + t) * P.v_heads + h;
+                be = E::to_float(P.beta[at]); gsum = E::to_float(P.g[at]);
+            }
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const float y = __shfl_up_sync(0xffffffffu, gsum, o); if (lane >= o) gsum += y; }
+            vb[tid] = be; vG[tid] = gsum;
         }
-    }
-    __syncthreads();
-    for (int i = tid; i < CH * CH; i += 128) {
-        const int t = i / CH, s = i % CH;
-        out[PREP_A + i] = (t < n && s < n) ? Xm[t * 65 + s] * vb[s] : 0.f;        /* A = X diag(beta) */
-    }
-    if (tid < CH) {
-        const float Gn = vG[CH - 1];
-        out[PREP_VA + tid] = expf(vG[tid]) * vk[tid];                 /* scales Kn S_0 rows: e^G_t / |k_t| */
-        out[PREP_VB + tid] = expf(vG[tid]) * vq[tid];                 /* scales Q S_0 rows */
-        out[PREP_VC + tid] = tid < n ? expf(Gn - vG[tid]) * vk[tid] : 0.f;   /* scales D rows into the state */
-        if (tid == 0) out[PREP_GC] = expf(Gn);
+        __syncthreads();
+        if (tid < 128 && (tid & 32)) vG[tid] += vG[(tid & ~63) + 31];      /* G_t, flat past the chunk's end */
+        __syncthreads();
+        /* L transposed into shared memory (t runs fastest), M straight to scratch (s runs fastest) */
+        for (int i = tid; i < nh * CH * CH; i += 256) {
+            const int hq = i / (CH * CH), s = (i / CH) % CH, tt = i % CH;
+            float l = 0.f;
+            if (s < tt && tt < n) l = vb[hq * CH + tt] * expf(vG[hq * CH + tt] - vG[hq * CH + s]) * ik[tt] * ik[s] * KK[tt * GL + s];
+            LT[(hq * CH + s) * TL + tt] = l;
+        }
+        for (int i = tid; i < nh * CH * CH; i += 256) {
+            const int hq = i / (CH * CH), tt = (i / CH) % CH, s = i % CH;
+            float m = 0.f;
+            if (s <= tt && tt < n) m = expf(vG[hq * CH + tt] - vG[hq * CH + s]) * iq[tt] * ik[s] * QK[tt * GL + s];
+            P.prep[(((uint64_t)b * P.chunks + c) * P.v_heads + kh * rep + p0 + hq) * PREP_FLOATS + PREP_M + tt * CH + s] = m;
+        }
+        __syncthreads();
+        float* out = P.prep + (((uint64_t)b * P.chunks + c) * P.v_heads + h) * PREP_FLOATS;
+        if (tid < 128) {
+            if (hh < nh) {
+                /* X = (I + L)^-1, column t of it: x_s is final once every s' < s has been taken out of the rows below */
+                float x[CH];
+#pragma unroll
+                for (int r = 0; r < CH; ++r) x[r] = (r == t) ? 1.f : 0.f;
+#pragma unroll
+                for (int s = 0; s < CH - 1; ++s) {
+                    const float xs = x[s];
+                    const float* row = LT + (hh * CH + s) * TL;
+#pragma unroll
+                    for (int tg = ((s + 1) / 4) * 4; tg < CH; tg += 4) {
+                        const float4 l = *reinterpret_cast<const float4*>(row + tg);
+                        if (tg + 0 > s) x[tg + 0] -= l.x * xs;
+                        if (tg + 1 > s) x[tg + 1] -= l.y * xs;
+                        if (tg + 2 > s) x[tg + 2] -= l.z * xs;
+                        if (tg + 3 > s) x[tg + 3] -= l.w * xs;
+                    }
+                }
+                const float be = vb[hh * CH + t];
+#pragma unroll
+                for (int r = 0; r < CH; ++r) out[PREP_A + r * CH + t] = x[r] * be;       /* A = X diag(beta) */
+            }
+        } else if (hh < nh) {
+            const float G = vG[hh * CH + t], Gn = vG[hh * CH + CH - 1];
+            out[PREP_VA + t] = expf(G) * ik[t];                        /* scales Kn S_0 rows: e^G_t / |k_t| */
+            out[PREP_VB + t] = expf(G) * iq[t];                        /* scales Q S_0 rows */
+            out[PREP_VC + t] = t < n ? expf(Gn - G) * ik[t] : 0.f;     /* scales D rows into the state */
+            if (t == 0) out[PREP_GC] = expf(Gn);
+        }
     }
 }
 
-/* ---- kernel 2: the serial walk, a block a (sequence, value head, 32 columns) ------------------------------------- */
+/* ---- kernel 2: the serial walk, a block a (sequence, value head, 32 columns) -------------------------------------
+ * What a chunk needs — its k, q and v rows as they lie in the cache (16 bits), A, M and the row vectors from kernel 1 —
+ * is fetched with 16-byte asynchronous copies into one of two stages while the chunk before it is being computed, so the
+ * serial path waits on arithmetic and not on memory.  k and q stay 16-bit in shared memory and widen as they are read. */
+template <int D> struct ChunkSmem {
+    static constexpr int LDH = D + 8;                      /* halves a k or q row: 16-byte rows, 8 banks apart for row pairs */
+    static constexpr int TL = CH + 4;                      /* floats an A or M row */
+    static constexpr size_t STATE = (size_t)D * CNC * 4, RD = (size_t)CH * CNC * 4;
+    static constexpr size_t KQ = (size_t)CH * LDH * 2, V = (size_t)CH * CNC * 2, AM = (size_t)CH * TL * 4, VEC = 4 * CH * 4;
+    static constexpr size_t STAGE = 2 * KQ + V + 2 * AM + VEC;
+    static constexpr size_t TOTAL = STATE + 2 * RD + 2 * STAGE;
+};
+
 template <int D, int DT>
 __global__ void __launch_bounds__(256, 1) deltanet_chunk_kernel(const ChunkParams P) {
     using E = Elem<DT>;
-    constexpr int LD = D + 4, CB = D / CNC;
-    extern __shared__ float sm[];
-    float* Ss = sm;                      /* [D][32] the state block */
-    float* kf = Ss + D * CNC;            /* [64][LD] raw k */
-    float* qf = kf + CH * LD;            /* [64][LD] raw q */
-    float* Am = qf + CH * LD;            /* [64][65] */
-    float* Mm = Am + CH * 65;            /* [64][65] */
-    float* Rm = Mm + CH * 65;            /* [64][32]: V - scaled Kn S_0, then D scaled for the state update */
-    float* Dm = Rm + CH * CNC;           /* [64][32]: D */
-    float* va = Dm + CH * CNC; float* vb = va + CH; float* vc = vb + CH; float* gc = vc + CH;
+    using L = ChunkSmem<D>;
+    constexpr int LDH = L::LDH, TL = L::TL, CB = D / CNC, CPR = D / 8;
+    extern __shared__ __align__(16) unsigned char smb[];
+    float* Ss = reinterpret_cast<float*>(smb);                       /* [D][32] the state block */
+    float* Rm = reinterpret_cast<float*>(smb + L::STATE);            /* [64][32]: V - scaled Kn S_0 */
+    float* Dm = Rm + CH * CNC;                                       /* [64][32]: D, then D scaled for the state update */
+    unsigned char* stage0 = smb + L::STATE + 2 * L::RD;
     const int tid = threadIdx.x;
     const uint32_t cb = blockIdx.x % CB, h = (blockIdx.x / CB) % P.v_heads, b = blockIdx.x / (CB * P.v_heads);
     const uint32_t rep = P.v_heads / P.k_heads, kh = h / rep;
     const uint64_t ch = (uint64_t)(2 * P.k_heads + P.v_heads) * D, vd = (uint64_t)P.v_heads * D;
     const int j0 = cb * CNC;
     float* Sg = P.S + ((uint64_t)b * P.v_heads + h) * D * D;
+
+    auto fetch = [&](uint32_t c) {
+        unsigned char* st = stage0 + (size_t)(c & 1u) * L::STAGE;
+        uint16_t* kr = reinterpret_cast<uint16_t*>(st);
+        uint16_t* qr = reinterpret_cast<uint16_t*>(st + L::KQ);
+        uint16_t* vr = reinterpret_cast<uint16_t*>(st + 2 * L::KQ);
+        float* Am = reinterpret_cast<float*>(st + 2 * L::KQ + L::V);
+        float* Mm = Am + CH * TL;
+        float* vec = Mm + CH * TL;
+        const uint64_t t0 = P.row0 + (uint64_t)c * CH;
+        const int n = (int)((P.row0 + P.seg_rows - t0) < CH ? (P.row0 + P.seg_rows - t0) : CH);
+        const uint16_t* cv = P.conved + ((uint64_t)b * P.rows + t0) * ch;
+        const float* pr = P.prep + (((uint64_t)b * P.chunks + c) * P.v_heads + h) * PREP_FLOATS;
+        for (int i = tid; i < 2 * CH * CPR; i += 256) {
+            const int which = i / (CH * CPR), r = (i / CPR) % CH, p = i % CPR;
+            const int rr = r < n ? r : 0;
+            cp_async16((which ? qr : kr) + r * LDH + p * 8, cv + (uint64_t)rr * ch + (uint64_t)(which ? kh : P.k_heads + kh) * D + p * 8, r < n ? 16u : 0u);
+        }
+        for (int i = tid; i < CH * (CNC / 8); i += 256) {
+            const int r = i / (CNC / 8), p = i % (CNC / 8);
+            const int rr = r < n ? r : 0;
+            cp_async16(vr + r * CNC + p * 8, cv + (uint64_t)rr * ch + (uint64_t)2 * P.k_heads * D + (uint64_t)h * D + j0 + p * 8, r < n ? 16u : 0u);
+        }
+        for (int i = tid; i < 2 * CH * (CH / 4); i += 256) {
+            const int which = i / (CH * (CH / 4)), r = (i / (CH / 4)) % CH, p = i % (CH / 4);
+            cp_async16((which ? Mm : Am) + r * TL + p * 4, pr + (which ? PREP_M : PREP_A) + r * CH + p * 4, 16u);
+        }
+        if (tid < CH) cp_async16(vec + tid * 4, pr + PREP_VA + tid * 4, 16u);
+    };
+
+    fetch(0);
+    cp_async_commit();
     for (int i = tid; i < D * CNC; i += 256) Ss[i] = Sg[(uint64_t)(i / CNC) * D + j0 + i % CNC];
     bool hit = false;
     const int ty = tid >> 3, tx = tid & 7;           /* 32 x 8: two rows and four columns of a 64 x 32 product a thread */
@@ -147,33 +266,29 @@ __global__ void __launch_bounds__(256, 1) deltanet_chunk_kernel(const ChunkParam
     for (uint32_t c = 0; c < P.chunks; ++c) {
         const uint64_t t0 = P.row0 + (uint64_t)c * CH;
         const int n = (int)((P.row0 + P.seg_rows - t0) < CH ? (P.row0 + P.seg_rows - t0) : CH);
-        const uint16_t* cv = P.conved + ((uint64_t)b * P.rows + t0) * ch;
-        const float* pr = P.prep + (((uint64_t)b * P.chunks + c) * P.v_heads + h) * PREP_FLOATS;
-        __syncthreads();                              /* the previous chunk's readers are done with the buffers */
-        for (int i = tid; i < CH * D; i += 256) {
-            const int t = i / D, e = i % D;
-            kf[t * LD + e] = t < n ? E::to_float(cv[(uint64_t)t * ch + (P.k_heads + kh) * D + e]) : 0.f;
-            qf[t * LD + e] = t < n ? E::to_float(cv[(uint64_t)t * ch + kh * D + e]) : 0.f;
-        }
-        for (int i = tid; i < CH * CH; i += 256) { Am[(i / CH) * 65 + i % CH] = pr[PREP_A + i]; Mm[(i / CH) * 65 + i % CH] = pr[PREP_M + i]; }
-        if (tid < CH) { va[tid] = pr[PREP_VA + tid]; vb[tid] = pr[PREP_VB + tid]; vc[tid] = pr[PREP_VC + tid]; if (tid == 0) gc[0] = pr[PREP_GC]; }
-        for (int i = tid; i < CH * CNC; i += 256) {
-            const int t = i / CNC, jj = i % CNC;
-            Rm[i] = t < n ? E::to_float(cv[(uint64_t)t * ch + (uint64_t)2 * P.k_heads * D + (uint64_t)h * D + j0 + jj]) : 0.f;
-        }
+        unsigned char* st = stage0 + (size_t)(c & 1u) * L::STAGE;
+        const uint16_t* kr = reinterpret_cast<const uint16_t*>(st);
+        const uint16_t* qr = reinterpret_cast<const uint16_t*>(st + L::KQ);
+        const uint16_t* vr = reinterpret_cast<const uint16_t*>(st + 2 * L::KQ);
+        const float* Am = reinterpret_cast<const float*>(st + 2 * L::KQ + L::V);
+        const float* Mm = Am + CH * TL;
+        const float* va = Mm + CH * TL; const float* vb = va + CH; const float* vc = vb + CH; const float* gc = vc + CH;
+        /* the other stage's last readers passed the barrier ahead of the state write of the chunk before: refill it */
+        if (c + 1 < P.chunks) fetch(c + 1);
+        cp_async_commit();
+        cp_async_wait<1>();
         __syncthreads();
 
         /* (1) K S_0 and Q S_0 together: rows 2ty, 2ty+1; columns 4tx..4tx+3 */
         float ks[2][4] = {}, qs[2][4] = {};
         {
-            const float* k0 = kf + (2 * ty) * LD; const float* k1 = k0 + LD;
-            const float* q0 = qf + (2 * ty) * LD; const float* q1 = q0 + LD;
+            const uint16_t* k0 = kr + (2 * ty) * LDH; const uint16_t* k1 = k0 + LDH;
+            const uint16_t* q0 = qr + (2 * ty) * LDH; const uint16_t* q1 = q0 + LDH;
 #pragma unroll 2
             for (int i = 0; i < D; i += 4) {
-                const float4 a0 = *reinterpret_cast<const float4*>(k0 + i), a1 = *reinterpret_cast<const float4*>(k1 + i);
-                const float4 b0 = *reinterpret_cast<const float4*>(q0 + i), b1 = *reinterpret_cast<const float4*>(q1 + i);
-                const float ka0[4] = {a0.x, a0.y, a0.z, a0.w}, ka1[4] = {a1.x, a1.y, a1.z, a1.w};
-                const float qa0[4] = {b0.x, b0.y, b0.z, b0.w}, qa1[4] = {b1.x, b1.y, b1.z, b1.w};
+                float ka0[4], ka1[4], qa0[4], qa1[4];
+                unpack4<DT>(*reinterpret_cast<const uint2*>(k0 + i), ka0); unpack4<DT>(*reinterpret_cast<const uint2*>(k1 + i), ka1);
+                unpack4<DT>(*reinterpret_cast<const uint2*>(q0 + i), qa0); unpack4<DT>(*reinterpret_cast<const uint2*>(q1 + i), qa1);
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const float4 s4 = *reinterpret_cast<const float4*>(Ss + (i + u) * CNC + 4 * tx);
@@ -188,22 +303,25 @@ __global__ void __launch_bounds__(256, 1) deltanet_chunk_kernel(const ChunkParam
         }
         /* R = V - diag(e^G / |k|) K S_0 */
 #pragma unroll
-        for (int rr = 0; rr < 2; ++rr)
-#pragma unroll
-            for (int x = 0; x < 4; ++x) Rm[(2 * ty + rr) * CNC + 4 * tx + x] -= va[2 * ty + rr] * ks[rr][x];
+        for (int rr = 0; rr < 2; ++rr) {
+            float v4[4];
+            unpack4<DT>(*reinterpret_cast<const uint2*>(vr + (2 * ty + rr) * CNC + 4 * tx), v4);
+            const float a = va[2 * ty + rr];
+            *reinterpret_cast<float4*>(Rm + (2 * ty + rr) * CNC + 4 * tx) =
+                make_float4(v4[0] - a * ks[rr][0], v4[1] - a * ks[rr][1], v4[2] - a * ks[rr][2], v4[3] - a * ks[rr][3]);
+        }
         __syncthreads();
         /* (2) D = A R, A lower triangular */
         float dd[2][4] = {};
         for (int s = 0; s <= 2 * ty + 1; ++s) {
             const float4 r4 = *reinterpret_cast<const float4*>(Rm + s * CNC + 4 * tx);
-            const float a0 = Am[(2 * ty) * 65 + s], a1 = Am[(2 * ty + 1) * 65 + s];
+            const float a0 = Am[(2 * ty) * TL + s], a1 = Am[(2 * ty + 1) * TL + s];
             dd[0][0] += a0 * r4.x; dd[0][1] += a0 * r4.y; dd[0][2] += a0 * r4.z; dd[0][3] += a0 * r4.w;
             dd[1][0] += a1 * r4.x; dd[1][1] += a1 * r4.y; dd[1][2] += a1 * r4.z; dd[1][3] += a1 * r4.w;
         }
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr)
-#pragma unroll
-            for (int x = 0; x < 4; ++x) Dm[(2 * ty + rr) * CNC + 4 * tx + x] = dd[rr][x];
+            *reinterpret_cast<float4*>(Dm + (2 * ty + rr) * CNC + 4 * tx) = make_float4(dd[rr][0], dd[rr][1], dd[rr][2], dd[rr][3]);
         __syncthreads();
         /* (3) O = diag(e^G / |q| / sqrt d) Q S_0 + M D, rounded, with the block's sum of squares for the norm */
         float oo[2][4];
@@ -213,7 +331,7 @@ __global__ void __launch_bounds__(256, 1) deltanet_chunk_kernel(const ChunkParam
             for (int x = 0; x < 4; ++x) oo[rr][x] = vb[2 * ty + rr] * qs[rr][x];
         for (int s = 0; s <= 2 * ty + 1; ++s) {
             const float4 d4 = *reinterpret_cast<const float4*>(Dm + s * CNC + 4 * tx);
-            const float m0 = Mm[(2 * ty) * 65 + s], m1 = Mm[(2 * ty + 1) * 65 + s];
+            const float m0 = Mm[(2 * ty) * TL + s], m1 = Mm[(2 * ty + 1) * TL + s];
             oo[0][0] += m0 * d4.x; oo[0][1] += m0 * d4.y; oo[0][2] += m0 * d4.z; oo[0][3] += m0 * d4.w;
             oo[1][0] += m1 * d4.x; oo[1][1] += m1 * d4.y; oo[1][2] += m1 * d4.z; oo[1][3] += m1 * d4.w;
         }
@@ -235,7 +353,7 @@ __global__ void __launch_bounds__(256, 1) deltanet_chunk_kernel(const ChunkParam
         __syncthreads();
         for (int i = tid; i < CH * CNC; i += 256) Dm[i] *= vc[i / CNC];
         __syncthreads();
-        /* (4) S = e^(G_C) S_0 + K^T D': rows 4(tid/8)..+3 of the state for D = 128 (D/32 rows a thread), columns 4tx..+3 */
+        /* (4) S = e^(G_C) S_0 + K^T D': D/32 rows of the state a thread, columns 4tx..+3 */
         {
             constexpr int RP = D / 32;                 /* state rows a thread */
             const int i0 = (tid >> 3) * RP;
@@ -249,17 +367,20 @@ __global__ void __launch_bounds__(256, 1) deltanet_chunk_kernel(const ChunkParam
 #pragma unroll 4
             for (int t = 0; t < CH; ++t) {
                 const float4 d4 = *reinterpret_cast<const float4*>(Dm + t * CNC + 4 * tx);
+                float kv[4];
+                if constexpr (RP == 4) unpack4<DT>(*reinterpret_cast<const uint2*>(kr + t * LDH + i0), kv);
+                else { const float2 k2 = E::unpack2(*reinterpret_cast<const uint32_t*>(kr + t * LDH + i0)); kv[0] = k2.x; kv[1] = k2.y; }
 #pragma unroll
                 for (int a = 0; a < RP; ++a) {
-                    const float kv = kf[t * LD + i0 + a];
-                    acc[a][0] += kv * d4.x; acc[a][1] += kv * d4.y; acc[a][2] += kv * d4.z; acc[a][3] += kv * d4.w;
+                    acc[a][0] += kv[a] * d4.x; acc[a][1] += kv[a] * d4.y; acc[a][2] += kv[a] * d4.z; acc[a][3] += kv[a] * d4.w;
                 }
             }
-            __syncthreads();                           /* every thread has read the old state */
+            __syncthreads();                           /* every thread has read the old state and this chunk's stage */
 #pragma unroll
             for (int a = 0; a < RP; ++a) *reinterpret_cast<float4*>(Ss + (i0 + a) * CNC + 4 * tx) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
         }
     }
+    cp_async_wait<0>();
     __syncthreads();
     for (int i = tid; i < D * CNC; i += 256) Sg[(uint64_t)(i / CNC) * D + j0 + i % CNC] = Ss[i];
     if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
@@ -268,7 +389,8 @@ __global__ void __launch_bounds__(256, 1) deltanet_chunk_kernel(const ChunkParam
 /* ---------------------------------------------------------------------------------------------------------- */
 
 bool deltanet_chunked_fits(const DeltaCall& c) {
-    return (c.head_dim == 64 || c.head_dim == 128) && c.rows >= 32 && ((uintptr_t)c.out & 7u) == 0 && ((uintptr_t)c.S & 15u) == 0;
+    return (c.head_dim == 64 || c.head_dim == 128) && c.rows >= 32 && ((uintptr_t)c.out & 7u) == 0 && ((uintptr_t)c.S & 15u) == 0 &&
+           ((uintptr_t)c.conved & 15u) == 0;       /* rows of the cache are fetched 16 bytes at a time */
 }
 
 size_t deltanet_chunked_scratch_floats(const DeltaCall& c) {
@@ -279,8 +401,8 @@ size_t deltanet_chunked_scratch_floats(const DeltaCall& c) {
 template <int D, int DT>
 static cudaError_t launch_chunked(const DeltaCall& c, float* ss, float* prep) {
     constexpr int LD = D + 4;
-    const size_t smem1 = (size_t)(2 * CH * LD + 2 * CH * 65 + 4 * CH) * sizeof(float);
-    const size_t smem2 = (size_t)(D * CNC + 2 * CH * LD + 2 * CH * 65 + 2 * CH * CNC + 4 * CH) * sizeof(float);
+    const size_t smem1 = (size_t)(2 * CH * LD + 2 * CH * (CH + 1) + 6 * CH) * sizeof(float);
+    const size_t smem2 = ChunkSmem<D>::TOTAL;
     static bool attr_set[64] = {};
     int dev = 0; cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
@@ -294,7 +416,7 @@ static cudaError_t launch_chunked(const DeltaCall& c, float* ss, float* prep) {
     P.k_heads = c.k_heads; P.v_heads = c.v_heads; P.seqs = c.seqs; P.rows = c.rows;
     for (uint64_t row0 = 0; row0 < c.rows; row0 += 2048) {
         P.row0 = row0; P.seg_rows = (c.rows - row0) < 2048 ? (c.rows - row0) : 2048; P.chunks = (uint32_t)((P.seg_rows + CH - 1) / CH);
-        deltanet_prep_kernel<D, DT><<<c.seqs * c.v_heads * P.chunks, 128, smem1, c.stream>>>(P);
+        deltanet_prep_kernel<D, DT><<<c.seqs * c.k_heads * P.chunks, 256, smem1, c.stream>>>(P);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
         deltanet_chunk_kernel<D, DT><<<c.seqs * c.v_heads * (D / CNC), 256, smem2, c.stream>>>(P);
