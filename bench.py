@@ -231,6 +231,94 @@ def cpu_baseline_paged(wl: PagedWorkload, budget_s=20.0):
             "sample": f"{len(picked)} longest sequences of the batch ({positions} positions, {nbytes / 1e6:.0f} MB of KV), fp16 copies, best of <=5 passes; SILVANN_CPU_AVX512=0"}
 
 
+def gpu_baseline(torch, wl: PagedWorkload, pk, steps):
+    """The reference's own CUDA family (nvidia_cuda12, built unmodified for sm_100 into oracle/_ref) on the same card, door
+    for door: a reported baseline beside the CPU one.  Configuration 3 has no paged form there, so — as for the CPU
+    baseline — whole sequences are gathered to the contiguous planes its doors take (outside the timed region) and each is
+    attended with attention_scores + attention_mix; configurations 1, 2 and 5 are the door sequences the reference's
+    runtime issues.  fp16 throughout: the reference has no bf16 door, and the inputs are fp16-exact."""
+    import oracle
+    R = oracle.reference_cuda()
+    if R is None:
+        return {"unavailable": "oracle/_ref holds no nvidia_cuda12 family, or it counts no card here"}
+    out = {"kind": "reference nvidia_cuda12 family (sm_100 build), same card, CUDA events"}
+    L = wl.layout
+    order = np.argsort(L.seq_lens)[::-1][:8]
+    planes, positions = [], 0
+    for s in order:
+        n = int(L.seq_lens[s]); positions += n
+        pages = torch.from_numpy(L.page_table[s, :(n + wl.page_positions - 1) // wl.page_positions].astype(np.int64)).cuda()
+        ks = wl.k_pool[pages].reshape(-1, L.kv_heads, L.head_dim)[:n].to(torch.float16).contiguous()
+        vs = wl.v_pool[pages].reshape(-1, L.kv_heads, L.head_dim)[:n].to(torch.float16).contiguous()
+        planes.append((wl.q[s].to(torch.float16).contiguous(), ks, vs, n))
+    p = torch.zeros(L.q_heads * int(L.seq_lens.max()), device="cuda", dtype=torch.float32)
+    o = torch.zeros((L.q_heads, L.head_dim), device="cuda", dtype=torch.float16)
+    over = torch.zeros(4, device="cuda", dtype=torch.int32)          # the fault word every door that rounds is handed
+
+    def sample():
+        for qs, ks, vs, n in planes:
+            R.nn.attention_scores(p.data_ptr(), qs.data_ptr(), ks.data_ptr(), L.q_heads, L.kv_heads, L.head_dim, n)
+            R.nn.attention_mix(o.data_ptr(), p.data_ptr(), vs.data_ptr(), L.q_heads, L.kv_heads, L.head_dim, n, over.data_ptr())
+    ms = time_loop(torch, sample, max(2, min(steps, 5)), 1)
+    nbytes = positions * 2 * L.kv_heads * L.head_dim * 2
+    out["value"], out["unit"] = nbytes / ms / 1e6, UNIT
+    out["sample"] = f"the 8 longest sequences of the batch ({positions} positions, {nbytes / 1e6:.0f} MB of KV), gathered to contiguous fp16 planes outside the timed region"
+    del planes
+    gen = torch.Generator(device="cuda"); gen.manual_seed(78)
+
+    # configuration 1: the door pair, 64 caches cycled
+    qh, kvh, d, n, copies = 16, 4, 128, 8192, 64
+    k = torch.randn((copies, n, kvh, d), generator=gen, device="cuda", dtype=torch.float16)
+    v = torch.randn((copies, n, kvh, d), generator=gen, device="cuda", dtype=torch.float16)
+    q = torch.randn((qh, d), generator=gen, device="cuda", dtype=torch.float16)
+    o1 = torch.zeros((qh, d), device="cuda", dtype=torch.float16)
+    state = {"i": 0}
+
+    def pair():
+        i = state["i"] = (state["i"] + 1) % copies
+        R.nn.attention_scores(p.data_ptr(), q.data_ptr(), k[i].data_ptr(), qh, kvh, d, n)
+        R.nn.attention_mix(o1.data_ptr(), p.data_ptr(), v[i].data_ptr(), qh, kvh, d, n, over.data_ptr())
+    ms = time_loop(torch, pair, 100, 10)
+    out["config1_decode_doors"] = {"value": 2 * n * kvh * d * 2 / ms / 1e6, "unit": UNIT, "ms_per_call": ms}
+    del k, v
+
+    # configuration 2: the three causal doors, 256 rows a call as the reference's runtime drives them
+    qh, kvh, d, T, chunk = 16, 2, 256, 4096, 256
+    q = (torch.randn((T, qh, d), generator=gen, device="cuda", dtype=torch.float16) * 0.5)
+    k = (torch.randn((T, kvh, d), generator=gen, device="cuda", dtype=torch.float16) * 0.5)
+    v = (torch.randn((T, kvh, d), generator=gen, device="cuda", dtype=torch.float16) * 0.5)
+    o2 = torch.zeros((T, qh, d), device="cuda", dtype=torch.float16)
+    pc = torch.zeros(chunk * qh * T, device="cuda", dtype=torch.float32)
+
+    def prefill():
+        for first in range(0, T, chunk):
+            R.nn.attention_causal_scores_grouped(pc.data_ptr(), q[first].data_ptr(), k.data_ptr(), qh, kvh, d, first, chunk)
+            R.nn.attention_causal_softmax(pc.data_ptr(), qh, first, chunk)
+            R.nn.attention_causal_mix(o2[first].data_ptr(), pc.data_ptr(), v.data_ptr(), qh, kvh, d, first, chunk, over.data_ptr())
+    ms = time_loop(torch, prefill, 3, 1)
+    out["config2_causal_prefill"] = {"value": 4.0 * qh * d * T * (T + 1) / 2 / ms / 1e9, "unit": "TFLOP/s", "ms_per_call": ms}
+    del q, k, v, o2, pc
+
+    # configuration 5: one recurrent step (one sequence), and the 8,192-position prompt through deltanet_steps_gate
+    heads, d, T = 32, 128, 8192
+    S = torch.zeros((heads, d, d), device="cuda", dtype=torch.float32)
+    conved = torch.randn((T, 3 * heads * d), generator=gen, device="cuda", dtype=torch.float16) * 0.1
+    z = torch.randn((T, heads * d), generator=gen, device="cuda", dtype=torch.float16)
+    beta = torch.rand((T, heads), generator=gen, device="cuda", dtype=torch.float32).to(torch.float16)
+    g = (-torch.rand((T, heads), generator=gen, device="cuda", dtype=torch.float32)).to(torch.float16)
+    w = torch.ones(d, device="cuda", dtype=torch.float16)
+    o5 = torch.zeros((T, heads * d), device="cuda", dtype=torch.float16)
+    ms = time_loop(torch, lambda: R.nn.deltanet_step(S.data_ptr(), conved.data_ptr(), z.data_ptr(), beta.data_ptr(), g.data_ptr(), w.data_ptr(),
+                                                     o5.data_ptr(), heads, heads, d, over.data_ptr()), 100, 10)
+    out["config5_deltanet_decode_1seq"] = {"ms_per_step": ms}
+    S.zero_()
+    ms = time_loop(torch, lambda: R.nn.deltanet_steps_gate(S.data_ptr(), conved.data_ptr(), z.data_ptr(), beta.data_ptr(), g.data_ptr(), w.data_ptr(),
+                                                           o5.data_ptr(), heads, heads, d, T, 0, over.data_ptr()), 2, 1)
+    out["config5_deltanet_prefill_8192"] = {"value": T / ms * 1e3, "unit": "positions/s", "ms": ms}
+    R.sys.compute_completed()
+    return out
+
+
 def other_workloads(torch, fam, pk, steps, warmup):
     """Configurations 1, 4 and 5 (and 2 when the prefill kernel fits), each timed alone on one GPU."""
     from silvann_b200 import ext, workloads
@@ -450,6 +538,8 @@ def run_ours(args):
                             "algorithmic_bytes_per_launch": wl.kv_bytes}
         if world == 1:
             line["cpu_baseline"] = cpu_baseline_paged(wl)
+            if not args.no_others:
+                line["gpu_baseline"] = gpu_baseline(torch, wl, pk, steps)
             if not args.no_others:
                 line["others"] = other_workloads(torch, fam, pk, steps, warmup)
     e2e.close()

@@ -309,3 +309,24 @@ def reference() -> Reference | None:
         if so is not None and so.exists():
             _reference = Reference(so)
     return _reference
+
+
+_reference_cuda = None
+_reference_cuda_tried = False
+
+
+def reference_cuda():
+    """The reference's own CUDA family (oracle/_ref/libsilvann_nvidia_cuda12.so, built by oracle/build.py) as a table of
+    doors that take DEVICE addresses, bound to device 0 of the cards it counts — the same-card baseline.  None when the
+    library is not there or counts no card on this machine."""
+    global _reference_cuda, _reference_cuda_tried
+    if not _reference_cuda_tried:
+        _reference_cuda_tried = True
+        from . import build
+        so = build.build_reference_cuda()
+        if so is not None and so.exists():
+            from silvann_b200.abi import Family
+            fam = Family(so)
+            if fam.sys.device_count() >= 1 and fam.sys.bind_device(0) == 1:
+                _reference_cuda = fam
+    return _reference_cuda

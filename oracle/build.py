@@ -51,6 +51,29 @@ def build_reference(force: bool = False) -> Path | None:
     return REF
 
 
+REF_CUDA = REF_DIR / "libsilvann_nvidia_cuda12.so"
+
+
+def build_reference_cuda(force: bool = False) -> Path | None:
+    """The reference's own CUDA family for sm_100 — the same-card baseline the B200 family is measured beside — built
+    with the reference's recipe for it (engine/scripts/build_silicon_families.sh:141-156 of that tree: one translation
+    unit that includes silicon_families/nvidia_cuda12/unit.cuh; nvcc -O2 -std=c++17 -cudart static).  None when the
+    sources are not on this machine and no earlier build is present."""
+    unit = REFERENCE_TREE / "engine" / "src" / "silicon_families" / "nvidia_cuda12" / "unit.cuh"
+    if not unit.exists():
+        return REF_CUDA if REF_CUDA.exists() else None
+    if REF_CUDA.exists() and not force:
+        return REF_CUDA
+    REF_DIR.mkdir(exist_ok=True)
+    with tempfile.TemporaryDirectory() as tmp:
+        tu = Path(tmp) / "nvidia_cuda12.cu"
+        tu.write_text('#include "silicon_families/nvidia_cuda12/unit.cuh"\n')
+        cmd = ["nvcc", "-gencode", "arch=compute_100,code=sm_100", "-O2", "-std=c++17", "-cudart", "static", "-w",
+               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared", "-I", str(REFERENCE_TREE / "engine" / "src"), str(tu), "-o", str(REF_CUDA)]
+        subprocess.run(cmd, check=True)
+    return REF_CUDA
+
+
 def engine_path() -> Path:
     import sysconfig
     return REF_DIR / ("silvann_engine_cpu" + sysconfig.get_config_var("EXT_SUFFIX"))
@@ -78,3 +101,4 @@ if __name__ == "__main__":
     print(build_port(force="-f" in sys.argv))
     print(build_reference(force="-f" in sys.argv))
     print(build_engine(force="-f" in sys.argv))
+    print(build_reference_cuda(force="-f" in sys.argv))
