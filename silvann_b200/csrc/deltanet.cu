@@ -41,7 +41,21 @@ struct DeltaParams {
     int gate;
 };
 
-template <int D, int DT, bool PRE>
+/* the blocks of a head as a thread-block cluster: a barrier over all of them, and a float read from a peer's shared memory */
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t rank) {
+    uint32_t remote; float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+/* FUSE: the kernel is launched with the d/32 blocks of a head as one cluster; they hand each other their sums of squares
+ * through distributed shared memory and finish the read-out (norm, weight, gate) themselves — one launch a step, which
+ * is what a decode step of one sequence is bound by.  The sums are added in block order, as the norm kernel adds them. */
+template <int D, int DT, bool PRE, bool FUSE>
 __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaParams P) {
     using E = Elem<DT>;
     constexpr int CB = D / DN_COLS;            /* column blocks per head */
@@ -55,6 +69,7 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
     __shared__ __align__(16) float qk[2][2][D];   /* [buffer][q|k][i] as fp32 */
     __shared__ float red1[DN_RG][DN_COLS + 2];     /* first fold, per row group: S^T k partials, then |q|^2 and |k|^2 */
     __shared__ float red2[DN_RG][DN_COLS];         /* second fold: read-out partials */
+    __shared__ float cl_ss[2];                     /* FUSE: this block's sum of squares, even and odd positions */
 
     float* Sh = P.S + ((uint64_t)b * P.v_heads + h) * D * D;
     float s[R];
@@ -113,6 +128,9 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
                 }
             }
         }
+        /* FUSE: the gate's input and the norm's weight are on their way while the state is worked */
+        const uint16_t z_bits = (FUSE && rg == 0) ? P.z[((uint64_t)b * P.rows + t) * vd + (uint64_t)h * D + j] : (uint16_t)0;
+        const uint16_t w_bits = (FUSE && rg == 0) ? P.w[j] : (uint16_t)0;
         const float* qv = qk[buf][0] + rg * R;
         const float* kv_ = qk[buf][1] + rg * R;
         float kvp = 0.f, qq = 0.f, kk = 0.f;
@@ -150,13 +168,31 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
         }
         red2[rg][c] = (op4[0] + op4[1]) + (op4[2] + op4[3]);
         __syncthreads();
+        uint16_t oh = 0;
         if (rg == 0) {
             const float o = (red2[0][c] + red2[1][c] + red2[2][c] + red2[3][c]) * inv_q;
-            const uint16_t oh = E::from_float(o, hit);
-            oo[t * vd + (uint64_t)h * D + j] = oh;
+            oh = E::from_float(o, hit);
             float sq = E::to_float(oh); sq *= sq;
             for (int x = 16; x > 0; x >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, x);
-            if (c == 0) ss[(t * P.v_heads + h) * CB + cb] = sq;
+            if (!FUSE) {
+                oo[t * vd + (uint64_t)h * D + j] = oh;
+                if (c == 0) ss[(t * P.v_heads + h) * CB + cb] = sq;
+            } else if (c == 0) cl_ss[t & 1] = sq;
+        }
+        if (FUSE) {
+            /* a slot is rewritten two positions later, after the cluster barrier of the position between */
+            cluster_sync_all();
+            if (rg == 0) {
+                float sum = 0.f;
+#pragma unroll
+                for (int r = 0; r < CB; ++r) sum += ld_cluster_f32(&cl_ss[t & 1], (uint32_t)r);
+                const float scale = 1.0f / sqrtf(sum / (float)D + 1e-6f);
+                const float zr = E::to_float(z_bits);
+                const float zc = zr < -88.0f ? -88.0f : (zr > 88.0f ? 88.0f : zr);
+                const float sg = 1.0f / (1.0f + expf(-zc));
+                const float gz = P.gate == 1 ? sg : zc * sg;
+                oo[t * vd + (uint64_t)h * D + j] = E::from_float(E::to_float(oh) * scale * E::to_float(w_bits) * gz, hit);
+            }
         }
         /* Two barriers a position are enough because the folds use separate arrays: red1 is rewritten after this
          * position's second barrier, which follows every read of it; red2 is rewritten after the next position's first
@@ -166,6 +202,7 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
 #pragma unroll
     for (int i = 0; i < R; ++i) Sh[(uint64_t)(rg * R + i) * D + j] = s[i];
     if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
+    if (FUSE) cluster_sync_all();                  /* no block leaves while a peer may still read its slot */
 }
 
 /* The per-position scalars of a run of positions, off the serial path: a warp a (sequence, position, key head) folds
@@ -244,6 +281,11 @@ bool deltanet_fits(const DeltaCall& c) {
     return ((uintptr_t)c.S & 3u) == 0;
 }
 
+static unsigned fuse_blocks_max() {
+    static const unsigned v = []() { const char* e = getenv("SILVANN_B200_DELTANET_FUSE_BLOCKS"); return e ? (unsigned)strtoul(e, nullptr, 10) : 1024u; }();
+    return v;
+}
+
 template <int D, int DT>
 static cudaError_t launch_dn(const DeltaCall& c, float* ss) {
     DeltaParams P;
@@ -260,10 +302,24 @@ static cudaError_t launch_dn(const DeltaCall& c, float* ss) {
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
         note_launch(1);
         P.sc = sc;
-        deltanet_steps_kernel<D, DT, true><<<blocks, DN_THREADS, 0, c.stream>>>(P);
-    } else {
+        deltanet_steps_kernel<D, DT, true, false><<<blocks, DN_THREADS, 0, c.stream>>>(P);
+    } else if (blocks > fuse_blocks_max()) {
         P.sc = nullptr;
-        deltanet_steps_kernel<D, DT, false><<<blocks, DN_THREADS, 0, c.stream>>>(P);
+        deltanet_steps_kernel<D, DT, false, false><<<blocks, DN_THREADS, 0, c.stream>>>(P);
+    } else {
+        /* one position of a few sequences: the d/32 blocks of a head as a cluster, the read-out finished in the same
+         * launch.  With many sequences the card is full either way and the cluster barrier costs more than a launch. */
+        P.sc = nullptr;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(blocks); cfg.blockDim = dim3(DN_THREADS); cfg.dynamicSmemBytes = 0; cfg.stream = c.stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = D / DN_COLS; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, deltanet_steps_kernel<D, DT, false, true>, P);
+        if (e != cudaSuccess) return e;
+        note_launch(1);
+        return cudaGetLastError();
     }
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
