@@ -319,6 +319,28 @@ def gpu_baseline(torch, wl: PagedWorkload, pk, steps):
     return out
 
 
+def config1_graph(torch, ext, gen, copies=64):
+    """Configuration 1 without the host in the loop: `copies` decode launches (the extension call the door pair fuses into),
+    one per distinct cache, captured once into a CUDA graph on a side stream.  Answers (replay, bytes a launch, unit)."""
+    qh, kvh, d, n = 16, 4, 128, 8192
+    k = torch.randn((copies, n, kvh, d), generator=gen, device="cuda", dtype=torch.float16)
+    v = torch.randn((copies, n, kvh, d), generator=gen, device="cuda", dtype=torch.float16)
+    q = torch.randn((qh, d), generator=gen, device="cuda", dtype=torch.float16)
+    o = torch.zeros((copies, qh, d), device="cuda", dtype=torch.float16)
+    side = torch.cuda.Stream()
+    ext.decode(o[0], None, q, k[0], v[0], qh, kvh, d, n, ext.FP16)          # scratch is allocated outside the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(copies):
+            ext.decode(o[i], None, q, k[i], v[i], qh, kvh, d, n, ext.FP16, stream=side.cuda_stream)
+    keep = (k, v, q, o, side)
+
+    def replay(_keep=keep):
+        graph.replay()
+    return replay, 2 * n * kvh * d * 2, "bytes"
+
+
 def other_workloads(torch, fam, pk, steps, warmup):
     """Configurations 1, 4 and 5 (and 2 when the prefill kernel fits), each timed alone on one GPU."""
     from silvann_b200 import ext, workloads
@@ -345,6 +367,12 @@ def other_workloads(torch, fam, pk, steps, warmup):
     out["config1_decode_doors"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms, "frac_hbm": nbytes / ms / 1e6 / hbm,
                                    "note": "attention_scores+attention_mix door pair, fp16, 16.8 MB of KV a call, 64 caches cycled"}
     del k, v
+    replay, nb1, _ = config1_graph(torch, ext, gen)
+    ms = time_loop(torch, replay, 20, 3) / 64
+    out["config1_decode_kernel"] = {"value": nb1 / ms / 1e6, "unit": UNIT, "ms_per_call": ms, "frac_hbm": nb1 / ms / 1e6 / hbm,
+                                    "note": "the same fused launch without the host in the loop: a CUDA graph of 64 launches, a distinct cache each"}
+    del replay
+    torch.cuda.empty_cache()
 
     # configuration 4 on one GPU, everything in HBM (537 MB a pass)
     qh, kvh, d, L = 32, 4, 128, 262144
@@ -647,6 +675,25 @@ def run_case(args):
         o = torch.zeros_like(q)
         fn = lambda: ext.decode(o, None, q, k, v, qh, kvh, d, n, ext.BF16)
         work, unit = 2 * n * kvh * d * 2, "bytes"
+    elif name == "decode_cfg1":
+        # configuration 1 through the two doors (one fused launch a pair), 16 distinct caches cycled: 268 MB in all
+        qh, kvh, d, n, copies = 16, 4, 128, 8192, 16
+        k = torch.randn((copies, n, kvh, d), generator=gen, device="cuda", dtype=torch.float16)
+        v = torch.randn((copies, n, kvh, d), generator=gen, device="cuda", dtype=torch.float16)
+        q = torch.randn((qh, d), generator=gen, device="cuda", dtype=torch.float16)
+        p = torch.zeros((qh, n), device="cuda", dtype=torch.float32)
+        o = torch.zeros((qh, d), device="cuda", dtype=torch.float16)
+        state = {"i": 0}
+
+        def fn():
+            i = state["i"] = (state["i"] + 1) % copies
+            fam.nn.attention_scores(p.data_ptr(), q.data_ptr(), k[i].data_ptr(), qh, kvh, d, n)
+            fam.nn.attention_mix(o.data_ptr(), p.data_ptr(), v[i].data_ptr(), qh, kvh, d, n, None)
+        work, unit = 2 * n * kvh * d * 2, "bytes"
+    elif name == "decode_cfg1_graph":
+        # configuration 1 as the card sees it: one CUDA graph of 64 decode launches, a distinct cache each (1.07 GB)
+        fn, work, unit = config1_graph(torch, ext, gen)
+        work *= 64
     elif name == "deltanet_64":
         heads, d, seqs = 32, 128, 64
         S = torch.zeros((seqs, heads, d, d), device="cuda", dtype=torch.float32)
@@ -691,7 +738,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the secondary configurations (faster; used under profilers)")
-    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, deltanet_64, deltanet_prefill, prefill_small)")
+    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, decode_cfg1, decode_cfg1_graph, deltanet_64, deltanet_prefill, prefill_small)")
     args = ap.parse_args()
     if args.case:
         run_case(args)

@@ -53,6 +53,18 @@ struct DecodeParams {
     float scale_log2;
 };
 
+#ifdef SV_DECODE_TRACE
+/* Development aid, compiled only on request: every block leaves %globaltimer stamps (ns) of its phases here. */
+__device__ unsigned long long g_dec_trace[256 * 16];
+__device__ __forceinline__ unsigned long long sv_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define SV_DTR(k) do { if (threadIdx.x == 0 && blockIdx.x < 256) g_dec_trace[blockIdx.x * 16 + (k)] = sv_gtime(); } while (0)
+extern "C" __attribute__((visibility("default"))) int sv_decode_trace_read(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_dec_trace, sizeof(unsigned long long) * 256 * 16);
+}
+#else
+#define SV_DTR(k) do {} while (0)
+#endif
+
 template <int D, int DT, int NHT>
 __global__ void __launch_bounds__((DecodeCfg<D>::NW + 1) * 32, 1)
 decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
@@ -75,6 +87,7 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     uint32_t* ticket_s = (uint32_t*)abort_flag + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    SV_DTR(0);
 
     /* ---- which work is this block's ---- */
     int seq, kvh, head0, heads, tile_begin, tile_end, split, nsplit, slot_base, slot_stride, ticket;
@@ -143,6 +156,7 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
             *reinterpret_cast<uint4*>(q_base + (j / 8) * (HPB * 128) + swz128(r, j % 8)) = val;
         }
         asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+        SV_DTR(1);
 
         uint32_t qf[QREG ? NHT : 1][QREG ? KS : 1][2];
         const uint32_t q_u32 = smem_u32(q_base);
@@ -164,6 +178,7 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
         for (int it = 0; it < nt; ++it) {
             const int s = it % Cfg::STAGES;
             if (!mbar_wait(&full[s], (it / Cfg::STAGES) & 1, abort_flag, P.status)) break;
+            if (it == 0) SV_DTR(2);
             const uint32_t kst = smem_u32(stage_base + s * Cfg::STAGE_BYTES), vst = kst + Cfg::K_BYTES;
             const int pos0 = (tile_begin + it) * BT + warp * 16;
 
@@ -275,6 +290,7 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
             }
         }
     }
+    SV_DTR(3);
     __syncthreads();
 
     const uint32_t SF = P.slot_floats;                /* floats per head in scratch: D + 2 */
@@ -301,9 +317,9 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
                 if (e == 0) { r[0] = m * SV_LN2; r[1] = l; }
             }
         } else {
-            float* r = my_slot + (size_t)h * SF;
-            r[2 + e] = acc;
-            if (e == 0) { r[0] = m; r[1] = l; }
+            /* a slot: the heads' accumulators, D floats each on a 16-byte boundary, then (m, l) pairs a head */
+            my_slot[(size_t)h * D + e] = acc;
+            if (e == 0) { my_slot[HPB * D + 2 * h] = m; my_slot[HPB * D + 2 * h + 1] = l; }
         }
     }
     if (single) {
@@ -312,60 +328,122 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     }
 
     /* ---- arrive; the last block of the group merges all splits in split order ---- */
+    SV_DTR(4);
     __threadfence();
     __syncthreads();
     if (tid == 0) *ticket_s = atomicAdd(&P.tickets[ticket], 1u);
     __syncthreads();
+    SV_DTR(5);
     if (*ticket_s != (uint32_t)(nsplit - 1)) return;
     __threadfence();
-    /* first the per-(head, split) factors e^(m_s - m) and the merged l, a warp a head, lanes across splits ... */
+    /* The block is alone with its group by now and bound by trips to L2, so everything it needs is asked for at once:
+     * a thread owns four neighbouring elements of a head over one run of splits and has that run's accumulators in
+     * flight (16 bytes a load, no branch between the loads) while the warps that own a head fetch the splits' (m, l) and
+     * make the factors e^(m_s - m); then the run is summed in split order, the runs in run order — a fixed order, so
+     * results repeat bit for bit. */
+    constexpr int THREADS = (NW + 1) * 32, RUN_MAX = 16;
     float* fac = (float*)stage_base;                  /* [heads][nsplit] */
     float* mh = fac + HPB * nsplit;                   /* [heads] merged m (log2 units), then merged l */
     float* lh = mh + HPB;
-    for (int h = warp; h < heads; h += NW + 1) {
+    float4* part = (float4*)(lh + HPB + ((4 - ((2 * HPB + HPB * nsplit) & 3)) & 3));   /* [runs][heads * D / 4] */
+    const int e4n = heads * (D / 4);
+    int runs = THREADS / e4n;                         /* thread groups that share the splits of an element */
+    if (runs < 1) runs = 1;
+    if (runs > nsplit) runs = nsplit;
+    int run_len = (nsplit + runs - 1) / runs;
+    const size_t slot_f = (size_t)HPB * SF, step = (size_t)slot_stride * slot_f;
+    const float* base = P.partials + (size_t)slot_base * slot_f;
+    const bool one_pass = run_len <= RUN_MAX && runs * e4n <= THREADS;
+    /* the (m, l) of a split a lane, asked for ahead of the accumulators so that they are back first */
+    const bool ml_lanes = nsplit <= 32 && warp < heads;
+    float ms_l = -INFINITY, ls_l = 0.f;
+    if (ml_lanes && lane < nsplit) {
+        const float* r = base + (size_t)lane * step + HPB * D + 2 * warp;
+        ms_l = __ldcg(r); ls_l = __ldcg(r + 1);
+    }
+    float4 x[RUN_MAX];
+    int my_e4 = 0, my_run = 0, s0 = 0, s1 = 0;
+    if (one_pass && tid < runs * e4n) {
+        my_e4 = tid % e4n; my_run = tid / e4n; s0 = my_run * run_len; s1 = min(nsplit, s0 + run_len);
+        const float* r = base + (size_t)(my_e4 / (D / 4)) * D + (my_e4 % (D / 4)) * 4;
+#pragma unroll
+        for (int u = 0; u < RUN_MAX; ++u) x[u] = __ldcg(reinterpret_cast<const float4*>(r + (size_t)min(s0 + u, nsplit - 1) * step));
+    }
+    if (ml_lanes) {
+        const int h = warp;
+        float m = ms_l;
+        for (int xo = 16; xo > 0; xo >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, xo));
+        const float f = (ms_l == -INFINITY) ? 0.f : fast_exp2(ms_l - m);
+        if (lane < nsplit) fac[h * nsplit + lane] = f;
+        float l = ls_l * f;
+        for (int xo = 16; xo > 0; xo >>= 1) l += __shfl_xor_sync(0xffffffffu, l, xo);
+        if (lane == 0) { mh[h] = m; lh[h] = l; }
+    }
+    for (int h = warp + (ml_lanes ? NW + 1 : 0); h < heads; h += NW + 1) {      /* the heads no warp took above */
         float m = -INFINITY;
-        for (int s = lane; s < nsplit; s += 32)
-            m = fmaxf(m, __ldcg(P.partials + ((size_t)(slot_base + s * slot_stride) * HPB + h) * SF));
-        for (int x = 16; x > 0; x >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, x));
+        for (int sp = lane; sp < nsplit; sp += 32) m = fmaxf(m, __ldcg(base + (size_t)sp * step + HPB * D + 2 * h));
+        for (int xo = 16; xo > 0; xo >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, xo));
         float l = 0.f;
-        for (int s = lane; s < nsplit; s += 32) {
-            const float* r = P.partials + ((size_t)(slot_base + s * slot_stride) * HPB + h) * SF;
+        for (int sp = lane; sp < nsplit; sp += 32) {
+            const float* r = base + (size_t)sp * step + HPB * D + 2 * h;
             const float ms = __ldcg(r);
             const float f = (ms == -INFINITY) ? 0.f : fast_exp2(ms - m);
-            fac[h * nsplit + s] = f;
+            fac[h * nsplit + sp] = f;
             l += __ldcg(r + 1) * f;
         }
-        for (int x = 16; x > 0; x >>= 1) l += __shfl_xor_sync(0xffffffffu, l, x);
+        for (int xo = 16; xo > 0; xo >>= 1) l += __shfl_xor_sync(0xffffffffu, l, xo);
         if (lane == 0) { mh[h] = m; lh[h] = l; }
     }
     __syncthreads();
-    /* ... then each output element: the splits' accumulators in split order, neighbouring threads neighbouring
-     * elements, so every load is a coalesced read of what the other blocks left in L2 */
-    for (int i = tid; i < heads * D; i += (NW + 1) * 32) {
-        const int h = i / D, e = i % D;
-        const float* r = P.partials + ((size_t)slot_base * HPB + h) * SF + 2 + e;
-        const size_t step = (size_t)slot_stride * HPB * SF;
-        const float* f = fac + h * nsplit;
-        float acc = 0.f;
-        int s = 0;
-        for (; s + 8 <= nsplit; s += 8) {
-            float x[8];
+    SV_DTR(7);
+    if (one_pass) {
+        if (tid < runs * e4n) {
+            const float* f = fac + (my_e4 / (D / 4)) * nsplit;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int u = 0; u < 8; ++u) x[u] = __ldcg(r + (size_t)(s + u) * step);
-#pragma unroll
-            for (int u = 0; u < 8; ++u) acc += x[u] * f[s + u];
+            for (int u = 0; u < RUN_MAX; ++u)
+                if (s0 + u < s1) { const float w = f[s0 + u]; acc.x += x[u].x * w; acc.y += x[u].y * w; acc.z += x[u].z * w; acc.w += x[u].w * w; }
+            part[my_run * e4n + my_e4] = acc;
         }
-        for (; s < nsplit; ++s) acc += __ldcg(r + (size_t)s * step) * f[s];
+        __syncthreads();
+    }
+    for (int i4 = tid; i4 < e4n; i4 += THREADS) {
+        const int h = i4 / (D / 4), e = (i4 % (D / 4)) * 4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (one_pass) {
+            for (int g = 0; g < runs; ++g) { const float4 p4 = part[g * e4n + i4]; acc.x += p4.x; acc.y += p4.y; acc.z += p4.z; acc.w += p4.w; }
+        } else {
+            /* many splits, or more elements than threads: eight loads in flight at a time */
+            const float* r = base + (size_t)h * D + e;
+            const float* f = fac + h * nsplit;
+            int sp = 0;
+            for (; sp + 8 <= nsplit; sp += 8) {
+                float4 y[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) y[u] = __ldcg(reinterpret_cast<const float4*>(r + (size_t)(sp + u) * step));
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { const float w = f[sp + u]; acc.x += y[u].x * w; acc.y += y[u].y * w; acc.z += y[u].z * w; acc.w += y[u].w * w; }
+            }
+            for (; sp < nsplit; ++sp) {
+                const float4 y = __ldcg(reinterpret_cast<const float4*>(r + (size_t)sp * step));
+                const float w = f[sp]; acc.x += y.x * w; acc.y += y.y * w; acc.z += y.z * w; acc.w += y.w * w;
+            }
+        }
         const float m = mh[h], l = lh[h];
         const size_t hq = (size_t)seq * P.q_heads + head0 + h;
-        if (P.o) ((uint16_t*)P.o)[hq * D + e] = E::from_float(acc / l, hit);
+        if (P.o) {
+            uint16_t* op = (uint16_t*)P.o + hq * D + e;
+            op[0] = E::from_float(acc.x / l, hit); op[1] = E::from_float(acc.y / l, hit);
+            op[2] = E::from_float(acc.z / l, hit); op[3] = E::from_float(acc.w / l, hit);
+        }
         if (P.res) {
             float* ro = P.res + hq * (D + 2);
-            ro[2 + e] = acc;
+            ro[2 + e] = acc.x; ro[3 + e] = acc.y; ro[4 + e] = acc.z; ro[5 + e] = acc.w;
             if (e == 0) { ro[0] = m * SV_LN2; ro[1] = l; }
         }
     }
     if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
+    SV_DTR(6);
     if (tid == 0) P.tickets[ticket] = 0u;             /* ready for the next launch */
 }
 
