@@ -5,14 +5,23 @@
  * rows x (first + rows) fp32 weights buffer they pass between them.  Row r of the call is position first + r and attends
  * cache rows 0 .. first + r; query head h reads kv head h / (q_heads / kv_heads).
  *
- * A block owns 128 query rows of one head.  Roles: warp 0 issues TMA loads (Q once, then a ring of K and V tiles of 64
- * keys, 128-byte swizzle); one thread of warp 1 issues the MMAs — S = Q·K^T into one of two TMEM buffers (M 128, N 64,
- * K = head_dim in steps of 16) and O += P·V (M 128, N = head_dim, K 64) with the accumulator O resident in TMEM for
- * the whole row block; warps 2-5 (one thread per query row, its row of S read straight from TMEM with tcgen05.ld, so
- * row max and row sum need no shuffles) run the online softmax, write P as 16-bit into a swizzled shared tile for the
- * second MMA, rescale O in TMEM only when a row's maximum has grown by more than 2^8 (the reference maximum is otherwise
- * kept, which is exact: every weight and the normaliser are relative to the same reference), and finally divide and
- * store.  S for tile j+1 is issued before the softmax of tile j has finished, so the tensor pipe and the softmax overlap.
+ * A block owns 128 query rows of one head; 11 warps in four roles.
+ *   warp 0      TMA: Q once (128 x head_dim, kept in shared memory for the whole block), then rings of K tiles and V
+ *               tiles of 64 keys (128-byte swizzle; 3 + 2 stages at head_dim 256, 4 + 4 below).
+ *   warp 1      one thread issues the score MMAs S = Q.K^T (M 128, N 64, K = head_dim in steps of 16, both operands in
+ *               shared memory) into one of THREE score buffers in TMEM, so scores run two tiles ahead of the softmax.
+ *   warps 2-9   the online softmax, two warps a TMEM lane quadrant: a thread owns half of one query row (32 of the
+ *               tile's 64 scores, read with tcgen05.ld), the two halves exchange max and sum through shared memory.
+ *               The weights go back INTO TMEM, 16-bit, over the scores they came from (tcgen05.st), and are the A
+ *               operand of the value MMA there: P never touches shared memory.  O is rescaled in TMEM only when a
+ *               row's maximum has grown by more than 2^8 (the reference maximum is otherwise kept, which is exact:
+ *               every weight and the normaliser are relative to the same reference).
+ *   warp 10     one thread issues the value MMAs O += P.V (M 128, N = head_dim, K 64; A from TMEM, B MN-major from
+ *               shared memory) with O resident in TMEM for the whole row block.
+ * Two issuing threads because the MMA queue is shallow and a satisfied mbarrier wait costs ~100 cycles: with one thread
+ * every wait for the softmax was a bubble in the tensor pipe.  TMEM columns: O in [0, head_dim), score buffer b at
+ * head_dim + 64 b.  The epilogue divides by the row sum and stores 16-bit rows, or leaves (m ln 2, l, acc) a row in the
+ * reference's residual layout (the many-row residual doors).
  *
  * Every mbarrier wait is bounded; a wait that runs out raises the block's abort flag, ORs "B2TO" into the device status
  * word, and every role falls through to the common exit, where TMEM is released.  No multicast, no cluster.
