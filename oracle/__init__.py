@@ -82,6 +82,10 @@ class Port:
             "oracle_attention_mix_rows": [vp, u64, vp, u64, vp, u64, vp, u64, u64, u64, u64, i32, vp],
             "oracle_deltanet_gates_rows": [vp, vp, vp, vp, vp, vp, u64, u64],
             "oracle_deltanet_conv_steps": [vp, vp, vp, vp, u64, u64],
+            "oracle_turboquant_decode": [vp, vp, vp, u64, u64, u64],
+            "oracle_hadamard_blocks": [vp, vp, vp, u64, u64, u64],
+            "oracle_turboquant_encode_rows": [vp, vp, vp, u64, u64, u64],
+            "oracle_attention_residual_tq": [vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u64],
         }
         for name, args in sig.items():
             fn = getattr(self.lib, name)
@@ -286,6 +290,70 @@ class Reference:
             self.nn.deltanet_steps_gate(_p(S), _p(conved), _p(z), _p(beta), _p(g), _p(w), _p(out), kh, vh, d, rows, gate, _p(self.over))
         self.wait()
         return out
+
+
+# ---- the TurboQuant-coded tiers: the same four operations through either implementation --------------------------------
+
+def tq_row_bytes(d: int, cols: int) -> int:
+    per = 16 // d
+    return ((cols + per - 1) // per) * 2
+
+
+def tq_levels(impl, d: int) -> np.ndarray:
+    """The 2^d levels of width d as fp16 bit patterns: every code decoded at scale 1."""
+    n = 1 << d
+    per = 16 // d
+    units = np.zeros((n + per - 1) // per, np.uint16)
+    for c in range(n):
+        units[c // per] |= np.uint16(c << (d * (c % per)))
+    codes = units.view(np.uint8).copy()
+    lut = np.array([0x3C00], np.uint16).view(np.uint8).copy()
+    return tq_decode(impl, codes, lut, d, 1, n).reshape(n)
+
+
+def tq_decode(impl, codes, luts, d, rows, cols):
+    out = np.zeros((rows, cols), np.uint16)
+    if isinstance(impl, Port):
+        impl.lib.oracle_turboquant_decode(_p(out), _p(codes), _p(luts), d, rows, cols)
+    else:
+        impl.nn.turboquant_decode(_p(out), _p(codes), codes.nbytes, _p(luts), luts.nbytes, d, rows, cols, _p(impl.over))
+        impl.wait()
+    return out
+
+
+def hadamard_blocks(impl, x, sign, block, inverse):
+    out = np.zeros_like(x)
+    if isinstance(impl, Port):
+        impl.lib.oracle_hadamard_blocks(_p(out), _p(x), _p(sign), x.size, block, inverse)
+    else:
+        impl.nn.hadamard_blocks(_p(out), _p(x), _p(sign), x.size, block, inverse, _p(impl.over))
+        impl.wait()
+    return out
+
+
+def tq_encode_rows(impl, x, d):
+    rows, cols = x.shape
+    codes = np.zeros((rows, tq_row_bytes(d, cols)), np.uint8)
+    scales = np.zeros(rows, np.uint16)
+    if isinstance(impl, Port):
+        impl.lib.oracle_turboquant_encode_rows(_p(codes), _p(scales), _p(x), rows, cols, d)
+    else:
+        impl.nn.turboquant_encode_rows(_p(codes), _p(scales), _p(x), rows, cols, d, _p(impl.over))
+        impl.wait()
+    return codes, scales
+
+
+def residual_tq(impl, q, kcodes, kscales, vcodes, vscales, qh, kvh, dh, length, d):
+    """attention_weights_tq + attention_residual_mix_tq: (m, l, acc) a head over `length` coded positions."""
+    p = np.zeros((qh, length), np.float32)
+    res = np.zeros((qh, dh + 2), np.float32)
+    if isinstance(impl, Port):
+        impl.lib.oracle_attention_residual_tq(_p(p), _p(res), _p(q), _p(kcodes), _p(kscales), _p(vcodes), _p(vscales), qh, kvh, dh, length, d)
+    else:
+        impl.nn.attention_weights_tq(_p(p), _p(res), _p(q), _p(kcodes), _p(kscales), qh, kvh, dh, length, d)
+        impl.nn.attention_residual_mix_tq(_p(res), _p(p), _p(vcodes), _p(vscales), qh, kvh, dh, length, d)
+        impl.wait()
+    return res
 
 
 _port = None

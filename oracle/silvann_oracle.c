@@ -332,3 +332,106 @@ void oracle_deltanet_conv_steps(uint16_t* o, uint16_t* s, const uint16_t* w, con
             s[c * 3] = s[c * 3 + 1]; s[c * 3 + 1] = s[c * 3 + 2]; s[c * 3 + 2] = xt;
         }
 }
+
+/* ---- the TurboQuant-coded tiers of the cache (kernels.cuh:2819-2986) ------------------------------------------------
+ * The level tables are the format's: Lloyd-Max levels of a standard normal, regenerated by
+ * silvann_b200/csrc/gen_tq_levels.py and pinned to the reference's own turboquant_decode door by tests/test_tq_levels.py. */
+static const uint16_t tq_levels[318] = {
+#include "../silvann_b200/csrc/tq_levels.inc"
+};
+static uint32_t tq_table_at(uint64_t d) { return d == 1 ? 0u : d == 2 ? 2u : d == 3 ? 6u : d == 4 ? 14u : d == 5 ? 30u : 62u; }
+static float tq_level(uint64_t d, uint32_t code) {                                     /* kernels.cuh:2650-2653 */
+    return d == 16 ? f16_to_f32((uint16_t)code) : f16_to_f32(tq_levels[tq_table_at(d) + code]);
+}
+static uint64_t tq_row_bytes(uint64_t d, uint64_t cols) { const uint64_t per = 16 / d; return ((cols + per - 1) / per) * 2; }   /* :2814-2817 */
+static float tq_element(const uint8_t* row, float scale, uint64_t d, uint64_t c) {     /* :2897-2901 */
+    const uint64_t per = 16 / d;
+    const uint32_t unit = (uint32_t)row[(c / per) * 2] | ((uint32_t)row[(c / per) * 2 + 1] << 8);
+    return scale * tq_level(d, (unit >> (uint32_t)(d * (c % per))) & ((1u << (uint32_t)d) - 1u));
+}
+/* turboquant_decode (kernels.cuh:1281-1298) for a matrix whose rooms hold every row */
+void oracle_turboquant_decode(uint16_t* out, const uint8_t* weights, const uint8_t* luts, uint64_t d, uint64_t rows, uint64_t cols) {
+    const uint64_t need = tq_row_bytes(d, cols);
+    for (uint64_t r = 0; r < rows; ++r) {
+        const float scale = d == 16 ? 1.0f : f16_to_f32((uint16_t)((uint32_t)luts[r * 2] | ((uint32_t)luts[r * 2 + 1] << 8)));
+        for (uint64_t c = 0; c < cols; ++c) out[r * cols + c] = f32_to_f16(tq_element(weights + r * need, scale, d, c), 0);
+    }
+}
+/* hadamard_blocks (kernels.cuh:2829-2855): R = H·(S ⊙ u) a block, or its transpose S ⊙ H·u; even and odd columns summed apart */
+void oracle_hadamard_blocks(uint16_t* out, const uint16_t* in, const uint16_t* sign, uint64_t n, uint64_t block, uint64_t inverse) {
+    const float norm = 1.0f / sqrtf((float)(uint32_t)block);
+    for (uint64_t i = 0; i < n; ++i) {
+        const uint64_t a = i - i % block, r = i - a;
+        float s0 = 0.0f, s1 = 0.0f;
+        for (uint64_t c = 0; c < block; c += 2) {
+            float v0 = f16_to_f32(in[a + c]), v1 = f16_to_f32(in[a + c + 1]);
+            if (!inverse) { v0 *= f16_to_f32(sign[c]); v1 *= f16_to_f32(sign[c + 1]); }
+            s0 += (__builtin_popcountll(r & c) & 1) ? -v0 : v0;
+            s1 += (__builtin_popcountll(r & (c + 1)) & 1) ? -v1 : v1;
+        }
+        float sum = (s0 + s1) * norm;
+        if (inverse) sum *= f16_to_f32(sign[r]);
+        out[i] = f32_to_f16(sum, 0);
+    }
+}
+/* turboquant_encode_rows (kernels.cuh:2857-2895): scale = fp16(clip · rms), a code = how many midpoints lie below x / scale */
+void oracle_turboquant_encode_rows(uint8_t* codes, uint16_t* scales, const uint16_t* x, uint64_t rows, uint64_t cols, uint64_t d) {
+    const uint64_t per = 16 / d, row_bytes = tq_row_bytes(d, cols), units = row_bytes / 2;
+    const float clip = d == 4 ? 2.7325895709952577f : 4.6036453045214065f;
+    for (uint64_t r = 0; r < rows; ++r) {
+        const uint16_t* xr = x + r * cols;
+        float part = 0.0f;
+        for (uint64_t c = 0; c < cols; ++c) { const float v = f16_to_f32(xr[c]); part += v * v; }
+        uint16_t sh = f32_to_f16(clip * sqrtf(part / (float)cols), 0);
+        float scale = f16_to_f32(sh);
+        const int dead = scale < 6.103515625e-05f;
+        if (dead) { sh = 0; scale = 0.0f; }
+        scales[r] = sh;
+        for (uint64_t u = 0; u < units; ++u) {
+            uint32_t unit = 0;
+            for (uint64_t s = 0; s < per; ++s) {
+                const uint64_t c = u * per + s;
+                if (c >= cols || dead) continue;
+                const float v = f16_to_f32(xr[c]) / scale;
+                uint32_t lo = 0, hi = (1u << (uint32_t)d) - 1u;
+                while (lo < hi) {
+                    const uint32_t mid = (lo + hi) >> 1;
+                    if (0.5f * (tq_level(d, mid) + tq_level(d, mid + 1)) < v) lo = mid + 1; else hi = mid;
+                }
+                unit |= lo << (uint32_t)(d * s);
+            }
+            codes[r * row_bytes + u * 2] = (uint8_t)(unit & 0xff);
+            codes[r * row_bytes + u * 2 + 1] = (uint8_t)(unit >> 8);
+        }
+    }
+}
+/* attention_weights_tq + attention_residual_mix_tq (kernels.cuh:2904-2986): the residual of one query over coded rows */
+void oracle_attention_residual_tq(float* p, float* res, const uint16_t* q, const uint8_t* kcodes, const uint16_t* kscales,
+                                  const uint8_t* vcodes, const uint16_t* vscales, uint64_t qh, uint64_t kvh, uint64_t dh, uint64_t len, uint64_t d) {
+    const uint64_t group = qh / kvh, row_bytes = tq_row_bytes(d, dh);
+    const float inv = 1.0f / sqrtf((float)(uint32_t)dh);
+    for (uint64_t h = 0; h < qh; ++h) {
+        const uint64_t g = h / group;
+        float* ph = p + h * len;
+        float top = -INFINITY;
+        for (uint64_t t = 0; t < len; ++t) {
+            const uint64_t row = t * kvh + g;
+            const float scale = f16_to_f32(kscales[row]);
+            float dot = 0.0f;
+            for (uint64_t e = 0; e < dh; ++e) dot += f16_to_f32(q[h * dh + e]) * tq_element(kcodes + row * row_bytes, scale, d, e);
+            ph[t] = dot * inv;
+            if (ph[t] > top) top = ph[t];
+        }
+        float sum = 0.0f;
+        for (uint64_t t = 0; t < len; ++t) { ph[t] = expf(ph[t] - top); sum += ph[t]; }
+        res[h * (dh + 2)] = top; res[h * (dh + 2) + 1] = sum;
+        for (uint64_t e = 0; e < dh; ++e) {
+            float acc = 0.0f;
+            for (uint64_t t = 0; t < len; ++t) {
+                const uint64_t row = t * kvh + g;
+                acc += ph[t] * tq_element(vcodes + row * row_bytes, f16_to_f32(vscales[row]), d, e);
+            }
+            res[h * (dh + 2) + 2 + e] = acc;
+        }
+    }
+}

@@ -442,6 +442,56 @@ static void d_vector_sum(sv_h16* out, sv_vector_parts parts, sv_u64 n, sv_fault*
     check("vector_sum", sv::vector_sum_launch(out, parts.at, parts.count, n, over, 0));
 }
 
+/* ---- the TurboQuant-coded tiers (tq.cu) ---- */
+static void d_turboquant_decode(sv_h16* out, const sv_u8* weights, sv_u64 w_room, const sv_u8* luts, sv_u64 l_room, sv_u64 d, sv_u64 rows,
+                                sv_u64 cols, sv_fault* over) {
+    flush();
+    if (!sv::tq_width_ok(d)) { launch_refused("turboquant_decode", cudaSuccess); return; }
+    if (rows * cols == 0) return;
+    check("turboquant_decode", sv::tq_decode_launch(out, weights, w_room, luts, l_room, d, rows, cols, over, 0));
+}
+static void d_hadamard_blocks(sv_h16* out, const sv_h16* in, const sv_h16* sign, sv_u64 n, sv_u64 block, sv_u64 inverse, sv_fault* over) {
+    flush();
+    if (block < 2 || block > 512 || (block & (block - 1)) != 0 || n % block != 0) { launch_refused("hadamard_blocks", cudaSuccess); return; }
+    if (n == 0) return;
+    check("hadamard_blocks", sv::hadamard_blocks_launch(out, in, sign, n, block, inverse, over, 0));
+}
+static void d_turboquant_encode_rows(sv_u8* codes, sv_h16* scales, const sv_h16* x, sv_u64 rows, sv_u64 cols, sv_u64 d, sv_fault* over) {
+    flush();
+    if ((d != 4 && d != 8) || cols == 0) { launch_refused("turboquant_encode_rows", cudaSuccess); return; }
+    if (rows == 0) return;
+    check("turboquant_encode_rows", sv::tq_encode_rows_launch(codes, scales, x, rows, cols, d, over, 0));
+}
+static bool tq_shape_ok(sv_u64 qh, sv_u64 kvh, sv_u64 dh, sv_u64 d) {
+    return kvh != 0 && qh % kvh == 0 && dh != 0 && dh <= 8192 && sv::tq_width_ok(d) && d != 16;
+}
+static void d_attention_weights_tq(float* p, float* res, const sv_h16* q, const sv_u8* codes, const sv_h16* scales, sv_u64 qh, sv_u64 kvh,
+                                   sv_u64 dh, sv_u64 length, sv_u64 d) {
+    flush();
+    if (!tq_shape_ok(qh, kvh, dh, d)) { launch_refused("attention_weights_tq", cudaSuccess); return; }
+    check("attention_weights_tq", sv::tq_weights_launch(p, res, q, codes, scales, qh, kvh, dh, length, d, 1, 0));
+}
+static void d_attention_residual_mix_tq(float* res, const float* p, const sv_u8* codes, const sv_h16* scales, sv_u64 qh, sv_u64 kvh, sv_u64 dh,
+                                        sv_u64 length, sv_u64 d) {
+    flush();
+    if (!tq_shape_ok(qh, kvh, dh, d)) { launch_refused("attention_residual_mix_tq", cudaSuccess); return; }
+    check("attention_residual_mix_tq", sv::tq_residual_mix_launch(res, p, codes, scales, qh, kvh, dh, length, d, 1, 0));
+}
+static void d_attention_weights_tq_rows(float* p, float* res, const sv_h16* q, const sv_u8* codes, const sv_h16* scales, sv_u64 qh, sv_u64 kvh,
+                                        sv_u64 dh, sv_u64 length, sv_u64 d, sv_u64 rows) {
+    flush();
+    if (!tq_shape_ok(qh, kvh, dh, d)) { launch_refused("attention_weights_tq_rows", cudaSuccess); return; }
+    if (rows == 0) return;
+    check("attention_weights_tq_rows", sv::tq_weights_launch(p, res, q, codes, scales, qh, kvh, dh, length, d, rows, 0));
+}
+static void d_attention_residual_mix_tq_rows(float* res, const float* p, const sv_u8* codes, const sv_h16* scales, sv_u64 qh, sv_u64 kvh,
+                                             sv_u64 dh, sv_u64 length, sv_u64 d, sv_u64 rows) {
+    flush();
+    if (!tq_shape_ok(qh, kvh, dh, d)) { launch_refused("attention_residual_mix_tq_rows", cudaSuccess); return; }
+    if (rows == 0) return;
+    check("attention_residual_mix_tq_rows", sv::tq_residual_mix_launch(res, p, codes, scales, qh, kvh, dh, length, d, rows, 0));
+}
+
 /* ================================================================================================================ */
 /* tables and the entry                                                                                             */
 
@@ -482,6 +532,13 @@ static void install_doors() {
     g_nn.deltanet_gates_rows = d_deltanet_gates_rows;
     g_nn.deltanet_conv_step = d_deltanet_conv_step;
     g_nn.deltanet_conv_steps = d_deltanet_conv_steps;
+    g_nn.turboquant_decode = d_turboquant_decode;
+    g_nn.hadamard_blocks = d_hadamard_blocks;
+    g_nn.turboquant_encode_rows = d_turboquant_encode_rows;
+    g_nn.attention_weights_tq = d_attention_weights_tq;
+    g_nn.attention_residual_mix_tq = d_attention_residual_mix_tq;
+    g_nn.attention_weights_tq_rows = d_attention_weights_tq_rows;
+    g_nn.attention_residual_mix_tq_rows = d_attention_residual_mix_tq_rows;
 }
 
 }  // namespace svf

@@ -91,6 +91,18 @@ cudaError_t deltanet_conv_steps_launch(uint16_t* o, uint16_t* s, const uint16_t*
                                        unsigned int* over, cudaStream_t st);
 cudaError_t vector_sum_launch(uint16_t* out, const uint64_t* parts, uint64_t count, uint64_t n, unsigned int* over,
                               cudaStream_t st);
+/* ---- the TurboQuant-coded tiers of the cache, as worded (tq.cu) ------------------------------------------------ */
+bool tq_width_ok(uint64_t d);
+cudaError_t tq_decode_launch(uint16_t* out, const uint8_t* weights, uint64_t w_room, const uint8_t* luts, uint64_t l_room, uint64_t d,
+                             uint64_t rows, uint64_t cols, unsigned int* over, cudaStream_t st);
+cudaError_t hadamard_blocks_launch(uint16_t* out, const uint16_t* in, const uint16_t* sign, uint64_t n, uint64_t block, uint64_t inverse,
+                                   unsigned int* over, cudaStream_t st);
+cudaError_t tq_encode_rows_launch(uint8_t* codes, uint16_t* scales, const uint16_t* x, uint64_t rows, uint64_t cols, uint64_t d,
+                                  unsigned int* over, cudaStream_t st);
+cudaError_t tq_weights_launch(float* p, float* res, const uint16_t* q, const uint8_t* codes, const uint16_t* scales, uint64_t qh, uint64_t kvh,
+                              uint64_t d_head, uint64_t length, uint64_t d, uint64_t rows, cudaStream_t st);
+cudaError_t tq_residual_mix_launch(float* res, const float* p, const uint8_t* codes, const uint16_t* scales, uint64_t qh, uint64_t kvh,
+                                   uint64_t d_head, uint64_t length, uint64_t d, uint64_t rows, cudaStream_t st);
 
 }  // namespace sv
 

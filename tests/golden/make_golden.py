@@ -91,6 +91,30 @@ def main():
     beta, g, o = oracle.deltanet_inputs(R, a, b, a_log, dt_bias, w, x, window, heads, rows, ch)
     out["dni_beta"], out["dni_g"], out["dni_o"], out["dni_window"] = beta, g, o, window
 
+    # the TurboQuant-coded tiers: the level tables, the rotation both ways, rows encoded at 8 and 4 bits, a residual over them
+    for d in (1, 2, 3, 4, 5, 8):
+        out[f"tq_levels_{d}"] = oracle.tq_levels(R, d)
+    dh = 128
+    sign = to_bits(np.where(rng.random(dh) < 0.5, -1.0, 1.0).astype(np.float32), 0)
+    x = bits((6, dh))
+    rot = oracle.hadamard_blocks(R, x, sign, dh, 0)
+    out["tq_sign"], out["tq_x"], out["tq_rot"], out["tq_unrot"] = sign, x, rot, oracle.hadamard_blocks(R, rot, sign, dh, 1)
+    rows = bits((40, dh))
+    rows[7] = 0                                              # a dead row: stored as zeros with a zero scale
+    rows[8] = to_bits(np.full(dh, 1e-6, np.float32), 0)      # below a normal half once scaled: dead as well
+    out["tq_rows"] = rows
+    for d in (4, 8):
+        out[f"tq_codes_{d}"], out[f"tq_scales_{d}"] = oracle.tq_encode_rows(R, rows, d)
+    qh, kvh, L = 8, 2, 50
+    q = bits((qh, dh))
+    kr, vr = bits((L * kvh, dh)), bits((L * kvh, dh))
+    out["tq_res_shape"] = np.array([qh, kvh, dh, L])
+    out["tq_res_q"], out["tq_res_k"], out["tq_res_v"] = q, kr, vr
+    for d in (4, 8):
+        kc, ks = oracle.tq_encode_rows(R, kr, d)
+        vc, vs = oracle.tq_encode_rows(R, vr, d)
+        out[f"tq_res_{d}"] = oracle.residual_tq(R, q, kc, ks, vc, vs, qh, kvh, dh, L, d)
+
     path = Path(__file__).with_name("reference_x86_avx2.npz")
     np.savez_compressed(path, **out)
     print(path, path.stat().st_size, "bytes,", len(out), "arrays")

@@ -1,6 +1,7 @@
 """The drop-in claim, tested with the reference's own engine: its evaluator and its nn verbs, unmodified, load a family
 by path (engine/src/pybind.cuh:399-406), boot on it and run `(nn__attention__decode ...)`, `(nn__attention__residual ...)`,
-`(nn__attention__merge ...)`, `(nn__attention__finish ...)`, `(nn__deltanet__step ...)` and `(nn__deltanet__conv_step ...)`
+`(nn__attention__merge ...)`, `(nn__attention__finish ...)`, `(nn__attention__residual_tq ...)`, `(nn__deltanet__step ...)` and
+`(nn__deltanet__conv_step ...)`
 (engine/src/packages/nn/cpu/opcodes/attention__abi.cuh:120-243, deltanet__abi.cuh:55-125).
 
 Without a GPU the family is the reference's own x86_avx2, and the answers must equal, bit for bit, the same doors called
@@ -122,6 +123,31 @@ def _deltanet_forms(s, reference, exact):
     s.release_buffers()
 
 
+def _tq_forms(s, reference, exact):
+    """`(nn__attention__residual_tq q kcodes kscales vcodes vscales scores res q_heads kv_heads head_dim d count)`
+    (attention__abi.cuh:245-272): the residual over a coded tier, finished with the plain verb."""
+    qh, kvh, dh, L = 16, 4, 128, 2000
+    rng = np.random.default_rng(47)
+    q = to_bits(rng.standard_normal((qh, dh)).astype(np.float32), FP16)
+    kr = to_bits(rng.standard_normal((L * kvh, dh)).astype(np.float32), FP16)
+    vr = to_bits(rng.standard_normal((L * kvh, dh)).astype(np.float32), FP16)
+    for d in (8, 4):
+        kc, ks = oracle.tq_encode_rows(reference, kr, d)
+        vc, vs = oracle.tq_encode_rows(reference, vr, d)
+        bufs = [s.buffer(a.nbytes, a.tobytes()) for a in (q, kc, ks, vc, vs)]
+        scores, res, out = s.buffer(2 * qh * L * 4), s.buffer(2 * qh * (dh + 2) * 4), s.buffer(qh * dh * 2)
+        s.run("nn__attention__residual_tq", *bufs, scores, res, qh, kvh, dh, d, L)
+        s.run("nn__attention__finish", res, out, qh, dh)
+        got = _u16(out.read(), (qh, dh))
+        want_res = oracle.residual_tq(reference, q, kc, ks, vc, vs, qh, kvh, dh, L, d)
+        want = reference.finish(want_res, qh, dh)
+        if exact:
+            assert np.array_equal(got, want)
+        else:
+            assert_close16(got, oracle.from_bits(want, FP16), FP16, f"residual over a {d}-bit tier through the engine")
+        s.release_buffers()
+
+
 @pytest.fixture(scope="module")
 def cpu_session(reference):
     if reference is None or engine_driver.engine_module() is None:
@@ -134,6 +160,7 @@ def cpu_session(reference):
 def test_engine_runs_reference_family(cpu_session, reference):
     _attention_forms(cpu_session, reference, exact=True)
     _deltanet_forms(cpu_session, reference, exact=True)
+    _tq_forms(cpu_session, reference, exact=True)
 
 
 @pytest.fixture(scope="module")
@@ -158,5 +185,6 @@ def test_engine_runs_this_family(gpu_session, reference):
     _deltanet_forms(gpu_session, reference, exact=False)
     after = ext.counters()
     assert after["deltanet"] - mid["deltanet"] == 2
-    assert after["refused"] == before["refused"]
+    _tq_forms(gpu_session, reference, exact=False)
+    assert ext.counters()["refused"] == before["refused"]
     assert ext.device_status() == 0

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 import oracle
-from oracle import from_bits, to_bits
+from oracle import FP16, from_bits, to_bits
 
 DEC = ["dec_a", "dec_b", "dec_c", "dec_d"]
 
@@ -136,3 +136,40 @@ def test_row_residuals_golden_stand_for_the_causal_answer(golden, port):
     res = golden["rr_res"]
     _, want = port.prefill(golden["rr_q"], golden["rr_k"], golden["rr_v"], qh, kvh, d, first, rows)
     np.testing.assert_allclose(res[:, :, 2:] / res[:, :, 1:2], want, rtol=0, atol=1e-5)
+
+
+# ---- the TurboQuant-coded tiers ------------------------------------------------------------------------------------
+
+def test_port_rotation_both_ways(golden, port):
+    sign, x = golden["tq_sign"], golden["tq_x"]
+    rot = oracle.hadamard_blocks(port, x, sign, 128, 0)
+    assert np.array_equal(rot, golden["tq_rot"])
+    assert np.array_equal(oracle.hadamard_blocks(port, rot, sign, 128, 1), golden["tq_unrot"])
+    # R^T R = I up to the two roundings to 16 bits
+    back = oracle.from_bits(golden["tq_unrot"], FP16)
+    assert np.abs(back - oracle.from_bits(x, FP16)).max() < 4e-3
+
+
+@pytest.mark.parametrize("d", [4, 8])
+def test_port_encode_rows(golden, port, d):
+    codes, scales = oracle.tq_encode_rows(port, golden["tq_rows"], d)
+    assert np.array_equal(scales, golden[f"tq_scales_{d}"])
+    assert np.array_equal(codes, golden[f"tq_codes_{d}"])
+    assert scales[7] == 0 and scales[8] == 0 and not codes[7].any() and not codes[8].any(), "dead rows are stored as zeros"
+    # and what was stored is the input to within the code's step: decode and compare
+    x = oracle.from_bits(golden["tq_rows"], FP16)
+    back = oracle.from_bits(oracle.tq_decode(port, codes, scales.view(np.uint8).copy(), d, *x.shape), FP16)
+    live = np.ones(len(x), bool); live[[7, 8]] = False
+    err = np.sqrt(((back[live] - x[live]) ** 2).mean(axis=1) / (x[live] ** 2).mean(axis=1))      # rms error over rms, a row
+    assert err.max() < (0.15 if d == 4 else 0.02), err.max()
+
+
+@pytest.mark.parametrize("d", [4, 8])
+def test_port_residual_over_coded_rows(golden, port, d):
+    qh, kvh, dh, L = (int(v) for v in golden["tq_res_shape"])
+    kc, ks = oracle.tq_encode_rows(port, golden["tq_res_k"], d)
+    vc, vs = oracle.tq_encode_rows(port, golden["tq_res_v"], d)
+    res = oracle.residual_tq(port, golden["tq_res_q"], kc, ks, vc, vs, qh, kvh, dh, L, d)
+    want = golden[f"tq_res_{d}"]
+    assert np.allclose(res[:, 0], want[:, 0], rtol=0, atol=2e-5) and np.allclose(res[:, 1], want[:, 1], rtol=2e-5)
+    assert np.abs(res[:, 2:] - want[:, 2:]).max() <= 2e-5 * np.abs(want[:, 2:]).max() + 1e-6
