@@ -101,6 +101,11 @@ cudaError_t tq_encode_rows_launch(uint8_t* codes, uint16_t* scales, const uint16
                                   unsigned int* over, cudaStream_t st);
 cudaError_t tq_weights_launch(float* p, float* res, const uint16_t* q, const uint8_t* codes, const uint16_t* scales, uint64_t qh, uint64_t kvh,
                               uint64_t d_head, uint64_t length, uint64_t d, uint64_t rows, cudaStream_t st);
+/* the pair weights_tq + residual_mix_tq as one kernel, codes expanded in flight (tq_decode.cu) */
+bool tq_attend_fits(const void* q, const void* kcodes, const void* kscales, const void* vcodes, const void* vscales, uint64_t qh, uint64_t kvh,
+                    uint64_t dh, uint64_t length, uint64_t d);
+cudaError_t tq_attend_launch(float* res, const uint16_t* q, const uint8_t* kcodes, const uint16_t* kscales, const uint8_t* vcodes,
+                             const uint16_t* vscales, uint64_t qh, uint64_t kvh, uint64_t dh, uint64_t length, uint64_t d, cudaStream_t st);
 cudaError_t tq_residual_mix_launch(float* res, const float* p, const uint8_t* codes, const uint16_t* scales, uint64_t qh, uint64_t kvh,
                                    uint64_t d_head, uint64_t length, uint64_t d, uint64_t rows, cudaStream_t st);
 

@@ -100,7 +100,8 @@ def test_residual_over_coded_rows_as_the_doors_word_it(cuda, fam, golden, port, 
     np.testing.assert_allclose(g3[1, :, 2:] / g3[1, :, 1:2], half[:, 2:] / half[:, 1:2], rtol=0, atol=2e-3)
 
 
-@pytest.mark.parametrize("d,dh,qh,kvh,L", [(8, 128, 16, 4, 3000), (4, 128, 16, 4, 5000), (4, 256, 16, 2, 2500), (8, 256, 8, 2, 1111), (4, 64, 8, 8, 700)])
+@pytest.mark.parametrize("d,dh,qh,kvh,L", [(8, 128, 16, 4, 3000), (4, 128, 16, 4, 5000), (4, 256, 16, 2, 2500), (8, 256, 8, 2, 1111), (4, 64, 8, 8, 700),
+                                           (4, 128, 32, 2, 4000), (8, 128, 32, 2, 129), (8, 256, 24, 2, 40000), (4, 256, 3, 1, 7), (8, 128, 4, 4, 128)])
 def test_a_tier_at_size_against_the_reference_run_here(cuda, fam, reference, port, d, dh, qh, kvh, L):
     """Rows rotated, encoded ON THE CARD, attended on the card; the oracle attends the card's codes on the host."""
     impl = reference if reference is not None else port
@@ -122,7 +123,9 @@ def test_a_tier_at_size_against_the_reference_run_here(cuda, fam, reference, por
     fam.nn.attention_residual_mix_tq(res.data_ptr(), p.data_ptr(), vc.data_ptr(), vs.data_ptr(), qh, kvh, dh, L, d)
     fam.nn.attention_finish(o.data_ptr(), res.data_ptr(), qh, dh, None)
     assert fam.sys.compute_completed()
-    assert ext.counters()["refused"] == before["refused"] and ext.device_status() == 0
+    after = ext.counters()
+    assert after["refused"] == before["refused"] and ext.device_status() == 0
+    assert after["fused_residual"] - before["fused_residual"] == (1 if dh in (128, 256) else 0), "the pair is one kernel at head_dim 128 and 256"
     want = oracle.residual_tq(impl, q, kc.cpu().numpy(), host_bits(ks), vc.cpu().numpy(), host_bits(vs), qh, kvh, dh, L, d)
     got = res.cpu().numpy()
     np.testing.assert_allclose(got[:, 2:] / got[:, 1:2], want[:, 2:] / want[:, 1:2], rtol=0, atol=2e-3)
