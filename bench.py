@@ -386,6 +386,35 @@ def other_workloads(torch, fam, pk, steps, warmup):
                                                  "note": "262,144 positions, 32q/4kv, d128, bf16, all KV in HBM"}
     del k, v
 
+    # a TurboQuant-coded tier (the reference's default cache for Qwen): one query over 262,144 coded positions through the
+    # attention_weights_tq + attention_residual_mix_tq door pair (one fused launch), two distinct tiers alternated
+    for dh, tqh, tkvh in ((128, 32, 4), (256, 16, 2)):
+        for width in (8, 4):
+            Lt = 262144
+            rb = dh * width // 8
+            kc = torch.randint(0, 256, (2, Lt * tkvh, rb), generator=gen, device="cuda", dtype=torch.uint8)
+            vc = torch.randint(0, 256, (2, Lt * tkvh, rb), generator=gen, device="cuda", dtype=torch.uint8)
+            ks = (torch.rand((2, Lt * tkvh), generator=gen, device="cuda") * 0.5 + 0.75).to(torch.float16)
+            vs = (torch.rand((2, Lt * tkvh), generator=gen, device="cuda") * 0.5 + 0.75).to(torch.float16)
+            tq_q = torch.randn((tqh, dh), generator=gen, device="cuda", dtype=torch.float16) * 0.25
+            tp = torch.zeros((tqh, 8), device="cuda", dtype=torch.float32)        # never written by the fused pair
+            tres = torch.zeros((tqh, dh + 2), device="cuda", dtype=torch.float32)
+            tstate = {"i": 0}
+
+            def tq_pair():
+                i = tstate["i"] = 1 - tstate["i"]
+                fam.nn.attention_weights_tq(tp.data_ptr(), tres.data_ptr(), tq_q.data_ptr(), kc[i].data_ptr(), ks[i].data_ptr(), tqh, tkvh, dh, Lt, width)
+                fam.nn.attention_residual_mix_tq(tres.data_ptr(), tp.data_ptr(), vc[i].data_ptr(), vs[i].data_ptr(), tqh, tkvh, dh, Lt, width)
+            before = ext.counters()["fused_residual"]
+            ms = time_loop(torch, tq_pair, max(steps, 20), max(warmup, 3))
+            assert ext.counters()["fused_residual"] > before, "the coded pair did not take the fused kernel"
+            nbytes = 2 * Lt * tkvh * (rb + 2)
+            out[f"tq{width}_tier_d{dh}"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms, "frac_hbm": nbytes / ms / 1e6 / hbm,
+                                            "positions_per_s": Lt / ms * 1e3,
+                                            "note": f"262,144 positions coded at {width} bits, {tqh}q/{tkvh}kv heads of {dh}: {nbytes / 1e6:.0f} MB of codes and scales a call"}
+            del kc, vc, ks, vs
+    torch.cuda.empty_cache()
+
     # configuration 5: recurrent decode steps (batched so that state traffic is real) and the prompt
     heads, d = 32, 128
     for seqs, tag in ((1, "config5_deltanet_decode_1seq"), (64, "config5_deltanet_decode_64seq")):
@@ -694,6 +723,24 @@ def run_case(args):
         # configuration 1 as the card sees it: one CUDA graph of 64 decode launches, a distinct cache each (1.07 GB)
         fn, work, unit = config1_graph(torch, ext, gen)
         work *= 64
+    elif name in ("tq8_small", "tq4_small"):
+        # a coded tier of 262,144 positions, 32q/4kv heads of 128, through the door pair (one fused launch): 273 / 138 MB
+        width, dh, tqh, tkvh, Lt = (8 if name == "tq8_small" else 4), 128, 32, 4, 262144
+        rb = dh * width // 8
+        kc = torch.randint(0, 256, (2, Lt * tkvh, rb), generator=gen, device="cuda", dtype=torch.uint8)
+        vc = torch.randint(0, 256, (2, Lt * tkvh, rb), generator=gen, device="cuda", dtype=torch.uint8)
+        ks = (torch.rand((2, Lt * tkvh), generator=gen, device="cuda") * 0.5 + 0.75).to(torch.float16)
+        vs = (torch.rand((2, Lt * tkvh), generator=gen, device="cuda") * 0.5 + 0.75).to(torch.float16)
+        tq_q = torch.randn((tqh, dh), generator=gen, device="cuda", dtype=torch.float16) * 0.25
+        tp = torch.zeros((tqh, 8), device="cuda", dtype=torch.float32)
+        tres = torch.zeros((tqh, dh + 2), device="cuda", dtype=torch.float32)
+        tstate = {"i": 0}
+
+        def fn():
+            i = tstate["i"] = 1 - tstate["i"]
+            fam.nn.attention_weights_tq(tp.data_ptr(), tres.data_ptr(), tq_q.data_ptr(), kc[i].data_ptr(), ks[i].data_ptr(), tqh, tkvh, dh, Lt, width)
+            fam.nn.attention_residual_mix_tq(tres.data_ptr(), tp.data_ptr(), vc[i].data_ptr(), vs[i].data_ptr(), tqh, tkvh, dh, Lt, width)
+        work, unit = 2 * Lt * tkvh * (rb + 2), "bytes"
     elif name == "deltanet_64":
         heads, d, seqs = 32, 128, 64
         S = torch.zeros((seqs, heads, d, d), device="cuda", dtype=torch.float32)
@@ -738,7 +785,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the secondary configurations (faster; used under profilers)")
-    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, decode_cfg1, decode_cfg1_graph, deltanet_64, deltanet_prefill, prefill_small)")
+    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, decode_cfg1, decode_cfg1_graph, tq8_small, tq4_small, deltanet_64, deltanet_prefill, prefill_small)")
     args = ap.parse_args()
     if args.case:
         run_case(args)

@@ -42,7 +42,7 @@ template <int DH, int W> struct TqCfg {
     static constexpr int TILE = BT * RB;                  /* a K (or V) tile */
     static constexpr int STAGE = 2 * TILE;
     static constexpr int STAGES = (128 * 1024) / STAGE > 8 ? 8 : (128 * 1024) / STAGE;
-    static constexpr int LUT_BYTES = 256 * 32 * 4;
+    static constexpr int LUT_BYTES = 256 * 256;             /* 256 entries, each 32 copies (a bank each) in a 256-byte slot */
     static constexpr int QB = RB / 4;                     /* bytes of a key row a lane reads (its quarter) */
     static constexpr int EB = RB / 8;                     /* bytes of a value row a lane reads (its eighth) */
     static constexpr int KS = DH / 16;                    /* k-steps of the score product = m-tiles of the value product */
@@ -76,11 +76,14 @@ __device__ __forceinline__ uint4 lds128(uint32_t a) {
 __device__ __forceinline__ uint2 lds64(uint32_t a) {
     uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v;
 }
-/* the table entry of byte `idx` of word `w` for this lane: lut_lane + 128 * byte */
+/* The table entry of byte `idx` of word `w` for this lane.  An entry is 256 bytes apart from the next (its 32 copies, one
+ * a bank, then padding), so the byte moved into bits 8..15 by ONE byte-permute is the entry's offset.  Not volatile: the
+ * table never changes while tiles are walked, and the address depends on code words that were read after the tile's
+ * barrier, so the compiler may schedule the lookups of several MMA steps together but never ahead of the data. */
 __device__ __forceinline__ uint32_t lut_at(uint32_t lut_lane, uint32_t w, int idx) {
     uint32_t v;
-    const uint32_t off = idx == 0 ? (w << 7) & 0x7f80u : ((w >> (8 * idx - 7)) & 0x7f80u);
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(lut_lane + off));
+    const uint32_t off = __byte_perm(w, 0u, 0x4404u | ((uint32_t)idx << 4));
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(lut_lane + off));
     return v;
 }
 __device__ __forceinline__ uint32_t lo_lo(uint32_t a, uint32_t b) { return __byte_perm(a, b, 0x5410); }   /* (a.lo, b.lo) */
@@ -119,14 +122,14 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         *abort_flag = 0u;
         mbar_fence_init();
     }
-    /* the level table, every entry once a bank: [byte][bank].  8 bits: the byte's level in both halves.  4 bits: the
+    /* the level table, every entry once a bank: [byte][bank], 256 bytes an entry.  8 bits: the byte's level in both halves.  4 bits: the
      * low nibble's level in the low half, the high nibble's in the high half. */
     for (int i = tid; i < 256 * 32; i += THREADS) {
         const int b = i >> 5;
         uint32_t e;
         if (W == 8) { const uint32_t l = g_tq_levels_fused[62 + b]; e = l | (l << 16); }
         else e = (uint32_t)g_tq_levels_fused[14 + (b & 15)] | ((uint32_t)g_tq_levels_fused[14 + (b >> 4)] << 16);
-        lut[i] = e;
+        lut[b * 64 + (i & 31)] = e;
     }
     __syncthreads();
 
@@ -176,14 +179,23 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         const uint32_t lut_lane = smem_u32(lut) + lane * 4;
         const int rowA = warp * 16 + g8, rowB = rowA + 8;          /* this lane's score rows (positions of the tile) */
         const int pv0 = warp * 16 + 2 * t4;                        /* its value positions: pv0, pv0+1, pv0+8, pv0+9 */
+        /* The rows' scales run one tile ahead in registers: they are single halves scattered 2·kv_heads bytes apart, a trip
+         * to L2 or HBM each, and nothing else in the loop waits that long once the ring is full. */
+        uint16_t n_ksA = 0, n_ksB = 0, n_vsA = 0, n_vsB = 0;
+        auto fetch_scales = [&](int tile_it) {
+            const int p0 = (tile_begin + tile_it) * BT;
+            const bool a = p0 + rowA < len, b = p0 + rowB < len;
+            const size_t at_a = (size_t)(p0 + rowA) * P.kv_heads + kvh, at_b = (size_t)(p0 + rowB) * P.kv_heads + kvh;
+            n_ksA = a ? P.kscales[at_a] : (uint16_t)0; n_ksB = b ? P.kscales[at_b] : (uint16_t)0;
+            n_vsA = a ? P.vscales[at_a] : (uint16_t)0; n_vsB = b ? P.vscales[at_b] : (uint16_t)0;
+        };
+        if (nt > 0) fetch_scales(0);
         for (int it = 0; it < nt; ++it) {
             const int s = it % Cfg::STAGES;
             const int pos0 = (tile_begin + it) * BT;
-            /* the rows' scales, asked for before the wait for the tile */
             const bool vA = pos0 + rowA < len, vB = pos0 + rowB < len;
-            const size_t sa_at = (size_t)(pos0 + rowA) * P.kv_heads + kvh, sb_at = (size_t)(pos0 + rowB) * P.kv_heads + kvh;
-            const uint16_t ksA = vA ? P.kscales[sa_at] : (uint16_t)0, ksB = vB ? P.kscales[sb_at] : (uint16_t)0;
-            const uint16_t vsA = vA ? P.vscales[sa_at] : (uint16_t)0, vsB = vB ? P.vscales[sb_at] : (uint16_t)0;
+            const uint16_t ksA = n_ksA, ksB = n_ksB, vsA = n_vsA, vsB = n_vsB;
+            if (it + 1 < nt) fetch_scales(it + 1);
             if (!mbar_wait(&full[s], (it / Cfg::STAGES) & 1, abort_flag, P.status)) break;
             const uint32_t kt = smem_u32(stage_base + s * Cfg::STAGE), vt = kt + Cfg::TILE;
 
