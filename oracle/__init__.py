@@ -82,6 +82,13 @@ class Port:
             "oracle_attention_mix_rows": [vp, u64, vp, u64, vp, u64, vp, u64, u64, u64, u64, i32, vp],
             "oracle_deltanet_gates_rows": [vp, vp, vp, vp, vp, vp, u64, u64],
             "oracle_deltanet_conv_steps": [vp, vp, vp, vp, u64, u64],
+            "oracle_vector_add": [vp, vp, vp, u64],
+            "oracle_vector_copy_rows": [vp, u64, vp, u64, u64, u64],
+            "oracle_rmsnorm_rows": [vp, vp, vp, u64, u64, u64, u64, C.c_float],
+            "oracle_rope_rows": [vp, vp, vp, u64, u64, u64, u64, u64],
+            "oracle_rope_interleaved": [vp, vp, vp, u64, u64, u64, u64],
+            "oracle_rope_angles": [vp, u64, vp, C.c_float, u64, u64, u64, i32],
+            "oracle_attention_gate_rows": [vp, vp, vp, u64, u64],
             "oracle_turboquant_decode": [vp, vp, vp, u64, u64, u64],
             "oracle_hadamard_blocks": [vp, vp, vp, u64, u64, u64],
             "oracle_turboquant_encode_rows": [vp, vp, vp, u64, u64, u64],

@@ -435,3 +435,59 @@ void oracle_attention_residual_tq(float* p, float* res, const uint16_t* q, const
         }
     }
 }
+
+/* ---- the small steps either side of attention in a mixer ------------------------------------------------------------ */
+void oracle_vector_add(uint16_t* z, const uint16_t* x, const uint16_t* y, uint64_t n) {                  /* kernels.cuh:103-113 */
+    for (uint64_t i = 0; i < n; ++i) z[i] = f32_to_f16(f16_to_f32(x[i]) + f16_to_f32(y[i]), 0);
+}
+void oracle_vector_copy_rows(uint16_t* out, uint64_t out_row, const uint16_t* in, uint64_t in_row, uint64_t width, uint64_t rows) {   /* :3874-3881 */
+    for (uint64_t t = 0; t < rows; ++t) for (uint64_t j = 0; j < width; ++j) out[t * out_row + j] = in[t * in_row + j];
+}
+void oracle_rmsnorm_rows(uint16_t* o, const uint16_t* x, const uint16_t* w, uint64_t n, uint64_t rows, uint64_t x_stride, uint64_t o_stride, float eps) {
+    for (uint64_t r = 0; r < rows; ++r) {                                                                  /* :158-176, 1700-1705 */
+        const uint16_t* xr = x + r * x_stride;
+        float part = 0.0f;
+        for (uint64_t i = 0; i < n; ++i) { const float v = f16_to_f32(xr[i]); part += v * v; }
+        const float scale = 1.0f / sqrtf(part / (float)n + eps);
+        for (uint64_t i = 0; i < n; ++i) o[r * o_stride + i] = f32_to_f16((f16_to_f32(xr[i]) * scale) * f16_to_f32(w[i]), 0);
+    }
+}
+void oracle_rope_rows(uint16_t* o, const uint16_t* x, const float* cs, uint64_t rows, uint64_t heads, uint64_t head_stride, uint64_t row_stride, uint64_t rot) {
+    const uint64_t pairs = rot / 2;                                                                        /* :1710-1727; rows = 1 is :843-858 */
+    for (uint64_t r = 0; r < rows; ++r) for (uint64_t e = 0; e < heads; ++e) for (uint64_t k = 0; k < pairs; ++k) {
+        const uint64_t at = r * row_stride + e * head_stride + k;
+        const float a = f16_to_f32(x[at]), b = f16_to_f32(x[at + pairs]), c = cs[r * rot + k], s = cs[r * rot + pairs + k];
+        o[at] = f32_to_f16(a * c - b * s, 0); o[at + pairs] = f32_to_f16(b * c + a * s, 0);
+    }
+}
+void oracle_rope_interleaved(uint16_t* o, const uint16_t* x, const float* cs, uint64_t heads, uint64_t head_stride, uint64_t rot, uint64_t inverse) {
+    const uint64_t pairs = rot / 2;                                                                        /* :1733-1749 */
+    for (uint64_t h = 0; h < heads; ++h) for (uint64_t k = 0; k < pairs; ++k) {
+        const uint64_t at = h * head_stride + 2 * k;
+        const float a = f16_to_f32(x[at]), b = f16_to_f32(x[at + 1]), c = cs[k], sn = inverse ? -cs[pairs + k] : cs[pairs + k];
+        o[at] = f32_to_f16(a * c - b * sn, 0); o[at + 1] = f32_to_f16(b * c + a * sn, 0);
+    }
+}
+/* mode 0: rows from position `first` (:871-886, 1754-1767) · 1: M-RoPE (:1770-1784) · 2: axial (:1789-1803) */
+void oracle_rope_angles(float* cs, uint64_t first, const uint32_t* positions, float theta, uint64_t head_dim, uint64_t rows, uint64_t sections, int mode) {
+    const uint64_t pairs = head_dim / 2, per_axis = pairs / 2;
+    const float r = expf(-2.0f / (float)(uint32_t)(mode == 2 ? pairs : head_dim) * logf(theta));
+    for (uint64_t row = 0; row < rows; ++row) for (uint64_t k = 0; k < pairs; ++k) {
+        uint64_t steps = k, pos = first + row;
+        if (mode == 1) {
+            const uint64_t third = k % 3, by_row = sections & 0xFFFF, by_column = (sections >> 16) & 0xFFFF;
+            pos = positions[3 * row + ((third == 1 && k < 3 * by_row) ? 1 : (third == 2 && k < 3 * by_column) ? 2 : 0)];
+        } else if (mode == 2) { const uint64_t axis = k < per_axis ? 0 : 1; steps = k - axis * per_axis; pos = positions[2 * row + axis]; }
+        float frequency = 1.0f;
+        for (uint64_t m = 0; m < steps; ++m) frequency *= r;
+        const float angle = (float)pos * frequency;
+        cs[row * head_dim + k] = cosf(angle); cs[row * head_dim + pairs + k] = sinf(angle);
+    }
+}
+void oracle_attention_gate_rows(uint16_t* o, const uint16_t* att, const uint16_t* qg, uint64_t heads, uint64_t head_dim) {   /* :2062-2076 */
+    for (uint64_t i = 0; i < heads * head_dim; ++i) {
+        const uint64_t h = i / head_dim, e = i - h * head_dim;
+        const uint16_t gate = f32_to_f16(1.0f / (1.0f + expf(-f16_to_f32(qg[h * 2 * head_dim + head_dim + e]))), 0);
+        o[i] = f32_to_f16(f16_to_f32(att[i]) * f16_to_f32(gate), 0);
+    }
+}

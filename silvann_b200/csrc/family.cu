@@ -444,6 +444,60 @@ static void d_vector_sum(sv_h16* out, sv_vector_parts parts, sv_u64 n, sv_fault*
     check("vector_sum", sv::vector_sum_launch(out, parts.at, parts.count, n, over, 0));
 }
 
+/* ---- the small steps either side of attention (mixer_doors.cu) ---- */
+static void d_vector_add(sv_h16* z, const sv_h16* x, const sv_h16* y, sv_u64 n, sv_fault* over) {
+    flush();
+    if (n) check("vector_add", sv::vector_add_launch(z, x, y, n, over, 0));
+}
+static void d_vector_copy(sv_h16* out, const sv_h16* in, sv_u64 n) {
+    flush();
+    if (n) check("vector_copy", sv::vector_copy_rows_launch(out, n, in, n, n, 1, 0));
+}
+static void d_vector_copy_rows(sv_h16* out, sv_u64 out_row, const sv_h16* in, sv_u64 in_row, sv_u64 width, sv_u64 rows) {
+    flush();
+    if (width * rows) check("vector_copy_rows", sv::vector_copy_rows_launch(out, out_row, in, in_row, width, rows, 0));
+}
+static void d_rmsnorm(sv_h16* o, const sv_h16* x, const sv_h16* w, sv_u64 n, float eps, sv_fault* over) {
+    flush();
+    if (n) check("rmsnorm", sv::rmsnorm_rows_launch(o, x, w, n, 1, n, n, eps, over, 0));
+}
+static void d_rmsnorm_rows(sv_h16* o, const sv_h16* x, const sv_h16* w, sv_u64 n, sv_u64 rows, sv_u64 x_stride, sv_u64 o_stride, float eps, sv_fault* over) {
+    flush();
+    if (n * rows) check("rmsnorm_rows", sv::rmsnorm_rows_launch(o, x, w, n, rows, x_stride, o_stride, eps, over, 0));
+}
+static void d_rope(sv_h16* o, const sv_h16* x, const float* cs, sv_u64 heads, sv_u64 head_dim, sv_fault* over) {
+    flush();
+    if (heads * (head_dim / 2)) check("rope", sv::rope_rows_launch(o, x, cs, 1, heads, head_dim, 0, head_dim, over, 0));
+}
+static void d_rope_rows(sv_h16* o, const sv_h16* x, const float* cs, sv_u64 rows, sv_u64 heads, sv_u64 head_stride, sv_u64 row_stride, sv_u64 rot, sv_fault* over) {
+    flush();
+    if (rows * heads * (rot / 2)) check("rope_rows", sv::rope_rows_launch(o, x, cs, rows, heads, head_stride, row_stride, rot, over, 0));
+}
+static void d_rope_interleaved(sv_h16* o, const sv_h16* x, const float* cs, sv_u64 heads, sv_u64 head_stride, sv_u64 rot, sv_u64 inverse, sv_fault* over) {
+    flush();
+    if (heads * (rot / 2)) check("rope_interleaved", sv::rope_interleaved_launch(o, x, cs, heads, head_stride, rot, inverse, over, 0));
+}
+static void d_rope_angles(float* cs, sv_u64 position, float theta, sv_u64 head_dim) {
+    flush();
+    if (head_dim / 2) check("rope_angles", sv::rope_angles_launch(cs, position, nullptr, theta, head_dim, 1, 0, 0, 0));
+}
+static void d_rope_angles_rows(float* cs, sv_u64 first, float theta, sv_u64 head_dim, sv_u64 rows) {
+    flush();
+    if (rows * (head_dim / 2)) check("rope_angles_rows", sv::rope_angles_launch(cs, first, nullptr, theta, head_dim, rows, 0, 0, 0));
+}
+static void d_rope_angles_mrope_rows(float* cs, const sv_u32* positions, float theta, sv_u64 head_dim, sv_u64 rows, sv_u64 sections) {
+    flush();
+    if (rows * (head_dim / 2)) check("rope_angles_mrope_rows", sv::rope_angles_launch(cs, 0, positions, theta, head_dim, rows, sections, 1, 0));
+}
+static void d_rope_angles_axial_rows(float* cs, const sv_u32* positions, float theta, sv_u64 head_dim, sv_u64 rows) {
+    flush();
+    if (rows * (head_dim / 2)) check("rope_angles_axial_rows", sv::rope_angles_launch(cs, 0, positions, theta, head_dim, rows, 0, 2, 0));
+}
+static void d_attention_gate_rows(sv_h16* o, const sv_h16* att, const sv_h16* qg, sv_u64 heads, sv_u64 head_dim, sv_fault* over) {
+    flush();
+    if (heads * head_dim) check("attention_gate_rows", sv::attention_gate_rows_launch(o, att, qg, heads, head_dim, over, 0));
+}
+
 /* ---- the TurboQuant-coded tiers (tq.cu) ---- */
 static void d_turboquant_decode(sv_h16* out, const sv_u8* weights, sv_u64 w_room, const sv_u8* luts, sv_u64 l_room, sv_u64 d, sv_u64 rows,
                                 sv_u64 cols, sv_fault* over) {
@@ -557,6 +611,19 @@ static void install_doors() {
     g_nn.deltanet_gates_rows = d_deltanet_gates_rows;
     g_nn.deltanet_conv_step = d_deltanet_conv_step;
     g_nn.deltanet_conv_steps = d_deltanet_conv_steps;
+    g_nn.vector_add = d_vector_add;
+    g_nn.vector_copy = d_vector_copy;
+    g_nn.vector_copy_rows = d_vector_copy_rows;
+    g_nn.rmsnorm = d_rmsnorm;
+    g_nn.rmsnorm_rows = d_rmsnorm_rows;
+    g_nn.rope = d_rope;
+    g_nn.rope_rows = d_rope_rows;
+    g_nn.rope_interleaved = d_rope_interleaved;
+    g_nn.rope_angles = d_rope_angles;
+    g_nn.rope_angles_rows = d_rope_angles_rows;
+    g_nn.rope_angles_mrope_rows = d_rope_angles_mrope_rows;
+    g_nn.rope_angles_axial_rows = d_rope_angles_axial_rows;
+    g_nn.attention_gate_rows = d_attention_gate_rows;
     g_nn.turboquant_decode = d_turboquant_decode;
     g_nn.hadamard_blocks = d_hadamard_blocks;
     g_nn.turboquant_encode_rows = d_turboquant_encode_rows;

@@ -91,6 +91,19 @@ cudaError_t deltanet_conv_steps_launch(uint16_t* o, uint16_t* s, const uint16_t*
                                        unsigned int* over, cudaStream_t st);
 cudaError_t vector_sum_launch(uint16_t* out, const uint64_t* parts, uint64_t count, uint64_t n, unsigned int* over,
                               cudaStream_t st);
+/* ---- the small steps either side of attention in a mixer (mixer_doors.cu) ------------------------------------- */
+cudaError_t vector_add_launch(uint16_t* z, const uint16_t* x, const uint16_t* y, uint64_t n, unsigned int* over, cudaStream_t st);
+cudaError_t vector_copy_rows_launch(uint16_t* out, uint64_t out_row, const uint16_t* in, uint64_t in_row, uint64_t width, uint64_t rows, cudaStream_t st);
+cudaError_t rmsnorm_rows_launch(uint16_t* o, const uint16_t* x, const uint16_t* w, uint64_t n, uint64_t rows, uint64_t x_stride, uint64_t o_stride,
+                                float eps, unsigned int* over, cudaStream_t st);
+cudaError_t rope_rows_launch(uint16_t* o, const uint16_t* x, const float* cs, uint64_t rows, uint64_t heads, uint64_t head_stride, uint64_t row_stride,
+                             uint64_t rot, unsigned int* over, cudaStream_t st);
+cudaError_t rope_interleaved_launch(uint16_t* o, const uint16_t* x, const float* cs, uint64_t heads, uint64_t head_stride, uint64_t rot, uint64_t inverse,
+                                    unsigned int* over, cudaStream_t st);
+cudaError_t rope_angles_launch(float* cs, uint64_t first, const uint32_t* positions, float theta, uint64_t head_dim, uint64_t rows, uint64_t sections,
+                               int mode /*0 plain, 1 M-RoPE, 2 axial*/, cudaStream_t st);
+cudaError_t attention_gate_rows_launch(uint16_t* o, const uint16_t* att, const uint16_t* qg, uint64_t heads, uint64_t head_dim, unsigned int* over,
+                                       cudaStream_t st);
 /* ---- the TurboQuant-coded tiers of the cache, as worded (tq.cu) ------------------------------------------------ */
 bool tq_width_ok(uint64_t d);
 cudaError_t tq_decode_launch(uint16_t* out, const uint8_t* weights, uint64_t w_room, const uint8_t* luts, uint64_t l_room, uint64_t d,

@@ -115,6 +115,61 @@ def main():
         vc, vs = oracle.tq_encode_rows(R, vr, d)
         out[f"tq_res_{d}"] = oracle.residual_tq(R, q, kc, ks, vc, vs, qh, kvh, dh, L, d)
 
+    # the small steps either side of attention in a mixer
+    P_ = oracle._p
+    over = R.over
+    n = 1000
+    x, y = bits((n,)), bits((n,))
+    z = np.zeros(n, np.uint16)
+    R.nn.vector_add(P_(z), P_(x), P_(y), n, P_(over)); R.wait()
+    out["mx_add_x"], out["mx_add_y"], out["mx_add_z"] = x, y, z
+    xr, w = bits((5, 300)), bits((256,))
+    o = np.zeros((5, 256), np.uint16)
+    R.nn.rmsnorm_rows(P_(o), P_(xr), P_(w), 256, 5, 300, 256, np.float32(1e-6), P_(over)); R.wait()
+    out["mx_norm_x"], out["mx_norm_w"], out["mx_norm_o"] = xr, w, o
+    x1, w1 = bits((2048,)), bits((2048,))
+    o1 = np.zeros(2048, np.uint16)
+    R.nn.rmsnorm(P_(o1), P_(x1), P_(w1), 2048, np.float32(1e-5), P_(over)); R.wait()
+    out["mx_norm1_x"], out["mx_norm1_w"], out["mx_norm1_o"] = x1, w1, o1
+    for tag, theta, hd, pos in (("a", 1e7, 64, 123456), ("b", 1e4, 128, 77), ("c", 1e6, 256, 4095)):
+        cs = np.zeros(hd, np.float32)
+        R.nn.rope_angles(P_(cs), pos, np.float32(theta), hd); R.wait()
+        out[f"mx_ang_{tag}"] = cs
+        out[f"mx_ang_{tag}_args"] = np.array([theta, hd, pos], np.float64)
+    csr = np.zeros((4, 64), np.float32)
+    R.nn.rope_angles_rows(P_(csr), 100000, np.float32(1e7), 64, 4); R.wait()
+    out["mx_ang_rows"] = csr
+    pos3 = np.array([[5, 2, 9], [1000, 17, 3], [7, 7, 7], [65000, 40, 41]], np.uint32)
+    csm = np.zeros((4, 64), np.float32)
+    R.nn.rope_angles_mrope_rows(P_(csm), P_(pos3), np.float32(1e7), 64, 4, 11 | (10 << 16)); R.wait()
+    out["mx_ang_mrope_pos"], out["mx_ang_mrope"] = pos3, csm
+    pos2 = np.array([[3, 8], [30, 1], [0, 0]], np.uint32)
+    csa = np.zeros((3, 72), np.float32)
+    R.nn.rope_angles_axial_rows(P_(csa), P_(pos2), np.float32(1e4), 72, 3); R.wait()
+    out["mx_ang_axial_pos"], out["mx_ang_axial"] = pos2, csa
+    xh = bits((4, 64))
+    oh = np.zeros_like(xh)
+    R.nn.rope(P_(oh), P_(xh), P_(out["mx_ang_a"]), 4, 64, P_(over)); R.wait()
+    out["mx_rope_x"], out["mx_rope_o"] = xh, oh
+    xrr = bits((3, 256))
+    orr = xrr.copy()
+    R.nn.rope_rows(P_(orr), P_(xrr), P_(csr), 3, 2, 128, 256, 64, P_(over)); R.wait()
+    out["mx_rope_rows_x"], out["mx_rope_rows_o"] = xrr, orr
+    xi = bits((3, 96))
+    for inv in (0, 1):
+        oi = xi.copy()
+        R.nn.rope_interleaved(P_(oi[:, 32:]), P_(xi[:, 32:]), P_(out["mx_ang_a"]), 3, 96, 64, inv, P_(over)); R.wait()
+        out[f"mx_rope_il_{inv}"] = oi
+    out["mx_rope_il_x"] = xi
+    att, qg = bits((6, 64)), bits((6, 128), 2.0)
+    og = np.zeros_like(att)
+    R.nn.attention_gate_rows(P_(og), P_(att), P_(qg), 6, 64, P_(over)); R.wait()
+    out["mx_gate_att"], out["mx_gate_qg"], out["mx_gate_o"] = att, qg, og
+    src = bits((4, 50))
+    dst = np.zeros((4, 40), np.uint16)
+    R.nn.vector_copy_rows(P_(dst), 40, P_(src), 50, 33, 4); R.wait()
+    out["mx_copy_src"], out["mx_copy_dst"] = src, dst
+
     path = Path(__file__).with_name("reference_x86_avx2.npz")
     np.savez_compressed(path, **out)
     print(path, path.stat().st_size, "bytes,", len(out), "arrays")

@@ -1,0 +1,92 @@
+"""The small steps either side of attention in a layer's mixer on a B200 — add, copies, RMS norm, the rotary angles and the
+three rotations, the output gate — against outputs of the reference's CPU family (tests/golden/)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from oracle import from_bits
+from util import dev, host_bits
+
+pytestmark = pytest.mark.gpu
+
+
+def one_ulp(got, want, what):
+    d = np.abs(got.astype(np.int32) - want.astype(np.int32))
+    assert (d <= 1).all(), f"{what}: {int(d.max())} fp16 steps"
+
+
+def test_add_copy_norm_gate(cuda, fam, golden):
+    g = golden
+    x, y = dev(cuda, g["mx_add_x"]), dev(cuda, g["mx_add_y"])
+    z = cuda.zeros_like(x)
+    fam.nn.vector_add(z.data_ptr(), x.data_ptr(), y.data_ptr(), x.numel(), None)
+    xr, w = dev(cuda, g["mx_norm_x"]), dev(cuda, g["mx_norm_w"])
+    o = cuda.zeros((5, 256), dtype=cuda.int16, device="cuda")
+    fam.nn.rmsnorm_rows(o.data_ptr(), xr.data_ptr(), w.data_ptr(), 256, 5, 300, 256, C.c_float(1e-6), None)
+    x1, w1 = dev(cuda, g["mx_norm1_x"]), dev(cuda, g["mx_norm1_w"])
+    o1 = cuda.zeros(2048, dtype=cuda.int16, device="cuda")
+    fam.nn.rmsnorm(o1.data_ptr(), x1.data_ptr(), w1.data_ptr(), 2048, C.c_float(1e-5), None)
+    att, qg = dev(cuda, g["mx_gate_att"]), dev(cuda, g["mx_gate_qg"])
+    og = cuda.zeros_like(att)
+    fam.nn.attention_gate_rows(og.data_ptr(), att.data_ptr(), qg.data_ptr(), 6, 64, None)
+    src = dev(cuda, g["mx_copy_src"])
+    dst = cuda.zeros((4, 40), dtype=cuda.int16, device="cuda")
+    fam.nn.vector_copy_rows(dst.data_ptr(), 40, src.data_ptr(), 50, 33, 4)
+    flat = cuda.zeros(200, dtype=cuda.int16, device="cuda")
+    fam.nn.vector_copy(flat.data_ptr(), src.data_ptr(), 200)
+    assert fam.sys.compute_completed()
+    assert np.array_equal(host_bits(z), g["mx_add_z"])
+    one_ulp(host_bits(o), g["mx_norm_o"], "rmsnorm_rows")          # the sum of squares is folded in the block's order
+    one_ulp(host_bits(o1), g["mx_norm1_o"], "rmsnorm")
+    one_ulp(host_bits(og), g["mx_gate_o"], "attention_gate_rows")  # expf on the card against libm's, then two roundings
+    assert np.array_equal(host_bits(dst), g["mx_copy_dst"])
+    assert np.array_equal(host_bits(flat), g["mx_copy_src"].reshape(-1))
+
+
+def test_rotary_angles(cuda, fam, golden):
+    g = golden
+    for tag in "abc":
+        theta, hd, pos = g[f"mx_ang_{tag}_args"]
+        cs = cuda.zeros(int(hd), dtype=cuda.float32, device="cuda")
+        fam.nn.rope_angles(cs.data_ptr(), int(pos), C.c_float(theta), int(hd))
+        assert fam.sys.compute_completed()
+        # same fp32 angle as the reference (r is made exactly as libm makes it); cosf/sinf on the card are within 2 ulps
+        np.testing.assert_allclose(cs.cpu().numpy(), g[f"mx_ang_{tag}"], rtol=0, atol=5e-7)
+    cs = cuda.zeros((4, 64), dtype=cuda.float32, device="cuda")
+    fam.nn.rope_angles_rows(cs.data_ptr(), 100000, C.c_float(1e7), 64, 4)
+    pos3 = dev(cuda, g["mx_ang_mrope_pos"])
+    csm = cuda.zeros((4, 64), dtype=cuda.float32, device="cuda")
+    fam.nn.rope_angles_mrope_rows(csm.data_ptr(), pos3.data_ptr(), C.c_float(1e7), 64, 4, 11 | (10 << 16))
+    pos2 = dev(cuda, g["mx_ang_axial_pos"])
+    csa = cuda.zeros((3, 72), dtype=cuda.float32, device="cuda")
+    fam.nn.rope_angles_axial_rows(csa.data_ptr(), pos2.data_ptr(), C.c_float(1e4), 72, 3)
+    assert fam.sys.compute_completed()
+    np.testing.assert_allclose(cs.cpu().numpy(), g["mx_ang_rows"], rtol=0, atol=5e-7)
+    np.testing.assert_allclose(csm.cpu().numpy(), g["mx_ang_mrope"], rtol=0, atol=5e-7)
+    np.testing.assert_allclose(csa.cpu().numpy(), g["mx_ang_axial"], rtol=0, atol=5e-7)
+
+
+def test_rotations(cuda, fam, golden):
+    g = golden
+    cs_a = cuda.from_numpy(g["mx_ang_a"]).cuda()
+    cs_r = cuda.from_numpy(g["mx_ang_rows"]).cuda()
+    xh = dev(cuda, g["mx_rope_x"])
+    oh = cuda.zeros_like(xh)
+    fam.nn.rope(oh.data_ptr(), xh.data_ptr(), cs_a.data_ptr(), 4, 64, None)
+    xr = dev(cuda, g["mx_rope_rows_x"])
+    fam.nn.rope_rows(xr.data_ptr(), xr.data_ptr(), cs_r.data_ptr(), 3, 2, 128, 256, 64, None)       # in place, partial: 64 of 128
+    outs = []
+    for inv in (0, 1):
+        xi = dev(cuda, g["mx_rope_il_x"])
+        at = xi.data_ptr() + 32 * 2                                                                  # a head's tail is what turns
+        fam.nn.rope_interleaved(at, at, cs_a.data_ptr(), 3, 96, 64, inv, None)
+        outs.append(xi)
+    assert fam.sys.compute_completed()
+    assert np.array_equal(host_bits(oh), g["mx_rope_o"])
+    assert np.array_equal(host_bits(xr), g["mx_rope_rows_o"])
+    for inv in (0, 1):
+        assert np.array_equal(host_bits(outs[inv]), g[f"mx_rope_il_{inv}"])
+    # turning one way and back is the identity up to two roundings
+    back = from_bits(host_bits(outs[0]), 0)
+    assert np.isfinite(back).all()

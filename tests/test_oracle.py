@@ -173,3 +173,38 @@ def test_port_residual_over_coded_rows(golden, port, d):
     want = golden[f"tq_res_{d}"]
     assert np.allclose(res[:, 0], want[:, 0], rtol=0, atol=2e-5) and np.allclose(res[:, 1], want[:, 1], rtol=2e-5)
     assert np.abs(res[:, 2:] - want[:, 2:]).max() <= 2e-5 * np.abs(want[:, 2:]).max() + 1e-6
+
+
+# ---- the small steps either side of attention in a mixer -----------------------------------------------------------
+
+def test_port_mixer_steps(golden, port):
+    P, L = oracle._p, port.lib
+    g = golden
+    z = np.zeros_like(g["mx_add_z"]); L.oracle_vector_add(P(z), P(g["mx_add_x"]), P(g["mx_add_y"]), z.size)
+    assert np.array_equal(z, g["mx_add_z"])
+    o = np.zeros_like(g["mx_norm_o"]); L.oracle_rmsnorm_rows(P(o), P(g["mx_norm_x"]), P(g["mx_norm_w"]), 256, 5, 300, 256, 1e-6)
+    assert (np.abs(o.astype(np.int32) - g["mx_norm_o"].astype(np.int32)) <= 1).all()           # the sum's order is the family's own
+    o1 = np.zeros_like(g["mx_norm1_o"]); L.oracle_rmsnorm_rows(P(o1), P(g["mx_norm1_x"]), P(g["mx_norm1_w"]), 2048, 1, 2048, 2048, 1e-5)
+    assert (np.abs(o1.astype(np.int32) - g["mx_norm1_o"].astype(np.int32)) <= 1).all()
+    for tag in "abc":
+        theta, hd, pos = g[f"mx_ang_{tag}_args"]
+        cs = np.zeros(int(hd), np.float32); L.oracle_rope_angles(P(cs), int(pos), None, theta, int(hd), 1, 0, 0)
+        assert np.array_equal(cs, g[f"mx_ang_{tag}"])
+    cs = np.zeros((4, 64), np.float32); L.oracle_rope_angles(P(cs), 100000, None, 1e7, 64, 4, 0, 0)
+    assert np.array_equal(cs, g["mx_ang_rows"])
+    csm = np.zeros((4, 64), np.float32); L.oracle_rope_angles(P(csm), 0, P(g["mx_ang_mrope_pos"]), 1e7, 64, 4, 11 | (10 << 16), 1)
+    assert np.array_equal(csm, g["mx_ang_mrope"])
+    csa = np.zeros((3, 72), np.float32); L.oracle_rope_angles(P(csa), 0, P(g["mx_ang_axial_pos"]), 1e4, 72, 3, 0, 2)
+    assert np.array_equal(csa, g["mx_ang_axial"])
+    oh = np.zeros_like(g["mx_rope_o"]); L.oracle_rope_rows(P(oh), P(g["mx_rope_x"]), P(g["mx_ang_a"]), 1, 4, 64, 0, 64)
+    assert np.array_equal(oh, g["mx_rope_o"])
+    orr = g["mx_rope_rows_x"].copy(); L.oracle_rope_rows(P(orr), P(g["mx_rope_rows_x"]), P(g["mx_ang_rows"]), 3, 2, 128, 256, 64)
+    assert np.array_equal(orr, g["mx_rope_rows_o"])
+    for inv in (0, 1):
+        xi = g["mx_rope_il_x"]; oi = xi.copy()
+        L.oracle_rope_interleaved(P(oi[:, 32:]), P(xi[:, 32:]), P(g["mx_ang_a"]), 3, 96, 64, inv)
+        assert np.array_equal(oi, g[f"mx_rope_il_{inv}"])
+    og = np.zeros_like(g["mx_gate_o"]); L.oracle_attention_gate_rows(P(og), P(g["mx_gate_att"]), P(g["mx_gate_qg"]), 6, 64)
+    assert np.array_equal(og, g["mx_gate_o"])
+    dst = np.zeros_like(g["mx_copy_dst"]); L.oracle_vector_copy_rows(P(dst), 40, P(g["mx_copy_src"]), 50, 33, 4)
+    assert np.array_equal(dst, g["mx_copy_dst"])
