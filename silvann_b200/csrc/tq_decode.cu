@@ -25,6 +25,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "tensormap.cuh"
+#include <stdio.h>
 #include <string.h>
 
 namespace sv {
@@ -34,14 +35,20 @@ static __device__ const uint16_t g_tq_levels_fused[318] = {
 };
 
 template <int DH, int W> struct TqCfg {
-    static constexpr int NW = 8;                          /* consumer warps, 16 positions of a tile each */
-    static constexpr int BT = 16 * NW;
     static constexpr int RB = DH * W / 8;                 /* bytes a coded row */
+    /* consumer warps, 16 positions of a tile each.  The kernel is bound by instruction issue with few warps to pick from,
+     * so as many as registers (query fragments live in shared memory for this) and the ring allow: fifteen and the producer
+     * fill the four schedulers' register files at 128 registers a thread (a scheduler's warps share 16 K registers); eight
+     * where a 256-byte row makes the tiles too large for two stages of 240 positions. */
+    static constexpr int NW = RB > 128 ? 8 : 15;
+    static constexpr int BT = 16 * NW;
     static constexpr int BOX = RB > 128 ? 128 : RB;       /* bytes a TMA box row; the swizzle's span */
     static constexpr int BOXES = RB / BOX;
     static constexpr int TILE = BT * RB;                  /* a K (or V) tile */
     static constexpr int STAGE = 2 * TILE;
-    static constexpr int STAGES = (128 * 1024) / STAGE > 8 ? 8 : (128 * 1024) / STAGE;
+    static constexpr int RING = RB > 128 ? 128 * 1024 : 120 * 1024;
+    static constexpr int STAGES = RING / STAGE > 8 ? 8 : RING / STAGE;
+    static constexpr int QROW = DH * 2 + 16;              /* bytes a query head in shared memory: 16 bytes of padding spread the heads over the banks */
     static constexpr int LUT_BYTES = 256 * 256;             /* 256 entries, each 32 copies (a bank each) in a 256-byte slot */
     static constexpr int QB = RB / 4;                     /* bytes of a key row a lane reads (its quarter) */
     static constexpr int EB = RB / 8;                     /* bytes of a value row a lane reads (its eighth) */
@@ -102,7 +109,8 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* stage_base = smem;
     uint32_t* lut = (uint32_t*)(smem + Cfg::STAGES * Cfg::STAGE);
-    uint64_t* full = (uint64_t*)((uint8_t*)lut + Cfg::LUT_BYTES);
+    uint8_t* q_s = (uint8_t*)lut + Cfg::LUT_BYTES;          /* [HPB] query heads, zero past `heads` */
+    uint64_t* full = (uint64_t*)(q_s + HPB * Cfg::QROW);
     uint64_t* empty = full + Cfg::STAGES;
     volatile uint32_t* abort_flag = (volatile uint32_t*)(empty + Cfg::STAGES);
     uint32_t* ticket_s = (uint32_t*)abort_flag + 1;
@@ -130,6 +138,12 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         if (W == 8) { const uint32_t l = g_tq_levels_fused[62 + b]; e = l | (l << 16); }
         else e = (uint32_t)g_tq_levels_fused[14 + (b & 15)] | ((uint32_t)g_tq_levels_fused[14 + (b >> 4)] << 16);
         lut[b * 64 + (i & 31)] = e;
+    }
+    for (int i = tid; i < HPB * (DH / 4); i += THREADS) {           /* 8 bytes a step */
+        const int h = i / (DH / 4), e = (i % (DH / 4)) * 4;
+        uint2 v = make_uint2(0u, 0u);
+        if (h < heads) v = *reinterpret_cast<const uint2*>(P.q + (size_t)(head0 + h) * DH + e);
+        *reinterpret_cast<uint2*>(q_s + h * Cfg::QROW + e * 2) = v;
     }
     __syncthreads();
 
@@ -162,20 +176,9 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
             }
         }
     } else {
-        /* ---- consumers.  The query fragments first: for k-step kk this lane's four contraction slots are elements
-         * t4·DH/4 + 4kk .. +3 of its head (g8), the order in which it will read the coded keys. ---- */
-        uint32_t qf[NHT][KS][2];
-#pragma unroll
-        for (int n = 0; n < NHT; ++n) {
-            const int h = n * 8 + g8;
-            const uint16_t* qh = P.q + (size_t)(head0 + h) * DH + t4 * (DH / 4);
-#pragma unroll
-            for (int kk = 0; kk < KS; ++kk) {
-                uint2 v = make_uint2(0u, 0u);
-                if (h < heads) v = *reinterpret_cast<const uint2*>(qh + 4 * kk);
-                qf[n][kk][0] = v.x; qf[n][kk][1] = v.y;
-            }
-        }
+        /* ---- consumers.  For k-step kk this lane's four contraction slots are elements t4·DH/4 + 4kk .. +3 of its head
+         * (g8) — the order in which it reads the coded keys — so a query fragment is 8 bytes of the staged head. ---- */
+        const uint32_t q_lane = smem_u32(q_s) + g8 * Cfg::QROW + t4 * (DH / 2);
         const uint32_t lut_lane = smem_u32(lut) + lane * 4;
         const int rowA = warp * 16 + g8, rowB = rowA + 8;          /* this lane's score rows (positions of the tile) */
         const int pv0 = warp * 16 + 2 * t4;                        /* its value positions: pv0, pv0+1, pv0+8, pv0+9 */
@@ -225,8 +228,10 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                 }
 #pragma unroll
                 for (int n = 0; n < NHT; ++n) {
-                    if (kk & 1) mma16816<DT>(sb[n], a0, a1, a2, a3, qf[n][kk][0], qf[n][kk][1]);
-                    else        mma16816<DT>(sa[n], a0, a1, a2, a3, qf[n][kk][0], qf[n][kk][1]);
+                    uint32_t b0, b1;
+                    asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(q_lane + n * 8 * Cfg::QROW + kk * 8));
+                    if (kk & 1) mma16816<DT>(sb[n], a0, a1, a2, a3, b0, b1);
+                    else        mma16816<DT>(sa[n], a0, a1, a2, a3, b0, b1);
                 }
             }
 
@@ -319,6 +324,7 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     float* wl = wm + NW * HPB;                        /* [NW][HPB] */
     float* wo = wl + NW * HPB;                        /* [NW][HPB][DH] */
     static_assert((size_t)NW * HPB * (DH + 2) * 4 <= (size_t)Cfg::STAGES * Cfg::STAGE + Cfg::LUT_BYTES, "the fold fits in the ring and the table");
+    static_assert(Cfg::STAGES >= 2, "at least two stages in the ring");
     if (warp < NW) {
         const int c2 = t4 * 2;
 #pragma unroll
@@ -461,7 +467,7 @@ bool tq_attend_fits(const void* q, const void* kcodes, const void* kscales, cons
 template <int DH, int W, int NHT>
 static cudaError_t tq_launch_one(const CUtensorMap& km, const CUtensorMap& vm, const TqParams& P, uint32_t blocks, cudaStream_t st) {
     using Cfg = TqCfg<DH, W>;
-    const size_t smem = 1024 + (size_t)Cfg::STAGES * Cfg::STAGE + Cfg::LUT_BYTES + 2 * Cfg::STAGES * 8 + 64;
+    const size_t smem = 1024 + (size_t)Cfg::STAGES * Cfg::STAGE + Cfg::LUT_BYTES + (size_t)8 * NHT * Cfg::QROW + 2 * Cfg::STAGES * 8 + 64;
     static bool attr_set[64] = {};
     int dev = 0; cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
@@ -471,7 +477,14 @@ static cudaError_t tq_launch_one(const CUtensorMap& km, const CUtensorMap& vm, c
     }
     tq_attend_kernel<DH, W, NHT><<<blocks, (Cfg::NW + 1) * 32, smem, st>>>(km, vm, P);
     note_launch(1);
-    return cudaGetLastError();
+    cudaError_t le = cudaGetLastError();           /* a refusal names what was asked for: the message the door prints has no room for it */
+    if (le != cudaSuccess) {
+        cudaFuncAttributes fa;
+        if (cudaFuncGetAttributes(&fa, tq_attend_kernel<DH, W, NHT>) == cudaSuccess)
+            fprintf(stderr, "tq_attend<%d,%d,%d>: regs %d maxThreads %d static smem %zu max dyn %d asked %zu threads %d\n", DH, W, NHT, fa.numRegs,
+                    fa.maxThreadsPerBlock, fa.sharedSizeBytes, fa.maxDynamicSharedSizeBytes, smem, (Cfg::NW + 1) * 32);
+    }
+    return le;
 }
 
 cudaError_t tq_attend_launch(float* res, const uint16_t* q, const uint8_t* kcodes, const uint16_t* kscales, const uint8_t* vcodes,
@@ -482,7 +495,7 @@ cudaError_t tq_attend_launch(float* res, const uint16_t* q, const uint8_t* kcode
     const uint32_t group = (uint32_t)(qh / kvh);
     const uint32_t hpb = (group > 8u && dh == 128) ? 16u : 8u, hb = (group + hpb - 1) / hpb;
     const uint32_t rb = (uint32_t)(dh * d / 8), box = rb > 128 ? 128u : rb;
-    constexpr uint32_t BT = 128;
+    const uint32_t BT = rb > 128 ? 128u : 240u;            /* TqCfg::BT */
     CUtensorMap km, vm;
     if (!make_map_2d_bytes(&km, kcodes, (uint64_t)kvh * rb, length, (uint64_t)kvh * rb, box, BT) ||
         !make_map_2d_bytes(&vm, vcodes, (uint64_t)kvh * rb, length, (uint64_t)kvh * rb, box, BT)) return cudaErrorInvalidValue;
