@@ -430,6 +430,24 @@ def other_workloads(torch, fam, pk, steps, warmup):
         out[tag] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_step": ms, "frac_hbm": nbytes / ms / 1e6 / hbm,
                     "note": f"{seqs} sequence(s) x 32 heads x 128x128 fp32 state, read and written once a step"
                             + (" (2 MiB of state: stays in L2 between steps)" if seqs == 1 else "")}
+    # the one-sequence step without the host in the loop: 64 steps captured once in a CUDA graph
+    S = torch.zeros((1, heads, d, d), device="cuda", dtype=torch.float32)
+    conved = torch.randn((64, 3 * heads * d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.1
+    z = torch.randn((64, heads * d), generator=gen, device="cuda", dtype=torch.bfloat16)
+    beta = torch.rand((64, heads), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    g = (-torch.rand((64, heads), generator=gen, device="cuda", dtype=torch.float32)).to(torch.bfloat16)
+    o = torch.zeros((64, heads * d), device="cuda", dtype=torch.bfloat16)
+    side = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(64):
+            ext.deltanet(S, conved[i], z[i], beta[i], g[i], w, o[i], heads, heads, d, 1, 1, 0, ext.BF16, stream=side.cuda_stream)
+    ms = time_loop(torch, graph.replay, 20, 3) / 64
+    nbytes = 2 * heads * d * d * 4 + 3 * heads * d * 2 + 2 * heads * d * 2 + 2 * heads * 2 + d * 2
+    out["config5_deltanet_decode_1seq_graph"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_step": ms, "frac_hbm": nbytes / ms / 1e6 / hbm,
+                                                 "note": "the same step, 64 consecutive positions of one sequence captured in a CUDA graph (no host between launches)"}
+    del graph
     T = 8192
     S = torch.zeros((1, heads, d, d), device="cuda", dtype=torch.float32)
     conved = torch.randn((T, 3 * heads * d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.1

@@ -41,22 +41,35 @@ struct DeltaParams {
     int gate;
 };
 
-/* the blocks of a head as a thread-block cluster: a barrier over all of them, and a float read from a peer's shared memory */
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+#ifdef SV_DN_TRACE
+/* Development aid, compiled only on request: every block leaves %globaltimer stamps (ns) of its phases here. */
+__device__ unsigned long long g_dn_trace[256 * 8];
+__device__ __forceinline__ unsigned long long sv_dn_time() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define SV_NTR(k) do { if (threadIdx.x == 0 && blockIdx.x < 256) g_dn_trace[blockIdx.x * 8 + (k)] = sv_dn_time(); } while (0)
+extern "C" __attribute__((visibility("default"))) int sv_dn_trace_read(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_dn_trace, sizeof(unsigned long long) * 256 * 8);
 }
-__device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t rank) {
-    uint32_t remote; float v;
+#else
+#define SV_NTR(k) do {} while (0)
+#endif
+
+/* the blocks of a head as a thread-block cluster: the two halves of a barrier over all of them, and a float written into a peer's shared memory */
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ void st_cluster_f32(float* local, uint32_t rank, float v) {
+    uint32_t remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
-/* FUSE: the kernel is launched with the d/32 blocks of a head as one cluster; they hand each other their sums of squares
- * through distributed shared memory and finish the read-out (norm, weight, gate) themselves — one launch a step, which
- * is what a decode step of one sequence is bound by.  The sums are added in block order, as the norm kernel adds them. */
+/* FUSE (one position): the kernel is launched with the d/32 blocks of a head as one cluster; each block PUSHES its sum of
+ * squares into every block's shared memory, arrives at the cluster barrier, stores its slice of the state while the
+ * barrier completes, waits, and finishes the read-out (norm, weight, gate) from its own shared memory — one launch a
+ * step, which is what a decode step of one sequence is bound by, and no block reads a peer after the barrier, so none
+ * has to wait for the others before it leaves.  The sums are added in block order, as the norm kernel adds them. */
 template <int D, int DT, bool PRE, bool FUSE>
 __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaParams P) {
+    SV_NTR(0);
     using E = Elem<DT>;
     constexpr int CB = D / DN_COLS;            /* column blocks per head */
     constexpr int R = D / DN_RG;               /* keys per thread */
@@ -69,7 +82,7 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
     __shared__ __align__(16) float qk[2][2][D];   /* [buffer][q|k][i] as fp32 */
     __shared__ float red1[DN_RG][DN_COLS + 2];     /* first fold, per row group: S^T k partials, then |q|^2 and |k|^2 */
     __shared__ float red2[DN_RG][DN_COLS];         /* second fold: read-out partials */
-    __shared__ float cl_ss[2];                     /* FUSE: this block's sum of squares, even and odd positions */
+    __shared__ float cl_ss[8];                     /* FUSE: every block of the head's sum of squares, pushed here by its owner */
 
     float* Sh = P.S + ((uint64_t)b * P.v_heads + h) * D * D;
     float s[R];
@@ -102,6 +115,7 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
         n_qk[u] = (P.rows > 1 && i < 2 * D) ? qk_src(cv + ch, i) : (uint16_t)0;
     }
     __syncthreads();
+    SV_NTR(1);
 
     const float inv_sqrt_d = 1.0f / sqrtf((float)D);
     bool hit = false;
@@ -149,6 +163,7 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
         red1[rg][c] = kvp;
         if (!PRE && c == 0) { red1[rg][DN_COLS] = qq; red1[rg][DN_COLS + 1] = kk; }
         __syncthreads();
+    SV_NTR(2);
         float kvsum = 0.f, qsum = 0.f, ksum = 0.f;
 #pragma unroll
         for (int r = 0; r < DN_RG; ++r) { kvsum += red1[r][c]; if (!PRE) { qsum += red1[r][DN_COLS]; ksum += red1[r][DN_COLS + 1]; } }
@@ -168,6 +183,7 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
         }
         red2[rg][c] = (op4[0] + op4[1]) + (op4[2] + op4[3]);
         __syncthreads();
+    SV_NTR(3);
         uint16_t oh = 0;
         if (rg == 0) {
             const float o = (red2[0][c] + red2[1][c] + red2[2][c] + red2[3][c]) * inv_q;
@@ -177,15 +193,19 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
             if (!FUSE) {
                 oo[t * vd + (uint64_t)h * D + j] = oh;
                 if (c == 0) ss[(t * P.v_heads + h) * CB + cb] = sq;
-            } else if (c == 0) cl_ss[t & 1] = sq;
+            } else if (c < CB) st_cluster_f32(&cl_ss[cb], (uint32_t)c, sq);        /* lane r tells block r of the head */
         }
         if (FUSE) {
-            /* a slot is rewritten two positions later, after the cluster barrier of the position between */
-            cluster_sync_all();
+            cluster_arrive();
+            /* the state goes home while the barrier completes */
+#pragma unroll
+            for (int i = 0; i < R; ++i) Sh[(uint64_t)(rg * R + i) * D + j] = s[i];
+            cluster_wait();
+    SV_NTR(4);
             if (rg == 0) {
                 float sum = 0.f;
 #pragma unroll
-                for (int r = 0; r < CB; ++r) sum += ld_cluster_f32(&cl_ss[t & 1], (uint32_t)r);
+                for (int r = 0; r < CB; ++r) sum += cl_ss[r];
                 const float scale = 1.0f / sqrtf(sum / (float)D + 1e-6f);
                 const float zr = E::to_float(z_bits);
                 const float zc = zr < -88.0f ? -88.0f : (zr > 88.0f ? 88.0f : zr);
@@ -199,10 +219,13 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
          * barrier, which the readers above reach only after reading; qk[buf] is rewritten by the next position's
          * prefetch, after the second barrier that follows its last read. */
     }
+    if (!FUSE) {
 #pragma unroll
-    for (int i = 0; i < R; ++i) Sh[(uint64_t)(rg * R + i) * D + j] = s[i];
+        for (int i = 0; i < R; ++i) Sh[(uint64_t)(rg * R + i) * D + j] = s[i];
+    }
     if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
-    if (FUSE) cluster_sync_all();                  /* no block leaves while a peer may still read its slot */
+    SV_NTR(5);
+    SV_NTR(6);
 }
 
 /* The per-position scalars of a run of positions, off the serial path: a warp a (sequence, position, key head) folds
