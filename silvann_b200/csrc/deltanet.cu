@@ -254,25 +254,46 @@ __global__ void __launch_bounds__(128) deltanet_scalars_kernel(float4* sc, const
     }
 }
 
-/* out <- half(out · rsqrt(mean(out^2) + 1e-6) · w · gate(z)), the head's sum of squares read from the blocks' parts. */
+/* out <- half(out · rsqrt(mean(out^2) + 1e-6) · w · gate(z)), the head's sum of squares read from the blocks' parts.
+ * Eight neighbouring elements a thread (16 bytes of out, of z and of w a load): the kernel moves 6 bytes an element and
+ * is bound by how many loads are in flight, which two-byte loads kept low. */
 template <int D, int DT>
 __global__ void __launch_bounds__(256) deltanet_norm_kernel(uint16_t* out, const float* ss, const uint16_t* z, const uint16_t* w,
                                                             uint64_t heads_total, int gate, unsigned int* over) {
     using E = Elem<DT>;
     constexpr int CB = D / DN_COLS;
     bool hit = false;
-    const uint64_t n = heads_total * D;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint64_t hh = i / D; const int e = (int)(i % D);
+    const uint64_t n8 = heads_total * (D / 8);
+    const bool wide = (((uintptr_t)out | (uintptr_t)z | (uintptr_t)w) & 15u) == 0;
+    for (uint64_t i8 = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i8 < n8; i8 += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t hh = i8 / (D / 8); const int e0 = (int)(i8 % (D / 8)) * 8;
+        const uint64_t i0 = hh * D + e0;
         float sum = 0.f;
 #pragma unroll
         for (int k = 0; k < CB; ++k) sum += ss[hh * CB + k];
         const float scale = 1.0f / sqrtf(sum / (float)D + 1e-6f);
-        const float zr = E::to_float(z[i]);
-        const float zc = zr < -88.0f ? -88.0f : (zr > 88.0f ? 88.0f : zr);
-        const float sg = 1.0f / (1.0f + expf(-zc));
-        const float gz = gate == 1 ? sg : zc * sg;
-        out[i] = E::from_float(E::to_float(out[i]) * scale * E::to_float(w[e]) * gz, hit);
+        uint16_t ov[8], zv[8], wv[8];
+        if (wide) {
+            *reinterpret_cast<uint4*>(ov) = *reinterpret_cast<const uint4*>(out + i0);
+            *reinterpret_cast<uint4*>(zv) = *reinterpret_cast<const uint4*>(z + i0);
+            *reinterpret_cast<uint4*>(wv) = *reinterpret_cast<const uint4*>(w + e0);
+        } else {
+#pragma unroll
+            for (int x = 0; x < 8; ++x) { ov[x] = out[i0 + x]; zv[x] = z[i0 + x]; wv[x] = w[e0 + x]; }
+        }
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+            const float zr = E::to_float(zv[x]);
+            const float zc = zr < -88.0f ? -88.0f : (zr > 88.0f ? 88.0f : zr);
+            const float sg = 1.0f / (1.0f + expf(-zc));
+            const float gz = gate == 1 ? sg : zc * sg;
+            ov[x] = E::from_float(E::to_float(ov[x]) * scale * E::to_float(wv[x]) * gz, hit);
+        }
+        if (wide) *reinterpret_cast<uint4*>(out + i0) = *reinterpret_cast<const uint4*>(ov);
+        else {
+#pragma unroll
+            for (int x = 0; x < 8; ++x) out[i0 + x] = ov[x];
+        }
     }
     if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
 }
@@ -348,7 +369,7 @@ static cudaError_t launch_dn(const DeltaCall& c, float* ss) {
     if (e != cudaSuccess) return e;
     const uint64_t heads_total = (uint64_t)c.seqs * c.rows * c.v_heads;
     /* z and out are laid out [seq][row][head][d], so one flat pass covers every sequence */
-    uint64_t nb = (heads_total * D + 255) / 256; if (nb > 148 * 16) nb = 148 * 16;
+    uint64_t nb = (heads_total * (D / 8) + 255) / 256; if (nb > 148 * 16) nb = 148 * 16;
     deltanet_norm_kernel<D, DT><<<(unsigned)nb, 256, 0, c.stream>>>(c.out, ss, c.z, c.w, heads_total, c.gate, c.over);
     note_launch(2);
     return cudaGetLastError();
@@ -357,7 +378,7 @@ static cudaError_t launch_dn(const DeltaCall& c, float* ss) {
 template <int D, int DT>
 static cudaError_t launch_norm(const DeltaCall& c, const float* ss) {
     const uint64_t heads_total = (uint64_t)c.seqs * c.rows * c.v_heads;
-    uint64_t nb = (heads_total * D + 255) / 256; if (nb > 148 * 16) nb = 148 * 16;
+    uint64_t nb = (heads_total * (D / 8) + 255) / 256; if (nb > 148 * 16) nb = 148 * 16;
     deltanet_norm_kernel<D, DT><<<(unsigned)nb, 256, 0, c.stream>>>(c.out, ss, c.z, c.w, heads_total, c.gate, c.over);
     note_launch(1);
     return cudaGetLastError();
