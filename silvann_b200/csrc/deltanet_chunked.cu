@@ -11,8 +11,10 @@
  * L, M and the inverse A = (I + L)^-1 diag(beta) depend on k, q, beta, g only — not on the state and not on the values —
  * so a first kernel makes them for every chunk of the run at once (a block a chunk and value head), and only the three
  * products with the state are left on the serial path, where a block owns 32 value columns of one head as in the
- * position-at-a-time kernel.  Everything is fp32 FMA: the state is an fp32 quantity and its parity bar is relative 1e-3
- * after thousands of positions, so no operand is rounded to a tensor-core input type.
+ * position-at-a-time kernel.  The state is an fp32 quantity held to a relative 1e-3 after thousands of positions, so
+ * nothing of it is rounded to a 16-bit tensor-core type: the Gram products and the triangular products are fp32 FMA, and
+ * the two products with the state run on the tensor cores in TF32 with the state (or D) split into two terms — k and q
+ * are exact in TF32, the pair of terms carries 21 significand bits.
  *
  * The read-out leaves here rounded to 16 bits with each block's sum of squares beside it, exactly as the recurrent
  * kernel leaves it, and the same norm-and-gate kernel finishes it. */
@@ -52,12 +54,26 @@ template <int DT> __device__ __forceinline__ void unpack4(uint2 u, float* f) {
     f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
 }
 
+/* D (16 x 8, fp32) += A (16 x 8) · B (8 x 8), TF32 inputs: the warp MMA of the two products with the state */
+__device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+/* a 16-bit input as TF32 bits: exact, both types have at most 10 significand bits */
+template <int DT> __device__ __forceinline__ uint32_t tf32_of(uint16_t h) { return __float_as_uint(Elem<DT>::to_float(h)); }
+/* an fp32 number as two TF32 terms, hi + lo: hi its top 19 bits, lo the rest (the MMA reads lo's top 19 bits), so the
+ * pair carries 21 significand bits — a relative 2^-21 against the 1e-3 the state is held to */
+__device__ __forceinline__ void tf32_split(float x, uint32_t& hi, uint32_t& lo) {
+    hi = __float_as_uint(x) & 0xffffe000u;
+    lo = __float_as_uint(x - __uint_as_float(hi));
+}
+
 /* ---- kernel 1: everything about a chunk that does not depend on the state ------------------------------------
  * A block a (sequence, chunk, KEY head), 256 threads.  The two Gram products K K^T and Q K^T belong to the key head and
- * are made once, register-tiled (a thread owns rows ti, ti+16, ti+32, ti+48 against si, si+16, ..., so that the 16
- * lanes that differ in si read 16 consecutive rows of shared memory); then, two value heads of the key head at a time,
- * L is built transposed, (I + L)^-1 comes out of a right-looking substitution that lives in registers (a thread a
- * column, 64 running rows, the loop fully unrolled so that L is read four rows at a load), and A, M and the row vectors
+ * are made once, below the diagonal, on the tensor cores (TF32 holds k and q exactly; the sums are fp32); then, two
+ * value heads of the key head at a time, L is built transposed, (I + L)^-1 comes out of a right-looking substitution
+ * that lives in registers (a thread a column, 64 running rows, the loop fully unrolled so that L is read four rows at a
+ * load), and A, M and the row vectors
  * go to scratch. */
 template <int D, int DT>
 __global__ void __launch_bounds__(256, 2) deltanet_prep_kernel(const ChunkParams P) {
@@ -104,32 +120,29 @@ __global__ void __launch_bounds__(256, 2) deltanet_prep_kernel(const ChunkParams
     }
     __syncthreads();
     {
-        const int ti = tid >> 4, si = tid & 15;
-        float kk[4][4] = {}, qk[4][4] = {};
-#pragma unroll 2
-        for (int e = 0; e < D; e += 4) {
-            float4 kt[4], qt[4], ks[4];
-#pragma unroll
-            for (int a = 0; a < 4; ++a) {
-                kt[a] = *reinterpret_cast<const float4*>(kf + (ti + 16 * a) * LD + e);
-                qt[a] = *reinterpret_cast<const float4*>(qf + (ti + 16 * a) * LD + e);
-                ks[a] = *reinterpret_cast<const float4*>(kf + (si + 16 * a) * LD + e);
+        /* K K^T and Q K^T below the diagonal on the tensor cores: k and q are exact in TF32 and the sums are fp32, so the
+         * products are the fp32 ones.  A warp owns 16 rows t and every other 8-column tile s up to its diagonal. */
+        const int warp = tid >> 5, g8 = lane >> 2, t4 = lane & 3;
+        const int r1 = (warp & 3) * 16;
+        const float* kA = kf + (r1 + g8) * LD + t4; const float* kB = kA + 8 * LD;
+        const float* qA = qf + (r1 + g8) * LD + t4; const float* qB = qA + 8 * LD;
+        for (int nt = (warp >> 2); nt * 8 <= r1 + 15; nt += 2) {
+            float ck[4] = {}, cq[4] = {};
+            const float* sB = kf + (nt * 8 + g8) * LD + t4;                  /* B[k][n = s] = K[s][k] */
+#pragma unroll 4
+            for (int k0 = 0; k0 < D; k0 += 8) {
+                const uint32_t b0 = __float_as_uint(sB[k0]), b1 = __float_as_uint(sB[k0 + 4]);
+                mma_tf32(ck, __float_as_uint(kA[k0]), __float_as_uint(kB[k0]), __float_as_uint(kA[k0 + 4]), __float_as_uint(kB[k0 + 4]), b0, b1);
+                mma_tf32(cq, __float_as_uint(qA[k0]), __float_as_uint(qB[k0]), __float_as_uint(qA[k0 + 4]), __float_as_uint(qB[k0 + 4]), b0, b1);
             }
 #pragma unroll
-            for (int a = 0; a < 4; ++a)
-#pragma unroll
-                for (int bb = 0; bb <= a; ++bb) {       /* rows ti+16a against si+16bb: below the diagonal when a > bb */
-                    kk[a][bb] += kt[a].x * ks[bb].x + kt[a].y * ks[bb].y + kt[a].z * ks[bb].z + kt[a].w * ks[bb].w;
-                    qk[a][bb] += qt[a].x * ks[bb].x + qt[a].y * ks[bb].y + qt[a].z * ks[bb].z + qt[a].w * ks[bb].w;
-                }
+            for (int hh = 0; hh < 2; ++hh) {
+                float* kd = KK + (r1 + g8 + 8 * hh) * GL + nt * 8 + 2 * t4;
+                float* qd = QK + (r1 + g8 + 8 * hh) * GL + nt * 8 + 2 * t4;
+                kd[0] = ck[2 * hh]; kd[1] = ck[2 * hh + 1];
+                qd[0] = cq[2 * hh]; qd[1] = cq[2 * hh + 1];
+            }
         }
-#pragma unroll
-        for (int a = 0; a < 4; ++a)
-#pragma unroll
-            for (int bb = 0; bb <= a; ++bb) {
-                KK[(ti + 16 * a) * GL + si + 16 * bb] = kk[a][bb];
-                QK[(ti + 16 * a) * GL + si + 16 * bb] = qk[a][bb];
-            }
     }
 
     for (uint32_t p0 = 0; p0 < rep; p0 += 2) {
@@ -205,23 +218,28 @@ __global__ void __launch_bounds__(256, 2) deltanet_prep_kernel(const ChunkParams
 template <int D> struct ChunkSmem {
     static constexpr int LDH = D + 8;                      /* halves a k or q row: 16-byte rows, 8 banks apart for row pairs */
     static constexpr int TL = CH + 4;                      /* floats an A or M row */
-    static constexpr size_t STATE = (size_t)D * CNC * 4, RD = (size_t)CH * CNC * 4;
+    static constexpr int SP = CNC + 8;                     /* floats a row of the state block and of the 64 x 32 products: rows 8 banks apart,
+                                                            * so the B fragments of an MMA (4 rows x 8 columns a load) touch 32 banks */
+    static constexpr size_t STATE = (size_t)D * SP * 4, RD = (size_t)CH * SP * 4;
     static constexpr size_t KQ = (size_t)CH * LDH * 2, V = (size_t)CH * CNC * 2, AM = (size_t)CH * TL * 4, VEC = 4 * CH * 4;
     static constexpr size_t STAGE = 2 * KQ + V + 2 * AM + VEC;
-    static constexpr size_t TOTAL = STATE + 2 * RD + 2 * STAGE;
+    static constexpr size_t SQ = 2 * CH * 4;               /* two warps' halves of a row's sum of squares */
+    static constexpr size_t TOTAL = STATE + 3 * RD + SQ + 2 * STAGE;
 };
 
 template <int D, int DT>
 __global__ void __launch_bounds__(256, 1) deltanet_chunk_kernel(const ChunkParams P) {
     using E = Elem<DT>;
     using L = ChunkSmem<D>;
-    constexpr int LDH = L::LDH, TL = L::TL, CB = D / CNC, CPR = D / 8;
+    constexpr int LDH = L::LDH, TL = L::TL, SP = L::SP, CB = D / CNC, CPR = D / 8;
     extern __shared__ __align__(16) unsigned char smb[];
-    float* Ss = reinterpret_cast<float*>(smb);                       /* [D][32] the state block */
-    float* Rm = reinterpret_cast<float*>(smb + L::STATE);            /* [64][32]: V - scaled Kn S_0 */
-    float* Dm = Rm + CH * CNC;                                       /* [64][32]: D, then D scaled for the state update */
-    unsigned char* stage0 = smb + L::STATE + 2 * L::RD;
-    const int tid = threadIdx.x;
+    float* Ss = reinterpret_cast<float*>(smb);                       /* [D][SP] the state block */
+    float* Rm = reinterpret_cast<float*>(smb + L::STATE);            /* [64][SP]: V - scaled Kn S_0 */
+    float* Dm = Rm + CH * SP;                                        /* [64][SP]: D, then D scaled for the state update */
+    float* Qm = Dm + CH * SP;                                        /* [64][SP]: Q S_0 */
+    float* Qs = Qm + CH * SP;                                        /* [2][64]: a row's sum of squares, the two column halves */
+    unsigned char* stage0 = smb + L::STATE + 3 * L::RD + L::SQ;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t4 = lane & 3;
     const uint32_t cb = blockIdx.x % CB, h = (blockIdx.x / CB) % P.v_heads, b = blockIdx.x / (CB * P.v_heads);
     const uint32_t rep = P.v_heads / P.k_heads, kh = h / rep;
     const uint64_t ch = (uint64_t)(2 * P.k_heads + P.v_heads) * D, vd = (uint64_t)P.v_heads * D;
@@ -259,9 +277,13 @@ __global__ void __launch_bounds__(256, 1) deltanet_chunk_kernel(const ChunkParam
 
     fetch(0);
     cp_async_commit();
-    for (int i = tid; i < D * CNC; i += 256) Ss[i] = Sg[(uint64_t)(i / CNC) * D + j0 + i % CNC];
+    for (int i = tid; i < D * CNC; i += 256) Ss[(i / CNC) * SP + i % CNC] = Sg[(uint64_t)(i / CNC) * D + j0 + i % CNC];
     bool hit = false;
-    const int ty = tid >> 3, tx = tid & 7;           /* 32 x 8: two rows and four columns of a 64 x 32 product a thread */
+    /* the state products on the tensor cores: a warp owns 16 rows by 16 columns of K S_0 and of Q S_0 ... */
+    const int r1 = (warp & 3) * 16, c1 = (warp >> 2) * 16;
+    /* ... and, for the update, 16 rows of the state by all 32 columns (head_dim 128) or by 16 of them (head_dim 64) */
+    constexpr int NT4 = (D / 16 >= 8) ? 4 : 2;       /* 8-column tiles a warp in the update */
+    const int i4 = (D / 16 >= 8) ? warp * 16 : (warp & 3) * 16, c4 = (D / 16 >= 8) ? 0 : (warp >> 2) * 16;
 
     for (uint32_t c = 0; c < P.chunks; ++c) {
         const uint64_t t0 = P.row0 + (uint64_t)c * CH;
@@ -279,110 +301,153 @@ __global__ void __launch_bounds__(256, 1) deltanet_chunk_kernel(const ChunkParam
         cp_async_wait<1>();
         __syncthreads();
 
-        /* (1) K S_0 and Q S_0 together: rows 2ty, 2ty+1; columns 4tx..4tx+3 */
-        float ks[2][4] = {}, qs[2][4] = {};
+        /* (1) K S_0 and Q S_0: k and q are exact in TF32, the state goes in as two terms */
         {
-            const uint16_t* k0 = kr + (2 * ty) * LDH; const uint16_t* k1 = k0 + LDH;
-            const uint16_t* q0 = qr + (2 * ty) * LDH; const uint16_t* q1 = q0 + LDH;
-#pragma unroll 2
-            for (int i = 0; i < D; i += 4) {
-                float ka0[4], ka1[4], qa0[4], qa1[4];
-                unpack4<DT>(*reinterpret_cast<const uint2*>(k0 + i), ka0); unpack4<DT>(*reinterpret_cast<const uint2*>(k1 + i), ka1);
-                unpack4<DT>(*reinterpret_cast<const uint2*>(q0 + i), qa0); unpack4<DT>(*reinterpret_cast<const uint2*>(q1 + i), qa1);
+            float ak[2][4] = {}, aq[2][4] = {};
+            const uint16_t* kA = kr + (r1 + g8) * LDH + t4; const uint16_t* kB = kA + 8 * LDH;
+            const uint16_t* qA = qr + (r1 + g8) * LDH + t4; const uint16_t* qB = qA + 8 * LDH;
+            const float* sB = Ss + t4 * SP + c1 + g8;
+#pragma unroll 4
+            for (int k0 = 0; k0 < D; k0 += 8) {
+                const uint32_t k_0 = tf32_of<DT>(kA[k0]), k_1 = tf32_of<DT>(kB[k0]), k_2 = tf32_of<DT>(kA[k0 + 4]), k_3 = tf32_of<DT>(kB[k0 + 4]);
+                const uint32_t q_0 = tf32_of<DT>(qA[k0]), q_1 = tf32_of<DT>(qB[k0]), q_2 = tf32_of<DT>(qA[k0 + 4]), q_3 = tf32_of<DT>(qB[k0 + 4]);
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const float4 s4 = *reinterpret_cast<const float4*>(Ss + (i + u) * CNC + 4 * tx);
-                    const float sv4[4] = {s4.x, s4.y, s4.z, s4.w};
+                for (int j = 0; j < 2; ++j) {
+                    uint32_t h0, l0, h1, l1;
+                    tf32_split(sB[k0 * SP + 8 * j], h0, l0);
+                    tf32_split(sB[(k0 + 4) * SP + 8 * j], h1, l1);
+                    mma_tf32(ak[j], k_0, k_1, k_2, k_3, h0, h1); mma_tf32(ak[j], k_0, k_1, k_2, k_3, l0, l1);
+                    mma_tf32(aq[j], q_0, q_1, q_2, q_3, h0, h1); mma_tf32(aq[j], q_0, q_1, q_2, q_3, l0, l1);
+                }
+            }
+            /* R = V - diag(e^G / |k|) K S_0, and Q S_0 kept for the read-out */
 #pragma unroll
-                    for (int x = 0; x < 4; ++x) {
-                        ks[0][x] += ka0[u] * sv4[x]; ks[1][x] += ka1[u] * sv4[x];
-                        qs[0][x] += qa0[u] * sv4[x]; qs[1][x] += qa1[u] * sv4[x];
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int row = r1 + g8 + 8 * hh, col = c1 + 8 * j + 2 * t4;
+                    const float2 v2 = E::unpack2(*reinterpret_cast<const uint32_t*>(vr + row * CNC + col));
+                    const float a = va[row];
+                    *reinterpret_cast<float2*>(Rm + row * SP + col) = make_float2(v2.x - a * ak[j][2 * hh], v2.y - a * ak[j][2 * hh + 1]);
+                    *reinterpret_cast<float2*>(Qm + row * SP + col) = make_float2(aq[j][2 * hh], aq[j][2 * hh + 1]);
+                }
+        }
+        __syncthreads();
+        /* (2) D = A R, A lower triangular: both operands fp32, so three MMAs a step (hi·hi, hi·lo, lo·hi); a warp's 16 rows need
+         * only the k-steps up to their diagonal */
+        {
+            float ad[2][4] = {};
+            const float* aA = Am + (r1 + g8) * TL + t4; const float* aB = aA + 8 * TL;
+            const float* rB = Rm + t4 * SP + c1 + g8;
+            for (int k0 = 0; k0 < r1 + 16; k0 += 8) {
+                uint32_t ah[4], al[4];
+                tf32_split(aA[k0], ah[0], al[0]); tf32_split(aB[k0], ah[1], al[1]);
+                tf32_split(aA[k0 + 4], ah[2], al[2]); tf32_split(aB[k0 + 4], ah[3], al[3]);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    uint32_t h0, l0, h1, l1;
+                    tf32_split(rB[k0 * SP + 8 * j], h0, l0);
+                    tf32_split(rB[(k0 + 4) * SP + 8 * j], h1, l1);
+                    mma_tf32(ad[j], ah[0], ah[1], ah[2], ah[3], h0, h1);
+                    mma_tf32(ad[j], ah[0], ah[1], ah[2], ah[3], l0, l1);
+                    mma_tf32(ad[j], al[0], al[1], al[2], al[3], h0, h1);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh)
+                    *reinterpret_cast<float2*>(Dm + (r1 + g8 + 8 * hh) * SP + c1 + 8 * j + 2 * t4) = make_float2(ad[j][2 * hh], ad[j][2 * hh + 1]);
+        }
+        __syncthreads();
+        /* (3) O = diag(e^G / |q| / sqrt d) Q S_0 + M D the same way, rounded, with the block's sum of squares for the norm */
+        {
+            float ao[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int row = r1 + g8 + 8 * hh;
+                    const float2 q2 = *reinterpret_cast<const float2*>(Qm + row * SP + c1 + 8 * j + 2 * t4);
+                    ao[j][2 * hh] = vb[row] * q2.x; ao[j][2 * hh + 1] = vb[row] * q2.y;
+                }
+            const float* mA = Mm + (r1 + g8) * TL + t4; const float* mB = mA + 8 * TL;
+            const float* dB = Dm + t4 * SP + c1 + g8;
+            for (int k0 = 0; k0 < r1 + 16; k0 += 8) {
+                uint32_t ah[4], al[4];
+                tf32_split(mA[k0], ah[0], al[0]); tf32_split(mB[k0], ah[1], al[1]);
+                tf32_split(mA[k0 + 4], ah[2], al[2]); tf32_split(mB[k0 + 4], ah[3], al[3]);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    uint32_t h0, l0, h1, l1;
+                    tf32_split(dB[k0 * SP + 8 * j], h0, l0);
+                    tf32_split(dB[(k0 + 4) * SP + 8 * j], h1, l1);
+                    mma_tf32(ao[j], ah[0], ah[1], ah[2], ah[3], h0, h1);
+                    mma_tf32(ao[j], ah[0], ah[1], ah[2], ah[3], l0, l1);
+                    mma_tf32(ao[j], al[0], al[1], al[2], al[3], h0, h1);
+                }
+            }
+            /* a row's 32 columns are spread over two warps (16 each) and the four lanes of a group: fold in that order */
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int t = r1 + g8 + 8 * hh;
+                float sq = 0.f;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const uint16_t w0 = E::from_float(ao[j][2 * hh], hit), w1 = E::from_float(ao[j][2 * hh + 1], hit);
+                    const float f0 = E::to_float(w0), f1 = E::to_float(w1);
+                    sq += f0 * f0 + f1 * f1;
+                    if (t < n) {
+                        uint16_t* orow = P.out + ((uint64_t)b * P.rows + t0 + t) * vd + (uint64_t)h * D + j0 + c1 + 8 * j + 2 * t4;
+                        *reinterpret_cast<uint32_t*>(orow) = (uint32_t)w0 | ((uint32_t)w1 << 16);
                     }
                 }
+                sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+                sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+                if (t4 == 0) Qs[(warp >> 2) * CH + t] = sq;
             }
         }
-        /* R = V - diag(e^G / |k|) K S_0 */
-#pragma unroll
-        for (int rr = 0; rr < 2; ++rr) {
-            float v4[4];
-            unpack4<DT>(*reinterpret_cast<const uint2*>(vr + (2 * ty + rr) * CNC + 4 * tx), v4);
-            const float a = va[2 * ty + rr];
-            *reinterpret_cast<float4*>(Rm + (2 * ty + rr) * CNC + 4 * tx) =
-                make_float4(v4[0] - a * ks[rr][0], v4[1] - a * ks[rr][1], v4[2] - a * ks[rr][2], v4[3] - a * ks[rr][3]);
-        }
         __syncthreads();
-        /* (2) D = A R, A lower triangular */
-        float dd[2][4] = {};
-        for (int s = 0; s <= 2 * ty + 1; ++s) {
-            const float4 r4 = *reinterpret_cast<const float4*>(Rm + s * CNC + 4 * tx);
-            const float a0 = Am[(2 * ty) * TL + s], a1 = Am[(2 * ty + 1) * TL + s];
-            dd[0][0] += a0 * r4.x; dd[0][1] += a0 * r4.y; dd[0][2] += a0 * r4.z; dd[0][3] += a0 * r4.w;
-            dd[1][0] += a1 * r4.x; dd[1][1] += a1 * r4.y; dd[1][2] += a1 * r4.z; dd[1][3] += a1 * r4.w;
-        }
-#pragma unroll
-        for (int rr = 0; rr < 2; ++rr)
-            *reinterpret_cast<float4*>(Dm + (2 * ty + rr) * CNC + 4 * tx) = make_float4(dd[rr][0], dd[rr][1], dd[rr][2], dd[rr][3]);
+        if (tid < n) P.ss[(((uint64_t)b * P.rows + t0 + tid) * P.v_heads + h) * CB + cb] = Qs[tid] + Qs[CH + tid];
+        /* the state update reads D scaled by e^(G_C - G_t) / |k_t|: scale it in place (every reader of D passed the barrier above) */
+        for (int i = tid; i < CH * CNC; i += 256) Dm[(i / CNC) * SP + i % CNC] *= vc[i / CNC];
         __syncthreads();
-        /* (3) O = diag(e^G / |q| / sqrt d) Q S_0 + M D, rounded, with the block's sum of squares for the norm */
-        float oo[2][4];
-#pragma unroll
-        for (int rr = 0; rr < 2; ++rr)
-#pragma unroll
-            for (int x = 0; x < 4; ++x) oo[rr][x] = vb[2 * ty + rr] * qs[rr][x];
-        for (int s = 0; s <= 2 * ty + 1; ++s) {
-            const float4 d4 = *reinterpret_cast<const float4*>(Dm + s * CNC + 4 * tx);
-            const float m0 = Mm[(2 * ty) * TL + s], m1 = Mm[(2 * ty + 1) * TL + s];
-            oo[0][0] += m0 * d4.x; oo[0][1] += m0 * d4.y; oo[0][2] += m0 * d4.z; oo[0][3] += m0 * d4.w;
-            oo[1][0] += m1 * d4.x; oo[1][1] += m1 * d4.y; oo[1][2] += m1 * d4.z; oo[1][3] += m1 * d4.w;
-        }
-#pragma unroll
-        for (int rr = 0; rr < 2; ++rr) {
-            const int t = 2 * ty + rr;
-            float sq = 0.f;
-            uint16_t w[4];
-#pragma unroll
-            for (int x = 0; x < 4; ++x) { w[x] = E::from_float(oo[rr][x], hit); const float f = E::to_float(w[x]); sq += f * f; }
-            for (int x = 1; x < 8; x <<= 1) sq += __shfl_xor_sync(0xffffffffu, sq, x);
-            if (t < n) {
-                uint16_t* orow = P.out + ((uint64_t)b * P.rows + t0 + t) * vd + (uint64_t)h * D + j0 + 4 * tx;
-                *reinterpret_cast<uint2*>(orow) = make_uint2((uint32_t)w[0] | ((uint32_t)w[1] << 16), (uint32_t)w[2] | ((uint32_t)w[3] << 16));
-                if (tx == 0) P.ss[(((uint64_t)b * P.rows + t0 + t) * P.v_heads + h) * CB + cb] = sq;
-            }
-        }
-        /* the state update reads D scaled by e^(G_C - G_t) / |k_t|: scale it in place (every reader of D is past) */
-        __syncthreads();
-        for (int i = tid; i < CH * CNC; i += 256) Dm[i] *= vc[i / CNC];
-        __syncthreads();
-        /* (4) S = e^(G_C) S_0 + K^T D': D/32 rows of the state a thread, columns 4tx..+3 */
+        /* (4) S = e^(G_C) S_0 + K^T D' on the tensor cores: a warp owns its rows of the state, reads and writes nobody else's */
         {
-            constexpr int RP = D / 32;                 /* state rows a thread */
-            const int i0 = (tid >> 3) * RP;
-            float acc[RP][4];
+            float acc[NT4][4];
             const float g = gc[0];
 #pragma unroll
-            for (int a = 0; a < RP; ++a) {
-                const float4 s4 = *reinterpret_cast<const float4*>(Ss + (i0 + a) * CNC + 4 * tx);
-                acc[a][0] = g * s4.x; acc[a][1] = g * s4.y; acc[a][2] = g * s4.z; acc[a][3] = g * s4.w;
-            }
-#pragma unroll 4
-            for (int t = 0; t < CH; ++t) {
-                const float4 d4 = *reinterpret_cast<const float4*>(Dm + t * CNC + 4 * tx);
-                float kv[4];
-                if constexpr (RP == 4) unpack4<DT>(*reinterpret_cast<const uint2*>(kr + t * LDH + i0), kv);
-                else { const float2 k2 = E::unpack2(*reinterpret_cast<const uint32_t*>(kr + t * LDH + i0)); kv[0] = k2.x; kv[1] = k2.y; }
+            for (int j = 0; j < NT4; ++j)
 #pragma unroll
-                for (int a = 0; a < RP; ++a) {
-                    acc[a][0] += kv[a] * d4.x; acc[a][1] += kv[a] * d4.y; acc[a][2] += kv[a] * d4.z; acc[a][3] += kv[a] * d4.w;
+                for (int hh = 0; hh < 2; ++hh) {
+                    const float2 s2 = *reinterpret_cast<const float2*>(Ss + (i4 + g8 + 8 * hh) * SP + c4 + 8 * j + 2 * t4);
+                    acc[j][2 * hh] = g * s2.x; acc[j][2 * hh + 1] = g * s2.y;
+                }
+            const uint16_t* kT = kr + t4 * LDH + i4 + g8;           /* K^T[i][p] = K[p][i] */
+            const float* dB = Dm + t4 * SP + c4 + g8;
+#pragma unroll 2
+            for (int p0 = 0; p0 < CH; p0 += 8) {
+                const uint32_t a0 = tf32_of<DT>(kT[p0 * LDH]), a1 = tf32_of<DT>(kT[p0 * LDH + 8]);
+                const uint32_t a2 = tf32_of<DT>(kT[(p0 + 4) * LDH]), a3 = tf32_of<DT>(kT[(p0 + 4) * LDH + 8]);
+#pragma unroll
+                for (int j = 0; j < NT4; ++j) {
+                    uint32_t h0, l0, h1, l1;
+                    tf32_split(dB[p0 * SP + 8 * j], h0, l0);
+                    tf32_split(dB[(p0 + 4) * SP + 8 * j], h1, l1);
+                    mma_tf32(acc[j], a0, a1, a2, a3, h0, h1); mma_tf32(acc[j], a0, a1, a2, a3, l0, l1);
                 }
             }
-            __syncthreads();                           /* every thread has read the old state and this chunk's stage */
 #pragma unroll
-            for (int a = 0; a < RP; ++a) *reinterpret_cast<float4*>(Ss + (i0 + a) * CNC + 4 * tx) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+            for (int j = 0; j < NT4; ++j)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh)
+                    *reinterpret_cast<float2*>(Ss + (i4 + g8 + 8 * hh) * SP + c4 + 8 * j + 2 * t4) = make_float2(acc[j][2 * hh], acc[j][2 * hh + 1]);
         }
+        __syncthreads();                               /* every warp is done with this chunk's stage before the next fetch overwrites it */
     }
     cp_async_wait<0>();
     __syncthreads();
-    for (int i = tid; i < D * CNC; i += 256) Sg[(uint64_t)(i / CNC) * D + j0 + i % CNC] = Ss[i];
+    for (int i = tid; i < D * CNC; i += 256) Sg[(uint64_t)(i / CNC) * D + j0 + i % CNC] = Ss[(i / CNC) * SP + i % CNC];
     if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
 }
 
