@@ -93,6 +93,8 @@ class Port:
             "oracle_hadamard_blocks": [vp, vp, vp, u64, u64, u64],
             "oracle_turboquant_encode_rows": [vp, vp, vp, u64, u64, u64],
             "oracle_attention_residual_tq": [vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u64],
+            "oracle_hadamard_rotate": [vp, vp, vp, u64],
+            "oracle_turboquant_gemv": [vp, vp, vp, vp, u64, u64, u64],
         }
         for name, args in sig.items():
             fn = getattr(self.lib, name)
@@ -361,6 +363,28 @@ def residual_tq(impl, q, kcodes, kscales, vcodes, vscales, qh, kvh, dh, length, 
         impl.nn.attention_residual_mix_tq(_p(res), _p(p), _p(vcodes), _p(vscales), qh, kvh, dh, length, d)
         impl.wait()
     return res
+
+
+def hadamard_rotate(impl, x, sign):
+    """The rotation over a whole row (hadamard_rotate): blocks of 512, then a 256 and a 128."""
+    out = np.zeros_like(x)
+    if isinstance(impl, Port):
+        impl.lib.oracle_hadamard_rotate(_p(out), _p(x), _p(sign), x.size)
+    else:
+        impl.nn.hadamard_rotate(_p(out), _p(x), _p(sign), x.size, _p(impl.over))
+        impl.wait()
+    return out
+
+
+def tq_gemv(impl, codes, luts, x, d, rows, cols):
+    """turboquant_gemv: a coded matrix of `rows` rows times the 16-bit vector x."""
+    out = np.zeros(rows, np.uint16)
+    if isinstance(impl, Port):
+        impl.lib.oracle_turboquant_gemv(_p(out), _p(codes), _p(luts), _p(x), d, rows, cols)
+    else:
+        impl.nn.turboquant_gemv(_p(out), _p(codes), codes.nbytes, _p(luts), luts.nbytes, _p(x), d, rows, cols, _p(impl.over))
+        impl.wait()
+    return out
 
 
 _port = None

@@ -491,3 +491,38 @@ void oracle_attention_gate_rows(uint16_t* o, const uint16_t* att, const uint16_t
         o[i] = f32_to_f16(f16_to_f32(att[i]) * f16_to_f32(gate), 0);
     }
 }
+
+/* ---- the weight path's doors a mixer runs around its attention ------------------------------------------------------
+ * hadamard_rotate (kernels.cuh:2189-2231): the block rotation H·(S ⊙ u)/sqrt(b) over a row of n — blocks of 512, then one of
+ * 256 and one of 128 for what is left; a row shorter than 512 is one block of n.  Four running sums, columns c mod 4. */
+void oracle_hadamard_rotate(uint16_t* out, const uint16_t* in, const uint16_t* sign, uint64_t n) {
+    const uint64_t whole = n < 512 ? 0 : (n / 512) * 512, rest = n - whole;
+    for (uint64_t i = 0; i < n; ++i) {
+        uint64_t a = 0, b = n;
+        if (i < whole) { a = i - i % 512; b = 512; }
+        else if (whole != 0) {
+            if (rest >= 256 && i < whole + 256) { a = whole; b = 256; }
+            else { a = whole + (rest >= 256 ? 256 : 0); b = 128; }
+        }
+        const uint64_t r = i - a;
+        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        uint64_t c = 0;
+        for (; c + 4 <= b; c += 4)
+            for (int k = 0; k < 4; ++k) {
+                const float v = f16_to_f32(in[a + c + k]) * f16_to_f32(sign[c + k]);
+                s[k] += (__builtin_popcountll(r & (c + k)) & 1) ? -v : v;
+            }
+        for (; c < b; ++c) { const float v = f16_to_f32(in[a + c]) * f16_to_f32(sign[c]); s[0] += (__builtin_popcountll(r & c) & 1) ? -v : v; }
+        out[i] = f32_to_f16(((s[0] + s[1]) + (s[2] + s[3])) / sqrtf((float)b), 0);
+    }
+}
+/* turboquant_gemv (kernels.cuh:1405-1447): out[r] = half(scale_r · sum_c level(code[r][c]) · x[c]); the sum in column order */
+void oracle_turboquant_gemv(uint16_t* out, const uint8_t* weights, const uint8_t* luts, const uint16_t* x, uint64_t d, uint64_t rows, uint64_t cols) {
+    const uint64_t need = tq_row_bytes(d, cols);
+    for (uint64_t r = 0; r < rows; ++r) {
+        float part = 0.0f;
+        for (uint64_t c = 0; c < cols; ++c) part += tq_element(weights + r * need, 1.0f, d, c) * f16_to_f32(x[c]);
+        const float scale = d == 16 ? 1.0f : f16_to_f32((uint16_t)((uint32_t)luts[r * 2] | ((uint32_t)luts[r * 2 + 1] << 8)));
+        out[r] = f32_to_f16(part * scale, 0);
+    }
+}

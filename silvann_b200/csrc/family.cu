@@ -571,6 +571,37 @@ static void d_attention_residual_mix_tq_rows(float* res, const float* p, const s
     check("attention_residual_mix_tq_rows", sv::tq_residual_mix_launch(res, p, codes, scales, qh, kvh, dh, length, d, rows, 0));
 }
 
+/* ---- the weight path's doors a mixer verb cannot run without, as worded (tq.cu) ---- */
+static void d_hadamard_rotate(sv_h16* out, const sv_h16* in, const sv_h16* sign, sv_u64 n, sv_fault* over) {
+    flush();
+    const bool apart = !(out < in + n && in < out + n);           /* a lane reads the whole block it writes into */
+    const bool shaped = n != 0 && (n < 512 ? (n & (n - 1)) == 0 : (n % 512) % 128 == 0);
+    if (!apart || !shaped) { launch_refused("hadamard_rotate", cudaSuccess); return; }
+    check("hadamard_rotate", sv::hadamard_rotate_launch(out, in, sign, n, over, 0));
+}
+static void d_rmsnorm_rotate(sv_h16* rot, sv_h16* o, const sv_h16* x, const sv_h16* w, const sv_h16* sign, sv_u64 n, float eps, sv_fault* over) {
+    d_rmsnorm(o, x, w, n, eps, over);                             /* nn's definition: the two doors, one after the other */
+    d_hadamard_rotate(rot, o, sign, n, over);
+}
+static void d_turboquant_gemv(sv_h16* out, const sv_u8* weights, sv_u64 w_room, const sv_u8* luts, sv_u64 l_room, const sv_h16* x, sv_u64 d,
+                              sv_u64 rows, sv_u64 cols, sv_fault* over) {
+    flush();
+    if (!sv::tq_width_ok(d)) { launch_refused("turboquant_gemv", cudaSuccess); return; }
+    if (rows == 0 || cols == 0) return;
+    sv_tq_groups g;
+    memset(&g, 0, sizeof g);
+    g.codes[0] = (sv_u64)(uintptr_t)weights; g.luts[0] = (sv_u64)(uintptr_t)luts; g.rows[0] = rows; g.d[0] = d; g.out_at[0] = 0; g.count = 1;
+    check("turboquant_gemv", sv::tq_gemv_groups_launch(out, &g, w_room ? w_room : 1, l_room ? l_room : 1, x, cols, over, 0));
+}
+static void d_turboquant_gemv_groups(sv_h16* out, sv_tq_groups g, const sv_h16* x, sv_u64 cols, sv_fault* over) {
+    flush();
+    if (g.count == 0 || cols == 0) return;
+    if (g.count > 12) { launch_refused("turboquant_gemv_groups", cudaSuccess); return; }
+    const cudaError_t e = sv::tq_gemv_groups_launch(out, &g, 0, 0, x, cols, over, 0);
+    if (e == cudaErrorInvalidValue) { (void)cudaGetLastError(); launch_refused("turboquant_gemv_groups", cudaSuccess); return; }
+    check("turboquant_gemv_groups", e);
+}
+
 /* ================================================================================================================ */
 /* tables and the entry                                                                                             */
 
@@ -624,6 +655,10 @@ static void install_doors() {
     g_nn.rope_angles_mrope_rows = d_rope_angles_mrope_rows;
     g_nn.rope_angles_axial_rows = d_rope_angles_axial_rows;
     g_nn.attention_gate_rows = d_attention_gate_rows;
+    g_nn.hadamard_rotate = d_hadamard_rotate;
+    g_nn.rmsnorm_rotate = d_rmsnorm_rotate;
+    g_nn.turboquant_gemv = d_turboquant_gemv;
+    g_nn.turboquant_gemv_groups = d_turboquant_gemv_groups;
     g_nn.turboquant_decode = d_turboquant_decode;
     g_nn.hadamard_blocks = d_hadamard_blocks;
     g_nn.turboquant_encode_rows = d_turboquant_encode_rows;

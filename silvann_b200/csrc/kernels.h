@@ -114,6 +114,9 @@ cudaError_t tq_encode_rows_launch(uint8_t* codes, uint16_t* scales, const uint16
                                   unsigned int* over, cudaStream_t st);
 cudaError_t tq_weights_launch(float* p, float* res, const uint16_t* q, const uint8_t* codes, const uint16_t* scales, uint64_t qh, uint64_t kvh,
                               uint64_t d_head, uint64_t length, uint64_t d, uint64_t rows, cudaStream_t st);
+cudaError_t hadamard_rotate_launch(uint16_t* out, const uint16_t* in, const uint16_t* sign, uint64_t n, unsigned int* over, cudaStream_t st);
+cudaError_t tq_gemv_groups_launch(uint16_t* out, const void* groups /* sv_tq_groups */, uint64_t w_room, uint64_t l_room, const uint16_t* x,
+                                  uint64_t cols, unsigned int* over, cudaStream_t st);
 /* the pair weights_tq + residual_mix_tq as one kernel, codes expanded in flight (tq_decode.cu) */
 bool tq_attend_fits(const void* q, const void* kcodes, const void* kscales, const void* vcodes, const void* vscales, uint64_t qh, uint64_t kvh,
                     uint64_t dh, uint64_t length, uint64_t d);

@@ -16,6 +16,7 @@
  * The fast path (one fused kernel for the weights/mix pair, codes expanded in flight) is tq_decode.cu. */
 #include "common.cuh"
 #include "kernels.h"
+#include <string.h>
 
 namespace sv {
 
@@ -211,6 +212,74 @@ __global__ void __launch_bounds__(256) tq_residual_mix_kernel(float* res, const 
     }
 }
 
+/* ---- the weight path's three doors a mixer cannot run without, AS WORDED (block a row; not a fast path) -------------
+ * hadamard_rotate (kernels.cuh:2189-2231): the rotation over a row of n in blocks of 512, then a 256 and a 128 for what
+ * is left (a row shorter than 512 is one block); a lane an output, four running sums as the reference adds them.
+ * turboquant_gemv (:1405-1447): out[r] = half(scale_r · sum_c level(code[r][c]) · x[c]), a row its room does not hold
+ * skipped.  turboquant_gemv_groups (:1453-1461): the gemv once a group over one shared x. */
+__global__ void __launch_bounds__(256) hadamard_rotate_kernel(uint16_t* out, const uint16_t* in, const uint16_t* sign, uint64_t n, unsigned int* over) {
+    const uint64_t whole = n < 512 ? 0 : (n / 512) * 512, rest = n - whole;
+    bool hit = false;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t a = 0, b = n;
+        if (i < whole) { a = i - i % 512; b = 512; }
+        else if (whole != 0) {
+            if (rest >= 256 && i < whole + 256) { a = whole; b = 256; }
+            else { a = whole + (rest >= 256 ? 256 : 0); b = 128; }
+        }
+        const uint64_t r = i - a;
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        uint64_t c = 0;
+        for (; c + 4 <= b; c += 4)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const float v = H::to_float(in[a + c + x]) * H::to_float(sign[c + x]);
+                s[x] += (__popcll(r & (c + x)) & 1) ? -v : v;
+            }
+        for (; c < b; ++c) { const float v = H::to_float(in[a + c]) * H::to_float(sign[c]); s[0] += (__popcll(r & c) & 1) ? -v : v; }
+        out[i] = H::from_float(((s[0] + s[1]) + (s[2] + s[3])) / sqrtf((float)b), hit);
+    }
+    if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
+}
+
+struct GemvGroups { uint64_t codes[12], luts[12], rows[12], d[12], out_at[12], count; };
+
+__global__ void __launch_bounds__(128) tq_gemv_groups_kernel(uint16_t* out, GemvGroups g, uint64_t w_room0, uint64_t l_room0, const uint16_t* x,
+                                                             uint64_t cols, unsigned int* over) {
+    __shared__ float sh[4];
+    bool hit = false;
+    uint64_t row0 = 0;
+    for (uint64_t i = 0; i < g.count && i < 12; ++i) {
+        const uint64_t d = g.d[i], per = 16 / d, row_bytes = tq_row_bytes(d, cols), units = (cols + per - 1) / per;
+        const uint8_t* weights = (const uint8_t*)g.codes[i];
+        const uint8_t* luts = (const uint8_t*)g.luts[i];
+        const uint64_t w_room = g.count == 1 && w_room0 ? w_room0 : g.rows[i] * row_bytes, l_room = g.count == 1 && l_room0 ? l_room0 : g.rows[i] * 2;
+        const uint64_t rows_held = row_bytes == 0 ? 0 : w_room / row_bytes, scales_held = l_room / 2;
+        const uint32_t mask = (uint32_t)((1ull << d) - 1ull);
+        for (uint64_t r = blockIdx.x; r < g.rows[i]; r += gridDim.x) {
+            if (r >= rows_held || (d != 16 && r >= scales_held)) continue;        /* the whole block skips it together */
+            const uint8_t* row = weights + r * row_bytes;
+            float part = 0.f;
+            for (uint64_t u = threadIdx.x; u < units; u += blockDim.x) {
+                const uint32_t unit = (uint32_t)row[u * 2] | ((uint32_t)row[u * 2 + 1] << 8);
+                const uint64_t c0 = u * per;
+                for (uint64_t s = 0; s < per && c0 + s < cols; ++s) part += tq_level(d, (unit >> (uint32_t)(d * s)) & mask) * H::to_float(x[c0 + s]);
+            }
+            for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = part;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const float scale = d == 16 ? 1.0f : H::to_float((uint16_t)((uint32_t)luts[r * 2] | ((uint32_t)luts[r * 2 + 1] << 8)));
+                out[g.out_at[i] + r] = H::from_float(((sh[0] + sh[1]) + (sh[2] + sh[3])) * scale, hit);
+            }
+            __syncthreads();
+        }
+        row0 += g.rows[i];
+    }
+    (void)row0;
+    if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
+}
+
 /* ---------------------------------------------------------------------------------------------------------- */
 
 static inline unsigned tq_grid(uint64_t items, unsigned cap = 4096u) { return (unsigned)(items < 1 ? 1 : (items > cap ? cap : items)); }
@@ -246,6 +315,24 @@ cudaError_t tq_residual_mix_launch(float* res, const float* p, const uint8_t* co
                                    uint64_t d_head, uint64_t length, uint64_t d, uint64_t rows, cudaStream_t st) {
     const unsigned threads = d_head >= 256 ? 256u : (d_head >= 128 ? 128u : 64u);
     tq_residual_mix_kernel<<<tq_grid(rows * qh), threads, 0, st>>>(res, p, codes, scales, qh, kvh, d_head, length, d, rows);
+    note_launch(1);
+    return cudaGetLastError();
+}
+
+cudaError_t hadamard_rotate_launch(uint16_t* out, const uint16_t* in, const uint16_t* sign, uint64_t n, unsigned int* over, cudaStream_t st) {
+    hadamard_rotate_kernel<<<tq_grid((n + 255) / 256), 256, 0, st>>>(out, in, sign, n, over);
+    note_launch(1);
+    return cudaGetLastError();
+}
+/* `g` is the by-value groups struct of the door (codes, luts, rows, d, out_at a group, then the count); one group with the
+ * rooms given is turboquant_gemv itself */
+cudaError_t tq_gemv_groups_launch(uint16_t* out, const void* g, uint64_t w_room, uint64_t l_room, const uint16_t* x, uint64_t cols,
+                                  unsigned int* over, cudaStream_t st) {
+    GemvGroups gg;
+    memcpy(&gg, g, sizeof gg);
+    uint64_t most = 1;
+    for (uint64_t i = 0; i < gg.count && i < 12; ++i) { if (!tq_width_known(gg.d[i])) return cudaErrorInvalidValue; if (gg.rows[i] > most) most = gg.rows[i]; }
+    tq_gemv_groups_kernel<<<tq_grid(most, 148u * 16u), 128, 0, st>>>(out, gg, w_room, l_room, x, cols, over);
     note_launch(1);
     return cudaGetLastError();
 }

@@ -21,7 +21,7 @@ REF_DIR = ROOT / "oracle" / "_ref"
 
 # What nn's package init sizes its rooms from at a boot; a boot with any of these lines left out is refused.  The
 # classes are small except `main`, which holds the K and V planes of the cases below.
-_DEVICE_POOLS = {"resid": (4096, 8), "main": (16 << 20, 10), "attn_out": (4096, 4), "logits": (8192, 1), "partials": (4096, 4)}
+_DEVICE_POOLS = {"resid": (4096, 48), "main": (16 << 20, 10), "attn_out": (1 << 20, 16), "logits": (8192, 1), "partials": (65536, 32)}
 _RAM_POOLS = {"result": (65536, 16), "experts": (4096, 1), "table": (128, 1)}
 _CARTRIDGES = {"sink": 4, "tq4": 16, "tq6": 16, "fp32": 16}
 
@@ -83,26 +83,16 @@ class Session:
     def buf(self, ref):
         return (self.OBJ, 0, ref)
 
-    def run(self, name, *args):
+    def run(self, name, *args, keep=False):
         """Runs `(name args...)`; an int argument is a number, a Buffer an object reference.  Answers (kind, value) and
-        raises when the machine's fault channel says a door or the verb refused."""
-        cells = [self.verb(name)] + [self.buf(a.ref) if isinstance(a, Buffer) else self.integer(a) for a in args]
-        e = self.e
-        prog = e.create_executable(cells)
-        pic = e.freeze(prog)
-        try:
-            got = e.execute((self.OBJ, 0, self.env), pic)
-        finally:
-            e.release(pic[2])
-            e.release(prog[2])
-        fault = e.sys.fault()
-        if fault["raised"] != 0:
-            e.sys.fault_clear()
-            raise RuntimeError(f"({name} ...) raised {fault}; answered {got}")
-        return got
+        raises when the machine's fault channel says a door or the verb refused.  An answer that is an object arrives with
+        a hold of its own (nothing the engine's interface hands out frees itself, pybind.cuh:510-512): it is given back
+        here unless the caller keeps the object — a verb that answers its output buffer would otherwise pin that buffer
+        out of its pool for good."""
+        return self.run_cells(name, [self.buf(a.ref) if isinstance(a, Buffer) else self.integer(a) for a in args], keep=keep)
 
     def buffer(self, nbytes: int, payload: bytes | None = None) -> "Buffer":
-        kind, ref = self.run("nn__buffer__getnew", nbytes)
+        kind, ref = self.run("nn__buffer__getnew", nbytes, keep=True)
         if kind != self.OBJ:
             raise RuntimeError(f"a {nbytes}-byte buffer was refused: {self.e.sys.fault()}")
         at = self.e.sys.peek(self.e.sys.full_address(ref))[2][0]
@@ -111,6 +101,48 @@ class Session:
             b.write(payload)
         self.held.append(b)
         return b
+
+    def table(self, cells) -> int:
+        """A node array of `cells` — a Buffer is an object reference, an int a number — as a model's verbs take their
+        planes (the reference builds one with `(sys__create kind n)` and `(sys__node_array__set t i cell)`, machine.py:642-647).
+        Answers the table's reference; release it with `release()`."""
+        kind, ref = self._run_cells([self.verb("sys__create"), self.integer(self.K["sys__node_array"]), self.integer(len(cells))])
+        if kind != self.K["sys__quoted_list"]:       # a constructor answers a datum: the reference, tagged quoted
+            raise RuntimeError(f"a table of {len(cells)} cells was refused: ({kind}, {ref}) {self.e.sys.fault()}")
+        for i, c in enumerate(cells):
+            cell = self.buf(c.ref) if isinstance(c, Buffer) else self.integer(c)
+            got = self._run_cells([self.verb("sys__node_array__set"), self.buf(ref), self.integer(i), cell])
+            fault = self.e.sys.fault()
+            if fault["raised"] != 0:
+                self.e.sys.fault_clear()
+                raise RuntimeError(f"cell {i} of the table was refused: {got} {fault}")
+            if got[0] == self.OBJ:
+                self.e.release(got[1])                   # the verb answers the value set, with a hold of the answer's own
+        return ref
+
+    def run_cells(self, name, cells, keep=False):
+        """`(name cells...)` with the cells given as (kind, verb, value) triples already."""
+        got = self._run_cells([self.verb(name)] + list(cells))
+        fault = self.e.sys.fault()
+        if fault["raised"] != 0:
+            self.e.sys.fault_clear()
+            raise RuntimeError(f"({name} ...) raised {fault}; answered {got}")
+        if not keep and got[0] in (self.OBJ, self.K["sys__quoted_list"]):
+            self.e.release(got[1])
+        return got
+
+    def _run_cells(self, cells):
+        e = self.e
+        prog = e.create_executable(cells)
+        pic = e.freeze(prog)
+        try:
+            return e.execute((self.OBJ, 0, self.env), pic)
+        finally:
+            e.release(pic[2])
+            e.release(prog[2])
+
+    def release(self, ref):
+        self.e.release(ref)
 
     def release_buffers(self):
         for b in self.held:

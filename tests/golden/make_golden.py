@@ -170,6 +170,36 @@ def main():
     R.nn.vector_copy_rows(P_(dst), 40, P_(src), 50, 33, 4); R.wait()
     out["mx_copy_src"], out["mx_copy_dst"] = src, dst
 
+    # the weight path's doors a mixer runs around its attention: the whole-row rotation, a coded matrix times a vector
+    # (alone and as groups over one vector), the norm and rotation in one door
+    from silvann_b200.abi import TqGroups
+    sign512 = to_bits(np.where(rng.random(512) < 0.5, -1.0, 1.0).astype(np.float32), 0)
+    out["wp_sign"] = sign512
+    for n in (96, 512, 896, 1152):
+        x = bits((n,))
+        out[f"wp_rot_x_{n}"], out[f"wp_rot_o_{n}"] = x, oracle.hadamard_rotate(R, x, sign512)
+    cols = 384
+    xv = bits((cols,))
+    out["wp_gemv_x"] = xv
+    mats = {}
+    for d, rows_ in ((4, 48), (8, 20), (5, 9)):
+        codes, scales = oracle.tq_encode_rows(R, bits((rows_, cols), 0.05), d)
+        mats[d] = (codes, scales, rows_)
+        out[f"wp_gemv_codes_{d}"], out[f"wp_gemv_scales_{d}"] = codes, scales
+        out[f"wp_gemv_o_{d}"] = oracle.tq_gemv(R, codes, scales.view(np.uint8).copy(), xv, d, rows_, cols)
+    g = TqGroups()
+    og = np.zeros(48 + 20, np.uint16)
+    for i, d in enumerate((4, 8)):
+        codes, scales, rows_ = mats[d]
+        g.codes[i], g.luts[i], g.rows[i], g.d[i], g.out_at[i] = codes.ctypes.data, scales.ctypes.data, rows_, d, (0, 48)[i]
+    g.count = 2
+    R.nn.turboquant_gemv_groups(P_(og), g, P_(xv), cols, P_(over)); R.wait()
+    out["wp_groups_o"] = og
+    xn, wn = bits((896,)), bits((896,))
+    hn, hr = np.zeros(896, np.uint16), np.zeros(896, np.uint16)
+    R.nn.rmsnorm_rotate(P_(hr), P_(hn), P_(xn), P_(wn), P_(sign512), 896, np.float32(1e-6), P_(over)); R.wait()
+    out["wp_nr_x"], out["wp_nr_w"], out["wp_nr_h"], out["wp_nr_hrot"] = xn, wn, hn, hr
+
     path = Path(__file__).with_name("reference_x86_avx2.npz")
     np.savez_compressed(path, **out)
     print(path, path.stat().st_size, "bytes,", len(out), "arrays")

@@ -148,6 +148,77 @@ def _tq_forms(s, reference, exact):
         s.release_buffers()
 
 
+# the tiered mixer's table (engine/src/packages/ai_qwen_3/contracts/objects/mixer.cuh:56-107): seventeen planes, eleven
+# numbers, eleven planes of the tiers, three tier sizes
+MIX = dict(H=512, QH=4, KVH=2, HD=128, ROT=64, D_Q=4, D_K=8, D_V=4, D_O=8, THETA=10000, SINK=4, HOT=8, WARM=8, STEPS=30)
+
+
+def _coded(reference, rng, rows, cols, d):
+    w = to_bits((rng.standard_normal((rows, cols)) / np.sqrt(cols)).astype(np.float32), FP16)
+    return oracle.tq_encode_rows(reference, w, d)
+
+
+def _tiered_mixer(s, reference):
+    """`(ai_qwen_3__attention_tiered x planes pos h1)` (engine/src/packages/ai_qwen_3/cpu/opcodes/mixer__abi.cuh:262-432), a
+    position at a time from an empty cache until the sink, the hot ring and the warm ring are full and the cold tier has
+    rows: the reference's whole attention mixer — norm and rotation, four coded projections, head norms, RoPE, the tiers'
+    bookkeeping (rotate, encode at 8 bits, decode and encode again at 4), a residual a tier merged into one softmax, the
+    gate, the out projection, the residual add — about forty door calls a position.  Answers h1 of every position and the
+    tiers as they stand at the end."""
+    m = MIX
+    H, qh, kvh, hd, rot = m["H"], m["QH"], m["KVH"], m["HD"], m["ROT"]
+    qw, kvw = qh * hd, kvh * hd
+    rng = np.random.default_rng(53)
+    mats = [_coded(reference, rng, 2 * qw, H, m["D_Q"]), _coded(reference, rng, kvw, H, m["D_K"]),
+            _coded(reference, rng, kvw, H, m["D_V"]), _coded(reference, rng, H, qw, m["D_O"])]
+    norms = [to_bits((1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32), FP16) for n in (H, hd, hd)]
+    signs = to_bits(np.where(rng.random(512) < 0.5, -1.0, 1.0).astype(np.float32), FP16)
+    xs = to_bits(rng.standard_normal((m["STEPS"], H)).astype(np.float32), FP16)
+    cold_rows = m["STEPS"] - m["SINK"] - m["HOT"] - m["WARM"]
+    rb8, rb4 = oracle.tq_row_bytes(8, hd), oracle.tq_row_bytes(4, hd)
+    rw = 4 * qh * (hd + 2)
+
+    def filled(a):
+        return s.buffer(a.nbytes, a.tobytes())
+
+    def room(nbytes):
+        return s.buffer(nbytes, bytes(nbytes))
+
+    planes = [filled(norms[0]),
+              filled(mats[0][0]), filled(mats[0][1]), filled(mats[1][0]), filled(mats[1][1]),
+              filled(mats[2][0]), filled(mats[2][1]), filled(mats[3][0]), filled(mats[3][1]),
+              filled(norms[1]), filled(norms[2]),
+              room(2 * m["SINK"] * kvw), room(2 * m["SINK"] * kvw),                           # the sink's keys and values
+              room(4 * rot),                                                                   # this position's angles
+              room(4 * qh * max(m["SINK"], m["HOT"], m["WARM"], cold_rows)),                   # scores
+              filled(signs),
+              room(2 * (2 * H + 2 * qw + kvw + 5 * qw + H))]                                    # the attention's scratch
+    numbers = [H, qh, kvh, hd, rot, m["D_Q"], m["D_K"], m["D_V"], m["D_O"], m["THETA"], 0]
+    tiers = [room(2 * m["HOT"] * kvw), room(2 * m["HOT"] * kvw),
+             room(m["WARM"] * kvh * rb8), room(2 * m["WARM"] * kvh), room(m["WARM"] * kvh * rb8), room(2 * m["WARM"] * kvh),
+             room(cold_rows * kvh * rb4), room(2 * cold_rows * kvh), room(cold_rows * kvh * rb4), room(2 * cold_rows * kvh),
+             room(4 * rw + 2 * (2 * qw + 3 * kvw))]
+    table = s.table(planes + numbers + tiers + [m["SINK"], m["HOT"], m["WARM"]])
+    xb, hb = room(2 * H), room(2 * H)
+    angles = planes[13]
+    pairs = rot // 2
+    freq = np.float64(m["THETA"]) ** (-2.0 * np.arange(pairs) / rot)
+    h1 = np.zeros((m["STEPS"], H), np.uint16)
+    for pos in range(m["STEPS"]):
+        a = pos * freq
+        angles.write(np.concatenate([np.cos(a), np.sin(a)]).astype(np.float32).tobytes())
+        xb.write(xs[pos].tobytes())
+        kind, _ = s.run_cells("ai_qwen_3__attention_tiered", [s.buf(xb.ref), s.buf(table), s.integer(pos), s.buf(hb.ref)])
+        assert kind == s.OBJ, f"position {pos}: the verb answers h1"
+        h1[pos] = _u16(hb.read(), (H,))
+    state = {"x": xs, "sink_k": _u16(planes[11].read(), (m["SINK"], kvw)), "hot_k": _u16(tiers[0].read(), (m["HOT"], kvw)),
+             "warm_ks": _u16(tiers[3].read(), (m["WARM"] * kvh,)), "cold_ks": _u16(tiers[7].read(), (cold_rows * kvh,)),
+             "warm_kc": np.frombuffer(tiers[2].read(), np.uint8).copy(), "cold_kc": np.frombuffer(tiers[6].read(), np.uint8).copy()}
+    s.release(table)
+    s.release_buffers()
+    return h1, state
+
+
 @pytest.fixture(scope="module")
 def cpu_session(reference):
     if reference is None or engine_driver.engine_module() is None:
@@ -161,10 +232,28 @@ def test_engine_runs_reference_family(cpu_session, reference):
     _attention_forms(cpu_session, reference, exact=True)
     _deltanet_forms(cpu_session, reference, exact=True)
     _tq_forms(cpu_session, reference, exact=True)
+    h1, state = _tiered_mixer(cpu_session, reference)
+    again, _ = _tiered_mixer(cpu_session, reference)
+    assert np.array_equal(h1, again), "the same program on the same family twice"
+    assert np.isfinite(oracle.from_bits(h1, FP16)).all() and (h1 != state["x"]).mean() > 0.9, "every position's answer was written"
+    assert state["warm_ks"].all() and state["cold_ks"].all() and state["hot_k"].any(axis=1).all(), "every tier holds rows at the end"
 
 
 @pytest.fixture(scope="module")
-def gpu_session(cuda):
+def mixer_on_reference_family(cuda, reference):
+    """The tiered mixer run on the reference's own CPU family through the same engine, before this family's session boots
+    (one machine is up at a time in a process): what the drop-in's answers are compared with."""
+    if reference is None or engine_driver.engine_module() is None:
+        pytest.fail("oracle/_ref holds no reference engine and family: build them where the reference tree is mounted")
+    s = engine_driver.Session(oracle.build.REF, "x86_avx2")
+    try:
+        return _tiered_mixer(s, reference)
+    finally:
+        s.close()
+
+
+@pytest.fixture(scope="module")
+def gpu_session(cuda, mixer_on_reference_family):
     import silvann_b200
     if engine_driver.engine_module() is None:
         pytest.fail("oracle/_ref holds no reference engine: build it where the reference tree is mounted")
@@ -188,3 +277,31 @@ def test_engine_runs_this_family(gpu_session, reference):
     _tq_forms(gpu_session, reference, exact=False)
     assert ext.counters()["refused"] == before["refused"]
     assert ext.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_engine_runs_the_tiered_mixer_on_this_family(gpu_session, mixer_on_reference_family, reference):
+    """The reference's whole attention mixer, a position at a time across every tier boundary, on this family against the
+    same program on the reference's CPU family.  The tiers quantise what earlier positions wrote, so the two families'
+    caches are compared too: a scale may differ by one fp16 step, and nearly every code must be the same."""
+    from silvann_b200 import ext
+    want, want_state = mixer_on_reference_family
+    before = ext.counters()
+    got, state = _tiered_mixer(gpu_session, reference)
+    after = ext.counters()
+    assert after["refused"] == before["refused"] and ext.device_status() == 0
+    m = MIX
+    cold_steps = m["STEPS"] - m["SINK"] - m["HOT"] - m["WARM"]
+    assert after["fused_residual"] - before["fused_residual"] >= m["STEPS"] + cold_steps, "the tiers' door pairs ran fused"
+    err = np.abs(oracle.from_bits(got, FP16) - oracle.from_bits(want, FP16))
+    print("tiered mixer: max |h1 - reference| a position:", np.round(err.max(axis=1), 5).tolist())
+    assert err.max() <= 2e-3 * max(1.0, float(np.abs(oracle.from_bits(want, FP16)).max())), f"h1 differs by {err.max()}"
+    for name in ("sink_k", "hot_k"):
+        d = np.abs(oracle.from_bits(state[name], FP16) - oracle.from_bits(want_state[name], FP16))
+        assert d.max() <= 4e-3, f"{name} differs by {d.max()}"
+    for name in ("warm_ks", "cold_ks"):
+        d = np.abs(state[name].astype(np.int32) - want_state[name].astype(np.int32))
+        assert d.max() <= 1, f"{name}: a scale {d.max()} fp16 steps away"
+    for name in ("warm_kc", "cold_kc"):
+        same = (state[name] == want_state[name]).mean()
+        assert same >= 0.97, f"{name}: only {same:.3f} of the code bytes are the reference's"

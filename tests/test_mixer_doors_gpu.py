@@ -90,3 +90,52 @@ def test_rotations(cuda, fam, golden):
     # turning one way and back is the identity up to two roundings
     back = from_bits(host_bits(outs[0]), 0)
     assert np.isfinite(back).all()
+
+
+def test_weight_path_doors(cuda, fam, golden):
+    """The whole-row rotation, a coded matrix times a vector (alone and as groups over one vector), the norm and rotation in
+    one door.  The rotation's four sums are the reference's own, so it is bit for bit; a gemv's sum is folded over a block."""
+    from silvann_b200.abi import TqGroups
+    g = golden
+    sign = dev(cuda, g["wp_sign"])
+    for n in (96, 512, 896, 1152):
+        x = dev(cuda, g[f"wp_rot_x_{n}"])
+        o = cuda.zeros_like(x)
+        fam.nn.hadamard_rotate(o.data_ptr(), x.data_ptr(), sign.data_ptr(), n, None)
+        assert fam.sys.compute_completed()
+        assert np.array_equal(host_bits(o), g[f"wp_rot_o_{n}"]), f"a row of {n}"
+    xv = dev(cuda, g["wp_gemv_x"])
+    cols = xv.numel()
+    held = {}
+    for d in (4, 8, 5):
+        codes, scales = dev(cuda, g[f"wp_gemv_codes_{d}"]), dev(cuda, g[f"wp_gemv_scales_{d}"])
+        rows = codes.shape[0]
+        held[d] = (codes, scales, rows)
+        o = cuda.zeros(rows, dtype=cuda.int16, device="cuda")
+        fam.nn.turboquant_gemv(o.data_ptr(), codes.data_ptr(), codes.numel(), scales.data_ptr(), scales.numel() * 2, xv.data_ptr(), d, rows, cols, None)
+        assert fam.sys.compute_completed()
+        one_ulp(host_bits(o), g[f"wp_gemv_o_{d}"], f"gemv at {d} bits")
+        # a room that holds fewer rows than named: those past it are left alone
+        o2 = cuda.full((rows,), 0x1234, dtype=cuda.int16, device="cuda")
+        short = (rows - 3) * (codes.numel() // rows)
+        fam.nn.turboquant_gemv(o2.data_ptr(), codes.data_ptr(), short, scales.data_ptr(), scales.numel() * 2, xv.data_ptr(), d, rows, cols, None)
+        assert fam.sys.compute_completed()
+        got = host_bits(o2)
+        one_ulp(got[:rows - 3], g[f"wp_gemv_o_{d}"][:rows - 3], "a short room")
+        assert (got[rows - 3:] == 0x1234).all()
+    gr = TqGroups()
+    for i, d in enumerate((4, 8)):
+        codes, scales, rows = held[d]
+        gr.codes[i], gr.luts[i], gr.rows[i], gr.d[i], gr.out_at[i] = codes.data_ptr(), scales.data_ptr(), rows, d, (0, 48)[i]
+    gr.count = 2
+    og = cuda.zeros(68, dtype=cuda.int16, device="cuda")
+    fam.nn.turboquant_gemv_groups(og.data_ptr(), gr, xv.data_ptr(), cols, None)
+    assert fam.sys.compute_completed()
+    one_ulp(host_bits(og), g["wp_groups_o"], "two groups over one vector")
+    xn, wn = dev(cuda, g["wp_nr_x"]), dev(cuda, g["wp_nr_w"])
+    h, hrot = cuda.zeros_like(xn), cuda.zeros_like(xn)
+    fam.nn.rmsnorm_rotate(hrot.data_ptr(), h.data_ptr(), xn.data_ptr(), wn.data_ptr(), sign.data_ptr(), 896, C.c_float(1e-6), None)
+    assert fam.sys.compute_completed()
+    one_ulp(host_bits(h), g["wp_nr_h"], "the norm of rmsnorm_rotate")
+    want = from_bits(g["wp_nr_hrot"], 0)
+    assert np.abs(from_bits(host_bits(hrot), 0) - want).max() <= 2e-3 * max(1.0, np.abs(want).max())

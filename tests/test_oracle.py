@@ -208,3 +208,22 @@ def test_port_mixer_steps(golden, port):
     assert np.array_equal(og, g["mx_gate_o"])
     dst = np.zeros_like(g["mx_copy_dst"]); L.oracle_vector_copy_rows(P(dst), 40, P(g["mx_copy_src"]), 50, 33, 4)
     assert np.array_equal(dst, g["mx_copy_dst"])
+
+
+def test_port_weight_path_doors(golden, port):
+    """The whole-row rotation and a coded matrix times a vector, restated, against the reference's CPU family bit for bit."""
+    g = golden
+    for n in (96, 512, 896, 1152):
+        assert np.array_equal(oracle.hadamard_rotate(port, g[f"wp_rot_x_{n}"], g["wp_sign"]), g[f"wp_rot_o_{n}"]), f"a row of {n}"
+    x, cols = g["wp_gemv_x"], g["wp_gemv_x"].size
+    outs = {}
+    for d in (4, 8, 5):
+        codes, scales = g[f"wp_gemv_codes_{d}"], g[f"wp_gemv_scales_{d}"]
+        outs[d] = oracle.tq_gemv(port, codes, scales.view(np.uint8).copy(), x, d, codes.shape[0], cols)
+        assert np.array_equal(outs[d], g[f"wp_gemv_o_{d}"]), f"width {d}"
+    assert np.array_equal(np.concatenate([outs[4], outs[8]]), g["wp_groups_o"])          # groups: the gemv once a group
+    # rmsnorm_rotate: the norm, then the rotation of what the norm stored
+    h = np.zeros(896, np.uint16)
+    port.lib.oracle_rmsnorm_rows(oracle._p(h), oracle._p(g["wp_nr_x"]), oracle._p(g["wp_nr_w"]), 896, 1, 896, 896, np.float32(1e-6))
+    assert np.array_equal(h, g["wp_nr_h"])
+    assert np.array_equal(oracle.hadamard_rotate(port, h, g["wp_sign"]), g["wp_nr_hrot"])
