@@ -575,7 +575,7 @@ static void d_attention_residual_mix_tq_rows(float* res, const float* p, const s
 static void d_hadamard_rotate(sv_h16* out, const sv_h16* in, const sv_h16* sign, sv_u64 n, sv_fault* over) {
     flush();
     const bool apart = !(out < in + n && in < out + n);           /* a lane reads the whole block it writes into */
-    const bool shaped = n != 0 && (n < 512 ? (n & (n - 1)) == 0 : (n % 512) % 128 == 0);
+    const bool shaped = n != 0 && (n < 512 || (n % 512) % 128 == 0);   /* past the whole blocks: a 256 and a 128, or a read past n */
     if (!apart || !shaped) { launch_refused("hadamard_rotate", cudaSuccess); return; }
     check("hadamard_rotate", sv::hadamard_rotate_launch(out, in, sign, n, over, 0));
 }
