@@ -94,6 +94,17 @@ class Port:
             "oracle_turboquant_encode_rows": [vp, vp, vp, u64, u64, u64],
             "oracle_attention_residual_tq": [vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u64],
             "oracle_hadamard_rotate": [vp, vp, vp, u64],
+            "oracle_kda_decays": [vp, vp, vp, vp, u64, u64, C.c_float, u64],
+            "oracle_kda_steps": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u64, u64, C.c_float, C.c_float, u64],
+            "oracle_attention_absorb_rows": [vp, vp, vp, u64, u64, u64, u64, C.c_float, u64],
+            "oracle_attention_expand_rows": [vp, vp, vp, u64, u64, u64, u64, u64, u64],
+            "oracle_index_layernorm": [vp, vp, vp, vp, u64, C.c_float],
+            "oracle_index_pool": [vp, vp, vp, vp, u64, u64, u64, u64],
+            "oracle_index_scores_rows": [vp, u64, vp, vp, vp, u64, u64, u64, u64, u64, u64, C.c_float],
+            "oracle_index_select": [vp, vp, vp, u64, u64, u64, u64, u64],
+            "oracle_index_select_rows": [vp, u64, vp, vp, u64, u64, u64, u64, u64],
+            "oracle_index_blocks": [vp, vp, u64, u64],
+            "oracle_index_gather_rows": [vp, u64, vp, vp, u64, vp, u64, u64, u64],
             "oracle_turboquant_gemv": [vp, vp, vp, vp, u64, u64, u64],
         }
         for name, args in sig.items():
@@ -367,24 +378,143 @@ def residual_tq(impl, q, kcodes, kscales, vcodes, vscales, qh, kvh, dh, length, 
 
 def hadamard_rotate(impl, x, sign):
     """The rotation over a whole row (hadamard_rotate): blocks of 512, then a 256 and a 128."""
+    P = getattr(impl, "ptr", _p)
     out = np.zeros_like(x)
     if isinstance(impl, Port):
         impl.lib.oracle_hadamard_rotate(_p(out), _p(x), _p(sign), x.size)
     else:
-        impl.nn.hadamard_rotate(_p(out), _p(x), _p(sign), x.size, _p(impl.over))
+        impl.nn.hadamard_rotate(P(out), P(x), P(sign), x.size, P(impl.over))
         impl.wait()
     return out
 
 
 def tq_gemv(impl, codes, luts, x, d, rows, cols):
     """turboquant_gemv: a coded matrix of `rows` rows times the 16-bit vector x."""
+    P = getattr(impl, "ptr", _p)
     out = np.zeros(rows, np.uint16)
     if isinstance(impl, Port):
         impl.lib.oracle_turboquant_gemv(_p(out), _p(codes), _p(luts), _p(x), d, rows, cols)
     else:
-        impl.nn.turboquant_gemv(_p(out), _p(codes), codes.nbytes, _p(luts), luts.nbytes, _p(x), d, rows, cols, _p(impl.over))
+        impl.nn.turboquant_gemv(P(out), P(codes), codes.nbytes, P(luts), luts.nbytes, P(x), d, rows, cols, P(impl.over))
         impl.wait()
     return out
+
+
+# ---- the GLM mixer's doors through either implementation ------------------------------------------------------------
+
+def kda_steps(impl, S, conved, f, b, dt, a_log, gate, w, heads, d, lower, eps, rows, decayed=False):
+    """Kimi Delta Attention over `rows` rows (kda_steps; rows = 1 through kda_step; decayed: kda_decays then
+    kda_steps_decayed).  conved is the rows' q, then their k, then their v.  Answers (state after, out)."""
+    P = getattr(impl, "ptr", _p)
+    S = S.copy()
+    out = np.zeros((rows, heads * d), np.uint16)
+    f32 = lambda v: C.c_float(float(v))
+    if isinstance(impl, Port):
+        eg = None
+        if decayed:
+            eg = np.zeros((rows, heads * d), np.float32)
+            impl.lib.oracle_kda_decays(_p(eg), _p(f), _p(dt), _p(a_log), heads, d, f32(lower), rows)
+        impl.lib.oracle_kda_steps(_p(S), _p(conved), _p(f), _p(eg) if decayed else None, _p(b), _p(dt), _p(a_log), _p(gate), _p(w), _p(out), heads, d,
+                                  f32(lower), f32(eps), rows)
+    elif decayed:
+        eg = np.zeros((rows, heads * d), np.float32)
+        impl.nn.kda_decays(P(eg), P(f), P(dt), P(a_log), heads, d, f32(lower), rows)
+        impl.nn.kda_steps_decayed(P(S), P(conved), P(eg), P(b), P(gate), P(w), P(out), heads, d, f32(eps), rows, P(impl.over))
+        impl.wait()
+    elif rows == 1:
+        impl.nn.kda_step(P(S), P(conved), P(f), P(b), P(dt), P(a_log), P(gate), P(w), P(out), heads, d, f32(lower), f32(eps), P(impl.over))
+        impl.wait()
+    else:
+        impl.nn.kda_steps(P(S), P(conved), P(f), P(b), P(dt), P(a_log), P(gate), P(w), P(out), heads, d, f32(lower), f32(eps), rows, P(impl.over))
+        impl.wait()
+    return S, out
+
+
+def absorb_rows(impl, q, W, heads, nope, latent, stride, scale, rows):
+    P = getattr(impl, "ptr", _p)
+    out = np.zeros((rows, heads * latent), np.uint16)
+    if isinstance(impl, Port):
+        impl.lib.oracle_attention_absorb_rows(_p(out), _p(q), _p(W), heads, nope, latent, stride, C.c_float(scale), rows)
+    else:
+        if rows == 1:
+            impl.nn.attention_absorb(P(out), P(q), P(W), heads, nope, latent, stride, C.c_float(scale), P(impl.over))
+        else:
+            impl.nn.attention_absorb_rows(P(out), P(q), P(W), heads, nope, latent, stride, C.c_float(scale), rows, P(impl.over))
+        impl.wait()
+    return out
+
+
+def expand_rows(impl, o, W, heads, width, latent, stride, offset, rows):
+    P = getattr(impl, "ptr", _p)
+    out = np.zeros((rows, heads * width), np.uint16)
+    if isinstance(impl, Port):
+        impl.lib.oracle_attention_expand_rows(_p(out), _p(o), _p(W), heads, width, latent, stride, offset, rows)
+    else:
+        if rows == 1:
+            impl.nn.attention_expand(P(out), P(o), P(W), heads, width, latent, stride, offset, P(impl.over))
+        else:
+            impl.nn.attention_expand_rows(P(out), P(o), P(W), heads, width, latent, stride, offset, rows, P(impl.over))
+        impl.wait()
+    return out
+
+
+def indexer(impl, x, lw, lb, keys, gates, ape, q, w, dim, kpool, heads, k, len0, rows, scale, src, block):
+    """The indexer's doors one after another on one set of inputs: the LayerNorm of x; the pooled keys of every whole pool of
+    the len0 + rows - 1 positions; the one-row scores, choice, block maxima and gather at position len0 - 1; and the rows
+    forms for `rows` rows from it.  Answers a dict of every door's output."""
+    P = getattr(impl, "ptr", _p)
+    g = {}
+    port = isinstance(impl, Port)
+    nn, lib = (None, impl.lib) if port else (impl.nn, None)
+    over = None if port else P(impl.over)
+    n_pos = len0 + rows - 1
+    pools_all, pools1 = n_pos // kpool, len0 // kpool
+    g["ln"] = np.zeros_like(x)
+    g["pooled"] = np.zeros((pools_all, dim), np.uint16)
+    g["scores"] = np.zeros(max(pools1, 1), np.float32)
+    g["index"] = np.zeros(min(k, max(pools1, 1)) * kpool + kpool, np.uint32)
+    g["count"] = np.zeros(1, np.uint32)
+    nblocks = (pools1 + block - 1) // block
+    g["blocks"] = np.zeros(max(nblocks, 1), np.float32)
+    srow = max(pools_all, 1)
+    g["scores_rows"] = np.zeros((rows, srow), np.float32)
+    irow = min(k, max(pools_all, 1)) * kpool + kpool
+    g["index_rows"] = np.zeros((rows, irow), np.uint32)
+    g["counts"] = np.zeros(rows, np.uint32)
+    row = src.shape[1]
+    tail = len0 - pools1 * kpool
+    if port:
+        lib.oracle_index_layernorm(_p(g["ln"]), _p(x), _p(lw), _p(lb), x.size, C.c_float(1e-5))
+        lib.oracle_index_pool(_p(g["pooled"]), _p(keys), _p(gates), _p(ape), 0, pools_all, dim, kpool)
+        lib.oracle_index_scores_rows(_p(g["scores"]), 0, _p(q), _p(w), _p(g["pooled"]), heads, dim, pools1, 0, 1, 0, C.c_float(scale))
+        lib.oracle_index_select(_p(g["index"]), _p(g["count"]), _p(g["scores"]), pools1, k, kpool, pools1 * kpool, tail)
+        lib.oracle_index_blocks(_p(g["blocks"]), _p(g["scores"]), pools1, block)
+        lib.oracle_index_scores_rows(_p(g["scores_rows"]), srow, _p(q), _p(w), _p(g["pooled"]), heads, dim, 0, len0, kpool, rows, C.c_float(scale))
+        lib.oracle_index_select_rows(_p(g["index_rows"]), irow, _p(g["counts"]), _p(g["scores_rows"]), srow, k, kpool, len0, rows)
+    else:
+        nn.index_layernorm(P(g["ln"]), P(x), P(lw), P(lb), x.size, C.c_float(1e-5), over)
+        nn.index_pool(P(g["pooled"]), P(keys), P(gates), P(ape), 0, pools_all, dim, kpool, over)
+        impl.wait()
+        nn.index_scores(P(g["scores"]), P(q), P(w), P(g["pooled"]), heads, dim, pools1, C.c_float(scale))
+        impl.wait()
+        nn.index_select(P(g["index"]), P(g["count"]), P(g["scores"]), pools1, k, kpool, pools1 * kpool, tail)
+        nn.index_blocks(P(g["blocks"]), P(g["scores"]), pools1, block)
+        nn.index_scores_rows(P(g["scores_rows"]), srow, P(q), P(w), P(g["pooled"]), heads, dim, len0, kpool, rows, C.c_float(scale))
+        impl.wait()
+        nn.index_select_rows(P(g["index_rows"]), irow, P(g["counts"]), P(g["scores_rows"]), srow, k, kpool, len0, rows)
+        impl.wait()
+    n1 = int(g["count"][0])
+    most = int(g["counts"].max())
+    g["gathered"] = np.zeros((n1, row), np.uint16)
+    g["gathered_rows"] = np.zeros((rows, most * row), np.uint16)
+    if port:
+        lib.oracle_index_gather_rows(_p(g["gathered"]), 0, _p(src), _p(g["index"]), 0, None, n1, row, 1)
+        lib.oracle_index_gather_rows(_p(g["gathered_rows"]), most * row, _p(src), _p(g["index_rows"]), irow, _p(g["counts"]), most, row, rows)
+    else:
+        nn.index_gather(P(g["gathered"]), P(src), P(g["index"]), n1, row)
+        nn.index_gather_rows(P(g["gathered_rows"]), most * row, P(src), P(g["index_rows"]), irow, P(g["counts"]), most, row, rows)
+        impl.wait()
+    return g
 
 
 _port = None

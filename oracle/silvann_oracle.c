@@ -526,3 +526,147 @@ void oracle_turboquant_gemv(uint16_t* out, const uint8_t* weights, const uint8_t
         out[r] = f32_to_f16(part * scale, 0);
     }
 }
+
+/* ---- the GLM mixer's doors: Kimi Delta Attention, the latent's absorb and expand, the sparse attention's indexer --------
+ * KDA (kernels.cuh:3301-3470): DeltaNet's recurrence with a decay a key channel.  `eg` null: the decays are made from f, dt
+ * and a_log (kda_step, kda_steps); else read (kda_steps_decayed, with kda_decays before it).  conved is the rows' q, then
+ * their k, then their v, each `heads·d` wide a row. */
+static float kda_decay(float lower, float a, uint16_t f, uint16_t dt) { return expf(lower / (1.0f + expf(-a * (f16_to_f32(f) + f16_to_f32(dt))))); }
+void oracle_kda_decays(float* eg, const uint16_t* f, const uint16_t* dt, const uint16_t* a_log, uint64_t heads, uint64_t d, float lower, uint64_t rows) {
+    const uint64_t width = heads * d;                                                                     /* :3400-3409 */
+    for (uint64_t x = 0; x < rows * width; ++x) { const uint64_t c = x % width; eg[x] = kda_decay(lower, expf(f16_to_f32(a_log[c / d])), f[x], dt[c]); }
+}
+void oracle_kda_steps(float* S, const uint16_t* conved, const uint16_t* f, const float* eg, const uint16_t* b, const uint16_t* dt, const uint16_t* a_log,
+                      const uint16_t* gate, const uint16_t* w, uint16_t* out, uint64_t heads, uint64_t d, float lower, float eps, uint64_t rows) {
+    const uint64_t width = heads * d;
+    const uint16_t *q = conved, *k = conved + rows * width, *v = conved + 2 * rows * width;
+    for (uint64_t h = 0; h < heads; ++h) {
+        float* Sh = S + h * d * d;
+        const float a = eg ? 0.0f : expf(f16_to_f32(a_log[h]));
+        for (uint64_t t = 0; t < rows; ++t) {                                                             /* :3312-3347 a row of a head */
+            const uint64_t at = t * width + h * d;
+            const float beta = 1.0f / (1.0f + expf(-f16_to_f32(b[t * heads + h])));
+            float qq = 0.0f, kk = 0.0f;
+            for (uint64_t i = 0; i < d; ++i) { const float qi = f16_to_f32(q[at + i]), ki = f16_to_f32(k[at + i]); qq += qi * qi; kk += ki * ki; }
+            const float inv_q = 1.0f / sqrtf(qq + 1e-6f) / sqrtf((float)d), inv_k = 1.0f / sqrtf(kk + 1e-6f);
+            float oo = 0.0f;
+            for (uint64_t j = 0; j < d; ++j) {
+                float kv = 0.0f;
+                for (uint64_t i = 0; i < d; ++i) {
+                    Sh[i * d + j] *= eg ? eg[at + i] : kda_decay(lower, a, f[at + i], dt[h * d + i]);
+                    kv += Sh[i * d + j] * f16_to_f32(k[at + i]) * inv_k;
+                }
+                const float delta = (f16_to_f32(v[at + j]) - kv) * beta;
+                float o = 0.0f;
+                for (uint64_t i = 0; i < d; ++i) { const float s = Sh[i * d + j] + f16_to_f32(k[at + i]) * inv_k * delta; Sh[i * d + j] = s; o += s * f16_to_f32(q[at + i]); }
+                out[at + j] = f32_to_f16(o * inv_q, 0);
+                const float oj = f16_to_f32(out[at + j]);
+                oo += oj * oj;
+            }
+            const float scale = 1.0f / sqrtf(oo / (float)d + eps);                                        /* :3350-3359 */
+            for (uint64_t j = 0; j < d; ++j)
+                out[at + j] = f32_to_f16(f16_to_f32(out[at + j]) * scale * f16_to_f32(w[j]) / (1.0f + expf(-f16_to_f32(gate[at + j]))), 0);
+        }
+    }
+}
+/* attention_absorb_rows (:3596-3627), attention_expand_rows (:3629-3664) */
+void oracle_attention_absorb_rows(uint16_t* out, const uint16_t* q, const uint16_t* W, uint64_t heads, uint64_t nope, uint64_t latent, uint64_t stride,
+                                  float scale, uint64_t rows) {
+    for (uint64_t t = 0; t < rows; ++t) for (uint64_t h = 0; h < heads; ++h) for (uint64_t c = 0; c < latent; ++c) {
+        float sum = 0.0f;
+        for (uint64_t i = 0; i < nope; ++i) sum += f16_to_f32(W[(h * stride + i) * latent + c]) * f16_to_f32(q[(t * heads + h) * nope + i]);
+        out[(t * heads + h) * latent + c] = f32_to_f16(sum * scale, 0);
+    }
+}
+void oracle_attention_expand_rows(uint16_t* out, const uint16_t* o, const uint16_t* W, uint64_t heads, uint64_t width, uint64_t latent, uint64_t stride,
+                                  uint64_t offset, uint64_t rows) {
+    for (uint64_t t = 0; t < rows; ++t) for (uint64_t r = 0; r < heads * width; ++r) {
+        const uint64_t h = r / width;
+        float sum = 0.0f;
+        for (uint64_t c = 0; c < latent; ++c) sum += f16_to_f32(W[(h * stride + offset + r % width) * latent + c]) * f16_to_f32(o[(t * heads + h) * latent + c]);
+        out[t * heads * width + r] = f32_to_f16(sum, 0);
+    }
+}
+/* the indexer (:3666-3846) */
+void oracle_index_layernorm(uint16_t* o, const uint16_t* x, const uint16_t* w, const uint16_t* b, uint64_t n, float eps) {
+    float sum = 0.0f, sq = 0.0f;
+    for (uint64_t i = 0; i < n; ++i) sum += f16_to_f32(x[i]);
+    const float mean = sum / (float)n;
+    for (uint64_t i = 0; i < n; ++i) { const float dd = f16_to_f32(x[i]) - mean; sq += dd * dd; }
+    const float inv = 1.0f / sqrtf(sq / (float)n + eps);
+    for (uint64_t i = 0; i < n; ++i) o[i] = f32_to_f16((f16_to_f32(x[i]) - mean) * inv * f16_to_f32(w[i]) + f16_to_f32(b[i]), 0);
+}
+void oracle_index_pool(uint16_t* pooled, const uint16_t* keys, const uint16_t* gates, const uint16_t* ape, uint64_t first, uint64_t pools, uint64_t dim,
+                       uint64_t kpool) {
+    for (uint64_t e = 0; e < pools * dim; ++e) {
+        const uint64_t p = first + e / dim, c = e % dim;
+        float top = -INFINITY, den = 0.0f, num = 0.0f;
+        for (uint64_t i = 0; i < kpool; ++i) { const float l = f16_to_f32(gates[(p * kpool + i) * dim + c]) + f16_to_f32(ape[i * dim + c]); if (l > top) top = l; }
+        for (uint64_t i = 0; i < kpool; ++i) {
+            const float wgt = expf(f16_to_f32(gates[(p * kpool + i) * dim + c]) + f16_to_f32(ape[i * dim + c]) - top);
+            den += wgt; num += wgt * f16_to_f32(keys[(p * kpool + i) * dim + c]);
+        }
+        pooled[p * dim + c] = f32_to_f16(num / den, 0);
+    }
+}
+static void index_score(float* scores, const uint16_t* q, const uint16_t* w, const uint16_t* pooled, uint64_t heads, uint64_t dim, uint64_t p, float scale) {
+    const float per_head = 1.0f / sqrtf((float)heads);
+    float part = 0.0f;
+    for (uint64_t h = 0; h < heads; ++h) {
+        float dot = 0.0f;
+        for (uint64_t c = 0; c < dim; ++c) dot += f16_to_f32(q[h * dim + c]) * f16_to_f32(pooled[p * dim + c]);
+        dot *= scale;
+        part += (dot > 0.0f ? dot : 0.0f) * f16_to_f32(w[h]) * per_head;
+    }
+    scores[p] = part;
+}
+/* rows = 0: the one-row door over `pools` pools; else row u, position len0 + u - 1, scores its (len0 + u) / kpool finished pools */
+void oracle_index_scores_rows(float* scores, uint64_t scores_row, const uint16_t* q, const uint16_t* w, const uint16_t* pooled, uint64_t heads, uint64_t dim,
+                              uint64_t pools, uint64_t len0, uint64_t kpool, uint64_t rows, float scale) {
+    if (rows == 0) { for (uint64_t p = 0; p < pools; ++p) index_score(scores, q, w, pooled, heads, dim, p, scale); return; }
+    for (uint64_t u = 0; u < rows; ++u) for (uint64_t p = 0; p < (len0 + u) / kpool; ++p)
+        index_score(scores + u * scores_row, q + u * heads * dim, w + u * heads, pooled, heads, dim, p, scale);
+}
+static uint32_t index_key(float f) { uint32_t u; memcpy(&u, &f, 4); return (u & 0x80000000u) ? ~u : (u | 0x80000000u); }
+/* the k largest scores' pools (ties by lowest index) as positions in index order, then the tail's positions (:3789-3818) */
+void oracle_index_select(uint32_t* index, uint32_t* count, const float* scores, uint64_t pools, uint64_t k, uint64_t kpool, uint64_t tail_first, uint64_t tail) {
+    uint32_t cut = 0;
+    if (pools > k)
+        for (int bit = 31; bit >= 0; --bit) {
+            const uint32_t want = cut | (1u << bit);
+            uint64_t have = 0;
+            for (uint64_t p = 0; p < pools; ++p) have += index_key(scores[p]) >= want;
+            if (have >= k) cut = want;
+        }
+    uint64_t above = 0, n = 0;
+    if (pools > k) for (uint64_t p = 0; p < pools; ++p) above += index_key(scores[p]) > cut;
+    uint64_t ties = pools > k ? k - above : 0;
+    for (uint64_t p = 0; p < pools; ++p) {
+        int take = pools <= k;
+        if (!take) { const uint32_t key = index_key(scores[p]); if (key > cut) take = 1; else if (key == cut && ties != 0) { take = 1; --ties; } }
+        if (take) for (uint64_t i = 0; i < kpool; ++i) index[n++] = (uint32_t)(p * kpool + i);
+    }
+    for (uint64_t i = 0; i < tail; ++i) index[n++] = (uint32_t)(tail_first + i);
+    count[0] = (uint32_t)n;
+}
+void oracle_index_select_rows(uint32_t* index, uint64_t index_row, uint32_t* counts, const float* scores, uint64_t scores_row, uint64_t k, uint64_t kpool,
+                              uint64_t len0, uint64_t rows) {
+    for (uint64_t u = 0; u < rows; ++u) {
+        const uint64_t len = len0 + u, pools = len / kpool;
+        oracle_index_select(index + u * index_row, counts + u, scores + u * scores_row, pools, k, kpool, pools * kpool, len - pools * kpool);
+    }
+}
+void oracle_index_blocks(float* out, const float* scores, uint64_t pools, uint64_t block) {
+    for (uint64_t b = 0; b < (pools + block - 1) / block; ++b) {
+        const uint64_t end = (b + 1) * block < pools ? (b + 1) * block : pools;
+        float best = scores[b * block];
+        for (uint64_t p = b * block + 1; p < end; ++p) best = scores[p] > best ? scores[p] : best;
+        out[b] = best;
+    }
+}
+/* counts null: one row of `most` positions (index_gather); else row u's counts[u] positions (index_gather_rows) */
+void oracle_index_gather_rows(uint16_t* out, uint64_t out_row, const uint16_t* src, const uint32_t* index, uint64_t index_row, const uint32_t* counts,
+                              uint64_t most, uint64_t row, uint64_t rows) {
+    for (uint64_t u = 0; u < rows; ++u) for (uint64_t i = 0; i < (counts ? counts[u] : most); ++i) for (uint64_t e = 0; e < row; ++e)
+        out[u * out_row + i * row + e] = src[(uint64_t)index[u * index_row + i] * row + e];
+}

@@ -602,6 +602,102 @@ static void d_turboquant_gemv_groups(sv_h16* out, sv_tq_groups g, const sv_h16* 
     check("turboquant_gemv_groups", e);
 }
 
+/* ---- the GLM mixer's doors (glm_doors.cu): KDA, the latent's absorb and expand, the indexer ---- */
+static void d_kda_steps(float* S, const sv_h16* conved, const sv_h16* f, const sv_h16* b, const sv_h16* dt, const sv_h16* a_log, const sv_h16* gate,
+                        const sv_h16* w, sv_h16* out, sv_u64 heads, sv_u64 head_dim, float lower, float eps, sv_u64 rows, sv_fault* over) {
+    flush();
+    if (heads == 0 || head_dim == 0 || rows == 0) return;
+    check("kda_steps", sv::kda_steps_launch(S, conved, f, nullptr, b, dt, a_log, gate, w, out, heads, head_dim, lower, eps, rows, over, 0));
+}
+static void d_kda_step(float* S, const sv_h16* conved, const sv_h16* f, const sv_h16* b, const sv_h16* dt, const sv_h16* a_log, const sv_h16* gate,
+                       const sv_h16* w, sv_h16* out, sv_u64 heads, sv_u64 head_dim, float lower, float eps, sv_fault* over) {
+    d_kda_steps(S, conved, f, b, dt, a_log, gate, w, out, heads, head_dim, lower, eps, 1, over);      /* one row: q, k, v side by side */
+}
+static void d_kda_decays(float* eg, const sv_h16* f, const sv_h16* dt, const sv_h16* a_log, sv_u64 heads, sv_u64 head_dim, float lower, sv_u64 rows) {
+    flush();
+    if (heads * head_dim * rows == 0) return;
+    check("kda_decays", sv::kda_decays_launch(eg, f, dt, a_log, heads, head_dim, lower, rows, 0));
+}
+static void d_kda_steps_decayed(float* S, const sv_h16* conved, const float* eg, const sv_h16* b, const sv_h16* gate, const sv_h16* w, sv_h16* out,
+                                sv_u64 heads, sv_u64 head_dim, float eps, sv_u64 rows, sv_fault* over) {
+    flush();
+    if (heads == 0 || head_dim == 0 || rows == 0) return;
+    if (eg == nullptr) { launch_refused("kda_steps_decayed", cudaSuccess); return; }
+    check("kda_steps_decayed", sv::kda_steps_launch(S, conved, nullptr, eg, b, nullptr, nullptr, gate, w, out, heads, head_dim, 0.f, eps, rows, over, 0));
+}
+static void d_attention_absorb_rows(sv_h16* out, const sv_h16* q, const sv_h16* W, sv_u64 heads, sv_u64 nope, sv_u64 latent, sv_u64 stride, float scale,
+                                    sv_u64 rows, sv_fault* over) {
+    flush();
+    if (heads * latent * rows == 0) return;
+    const cudaError_t e = sv::absorb_launch(out, q, W, heads, nope, latent, stride, scale, rows, over, 0);
+    if (e == cudaErrorInvalidValue) { (void)cudaGetLastError(); launch_refused("attention_absorb", cudaSuccess); return; }
+    check("attention_absorb", e);
+}
+static void d_attention_absorb(sv_h16* out, const sv_h16* q, const sv_h16* W, sv_u64 heads, sv_u64 nope, sv_u64 latent, sv_u64 stride, float scale,
+                               sv_fault* over) {
+    d_attention_absorb_rows(out, q, W, heads, nope, latent, stride, scale, 1, over);
+}
+static void d_attention_expand_rows(sv_h16* out, const sv_h16* o, const sv_h16* W, sv_u64 heads, sv_u64 width, sv_u64 latent, sv_u64 stride, sv_u64 offset,
+                                    sv_u64 rows, sv_fault* over) {
+    flush();
+    if (heads * width * rows == 0) return;
+    check("attention_expand", sv::expand_launch(out, o, W, heads, width, latent, stride, offset, rows, over, 0));
+}
+static void d_attention_expand(sv_h16* out, const sv_h16* o, const sv_h16* W, sv_u64 heads, sv_u64 width, sv_u64 latent, sv_u64 stride, sv_u64 offset,
+                               sv_fault* over) {
+    d_attention_expand_rows(out, o, W, heads, width, latent, stride, offset, 1, over);
+}
+static void d_index_layernorm(sv_h16* o, const sv_h16* x, const sv_h16* w, const sv_h16* b, sv_u64 n, float eps, sv_fault* over) {
+    flush();
+    if (n == 0) return;
+    check("index_layernorm", sv::index_layernorm_launch(o, x, w, b, n, eps, over, 0));
+}
+static void d_index_pool(sv_h16* pooled, const sv_h16* keys, const sv_h16* gates, const sv_h16* ape, sv_u64 first, sv_u64 pools, sv_u64 dim, sv_u64 kpool,
+                         sv_fault* over) {
+    flush();
+    if (pools * dim == 0) return;
+    check("index_pool", sv::index_pool_launch(pooled, keys, gates, ape, first, pools, dim, kpool, over, 0));
+}
+static void d_index_scores(float* scores, const sv_h16* q, const sv_h16* w, const sv_h16* pooled, sv_u64 heads, sv_u64 dim, sv_u64 pools, float scale) {
+    flush();
+    if (pools == 0) return;
+    check("index_scores", sv::index_scores_launch(scores, 0, q, w, pooled, heads, dim, pools, 0, 1, 0, scale, 0));
+}
+static void d_index_scores_rows(float* scores, sv_u64 scores_row, const sv_h16* q, const sv_h16* w, const sv_h16* pooled, sv_u64 heads, sv_u64 dim,
+                                sv_u64 len0, sv_u64 kpool, sv_u64 rows, float scale) {
+    flush();
+    if (rows == 0 || kpool == 0 || (len0 + rows - 1) / kpool == 0) return;
+    check("index_scores_rows", sv::index_scores_launch(scores, scores_row, q, w, pooled, heads, dim, 0, len0, kpool, rows, scale, 0));
+}
+static void d_index_select(sv_u32* index, sv_u32* count, const float* scores, sv_u64 pools, sv_u64 k, sv_u64 kpool, sv_u64 tail_first, sv_u64 tail) {
+    flush();
+    check("index_select", sv::index_select_launch(index, 0, count, scores, 0, pools, k, kpool, tail_first, tail, 0, 0, 0));
+}
+static void d_index_select_rows(sv_u32* index, sv_u64 index_row, sv_u32* counts, const float* scores, sv_u64 scores_row, sv_u64 k, sv_u64 kpool, sv_u64 len0,
+                                sv_u64 rows) {
+    flush();
+    if (rows == 0) return;
+    if (kpool == 0) { launch_refused("index_select_rows", cudaSuccess); return; }
+    check("index_select_rows", sv::index_select_launch(index, index_row, counts, scores, scores_row, 0, k, kpool, 0, 0, len0, rows, 0));
+}
+static void d_index_blocks(float* out, const float* scores, sv_u64 pools, sv_u64 block) {
+    flush();
+    if (pools == 0) return;
+    if (block == 0) { launch_refused("index_blocks", cudaSuccess); return; }
+    check("index_blocks", sv::index_blocks_launch(out, scores, pools, block, 0));
+}
+static void d_index_gather(sv_h16* out, const sv_h16* src, const sv_u32* index, sv_u64 n, sv_u64 row) {
+    flush();
+    if (n * row == 0) return;
+    check("index_gather", sv::index_gather_launch(out, 0, src, index, 0, nullptr, n, row, 1, 0));
+}
+static void d_index_gather_rows(sv_h16* out, sv_u64 out_row, const sv_h16* src, const sv_u32* index, sv_u64 index_row, const sv_u32* counts, sv_u64 most,
+                                sv_u64 row, sv_u64 rows) {
+    flush();
+    if (rows * most * row == 0) return;
+    check("index_gather_rows", sv::index_gather_launch(out, out_row, src, index, index_row, counts, most, row, rows, 0));
+}
+
 /* ================================================================================================================ */
 /* tables and the entry                                                                                             */
 
@@ -655,6 +751,23 @@ static void install_doors() {
     g_nn.rope_angles_mrope_rows = d_rope_angles_mrope_rows;
     g_nn.rope_angles_axial_rows = d_rope_angles_axial_rows;
     g_nn.attention_gate_rows = d_attention_gate_rows;
+    g_nn.kda_step = d_kda_step;
+    g_nn.kda_steps = d_kda_steps;
+    g_nn.kda_decays = d_kda_decays;
+    g_nn.kda_steps_decayed = d_kda_steps_decayed;
+    g_nn.attention_absorb = d_attention_absorb;
+    g_nn.attention_absorb_rows = d_attention_absorb_rows;
+    g_nn.attention_expand = d_attention_expand;
+    g_nn.attention_expand_rows = d_attention_expand_rows;
+    g_nn.index_layernorm = d_index_layernorm;
+    g_nn.index_pool = d_index_pool;
+    g_nn.index_scores = d_index_scores;
+    g_nn.index_scores_rows = d_index_scores_rows;
+    g_nn.index_select = d_index_select;
+    g_nn.index_select_rows = d_index_select_rows;
+    g_nn.index_blocks = d_index_blocks;
+    g_nn.index_gather = d_index_gather;
+    g_nn.index_gather_rows = d_index_gather_rows;
     g_nn.hadamard_rotate = d_hadamard_rotate;
     g_nn.rmsnorm_rotate = d_rmsnorm_rotate;
     g_nn.turboquant_gemv = d_turboquant_gemv;

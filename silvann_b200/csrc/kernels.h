@@ -104,6 +104,28 @@ cudaError_t rope_angles_launch(float* cs, uint64_t first, const uint32_t* positi
                                int mode /*0 plain, 1 M-RoPE, 2 axial*/, cudaStream_t st);
 cudaError_t attention_gate_rows_launch(uint16_t* o, const uint16_t* att, const uint16_t* qg, uint64_t heads, uint64_t head_dim, unsigned int* over,
                                        cudaStream_t st);
+/* ---- the GLM mixer's doors: Kimi Delta Attention, latent absorb / expand, the sparse attention's indexer (glm_doors.cu) ---- */
+cudaError_t kda_decays_launch(float* eg, const uint16_t* f, const uint16_t* dt, const uint16_t* a_log, uint64_t heads, uint64_t head_dim, float lower,
+                              uint64_t rows, cudaStream_t st);
+cudaError_t kda_steps_launch(float* S, const uint16_t* conved, const uint16_t* f, const float* eg /*null: made from f, dt, a_log*/, const uint16_t* b,
+                             const uint16_t* dt, const uint16_t* a_log, const uint16_t* gate, const uint16_t* w, uint16_t* out, uint64_t heads,
+                             uint64_t head_dim, float lower, float eps, uint64_t rows, unsigned int* over, cudaStream_t st);
+cudaError_t absorb_launch(uint16_t* out, const uint16_t* q, const uint16_t* W, uint64_t heads, uint64_t nope, uint64_t latent, uint64_t stride, float scale,
+                          uint64_t rows, unsigned int* over, cudaStream_t st);
+cudaError_t expand_launch(uint16_t* out, const uint16_t* o, const uint16_t* W, uint64_t heads, uint64_t width, uint64_t latent, uint64_t stride,
+                          uint64_t offset, uint64_t rows, unsigned int* over, cudaStream_t st);
+cudaError_t index_layernorm_launch(uint16_t* o, const uint16_t* x, const uint16_t* w, const uint16_t* b, uint64_t n, float eps, unsigned int* over,
+                                   cudaStream_t st);
+cudaError_t index_pool_launch(uint16_t* pooled, const uint16_t* keys, const uint16_t* gates, const uint16_t* ape, uint64_t first, uint64_t pools, uint64_t dim,
+                              uint64_t kpool, unsigned int* over, cudaStream_t st);
+/* rows = 0: the one-row doors (every one of `pools` pools; the caller's tail) */
+cudaError_t index_scores_launch(float* scores, uint64_t scores_row, const uint16_t* q, const uint16_t* w, const uint16_t* pooled, uint64_t heads, uint64_t dim,
+                                uint64_t pools, uint64_t len0, uint64_t kpool, uint64_t rows, float scale, cudaStream_t st);
+cudaError_t index_select_launch(uint32_t* index, uint64_t index_row, uint32_t* counts, const float* scores, uint64_t scores_row, uint64_t pools, uint64_t k,
+                                uint64_t kpool, uint64_t tail_first, uint64_t tail, uint64_t len0, uint64_t rows, cudaStream_t st);
+cudaError_t index_blocks_launch(float* out, const float* scores, uint64_t pools, uint64_t block, cudaStream_t st);
+cudaError_t index_gather_launch(uint16_t* out, uint64_t out_row, const uint16_t* src, const uint32_t* index, uint64_t index_row, const uint32_t* counts /*null: all*/,
+                                uint64_t most, uint64_t row, uint64_t rows, cudaStream_t st);
 /* ---- the TurboQuant-coded tiers of the cache, as worded (tq.cu) ------------------------------------------------ */
 bool tq_width_ok(uint64_t d);
 cudaError_t tq_decode_launch(uint16_t* out, const uint8_t* weights, uint64_t w_room, const uint8_t* luts, uint64_t l_room, uint64_t d,

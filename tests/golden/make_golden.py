@@ -200,6 +200,53 @@ def main():
     R.nn.rmsnorm_rotate(P_(hr), P_(hn), P_(xn), P_(wn), P_(sign512), 896, np.float32(1e-6), P_(over)); R.wait()
     out["wp_nr_x"], out["wp_nr_w"], out["wp_nr_h"], out["wp_nr_hrot"] = xn, wn, hn, hr
 
+    # the GLM mixer's doors: Kimi Delta Attention (rows from an empty state, then one more row; made and ready-made decays;
+    # a head width no register form covers), the latent's absorb and expand, the indexer's doors one after another
+    for tag, (heads, d, rows_) in {"kda_a": (2, 128, 4), "kda_b": (3, 64, 3), "kda_c": (1, 96, 2)}.items():
+        W = heads * d
+        inp = dict(conved=bits((3, rows_ + 1, W)), f=bits((rows_ + 1, W)), b=bits((rows_ + 1, heads)), dt=bits((W,)), a_log=bits((heads,), 0.3),
+                   gate=bits((rows_ + 1, W)), w=bits((d,)))
+        for k_, v_ in inp.items():
+            out[f"{tag}_{k_}"] = v_
+        out[f"{tag}_shape"] = np.array([heads, d, rows_])
+        first = dict(inp, conved=np.ascontiguousarray(inp["conved"][:, :rows_]), f=inp["f"][:rows_].copy(), b=inp["b"][:rows_].copy(), gate=inp["gate"][:rows_].copy())
+        last = dict(inp, conved=np.ascontiguousarray(inp["conved"][:, rows_:]), f=inp["f"][rows_:].copy(), b=inp["b"][rows_:].copy(), gate=inp["gate"][rows_:].copy())
+        S0 = np.zeros((heads, d, d), np.float32)
+        S1, o1 = oracle.kda_steps(R, S0, heads=heads, d=d, lower=-5.0, eps=1e-5, rows=rows_, **first)
+        S1d, o1d = oracle.kda_steps(R, S0, heads=heads, d=d, lower=-5.0, eps=1e-5, rows=rows_, decayed=True, **first)
+        assert np.array_equal(S1, S1d) and np.array_equal(o1, o1d), "ready-made decays are the same bits"
+        S2, o2 = oracle.kda_steps(R, S1, heads=heads, d=d, lower=-5.0, eps=1e-5, rows=1, **last)
+        out[f"{tag}_S1"], out[f"{tag}_o1"], out[f"{tag}_S2"], out[f"{tag}_o2"] = S1, o1, S2, o2
+    heads, nope, vd, lat, rows_ = 4, 48, 40, 128, 3
+    Wm, qa, oa = bits((heads * (nope + vd), lat), 0.1), bits((rows_, heads * nope)), bits((rows_, heads * lat))
+    out["mla_shape"] = np.array([heads, nope, vd, lat, rows_])
+    out["mla_W"], out["mla_q"], out["mla_o"] = Wm, qa, oa
+    out["mla_absorbed"] = oracle.absorb_rows(R, qa, Wm, heads, nope, lat, nope + vd, 0.125, rows_)
+    out["mla_absorbed_1"] = oracle.absorb_rows(R, qa[:1].copy(), Wm, heads, nope, lat, nope + vd, 0.125, 1)
+    out["mla_expanded"] = oracle.expand_rows(R, oa, Wm, heads, vd, lat, nope + vd, nope, rows_)
+    out["mla_expanded_1"] = oracle.expand_rows(R, oa[:1].copy(), Wm, heads, vd, lat, nope + vd, nope, 1)
+    dim, kpool, ih, k_, len0, rows_, block = 32, 4, 8, 5, 45, 6, 3
+    n_pos = len0 + rows_ - 1
+    ix = dict(x=bits((dim,)), lw=bits((dim,)), lb=bits((dim,)), keys=bits((n_pos, dim)), gates=bits((n_pos, dim)), ape=bits((kpool, dim)),
+              q=bits((rows_, ih * dim)), w=bits((rows_, ih)), src=bits((n_pos, 24)))
+    ix["keys"][8:12] = ix["keys"][16:20]            # two pools alike in every number: a tie, settled by the lower index
+    ix["gates"][8:12] = ix["gates"][16:20]
+    out["ix_shape"] = np.array([dim, kpool, ih, k_, len0, rows_, block])
+    for name, arr in ix.items():
+        out[f"ix_in_{name}"] = arr
+    got = oracle.indexer(R, dim=dim, kpool=kpool, heads=ih, k=k_, len0=len0, rows=rows_, scale=0.17, block=block, **ix)
+    for name, arr in got.items():
+        out[f"ix_{name}"] = arr
+    # the choice alone on scores full of ties (and both zeros, which order apart): the cut falls inside a run of equals
+    tied = rng.integers(-3, 4, 64).astype(np.float32) * np.float32(0.5)
+    tied[5], tied[9] = np.float32(-0.0), np.float32(0.0)
+    out["ixsel_scores"] = tied
+    for k_ in (1, 7, 20, 63, 64, 80):
+        index = np.zeros(min(k_, 64) * 2 + 3, np.uint32)
+        count = np.zeros(1, np.uint32)
+        R.nn.index_select(P_(index), P_(count), P_(tied), 64, k_, 2, 128, 3); R.wait()
+        out[f"ixsel_{k_}"] = index[: int(count[0])].copy()
+
     path = Path(__file__).with_name("reference_x86_avx2.npz")
     np.savez_compressed(path, **out)
     print(path, path.stat().st_size, "bytes,", len(out), "arrays")

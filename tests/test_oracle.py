@@ -227,3 +227,17 @@ def test_port_weight_path_doors(golden, port):
     port.lib.oracle_rmsnorm_rows(oracle._p(h), oracle._p(g["wp_nr_x"]), oracle._p(g["wp_nr_w"]), 896, 1, 896, 896, np.float32(1e-6))
     assert np.array_equal(h, g["wp_nr_h"])
     assert np.array_equal(oracle.hadamard_rotate(port, h, g["wp_sign"]), g["wp_nr_hrot"])
+
+
+def test_port_glm_doors(golden, port):
+    """Kimi Delta Attention, the latent's absorb and expand and the indexer, restated, against the reference's CPU family."""
+    import glm_cases
+    glm_cases.check_kda(golden, lambda S, **kw: oracle.kda_steps(port, S, **kw), state_rtol=1e-6, out_atol=2e-4)
+    glm_cases.check_mla(golden, lambda *a: oracle.absorb_rows(port, *a), lambda *a: oracle.expand_rows(port, *a), steps=0)
+    glm_cases.check_indexer(golden, lambda **kw: oracle.indexer(port, **kw))
+
+    def select(scores, pools, k, kpool, tail_first, tail):
+        index, count = np.zeros(min(k, pools) * kpool + tail, np.uint32), np.zeros(1, np.uint32)
+        port.lib.oracle_index_select(oracle._p(index), oracle._p(count), oracle._p(scores), pools, k, kpool, tail_first, tail)
+        return index[: int(count[0])]
+    glm_cases.check_select(golden, select)
