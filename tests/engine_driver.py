@@ -21,7 +21,7 @@ REF_DIR = ROOT / "oracle" / "_ref"
 
 # What nn's package init sizes its rooms from at a boot; a boot with any of these lines left out is refused.  The
 # classes are small except `main`, which holds the K and V planes of the cases below.
-_DEVICE_POOLS = {"resid": (4096, 48), "main": (16 << 20, 10), "attn_out": (1 << 20, 16), "logits": (8192, 1), "partials": (65536, 32)}
+_DEVICE_POOLS = {"resid": (4096, 48), "main": (16 << 20, 10), "attn_out": (1 << 20, 16), "logits": (8192, 8), "partials": (65536, 32)}
 _RAM_POOLS = {"result": (65536, 16), "experts": (4096, 1), "table": (128, 1)}
 _CARTRIDGES = {"sink": 4, "tq4": 16, "tq6": 16, "fp32": 16}
 

@@ -219,6 +219,55 @@ def _tiered_mixer(s, reference):
     return h1, state
 
 
+DN_MIX = dict(H=512, KH=2, VH=4, HD=128, D_QKV=4, D_Z=8, D_A=8, D_B=8, D_OUT=4, STEPS=12)
+
+
+def _deltanet_mixer(s, reference):
+    """`(ai_qwen_3__deltanet x planes h1)` (engine/src/packages/ai_qwen_3/cpu/opcodes/mixer__abi.cuh:15-90), a position at a
+    time from an empty state: the norm and rotation, the four coded projections as one grouped launch, the gates, the
+    conv over its window, every head's recurrence, the rotation and the out projection, the residual add.  Answers h1 of
+    every position, and the state and the window as they stand at the end."""
+    m = DN_MIX
+    H, kh, vh, hd = m["H"], m["KH"], m["VH"], m["HD"]
+    vdim, ch = vh * hd, 2 * kh * hd + vh * hd
+    rng = np.random.default_rng(59)
+    mats = [_coded(reference, rng, ch, H, m["D_QKV"]), _coded(reference, rng, vdim, H, m["D_Z"]), _coded(reference, rng, vh, H, m["D_A"]),
+            _coded(reference, rng, vh, H, m["D_B"]), _coded(reference, rng, H, vdim, m["D_OUT"])]
+    half = lambda a: to_bits(np.asarray(a, np.float32), FP16)
+    norm_in, norm_w = half(1.0 + 0.1 * rng.standard_normal(H)), half(1.0 + 0.1 * rng.standard_normal(hd))
+    conv_w = half(rng.standard_normal((ch, 4)) * 0.5)
+    a_log, dt_bias = half(rng.uniform(-1.0, 1.0, vh)), half(rng.standard_normal(vh) * 0.5)
+    signs = half(np.where(rng.random(512) < 0.5, -1.0, 1.0))
+    xs = half(rng.standard_normal((m["STEPS"], H)))
+
+    def filled(a):
+        return s.buffer(a.nbytes, a.tobytes())
+
+    def room(nbytes):
+        return s.buffer(nbytes, bytes(nbytes))
+
+    proj = ch + vdim + 2 * vh
+    state, window = room(4 * vh * hd * hd), room(2 * ch * 3)
+    planes = [filled(norm_in)]
+    for codes, scales in mats[:4]:
+        planes += [filled(codes), filled(scales)]
+    planes += [filled(conv_w), filled(a_log), filled(dt_bias), filled(norm_w), filled(mats[4][0]), filled(mats[4][1]), state, window, filled(signs),
+               filled(half([-1.0])), room(2 * (2 * H + proj + 2 * vh + ch + 2 * vdim + H))]
+    numbers = [H, kh, vh, hd, m["D_QKV"], m["D_Z"], m["D_A"], m["D_B"], m["D_OUT"]]
+    table = s.table(planes + numbers)
+    xb, hb = room(2 * H), room(2 * H)
+    h1 = np.zeros((m["STEPS"], H), np.uint16)
+    for pos in range(m["STEPS"]):
+        xb.write(xs[pos].tobytes())
+        kind, _ = s.run_cells("ai_qwen_3__deltanet", [s.buf(xb.ref), s.buf(table), s.buf(hb.ref)])
+        assert kind == s.OBJ, f"position {pos}: the verb answers h1"
+        h1[pos] = _u16(hb.read(), (H,))
+    end = {"x": xs, "state": _f32(state.read(4 * vh * hd * hd), (vh, hd, hd)), "window": _u16(window.read(2 * ch * 3), (ch, 3))}
+    s.release(table)
+    s.release_buffers()
+    return h1, end
+
+
 @pytest.fixture(scope="module")
 def cpu_session(reference):
     if reference is None or engine_driver.engine_module() is None:
@@ -237,6 +286,10 @@ def test_engine_runs_reference_family(cpu_session, reference):
     assert np.array_equal(h1, again), "the same program on the same family twice"
     assert np.isfinite(oracle.from_bits(h1, FP16)).all() and (h1 != state["x"]).mean() > 0.9, "every position's answer was written"
     assert state["warm_ks"].all() and state["cold_ks"].all() and state["hot_k"].any(axis=1).all(), "every tier holds rows at the end"
+    h1, end = _deltanet_mixer(cpu_session, reference)
+    again, _ = _deltanet_mixer(cpu_session, reference)
+    assert np.array_equal(h1, again) and np.isfinite(oracle.from_bits(h1, FP16)).all() and (h1 != end["x"]).mean() > 0.9
+    assert np.abs(end["state"]).max() > 1e-3 and end["window"].any(), "the state and the window were written"
 
 
 @pytest.fixture(scope="module")
@@ -247,7 +300,7 @@ def mixer_on_reference_family(cuda, reference):
         pytest.fail("oracle/_ref holds no reference engine and family: build them where the reference tree is mounted")
     s = engine_driver.Session(oracle.build.REF, "x86_avx2")
     try:
-        return _tiered_mixer(s, reference)
+        return _tiered_mixer(s, reference), _deltanet_mixer(s, reference)
     finally:
         s.close()
 
@@ -285,7 +338,7 @@ def test_engine_runs_the_tiered_mixer_on_this_family(gpu_session, mixer_on_refer
     same program on the reference's CPU family.  The tiers quantise what earlier positions wrote, so the two families'
     caches are compared too: a scale may differ by one fp16 step, and nearly every code must be the same."""
     from silvann_b200 import ext
-    want, want_state = mixer_on_reference_family
+    want, want_state = mixer_on_reference_family[0]
     before = ext.counters()
     got, state = _tiered_mixer(gpu_session, reference)
     after = ext.counters()
@@ -305,3 +358,21 @@ def test_engine_runs_the_tiered_mixer_on_this_family(gpu_session, mixer_on_refer
     for name in ("warm_kc", "cold_kc"):
         same = (state[name] == want_state[name]).mean()
         assert same >= 0.97, f"{name}: only {same:.3f} of the code bytes are the reference's"
+
+
+@pytest.mark.gpu
+def test_engine_runs_the_deltanet_mixer_on_this_family(gpu_session, mixer_on_reference_family, reference):
+    """The reference's Gated DeltaNet mixer, a position at a time from an empty state, on this family against the same
+    program on the reference's CPU family: every position's answer, and the recurrent state and the conv window at the end."""
+    from silvann_b200 import ext
+    want, want_end = mixer_on_reference_family[1]
+    before = ext.counters()
+    got, end = _deltanet_mixer(gpu_session, reference)
+    after = ext.counters()
+    assert after["refused"] == before["refused"] and ext.device_status() == 0
+    assert after["deltanet"] - before["deltanet"] == DN_MIX["STEPS"]
+    err = np.abs(oracle.from_bits(got, FP16) - oracle.from_bits(want, FP16))
+    print("deltanet mixer: max |h1 - reference| a position:", np.round(err.max(axis=1), 5).tolist())
+    assert err.max() <= 2e-3 * max(1.0, float(np.abs(oracle.from_bits(want, FP16)).max())), f"h1 differs by {err.max()}"
+    np.testing.assert_allclose(end["state"], want_end["state"], rtol=0, atol=1e-3 * np.abs(want_end["state"]).max())
+    assert np.abs(oracle.from_bits(end["window"], FP16) - oracle.from_bits(want_end["window"], FP16)).max() <= 2e-3
