@@ -341,6 +341,30 @@ def config1_graph(torch, ext, gen, copies=64):
     return replay, 2 * n * kvh * d * 2, "bytes"
 
 
+def coded_weights(torch, gen, copies, rows, cols, width):
+    """`copies` distinct coded matrices (random codes, scales near 1/sqrt(cols)) and one input vector, on the card."""
+    rb = cols * width // 8
+    codes = torch.randint(0, 256, (copies, rows, rb), generator=gen, device="cuda", dtype=torch.uint8)
+    scales = ((torch.rand((copies, rows), generator=gen, device="cuda") * 0.5 + 0.75) * (3.0 / cols ** 0.5)).to(torch.float16)
+    x = torch.randn((cols,), generator=gen, device="cuda", dtype=torch.float16)
+    out = torch.zeros((rows,), device="cuda", dtype=torch.float16)
+    return codes, scales, x, out, rb
+
+
+def kda_workload(torch, gen, heads, d, rows):
+    W = heads * d
+    S = torch.randn((heads, d, d), generator=gen, device="cuda", dtype=torch.float32) * 0.05
+    conved = torch.randn((3, rows, W), generator=gen, device="cuda", dtype=torch.float16)
+    f = torch.randn((rows, W), generator=gen, device="cuda", dtype=torch.float16)
+    b = torch.randn((rows, heads), generator=gen, device="cuda", dtype=torch.float16)
+    dt = torch.randn((W,), generator=gen, device="cuda", dtype=torch.float16)
+    a_log = torch.randn((heads,), generator=gen, device="cuda", dtype=torch.float16) * 0.3
+    gate = torch.randn((rows, W), generator=gen, device="cuda", dtype=torch.float16)
+    w = torch.ones((d,), device="cuda", dtype=torch.float16)
+    out = torch.zeros((rows, W), device="cuda", dtype=torch.float16)
+    return S, conved, f, b, dt, a_log, gate, w, out
+
+
 def other_workloads(torch, fam, pk, steps, warmup):
     """Configurations 1, 4 and 5 (and 2 when the prefill kernel fits), each timed alone on one GPU."""
     from silvann_b200 import ext, workloads
@@ -414,6 +438,35 @@ def other_workloads(torch, fam, pk, steps, warmup):
                                             "note": f"262,144 positions coded at {width} bits, {tqh}q/{tkvh}kv heads of {dh}: {nbytes / 1e6:.0f} MB of codes and scales a call"}
             del kc, vc, ks, vs
     torch.cuda.empty_cache()
+
+    # the weight path of a decode step: a coded matrix times one vector through the turboquant_gemv door, distinct matrices
+    # cycled so that every call reads its codes from HBM (8 x 33.5 MB at 4 bits, 4 x 67 MB at 8)
+    import ctypes as C
+    for width, copies in ((4, 8), (8, 4)):
+        rows, cols = 16384, 4096
+        codes, scales, xv, ov, rb = coded_weights(torch, gen, copies, rows, cols, width)
+        gstate = {"i": 0}
+
+        def gemv():
+            i = gstate["i"] = (gstate["i"] + 1) % copies
+            fam.nn.turboquant_gemv(ov.data_ptr(), codes[i].data_ptr(), rows * rb, scales[i].data_ptr(), rows * 2, xv.data_ptr(), width, rows, cols, None)
+        before = ext.counters()["gemv_fast"]
+        ms = time_loop(torch, gemv, max(steps * 5, 50), max(warmup, 5))
+        assert ext.counters()["gemv_fast"] > before, "the coded matrix did not take the tensor-core kernel"
+        nbytes = rows * (rb + 2) + cols * 2 + rows * 2
+        out[f"tq{width}_gemv_16384x4096"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms, "frac_hbm": nbytes / ms / 1e6 / hbm,
+                                             "note": f"turboquant_gemv door, 16,384 rows of 4,096 codes at {width} bits: {nbytes / 1e6:.1f} MB a call, {copies} matrices cycled"}
+        del codes, scales
+    torch.cuda.empty_cache()
+
+    # Kimi Delta Attention, one decode step of 64 heads of 128 (GLM's shape): the state read and written once, 8.4 MB
+    heads, d = 64, 128
+    S, conved, f, b, dt, a_log, gate, w, o = kda_workload(torch, gen, heads, d, 1)
+    ms = time_loop(torch, lambda: fam.nn.kda_step(S.data_ptr(), conved.data_ptr(), f.data_ptr(), b.data_ptr(), dt.data_ptr(), a_log.data_ptr(), gate.data_ptr(),
+                                                  w.data_ptr(), o.data_ptr(), heads, d, C.c_float(-5.0), C.c_float(1e-5), None), max(steps * 10, 100), 10)
+    nbytes = 2 * heads * d * d * 4 + 6 * heads * d * 2
+    out["kda_decode_64heads"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_step": ms, "frac_hbm": nbytes / ms / 1e6 / hbm,
+                                 "note": "kda_step door, 64 heads x 128x128 fp32 state (8.4 MB: stays in L2 between steps), one block a head"}
 
     # configuration 5: recurrent decode steps (batched so that state traffic is real) and the prompt
     heads, d = 32, 128
@@ -759,6 +812,24 @@ def run_case(args):
             fam.nn.attention_weights_tq(tp.data_ptr(), tres.data_ptr(), tq_q.data_ptr(), kc[i].data_ptr(), ks[i].data_ptr(), tqh, tkvh, dh, Lt, width)
             fam.nn.attention_residual_mix_tq(tres.data_ptr(), tp.data_ptr(), vc[i].data_ptr(), vs[i].data_ptr(), tqh, tkvh, dh, Lt, width)
         work, unit = 2 * Lt * tkvh * (rb + 2), "bytes"
+    elif name in ("gemv4_small", "gemv8_small"):
+        # a coded matrix of 16,384 x 4,096 through the turboquant_gemv door, 8 / 4 distinct matrices cycled (268 MB)
+        width = 4 if name == "gemv4_small" else 8
+        rows, cols, copies = 16384, 4096, (8 if width == 4 else 4)
+        codes, scales, xv, ov, rb = coded_weights(torch, gen, copies, rows, cols, width)
+        gstate = {"i": 0}
+
+        def fn():
+            i = gstate["i"] = (gstate["i"] + 1) % copies
+            fam.nn.turboquant_gemv(ov.data_ptr(), codes[i].data_ptr(), rows * rb, scales[i].data_ptr(), rows * 2, xv.data_ptr(), width, rows, cols, None)
+        work, unit = rows * (rb + 2) + cols * 2 + rows * 2, "bytes"
+    elif name == "kda_decode":
+        import ctypes as C
+        heads, d = 64, 128
+        S, conved, f, b, dt, a_log, gate, w, o = kda_workload(torch, gen, heads, d, 1)
+        fn = lambda: fam.nn.kda_step(S.data_ptr(), conved.data_ptr(), f.data_ptr(), b.data_ptr(), dt.data_ptr(), a_log.data_ptr(), gate.data_ptr(),
+                                     w.data_ptr(), o.data_ptr(), heads, d, C.c_float(-5.0), C.c_float(1e-5), None)
+        work, unit = 2 * heads * d * d * 4 + 6 * heads * d * 2, "bytes"
     elif name == "deltanet_64":
         heads, d, seqs = 32, 128, 64
         S = torch.zeros((seqs, heads, d, d), device="cuda", dtype=torch.float32)

@@ -290,7 +290,8 @@ const silvann_b200_family* silvann_silicon_family_get(uint32_t abi_version);
 #define SILVANN_B200_COUNTER_DELTANET        5   /* DeltaNet door calls */
 #define SILVANN_B200_COUNTER_LAUNCHES        6   /* kernels of this library launched, all paths */
 #define SILVANN_B200_COUNTER_EXT_CALLS       7   /* silvann_b200_* compute entry points called */
-#define SILVANN_B200_COUNTERS                8
+#define SILVANN_B200_COUNTER_GEMV_FAST       8   /* coded matrix-vector doors answered by the tensor-core kernel */
+#define SILVANN_B200_COUNTERS                9
 
 const char* silvann_b200_last_error(void);
 /* Copies min(n, SILVANN_B200_COUNTERS) process-wide counters into out; reset != 0 zeroes them afterwards. */

@@ -583,6 +583,10 @@ static void d_rmsnorm_rotate(sv_h16* rot, sv_h16* o, const sv_h16* x, const sv_h
     d_rmsnorm(o, x, w, n, eps, over);                             /* nn's definition: the two doors, one after the other */
     d_hadamard_rotate(rot, o, sign, n, over);
 }
+static bool gemv_fast_off() {
+    static const bool off = [] { const char* e = getenv("SILVANN_B200_GEMV_AS_WORDED"); return e && e[0] == '1'; }();
+    return off;
+}
 static void d_turboquant_gemv(sv_h16* out, const sv_u8* weights, sv_u64 w_room, const sv_u8* luts, sv_u64 l_room, const sv_h16* x, sv_u64 d,
                               sv_u64 rows, sv_u64 cols, sv_fault* over) {
     flush();
@@ -591,15 +595,38 @@ static void d_turboquant_gemv(sv_h16* out, const sv_u8* weights, sv_u64 w_room, 
     sv_tq_groups g;
     memset(&g, 0, sizeof g);
     g.codes[0] = (sv_u64)(uintptr_t)weights; g.luts[0] = (sv_u64)(uintptr_t)luts; g.rows[0] = rows; g.d[0] = d; g.out_at[0] = 0; g.count = 1;
+    if (!gemv_fast_off() && sv::tq_gemv_fast_fits(&g, cols, 1)) {
+        const sv_u64 row_bytes = cols * d / 8;
+        sv_u64 cap = rows;                                                  /* a row its rooms do not hold is left alone */
+        if (w_room / row_bytes < cap) cap = w_room / row_bytes;
+        if (l_room / 2 < cap) cap = l_room / 2;
+        const cudaError_t e = sv::tq_gemv_fast_launch(out, &g, &cap, x, cols, 1, 0, over, 0);
+        if (e != cudaErrorInvalidValue) { if (e == cudaSuccess) bump(SILVANN_B200_COUNTER_GEMV_FAST); check("turboquant_gemv", e); return; }
+        (void)cudaGetLastError();
+    }
     check("turboquant_gemv", sv::tq_gemv_groups_launch(out, &g, w_room ? w_room : 1, l_room ? l_room : 1, x, cols, over, 0));
 }
-static void d_turboquant_gemv_groups(sv_h16* out, sv_tq_groups g, const sv_h16* x, sv_u64 cols, sv_fault* over) {
+static void d_turboquant_gemv_groups_n(sv_h16* out, sv_tq_groups g, const sv_h16* x, sv_u64 cols, sv_u64 n, sv_u64 out_stride, sv_fault* over) {
     flush();
-    if (g.count == 0 || cols == 0) return;
+    if (g.count == 0 || cols == 0 || n == 0) return;
     if (g.count > 12) { launch_refused("turboquant_gemv_groups", cudaSuccess); return; }
-    const cudaError_t e = sv::tq_gemv_groups_launch(out, &g, 0, 0, x, cols, over, 0);
-    if (e == cudaErrorInvalidValue) { (void)cudaGetLastError(); launch_refused("turboquant_gemv_groups", cudaSuccess); return; }
-    check("turboquant_gemv_groups", e);
+    if (!gemv_fast_off() && sv::tq_gemv_fast_fits(&g, cols, n)) {
+        const cudaError_t e = sv::tq_gemv_fast_launch(out, &g, nullptr, x, cols, n, out_stride, over, 0);
+        if (e != cudaErrorInvalidValue) { if (e == cudaSuccess) bump(SILVANN_B200_COUNTER_GEMV_FAST); check("turboquant_gemv_groups", e); return; }
+        (void)cudaGetLastError();
+    }
+    for (sv_u64 k = 0; k < n; ++k) {                                        /* as worded: the one-input door an input at a time */
+        sv_tq_groups gk = g;
+        sv_h16* o = out;
+        if (out_stride != 0) o += k * out_stride;
+        else for (sv_u64 i = 0; i < gk.count; ++i) gk.out_at[i] += k * gk.rows[i];
+        const cudaError_t e = sv::tq_gemv_groups_launch(o, &gk, 0, 0, x + k * cols, cols, over, 0);
+        if (e == cudaErrorInvalidValue) { (void)cudaGetLastError(); launch_refused("turboquant_gemv_groups", cudaSuccess); return; }
+        check("turboquant_gemv_groups", e);
+    }
+}
+static void d_turboquant_gemv_groups(sv_h16* out, sv_tq_groups g, const sv_h16* x, sv_u64 cols, sv_fault* over) {
+    d_turboquant_gemv_groups_n(out, g, x, cols, 1, 0, over);
 }
 
 /* ---- the GLM mixer's doors (glm_doors.cu): KDA, the latent's absorb and expand, the indexer ---- */
@@ -772,6 +799,7 @@ static void install_doors() {
     g_nn.rmsnorm_rotate = d_rmsnorm_rotate;
     g_nn.turboquant_gemv = d_turboquant_gemv;
     g_nn.turboquant_gemv_groups = d_turboquant_gemv_groups;
+    g_nn.turboquant_gemv_groups_n = d_turboquant_gemv_groups_n;
     g_nn.turboquant_decode = d_turboquant_decode;
     g_nn.hadamard_blocks = d_hadamard_blocks;
     g_nn.turboquant_encode_rows = d_turboquant_encode_rows;
