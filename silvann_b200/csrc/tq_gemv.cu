@@ -11,14 +11,20 @@
  *     never pass through fp32 registers, and the eight columns of the B operand are eight INPUT VECTORS — the groups-over-
  *     n-inputs door reads a matrix once for all of them;
  *   · a sum does not care about its order, so the MMA's k index is permuted to follow the bytes as they lie: lane (g, t)
- *     of a warp loads 16 neighbouring bytes of rows g and g + 8 straight into registers (no staging in shared memory) and
- *     uses them as its A fragments; the matching x values sit in registers as B fragments for the whole kernel;
+ *     of a warp takes 16 neighbouring bytes of rows g and g + 8 as its A fragments; the matching x values sit in registers
+ *     as B fragments for the whole kernel;
+ *   · the codes come through a ring of shared-memory stages filled by bulk copies (a row a copy, rows 64 bytes further apart
+ *     than they are long, so the 16-byte reads of a quarter-warp never share a bank) that complete on mbarriers: loads held
+ *     in registers serialised on the few register scoreboards (a wait for an old load waited for the newest too), copies
+ *     by the async proxy do not;
  *   · the table is 256 bytes an entry — 32 copies of the 4-bit pair table, then 32 of the 8-bit table, one a bank — so a
  *     lookup never conflicts and its offset is ONE byte-permute of the code word;
- *   · a block is 16 warps that split a row's bytes 64 at a time; their partial sums for a tile of 16 rows meet in shared
- *     memory, double-buffered, one barrier a tile.
- * Shapes it takes: widths 4 and 8, row bytes a multiple of 64, codes 16-byte aligned, at most 8 inputs, at most
- * 64 x registers a thread (cols ≤ 8,192).  Anything else stays with the as-worded kernel in tq.cu. */
+ *   · a block is 16 warps that split a row's bytes 64 at a time; their partial sums for a step (one to four tiles of 16
+ *     rows, about 32 KB of codes) meet in shared memory, double-buffered, one barrier a step, after which the step's stage
+ *     is filled again.
+ * Shapes it takes: widths 4 and 8, row bytes a multiple of 64 and at most 4,096, codes 16-byte aligned, at most 8 inputs.
+ * Anything else stays with the as-worded kernel in tq.cu.  Every mbarrier wait is bounded; one that runs out ORs "B2TO"
+ * into the device's status word and the block leaves. */
 #include "common.cuh"
 #include "kernels.h"
 #include <string.h>
@@ -33,120 +39,291 @@ static __device__ const uint16_t g_tq_levels_gemv[318] = {
 
 constexpr int GV_WARPS = 16, GV_THREADS = GV_WARPS * 32, GV_LUT_BYTES = 256 * 256;
 
+constexpr int GV_STAGES_MAX = 4, GV_ROW_PAD = 64, GV_TS_MAX = 2;       /* slots of the ring at most; a row's padding; tiles a step at most */
+
+/* The table as a block holds it (256 entries of 256 bytes: 32 copies of the 4-bit pair, then 32 of the 8-bit level twice),
+ * made once a device and copied into every block by one bulk copy instead of being built again by each. */
+__device__ uint4 g_gv_lut_image[GV_LUT_BYTES / 16];
+__global__ void __launch_bounds__(256) gv_lut_image_kernel() {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < 256 * 16; i += gridDim.x * blockDim.x) {
+        const int b = i >> 4, q = i & 15;
+        const uint32_t l8 = g_tq_levels_gemv[62 + b];
+        const uint32_t e = q < 8 ? ((uint32_t)g_tq_levels_gemv[14 + (b & 15)] | ((uint32_t)g_tq_levels_gemv[14 + (b >> 4)] << 16)) : (l8 | (l8 << 16));
+        g_gv_lut_image[i] = make_uint4(e, e, e, e);
+    }
+}
+
+cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_t* rows_cap, const uint16_t* x, uint64_t cols, uint64_t inputs,
+                                uint64_t out_stride, unsigned int* over, cudaStream_t st);
+#ifdef SV_GEMV_TRACE
+/* Development aid, compiled only on request: every block leaves %globaltimer stamps (ns) of its phases here. */
+__device__ unsigned long long g_gv_trace[256 * 32];
+__device__ __forceinline__ unsigned long long gv_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define SV_GTR(k) do { if (threadIdx.x == 0 && blockIdx.x < 256 && (k) < 32) g_gv_trace[blockIdx.x * 32 + (k)] = gv_gtime(); } while (0)
+#define SV_GTS(n, k) do { if ((n) < 4) SV_GTR(2 + (n) * 4 + (k)); } while (0)
+extern "C" __attribute__((visibility("default"))) int sv_gemv_trace_read(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_gv_trace, sizeof(unsigned long long) * 256 * 32);
+}
+extern "C" __attribute__((visibility("default"))) int sv_gemv_trace_run(uint16_t* out, const void* groups, const uint16_t* x, uint64_t cols) {
+    return (int)tq_gemv_fast_launch(out, groups, nullptr, x, cols, 1, 0, nullptr, 0);
+}
+#else
+#define SV_GTR(k) do {} while (0)
+#define SV_GTS(n, k) do {} while (0)
+#endif
+
 struct GemvFast {
     const uint8_t* codes[12];
     const uint16_t* scales[12];
-    uint32_t rows[12], d[12], tile0[13];       /* group i's tiles of 16 rows are [tile0[i], tile0[i+1]) */
+    uint32_t rows[12], d[12], halves[12], step0[13];   /* group i's steps (ts tiles of 16 rows each) are [step0[i], step0[i+1]); halves: slots a step */
     uint64_t out_at[12];
-    uint32_t count, cols, inputs;
+    uint32_t count, cols, inputs, x_wide;      /* x_wide: x may be read 16 bytes at a time */
+    uint32_t ts, stage_bytes, smem_bytes;      /* tiles a step; bytes a stage; the block's dynamic shared memory */
     uint64_t out_stride;
+    unsigned int* status;
 };
 
-__device__ __forceinline__ uint32_t gv_lut(uint32_t lut, uint32_t lane4, uint32_t w, int idx) {
+/* The table entry of byte `idx` of word `w` for this lane.  The table starts on a 64 KB boundary of the shared window and
+ * an entry is 256 bytes, so the address is ONE byte-permute: bytes 3, 2 and 0 of `lane_at` (the table's base, and this
+ * lane's bank within an entry) around the code byte. */
+__device__ __forceinline__ uint32_t gv_lut(uint32_t lane_at, uint32_t w, int idx) {
     uint32_t v;
-    const uint32_t off = __byte_perm(w, lane4, 0x5504u | ((uint32_t)idx << 4));        /* (code byte) << 8 | lane · 4 */
-    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(lut + off));
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(__byte_perm(w, lane_at, 0x7604u | ((uint32_t)idx << 4))));
     return v;
 }
-__device__ __forceinline__ uint4 gv_ldg(const uint8_t* p) {
+__device__ __forceinline__ uint4 gv_lds128(uint32_t a) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
     return v;
+}
+/* `bytes` (a multiple of 16) from global to shared, both 16-byte aligned, completion counted on `bar` */
+__device__ __forceinline__ void gv_bulk(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy) : "memory");
 }
 
-/* NIW: the 64-byte pieces of a row one warp owns at most (pieces warp, warp + 16, ...).  x registers a thread: 16·NIW. */
+/* One 64-byte piece of rows g and g + 8 through the table and the tensor cores: 8 MMAs at 4 bits (bytes 2m, 2m+1 are four
+ * codes a row), 4 at 8 bits (bytes 4m .. 4m+3), alternating between two accumulators so that an MMA does not wait for the
+ * one before it.  The sixteen lookups of half a piece are all asked for before the first MMA that needs one: a lookup is a
+ * shared-memory round trip, and four at a time (an MMA's worth) left the warp waiting for each. */
+__device__ __forceinline__ void gv_piece(float (&c0)[4], float (&c1)[4], const uint4& wa, const uint4& wb, const uint32_t* xr, uint32_t d, uint32_t at4,
+                                         uint32_t at8) {
+    const uint32_t wsa[4] = {wa.x, wa.y, wa.z, wa.w}, wsb[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        uint32_t la[8], lb[8];                                               /* the eight bytes of this half of row g, of row g + 8 */
+        if (d == 4) {
+#pragma unroll
+            for (int b = 0; b < 8; ++b) { la[b] = gv_lut(at4, wsa[half * 2 + (b >> 2)], b & 3); lb[b] = gv_lut(at4, wsb[half * 2 + (b >> 2)], b & 3); }
+#pragma unroll
+            for (int m = 0; m < 4; ++m)                                      /* bytes 2m, 2m + 1 of the half */
+                mma16816<SV_DTYPE_FP16>((m & 1) ? c1 : c0, la[2 * m], lb[2 * m], la[2 * m + 1], lb[2 * m + 1], xr[half * 8 + 2 * m], xr[half * 8 + 2 * m + 1]);
+        } else {
+#pragma unroll
+            for (int b = 0; b < 8; ++b) { la[b] = gv_lut(at8, wsa[half * 2 + (b >> 2)], b & 3); lb[b] = gv_lut(at8, wsb[half * 2 + (b >> 2)], b & 3); }
+#pragma unroll
+            for (int m = 0; m < 2; ++m)                                      /* bytes 4m .. 4m + 3 of the half */
+                mma16816<SV_DTYPE_FP16>((m & 1) ? c1 : c0, __byte_perm(la[4 * m], la[4 * m + 1], 0x5410), __byte_perm(lb[4 * m], lb[4 * m + 1], 0x5410),
+                                        __byte_perm(la[4 * m + 2], la[4 * m + 3], 0x5410), __byte_perm(lb[4 * m + 2], lb[4 * m + 3], 0x5410),
+                                        xr[half * 4 + 2 * m], xr[half * 4 + 2 * m + 1]);
+        }
+    }
+}
+
+/* NIW: the 64-byte pieces of a row one warp owns at most (pieces warp, warp + 16, ...); x registers a thread: 16·NIW.
+ * Sixteen warps work the codes and a seventeenth only fetches: a copy's issue waits for the memory system to take it, and
+ * a warp that both fetched and worked made the whole block wait for that at the next barrier.  The ring's slots are
+ * handed back and forth on mbarriers (`full`: the copies' bytes; `empty`: one arrival a working warp).
+ * A step is ts tiles of 16 rows; where 16 rows of a group are more than a slot holds, a row is cut in two halves and a
+ * step takes two slots, one after the other (a.halves). */
 template <int NIW>
-__global__ void __launch_bounds__(GV_THREADS, 1) tq_gemv_fast_kernel(uint16_t* out, GemvFast a, const uint16_t* x, unsigned int* over) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    uint32_t* lut_w = reinterpret_cast<uint32_t*>(smem);
-    float* part = reinterpret_cast<float*>(smem + GV_LUT_BYTES);              /* [2][GV_WARPS][16 rows][8 inputs] */
+__global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16_t* out, GemvFast a, const uint16_t* x, unsigned int* over) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint32_t stage_at_s[GV_STAGES_MAX];
+    __shared__ uint32_t stages_s;
+    /* The table sits on the first 64 KB boundary of the shared window inside this block's memory; the partial sums, the
+     * barriers and the ring's slots are carved from what lies before it and after it. */
+    const uint32_t ts = a.ts;
+    const uint32_t base = smem_u32(smem), lut = (base + 0xFFFFu) & ~0xFFFFu, end = base + a.smem_bytes;
+    const uint32_t part_bytes = 2u * ts * GV_WARPS * 128u * (uint32_t)sizeof(float), small = part_bytes + 128u;
+    uint32_t before = base, after = lut + (uint32_t)GV_LUT_BYTES;            /* the next free byte either side */
+    uint32_t part_at;
+    if (lut - before >= small) { part_at = before; before += small; } else { part_at = after; after += small; }
+    float* part = reinterpret_cast<float*>(smem + (part_at - base));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + (part_at - base) + part_bytes);
+    uint64_t* empty = full + GV_STAGES_MAX;
+    uint64_t* table_bar = empty + GV_STAGES_MAX;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(table_bar + 1);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-    for (int i = tid; i < 256 * 32; i += GV_THREADS) {
-        const int b = i >> 5, l = i & 31;
-        const uint32_t l8 = g_tq_levels_gemv[62 + b];
-        lut_w[b * 64 + l] = (uint32_t)g_tq_levels_gemv[14 + (b & 15)] | ((uint32_t)g_tq_levels_gemv[14 + (b >> 4)] << 16);
-        lut_w[b * 64 + 32 + l] = l8 | (l8 << 16);
+    SV_GTR(0);
+    if (tid == 0) {
+        uint32_t n = 0;
+        for (; n < (uint32_t)GV_STAGES_MAX && before + a.stage_bytes <= lut; ++n, before += a.stage_bytes) stage_at_s[n] = before;
+        for (; n < (uint32_t)GV_STAGES_MAX && after + a.stage_bytes <= end; ++n, after += a.stage_bytes) stage_at_s[n] = after;
+        stages_s = n;
+        for (uint32_t st = 0; st < (uint32_t)GV_STAGES_MAX; ++st) { mbar_init(&full[st], 1); mbar_init(&empty[st], GV_WARPS); }
+        mbar_init(table_bar, 1);
+        *abort_flag = 0u;
+        mbar_fence_init();
     }
     __syncthreads();
-    const uint32_t lut4 = smem_u32(smem), lut8 = lut4 + 128u, lane4 = (uint32_t)lane * 4u;
-    const uint32_t tiles = a.tile0[a.count];
+    const uint32_t S = stages_s;
+    if (S < 2) return;                                                       /* the launcher sized the block's memory so that two fit */
+    const uint32_t steps = a.step0[a.count];
+
+    auto place = [&](uint32_t s, int& gi, uint32_t& row0) {                  /* where step `s` lies: its group, its first row */
+        gi = 0;
+        while (s >= a.step0[gi + 1]) ++gi;
+        row0 = (s - a.step0[gi]) * (16u * ts);
+    };
+
+    if (warp == GV_WARPS) {
+        /* ---- the fetching warp: the table, then slot after slot as the working warps hand them back ---- */
+        const uint64_t policy = l2_policy_evict_first();
+        if (lane == 0) { mbar_expect_tx(table_bar, GV_LUT_BYTES); gv_bulk(lut, g_gv_lut_image, GV_LUT_BYTES, table_bar, l2_policy_evict_last()); }
+        uint32_t m = 0;                                                      /* slots filled so far */
+        int gi = -1;
+        uint32_t lo = 0, hi = 0, row_bytes = 0, rows = 0, halves = 1, seg = 0;
+        const uint8_t* codes = nullptr;
+        for (uint32_t s = blockIdx.x; s < steps; s += gridDim.x) {
+            while (s >= hi) {                                                /* a group's numbers are read once, as its first step comes */
+                ++gi; lo = a.step0[gi]; hi = a.step0[gi + 1];
+                row_bytes = a.cols * a.d[gi] / 8u; rows = a.rows[gi]; halves = a.halves[gi]; seg = row_bytes / halves; codes = a.codes[gi];
+            }
+            const uint32_t row0 = (s - lo) * (16u * ts), there = min(16u * ts, rows - row0);
+            for (uint32_t h = 0; h < halves; ++h, ++m) {
+                const uint32_t slot = m % S;
+                if (m >= S && !mbar_wait(&empty[slot], ((m / S) - 1u) & 1u, abort_flag, a.status)) { s = steps; break; }
+                if (lane == 0) mbar_expect_tx(&full[slot], there * seg);
+                __syncwarp();
+                const uint32_t dst = stage_at_s[slot];
+                for (uint32_t r = (uint32_t)lane; r < there; r += 32u)
+                    gv_bulk(dst + r * (seg + GV_ROW_PAD), codes + (size_t)(row0 + r) * row_bytes + (size_t)h * seg, seg, &full[slot], policy);
+            }
+        }
+        return;                                                              /* nothing after this point waits for the fetching warp */
+    }
+
+    /* ---- the sixteen working warps ---- */
+    const uint32_t at4 = lut | ((uint32_t)lane * 4u), at8 = at4 + 128u;     /* the 4-bit pair table, then the 8-bit one, in every entry */
     uint32_t xr[NIW][16];                                                    /* this lane's B fragments: input g, the columns of its bytes */
-    uint32_t have_d = 0;
+    uint32_t have_d = 0, n = 0, m = 0;
+    bool table_ready = false, gave_up = false;
     int buf = 0;
     bool hit = false;
-    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, buf ^= 1) {
-        int gi = 0;
-        while (tile >= a.tile0[gi + 1]) ++gi;
-        const uint32_t d = a.d[gi], rows = a.rows[gi], row0 = (tile - a.tile0[gi]) * 16u;
-        const uint32_t row_bytes = a.cols * d / 8u, pieces = row_bytes / 64u, per_lane = d == 4 ? 32u : 16u;     /* columns a lane's 16 bytes hold */
+    int gi = -1;
+    uint32_t lo = 0, hi = 0, d = 0, rows = 0, row_bytes = 0, halves = 1, seg = 0, pieces = 0;
+    const uint16_t* sc = nullptr;
+    uint64_t out_row = 0, out_input = 0;                                     /* an answer's place: out_row + row + input · out_input */
+    for (uint32_t s = blockIdx.x; s < steps && !gave_up; s += gridDim.x, ++n, buf ^= 1) {
+        if (n == 1) SV_GTR(25);
+        while (s >= hi) {                                                    /* a group's numbers are read once, as its first step comes */
+            ++gi; lo = a.step0[gi]; hi = a.step0[gi + 1];
+            d = a.d[gi]; rows = a.rows[gi]; row_bytes = a.cols * d / 8u; halves = a.halves[gi]; seg = row_bytes / halves; pieces = row_bytes / 64u;
+            sc = a.scales[gi];
+            out_row = a.out_at[gi]; out_input = a.out_stride != 0 ? a.out_stride : (uint64_t)rows;
+        }
+        const uint32_t row0 = (s - lo) * (16u * ts);
+        const uint32_t per_lane = d == 4 ? 32u : 16u;                        /* columns a lane's 16 bytes hold */
+        if (n == 1) SV_GTR(26);
         if (d != have_d) {                                                   /* the columns a lane owns depend on the width */
             have_d = d;
 #pragma unroll
             for (int i = 0; i < NIW; ++i) {
                 const uint32_t piece = (uint32_t)warp + (uint32_t)i * GV_WARPS;
                 const uint32_t c0 = piece * (64u * 8u / d) + (uint32_t)t * per_lane;
+                const bool live = piece < pieces && (uint32_t)g < a.inputs;
+                const uint16_t* src = x + (size_t)g * a.cols + c0;
 #pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    uint32_t v = 0u;
-                    if (piece < pieces && (uint32_t)g < a.inputs && (uint32_t)e * 2u < per_lane)
-                        v = *reinterpret_cast<const uint32_t*>(x + (size_t)g * a.cols + c0 + e * 2);
-                    xr[i][e] = v;
+                for (int e = 0; e < 16; e += 4) {
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (live && (uint32_t)e * 2u < per_lane) {
+                        if (a.x_wide) v = *reinterpret_cast<const uint4*>(src + e * 2);
+                        else { const uint32_t* p = reinterpret_cast<const uint32_t*>(src + e * 2); v = make_uint4(p[0], p[1], p[2], p[3]); }
+                    }
+                    xr[i][e] = v.x; xr[i][e + 1] = v.y; xr[i][e + 2] = v.z; xr[i][e + 3] = v.w;
                 }
             }
         }
-        const uint32_t ra = min(row0 + (uint32_t)g, rows - 1u), rb = min(row0 + (uint32_t)g + 8u, rows - 1u);
-        const uint8_t* pa = a.codes[gi] + (size_t)ra * row_bytes + (size_t)t * 16u;
-        const uint8_t* pb = a.codes[gi] + (size_t)rb * row_bytes + (size_t)t * 16u;
-        uint4 wa[NIW], wb[NIW];
+        if (n == 1) SV_GTR(27);
+        uint16_t scale[GV_TS_MAX];                                                   /* this warp's outputs' rows' scales, on their way while the step is worked */
+        {
 #pragma unroll
-        for (int i = 0; i < NIW; ++i) {
-            const uint32_t piece = (uint32_t)warp + (uint32_t)i * GV_WARPS;
-            if (piece < pieces) { wa[i] = gv_ldg(pa + (size_t)piece * 64u); wb[i] = gv_ldg(pb + (size_t)piece * 64u); }
-            else { wa[i] = make_uint4(0, 0, 0, 0); wb[i] = wa[i]; }
-        }
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int i = 0; i < NIW; ++i) {
-            const uint32_t piece = (uint32_t)warp + (uint32_t)i * GV_WARPS;
-            if (piece >= pieces) continue;                                   /* the whole warp together */
-            const uint32_t wsa[4] = {wa[i].x, wa[i].y, wa[i].z, wa[i].w}, wsb[4] = {wb[i].x, wb[i].y, wb[i].z, wb[i].w};
-            if (d == 4) {
-#pragma unroll
-                for (int m = 0; m < 8; ++m) {                                /* bytes 2m, 2m+1: four codes a row */
-                    const uint32_t ua = wsa[m >> 1], ub = wsb[m >> 1];
-                    const int b0 = (m & 1) * 2;
-                    mma16816<SV_DTYPE_FP16>(c, gv_lut(lut4, lane4, ua, b0), gv_lut(lut4, lane4, ub, b0), gv_lut(lut4, lane4, ua, b0 + 1),
-                                            gv_lut(lut4, lane4, ub, b0 + 1), xr[i][2 * m], xr[i][2 * m + 1]);
-                }
-            } else {
-#pragma unroll
-                for (int m = 0; m < 4; ++m) {                                /* bytes 4m .. 4m+3: four codes a row */
-                    const uint32_t ua = wsa[m], ub = wsb[m];
-                    const uint32_t a0 = __byte_perm(gv_lut(lut8, lane4, ua, 0), gv_lut(lut8, lane4, ua, 1), 0x5410);
-                    const uint32_t a1 = __byte_perm(gv_lut(lut8, lane4, ub, 0), gv_lut(lut8, lane4, ub, 1), 0x5410);
-                    const uint32_t a2 = __byte_perm(gv_lut(lut8, lane4, ua, 2), gv_lut(lut8, lane4, ua, 3), 0x5410);
-                    const uint32_t a3 = __byte_perm(gv_lut(lut8, lane4, ub, 2), gv_lut(lut8, lane4, ub, 3), 0x5410);
-                    mma16816<SV_DTYPE_FP16>(c, a0, a1, a2, a3, xr[i][2 * m], xr[i][2 * m + 1]);
-                }
+            for (uint32_t sub = 0; sub < GV_TS_MAX; ++sub) {
+                const uint32_t r = row0 + sub * 16u + (uint32_t)warp;
+                scale[sub] = 0;
+                if (sub < ts && r < rows) asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(scale[sub]) : "l"(sc + r));
             }
         }
-        /* c0, c1: (row g, inputs 2t, 2t+1) · c2, c3: (row g + 8, the same inputs) */
-        float* mine = part + ((size_t)buf * GV_WARPS + warp) * 128;
-        *reinterpret_cast<float2*>(mine + g * 8 + t * 2) = make_float2(c[0], c[1]);
-        *reinterpret_cast<float2*>(mine + (g + 8) * 8 + t * 2) = make_float2(c[2], c[3]);
-        __syncthreads();                                                     /* one a tile: the other buffer is free again by the next */
-        if (tid < 128) {
-            const uint32_t r = (uint32_t)tid >> 3, k = (uint32_t)tid & 7u;
-            if (row0 + r < rows && k < a.inputs) {
-                float sum = 0.f;
+        SV_GTS(n, 0);
+        float c[GV_TS_MAX][4];                                               /* a tile's sums */
 #pragma unroll
-                for (int w = 0; w < GV_WARPS; ++w) sum += part[((size_t)buf * GV_WARPS + w) * 128 + tid];
-                const float scale = H::to_float(a.scales[gi][row0 + r]);
-                const uint64_t at = a.out_stride != 0 ? k * a.out_stride + a.out_at[gi] + row0 + r : a.out_at[gi] + (uint64_t)k * rows + row0 + r;
-                out[at] = H::from_float(sum * scale, hit);
+        for (int sub = 0; sub < GV_TS_MAX; ++sub) { c[sub][0] = 0.f; c[sub][1] = 0.f; c[sub][2] = 0.f; c[sub][3] = 0.f; }
+        for (uint32_t h = 0; h < halves; ++h, ++m) {
+            const uint32_t slot = m % S;
+            bool landed = mbar_wait(&full[slot], (m / S) & 1u, abort_flag, a.status);
+            if (!table_ready) { landed = mbar_wait(table_bar, 0u, abort_flag, a.status) && landed; table_ready = true; SV_GTR(1); }
+            {   /* every working warp goes on, or none: a vote on the working warps' own barrier */
+                uint32_t any;
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.or.pred p, 1, 512, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(any) : "r"(landed ? 0u : 1u) : "memory");
+                if (any) { gave_up = true; break; }
             }
+            if (h == 0) SV_GTS(n, 1);
+            const uint32_t slot_at = stage_at_s[slot] + (uint32_t)t * 16u, stride = seg + GV_ROW_PAD;
+#pragma unroll
+            for (uint32_t sub = 0; sub < GV_TS_MAX; ++sub) {
+                if (sub >= ts) break;
+                float c1[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint32_t at_a = slot_at + (sub * 16u + (uint32_t)g) * stride, at_b = at_a + 8u * stride;
+#pragma unroll
+                for (int i = 0; i < NIW; ++i) {
+                    const uint32_t piece = (uint32_t)warp + (uint32_t)i * GV_WARPS;
+                    if (piece >= pieces || (piece * 64u) / seg != h) continue;                       /* the whole warp together */
+                    const uint32_t off = piece * 64u - h * seg;
+                    const uint4 ua = gv_lds128(at_a + off), ub = gv_lds128(at_b + off);
+                    gv_piece(c[sub], c1, ua, ub, xr[i], d, at4, at8);
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) c[sub][e] += c1[e];
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[slot]);                        /* this warp has read the slot */
         }
+        if (gave_up) break;
+        /* c0, c1: (row g, inputs 2t, 2t+1) · c2, c3: (row g + 8, the same inputs).  Warp w's 128 sums are stored turned by
+         * 8·w places, so that the four lanes that later add one output's sixteen parts read four different bank groups. */
+#pragma unroll
+        for (uint32_t sub = 0; sub < GV_TS_MAX; ++sub) {
+            if (sub >= ts) break;
+            float* mine = part + (((size_t)buf * ts + sub) * GV_WARPS + warp) * 128;
+            *reinterpret_cast<float2*>(mine + ((g * 8 + t * 2 + warp * 8) & 127)) = make_float2(c[sub][0], c[sub][1]);
+            *reinterpret_cast<float2*>(mine + (((g + 8) * 8 + t * 2 + warp * 8) & 127)) = make_float2(c[sub][2], c[sub][3]);
+        }
+        SV_GTS(n, 2);
+        asm volatile("barrier.cta.sync 1, 512;" ::: "memory");              /* the working warps' partial sums are whole */
+        SV_GTS(n, 3);
+        /* warp w adds outputs 8w .. 8w+7 of each tile: lane l is output 8w + l/4, and adds the parts of warps l%4, +4, +8, +12 */
+#pragma unroll
+        for (uint32_t sub = 0; sub < GV_TS_MAX; ++sub) {
+            if (sub >= ts) break;
+            const uint32_t o = (uint32_t)warp * 8u + ((uint32_t)lane >> 2), q = (uint32_t)lane & 3u;
+            const float* from = part + ((size_t)buf * ts + sub) * GV_WARPS * 128;
+            float sum = 0.f;
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) { const uint32_t w = q + 4u * j; sum += from[w * 128u + ((o + 8u * w) & 127u)]; }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            const uint32_t r = row0 + sub * 16u + (o >> 3), k = o & 7u;
+            if (q == 0 && r < rows && k < a.inputs) out[out_row + r + k * out_input] = H::from_float(sum * H::to_float(scale[sub]), hit);
+        }
+        if (n == 0) SV_GTR(24);
     }
+    /* After a wait gave up, copies may still be on their way into this block's memory: the first working thread waits
+     * (bounded) for every slot's barrier to settle before the memory is given back. */
+    if (gave_up && tid == 0)
+        for (uint32_t st = 0; st < S; ++st) for (uint32_t i = 0; i < 4096u && !mbar_try_wait(&full[st], 0u) && !mbar_try_wait(&full[st], 1u); ++i) { }
+    SV_GTR(31);
     if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
 }
 
@@ -157,7 +334,7 @@ bool tq_gemv_fast_fits(const void* groups, uint64_t cols, uint64_t inputs) {
     if (g.count == 0 || g.count > 12 || inputs == 0 || inputs > 8 || cols == 0 || cols > 8192) return false;
     for (uint64_t i = 0; i < g.count; ++i) {
         if (g.d[i] != 4 && g.d[i] != 8) return false;
-        if ((cols * g.d[i] / 8) % 64 != 0 || cols * g.d[i] % 8 != 0) return false;
+        if ((cols * g.d[i] / 8) % 64 != 0 || cols * g.d[i] % 8 != 0 || cols * g.d[i] / 8 > 4096) return false;
         if (g.codes[i] % 16 != 0 || g.luts[i] % 2 != 0 || g.rows[i] > 0x0fffffffu) return false;
     }
     return true;
@@ -168,31 +345,73 @@ cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_
     struct G { uint64_t codes[12], luts[12], rows[12], d[12], out_at[12], count; } g;
     memcpy(&g, groups, sizeof g);
     if ((uintptr_t)x % 4 != 0 || (inputs > 1 && cols % 2 != 0)) return cudaErrorInvalidValue;
+    uint32_t most_pieces = 0, least_bytes = 0xffffffffu, most_bytes = 0;
+    for (uint64_t i = 0; i < g.count; ++i) {
+        const uint32_t row_bytes = (uint32_t)(cols * g.d[i] / 8);
+        if (row_bytes / 64 > most_pieces) most_pieces = row_bytes / 64;
+        if (row_bytes < least_bytes) least_bytes = row_bytes;
+        if (row_bytes > most_bytes) most_bytes = row_bytes;
+    }
+    const int niw = (int)((most_pieces + GV_WARPS - 1) / GV_WARPS);
+    if (niw < 1 || niw > 4) return cudaErrorInvalidValue;
+    /* A slot of the ring holds 16·ts rows of at most 2,048 bytes (a longer row is cut in two halves, a slot each): about
+     * 32 KB.  ts: tiles a step, so that a narrow matrix still moves about 32 KB a step; at most two, which keeps the partial
+     * sums at 32 KB.  The block takes all the shared memory there is; the table lands on a 64 KB boundary somewhere in its
+     * first 64 KB, and what is left either side of it holds the partial sums and two to four slots wherever it lands. */
+    uint32_t ts = 32768u / (16u * least_bytes);
+    ts = ts < 1 ? 1 : (ts > (uint32_t)GV_TS_MAX ? (uint32_t)GV_TS_MAX : ts);
+    const uint32_t smem_bytes = 227u * 1024u - 1024u;
+    uint32_t stage_bytes = 0;
+    for (;; --ts) {
+        stage_bytes = 0;
+        for (uint64_t i = 0; i < g.count; ++i) {
+            const uint32_t row_bytes = (uint32_t)(cols * g.d[i] / 8), seg = row_bytes > 2048u ? row_bytes / 2u : row_bytes;
+            if (row_bytes > 2048u && (row_bytes / 64u) % 32u != 0) return cudaErrorInvalidValue;          /* halves of whole sixteen-piece groups */
+            const uint32_t need = 16u * ts * (seg + GV_ROW_PAD);
+            if (need > stage_bytes) stage_bytes = need;
+        }
+        const uint32_t small = 2u * ts * GV_WARPS * 128u * 4u + 128u;
+        /* worst case: the table's boundary leaves 63 KB before it (the partial sums go there) and 227 - 128 KB after it */
+        if (2u * stage_bytes <= smem_bytes - 2u * 65536u && small <= 60u * 1024u) break;
+        if (ts == 1) return cudaErrorInvalidValue;
+    }
     GemvFast a;
     memset(&a, 0, sizeof a);
-    uint32_t tiles = 0, most_pieces = 0;
-    uint32_t n = 0;
+    uint32_t steps = 0, n = 0;
     for (uint64_t i = 0; i < g.count; ++i) {
         uint64_t rows = g.rows[i];
         if (rows_cap && rows_cap[i] < rows) rows = rows_cap[i];
         if (rows == 0) continue;                                             /* a group with no row to write */
+        /* with several inputs and no stride an input's answers sit `rows` apart: the NAMED rows, not the trimmed ones */
+        if (rows != g.rows[i] && inputs > 1 && out_stride == 0) return cudaErrorInvalidValue;
         a.codes[n] = (const uint8_t*)(uintptr_t)g.codes[i];
         a.scales[n] = (const uint16_t*)(uintptr_t)g.luts[i];
         a.rows[n] = (uint32_t)rows; a.d[n] = (uint32_t)g.d[i]; a.out_at[n] = g.out_at[i];
-        /* with several inputs and no stride an input's answers sit `rows` apart: the NAMED rows, not the trimmed ones */
-        if (rows != g.rows[i] && inputs > 1 && out_stride == 0) return cudaErrorInvalidValue;
-        a.tile0[n] = tiles;
-        tiles += (uint32_t)((rows + 15) / 16);
-        const uint32_t pieces = (uint32_t)(cols * g.d[i] / 8 / 64);
-        if (pieces > most_pieces) most_pieces = pieces;
+        a.halves[n] = cols * g.d[i] / 8 > 2048 ? 2u : 1u;
+        a.step0[n] = steps;
+        steps += (uint32_t)((rows + 16 * ts - 1) / (16 * ts));
         ++n;
     }
     if (n == 0) return cudaSuccess;
-    a.tile0[n] = tiles;
+    a.step0[n] = steps;
     a.count = n; a.cols = (uint32_t)cols; a.inputs = (uint32_t)inputs; a.out_stride = out_stride;
-    const int niw = (int)((most_pieces + GV_WARPS - 1) / GV_WARPS);
-    const size_t smem = GV_LUT_BYTES + 2 * GV_WARPS * 128 * sizeof(float);
-    const unsigned grid = tiles < 148u ? tiles : 148u;
+    a.x_wide = ((uintptr_t)x % 16 == 0 && cols % 8 == 0) ? 1u : 0u;
+    a.ts = ts; a.stage_bytes = stage_bytes; a.smem_bytes = smem_bytes;
+    a.status = device_status_word();
+    {   /* the table's image, once a device */
+        static bool made[64] = {};
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+        if (!made[dev]) {
+            gv_lut_image_kernel<<<16, 256, 0, st>>>();
+            const cudaError_t e = cudaGetLastError();
+            if (e != cudaSuccess) return e;
+            note_launch(1);
+            made[dev] = true;
+        }
+    }
+    const size_t smem = smem_bytes;
+    const unsigned grid = steps < 148u ? steps : 148u;
 #define SV_GV(N)                                                                                                                     \
     do {                                                                                                                             \
         static bool ready = false;                                                                                                   \
@@ -201,13 +420,12 @@ cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_
             if (e != cudaSuccess) return e;                                                                                          \
             ready = true;                                                                                                            \
         }                                                                                                                            \
-        tq_gemv_fast_kernel<N><<<grid, GV_THREADS, smem, st>>>(out, a, x, over);                                                     \
+        tq_gemv_fast_kernel<N><<<grid, GV_THREADS + 32, smem, st>>>(out, a, x, over);                                                     \
     } while (0)
-    if (niw <= 1) SV_GV(1);
+    if (niw == 1) SV_GV(1);
     else if (niw == 2) SV_GV(2);
     else if (niw == 3) SV_GV(3);
-    else if (niw == 4) SV_GV(4);
-    else return cudaErrorInvalidValue;
+    else SV_GV(4);
 #undef SV_GV
     note_launch(1);
     return cudaGetLastError();
