@@ -19,12 +19,18 @@
  *     by the async proxy do not;
  *   · the table is 256 bytes an entry — 32 copies of the 4-bit pair table, then 32 of the 8-bit table, one a bank — so a
  *     lookup never conflicts and its offset is ONE byte-permute of the code word;
- *   · a block is 16 warps that split a row's bytes 64 at a time; their partial sums for a step (one to four tiles of 16
- *     rows, about 32 KB of codes) meet in shared memory, double-buffered, one barrier a step, after which the step's stage
- *     is filled again.
- * Shapes it takes: widths 4 and 8, row bytes a multiple of 64 and at most 4,096, codes 16-byte aligned, at most 8 inputs.
- * Anything else stays with the as-worded kernel in tq.cu.  Every mbarrier wait is bounded; one that runs out ORs "B2TO"
- * into the device's status word and the block leaves. */
+ *   · a block is sixteen working warps that split a row's bytes 64 at a time, and a seventeenth that only fetches (a copy's
+ *     issue waits until the memory system takes it: a warp that both fetched and worked held the whole block up at the
+ *     next barrier).  The working warps' partial sums for a step (one or two tiles of 16 rows, about 32 KB of codes) meet
+ *     in shared memory, double-buffered, one barrier a step; every warp then adds one row's sixteen parts.
+ * Shapes it takes: widths 4 and 8, row bytes a multiple of 64 and at most 4,096 (a row longer than 2,048 bytes goes through
+ * the ring in two halves), codes 16-byte aligned, at most 8 inputs.  Anything else stays with the as-worded kernel in
+ * tq.cu.  Every mbarrier wait is bounded; one that runs out ORs "B2TO" into the device's status word and the block leaves.
+ *
+ * Where the time goes (16,384 x 4,096 at 4 bits, 33.6 MB, 20 us: 1.7 TB/s): a block works seven steps of about 2.0 us — the
+ * lookups and MMAs of a 32 KB step take 1.25 us on an SM (about half of the shared-memory pipe's 128 bytes a clock, the
+ * copies' writes into the ring included), the barrier, the sums and the wait for the next slot 0.8 us — after 2.3 us in
+ * which every SM's first three slots (14 MB over the card) arrive at the memory system's full rate. */
 #include "common.cuh"
 #include "kernels.h"
 #include <string.h>
@@ -102,6 +108,12 @@ __device__ __forceinline__ void gv_bulk(uint32_t dst, const void* src, uint32_t 
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy) : "memory");
 }
 
+/* m16n8k16, fp16 operands, fp32 sums; not volatile, so that the compiler may move it among the lookups around it */
+__device__ __forceinline__ void gv_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 /* One 64-byte piece of rows g and g + 8 through the table and the tensor cores: 8 MMAs at 4 bits (bytes 2m, 2m+1 are four
  * codes a row), 4 at 8 bits (bytes 4m .. 4m+3), alternating between two accumulators so that an MMA does not wait for the
  * one before it.  The sixteen lookups of half a piece are all asked for before the first MMA that needs one: a lookup is a
@@ -117,13 +129,13 @@ __device__ __forceinline__ void gv_piece(float (&c0)[4], float (&c1)[4], const u
             for (int b = 0; b < 8; ++b) { la[b] = gv_lut(at4, wsa[half * 2 + (b >> 2)], b & 3); lb[b] = gv_lut(at4, wsb[half * 2 + (b >> 2)], b & 3); }
 #pragma unroll
             for (int m = 0; m < 4; ++m)                                      /* bytes 2m, 2m + 1 of the half */
-                mma16816<SV_DTYPE_FP16>((m & 1) ? c1 : c0, la[2 * m], lb[2 * m], la[2 * m + 1], lb[2 * m + 1], xr[half * 8 + 2 * m], xr[half * 8 + 2 * m + 1]);
+                gv_mma((m & 1) ? c1 : c0, la[2 * m], lb[2 * m], la[2 * m + 1], lb[2 * m + 1], xr[half * 8 + 2 * m], xr[half * 8 + 2 * m + 1]);
         } else {
 #pragma unroll
             for (int b = 0; b < 8; ++b) { la[b] = gv_lut(at8, wsa[half * 2 + (b >> 2)], b & 3); lb[b] = gv_lut(at8, wsb[half * 2 + (b >> 2)], b & 3); }
 #pragma unroll
             for (int m = 0; m < 2; ++m)                                      /* bytes 4m .. 4m + 3 of the half */
-                mma16816<SV_DTYPE_FP16>((m & 1) ? c1 : c0, __byte_perm(la[4 * m], la[4 * m + 1], 0x5410), __byte_perm(lb[4 * m], lb[4 * m + 1], 0x5410),
+                gv_mma((m & 1) ? c1 : c0, __byte_perm(la[4 * m], la[4 * m + 1], 0x5410), __byte_perm(lb[4 * m], lb[4 * m + 1], 0x5410),
                                         __byte_perm(la[4 * m + 2], la[4 * m + 3], 0x5410), __byte_perm(lb[4 * m + 2], lb[4 * m + 3], 0x5410),
                                         xr[half * 4 + 2 * m], xr[half * 4 + 2 * m + 1]);
         }
