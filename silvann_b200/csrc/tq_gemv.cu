@@ -147,8 +147,9 @@ __device__ __forceinline__ void gv_piece(float (&c0)[4], float (&c1)[4], const u
  * a warp that both fetched and worked made the whole block wait for that at the next barrier.  The ring's slots are
  * handed back and forth on mbarriers (`full`: the copies' bytes; `empty`: one arrival a working warp).
  * A step is ts tiles of 16 rows; where 16 rows of a group are more than a slot holds, a row is cut in two halves and a
- * step takes two slots, one after the other (a.halves). */
-template <int NIW>
+ * step takes two slots, one after the other (a.halves).
+ * W: the one width of every group (4 or 8), so that the other width's code is not in the loop at all; 0: groups of both. */
+template <int NIW, int W>
 __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16_t* out, GemvFast a, const uint16_t* x, unsigned int* over) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint32_t stage_at_s[GV_STAGES_MAX];
@@ -231,12 +232,12 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
         if (n == 1) SV_GTR(25);
         while (s >= hi) {                                                    /* a group's numbers are read once, as its first step comes */
             ++gi; lo = a.step0[gi]; hi = a.step0[gi + 1];
-            d = a.d[gi]; rows = a.rows[gi]; row_bytes = a.cols * d / 8u; halves = a.halves[gi]; seg = row_bytes / halves; pieces = row_bytes / 64u;
+            d = W != 0 ? (uint32_t)W : a.d[gi]; rows = a.rows[gi]; row_bytes = a.cols * d / 8u; halves = a.halves[gi]; seg = row_bytes / halves; pieces = row_bytes / 64u;
             sc = a.scales[gi];
             out_row = a.out_at[gi]; out_input = a.out_stride != 0 ? a.out_stride : (uint64_t)rows;
         }
         const uint32_t row0 = (s - lo) * (16u * ts);
-        const uint32_t per_lane = d == 4 ? 32u : 16u;                        /* columns a lane's 16 bytes hold */
+        const uint32_t per_lane = (W != 0 ? (uint32_t)W : d) == 4 ? 32u : 16u;       /* columns a lane's 16 bytes hold */
         if (n == 1) SV_GTR(26);
         if (d != have_d) {                                                   /* the columns a lane owns depend on the width */
             have_d = d;
@@ -294,7 +295,7 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
                     if (piece >= pieces || (piece * 64u) / seg != h) continue;                       /* the whole warp together */
                     const uint32_t off = piece * 64u - h * seg;
                     const uint4 ua = gv_lds128(at_a + off), ub = gv_lds128(at_b + off);
-                    gv_piece(c[sub], c1, ua, ub, xr[i], d, at4, at8);
+                    gv_piece(c[sub], c1, ua, ub, xr[i], W != 0 ? (uint32_t)W : d, at4, at8);
                 }
 #pragma unroll
                 for (int e = 0; e < 4; ++e) c[sub][e] += c1[e];
@@ -424,20 +425,24 @@ cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_
     }
     const size_t smem = smem_bytes;
     const unsigned grid = steps < 148u ? steps : 148u;
-#define SV_GV(N)                                                                                                                     \
+#define SV_GV2(N, WW)                                                                                                               \
     do {                                                                                                                             \
         static bool ready = false;                                                                                                   \
         if (!ready) {                                                                                                                \
-            const cudaError_t e = cudaFuncSetAttribute(tq_gemv_fast_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            const cudaError_t e = cudaFuncSetAttribute(tq_gemv_fast_kernel<N, WW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return e;                                                                                          \
             ready = true;                                                                                                            \
         }                                                                                                                            \
-        tq_gemv_fast_kernel<N><<<grid, GV_THREADS + 32, smem, st>>>(out, a, x, over);                                                     \
+        tq_gemv_fast_kernel<N, WW><<<grid, GV_THREADS + 32, smem, st>>>(out, a, x, over);                                            \
     } while (0)
+#define SV_GV(N) do { if (one_width == 4) SV_GV2(N, 4); else if (one_width == 8) SV_GV2(N, 8); else SV_GV2(N, 0); } while (0)
+    uint32_t one_width = a.d[0];
+    for (uint32_t i = 1; i < n; ++i) if (a.d[i] != one_width) one_width = 0;
     if (niw == 1) SV_GV(1);
     else if (niw == 2) SV_GV(2);
     else if (niw == 3) SV_GV(3);
     else SV_GV(4);
+#undef SV_GV2
 #undef SV_GV
     note_launch(1);
     return cudaGetLastError();
