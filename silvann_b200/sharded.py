@@ -127,3 +127,39 @@ class LongContextRank:
 
     def close(self):
         self.tier.close()
+
+
+def sum_over_ranks(partial, dist, vector_sum, process_group=None, world=None, empty_like=None):
+    """The tensor-parallel sum that follows head-sharded attention, for ranks that are PROCESSES (one a card, NCCL between
+    them): every rank's 16-bit partial is gathered and the pieces are added in rank order by one launch of the family's
+    `vector_sum` door — `vector_sum(pieces) -> tensor`, fp32 sum over the pieces in the order given, rounded once — so every
+    rank holds the same bits, the bits the reference's in-process form makes when it reads the other cards' partials in
+    place (engine/src/packages/nn/gpu/kernels/kernels.cuh:117-126; nn/cpu/opcodes/partials__abi.cuh: the fan-in is in rank
+    order there too).  An all-reduce would round a partial sum at every hop in an order the library chooses; this costs
+    world-1 more copies of a vector of a few KB and keeps the answer the reference's.
+    """
+    world = world if world is not None else dist.get_world_size(process_group)
+    if world == 1:
+        return partial
+    import torch
+    as_bytes = partial.contiguous().view(torch.uint8)         # 16-bit patterns travel as bytes: neither NCCL nor gloo moves int16
+    empty_like = empty_like or (lambda t: t.new_empty(t.shape))
+    pieces = [empty_like(as_bytes) for _ in range(world)]
+    dist.all_gather(pieces, as_bytes, group=process_group)
+    return vector_sum([p.view(partial.dtype).view(partial.shape) for p in pieces])
+
+
+def family_vector_sum(torch, fam):
+    """`vector_sum` for sum_over_ranks through a bound family's door: the pieces are device tensors of 16-bit patterns."""
+    from .abi import VectorParts
+
+    def run(pieces):
+        n = pieces[0].numel()
+        out = torch.empty_like(pieces[0])
+        parts = VectorParts()
+        for i, p in enumerate(pieces):
+            parts.at[i] = p.data_ptr()
+        parts.count = len(pieces)
+        fam.nn.vector_sum(out.data_ptr(), parts, n, None)
+        return out
+    return run

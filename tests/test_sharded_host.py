@@ -73,3 +73,38 @@ def test_two_ranks_exchange_and_fold_over_gloo(tmp_path):
     o0, o1 = np.load(tmp_path / "o0.npy"), np.load(tmp_path / "o1.npy")
     assert np.array_equal(o0, o1)                                        # every rank of the group folds the same bits
     assert np.abs(oracle.from_bits(o0, 0) - np.load(tmp_path / "want.npy")).max() <= 2e-3
+
+
+def _sum_main(rank, world, port, tmp):
+    sys.path.insert(0, str(ROOT))
+    import torch
+    import torch.distributed as dist
+    import oracle
+    from silvann_b200 import sharded as sh
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    n = 5120
+    parts = [oracle.to_bits(np.random.default_rng(40 + r).standard_normal(n, dtype=np.float32), 0) for r in range(world)]
+
+    def vector_sum(pieces):                                  # the door's arithmetic: fp32 in the order given, rounded once
+        s = np.zeros(n, np.float32)
+        for p in pieces:
+            s += oracle.from_bits(p.numpy().view(np.uint16), 0)
+        return torch.from_numpy(oracle.to_bits(s, 0).view(np.int16))
+    total = sh.sum_over_ranks(torch.from_numpy(parts[rank].view(np.int16)), dist, vector_sum)
+    np.save(Path(tmp) / f"s{rank}.npy", total.numpy().view(np.uint16))
+    if rank == 0:
+        s = np.zeros(n, np.float32)
+        for p in parts:
+            s += oracle.from_bits(p, 0)
+        np.save(Path(tmp) / "want.npy", oracle.to_bits(s, 0))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_partial_sums_over_two_ranks_are_the_same_bits_everywhere(tmp_path):
+    import torch.multiprocessing as mp
+    port = 31500 + os.getpid() % 2000
+    mp.spawn(_sum_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    s0, s1, want = (np.load(tmp_path / f) for f in ("s0.npy", "s1.npy", "want.npy"))
+    assert np.array_equal(s0, s1) and np.array_equal(s0, want)

@@ -1,0 +1,49 @@
+"""The tensor-parallel partial sum with one PROCESS a card (NCCL between them): every rank gathers the others' 16-bit
+partials and adds them in rank order through the family's `vector_sum` door — the same bits on every rank, and the bits
+the fp32-sum-rounded-once definition gives.  Skipped where fewer than two B200s are visible."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _rank(rank, world, port, tmp):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    import oracle
+    import silvann_b200
+    from silvann_b200 import sharded
+    torch.cuda.set_device(rank)
+    fam = silvann_b200.family()
+    assert fam.sys.bind_device(rank) == 1
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    n = 5120
+    parts = [oracle.to_bits(np.random.default_rng(60 + r).standard_normal(n, dtype=np.float32), 0) for r in range(world)]
+    mine = torch.from_numpy(parts[rank].view(np.int16)).cuda()
+    total = sharded.sum_over_ranks(mine, dist, sharded.family_vector_sum(torch, fam))
+    assert fam.sys.compute_completed()
+    np.save(Path(tmp) / f"s{rank}.npy", total.cpu().numpy().view(np.uint16))
+    if rank == 0:
+        s = np.zeros(n, np.float32)
+        for p in parts:
+            s += oracle.from_bits(p, 0)
+        np.save(Path(tmp) / "want.npy", oracle.to_bits(s, 0))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_partial_sums_over_two_processes(cuda, tmp_path):
+    if cuda.cuda.device_count() < 2:
+        pytest.skip("one card visible")
+    import torch.multiprocessing as mp
+    port = 32500 + os.getpid() % 2000
+    mp.spawn(_rank, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    s0, s1, want = (np.load(tmp_path / f) for f in ("s0.npy", "s1.npy", "want.npy"))
+    assert np.array_equal(s0, s1) and np.array_equal(s0, want)
