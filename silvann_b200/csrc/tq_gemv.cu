@@ -45,7 +45,7 @@ static __device__ const uint16_t g_tq_levels_gemv[318] = {
 
 constexpr int GV_WARPS = 16, GV_THREADS = GV_WARPS * 32, GV_LUT_BYTES = 256 * 256;
 
-constexpr int GV_STAGES_MAX = 4, GV_ROW_PAD = 64, GV_TS_MAX = 2;       /* slots of the ring at most; a row's padding; tiles a step at most */
+constexpr int GV_STAGES_MAX = 4, GV_ROW_PAD = 64, GV_TS_MAX = 4;       /* slots of the ring at most; a row's padding; tiles a step at most */
 
 /* The table as a block holds it (256 entries of 256 bytes: 32 copies of the 4-bit pair, then 32 of the 8-bit level twice),
  * made once a device and copied into every block by one bulk copy instead of being built again by each. */
@@ -81,10 +81,10 @@ extern "C" __attribute__((visibility("default"))) int sv_gemv_trace_run(uint16_t
 struct GemvFast {
     const uint8_t* codes[12];
     const uint16_t* scales[12];
-    uint32_t rows[12], d[12], halves[12], step0[13];   /* group i's steps (ts tiles of 16 rows each) are [step0[i], step0[i+1]); halves: slots a step */
+    uint32_t rows[12], d[12], halves[12], tile0[13];   /* group i's tiles of 16 rows are [tile0[i], tile0[i+1]); halves: slots a tile */
     uint64_t out_at[12];
     uint32_t count, cols, inputs, x_wide;      /* x_wide: x may be read 16 bytes at a time */
-    uint32_t ts, stage_bytes, smem_bytes;      /* tiles a step; bytes a stage; the block's dynamic shared memory */
+    uint32_t ts, pi, stage_bytes, smem_bytes;  /* tiles a step at most; inputs rounded up to a power of two; bytes a slot; the block's shared memory */
     uint64_t out_stride;
     unsigned int* status;
 };
@@ -143,12 +143,15 @@ __device__ __forceinline__ void gv_piece(float (&c0)[4], float (&c1)[4], const u
 }
 
 /* NIW: the 64-byte pieces of a row one warp owns at most (pieces warp, warp + 16, ...); x registers a thread: 16·NIW.
+ * W: the one width of every group (4 or 8), so that the other width's code is not in the loop at all; 0: groups of both.
+ *
  * Sixteen warps work the codes and a seventeenth only fetches: a copy's issue waits for the memory system to take it, and
  * a warp that both fetched and worked made the whole block wait for that at the next barrier.  The ring's slots are
  * handed back and forth on mbarriers (`full`: the copies' bytes; `empty`: one arrival a working warp).
- * A step is ts tiles of 16 rows; where 16 rows of a group are more than a slot holds, a row is cut in two halves and a
- * step takes two slots, one after the other (a.halves).
- * W: the one width of every group (4 or 8), so that the other width's code is not in the loop at all; 0: groups of both. */
+ * A block takes a run of neighbouring tiles of 16 rows (every block as many, to within one) and walks it in steps of up to
+ * `ts` tiles: a tile is one slot of the ring — two, a half row each, where 16 whole rows are more than a slot holds — and
+ * the working warps meet ONCE a step, when their partial sums of the step's tiles are written (the sums are kept for as
+ * many inputs as there are, rounded up to a power of two, so that a decode step's take little room and are kept twice). */
 template <int NIW, int W>
 __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16_t* out, GemvFast a, const uint16_t* x, unsigned int* over) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -156,9 +159,10 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
     __shared__ uint32_t stages_s;
     /* The table sits on the first 64 KB boundary of the shared window inside this block's memory; the partial sums, the
      * barriers and the ring's slots are carved from what lies before it and after it. */
-    const uint32_t ts = a.ts;
+    const uint32_t ts = a.ts, pi = a.pi;
     const uint32_t base = smem_u32(smem), lut = (base + 0xFFFFu) & ~0xFFFFu, end = base + a.smem_bytes;
-    const uint32_t part_bytes = 2u * ts * GV_WARPS * 128u * (uint32_t)sizeof(float), small = part_bytes + 128u;
+    const uint32_t tile_floats = GV_WARPS * 16u * pi;                        /* a tile's partial sums: [warp][row][input] */
+    const uint32_t part_bytes = 2u * ts * tile_floats * (uint32_t)sizeof(float), small = part_bytes + 128u;
     uint32_t before = base, after = lut + (uint32_t)GV_LUT_BYTES;            /* the next free byte either side */
     uint32_t part_at;
     if (lut - before >= small) { part_at = before; before += small; } else { part_at = after; after += small; }
@@ -182,13 +186,9 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
     __syncthreads();
     const uint32_t S = stages_s;
     if (S < 2) return;                                                       /* the launcher sized the block's memory so that two fit */
-    const uint32_t steps = a.step0[a.count];
-
-    auto place = [&](uint32_t s, int& gi, uint32_t& row0) {                  /* where step `s` lies: its group, its first row */
-        gi = 0;
-        while (s >= a.step0[gi + 1]) ++gi;
-        row0 = (s - a.step0[gi]) * (16u * ts);
-    };
+    /* this block's run of tiles: every block as many, to within one */
+    const uint32_t tiles = a.tile0[a.count];
+    const uint32_t run_lo = (uint32_t)(((uint64_t)blockIdx.x * tiles) / gridDim.x), run_hi = (uint32_t)(((uint64_t)(blockIdx.x + 1) * tiles) / gridDim.x);
 
     if (warp == GV_WARPS) {
         /* ---- the fetching warp: the table, then slot after slot as the working warps hand them back ---- */
@@ -196,17 +196,17 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
         if (lane == 0) { mbar_expect_tx(table_bar, GV_LUT_BYTES); gv_bulk(lut, g_gv_lut_image, GV_LUT_BYTES, table_bar, l2_policy_evict_last()); }
         uint32_t m = 0;                                                      /* slots filled so far */
         int gi = -1;
-        uint32_t lo = 0, hi = 0, row_bytes = 0, rows = 0, halves = 1, seg = 0;
+        uint32_t hi = 0, lo = 0, row_bytes = 0, rows = 0, halves = 1, seg = 0;
         const uint8_t* codes = nullptr;
-        for (uint32_t s = blockIdx.x; s < steps; s += gridDim.x) {
-            while (s >= hi) {                                                /* a group's numbers are read once, as its first step comes */
-                ++gi; lo = a.step0[gi]; hi = a.step0[gi + 1];
+        for (uint32_t tile = run_lo; tile < run_hi; ++tile) {
+            while (tile >= hi) {                                             /* a group's numbers are read once, as its first tile comes */
+                ++gi; lo = a.tile0[gi]; hi = a.tile0[gi + 1];
                 row_bytes = a.cols * a.d[gi] / 8u; rows = a.rows[gi]; halves = a.halves[gi]; seg = row_bytes / halves; codes = a.codes[gi];
             }
-            const uint32_t row0 = (s - lo) * (16u * ts), there = min(16u * ts, rows - row0);
+            const uint32_t row0 = (tile - lo) * 16u, there = min(16u, rows - row0);
             for (uint32_t h = 0; h < halves; ++h, ++m) {
                 const uint32_t slot = m % S;
-                if (m >= S && !mbar_wait(&empty[slot], ((m / S) - 1u) & 1u, abort_flag, a.status)) { s = steps; break; }
+                if (m >= S && !mbar_wait(&empty[slot], ((m / S) - 1u) & 1u, abort_flag, a.status)) { tile = run_hi; break; }
                 if (lane == 0) mbar_expect_tx(&full[slot], there * seg);
                 __syncwarp();
                 const uint32_t dst = stage_at_s[slot];
@@ -221,24 +221,23 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
     const uint32_t at4 = lut | ((uint32_t)lane * 4u), at8 = at4 + 128u;     /* the 4-bit pair table, then the 8-bit one, in every entry */
     uint32_t xr[NIW][16];                                                    /* this lane's B fragments: input g, the columns of its bytes */
     uint32_t have_d = 0, n = 0, m = 0;
-    bool table_ready = false, gave_up = false;
+    bool table_ready = false, failed = false;
     int buf = 0;
     bool hit = false;
     int gi = -1;
     uint32_t lo = 0, hi = 0, d = 0, rows = 0, row_bytes = 0, halves = 1, seg = 0, pieces = 0;
     const uint16_t* sc = nullptr;
     uint64_t out_row = 0, out_input = 0;                                     /* an answer's place: out_row + row + input · out_input */
-    for (uint32_t s = blockIdx.x; s < steps && !gave_up; s += gridDim.x, ++n, buf ^= 1) {
-        if (n == 1) SV_GTR(25);
-        while (s >= hi) {                                                    /* a group's numbers are read once, as its first step comes */
-            ++gi; lo = a.step0[gi]; hi = a.step0[gi + 1];
+    for (uint32_t tile = run_lo; tile < run_hi; ++n, buf ^= 1) {
+        while (tile >= hi) {                                                 /* a group's numbers are read once, as its first tile comes */
+            ++gi; lo = a.tile0[gi]; hi = a.tile0[gi + 1];
             d = W != 0 ? (uint32_t)W : a.d[gi]; rows = a.rows[gi]; row_bytes = a.cols * d / 8u; halves = a.halves[gi]; seg = row_bytes / halves; pieces = row_bytes / 64u;
             sc = a.scales[gi];
             out_row = a.out_at[gi]; out_input = a.out_stride != 0 ? a.out_stride : (uint64_t)rows;
         }
-        const uint32_t row0 = (s - lo) * (16u * ts);
+        const uint32_t nt = min(ts, min(hi, run_hi) - tile);                 /* the tiles of this step: of one group, of this block's run */
+        const uint32_t row0 = (tile - lo) * 16u;
         const uint32_t per_lane = (W != 0 ? (uint32_t)W : d) == 4 ? 32u : 16u;       /* columns a lane's 16 bytes hold */
-        if (n == 1) SV_GTR(26);
         if (d != have_d) {                                                   /* the columns a lane owns depend on the width */
             have_d = d;
 #pragma unroll
@@ -258,83 +257,62 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
                 }
             }
         }
-        if (n == 1) SV_GTR(27);
-        uint16_t scale[GV_TS_MAX];                                                   /* this warp's outputs' rows' scales, on their way while the step is worked */
-        {
-#pragma unroll
-            for (uint32_t sub = 0; sub < GV_TS_MAX; ++sub) {
-                const uint32_t r = row0 + sub * 16u + (uint32_t)warp;
-                scale[sub] = 0;
-                if (sub < ts && r < rows) asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(scale[sub]) : "l"(sc + r));
-            }
-        }
+        /* the answer this thread will write after the step's barrier: tile o / (16·pi), row (o / pi) % 16, input o % pi; its
+         * row's scale is on its way while the step is worked */
+        const uint32_t o = (uint32_t)tid, o_tile = o / (16u * pi), o_row = row0 + o_tile * 16u + (o / pi) % 16u, o_in = o % pi;
+        const bool o_live = o_tile < nt && o_row < rows && o_in < a.inputs;
+        uint16_t scale = 0;
+        if (o_live) asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(scale) : "l"(sc + o_row));
         SV_GTS(n, 0);
-        float c[GV_TS_MAX][4];                                               /* a tile's sums */
-#pragma unroll
-        for (int sub = 0; sub < GV_TS_MAX; ++sub) { c[sub][0] = 0.f; c[sub][1] = 0.f; c[sub][2] = 0.f; c[sub][3] = 0.f; }
-        for (uint32_t h = 0; h < halves; ++h, ++m) {
-            const uint32_t slot = m % S;
-            bool landed = mbar_wait(&full[slot], (m / S) & 1u, abort_flag, a.status);
-            if (!table_ready) { landed = mbar_wait(table_bar, 0u, abort_flag, a.status) && landed; table_ready = true; SV_GTR(1); }
-            {   /* every working warp goes on, or none: a vote on the working warps' own barrier */
-                uint32_t any;
-                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.or.pred p, 1, 512, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                             : "=r"(any) : "r"(landed ? 0u : 1u) : "memory");
-                if (any) { gave_up = true; break; }
-            }
-            if (h == 0) SV_GTS(n, 1);
-            const uint32_t slot_at = stage_at_s[slot] + (uint32_t)t * 16u, stride = seg + GV_ROW_PAD;
-#pragma unroll
-            for (uint32_t sub = 0; sub < GV_TS_MAX; ++sub) {
-                if (sub >= ts) break;
-                float c1[4] = {0.f, 0.f, 0.f, 0.f};
-                const uint32_t at_a = slot_at + (sub * 16u + (uint32_t)g) * stride, at_b = at_a + 8u * stride;
+        float* mine = part + (size_t)buf * ts * tile_floats + (size_t)warp * 16u * pi;
+        for (uint32_t tq = 0; tq < nt; ++tq) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+            for (uint32_t h = 0; h < halves; ++h, ++m) {
+                const uint32_t slot = m % S;
+                bool landed = failed ? false : mbar_wait(&full[slot], (m / S) & 1u, abort_flag, a.status);
+                if (!table_ready && landed) { landed = mbar_wait(table_bar, 0u, abort_flag, a.status); table_ready = true; SV_GTR(1); }
+                if (!landed) { failed = true; continue; }                    /* said at the step's barrier: every warp leaves there, or none */
+                if (tq == 0 && h == 0) SV_GTS(n, 1);
+                const uint32_t stride = seg + GV_ROW_PAD, at_a = stage_at_s[slot] + (uint32_t)t * 16u + (uint32_t)g * stride, at_b = at_a + 8u * stride;
 #pragma unroll
                 for (int i = 0; i < NIW; ++i) {
                     const uint32_t piece = (uint32_t)warp + (uint32_t)i * GV_WARPS;
                     if (piece >= pieces || (piece * 64u) / seg != h) continue;                       /* the whole warp together */
                     const uint32_t off = piece * 64u - h * seg;
                     const uint4 ua = gv_lds128(at_a + off), ub = gv_lds128(at_b + off);
-                    gv_piece(c[sub], c1, ua, ub, xr[i], W != 0 ? (uint32_t)W : d, at4, at8);
+                    gv_piece(c, c1, ua, ub, xr[i], W != 0 ? (uint32_t)W : d, at4, at8);
                 }
-#pragma unroll
-                for (int e = 0; e < 4; ++e) c[sub][e] += c1[e];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[slot]);                    /* this warp has read the slot */
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[slot]);                        /* this warp has read the slot */
-        }
-        if (gave_up) break;
-        /* c0, c1: (row g, inputs 2t, 2t+1) · c2, c3: (row g + 8, the same inputs).  Warp w's 128 sums are stored turned by
-         * 8·w places, so that the four lanes that later add one output's sixteen parts read four different bank groups. */
-#pragma unroll
-        for (uint32_t sub = 0; sub < GV_TS_MAX; ++sub) {
-            if (sub >= ts) break;
-            float* mine = part + (((size_t)buf * ts + sub) * GV_WARPS + warp) * 128;
-            *reinterpret_cast<float2*>(mine + ((g * 8 + t * 2 + warp * 8) & 127)) = make_float2(c[sub][0], c[sub][1]);
-            *reinterpret_cast<float2*>(mine + (((g + 8) * 8 + t * 2 + warp * 8) & 127)) = make_float2(c[sub][2], c[sub][3]);
+            /* c0, c1: (row g, inputs 2t, 2t+1) · c2, c3: (row g + 8, the same inputs): kept for the inputs there are */
+            float* to = mine + (size_t)tq * tile_floats;
+            if (2u * (uint32_t)t < pi) {
+                to[(uint32_t)g * pi + 2u * t] = c[0] + c1[0];
+                to[((uint32_t)g + 8u) * pi + 2u * t] = c[2] + c1[2];
+                if (pi > 1u) { to[(uint32_t)g * pi + 2u * t + 1u] = c[1] + c1[1]; to[((uint32_t)g + 8u) * pi + 2u * t + 1u] = c[3] + c1[3]; }
+            }
         }
         SV_GTS(n, 2);
-        asm volatile("barrier.cta.sync 1, 512;" ::: "memory");              /* the working warps' partial sums are whole */
+        {   /* the working warps' partial sums are whole; and a vote: a warp whose wait gave up takes every warp out */
+            uint32_t any;
+            asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.or.pred p, 1, 512, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(any) : "r"(failed ? 1u : 0u) : "memory");
+            if (any) { failed = true; break; }
+        }
         SV_GTS(n, 3);
-        /* warp w adds outputs 8w .. 8w+7 of each tile: lane l is output 8w + l/4, and adds the parts of warps l%4, +4, +8, +12 */
-#pragma unroll
-        for (uint32_t sub = 0; sub < GV_TS_MAX; ++sub) {
-            if (sub >= ts) break;
-            const uint32_t o = (uint32_t)warp * 8u + ((uint32_t)lane >> 2), q = (uint32_t)lane & 3u;
-            const float* from = part + ((size_t)buf * ts + sub) * GV_WARPS * 128;
+        if (o_live) {                                                        /* sixteen warps' parts of one answer, in warp order */
+            const float* from = part + (size_t)buf * ts * tile_floats + (size_t)o_tile * tile_floats + ((o / pi) % 16u) * pi + o_in;
             float sum = 0.f;
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j) { const uint32_t w = q + 4u * j; sum += from[w * 128u + ((o + 8u * w) & 127u)]; }
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            const uint32_t r = row0 + sub * 16u + (o >> 3), k = o & 7u;
-            if (q == 0 && r < rows && k < a.inputs) out[out_row + r + k * out_input] = H::from_float(sum * H::to_float(scale[sub]), hit);
+            for (uint32_t w = 0; w < (uint32_t)GV_WARPS; ++w) sum += from[w * 16u * pi];
+            out[out_row + o_row + o_in * out_input] = H::from_float(sum * H::to_float(scale), hit);
         }
-        if (n == 0) SV_GTR(24);
+        tile += nt;
     }
     /* After a wait gave up, copies may still be on their way into this block's memory: the first working thread waits
      * (bounded) for every slot's barrier to settle before the memory is given back. */
-    if (gave_up && tid == 0)
+    if (failed && tid == 0)
         for (uint32_t st = 0; st < S; ++st) for (uint32_t i = 0; i < 4096u && !mbar_try_wait(&full[st], 0u) && !mbar_try_wait(&full[st], 1u); ++i) { }
     SV_GTR(31);
     if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
@@ -367,30 +345,27 @@ cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_
     }
     const int niw = (int)((most_pieces + GV_WARPS - 1) / GV_WARPS);
     if (niw < 1 || niw > 4) return cudaErrorInvalidValue;
-    /* A slot of the ring holds 16·ts rows of at most 2,048 bytes (a longer row is cut in two halves, a slot each): about
-     * 32 KB.  ts: tiles a step, so that a narrow matrix still moves about 32 KB a step; at most two, which keeps the partial
-     * sums at 32 KB.  The block takes all the shared memory there is; the table lands on a 64 KB boundary somewhere in its
-     * first 64 KB, and what is left either side of it holds the partial sums and two to four slots wherever it lands. */
-    uint32_t ts = 32768u / (16u * least_bytes);
+    /* A slot of the ring holds 16 rows of at most 2,048 bytes (a longer row is cut in two halves, a slot each): up to 33 KB.
+     * A step is up to four tiles, fewer when there are many inputs (the partial sums of a step — 16 warps x 16 rows x the
+     * inputs rounded up to a power of two — are kept twice in at most 16 KB).  The block takes all the shared memory there
+     * is; the table lands on a 64 KB boundary somewhere in its first 64 KB, and what is left either side of it holds the
+     * partial sums and two to four slots wherever it lands. */
+    uint32_t pi = 1;
+    while (pi < inputs) pi *= 2;
+    uint32_t ts = 8u / pi;
     ts = ts < 1 ? 1 : (ts > (uint32_t)GV_TS_MAX ? (uint32_t)GV_TS_MAX : ts);
     const uint32_t smem_bytes = 227u * 1024u - 1024u;
     uint32_t stage_bytes = 0;
-    for (;; --ts) {
-        stage_bytes = 0;
-        for (uint64_t i = 0; i < g.count; ++i) {
-            const uint32_t row_bytes = (uint32_t)(cols * g.d[i] / 8), seg = row_bytes > 2048u ? row_bytes / 2u : row_bytes;
-            if (row_bytes > 2048u && (row_bytes / 64u) % 32u != 0) return cudaErrorInvalidValue;          /* halves of whole sixteen-piece groups */
-            const uint32_t need = 16u * ts * (seg + GV_ROW_PAD);
-            if (need > stage_bytes) stage_bytes = need;
-        }
-        const uint32_t small = 2u * ts * GV_WARPS * 128u * 4u + 128u;
-        /* worst case: the table's boundary leaves 63 KB before it (the partial sums go there) and 227 - 128 KB after it */
-        if (2u * stage_bytes <= smem_bytes - 2u * 65536u && small <= 60u * 1024u) break;
-        if (ts == 1) return cudaErrorInvalidValue;
+    for (uint64_t i = 0; i < g.count; ++i) {
+        const uint32_t row_bytes = (uint32_t)(cols * g.d[i] / 8), seg = row_bytes > 2048u ? row_bytes / 2u : row_bytes;
+        if (row_bytes > 2048u && (row_bytes / 64u) % 32u != 0) return cudaErrorInvalidValue;              /* halves of whole sixteen-piece groups */
+        const uint32_t need = 16u * (seg + GV_ROW_PAD);
+        if (need > stage_bytes) stage_bytes = need;
     }
+    (void)least_bytes;
     GemvFast a;
     memset(&a, 0, sizeof a);
-    uint32_t steps = 0, n = 0;
+    uint32_t tiles = 0, n = 0;
     for (uint64_t i = 0; i < g.count; ++i) {
         uint64_t rows = g.rows[i];
         if (rows_cap && rows_cap[i] < rows) rows = rows_cap[i];
@@ -401,15 +376,16 @@ cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_
         a.scales[n] = (const uint16_t*)(uintptr_t)g.luts[i];
         a.rows[n] = (uint32_t)rows; a.d[n] = (uint32_t)g.d[i]; a.out_at[n] = g.out_at[i];
         a.halves[n] = cols * g.d[i] / 8 > 2048 ? 2u : 1u;
-        a.step0[n] = steps;
-        steps += (uint32_t)((rows + 16 * ts - 1) / (16 * ts));
+        a.tile0[n] = tiles;
+        tiles += (uint32_t)((rows + 15) / 16);
         ++n;
     }
     if (n == 0) return cudaSuccess;
-    a.step0[n] = steps;
+    a.tile0[n] = tiles;
+    const uint32_t steps = tiles;                                            /* the grid's size: a block has a tile at least */
     a.count = n; a.cols = (uint32_t)cols; a.inputs = (uint32_t)inputs; a.out_stride = out_stride;
     a.x_wide = ((uintptr_t)x % 16 == 0 && cols % 8 == 0) ? 1u : 0u;
-    a.ts = ts; a.stage_bytes = stage_bytes; a.smem_bytes = smem_bytes;
+    a.ts = ts; a.pi = pi; a.stage_bytes = stage_bytes; a.smem_bytes = smem_bytes;
     a.status = device_status_word();
     {   /* the table's image, once a device */
         static bool made[64] = {};

@@ -8,6 +8,8 @@ Without a GPU the family is the reference's own x86_avx2, and the answers must e
 directly — that pins the driver.  With a GPU the family is this repository's library, and the answers must be within 2e-3
 of the reference family's; the library's own counters must show that the verb's two doors ran as ONE fused launch.
 """
+import time
+
 import numpy as np
 import pytest
 
@@ -204,16 +206,20 @@ def _tiered_mixer(s, reference):
     pairs = rot // 2
     freq = np.float64(m["THETA"]) ** (-2.0 * np.arange(pairs) / rot)
     h1 = np.zeros((m["STEPS"], H), np.uint16)
+    seconds = []                                             # a position through the engine, its answer read back
     for pos in range(m["STEPS"]):
         a = pos * freq
         angles.write(np.concatenate([np.cos(a), np.sin(a)]).astype(np.float32).tobytes())
         xb.write(xs[pos].tobytes())
+        t0 = time.perf_counter()
         kind, _ = s.run_cells("ai_qwen_3__attention_tiered", [s.buf(xb.ref), s.buf(table), s.integer(pos), s.buf(hb.ref)])
         assert kind == s.OBJ, f"position {pos}: the verb answers h1"
         h1[pos] = _u16(hb.read(), (H,))
+        seconds.append(time.perf_counter() - t0)
     state = {"x": xs, "sink_k": _u16(planes[11].read(), (m["SINK"], kvw)), "hot_k": _u16(tiers[0].read(), (m["HOT"], kvw)),
              "warm_ks": _u16(tiers[3].read(), (m["WARM"] * kvh,)), "cold_ks": _u16(tiers[7].read(), (cold_rows * kvh,)),
-             "warm_kc": np.frombuffer(tiers[2].read(), np.uint8).copy(), "cold_kc": np.frombuffer(tiers[6].read(), np.uint8).copy()}
+             "warm_kc": np.frombuffer(tiers[2].read(), np.uint8).copy(), "cold_kc": np.frombuffer(tiers[6].read(), np.uint8).copy(),
+             "seconds": seconds}
     s.release(table)
     s.release_buffers()
     return h1, state
@@ -257,12 +263,15 @@ def _deltanet_mixer(s, reference):
     table = s.table(planes + numbers)
     xb, hb = room(2 * H), room(2 * H)
     h1 = np.zeros((m["STEPS"], H), np.uint16)
+    seconds = []
     for pos in range(m["STEPS"]):
         xb.write(xs[pos].tobytes())
+        t0 = time.perf_counter()
         kind, _ = s.run_cells("ai_qwen_3__deltanet", [s.buf(xb.ref), s.buf(table), s.buf(hb.ref)])
         assert kind == s.OBJ, f"position {pos}: the verb answers h1"
         h1[pos] = _u16(hb.read(), (H,))
-    end = {"x": xs, "state": _f32(state.read(4 * vh * hd * hd), (vh, hd, hd)), "window": _u16(window.read(2 * ch * 3), (ch, 3))}
+        seconds.append(time.perf_counter() - t0)
+    end = {"x": xs, "seconds": seconds, "state": _f32(state.read(4 * vh * hd * hd), (vh, hd, hd)), "window": _u16(window.read(2 * ch * 3), (ch, 3))}
     s.release(table)
     s.release_buffers()
     return h1, end
@@ -342,6 +351,9 @@ def test_engine_runs_the_tiered_mixer_on_this_family(gpu_session, mixer_on_refer
     before = ext.counters()
     got, state = _tiered_mixer(gpu_session, reference)
     after = ext.counters()
+    print(f"tiered mixer through the engine: median {1e6 * np.median(state['seconds'][8:]):.0f} us a position on this family "
+          f"({(after['launches'] - before['launches']) / MIX['STEPS']:.1f} launches a position), "
+          f"{1e6 * np.median(want_state['seconds'][8:]):.0f} us on the reference's CPU family")
     assert after["refused"] == before["refused"] and ext.device_status() == 0
     m = MIX
     cold_steps = m["STEPS"] - m["SINK"] - m["HOT"] - m["WARM"]
@@ -369,6 +381,9 @@ def test_engine_runs_the_deltanet_mixer_on_this_family(gpu_session, mixer_on_ref
     before = ext.counters()
     got, end = _deltanet_mixer(gpu_session, reference)
     after = ext.counters()
+    print(f"deltanet mixer through the engine: median {1e6 * np.median(end['seconds'][2:]):.0f} us a position on this family "
+          f"({(after['launches'] - before['launches']) / DN_MIX['STEPS']:.1f} launches a position), "
+          f"{1e6 * np.median(want_end['seconds'][2:]):.0f} us on the reference's CPU family")
     assert after["refused"] == before["refused"] and ext.device_status() == 0
     assert after["deltanet"] - before["deltanet"] == DN_MIX["STEPS"]
     err = np.abs(oracle.from_bits(got, FP16) - oracle.from_bits(want, FP16))
