@@ -21,16 +21,16 @@
  *     lookup never conflicts and its offset is ONE byte-permute of the code word;
  *   · a block is sixteen working warps that split a row's bytes 64 at a time, and a seventeenth that only fetches (a copy's
  *     issue waits until the memory system takes it: a warp that both fetched and worked held the whole block up at the
- *     next barrier).  The working warps' partial sums for a step (one or two tiles of 16 rows, about 32 KB of codes) meet
- *     in shared memory, double-buffered, one barrier a step; every warp then adds one row's sixteen parts.
+ *     next barrier).  A block walks a run of neighbouring tiles of 16 rows in steps of up to four; the working warps'
+ *     partial sums of a step meet in shared memory, double-buffered, one barrier a step.
  * Shapes it takes: widths 4 and 8, row bytes a multiple of 64 and at most 4,096 (a row longer than 2,048 bytes goes through
  * the ring in two halves), codes 16-byte aligned, at most 8 inputs.  Anything else stays with the as-worded kernel in
  * tq.cu.  Every mbarrier wait is bounded; one that runs out ORs "B2TO" into the device's status word and the block leaves.
  *
- * Where the time goes (16,384 x 4,096 at 4 bits, 33.6 MB, 20 us: 1.7 TB/s): a block works seven steps of about 2.0 us — the
- * lookups and MMAs of a 32 KB step take 1.25 us on an SM (about half of the shared-memory pipe's 128 bytes a clock, the
- * copies' writes into the ring included), the barrier, the sums and the wait for the next slot 0.8 us — after 2.3 us in
- * which every SM's first three slots (14 MB over the card) arrive at the memory system's full rate. */
+ * Where the time goes (16,384 x 4,096 at 4 bits, 33.6 MB, 16.8 us a call: 2.0 TB/s): a block has a run of seven tiles; a
+ * working warp spends 1,790 cycles on a tile's two pieces against the 1,280 the shared-memory pipe needs for the tile's 1,024
+ * lookups and 256 fetch wavefronts, after 2.7 us of prologue and first landing (every SM's first three slots, 14 MB over the
+ * card, are asked for at once). */
 #include "common.cuh"
 #include "kernels.h"
 #include <string.h>
@@ -222,6 +222,9 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
     uint32_t xr[NIW][16];                                                    /* this lane's B fragments: input g, the columns of its bytes */
     uint32_t have_d = 0, n = 0, m = 0;
     bool table_ready = false, failed = false;
+#ifdef SV_GEMV_TRACE
+    long long waited = 0, worked = 0;
+#endif
     int buf = 0;
     bool hit = false;
     int gi = -1;
@@ -269,10 +272,19 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
             float c[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
             for (uint32_t h = 0; h < halves; ++h, ++m) {
                 const uint32_t slot = m % S;
+#ifdef SV_GEMV_TRACE
+                const long long w0 = clock64();
+#endif
                 bool landed = failed ? false : mbar_wait(&full[slot], (m / S) & 1u, abort_flag, a.status);
+#ifdef SV_GEMV_TRACE
+                waited += clock64() - w0;
+#endif
                 if (!table_ready && landed) { landed = mbar_wait(table_bar, 0u, abort_flag, a.status); table_ready = true; SV_GTR(1); }
                 if (!landed) { failed = true; continue; }                    /* said at the step's barrier: every warp leaves there, or none */
                 if (tq == 0 && h == 0) SV_GTS(n, 1);
+#ifdef SV_GEMV_TRACE
+                const long long k0 = clock64();
+#endif
                 const uint32_t stride = seg + GV_ROW_PAD, at_a = stage_at_s[slot] + (uint32_t)t * 16u + (uint32_t)g * stride, at_b = at_a + 8u * stride;
 #pragma unroll
                 for (int i = 0; i < NIW; ++i) {
@@ -283,6 +295,9 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
                     gv_piece(c, c1, ua, ub, xr[i], W != 0 ? (uint32_t)W : d, at4, at8);
                 }
                 __syncwarp();
+#ifdef SV_GEMV_TRACE
+                worked += clock64() - k0;
+#endif
                 if (lane == 0) mbar_arrive(&empty[slot]);                    /* this warp has read the slot */
             }
             /* c0, c1: (row g, inputs 2t, 2t+1) · c2, c3: (row g + 8, the same inputs): kept for the inputs there are */
@@ -315,6 +330,9 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
     if (failed && tid == 0)
         for (uint32_t st = 0; st < S; ++st) for (uint32_t i = 0; i < 4096u && !mbar_try_wait(&full[st], 0u) && !mbar_try_wait(&full[st], 1u); ++i) { }
     SV_GTR(31);
+#ifdef SV_GEMV_TRACE
+    if (tid == 0 && blockIdx.x < 256) { g_gv_trace[blockIdx.x * 32 + 28] = (unsigned long long)waited; g_gv_trace[blockIdx.x * 32 + 29] = (unsigned long long)worked; g_gv_trace[blockIdx.x * 32 + 30] = m; }
+#endif
     if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
 }
 
