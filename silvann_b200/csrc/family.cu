@@ -81,7 +81,7 @@ static void run_pending_locked(Pending& pd) {
                                                                   x.res + r * x.qh * (x.d + 2), 0));
             break;
         }
-        case WEIGHTS_TQ:  check("attention_weights_tq", sv::tq_weights_launch(x.p, x.res, x.q, (const uint8_t*)x.k, x.scales, x.qh, x.kvh, x.d, x.length, x.width, 1, 0)); break;
+        case WEIGHTS_TQ:  check("attention_weights_tq", sv::tq_weights_launch(x.p, x.res, x.q, (const uint8_t*)x.k, x.scales, x.qh, x.kvh, x.d, x.length, x.width, x.rows, 0)); break;
         default: return;
     }
     bump(SILVANN_B200_COUNTER_FLUSHED);
@@ -521,54 +521,53 @@ static void d_turboquant_encode_rows(sv_u8* codes, sv_h16* scales, const sv_h16*
 static bool tq_shape_ok(sv_u64 qh, sv_u64 kvh, sv_u64 dh, sv_u64 d) {
     return kvh != 0 && qh % kvh == 0 && dh != 0 && dh <= 8192 && sv::tq_width_ok(d) && d != 16;
 }
-static void d_attention_weights_tq(float* p, float* res, const sv_h16* q, const sv_u8* codes, const sv_h16* scales, sv_u64 qh, sv_u64 kvh,
-                                   sv_u64 dh, sv_u64 length, sv_u64 d) {
+static void d_attention_weights_tq_rows(float* p, float* res, const sv_h16* q, const sv_u8* codes, const sv_h16* scales, sv_u64 qh, sv_u64 kvh,
+                                        sv_u64 dh, sv_u64 length, sv_u64 d, sv_u64 rows) {
     flush();
     if (!tq_shape_ok(qh, kvh, dh, d)) { launch_refused("attention_weights_tq", cudaSuccess); return; }
+    if (rows == 0) return;
     const int dev = current_device();
     if (fuse_enabled() && dev >= 0 && dev < DEVICES_MAX && length != 0) {
         /* deferred: if the values' door follows, the pair is one kernel over the coded rows and p is never written */
         std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
-        Pending x{WEIGHTS_TQ, p, res, q, (const uint16_t*)codes, qh, kvh, dh, length, 0, 0};
+        Pending x{WEIGHTS_TQ, p, res, q, (const uint16_t*)codes, qh, kvh, dh, length, 0, rows};
         x.scales = scales; x.width = d;
         g_pending[dev] = x;
         return;
     }
-    check("attention_weights_tq", sv::tq_weights_launch(p, res, q, codes, scales, qh, kvh, dh, length, d, 1, 0));
+    check("attention_weights_tq", sv::tq_weights_launch(p, res, q, codes, scales, qh, kvh, dh, length, d, rows, 0));
 }
-static void d_attention_residual_mix_tq(float* res, const float* p, const sv_u8* codes, const sv_h16* scales, sv_u64 qh, sv_u64 kvh, sv_u64 dh,
-                                        sv_u64 length, sv_u64 d) {
+static void d_attention_residual_mix_tq_rows(float* res, const float* p, const sv_u8* codes, const sv_h16* scales, sv_u64 qh, sv_u64 kvh,
+                                             sv_u64 dh, sv_u64 length, sv_u64 d, sv_u64 rows) {
     if (!tq_shape_ok(qh, kvh, dh, d)) { flush(); launch_refused("attention_residual_mix_tq", cudaSuccess); return; }
+    if (rows == 0) { flush(); return; }
     const int dev = current_device();
     if (dev >= 0 && dev < DEVICES_MAX) {
         std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
         Pending& x = g_pending[dev];
         if (x.kind == WEIGHTS_TQ && x.p == p && x.res == res && x.qh == qh && x.kvh == kvh && x.d == dh && x.length == length && x.width == d &&
-            sv::tq_attend_fits(x.q, x.k, x.scales, codes, scales, qh, kvh, dh, length, d)) {
+            x.rows == rows && sv::tq_attend_fits(x.q, x.k, x.scales, codes, scales, qh, kvh, dh, length, d)) {
             const Pending w = x;
-            x.kind = NONE;
-            check("attention_weights_tq+attention_residual_mix_tq",
-                  sv::tq_attend_launch(res, w.q, (const uint8_t*)w.k, w.scales, codes, scales, qh, kvh, dh, length, d, 0));
-            bump(SILVANN_B200_COUNTER_FUSED_RESIDUAL);
-            return;
+            const cudaError_t e = sv::tq_attend_launch(res, w.q, (const uint8_t*)w.k, w.scales, codes, scales, qh, kvh, dh, length, d, rows, 0);
+            if (e != cudaErrorInvalidValue) {                                /* the fused kernel took the pair: a row, or a chunk's rows */
+                x.kind = NONE;
+                check("attention_weights_tq+attention_residual_mix_tq", e);
+                bump(SILVANN_B200_COUNTER_FUSED_RESIDUAL);
+                return;
+            }
+            (void)cudaGetLastError();
         }
         run_pending_locked(x);
     }
-    check("attention_residual_mix_tq", sv::tq_residual_mix_launch(res, p, codes, scales, qh, kvh, dh, length, d, 1, 0));
+    check("attention_residual_mix_tq", sv::tq_residual_mix_launch(res, p, codes, scales, qh, kvh, dh, length, d, rows, 0));
 }
-static void d_attention_weights_tq_rows(float* p, float* res, const sv_h16* q, const sv_u8* codes, const sv_h16* scales, sv_u64 qh, sv_u64 kvh,
-                                        sv_u64 dh, sv_u64 length, sv_u64 d, sv_u64 rows) {
-    flush();
-    if (!tq_shape_ok(qh, kvh, dh, d)) { launch_refused("attention_weights_tq_rows", cudaSuccess); return; }
-    if (rows == 0) return;
-    check("attention_weights_tq_rows", sv::tq_weights_launch(p, res, q, codes, scales, qh, kvh, dh, length, d, rows, 0));
+static void d_attention_weights_tq(float* p, float* res, const sv_h16* q, const sv_u8* codes, const sv_h16* scales, sv_u64 qh, sv_u64 kvh,
+                                   sv_u64 dh, sv_u64 length, sv_u64 d) {
+    d_attention_weights_tq_rows(p, res, q, codes, scales, qh, kvh, dh, length, d, 1);
 }
-static void d_attention_residual_mix_tq_rows(float* res, const float* p, const sv_u8* codes, const sv_h16* scales, sv_u64 qh, sv_u64 kvh,
-                                             sv_u64 dh, sv_u64 length, sv_u64 d, sv_u64 rows) {
-    flush();
-    if (!tq_shape_ok(qh, kvh, dh, d)) { launch_refused("attention_residual_mix_tq_rows", cudaSuccess); return; }
-    if (rows == 0) return;
-    check("attention_residual_mix_tq_rows", sv::tq_residual_mix_launch(res, p, codes, scales, qh, kvh, dh, length, d, rows, 0));
+static void d_attention_residual_mix_tq(float* res, const float* p, const sv_u8* codes, const sv_h16* scales, sv_u64 qh, sv_u64 kvh, sv_u64 dh,
+                                        sv_u64 length, sv_u64 d) {
+    d_attention_residual_mix_tq_rows(res, p, codes, scales, qh, kvh, dh, length, d, 1);
 }
 
 /* ---- the weight path's doors a mixer verb cannot run without, as worded (tq.cu) ---- */

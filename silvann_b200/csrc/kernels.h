@@ -148,7 +148,7 @@ cudaError_t tq_gemv_groups_launch(uint16_t* out, const void* groups /* sv_tq_gro
 bool tq_attend_fits(const void* q, const void* kcodes, const void* kscales, const void* vcodes, const void* vscales, uint64_t qh, uint64_t kvh,
                     uint64_t dh, uint64_t length, uint64_t d);
 cudaError_t tq_attend_launch(float* res, const uint16_t* q, const uint8_t* kcodes, const uint16_t* kscales, const uint8_t* vcodes,
-                             const uint16_t* vscales, uint64_t qh, uint64_t kvh, uint64_t dh, uint64_t length, uint64_t d, cudaStream_t st);
+                             const uint16_t* vscales, uint64_t qh, uint64_t kvh, uint64_t dh, uint64_t length, uint64_t d, uint64_t rows /*of a prompt chunk; 1: one query*/, cudaStream_t st);
 cudaError_t tq_residual_mix_launch(float* res, const float* p, const uint8_t* codes, const uint16_t* scales, uint64_t qh, uint64_t kvh,
                                    uint64_t d_head, uint64_t length, uint64_t d, uint64_t rows, cudaStream_t st);
 

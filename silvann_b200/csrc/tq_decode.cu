@@ -63,6 +63,7 @@ struct TqParams {
     unsigned int* tickets;
     unsigned int* status;
     uint32_t q_heads, kv_heads, group, length, nsplit, head_blocks, heads_per_block, slot_floats;
+    uint32_t vgroup;                             /* rows · group: a kv head's query heads over every row of a prompt chunk, as one list */
     float scale_log2;
 };
 
@@ -118,8 +119,10 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t4 = lane & 3;
     const int hb = blockIdx.x % P.head_blocks, rest = blockIdx.x / P.head_blocks;
     const int kvh = rest % P.kv_heads, split = rest / P.kv_heads, nsplit = P.nsplit;
-    const int head0 = kvh * P.group + hb * P.heads_per_block;
-    const int heads = min((int)P.heads_per_block, (int)P.group - hb * (int)P.heads_per_block);
+    /* this block's query heads: entries v0 .. v0 + heads of the kv head's list — row v / group, head v % group of its group */
+    const int v0 = hb * P.heads_per_block;
+    const int heads = min((int)P.heads_per_block, (int)P.vgroup - v0);
+    auto head_at = [&](int h) { const int v = v0 + h; return (size_t)(v / (int)P.group) * P.q_heads + (size_t)kvh * P.group + (size_t)(v % (int)P.group); };
     const int len = (int)P.length;
     const int tiles = (len + BT - 1) / BT, chunk = (tiles + nsplit - 1) / nsplit;
     const int tile_begin = split * chunk, tile_end = min(tiles, tile_begin + chunk), nt = max(tile_end - tile_begin, 0);
@@ -142,7 +145,7 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     for (int i = tid; i < HPB * (DH / 4); i += THREADS) {           /* 8 bytes a step */
         const int h = i / (DH / 4), e = (i % (DH / 4)) * 4;
         uint2 v = make_uint2(0u, 0u);
-        if (h < heads) v = *reinterpret_cast<const uint2*>(P.q + (size_t)(head0 + h) * DH + e);
+        if (h < heads) v = *reinterpret_cast<const uint2*>(P.q + head_at(h) * DH + e);
         *reinterpret_cast<uint2*>(q_s + h * Cfg::QROW + e * 2) = v;
     }
     __syncthreads();
@@ -361,7 +364,7 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
             if (mw != -INFINITY) { const float f = fast_exp2(mw - m); acc += wo[(size_t)(w * HPB + h) * DH + e] * f; l += wl[w * HPB + h] * f; }
         }
         if (single) {
-            float* r = P.res + (size_t)(head0 + h) * (DH + 2);
+            float* r = P.res + head_at(h) * (DH + 2);
             r[2 + e] = acc;
             if (e == 0) { r[0] = m * SV_LN2; r[1] = l; }
         } else {
@@ -447,7 +450,7 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                 const float w = f[sp]; acc.x += y.x * w; acc.y += y.y * w; acc.z += y.z * w; acc.w += y.w * w;
             }
         }
-        float* ro = P.res + (size_t)(head0 + h) * (DH + 2);
+        float* ro = P.res + head_at(h) * (DH + 2);
         ro[2 + e] = acc.x; ro[3 + e] = acc.y; ro[4 + e] = acc.z; ro[5 + e] = acc.w;
         if (e == 0) { ro[0] = mh[h] * SV_LN2; ro[1] = lh[h]; }
     }
@@ -488,12 +491,14 @@ static cudaError_t tq_launch_one(const CUtensorMap& km, const CUtensorMap& vm, c
 }
 
 cudaError_t tq_attend_launch(float* res, const uint16_t* q, const uint8_t* kcodes, const uint16_t* kscales, const uint8_t* vcodes,
-                             const uint16_t* vscales, uint64_t qh, uint64_t kvh, uint64_t dh, uint64_t length, uint64_t d, cudaStream_t st) {
+                             const uint16_t* vscales, uint64_t qh, uint64_t kvh, uint64_t dh, uint64_t length, uint64_t d, uint64_t rows, cudaStream_t st) {
     DecodeScratch scratch;
     cudaError_t e = decode_device_scratch(&scratch);
     if (e != cudaSuccess) return e;
-    const uint32_t group = (uint32_t)(qh / kvh);
-    const uint32_t hpb = (group > 8u && dh == 128) ? 16u : 8u, hb = (group + hpb - 1) / hpb;
+    /* the rows of a prompt chunk see the same tier: their heads are more heads of the same kv head */
+    if (rows == 0 || rows * (qh / kvh) > 4096) return cudaErrorInvalidValue;
+    const uint32_t group = (uint32_t)(qh / kvh), vgroup = (uint32_t)rows * group;
+    const uint32_t hpb = (vgroup > 8u && dh == 128) ? 16u : 8u, hb = (vgroup + hpb - 1) / hpb;
     const uint32_t rb = (uint32_t)(dh * d / 8), box = rb > 128 ? 128u : rb;
     const uint32_t BT = rb > 128 ? 128u : 240u;            /* TqCfg::BT */
     CUtensorMap km, vm;
@@ -503,7 +508,7 @@ cudaError_t tq_attend_launch(float* res, const uint16_t* q, const uint8_t* kcode
     memset(&P, 0, sizeof P);
     P.res = res; P.q = q; P.kscales = kscales; P.vscales = vscales;
     P.partials = scratch.partials; P.tickets = scratch.tickets; P.status = device_status_word();
-    P.q_heads = (uint32_t)qh; P.kv_heads = (uint32_t)kvh; P.group = group; P.length = (uint32_t)length;
+    P.q_heads = (uint32_t)qh; P.kv_heads = (uint32_t)kvh; P.group = group; P.vgroup = vgroup; P.length = (uint32_t)length;
     P.head_blocks = hb; P.heads_per_block = hpb; P.slot_floats = (uint32_t)dh + 2u;
     P.scale_log2 = (1.0f / sqrtf((float)dh)) * SV_LOG2E;
     const uint32_t tiles = (uint32_t)((length + BT - 1) / BT), lanes = (uint32_t)kvh * hb;

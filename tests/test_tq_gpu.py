@@ -135,3 +135,31 @@ def test_a_tier_at_size_against_the_reference_run_here(cuda, fam, reference, por
     lse_got = got[:, 0] + np.log(got[:, 1])
     lse_want = want[:, 0] + np.log(want[:, 1])
     np.testing.assert_allclose(lse_got, lse_want, rtol=0, atol=2e-3)
+
+
+@pytest.mark.parametrize("d,dh,qh,kvh,L,rows", [(8, 128, 16, 2, 3000, 5), (4, 128, 32, 4, 1500, 3), (4, 256, 16, 2, 2000, 3), (8, 256, 8, 2, 700, 7), (8, 128, 8, 8, 333, 2)])
+def test_a_prompt_chunks_rows_over_a_tier_in_one_launch(cuda, fam, reference, port, d, dh, qh, kvh, L, rows):
+    """attention_weights_tq_rows + attention_residual_mix_tq_rows: the rows of a chunk see the same tier, so they are more
+    query heads of the same kv heads to the fused kernel; row r's residual is the one-row doors' for query r."""
+    impl = reference if reference is not None else port
+    rng = np.random.default_rng(1200 + d + dh + L + rows)
+    q = to_bits(rng.standard_normal((rows, qh, dh), dtype=np.float32), FP16)
+    kr = to_bits(rng.standard_normal((L * kvh, dh), dtype=np.float32), FP16)
+    vr = to_bits(rng.standard_normal((L * kvh, dh), dtype=np.float32), FP16)
+    kc, ks = oracle.tq_encode_rows(port, kr, d)
+    vc, vs = oracle.tq_encode_rows(port, vr, d)
+    tq_, tkc, tks, tvc, tvs = (dev(cuda, a) for a in (q, kc, ks, vc, vs))
+    p = cuda.zeros((rows * qh, L), dtype=cuda.float32, device="cuda")
+    res = cuda.zeros((rows, qh, dh + 2), dtype=cuda.float32, device="cuda")
+    before = ext.counters()
+    fam.nn.attention_weights_tq_rows(p.data_ptr(), res.data_ptr(), tq_.data_ptr(), tkc.data_ptr(), tks.data_ptr(), qh, kvh, dh, L, d, rows)
+    fam.nn.attention_residual_mix_tq_rows(res.data_ptr(), p.data_ptr(), tvc.data_ptr(), tvs.data_ptr(), qh, kvh, dh, L, d, rows)
+    assert fam.sys.compute_completed()
+    after = ext.counters()
+    assert after["refused"] == before["refused"] and ext.device_status() == 0
+    assert after["fused_residual"] - before["fused_residual"] == 1, "the rows pair is one kernel"
+    got = res.cpu().numpy()
+    for r in range(rows):
+        want = oracle.residual_tq(impl, q[r].copy(), kc, ks, vc, vs, qh, kvh, dh, L, d)
+        np.testing.assert_allclose(got[r, :, 2:] / got[r, :, 1:2], want[:, 2:] / want[:, 1:2], rtol=0, atol=2e-3, err_msg=f"row {r}")
+        np.testing.assert_allclose(got[r, :, 0] + np.log(got[r, :, 1]), want[:, 0] + np.log(want[:, 1]), rtol=0, atol=2e-3, err_msg=f"row {r} lse")
