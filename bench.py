@@ -436,6 +436,23 @@ def other_workloads(torch, fam, pk, steps, warmup):
             out[f"tq{width}_tier_d{dh}"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms, "frac_hbm": nbytes / ms / 1e6 / hbm,
                                             "positions_per_s": Lt / ms * 1e3,
                                             "note": f"262,144 positions coded at {width} bits, {tqh}q/{tkvh}kv heads of {dh}: {nbytes / 1e6:.0f} MB of codes and scales a call"}
+            if dh == 128 and width == 8:
+                # a prompt chunk's 16 rows over the same tier through the _rows door pair (one fused launch): the rows are more
+                # query heads of the same kv heads; the codes are read once a block of 16 of them
+                rows16 = 16
+                q16 = torch.randn((rows16, tqh, dh), generator=gen, device="cuda", dtype=torch.float16) * 0.25
+                res16 = torch.zeros((rows16, tqh, dh + 2), device="cuda", dtype=torch.float32)
+
+                def tq_rows():
+                    i = tstate["i"] = 1 - tstate["i"]
+                    fam.nn.attention_weights_tq_rows(tp.data_ptr(), res16.data_ptr(), q16.data_ptr(), kc[i].data_ptr(), ks[i].data_ptr(), tqh, tkvh, dh, Lt, width, rows16)
+                    fam.nn.attention_residual_mix_tq_rows(res16.data_ptr(), tp.data_ptr(), vc[i].data_ptr(), vs[i].data_ptr(), tqh, tkvh, dh, Lt, width, rows16)
+                before = ext.counters()["fused_residual"]
+                ms = time_loop(torch, tq_rows, max(steps // 2, 10), 3)
+                assert ext.counters()["fused_residual"] > before, "the coded rows pair did not take the fused kernel"
+                flops = 4.0 * rows16 * tqh * dh * Lt
+                out["tq8_tier_d128_rows16"] = {"value": rows16 * Lt / ms * 1e3, "unit": "row-positions/s", "ms_per_call": ms, "tflops": flops / ms / 1e9,
+                                               "note": "16 rows of a prompt chunk x 32q/4kv heads of 128 over 262,144 positions coded at 8 bits, one launch"}
             del kc, vc, ks, vs
     torch.cuda.empty_cache()
 
