@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 import oracle
-from oracle import from_bits, to_bits
+from oracle import FP16, from_bits, to_bits
 from silvann_b200 import ext, verbs, workloads
 from util import assert_close16, dev, host_bits
 
@@ -205,3 +205,23 @@ def test_argument_refusals(cuda):
         ext.decode(t, None, t, t, t, 16, 4, 128, 0, 0)            # empty range
     with pytest.raises(ext.B200Error):
         ext.decode(None, None, t, t, t, 16, 4, 128, 10, 0)        # nowhere to put the answer
+
+
+def test_latent_attention_shaped_decode(cuda, fam, reference, port):
+    """GLM's latent attention at decode: 64 query heads on ONE kv head 512 wide, the cached latent both keys and values
+    (the same plane handed to both doors).  Wider than the fused kernel's heads: the doors run as worded, and must."""
+    impl = reference if reference is not None else port
+    qh, kvh, d, L = 64, 1, 512, 1500
+    rng = np.random.default_rng(91)
+    q = to_bits(rng.standard_normal((qh, d)).astype(np.float32) * 0.25, FP16)
+    lat = to_bits(rng.standard_normal((L, kvh, d)).astype(np.float32) * 0.5, FP16)
+    tq_, tl = dev(cuda, q), dev(cuda, lat)
+    p = cuda.zeros((qh, L), dtype=cuda.float32, device="cuda")
+    o = cuda.zeros((qh, d), dtype=cuda.int16, device="cuda")
+    before = ext.counters()
+    fam.nn.attention_scores(p.data_ptr(), tq_.data_ptr(), tl.data_ptr(), qh, kvh, d, L)
+    fam.nn.attention_mix(o.data_ptr(), p.data_ptr(), tl.data_ptr(), qh, kvh, d, L, None)
+    assert fam.sys.compute_completed()
+    assert ext.counters()["refused"] == before["refused"] and ext.device_status() == 0
+    want = impl.decode(q, lat, lat, qh, kvh, d, L)
+    assert_close16(host_bits(o), from_bits(want, FP16), FP16, "64 heads over one 512-wide latent")
