@@ -485,6 +485,31 @@ def other_workloads(torch, fam, pk, steps, warmup):
     out["kda_decode_64heads"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_step": ms, "frac_hbm": nbytes / ms / 1e6 / hbm,
                                  "note": "kda_step door, 64 heads x 128x128 fp32 state (8.4 MB: stays in L2 between steps), one block a head"}
 
+    # the latent attention's two projections at decode (GLM's shape: 64 heads, 192 + 256 rows of a 512-wide latent a head):
+    # a head's key rows fold its query into the latent (absorb), its value rows unfold the answer (expand); 8 distinct W cycled
+    mh, nope, vd, lat, copies = 64, 192, 256, 512, 8
+    Wl = (torch.randn((copies, mh * (nope + vd), lat), generator=gen, device="cuda", dtype=torch.float16) * 0.05)
+    qa = torch.randn((mh * nope,), generator=gen, device="cuda", dtype=torch.float16)
+    oa = torch.randn((mh * lat,), generator=gen, device="cuda", dtype=torch.float16)
+    absorbed = torch.zeros((mh * lat,), device="cuda", dtype=torch.float16)
+    expanded = torch.zeros((mh * vd,), device="cuda", dtype=torch.float16)
+    mstate = {"i": 0}
+
+    def absorb():
+        i = mstate["i"] = (mstate["i"] + 1) % copies
+        fam.nn.attention_absorb(absorbed.data_ptr(), qa.data_ptr(), Wl[i].data_ptr(), mh, nope, lat, nope + vd, C.c_float(0.0722), None)
+
+    def expand():
+        i = mstate["i"] = (mstate["i"] + 1) % copies
+        fam.nn.attention_expand(expanded.data_ptr(), oa.data_ptr(), Wl[i].data_ptr(), mh, vd, lat, nope + vd, nope, None)
+    for tag, fn, nbytes in (("mla_absorb_64heads", absorb, mh * nope * lat * 2 + mh * nope * 2 + mh * lat * 2),
+                            ("mla_expand_64heads", expand, mh * vd * lat * 2 + mh * lat * 2 + mh * vd * 2)):
+        ms = time_loop(torch, fn, max(steps * 5, 50), 5)
+        out[tag] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms, "frac_hbm": nbytes / ms / 1e6 / hbm,
+                    "note": f"{tag.split('_')[1]} door, 64 heads: {nbytes / 1e6:.1f} MB of the latent's expansion a call, 8 matrices cycled"}
+    del Wl
+    torch.cuda.empty_cache()
+
     # configuration 5: recurrent decode steps (batched so that state traffic is real) and the prompt
     heads, d = 32, 128
     for seqs, tag in ((1, "config5_deltanet_decode_1seq"), (64, "config5_deltanet_decode_64seq")):
@@ -840,6 +865,26 @@ def run_case(args):
             i = gstate["i"] = (gstate["i"] + 1) % copies
             fam.nn.turboquant_gemv(ov.data_ptr(), codes[i].data_ptr(), rows * rb, scales[i].data_ptr(), rows * 2, xv.data_ptr(), width, rows, cols, None)
         work, unit = rows * (rb + 2) + cols * 2 + rows * 2, "bytes"
+    elif name in ("mla_absorb", "mla_expand"):
+        import ctypes as C
+        mh, nope, vd, lat, copies = 64, 192, 256, 512, 8
+        Wl = (torch.randn((copies, mh * (nope + vd), lat), generator=gen, device="cuda", dtype=torch.float16) * 0.05)
+        qa = torch.randn((mh * nope,), generator=gen, device="cuda", dtype=torch.float16)
+        oa = torch.randn((mh * lat,), generator=gen, device="cuda", dtype=torch.float16)
+        absorbed = torch.zeros((mh * lat,), device="cuda", dtype=torch.float16)
+        expanded = torch.zeros((mh * vd,), device="cuda", dtype=torch.float16)
+        mstate = {"i": 0}
+        if name == "mla_absorb":
+            def fn():
+                i = mstate["i"] = (mstate["i"] + 1) % copies
+                fam.nn.attention_absorb(absorbed.data_ptr(), qa.data_ptr(), Wl[i].data_ptr(), mh, nope, lat, nope + vd, C.c_float(0.0722), None)
+            work = mh * nope * lat * 2 + mh * nope * 2 + mh * lat * 2
+        else:
+            def fn():
+                i = mstate["i"] = (mstate["i"] + 1) % copies
+                fam.nn.attention_expand(expanded.data_ptr(), oa.data_ptr(), Wl[i].data_ptr(), mh, vd, lat, nope + vd, nope, None)
+            work = mh * vd * lat * 2 + mh * lat * 2 + mh * vd * 2
+        unit = "bytes"
     elif name == "kda_decode":
         import ctypes as C
         heads, d = 64, 128

@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(256) kda_steps_any_kernel(float* S, const uint
  * a thread owns 8 neighbouring columns (one 16-byte load a key row) when the latent's width and W's address allow, and
  * the block's threads past the columns split the nope rows between them; their sums meet in shared memory. */
 template <bool WIDE>
-__global__ void __launch_bounds__(256) absorb_kernel(uint16_t* out, const uint16_t* q, const uint16_t* W, uint64_t heads, uint64_t nope, uint64_t latent,
+__global__ void __launch_bounds__(512) absorb_kernel(uint16_t* out, const uint16_t* q, const uint16_t* W, uint64_t heads, uint64_t nope, uint64_t latent,
                                                      uint64_t stride, float scale, uint64_t rows, unsigned int* over) {
     extern __shared__ float acc[];                                         /* [slices][latent] */
     constexpr int PER = WIDE ? 8 : 1;
@@ -195,16 +195,30 @@ __global__ void __launch_bounds__(256) absorb_kernel(uint16_t* out, const uint16
                 float s[PER];
 #pragma unroll
                 for (int e = 0; e < PER; ++e) s[e] = 0.f;
-                for (uint64_t i = slice; i < nope; i += slices) {
-                    const float qi = H::to_float(qh[i]);
-                    if (WIDE) {
-                        const uint4 u = *reinterpret_cast<const uint4*>(Wh + i * latent + chunk * 8);
+                if (WIDE) {
+                    /* eight key rows' 16 bytes asked for before any is used: a column sum is one long chain of loads otherwise */
+                    uint64_t i = slice;
+                    for (; i + 7 * slices < nope; i += 8 * slices) {
+                        uint4 u[8];
+                        float qv[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) { u[k] = __ldg(reinterpret_cast<const uint4*>(Wh + (i + k * slices) * latent + chunk * 8)); qv[k] = H::to_float(qh[i + k * slices]); }
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            const uint32_t ws[4] = {u[k].x, u[k].y, u[k].z, u[k].w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) { const float2 p = H::unpack2(ws[e]); s[2 * e] += p.x * qv[k]; s[2 * e + 1] += p.y * qv[k]; }
+                        }
+                    }
+                    for (; i < nope; i += slices) {
+                        const float qi = H::to_float(qh[i]);
+                        const uint4 u = __ldg(reinterpret_cast<const uint4*>(Wh + i * latent + chunk * 8));
                         const uint32_t ws[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
                         for (int e = 0; e < 4; ++e) { const float2 p = H::unpack2(ws[e]); s[2 * e] += p.x * qi; s[2 * e + 1] += p.y * qi; }
-                    } else {
-                        s[0] += H::to_float(Wh[i * latent + chunk]) * qi;
                     }
+                } else {
+                    for (uint64_t i = slice; i < nope; i += slices) s[0] += H::to_float(Wh[i * latent + chunk]) * H::to_float(qh[i]);
                 }
 #pragma unroll
                 for (int e = 0; e < PER; ++e) acc[slice * latent + chunk * PER + e] = s[e];
@@ -450,12 +464,12 @@ cudaError_t kda_steps_launch(float* S, const uint16_t* conved, const uint16_t* f
 cudaError_t absorb_launch(uint16_t* out, const uint16_t* q, const uint16_t* W, uint64_t heads, uint64_t nope, uint64_t latent, uint64_t stride, float scale,
                           uint64_t rows, unsigned int* over, cudaStream_t st) {
     const bool wide = latent % 8 == 0 && (uintptr_t)W % 16 == 0;
-    const uint64_t chunks = wide ? latent / 8 : latent, across = chunks < 256 ? chunks : 256, slices = 256 / across;
+    const uint64_t chunks = wide ? latent / 8 : latent, across = chunks < 512 ? chunks : 512, slices = 512 / across;
     const size_t smem = (size_t)slices * latent * sizeof(float);
     if (smem > 48 * 1024) return cudaErrorInvalidValue;
     const unsigned g = glm_grid(rows * heads, 1, 148u * 16u);
-    if (wide) absorb_kernel<true><<<g, 256, smem, st>>>(out, q, W, heads, nope, latent, stride, scale, rows, over);
-    else absorb_kernel<false><<<g, 256, smem, st>>>(out, q, W, heads, nope, latent, stride, scale, rows, over);
+    if (wide) absorb_kernel<true><<<g, 512, smem, st>>>(out, q, W, heads, nope, latent, stride, scale, rows, over);
+    else absorb_kernel<false><<<g, 512, smem, st>>>(out, q, W, heads, nope, latent, stride, scale, rows, over);
     SV_GLM_DONE();
 }
 cudaError_t expand_launch(uint16_t* out, const uint16_t* o, const uint16_t* W, uint64_t heads, uint64_t width, uint64_t latent, uint64_t stride,
