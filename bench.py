@@ -510,6 +510,22 @@ def other_workloads(torch, fam, pk, steps, warmup):
     del Wl
     torch.cuda.empty_cache()
 
+    # the sparse attention's indexer at decode: 32 index heads of 128 score 8,192 pooled keys, the top 512 pools chosen
+    ih, idim, pools, topk, kpool = 32, 128, 8192, 512, 4
+    iq = torch.randn((ih * idim,), generator=gen, device="cuda", dtype=torch.float16)
+    iw = torch.randn((ih,), generator=gen, device="cuda", dtype=torch.float16)
+    pooled = torch.randn((pools, idim), generator=gen, device="cuda", dtype=torch.float16)
+    iscores = torch.zeros((pools,), device="cuda", dtype=torch.float32)
+    iindex = torch.zeros((topk * kpool + kpool,), device="cuda", dtype=torch.int32)
+    icount = torch.zeros((1,), device="cuda", dtype=torch.int32)
+
+    def indexer():
+        fam.nn.index_scores(iscores.data_ptr(), iq.data_ptr(), iw.data_ptr(), pooled.data_ptr(), ih, idim, pools, C.c_float(0.088))
+        fam.nn.index_select(iindex.data_ptr(), icount.data_ptr(), iscores.data_ptr(), pools, topk, kpool, pools * kpool, 3)
+    ms = time_loop(torch, indexer, max(steps * 5, 50), 5)
+    out["glm_indexer_8192pools"] = {"value": pools / ms * 1e3, "unit": "pools/s", "ms_per_call": ms,
+                                    "note": "index_scores + index_select: 32 heads of 128 over 8,192 pooled keys, the top 512 pools as positions (two launches)"}
+
     # configuration 5: recurrent decode steps (batched so that state traffic is real) and the prompt
     heads, d = 32, 128
     for seqs, tag in ((1, "config5_deltanet_decode_1seq"), (64, "config5_deltanet_decode_64seq")):

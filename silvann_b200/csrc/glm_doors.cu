@@ -333,6 +333,44 @@ __global__ void __launch_bounds__(256) index_scores_kernel(float* scores, uint64
     }
 }
 
+/* The same scores with the row's queries staged in shared memory once a block (a head's row one word longer than it is, so
+ * that the lanes — a head each — read different banks) and a pool's key staged once a warp: the sums run over the columns in
+ * the reference's order, from shared memory instead of 32 strided streams of global loads.  dim even; blockIdx.y is the row. */
+__global__ void __launch_bounds__(256) index_scores_staged_kernel(float* scores, uint64_t scores_row, const uint16_t* q, const uint16_t* w,
+                                                                  const uint16_t* pooled, uint32_t heads, uint32_t dim, uint64_t pools, uint64_t len0,
+                                                                  uint64_t kpool, uint64_t rows, float scale) {
+    extern __shared__ uint32_t ix_s[];
+    const uint32_t half_dim = dim / 2, qstride = half_dim + 1;
+    uint32_t* q_s = ix_s;                                    /* [heads][dim/2 + 1] words */
+    uint32_t* k_s = ix_s + heads * qstride + (threadIdx.x >> 5) * half_dim;   /* this warp's pool key */
+    const uint64_t u = blockIdx.y, mine = rows == 0 ? pools : (len0 + u) / kpool;
+    const uint32_t* qu = reinterpret_cast<const uint32_t*>(q + u * heads * dim);
+    for (uint32_t i = threadIdx.x; i < heads * half_dim; i += blockDim.x) q_s[(i / half_dim) * qstride + i % half_dim] = qu[i];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float per_head = 1.0f / sqrtf((float)heads);
+    for (uint64_t p = (uint64_t)blockIdx.x * 8 + warp; p < mine; p += (uint64_t)gridDim.x * 8) {
+        const uint32_t* kp = reinterpret_cast<const uint32_t*>(pooled + p * dim);
+        __syncwarp();
+        for (uint32_t c = lane; c < half_dim; c += 32) k_s[c] = kp[c];
+        __syncwarp();
+        float part = 0.f;
+        for (uint32_t h = lane; h < heads; h += 32) {
+            const uint32_t* qh = q_s + h * qstride;
+            float dot = 0.f;
+            for (uint32_t c = 0; c < half_dim; ++c) {
+                const float2 a = H::unpack2(qh[c]), b = H::unpack2(k_s[c]);
+                dot += a.x * b.x;
+                dot += a.y * b.y;
+            }
+            dot *= scale;
+            part += (dot > 0.f ? dot : 0.f) * H::to_float(w[u * heads + h]) * per_head;
+        }
+        for (int x = 16; x > 0; x >>= 1) part += __shfl_xor_sync(0xffffffffu, part, x);
+        if (lane == 0) scores[u * scores_row + p] = part;
+    }
+}
+
 __device__ __forceinline__ uint32_t index_key(float f) {                   /* orders as the score does (:3759-3764) */
     const uint32_t u = __float_as_uint(f);
     return (u & 0x80000000u) != 0u ? ~u : (u | 0x80000000u);
@@ -344,7 +382,7 @@ __device__ __forceinline__ uint32_t index_key(float f) {                   /* or
 __global__ void __launch_bounds__(1024) index_select_kernel(uint32_t* index, uint64_t index_row, uint32_t* counts, const float* scores, uint64_t scores_row,
                                                             uint64_t pools1, uint64_t k, uint64_t kpool, uint64_t tail_first1, uint64_t tail1, uint64_t len0,
                                                             uint64_t rows) {
-    __shared__ unsigned int total;
+    __shared__ unsigned int hist[256], found[2];
     __shared__ unsigned int warp_sum[2][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     for (uint64_t u = blockIdx.x; u < (rows == 0 ? 1 : rows); u += gridDim.x) {
@@ -352,18 +390,40 @@ __global__ void __launch_bounds__(1024) index_select_kernel(uint32_t* index, uin
         const uint64_t tail_first = rows == 0 ? tail_first1 : pools * kpool, tail = rows == 0 ? tail1 : len - pools * kpool;
         const float* sc = scores + u * scores_row;
         uint32_t* out = index + u * index_row;
+        /* the k-th largest key, a byte at a time from the top: a 256-bin count of the keys that carry the bytes found so far,
+         * walked down from the top bin until k keys are covered (the value the reference finds a bit at a time) */
         uint32_t cut = 0u;
         if (pools > k) {
-            for (int bit = 31; bit >= 0; --bit) {
-                const uint32_t want = cut | (1u << (uint32_t)bit);
-                unsigned int have = 0;
-                for (uint64_t p = threadIdx.x; p < pools; p += blockDim.x) have += index_key(sc[p]) >= want ? 1u : 0u;
-                if (threadIdx.x == 0) total = 0;
+            uint32_t known = 0u, need = (uint32_t)k;
+            for (int shift = 24; shift >= 0; shift -= 8) {
+                for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0u;
                 __syncthreads();
-                for (int s = 16; s > 0; s >>= 1) have += __shfl_xor_sync(0xffffffffu, have, s);
-                if (lane == 0 && have) atomicAdd(&total, have);
+                for (uint64_t first = 0; first < pools; first += blockDim.x) {             /* whole warps together: lanes that count the */
+                    const uint64_t p = first + threadIdx.x;                                    /* same bin add once, through their first */
+                    const uint32_t key = p < pools ? index_key(sc[p]) : 0u;
+                    const bool live = p < pools && (key & known) == cut;
+                    const uint32_t bin = live ? ((key >> shift) & 255u) : 256u;
+                    const unsigned same = __match_any_sync(0xffffffffu, bin);
+                    if (live && lane == __ffs(same) - 1) atomicAdd(&hist[bin], (unsigned int)__popc(same));
+                }
                 __syncthreads();
-                if ((uint64_t)total >= k) cut = want;
+                if (warp == 0) {
+                    /* walked down from the top bin, eight bins a lane: the lane whose bins take the count past `need` walks them */
+                    uint32_t mine8 = 0u;
+#pragma unroll
+                    for (int b = 0; b < 8; ++b) mine8 += hist[255 - 8 * lane - b];
+                    uint32_t upto = mine8;                                  /* this lane's bins and every lane's above */
+                    for (int d = 1; d < 32; d <<= 1) { const uint32_t o = __shfl_up_sync(0xffffffffu, upto, d); if (lane >= d) upto += o; }
+                    const unsigned reached = __ballot_sync(0xffffffffu, upto >= need);
+                    const int who = reached ? __ffs(reached) - 1 : 31;
+                    if (lane == who) {
+                        uint32_t covered = upto - mine8, bin = 255u - 8u * (uint32_t)lane;
+                        for (int b = 0; b < 8; ++b, --bin) { const uint32_t here = hist[bin]; if (covered + here >= need || b == 7) break; covered += here; }
+                        found[0] = bin; found[1] = need - covered;
+                    }
+                }
+                __syncthreads();
+                cut |= found[0] << shift; need = found[1]; known |= 255u << shift;
                 __syncthreads();
             }
         }
@@ -491,6 +551,16 @@ cudaError_t index_pool_launch(uint16_t* pooled, const uint16_t* keys, const uint
 cudaError_t index_scores_launch(float* scores, uint64_t scores_row, const uint16_t* q, const uint16_t* w, const uint16_t* pooled, uint64_t heads, uint64_t dim,
                                 uint64_t pools, uint64_t len0, uint64_t kpool, uint64_t rows, float scale, cudaStream_t st) {
     const uint64_t most = rows == 0 ? pools : (len0 + rows - 1) / kpool;
+    const size_t smem = ((size_t)heads * (dim / 2 + 1) + 8 * (dim / 2)) * 4;
+    if (dim % 2 == 0 && smem <= 48 * 1024 && heads < (1u << 16) && dim < (1u << 16) && rows <= 65535 && (uintptr_t)q % 4 == 0 && (uintptr_t)pooled % 4 == 0 &&
+        (heads * dim) % 2 == 0) {
+        const uint64_t urows = rows == 0 ? 1 : rows;
+        unsigned gx = glm_grid(most, 8, 148u * 8u);
+        if (urows > 1) { const unsigned per = (unsigned)((148u * 8u + urows - 1) / urows); if (gx > per) gx = per < 1 ? 1 : per; }
+        index_scores_staged_kernel<<<dim3(gx, (unsigned)urows), 256, smem, st>>>(scores, scores_row, q, w, pooled, (uint32_t)heads, (uint32_t)dim, pools, len0,
+                                                                                  kpool, rows, scale);
+        SV_GLM_DONE();
+    }
     index_scores_kernel<<<glm_grid((rows == 0 ? 1 : rows) * most, 8, 148u * 16u), 256, 0, st>>>(scores, scores_row, q, w, pooled, heads, dim, pools, len0, kpool,
                                                                                                  rows, scale);
     SV_GLM_DONE();
