@@ -13,7 +13,7 @@ from silvann_b200 import abi, ext
 
 ROOT = Path(__file__).resolve().parents[1]
 HEADER = ROOT / "include" / "silvann_b200.h"
-REFERENCE = Path("/root/reference/engine/src")
+REFERENCE = __import__("oracle.build", fromlist=["REFERENCE_TREE"]).REFERENCE_TREE / "engine" / "src"   # where the reference tree is mounted, if it is
 
 
 def test_library_is_built_and_loads():
