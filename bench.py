@@ -315,6 +315,23 @@ def gpu_baseline(torch, wl: PagedWorkload, pk, steps):
     ms = time_loop(torch, lambda: R.nn.deltanet_steps_gate(S.data_ptr(), conved.data_ptr(), z.data_ptr(), beta.data_ptr(), g.data_ptr(), w.data_ptr(),
                                                            o5.data_ptr(), heads, heads, d, T, 0, over.data_ptr()), 2, 1)
     out["config5_deltanet_prefill_8192"] = {"value": T / ms * 1e3, "unit": "positions/s", "ms": ms}
+    del S, conved, z, beta, g, o5
+    torch.cuda.empty_cache()
+
+    # the coded matrix-vector door on the same matrices as `others` times it on (the reference's CUDA family has a kernel of its
+    # own for widths 4 and 8: silicon_families/nvidia_cuda12/overrides/turboquant.cuh)
+    for width, copies in ((4, 8), (8, 4)):
+        rows, cols = 16384, 4096
+        codes, scales, xv, ov, rb = coded_weights(torch, gen, copies, rows, cols, width)
+        gstate = {"i": 0}
+
+        def gemv():
+            i = gstate["i"] = (gstate["i"] + 1) % copies
+            R.nn.turboquant_gemv(ov.data_ptr(), codes[i].data_ptr(), rows * rb, scales[i].data_ptr(), rows * 2, xv.data_ptr(), width, rows, cols, over.data_ptr())
+        ms = time_loop(torch, gemv, 50, 5)
+        nbytes = rows * (rb + 2) + cols * 2 + rows * 2
+        out[f"tq{width}_gemv_16384x4096"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms}
+        del codes, scales
     R.sys.compute_completed()
     return out
 
