@@ -332,6 +332,27 @@ def gpu_baseline(torch, wl: PagedWorkload, pk, steps):
         nbytes = rows * (rb + 2) + cols * 2 + rows * 2
         out[f"tq{width}_gemv_16384x4096"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms}
         del codes, scales
+    torch.cuda.empty_cache()
+
+    # a coded tier of 262,144 positions (32q/4kv heads of 128) through the reference's own weights_tq + residual_mix_tq kernels
+    dh, tqh, tkvh, Lt = 128, 32, 4, 262144
+    for width in (8, 4):
+        rb = dh * width // 8
+        kc = torch.randint(0, 256, (Lt * tkvh, rb), generator=gen, device="cuda", dtype=torch.uint8)
+        vc = torch.randint(0, 256, (Lt * tkvh, rb), generator=gen, device="cuda", dtype=torch.uint8)
+        ks = (torch.rand((Lt * tkvh,), generator=gen, device="cuda") * 0.5 + 0.75).to(torch.float16)
+        vs = (torch.rand((Lt * tkvh,), generator=gen, device="cuda") * 0.5 + 0.75).to(torch.float16)
+        tq_q = torch.randn((tqh, dh), generator=gen, device="cuda", dtype=torch.float16) * 0.25
+        tp = torch.zeros((tqh, Lt), device="cuda", dtype=torch.float32)
+        tres = torch.zeros((tqh, dh + 2), device="cuda", dtype=torch.float32)
+
+        def tq_pair():
+            R.nn.attention_weights_tq(tp.data_ptr(), tres.data_ptr(), tq_q.data_ptr(), kc.data_ptr(), ks.data_ptr(), tqh, tkvh, dh, Lt, width)
+            R.nn.attention_residual_mix_tq(tres.data_ptr(), tp.data_ptr(), vc.data_ptr(), vs.data_ptr(), tqh, tkvh, dh, Lt, width)
+        ms = time_loop(torch, tq_pair, 5, 2)
+        nbytes = 2 * Lt * tkvh * (rb + 2)
+        out[f"tq{width}_tier_d128"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms}
+        del kc, vc, ks, vs, tp
     R.sys.compute_completed()
     return out
 
