@@ -353,6 +353,12 @@ def gpu_baseline(torch, wl: PagedWorkload, pk, steps):
         nbytes = 2 * Lt * tkvh * (rb + 2)
         out[f"tq{width}_tier_d128"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms}
         del kc, vc, ks, vs, tp
+    # Kimi Delta Attention, one decode step of 64 heads of 128, through the reference's kda_step
+    import ctypes as C
+    S, conved, f, b, dt, a_log, gate, w, o = kda_workload(torch, gen, 64, 128, 1)
+    ms = time_loop(torch, lambda: R.nn.kda_step(S.data_ptr(), conved.data_ptr(), f.data_ptr(), b.data_ptr(), dt.data_ptr(), a_log.data_ptr(), gate.data_ptr(),
+                                                w.data_ptr(), o.data_ptr(), 64, 128, C.c_float(-5.0), C.c_float(1e-5), over.data_ptr()), 50, 5)
+    out["kda_decode_64heads"] = {"ms_per_step": ms}
     R.sys.compute_completed()
     return out
 
