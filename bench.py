@@ -138,7 +138,7 @@ class PagedWorkload:
         self.k_pool = torch.randn(shape, generator=gen, device="cuda", dtype=torch.bfloat16)
         self.v_pool = torch.randn(shape, generator=gen, device="cuda", dtype=torch.bfloat16)
         self.q = torch.randn((self.seqs, L.q_heads, L.head_dim), generator=gen, device="cuda", dtype=torch.bfloat16)
-        self.table = torch.from_numpy(np.maximum(L.page_table, 0)).cuda()
+        self.table = torch.from_numpy(L.page_table).cuda()
         self.out = torch.zeros((self.seqs, L.q_heads, L.head_dim), device="cuda", dtype=torch.bfloat16)
         self.plan = ext.Plan()
         self.plan.plan(L.seq_lens, L.q_heads, L.kv_heads, L.head_dim)
@@ -181,7 +181,7 @@ class EndToEnd:
         wl.plan.plan(L.seq_lens, L.q_heads, L.kv_heads, L.head_dim)
         sysd.memory_write(wl.q.data_ptr(), self.h_q, self.q_bytes)
         sysd.memory_write(self.rows_dev.data_ptr(), self.h_rows, 2 * wl.seqs * self.row_bytes)
-        wl.plan.append(wl.k_pool, wl.v_pool, self.rows_dev[0], self.rows_dev[1], wl.page_positions, wl.table, L.page_table.shape[1])
+        wl.plan.append(wl.k_pool, wl.v_pool, self.rows_dev[0], self.rows_dev[1], L.pool_pages, wl.page_positions, wl.table, L.page_table.shape[1])
         wl.step()
         sysd.memory_read(self.h_out, wl.out.data_ptr(), self.o_bytes)
 
@@ -650,17 +650,15 @@ def long_context(torch, dist, rank, world, steps, pk):
     h_len = max(0, min(HOST, shard.pos_hi) - shard.pos_lo)
     k_host = k[:h_len].cpu().pin_memory() if h_len else None
     v_host = v[:h_len].cpu().pin_memory() if h_len else None
-    pg = None
-    if world > kvh:                                  # every rank takes part in creating every group
-        for head in range(kvh):
-            members = [r for r in range(world) if r // (world // kvh) == head]
-            g = dist.new_group(members)
-            if rank in members:
-                pg = g
+    # the ranks that split a kv head's range exchange residuals through the library's own kernel over peer memory; the
+    # buffers' handles travel once, here
+    exchange = sharded.connect_exchange(torch, ext, dist, shard.group, rank, shard.q_heads * (d + 2) * 4) if world > 1 else None
+    if len(shard.group) == 1:
+        exchange = None
     out = {}
     for tag, (kh, vh, hl, kd, vd, dl) in {"tiered": (k_host, v_host, h_len, k[h_len:] if n > h_len else None, v[h_len:] if n > h_len else None, n - h_len),
                                            "resident": (None, None, 0, k, v, n)}.items():
-        runner = sharded.LongContextRank(torch, ext, shard, d, ext.BF16, kh, vh, hl, kd, vd, dl, dist, pg, chunk_positions=8192, stages=3)
+        runner = sharded.LongContextRank(torch, ext, shard, d, ext.BF16, kh, vh, hl, kd, vd, dl, dist, None, chunk_positions=0, stages=3, exchange=exchange)
         for _ in range(3):
             runner.step(q)
         if world > 1:
@@ -681,7 +679,7 @@ def long_context(torch, dist, rank, world, steps, pk):
         runner.close()
     out["tiered"]["host_tier_bytes"] = 2 * HOST * kvh * d * 2
     out["tiered"]["host_tier_gbs"] = out["tiered"]["host_tier_bytes"] / out["tiered"]["ms_per_step"] / 1e6
-    out["note"] = ("kv heads sharded over ranks" + (", each kv head's range halved over two ranks and residuals all-gathered (NCCL) and merged" if world > kvh else ", no collective")
+    out["note"] = ("kv heads sharded over ranks" + (", each kv head's range halved over two ranks, residuals pushed into the partner's memory and folded by one kernel a rank (no NCCL on the data path)" if world > kvh else ", no collective")
                    + "; tiered: first 65,536 positions streamed from pinned host RAM each step (PCIe-bound); resident: all positions in HBM")
     return out
 
@@ -864,7 +862,7 @@ def run_case(args):
         vp = torch.randn(shape, generator=gen, device="cuda", dtype=torch.bfloat16)
         q = torch.randn((8, L.q_heads, L.head_dim), generator=gen, device="cuda", dtype=torch.bfloat16)
         o = torch.zeros_like(q)
-        table = torch.from_numpy(np.maximum(L.page_table, 0)).cuda()
+        table = torch.from_numpy(L.page_table).cuda()
         plan = ext.Plan(); plan.plan(L.seq_lens, L.q_heads, L.kv_heads, L.head_dim)
         fn = lambda: plan.decode(o, None, q, kp, vp, L.pool_pages, workloads.PAGE_POSITIONS, table, L.page_table.shape[1], ext.BF16)
         work, unit = L.kv_bytes, "bytes"

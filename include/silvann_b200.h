@@ -296,8 +296,13 @@ const silvann_b200_family* silvann_silicon_family_get(uint32_t abi_version);
 const char* silvann_b200_last_error(void);
 /* Copies min(n, SILVANN_B200_COUNTERS) process-wide counters into out; reset != 0 zeroes them afterwards. */
 int silvann_b200_counters_read(uint64_t* out, uint32_t n, int reset);
-/* Waits for the bound device's default queue, then answers its status word: 0, or "B2TO" (0x4232544F) when a kernel
- * gave up on a bounded wait.  clear != 0 zeroes the word. */
+/* Waits for the bound device's default queue, then answers its status word: 0 when nothing went wrong; "B2TO"
+ * (0x4232544F) ORed in when a kernel gave up on a bounded wait; SILVANN_B200_STATUS_BAD_PAGE ORed in when a paged decode
+ * or append met a page-table entry, inside a sequence's length, that names no page of the pool (the tile was read as
+ * zeros, the row was not written).  The word of silvann_b200_decode_noalloc — which lives in that entry point's fixed
+ * array, because it may not allocate one — is ORed into the same answer.  clear != 0 zeroes both words. */
+#define SILVANN_B200_STATUS_TIMEOUT  0x4232544Fu
+#define SILVANN_B200_STATUS_BAD_PAGE 0x80000000u
 int silvann_b200_device_status(uint32_t* word, int clear);
 
 /* Fused split-KV decode of one query position over a contiguous cache — the work of attention_scores +
@@ -322,7 +327,9 @@ int silvann_b200_decode(void* o, float* res, const void* q, const void* k, const
  *   - all calls on a device share that one array: calls that overlap in time on a device race with each other, so
  *     keep them on one stream or otherwise serialised; tickets are re-zeroed on `stream` before each launch;
  *   - the first call on each device looks up the array's device address; make that first call before any stream
- *     capture begins.
+ *     capture begins;
+ *   - a bounded device-side wait that runs out is recorded in a word of the same array (nothing is allocated for it);
+ *     silvann_b200_device_status reads and clears that word together with the device's ordinary status word.
  * Operands and results are silvann_b200_decode's.  Returns 0, 1 (refused: shapes, alignment or size) or 2 (the CUDA
  * runtime refused); a one-line reason is written to `message` (may be null) — this entry keeps no error state. */
 int silvann_b200_decode_noalloc(void* o, float* res, const void* q, const void* k, const void* v, uint64_t q_heads,
@@ -347,7 +354,10 @@ int silvann_b200_plan_decode(silvann_b200_plan* plan, const int32_t* seq_lens, u
 /* What the last plan_decode produced: thread blocks, scratch slots, and the positions summed over sequences. */
 int silvann_b200_plan_info(const silvann_b200_plan* plan, uint32_t* blocks, uint32_t* slots, uint64_t* positions);
 /* q, o [seqs][q_heads][head_dim]; res [seqs][q_heads][head_dim + 2] or null; page_table is a DEVICE array
- * [seqs][table_stride] of int32 page numbers. */
+ * [seqs][table_stride] of int32 page numbers; columns past a sequence's last page may hold anything (-1 by custom)
+ * and are never read.  Refused when the longest planned sequence needs more columns than table_stride.  An entry
+ * inside a sequence's length that names no page of the pool is never used as an address: its positions read as zeros
+ * and SILVANN_B200_STATUS_BAD_PAGE is raised in the device status word. */
 int silvann_b200_paged_decode(silvann_b200_plan* plan, void* o, float* res, const void* q, const void* k_pool,
                               const void* v_pool, uint64_t pool_pages, uint32_t page_positions,
                               const int32_t* page_table, uint32_t table_stride, int dtype, sv_fault* over, void* stream);
@@ -355,9 +365,12 @@ int silvann_b200_paged_decode(silvann_b200_plan* plan, void* o, float* res, cons
 /* Writes each sequence's newest K and V row into its place in the pools: sequence s's row goes to position
  * len_s - 1 (the lengths of the last plan_decode), i.e. page page_table[s][(len_s-1) / page_positions].  k_rows and
  * v_rows are DEVICE arrays [seqs][kv_heads][head_dim] of 16-bit elements.  This is the pool-side half of what the
- * engine's mixer does when it projects k and v "straight into the cache row" (ai_qwen_3 mixer__abi.cuh:229-239). */
+ * engine's mixer does when it projects k and v "straight into the cache row" (ai_qwen_3 mixer__abi.cuh:229-239).
+ * Refused like paged_decode when the table's rows are too short for the plan; a sequence whose entry names no page of
+ * the pool (< 0 or >= pool_pages) is skipped and SILVANN_B200_STATUS_BAD_PAGE is raised in the device status word. */
 int silvann_b200_paged_append(silvann_b200_plan* plan, void* k_pool, void* v_pool, const void* k_rows, const void* v_rows,
-                              uint32_t page_positions, const int32_t* page_table, uint32_t table_stride, void* stream);
+                              uint64_t pool_pages, uint32_t page_positions, const int32_t* page_table, uint32_t table_stride,
+                              void* stream);
 
 /* One query position over a two-tier cache: the oldest host_len positions in pinned host RAM (k_host, v_host are HOST
  * addresses of [host_len][kv_heads][head_dim] planes), the next dev_len positions on the card.  The reference has no
@@ -365,7 +378,9 @@ int silvann_b200_paged_append(silvann_b200_plan* plan, void* k_pool, void* v_poo
  * and this does the same with one more tier: host chunks of `chunk_positions` are copied by cudaMemcpyAsync on a side
  * stream into a ring of `stages` staging buffers while `stream` attends the previous chunk; the card tier is attended
  * first.  o [q_heads][head_dim] and/or res [q_heads][head_dim + 2] (the merged residual, for a further merge across
- * devices).  The tier object owns the staging ring (2 * stages * chunk_positions * kv_heads * head_dim * 2 bytes). */
+ * devices).  The tier object owns the staging ring (2 * stages * chunk_positions * kv_heads * head_dim * 2 bytes);
+ * chunk_positions 0 lets the library size a chunk in bytes (8 MB a plane), which keeps the host link busy at any row
+ * width.  With no host positions the decode kernel writes the answer itself: one launch. */
 typedef struct silvann_b200_tier silvann_b200_tier;
 int silvann_b200_tier_create(silvann_b200_tier** tier, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim, int dtype,
                              uint32_t chunk_positions, uint32_t stages);
@@ -374,6 +389,48 @@ int silvann_b200_tier_decode(silvann_b200_tier* tier, void* o, float* res, const
                              uint64_t host_len, const void* k_dev, const void* v_dev, uint64_t dev_len, sv_fault* over, void* stream);
 /* Bytes copied host to device and chunks staged since the tier was created. */
 int silvann_b200_tier_stats(const silvann_b200_tier* tier, uint64_t* h2d_bytes, uint64_t* chunks);
+
+/* The exchange step of a sharded path among up to 8 cards of one box, as one kernel a card over peer memory.
+ *
+ * It replaces the reference's in-process collective — a `vector_sum` kernel that loads the other cards' partials in place
+ * after host-side marks (engine/src/silicon_families/nvidia_cuda12/overrides/vector.cuh:292-331, driven by
+ * nn__partials__reduce_onto, engine/src/packages/nn/cpu/opcodes/partials__abi.cuh:110-163, with its bounded patience
+ * :42-56) — and carries the residual fold of a KV range split over cards (attention_merge + attention_finish,
+ * engine/src/packages/nn/gpu/kernels/kernels.cuh:1243-1267).  A member PUSHES its piece into a slot of every member's
+ * buffer with plain stores, publishes a generation number beside it, waits (at most wait_ms, 0 = one second) for every
+ * member's number, then combines from its own memory in member order — so every member computes the same bits.
+ *
+ * An exchange object is one member's end: `members` cards, this one is `index` (the order of the fold / the sum);
+ * slot_bytes is the largest piece a member will push.  create allocates the member's buffer on the bound device.  The
+ * members then learn each other's buffers once: between processes (a process a card) each passes the 64-byte handle of
+ * exchange_handle to the others by any means and calls connect_handles with all members' handles in member order (its own
+ * entry is ignored); inside one process (the engine's model: a worker thread a card, peer_access granted) each calls
+ * connect_addresses with the addresses exchange_local answers.  After that every member calls the same exchange entry
+ * points in the same order.  A wait that runs out raises "B2TO" in the device status word and leaves the outputs
+ * unwritten; the object stays usable. */
+typedef struct silvann_b200_exchange silvann_b200_exchange;
+#define SILVANN_B200_EXCHANGE_HANDLE_BYTES 64u
+int silvann_b200_exchange_create(silvann_b200_exchange** exchange, uint32_t members, uint32_t index, uint64_t slot_bytes);
+int silvann_b200_exchange_destroy(silvann_b200_exchange* exchange);
+int silvann_b200_exchange_local(const silvann_b200_exchange* exchange, uint64_t* address, uint64_t* bytes);
+int silvann_b200_exchange_handle(const silvann_b200_exchange* exchange, void* handle, uint32_t handle_bytes);
+int silvann_b200_exchange_connect_handles(silvann_b200_exchange* exchange, const void* handles, uint32_t handle_bytes);
+int silvann_b200_exchange_connect_addresses(silvann_b200_exchange* exchange, const uint64_t* addresses);
+/* res_local [q_heads][head_dim + 2] is this member's residual of its range; o [q_heads][head_dim] and/or res receive the
+ * whole range's answer: ((r_0 + r_1) + r_2) + ... with attention_merge's arithmetic, then attention_finish's. */
+int silvann_b200_exchange_merge_finish(silvann_b200_exchange* exchange, void* o, float* res, const float* res_local, uint64_t q_heads,
+                                       uint64_t head_dim, int dtype, sv_fault* over, uint32_t wait_ms, void* stream);
+/* out[i] = round16(sum over members, in member order, of fp32(partial_member[i])) — vector_sum (kernels.cuh:117-126). */
+int silvann_b200_exchange_vector_sum(silvann_b200_exchange* exchange, void* out, const void* partial, uint64_t n, int dtype,
+                                     sv_fault* over, uint32_t wait_ms, void* stream);
+/* Stands in for an absent member where there are fewer cards than members (a one-card walk of a many-card plan): puts
+ * `data` where that member's push of the NEXT exchange would land and sets its flags.  Same stream as the exchange. */
+int silvann_b200_exchange_deposit(silvann_b200_exchange* exchange, uint32_t member, const void* data, uint64_t bytes, void* stream);
+/* silvann_b200_tier_decode for a member of a range split: the member's residual over its two tiers, then the exchange,
+ * as one call. */
+int silvann_b200_tier_decode_exchange(silvann_b200_tier* tier, silvann_b200_exchange* exchange, void* o, float* res, const void* q,
+                                      const void* k_host, const void* v_host, uint64_t host_len, const void* k_dev, const void* v_dev,
+                                      uint64_t dev_len, sv_fault* over, uint32_t wait_ms, void* stream);
 
 /* Causal grouped-query prefill in one kernel — attention_causal_scores_grouped + attention_causal_softmax +
  * attention_causal_mix (kernels.cuh:1028-1081, 2051-2060): row r is position first + r and attends cache rows
@@ -385,9 +442,12 @@ int silvann_b200_prefill(void* o, float* res, const void* q, const void* k, cons
 
 /* Gated DeltaNet over `rows` positions of `seqs` independent sequences (deltanet_steps_gate, kernels.cuh:650-718,
  * 2131-2165, with a dtype and a batch).  S [seqs][v_heads][d][d] fp32 in place; conved [seqs][rows][(2·k_heads +
- * v_heads)·d]; z, out [seqs][rows][v_heads·d]; beta, g [seqs][rows][v_heads]; w [d]. */
+ * v_heads)·d]; z, out [seqs][rows][v_heads·d]; beta, g [seqs][rows][v_heads]; w [d].  `readout` (may be null) receives
+ * [seqs][rows][v_heads·d] fp32: every position's read-out S^T qs as summed, before the first of the two roundings to
+ * 16 bits the door applies (kernels.cuh:677-688) — what a caller compares when it wants the recurrence's own error
+ * rather than the rounding's. */
 int silvann_b200_deltanet(float* S, const void* conved, const void* z, const void* beta, const void* g, const void* w,
-                          void* out, uint64_t k_heads, uint64_t v_heads, uint64_t head_dim, uint64_t rows,
+                          void* out, float* readout, uint64_t k_heads, uint64_t v_heads, uint64_t head_dim, uint64_t rows,
                           uint32_t seqs, uint32_t gate, int dtype, sv_fault* over, void* stream);
 
 #ifdef __cplusplus

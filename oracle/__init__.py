@@ -76,6 +76,7 @@ class Port:
             "oracle_attention_causal_mix": [vp, vp, vp, u64, u64, u64, u64, u64, i32, vp],
             "oracle_prefill": [vp, vp, vp, vp, vp, u64, u64, u64, u64, u64, i32, vp],
             "oracle_deltanet_steps": [vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, C.c_uint, i32, vp],
+            "oracle_deltanet_steps_readout": [vp, vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, C.c_uint, i32, vp],
             "oracle_attention_scores_grouped_rows": [vp, u64, vp, u64, vp, u64, vp, u64, u64, u64, u64, i32],
             "oracle_attention_softmax_lens": [vp, u64, vp, u64, u64],
             "oracle_attention_softmax_sink": [vp, vp, u64, u64],
@@ -168,11 +169,13 @@ class Port:
         return o, o32
 
     # Gated DeltaNet ------------------------------------------------------------------------------------------------
-    def deltanet(self, S, conved, z, beta, g, w, kh, vh, d, rows, gate=0, dtype=FP16):
-        """Updates S in place; answers out [rows][vh*d] bits."""
+    def deltanet(self, S, conved, z, beta, g, w, kh, vh, d, rows, gate=0, dtype=FP16, readout=None):
+        """Updates S in place; answers out [rows][vh*d] bits.  `readout`: a float32 [rows][vh*d] array that receives every
+        position's read-out before its first rounding to 16 bits."""
         out = np.empty((rows, vh * d), np.uint16)
         over = np.zeros(1, np.uint32)
-        self.lib.oracle_deltanet_steps(_p(S), _p(conved), _p(z), _p(beta), _p(g), _p(w), _p(out), kh, vh, d, rows, gate, dtype, _p(over))
+        self.lib.oracle_deltanet_steps_readout(_p(S), _p(conved), _p(z), _p(beta), _p(g), _p(w), _p(out), None if readout is None else _p(readout),
+                                               kh, vh, d, rows, gate, dtype, _p(over))
         return out
 
 
@@ -520,6 +523,32 @@ def indexer(impl, x, lw, lb, keys, gates, ape, q, w, dim, kpool, heads, k, len0,
 _port = None
 _reference = None
 _reference_tried = False
+
+
+class OnCard:
+    """This family on a card, worded as oracle/__init__.py's helpers word an implementation: `ptr(array)` is the address
+    of the array's copy in device memory (made at first sight), `nn` the family's doors, `wait()` the family's
+    compute_completed followed by every copy read back into its array — so a helper written for host pointers drives the
+    card's doors unchanged."""
+
+    def __init__(self, torch, fam):
+        self.torch, self.fam, self.nn, self.over = torch, fam, fam.nn, None
+        self.held = {}
+
+    def ptr(self, a):
+        if a is None:
+            return None
+        key = id(a)
+        if key not in self.held:
+            assert a.flags["C_CONTIGUOUS"]
+            self.held[key] = (a, self.torch.from_numpy(a.view(np.uint8).reshape(-1)).cuda())
+        return self.held[key][1].data_ptr()
+
+    def wait(self):
+        assert self.fam.sys.compute_completed(), "a door refused its launch"
+        for a, t in self.held.values():
+            if a.flags["WRITEABLE"] and a.size:
+                a.view(np.uint8).reshape(-1)[:] = t.cpu().numpy()
 
 
 def port() -> Port:

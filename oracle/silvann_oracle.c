@@ -205,24 +205,36 @@ void oracle_prefill(uint16_t* o, float* o32, const uint16_t* q, const uint16_t* 
 
 /* ---- Gated DeltaNet -------------------------------------------------------------------------------------------------- */
 
-/* One value head, one position (nn__deltanet__zzprivate_step_head, kernels.cuh:650-691). */
+/* One value head, one position (nn__deltanet__zzprivate_step_head, kernels.cuh:650-691).  The reference walks a column j
+ * of the state at a time (its inner loops run over the key index i); here i is the outer loop and j the inner one so that
+ * memory is walked with unit stride — every sum still receives its terms in the order i = 0, 1, ..., so each result is the
+ * same float.  `readout` (may be null) receives the read-out of the position before its first rounding to 16 bits. */
 static void deltanet_head(float* S, const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* z, float beta, float g,
-                          const uint16_t* w, uint16_t* out, uint64_t d, unsigned gate, int dt, int* hit) {
+                          const uint16_t* w, uint16_t* out, float* readout, uint64_t d, unsigned gate, int dt, int* hit) {
     float qq = 0.0f, kk = 0.0f;
     for (uint64_t i = 0; i < d; ++i) { const float qi = ld16(q[i], dt), ki = ld16(k[i], dt); qq += qi * qi; kk += ki * ki; }
     const float inv_q = 1.0f / sqrtf(qq + 1e-6f) / sqrtf((float)d), inv_k = 1.0f / sqrtf(kk + 1e-6f), decay = expf(g);
+    float kv[512], o[512], delta[512];
+    for (uint64_t j = 0; j < d; ++j) { kv[j] = 0.0f; o[j] = 0.0f; }
+    for (uint64_t i = 0; i < d; ++i) {
+        const float ki = ld16(k[i], dt);
+        const float* row = S + i * d;
+        for (uint64_t j = 0; j < d; ++j) kv[j] += row[j] * ki;
+    }
+    for (uint64_t j = 0; j < d; ++j) delta[j] = (ld16(v[j], dt) - decay * kv[j] * inv_k) * beta;
+    for (uint64_t i = 0; i < d; ++i) {
+        const float kn = ld16(k[i], dt) * inv_k, qi = ld16(q[i], dt);
+        float* row = S + i * d;
+        for (uint64_t j = 0; j < d; ++j) {
+            const float s = decay * row[j] + kn * delta[j];
+            row[j] = s;
+            o[j] += s * qi;
+        }
+    }
     float oo = 0.0f;
     for (uint64_t j = 0; j < d; ++j) {
-        float kv = 0.0f;
-        for (uint64_t i = 0; i < d; ++i) kv += S[i * d + j] * ld16(k[i], dt);
-        const float delta = (ld16(v[j], dt) - decay * kv * inv_k) * beta;
-        float o = 0.0f;
-        for (uint64_t i = 0; i < d; ++i) {
-            const float s = decay * S[i * d + j] + ld16(k[i], dt) * inv_k * delta;
-            S[i * d + j] = s;
-            o += s * ld16(q[i], dt);
-        }
-        out[j] = st16(o * inv_q, dt, hit);                 /* the read-out is rounded before its norm */
+        if (readout) readout[j] = o[j] * inv_q;
+        out[j] = st16(o[j] * inv_q, dt, hit);              /* the read-out is rounded before its norm */
         const float oj = ld16(out[j], dt);
         oo += oj * oj;
     }
@@ -234,11 +246,13 @@ static void deltanet_head(float* S, const uint16_t* q, const uint16_t* k, const 
     }
 }
 /* deltanet_steps_gate (kernels.cuh:2131-2165); rows = 1 and gate = 0 is deltanet_step (:707-718).
- * conved row = q heads, k heads, v heads; value head h reads key head h / (vh / kh). */
-void oracle_deltanet_steps(float* S, const uint16_t* conved, const uint16_t* z, const uint16_t* beta, const uint16_t* g, const uint16_t* w,
-                           uint16_t* out, uint64_t kh, uint64_t vh, uint64_t d, uint64_t rows, unsigned gate, int dt, unsigned* over) {
+ * conved row = q heads, k heads, v heads; value head h reads key head h / (vh / kh).  head_dim <= 512.
+ * `readout`: null, or [rows][vh*d] fp32 (see deltanet_head). */
+void oracle_deltanet_steps_readout(float* S, const uint16_t* conved, const uint16_t* z, const uint16_t* beta, const uint16_t* g, const uint16_t* w,
+                                   uint16_t* out, float* readout, uint64_t kh, uint64_t vh, uint64_t d, uint64_t rows, unsigned gate, int dt, unsigned* over) {
     const uint64_t rep = vh / kh, ch = (2 * kh + vh) * d, vd = vh * d;
     int hit = 0;
+    if (d > 512) return;
 #pragma omp parallel for schedule(static) reduction(| : hit)
     for (int64_t h = 0; h < (int64_t)vh; ++h)
         for (uint64_t t = 0; t < rows; ++t) {
@@ -246,10 +260,14 @@ void oracle_deltanet_steps(float* S, const uint16_t* conved, const uint16_t* z, 
             int one = 0;
             deltanet_head(S + (uint64_t)h * d * d, c + ((uint64_t)h / rep) * d, c + kh * d + ((uint64_t)h / rep) * d, c + 2 * kh * d + (uint64_t)h * d,
                           z + t * vd + (uint64_t)h * d, ld16(beta[t * vh + (uint64_t)h], dt), ld16(g[t * vh + (uint64_t)h], dt), w,
-                          out + t * vd + (uint64_t)h * d, d, gate, dt, &one);
+                          out + t * vd + (uint64_t)h * d, readout ? readout + t * vd + (uint64_t)h * d : 0, d, gate, dt, &one);
             hit |= one;
         }
     if (hit && over) *over = ORACLE_FAULT_OVERFLOW;
+}
+void oracle_deltanet_steps(float* S, const uint16_t* conved, const uint16_t* z, const uint16_t* beta, const uint16_t* g, const uint16_t* w,
+                           uint16_t* out, uint64_t kh, uint64_t vh, uint64_t d, uint64_t rows, unsigned gate, int dt, unsigned* over) {
+    oracle_deltanet_steps_readout(S, conved, z, beta, g, w, out, 0, kh, vh, d, rows, gate, dt, over);
 }
 
 /* vector_sum: parts added in the order given, one rounding (kernels.cuh:117-126) */

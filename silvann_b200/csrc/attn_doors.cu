@@ -11,6 +11,7 @@
  * summation order. */
 #include "common.cuh"
 #include "kernels.h"
+#include "residual.cuh"
 
 namespace sv {
 
@@ -117,12 +118,11 @@ __global__ void __launch_bounds__(128) merge_kernel(float* into, const float* a,
     const uint64_t w = d + 2;
     for (uint64_t h = blockIdx.x; h < qh; h += gridDim.x) {
         /* every thread reads the head's four scalars before any thread writes them: `into` may be `a` or `b` */
-        const float ma = a[h * w], la = a[h * w + 1], mb = b[h * w], lb = b[h * w + 1];
-        const float m = ma > mb ? ma : mb;
-        const float fa = expf(ma - m), fb = expf(mb - m);
+        float m = a[h * w], l = a[h * w + 1], fa, fb;
+        merge_scalars(m, l, b[h * w], b[h * w + 1], fa, fb);
         __syncthreads();
-        for (uint64_t e = threadIdx.x; e < d; e += blockDim.x) into[h * w + 2 + e] = a[h * w + 2 + e] * fa + b[h * w + 2 + e] * fb;
-        if (threadIdx.x == 0) { into[h * w] = m; into[h * w + 1] = la * fa + lb * fb; }
+        for (uint64_t e = threadIdx.x; e < d; e += blockDim.x) into[h * w + 2 + e] = merge_element(a[h * w + 2 + e], fa, b[h * w + 2 + e], fb);
+        if (threadIdx.x == 0) { into[h * w] = m; into[h * w + 1] = l; }
         __syncthreads();
     }
 }

@@ -16,6 +16,7 @@
 
 #define SV_FAULT_OVERFLOW 0x4E504F56u   /* "NPOV" — engine/src/packages/nn/contracts/objects/primitives.cuh:57 */
 #define SV_STATUS_TIMEOUT 0x4232544Fu   /* "B2TO" — a bounded device-side wait gave up */
+#define SV_STATUS_BAD_PAGE 0x80000000u  /* a page-table entry inside a sequence's length named no page of the pool (a bit the code above leaves clear) */
 
 /* How long a device-side wait may spin before giving up: tries of mbarrier.try_wait (each suspends for a
  * hardware-chosen slice) — in the order of a second at worst, far beyond any healthy TMA or MMA latency. */

@@ -18,6 +18,8 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "tensormap.cuh"
+#include <atomic>
+#include <mutex>
 #include <stdio.h>
 #include <string.h>
 
@@ -46,24 +48,13 @@ struct DecodeParams {
     const int32_t* seq_lens;
     unsigned int* over;
     unsigned int* status;
-    uint32_t table_stride, page_pos;
+    uint32_t table_stride, page_pos, pool_pages;
     uint32_t q_heads, kv_heads, group;
     uint32_t length, nsplit, head_blocks, heads_per_block;
     uint32_t slot_floats;
     float scale_log2;
 };
 
-#ifdef SV_DECODE_TRACE
-/* Development aid, compiled only on request: every block leaves %globaltimer stamps (ns) of its phases here. */
-__device__ unsigned long long g_dec_trace[256 * 16];
-__device__ __forceinline__ unsigned long long sv_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define SV_DTR(k) do { if (threadIdx.x == 0 && blockIdx.x < 256) g_dec_trace[blockIdx.x * 16 + (k)] = sv_gtime(); } while (0)
-extern "C" __attribute__((visibility("default"))) int sv_decode_trace_read(unsigned long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_dec_trace, sizeof(unsigned long long) * 256 * 16);
-}
-#else
-#define SV_DTR(k) do {} while (0)
-#endif
 
 template <int D, int DT, int NHT>
 __global__ void __launch_bounds__((DecodeCfg<D>::NW + 1) * 32, 1)
@@ -87,7 +78,6 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     uint32_t* ticket_s = (uint32_t*)abort_flag + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    SV_DTR(0);
 
     /* ---- which work is this block's ---- */
     int seq, kvh, head0, heads, tile_begin, tile_end, split, nsplit, slot_base, slot_stride, ticket;
@@ -135,7 +125,13 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
                 if (it >= Cfg::STAGES && !mbar_wait(&empty[s], ((it / Cfg::STAGES) - 1) & 1, abort_flag, P.status)) break;
                 const int pos0 = (tile_begin + it) * BT;
                 int32_t y = pos0;
-                if (pt) y = pt[pos0 / (int)P.page_pos] * (int)P.page_pos + pos0 % (int)P.page_pos;
+                if (pt) {
+                    /* an entry outside the pool (the -1 padding, a stale table) is never made into an address: the tile is
+                     * asked for past the pool's last row, where TMA answers zeros, and the status word says so */
+                    const int32_t page = pt[pos0 / (int)P.page_pos];
+                    if (page < 0 || page >= (int32_t)P.pool_pages) { y = (int32_t)P.pool_pages * (int)P.page_pos; if (P.status) atomicOr(P.status, SV_STATUS_BAD_PAGE); }
+                    else y = page * (int)P.page_pos + pos0 % (int)P.page_pos;
+                }
                 uint8_t* st = stage_base + s * Cfg::STAGE_BYTES;
                 mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
 #pragma unroll
@@ -156,7 +152,6 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
             *reinterpret_cast<uint4*>(q_base + (j / 8) * (HPB * 128) + swz128(r, j % 8)) = val;
         }
         asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
-        SV_DTR(1);
 
         uint32_t qf[QREG ? NHT : 1][QREG ? KS : 1][2];
         const uint32_t q_u32 = smem_u32(q_base);
@@ -178,7 +173,6 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
         for (int it = 0; it < nt; ++it) {
             const int s = it % Cfg::STAGES;
             if (!mbar_wait(&full[s], (it / Cfg::STAGES) & 1, abort_flag, P.status)) break;
-            if (it == 0) SV_DTR(2);
             const uint32_t kst = smem_u32(stage_base + s * Cfg::STAGE_BYTES), vst = kst + Cfg::K_BYTES;
             const int pos0 = (tile_begin + it) * BT + warp * 16;
 
@@ -268,6 +262,17 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
 
     /* ---- fold the four warps' partials through shared memory (the stage ring is free now) ---- */
     __syncthreads();
+    if (*abort_flag != 0u) {
+        /* a wait gave up: copies this block asked for may still be on their way into the ring, so one thread gives every
+         * stage a bounded chance to land before the ring is written over and the block leaves (the answer is not
+         * meaningful any more — the status word says so — but the arrival protocol below is kept whole) */
+        if (tid == 0)
+            for (int s = 0; s < Cfg::STAGES && s < nt; ++s) {
+                const int last = (nt - 1 - s) / Cfg::STAGES;            /* the last use of stage s */
+                for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(&full[s], last & 1); ++i) {}
+            }
+        __syncthreads();
+    }
     float* wm = (float*)stage_base;                   /* [NW][HPB] */
     float* wl = wm + NW * HPB;                        /* [NW][HPB] */
     float* wo = wl + NW * HPB;                        /* [NW][HPB][D] */
@@ -290,7 +295,6 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
             }
         }
     }
-    SV_DTR(3);
     __syncthreads();
 
     const uint32_t SF = P.slot_floats;                /* floats per head in scratch: D + 2 */
@@ -328,12 +332,10 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     }
 
     /* ---- arrive; the last block of the group merges all splits in split order ---- */
-    SV_DTR(4);
     __threadfence();
     __syncthreads();
     if (tid == 0) *ticket_s = atomicAdd(&P.tickets[ticket], 1u);
     __syncthreads();
-    SV_DTR(5);
     if (*ticket_s != (uint32_t)(nsplit - 1)) return;
     __threadfence();
     /* The block is alone with its group by now and bound by trips to L2, so everything it needs is asked for at once:
@@ -395,7 +397,6 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
         if (lane == 0) { mh[h] = m; lh[h] = l; }
     }
     __syncthreads();
-    SV_DTR(7);
     if (one_pass) {
         if (tid < runs * e4n) {
             const float* f = fac + (my_e4 / (D / 4)) * nsplit;
@@ -443,31 +444,36 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
         }
     }
     if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
-    SV_DTR(6);
     if (tid == 0) P.tickets[ticket] = 0u;             /* ready for the next launch */
 }
 
 /* ---------------------------------------------------------------------------------------------------------- */
 /* host side                                                                                                    */
 
+/* Per-device state made on first use.  Doors are called from up to eight worker threads at once, a thread a device,
+ * through the one table, so first use is decided under a lock; after that the values never change. */
 static constexpr int DEVICES_MAX = 64;
+static std::mutex g_once;
 static DecodeScratch g_scratch[DEVICES_MAX];
 static unsigned int* g_status[DEVICES_MAX];
-static uint32_t g_sms[DEVICES_MAX];
+static std::atomic<uint32_t> g_sms[DEVICES_MAX];
 
 uint32_t device_sm_count() {
     int d = 0;
     if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= DEVICES_MAX) return 148u;
-    if (g_sms[d] == 0u) {
-        int n = 0;
-        g_sms[d] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) == cudaSuccess && n > 0) ? (uint32_t)n : 148u;
+    uint32_t n = g_sms[d].load(std::memory_order_relaxed);
+    if (n == 0u) {
+        int v = 0;
+        n = (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, d) == cudaSuccess && v > 0) ? (uint32_t)v : 148u;
+        g_sms[d].store(n, std::memory_order_relaxed);
     }
-    return g_sms[d];
+    return n;
 }
 
 unsigned int* device_status_word() {
     int d = 0;
     if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= DEVICES_MAX) return nullptr;
+    std::lock_guard<std::mutex> hold(g_once);
     if (!g_status[d]) {
         unsigned int* p = nullptr;
         if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
@@ -482,6 +488,7 @@ cudaError_t decode_device_scratch(DecodeScratch* out) {
     cudaError_t e = cudaGetDevice(&d);
     if (e != cudaSuccess) return e;
     if (d < 0 || d >= DEVICES_MAX) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> hold(g_once);
     DecodeScratch& s = g_scratch[d];
     if (!s.partials) {
         const uint32_t slot_floats = 256 + 2;
@@ -532,12 +539,12 @@ static cudaError_t launch_one(const CUtensorMap& km, const CUtensorMap& vm, cons
                               cudaStream_t st) {
     using Cfg = DecodeCfg<D>;
     const size_t smem = 1024 + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES + Cfg::BOXES * 8 * NHT * 128 + 2 * Cfg::STAGES * 8 + 64;
-    static bool attr_set[DEVICES_MAX] = {};
+    static std::atomic<bool> attr_set[DEVICES_MAX];       /* setting the attribute twice is harmless; the flag only saves the call */
     int d = 0; cudaGetDevice(&d);
-    if (d >= 0 && d < DEVICES_MAX && !attr_set[d]) {
+    if (d >= 0 && d < DEVICES_MAX && !attr_set[d].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(decode_kernel<D, DT, NHT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        attr_set[d] = true;
+        attr_set[d].store(true, std::memory_order_release);
     }
     decode_kernel<D, DT, NHT><<<blocks, (Cfg::NW + 1) * 32, smem, st>>>(km, vm, P);
     note_launch(1);
@@ -557,7 +564,7 @@ cudaError_t decode_launch(const DecodeCall& c) {
     P.o = c.o; P.res = c.res; P.q = (const uint16_t*)c.q;
     P.partials = c.scratch.partials; P.tickets = c.scratch.tickets; P.items = c.items;
     P.page_table = c.page_table; P.seq_lens = c.seq_lens; P.over = c.over; P.status = device_status_word();
-    P.table_stride = c.table_stride; P.page_pos = c.page_pos;
+    P.table_stride = c.table_stride; P.page_pos = c.page_pos; P.pool_pages = c.page_pos ? (uint32_t)(c.kv_rows / c.page_pos) : 0u;
     P.q_heads = c.q_heads; P.kv_heads = c.kv_heads; P.group = group;
     P.length = c.length; P.head_blocks = hb; P.heads_per_block = hpb;
     P.slot_floats = c.head_dim + 2u;
@@ -629,7 +636,7 @@ namespace sv {
 
 static __device__ __align__(256) float g_static_scratch[SV_STATIC_FLOATS + SV_STATIC_TICKETS + 64];
 
-struct StaticScratch { float* base; bool ready; };
+struct StaticScratch { float* base; std::atomic<bool> ready; };
 static StaticScratch g_static[DEVICES_MAX];
 
 /* The device address of the array on the current device, looked up once per device. */
@@ -638,14 +645,29 @@ static cudaError_t static_scratch_address(float** out) {
     cudaError_t e = cudaGetDevice(&d);
     if (e != cudaSuccess) return e;
     if (d < 0 || d >= DEVICES_MAX) return cudaErrorInvalidDevice;
-    if (!g_static[d].ready) {
+    if (!g_static[d].ready.load(std::memory_order_acquire)) {
         void* ptr = nullptr;
         if ((e = cudaGetSymbolAddress(&ptr, g_static_scratch)) != cudaSuccess) return e;
-        g_static[d].base = (float*)ptr;
-        g_static[d].ready = true;
+        g_static[d].base = (float*)ptr;                    /* two threads racing here write the same address */
+        g_static[d].ready.store(true, std::memory_order_release);
     }
     *out = g_static[d].base;
     return cudaSuccess;
+}
+
+/* The allocation-free decode keeps its time-out word inside the fixed array (it may not allocate one).  This reads it
+ * for silvann_b200_device_status, which ORs it into its answer; a device on which that entry point has never run has
+ * no such word yet and answers 0.  The caller has already waited for the device's default queue. */
+cudaError_t static_status_take(unsigned int* word, int clear) {
+    *word = 0u;
+    int d = 0;
+    cudaError_t e = cudaGetDevice(&d);
+    if (e != cudaSuccess) return e;
+    if (d < 0 || d >= DEVICES_MAX || !g_static[d].ready.load(std::memory_order_acquire)) return cudaSuccess;
+    unsigned int* at = (unsigned int*)(g_static[d].base + SV_STATIC_FLOATS) + SV_STATIC_TICKETS;
+    if ((e = cudaMemcpy(word, at, sizeof *word, cudaMemcpyDeviceToHost)) != cudaSuccess) return e;
+    if (clear && *word != 0u) e = cudaMemset(at, 0, sizeof *word);
+    return e;
 }
 
 /* 0 ok · 1 the shapes are outside the kernel's fit · 2 the work does not fit the fixed scratch · 3 the runtime refused;
@@ -687,7 +709,7 @@ int decode_launch_static(const DecodeCall& c0, uint32_t* detail) {
     P.o = c.o; P.res = c.res; P.q = (const uint16_t*)c.q;
     P.partials = base; P.tickets = tickets; P.items = nullptr; P.page_table = nullptr; P.seq_lens = nullptr;
     P.over = c.over; P.status = status;
-    P.table_stride = 0; P.page_pos = 0;
+    P.table_stride = 0; P.page_pos = 0; P.pool_pages = 0;
     P.q_heads = c.q_heads; P.kv_heads = c.kv_heads; P.group = group;
     P.length = c.length; P.nsplit = ns; P.head_blocks = hb; P.heads_per_block = hpb;
     P.slot_floats = c.head_dim + 2u;

@@ -21,6 +21,8 @@
 #include "common.cuh"
 #include "kernels_deltanet.h"
 #include "kernels.h"
+#include <atomic>
+#include <mutex>
 #include <stdlib.h>
 
 namespace sv {
@@ -33,6 +35,7 @@ struct DeltaParams {
     float* S;
     const uint16_t *conved, *z, *beta, *g, *w;
     uint16_t* out;
+    float* readout;            /* null, or the fp32 read-out of every position before its first rounding */
     float* ss;                 /* scratch [seqs][rows][v_heads][d/32] */
     const float4* sc;          /* with PRE: per (seq, row, value head) {1/|q|/sqrt(d), 1/|k|, e^g, beta}, made by the scalars kernel */
     unsigned int* over;
@@ -41,17 +44,6 @@ struct DeltaParams {
     int gate;
 };
 
-#ifdef SV_DN_TRACE
-/* Development aid, compiled only on request: every block leaves %globaltimer stamps (ns) of its phases here. */
-__device__ unsigned long long g_dn_trace[256 * 8];
-__device__ __forceinline__ unsigned long long sv_dn_time() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define SV_NTR(k) do { if (threadIdx.x == 0 && blockIdx.x < 256) g_dn_trace[blockIdx.x * 8 + (k)] = sv_dn_time(); } while (0)
-extern "C" __attribute__((visibility("default"))) int sv_dn_trace_read(unsigned long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_dn_trace, sizeof(unsigned long long) * 256 * 8);
-}
-#else
-#define SV_NTR(k) do {} while (0)
-#endif
 
 /* the blocks of a head as a thread-block cluster: the two halves of a barrier over all of them, and a float written into a peer's shared memory */
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
@@ -69,7 +61,6 @@ __device__ __forceinline__ void st_cluster_f32(float* local, uint32_t rank, floa
  * has to wait for the others before it leaves.  The sums are added in block order, as the norm kernel adds them. */
 template <int D, int DT, bool PRE, bool FUSE>
 __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaParams P) {
-    SV_NTR(0);
     using E = Elem<DT>;
     constexpr int CB = D / DN_COLS;            /* column blocks per head */
     constexpr int R = D / DN_RG;               /* keys per thread */
@@ -115,7 +106,6 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
         n_qk[u] = (P.rows > 1 && i < 2 * D) ? qk_src(cv + ch, i) : (uint16_t)0;
     }
     __syncthreads();
-    SV_NTR(1);
 
     const float inv_sqrt_d = 1.0f / sqrtf((float)D);
     bool hit = false;
@@ -163,7 +153,6 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
         red1[rg][c] = kvp;
         if (!PRE && c == 0) { red1[rg][DN_COLS] = qq; red1[rg][DN_COLS + 1] = kk; }
         __syncthreads();
-    SV_NTR(2);
         float kvsum = 0.f, qsum = 0.f, ksum = 0.f;
 #pragma unroll
         for (int r = 0; r < DN_RG; ++r) { kvsum += red1[r][c]; if (!PRE) { qsum += red1[r][DN_COLS]; ksum += red1[r][DN_COLS + 1]; } }
@@ -183,11 +172,11 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
         }
         red2[rg][c] = (op4[0] + op4[1]) + (op4[2] + op4[3]);
         __syncthreads();
-    SV_NTR(3);
         uint16_t oh = 0;
         if (rg == 0) {
             const float o = (red2[0][c] + red2[1][c] + red2[2][c] + red2[3][c]) * inv_q;
             oh = E::from_float(o, hit);
+            if (P.readout) P.readout[((uint64_t)b * P.rows + t) * vd + (uint64_t)h * D + j] = o;
             float sq = E::to_float(oh); sq *= sq;
             for (int x = 16; x > 0; x >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, x);
             if (!FUSE) {
@@ -201,7 +190,6 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
 #pragma unroll
             for (int i = 0; i < R; ++i) Sh[(uint64_t)(rg * R + i) * D + j] = s[i];
             cluster_wait();
-    SV_NTR(4);
             if (rg == 0) {
                 float sum = 0.f;
 #pragma unroll
@@ -224,8 +212,6 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
         for (int i = 0; i < R; ++i) Sh[(uint64_t)(rg * R + i) * D + j] = s[i];
     }
     if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
-    SV_NTR(5);
-    SV_NTR(6);
 }
 
 /* The per-position scalars of a run of positions, off the serial path: a warp a (sequence, position, key head) folds
@@ -308,6 +294,8 @@ static cudaError_t ss_scratch(size_t floats, float** out) {
     cudaError_t e = cudaGetDevice(&d);
     if (e != cudaSuccess) return e;
     if (d < 0 || d >= 64) return cudaErrorInvalidDevice;
+    static std::mutex lock;                        /* a device's worker thread is the only grower of its block, but first use is not ordered */
+    std::lock_guard<std::mutex> hold(lock);
     if (g_ss_floats[d] < floats) {
         /* grow-only; the old block is released once the queue that may still read it has drained */
         if (g_ss[d]) { if ((e = cudaDeviceSynchronize()) != cudaSuccess) return e; cudaFree(g_ss[d]); g_ss[d] = nullptr; g_ss_floats[d] = 0; }
@@ -333,7 +321,7 @@ static unsigned fuse_blocks_max() {
 template <int D, int DT>
 static cudaError_t launch_dn(const DeltaCall& c, float* ss) {
     DeltaParams P;
-    P.S = c.S; P.conved = c.conved; P.z = c.z; P.beta = c.beta; P.g = c.g; P.w = c.w; P.out = c.out; P.ss = ss; P.over = c.over;
+    P.S = c.S; P.conved = c.conved; P.z = c.z; P.beta = c.beta; P.g = c.g; P.w = c.w; P.out = c.out; P.readout = c.readout; P.ss = ss; P.over = c.over;
     P.k_heads = c.k_heads; P.v_heads = c.v_heads; P.seqs = c.seqs; P.rows = c.rows; P.gate = c.gate;
     const unsigned blocks = c.seqs * c.v_heads * (D / DN_COLS);
     cudaError_t e;

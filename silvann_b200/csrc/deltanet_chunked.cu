@@ -19,6 +19,7 @@
  * The read-out leaves here rounded to 16 bits with each block's sum of squares beside it, exactly as the recurrent
  * kernel leaves it, and the same norm-and-gate kernel finishes it. */
 #include "common.cuh"
+#include <atomic>
 #include "kernels.h"
 #include "kernels_deltanet.h"
 
@@ -34,6 +35,7 @@ struct ChunkParams {
     float* S;
     const uint16_t *conved, *beta, *g;
     uint16_t* out;
+    float* readout;
     float* ss;
     float* prep;
     unsigned int* over;
@@ -400,6 +402,10 @@ __global__ void __launch_bounds__(256, 1) deltanet_chunk_kernel(const ChunkParam
                     if (t < n) {
                         uint16_t* orow = P.out + ((uint64_t)b * P.rows + t0 + t) * vd + (uint64_t)h * D + j0 + c1 + 8 * j + 2 * t4;
                         *reinterpret_cast<uint32_t*>(orow) = (uint32_t)w0 | ((uint32_t)w1 << 16);
+                        if (P.readout) {
+                            float* frow = P.readout + ((uint64_t)b * P.rows + t0 + t) * vd + (uint64_t)h * D + j0 + c1 + 8 * j + 2 * t4;
+                            frow[0] = ao[j][2 * hh]; frow[1] = ao[j][2 * hh + 1];
+                        }
                     }
                 }
                 sq += __shfl_xor_sync(0xffffffffu, sq, 1);
@@ -468,16 +474,16 @@ static cudaError_t launch_chunked(const DeltaCall& c, float* ss, float* prep) {
     constexpr int LD = D + 4;
     const size_t smem1 = (size_t)(2 * CH * LD + 2 * CH * (CH + 1) + 6 * CH) * sizeof(float);
     const size_t smem2 = ChunkSmem<D>::TOTAL;
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64];
     int dev = 0; cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(deltanet_prep_kernel<D, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(deltanet_chunk_kernel<D, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
         if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     ChunkParams P;
-    P.S = c.S; P.conved = c.conved; P.beta = c.beta; P.g = c.g; P.out = c.out; P.ss = ss; P.prep = prep; P.over = c.over;
+    P.S = c.S; P.conved = c.conved; P.beta = c.beta; P.g = c.g; P.out = c.out; P.readout = c.readout; P.ss = ss; P.prep = prep; P.over = c.over;
     P.k_heads = c.k_heads; P.v_heads = c.v_heads; P.seqs = c.seqs; P.rows = c.rows;
     for (uint64_t row0 = 0; row0 < c.rows; row0 += 2048) {
         P.row0 = row0; P.seg_rows = (c.rows - row0) < 2048 ? (c.rows - row0) : 2048; P.chunks = (uint32_t)((P.seg_rows + CH - 1) / CH);

@@ -54,7 +54,9 @@ SV_EXPORT int silvann_b200_device_status(uint32_t* word, int clear) {
     unsigned int w = 0;
     if ((e = cudaMemcpy(&w, dev, sizeof w, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail("device_status: read", e);
     if (clear && w != 0u && (e = cudaMemset(dev, 0, sizeof w)) != cudaSuccess) return cuda_fail("device_status: clear", e);
-    *word = w;
+    unsigned int w_static = 0;                    /* silvann_b200_decode_noalloc keeps its own word in its fixed array */
+    if ((e = sv::static_status_take(&w_static, clear)) != cudaSuccess) return cuda_fail("device_status: the fixed scratch's word", e);
+    *word = w | w_static;
     return SILVANN_B200_OK;
 }
 
@@ -106,6 +108,7 @@ struct silvann_b200_plan {
     cudaEvent_t uploaded;           /* the last upload has left the pinned buffers */
     uint32_t n_items, n_slots, n_tickets, seqs, q_heads, kv_heads, head_dim;
     uint64_t positions;
+    uint32_t max_len;               /* the longest sequence of the last plan_decode: bounds the page-table columns a launch reads */
     bool ready;
 };
 
@@ -147,10 +150,12 @@ SV_EXPORT int silvann_b200_plan_decode(silvann_b200_plan* p, const int32_t* seq_
     const uint32_t group = q_heads / kv_heads, hpb = group <= 8 ? 8u : 16u, hb = (group + hpb - 1) / hpb, lanes = kv_heads * hb;
     const uint32_t TILE = sv::decode_tile_positions(head_dim);
     uint64_t tiles_total = 0, positions = 0;
+    uint32_t max_len = 0;
     for (uint32_t s = 0; s < seqs; ++s) {
         if (seq_lens[s] <= 0) return fail(SILVANN_B200_E_ARGUMENT, "plan_decode: sequence %u has length %d", s, seq_lens[s]);
         tiles_total += ((uint64_t)seq_lens[s] + TILE - 1) / TILE;
         positions += (uint64_t)seq_lens[s];
+        max_len = std::max(max_len, (uint32_t)seq_lens[s]);
     }
     if (blocks_target == 0) blocks_target = sv::device_sm_count() * 4u;
     uint64_t chunk = (tiles_total * lanes + blocks_target - 1) / blocks_target;
@@ -233,7 +238,7 @@ SV_EXPORT int silvann_b200_plan_decode(silvann_b200_plan* p, const int32_t* seq_
     if ((e = cudaMemcpyAsync(p->lens_dev, p->lens_host, (size_t)seqs * sizeof(int32_t), cudaMemcpyHostToDevice, st)) != cudaSuccess) return cuda_fail("plan_decode: upload lens", e);
     if ((e = cudaEventRecord(p->uploaded, st)) != cudaSuccess) return cuda_fail("plan_decode: record", e);
     p->n_items = n; p->n_slots = slots; p->n_tickets = tickets; p->seqs = seqs; p->q_heads = q_heads; p->kv_heads = kv_heads;
-    p->head_dim = head_dim; p->positions = positions; p->ready = true;
+    p->head_dim = head_dim; p->positions = positions; p->max_len = max_len; p->ready = true;
     return SILVANN_B200_OK;
 }
 
@@ -254,6 +259,8 @@ SV_EXPORT int silvann_b200_paged_decode(silvann_b200_plan* p, void* o, float* re
     if (!dtype_ok(dtype)) return fail(SILVANN_B200_E_ARGUMENT, "paged_decode: dtype %d", dtype);
     if (page_positions == 0 || page_positions % sv::decode_tile_positions(p->head_dim) != 0) return fail(SILVANN_B200_E_ARGUMENT, "paged_decode: page of %u positions is not a multiple of %u", page_positions, sv::decode_tile_positions(p->head_dim));
     if (pool_pages == 0 || pool_pages * page_positions > 0x7FFFFFFFull) return fail(SILVANN_B200_E_ARGUMENT, "paged_decode: pool of %llu pages", (unsigned long long)pool_pages);
+    if ((p->max_len - 1u) / page_positions >= table_stride)
+        return fail(SILVANN_B200_E_ARGUMENT, "paged_decode: the longest planned sequence (%u positions) needs %u page-table columns and a row has %u", p->max_len, (p->max_len - 1u) / page_positions + 1u, table_stride);
     sv::DecodeCall c;
     memset(&c, 0, sizeof c);
     c.o = o; c.res = res; c.q = q; c.k = k_pool; c.v = v_pool; c.kv_rows = pool_pages * page_positions;
@@ -267,11 +274,17 @@ SV_EXPORT int silvann_b200_paged_decode(silvann_b200_plan* p, void* o, float* re
 
 __global__ void __launch_bounds__(128) paged_append_kernel(uint4* k_pool, uint4* v_pool, const uint4* k_rows, const uint4* v_rows,
                                                            const int32_t* lens, const int32_t* table, uint32_t table_stride,
-                                                           uint32_t page_pos, uint32_t row_vec) {
+                                                           uint32_t page_pos, uint32_t pool_pages, uint32_t row_vec, unsigned int* status) {
     const uint32_t s = blockIdx.x;
     const int32_t pos = lens[s] - 1;
     if (pos < 0) return;
-    const size_t at = ((size_t)table[(size_t)s * table_stride + pos / page_pos] * page_pos + pos % page_pos) * row_vec;
+    const uint32_t col = (uint32_t)pos / page_pos;
+    const int32_t page = col < table_stride ? table[(size_t)s * table_stride + col] : -1;
+    if (page < 0 || (uint32_t)page >= pool_pages) {      /* a stale or short table must not become a write somewhere else */
+        if (threadIdx.x == 0 && status) atomicOr(status, SV_STATUS_BAD_PAGE);
+        return;
+    }
+    const size_t at = ((size_t)page * page_pos + (uint32_t)pos % page_pos) * row_vec;
     for (uint32_t i = threadIdx.x; i < row_vec; i += blockDim.x) {
         k_pool[at + i] = k_rows[(size_t)s * row_vec + i];
         v_pool[at + i] = v_rows[(size_t)s * row_vec + i];
@@ -279,15 +292,19 @@ __global__ void __launch_bounds__(128) paged_append_kernel(uint4* k_pool, uint4*
 }
 
 SV_EXPORT int silvann_b200_paged_append(silvann_b200_plan* p, void* k_pool, void* v_pool, const void* k_rows, const void* v_rows,
-                                        uint32_t page_positions, const int32_t* page_table, uint32_t table_stride, void* stream) {
+                                        uint64_t pool_pages, uint32_t page_positions, const int32_t* page_table, uint32_t table_stride, void* stream) {
     called();
     if (!p || !p->ready) return fail(SILVANN_B200_E_STATE, "paged_append: plan_decode has not run");
     if (!k_pool || !v_pool || !k_rows || !v_rows || !page_table || page_positions == 0) return fail(SILVANN_B200_E_ARGUMENT, "paged_append: a null operand");
+    if (pool_pages == 0 || pool_pages * page_positions > 0x7FFFFFFFull) return fail(SILVANN_B200_E_ARGUMENT, "paged_append: pool of %llu pages", (unsigned long long)pool_pages);
+    if ((p->max_len - 1u) / page_positions >= table_stride)
+        return fail(SILVANN_B200_E_ARGUMENT, "paged_append: the longest planned sequence (%u positions) needs %u page-table columns and a row has %u", p->max_len, (p->max_len - 1u) / page_positions + 1u, table_stride);
     const uint32_t row_bytes = p->kv_heads * p->head_dim * 2u;
     if (row_bytes % 16u || (((uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)k_rows | (uintptr_t)v_rows) & 15u))
         return fail(SILVANN_B200_E_ARGUMENT, "paged_append: rows and pools must be 16-byte aligned");
     paged_append_kernel<<<p->seqs, 128, 0, (cudaStream_t)stream>>>((uint4*)k_pool, (uint4*)v_pool, (const uint4*)k_rows, (const uint4*)v_rows,
-                                                                  p->lens_dev, page_table, table_stride, page_positions, row_bytes / 16u);
+                                                                  p->lens_dev, page_table, table_stride, page_positions, (uint32_t)pool_pages,
+                                                                  row_bytes / 16u, sv::device_status_word());
     sv::note_launch(1);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? SILVANN_B200_OK : cuda_fail("paged_append: launch", e);
@@ -311,15 +328,15 @@ SV_EXPORT int silvann_b200_prefill(void* o, float* res, const void* q, const voi
 }
 
 SV_EXPORT int silvann_b200_deltanet(float* S, const void* conved, const void* z, const void* beta, const void* g, const void* w, void* out,
-                                    uint64_t k_heads, uint64_t v_heads, uint64_t head_dim, uint64_t rows, uint32_t seqs, uint32_t gate, int dtype,
-                                    sv_fault* over, void* stream) {
+                                    float* readout, uint64_t k_heads, uint64_t v_heads, uint64_t head_dim, uint64_t rows, uint32_t seqs, uint32_t gate,
+                                    int dtype, sv_fault* over, void* stream) {
     called();
     if (!S || !conved || !z || !beta || !g || !w || !out) return fail(SILVANN_B200_E_ARGUMENT, "deltanet: a null operand");
     if (!dtype_ok(dtype) || gate > 1u) return fail(SILVANN_B200_E_ARGUMENT, "deltanet: dtype %d or gate %u", dtype, gate);
     sv::DeltaCall c;
     memset(&c, 0, sizeof c);
     c.S = S; c.conved = (const uint16_t*)conved; c.z = (const uint16_t*)z; c.beta = (const uint16_t*)beta; c.g = (const uint16_t*)g;
-    c.w = (const uint16_t*)w; c.out = (uint16_t*)out; c.k_heads = (uint32_t)k_heads; c.v_heads = (uint32_t)v_heads;
+    c.w = (const uint16_t*)w; c.out = (uint16_t*)out; c.readout = readout; c.k_heads = (uint32_t)k_heads; c.v_heads = (uint32_t)v_heads;
     c.head_dim = (uint32_t)head_dim; c.seqs = seqs; c.rows = rows; c.gate = (int)gate; c.dtype = dtype; c.over = over; c.stream = (cudaStream_t)stream;
     if (!sv::deltanet_fits(c)) return fail(SILVANN_B200_E_ARGUMENT, "deltanet: head_dim %llu or heads %llu over %llu are outside the kernel's fit", (unsigned long long)head_dim, (unsigned long long)v_heads, (unsigned long long)k_heads);
     cudaError_t e = sv::deltanet_launch(c);

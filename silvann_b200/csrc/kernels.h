@@ -62,6 +62,7 @@ cudaError_t decode_device_scratch(DecodeScratch* out);
 uint32_t device_sm_count();
 void note_launch(uint32_t kernels);    /* adds to the library's launch counter (family.cu) */
 unsigned int* device_status_word();   /* device address of the bound device's status word (allocated on first use) */
+cudaError_t static_status_take(unsigned int* word, int clear);   /* the allocation-free decode's own status word (decode.cu) */
 
 /* ---- contract-faithful attention doors, any shape (attn_doors.cu) ------------------------------------------- */
 cudaError_t scores_launch(float* p, const uint16_t* q, const uint16_t* k, uint64_t qh, uint64_t kvh, uint64_t d,

@@ -12,6 +12,7 @@ struct DeltaCall {
     float* S;
     const uint16_t *conved, *z, *beta, *g, *w;
     uint16_t* out;
+    float* readout;      /* null, or [seqs][rows][v_heads·d] fp32: S^T qs of every position before its first rounding to 16 bits */
     uint32_t k_heads, v_heads, head_dim, seqs;
     uint64_t rows;
     int gate;      /* 0 silu(z), 1 sigmoid(z) */

@@ -28,6 +28,7 @@
  *
  * Algorithmic flops: 4 · q_heads · head_dim · rows·(rows+1)/2 (+ first·rows terms) — QK^T and PV, 2 flop a MAC. */
 #include "common.cuh"
+#include <atomic>
 #include "kernels.h"
 #include "tensormap.cuh"
 
@@ -124,15 +125,6 @@ __host__ __device__ constexpr uint32_t idesc_f16(int bf16, int b_mn_major, int m
            ((uint32_t)(m >> 4) << 24);
 }
 
-#ifdef SV_PREFILL_TRACE
-/* Development aid, compiled only on request: block 0 leaves clock64() stamps of its softmax and MMA phases here. */
-__device__ unsigned long long g_pf_trace[2 * 128 * 8];
-#define SV_TR_S(j, k) do { if (blockIdx.x == 0 && warp == 2 && lane == 0 && (j) < 128) g_pf_trace[(j) * 8 + (k)] = clock64(); } while (0)
-#define SV_TR_M(j, k) do { if (blockIdx.x == 0 && (j) < 128) g_pf_trace[1024 + (j) * 8 + (k)] = clock64(); } while (0)
-#else
-#define SV_TR_S(j, k) do {} while (0)
-#define SV_TR_M(j, k) do {} while (0)
-#endif
 
 template <int D> struct PrefillCfg {
     static constexpr int BOXES = D / 64;
@@ -257,10 +249,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             bool ok = mbar_wait(q_full, 0, abort_flag, P.status);
             for (int j = 0; ok && j < nt; ++j) {
                 const int s = j % KST, b = j % NSB;
-                SV_TR_M(j, 0);
                 if (!mbar_wait(&k_full[s], (j / KST) & 1, abort_flag, P.status)) break;
                 if (j >= NSB && !mbar_wait(&s_free[b], (j / NSB - 1) & 1, abort_flag, P.status)) break;
-                SV_TR_M(j, 1);
                 tc_fence_after();
                 const uint32_t lo = kd_lo + (uint32_t)s * (Cfg::KV_TILE_BYTES >> 4), d_s = t_s0 + b * PF_BN;
 #pragma unroll
@@ -269,7 +259,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                                lo + (kk / 4) * (Cfg::KV_BOX_BYTES >> 4) + (kk % 4) * 2, kd_hi, IDESC_S, kk > 0 ? 1u : 0u);
                 tc_commit(&k_empty[s]);
                 tc_commit(&s_full[b]);
-                SV_TR_M(j, 2);
             }
         }
     } else if (warp == 10) {
@@ -282,7 +271,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 const int s = j % VST, b = j % NSB;
                 if (!mbar_wait(&v_full[s], (j / VST) & 1, abort_flag, P.status)) break;
                 if (!mbar_wait(&p_full[b], (j / NSB) & 1, abort_flag, P.status)) break;
-                SV_TR_M(j, 3);
                 tc_fence_after();
                 /* V is [key][value column]: MN-major for B; 64-column groups are a box apart (LBO), 8-key groups
                  * 1024 bytes apart (SBO); sixteen keys a step.  P: sixteen keys = 8 packed columns a step. */
@@ -292,7 +280,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                     tc_mma_ts2(t_o, a_p + kk * 8, lo + kk * (2048 >> 4), vd_hi, IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
                 tc_commit(&pv_done[s]);
                 tc_commit(&s_free[b]);
-                SV_TR_M(j, 4);
             }
         }
     } else {
@@ -314,7 +301,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             const int b = j % NSB;
             /* the TMEM accesses below are warp-collective: the warp leaves the loop together or not at all */
             if (!__all_sync(0xffffffffu, mbar_wait(&s_full[b], (j / NSB) & 1, abort_flag, P.status))) { alive = false; break; }
-            SV_TR_S(j, 0);
             tc_fence_after();
             uint32_t sv[2][32];
             tmem_ld32(t_s0 + b * PF_BN + lane_off, sv[0]);
@@ -324,7 +310,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&xbar[quad]);
-            SV_TR_S(j, 1);
 
             const int key0 = j * PF_BN;
             if (key0 + PF_BN - 1 > pos) {                           /* keys of this tile lie past the row's position */
@@ -335,7 +320,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
 #pragma unroll
             for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c >> 5][c & 31]));
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * P.scale_log2;
-            SV_TR_S(j, 2);
             /* keep the reference maximum unless this tile's exceeds it by more than 8 (weights then stay <= 2^8) */
             float f = 1.f;
             const bool grow = (mx > m_ref + 8.f) || (m_ref == -INFINITY && mx != -INFINITY);
@@ -354,7 +338,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 pk[c >> 1] = w;
             }
             l = l * f + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-            SV_TR_S(j, 3);
 
             if (j > 0 && __any_sync(0xffffffffu, f != 1.f)) {
                 /* O may be rescaled only between PV MMAs: the previous one must have completed, the next waits for us */
@@ -371,7 +354,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 }
                 tmem_wait_st();
             }
-            SV_TR_S(j, 4);
             /* P over the scores, in place: 32 weights = 16 packed columns at this half's place, once the partner has read */
             if (!__all_sync(0xffffffffu, mbar_wait(&xbar[quad], j & 1, abort_flag, P.status))) { alive = false; break; }
             tmem_st16(t_s0 + b * PF_BN + half * 16 + lane_off, pk);
@@ -379,7 +361,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full[b]);
-            SV_TR_S(j, 5);
         }
         /* epilogue: the row's normaliser is the sum of its two halves'; O / l, rounded, to global — each warp of the pair
          * writes half of the row, which is contiguous in the output */
@@ -455,23 +436,18 @@ static cudaError_t launch_prefill(const PrefillCall& c) {
     P.q_heads = c.q_heads; P.kv_heads = c.kv_heads; P.group = c.q_heads / c.kv_heads;
     P.first = (uint32_t)c.first; P.rows = (uint32_t)c.rows; P.q_tiles = (uint32_t)((c.rows + PF_BM - 1) / PF_BM);
     P.scale_log2 = (1.0f / sqrtf((float)D)) * SV_LOG2E;
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64];
     int d = 0; cudaGetDevice(&d);
-    if (d >= 0 && d < 64 && !attr_set[d]) {
+    if (d >= 0 && d < 64 && !attr_set[d].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(prefill_kernel<D, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
         if (e != cudaSuccess) return e;
-        attr_set[d] = true;
+        attr_set[d].store(true, std::memory_order_release);
     }
     prefill_kernel<D, DT><<<P.q_tiles * c.q_heads, PF_THREADS, Cfg::SMEM, c.stream>>>(qm, km, vm, P);
     note_launch(1);
     return cudaGetLastError();
 }
 
-#ifdef SV_PREFILL_TRACE
-extern "C" __attribute__((visibility("default"))) int sv_prefill_trace_read(unsigned long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_pf_trace, sizeof(unsigned long long) * 2 * 128 * 8);
-}
-#endif
 
 cudaError_t prefill_launch(const PrefillCall& c) {
 #define SV_PF(DD) (c.dtype == SV_DTYPE_BF16 ? launch_prefill<DD, SV_DTYPE_BF16>(c) : launch_prefill<DD, SV_DTYPE_FP16>(c))

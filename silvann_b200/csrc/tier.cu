@@ -20,8 +20,12 @@
 
 #define SV_EXPORT extern "C" __attribute__((visibility("default")))
 #define SV_TIER_STAGES_MAX 8
+#define SV_TIER_COPY_BYTES (8ull << 20)      /* a plane's share of a chunk when the caller leaves the chunk size to the library */
 
 int sv_ext_fail(int code, const char* fmt, ...);      /* ext.cu: records the message for silvann_b200_last_error */
+struct silvann_b200_exchange;
+int sv_exchange_merge_finish(silvann_b200_exchange* x, void* o, float* res, const float* res_local, uint64_t q_heads, uint64_t head_dim, int dtype,
+                             sv_fault* over, uint32_t wait_ms, void* stream);      /* exchange.cu */
 
 struct silvann_b200_tier {
     int device;
@@ -57,7 +61,15 @@ SV_EXPORT int silvann_b200_tier_create(silvann_b200_tier** out, uint32_t q_heads
     if (kv_heads == 0 || q_heads % kv_heads != 0 || (head_dim != 64 && head_dim != 128 && head_dim != 256))
         return sv_ext_fail(SILVANN_B200_E_ARGUMENT, "tier_create: %u heads over %u, head_dim %u", q_heads, kv_heads, head_dim);
     if (dtype != SV_DTYPE_FP16 && dtype != SV_DTYPE_BF16) return sv_ext_fail(SILVANN_B200_E_ARGUMENT, "tier_create: dtype %d", dtype);
-    if (stages < 2 || stages > SV_TIER_STAGES_MAX || chunk_positions == 0 || chunk_positions % 128u != 0)
+    if (chunk_positions == 0) {
+        /* sized in bytes, not positions: a copy of a few megabytes a plane keeps the host link busy whatever the width of a
+         * row is (a rank that owns one kv head has rows of 256 bytes; 8,192 of them would be a 2 MB copy) */
+        const uint64_t row = (uint64_t)kv_heads * head_dim * 2u;
+        uint64_t n = (SV_TIER_COPY_BYTES + row - 1) / row;
+        n = (n + 127u) / 128u * 128u;
+        chunk_positions = (uint32_t)(n < 1024u ? 1024u : n);
+    }
+    if (stages < 2 || stages > SV_TIER_STAGES_MAX || chunk_positions % 128u != 0)
         return sv_ext_fail(SILVANN_B200_E_ARGUMENT, "tier_create: %u stages (2..%d) of %u positions (a multiple of 128)", stages, SV_TIER_STAGES_MAX, chunk_positions);
     silvann_b200_tier* t = new (std::nothrow) silvann_b200_tier();
     if (!t) return sv_ext_fail(SILVANN_B200_E_CUDA, "tier_create: out of host memory");
@@ -99,20 +111,21 @@ SV_EXPORT int silvann_b200_tier_stats(const silvann_b200_tier* t, uint64_t* h2d_
 }
 
 /* One piece of the cache into `res` (m, l, acc per head), enqueued on `st`. */
-static cudaError_t piece(const silvann_b200_tier* t, float* res, const void* q, const void* k, const void* v, uint64_t length, cudaStream_t st) {
+static cudaError_t piece(const silvann_b200_tier* t, void* o, float* res, const void* q, const void* k, const void* v, uint64_t length, sv_fault* over,
+                         cudaStream_t st) {
     sv::DecodeCall c;
     memset(&c, 0, sizeof c);
-    c.res = res; c.q = q; c.k = k; c.v = v; c.kv_rows = length; c.seqs = 1;
+    c.o = o; c.res = res; c.q = q; c.k = k; c.v = v; c.kv_rows = length; c.seqs = 1;
     c.q_heads = t->q_heads; c.kv_heads = t->kv_heads; c.head_dim = t->head_dim; c.length = (uint32_t)length;
-    c.dtype = t->dtype; c.stream = st;
+    c.dtype = t->dtype; c.over = over; c.stream = st;
     if (!sv::decode_fits(c)) return cudaErrorInvalidValue;
     cudaError_t e = sv::decode_device_scratch(&c.scratch);
     if (e != cudaSuccess) return e;
     return sv::decode_launch(c);
 }
 
-SV_EXPORT int silvann_b200_tier_decode(silvann_b200_tier* t, void* o, float* res, const void* q, const void* k_host, const void* v_host,
-                                       uint64_t host_len, const void* k_dev, const void* v_dev, uint64_t dev_len, sv_fault* over, void* stream) {
+static int tier_decode(silvann_b200_tier* t, silvann_b200_exchange* x, uint32_t wait_ms, void* o, float* res, const void* q, const void* k_host,
+                       const void* v_host, uint64_t host_len, const void* k_dev, const void* v_dev, uint64_t dev_len, sv_fault* over, void* stream) {
     if (!t || !q || (!o && !res)) return sv_ext_fail(SILVANN_B200_E_ARGUMENT, "tier_decode: a null operand");
     if (host_len + dev_len == 0 || host_len + dev_len > 0x7FFFFFFFull) return sv_ext_fail(SILVANN_B200_E_ARGUMENT, "tier_decode: %llu positions", (unsigned long long)(host_len + dev_len));
     if ((host_len && (!k_host || !v_host)) || (dev_len && (!k_dev || !v_dev))) return sv_ext_fail(SILVANN_B200_E_ARGUMENT, "tier_decode: a tier with positions and no planes");
@@ -120,6 +133,12 @@ SV_EXPORT int silvann_b200_tier_decode(silvann_b200_tier* t, void* o, float* res
     cudaError_t e = cudaSuccess;
     bool have = false;
 #define SV_TRY(call, what) do { e = (call); if (e != cudaSuccess) { (void)cudaGetLastError(); return sv_ext_fail(SILVANN_B200_E_CUDA, "tier_decode: %s: %s", what, cudaGetErrorString(e)); } } while (0)
+    if (host_len == 0 && !x) {
+        /* everything is on the card and nobody else holds a part of the range: the decode kernel writes the answer itself,
+         * with no running residual and no finishing launch */
+        SV_TRY(piece(t, o, res, q, k_dev, v_dev, dev_len, over, st), "card tier");
+        return SILVANN_B200_OK;
+    }
     const uint64_t nchunks = (host_len + t->chunk - 1) / t->chunk;
     /* queue the first copies before any compute so that they run under the card tier's kernel */
     uint64_t queued = 0;
@@ -136,7 +155,7 @@ SV_EXPORT int silvann_b200_tier_decode(silvann_b200_tier* t, void* o, float* res
     };
     for (; queued < nchunks && queued < t->stages - 1; ++queued) SV_TRY(queue_copy(queued), "copy");
     if (dev_len) {
-        SV_TRY(piece(t, t->acc, q, k_dev, v_dev, dev_len, st), "card tier");
+        SV_TRY(piece(t, nullptr, t->acc, q, k_dev, v_dev, dev_len, nullptr, st), "card tier");
         have = true;
     }
     for (uint64_t c = 0; c < nchunks; ++c) {
@@ -144,14 +163,27 @@ SV_EXPORT int silvann_b200_tier_decode(silvann_b200_tier* t, void* o, float* res
         const uint64_t n = (c + 1 == nchunks) ? host_len - c * t->chunk : t->chunk;
         if (queued < nchunks) { SV_TRY(queue_copy(queued), "copy"); ++queued; }
         SV_TRY(cudaStreamWaitEvent(st, t->full[s], 0), "wait for a chunk");
-        SV_TRY(piece(t, have ? t->tmp : t->acc, q, t->k_stage[s], t->v_stage[s], n, st), "host chunk");
+        SV_TRY(piece(t, nullptr, have ? t->tmp : t->acc, q, t->k_stage[s], t->v_stage[s], n, nullptr, st), "host chunk");
         SV_TRY(cudaEventRecord(t->freed[s], st), "record");
         t->freed_recorded[s] = true;
         if (have) SV_TRY(sv::merge_launch(t->acc, t->acc, t->tmp, t->q_heads, t->head_dim, st), "merge");
         have = true;
     }
+    if (x) return sv_exchange_merge_finish(x, o, res, t->acc, t->q_heads, t->head_dim, t->dtype, over, wait_ms, stream);
     if (res) SV_TRY(cudaMemcpyAsync(res, t->acc, (size_t)t->q_heads * (t->head_dim + 2u) * sizeof(float), cudaMemcpyDeviceToDevice, st), "residual out");
     if (o) SV_TRY(sv::finish_launch((uint16_t*)o, t->acc, t->q_heads, t->head_dim, over, t->dtype, st), "finish");
 #undef SV_TRY
     return SILVANN_B200_OK;
+}
+
+SV_EXPORT int silvann_b200_tier_decode(silvann_b200_tier* t, void* o, float* res, const void* q, const void* k_host, const void* v_host,
+                                       uint64_t host_len, const void* k_dev, const void* v_dev, uint64_t dev_len, sv_fault* over, void* stream) {
+    return tier_decode(t, nullptr, 0, o, res, q, k_host, v_host, host_len, k_dev, v_dev, dev_len, over, stream);
+}
+
+SV_EXPORT int silvann_b200_tier_decode_exchange(silvann_b200_tier* t, silvann_b200_exchange* x, void* o, float* res, const void* q, const void* k_host,
+                                                const void* v_host, uint64_t host_len, const void* k_dev, const void* v_dev, uint64_t dev_len,
+                                                sv_fault* over, uint32_t wait_ms, void* stream) {
+    if (!x) return sv_ext_fail(SILVANN_B200_E_ARGUMENT, "tier_decode_exchange: exchange is null");
+    return tier_decode(t, x, wait_ms, o, res, q, k_host, v_host, host_len, k_dev, v_dev, dev_len, over, stream);
 }

@@ -23,6 +23,7 @@
  * Algorithmic bytes a position and kv head: 2 · (head_dim · width / 8 + 2).
  * Every mbarrier wait is bounded; a wait that runs out ORs "B2TO" into the device's status word and the block leaves. */
 #include "common.cuh"
+#include <atomic>
 #include "kernels.h"
 #include "tensormap.cuh"
 #include <stdio.h>
@@ -471,12 +472,12 @@ template <int DH, int W, int NHT>
 static cudaError_t tq_launch_one(const CUtensorMap& km, const CUtensorMap& vm, const TqParams& P, uint32_t blocks, cudaStream_t st) {
     using Cfg = TqCfg<DH, W>;
     const size_t smem = 1024 + (size_t)Cfg::STAGES * Cfg::STAGE + Cfg::LUT_BYTES + (size_t)8 * NHT * Cfg::QROW + 2 * Cfg::STAGES * 8 + 64;
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64];
     int dev = 0; cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(tq_attend_kernel<DH, W, NHT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     tq_attend_kernel<DH, W, NHT><<<blocks, (Cfg::NW + 1) * 32, smem, st>>>(km, vm, P);
     note_launch(1);

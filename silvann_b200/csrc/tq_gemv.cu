@@ -32,6 +32,7 @@
  * lookups and 256 fetch wavefronts, after 2.7 us of prologue and first landing (every SM's first three slots, 14 MB over the
  * card, are asked for at once). */
 #include "common.cuh"
+#include <atomic>
 #include "kernels.h"
 #include <string.h>
 
@@ -61,22 +62,6 @@ __global__ void __launch_bounds__(256) gv_lut_image_kernel() {
 
 cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_t* rows_cap, const uint16_t* x, uint64_t cols, uint64_t inputs,
                                 uint64_t out_stride, unsigned int* over, cudaStream_t st);
-#ifdef SV_GEMV_TRACE
-/* Development aid, compiled only on request: every block leaves %globaltimer stamps (ns) of its phases here. */
-__device__ unsigned long long g_gv_trace[256 * 32];
-__device__ __forceinline__ unsigned long long gv_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define SV_GTR(k) do { if (threadIdx.x == 0 && blockIdx.x < 256 && (k) < 32) g_gv_trace[blockIdx.x * 32 + (k)] = gv_gtime(); } while (0)
-#define SV_GTS(n, k) do { if ((n) < 4) SV_GTR(2 + (n) * 4 + (k)); } while (0)
-extern "C" __attribute__((visibility("default"))) int sv_gemv_trace_read(unsigned long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_gv_trace, sizeof(unsigned long long) * 256 * 32);
-}
-extern "C" __attribute__((visibility("default"))) int sv_gemv_trace_run(uint16_t* out, const void* groups, const uint16_t* x, uint64_t cols) {
-    return (int)tq_gemv_fast_launch(out, groups, nullptr, x, cols, 1, 0, nullptr, 0);
-}
-#else
-#define SV_GTR(k) do {} while (0)
-#define SV_GTS(n, k) do {} while (0)
-#endif
 
 struct GemvFast {
     const uint8_t* codes[12];
@@ -172,7 +157,6 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
     uint64_t* table_bar = empty + GV_STAGES_MAX;
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(table_bar + 1);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-    SV_GTR(0);
     if (tid == 0) {
         uint32_t n = 0;
         for (; n < (uint32_t)GV_STAGES_MAX && before + a.stage_bytes <= lut; ++n, before += a.stage_bytes) stage_at_s[n] = before;
@@ -222,9 +206,6 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
     uint32_t xr[NIW][16];                                                    /* this lane's B fragments: input g, the columns of its bytes */
     uint32_t have_d = 0, n = 0, m = 0;
     bool table_ready = false, failed = false;
-#ifdef SV_GEMV_TRACE
-    long long waited = 0, worked = 0;
-#endif
     int buf = 0;
     bool hit = false;
     int gi = -1;
@@ -266,25 +247,14 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
         const bool o_live = o_tile < nt && o_row < rows && o_in < a.inputs;
         uint16_t scale = 0;
         if (o_live) asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(scale) : "l"(sc + o_row));
-        SV_GTS(n, 0);
         float* mine = part + (size_t)buf * ts * tile_floats + (size_t)warp * 16u * pi;
         for (uint32_t tq = 0; tq < nt; ++tq) {
             float c[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
             for (uint32_t h = 0; h < halves; ++h, ++m) {
                 const uint32_t slot = m % S;
-#ifdef SV_GEMV_TRACE
-                const long long w0 = clock64();
-#endif
                 bool landed = failed ? false : mbar_wait(&full[slot], (m / S) & 1u, abort_flag, a.status);
-#ifdef SV_GEMV_TRACE
-                waited += clock64() - w0;
-#endif
-                if (!table_ready && landed) { landed = mbar_wait(table_bar, 0u, abort_flag, a.status); table_ready = true; SV_GTR(1); }
+                if (!table_ready && landed) { landed = mbar_wait(table_bar, 0u, abort_flag, a.status); table_ready = true; }
                 if (!landed) { failed = true; continue; }                    /* said at the step's barrier: every warp leaves there, or none */
-                if (tq == 0 && h == 0) SV_GTS(n, 1);
-#ifdef SV_GEMV_TRACE
-                const long long k0 = clock64();
-#endif
                 const uint32_t stride = seg + GV_ROW_PAD, at_a = stage_at_s[slot] + (uint32_t)t * 16u + (uint32_t)g * stride, at_b = at_a + 8u * stride;
 #pragma unroll
                 for (int i = 0; i < NIW; ++i) {
@@ -295,9 +265,6 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
                     gv_piece(c, c1, ua, ub, xr[i], W != 0 ? (uint32_t)W : d, at4, at8);
                 }
                 __syncwarp();
-#ifdef SV_GEMV_TRACE
-                worked += clock64() - k0;
-#endif
                 if (lane == 0) mbar_arrive(&empty[slot]);                    /* this warp has read the slot */
             }
             /* c0, c1: (row g, inputs 2t, 2t+1) · c2, c3: (row g + 8, the same inputs): kept for the inputs there are */
@@ -308,14 +275,12 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
                 if (pi > 1u) { to[(uint32_t)g * pi + 2u * t + 1u] = c[1] + c1[1]; to[((uint32_t)g + 8u) * pi + 2u * t + 1u] = c[3] + c1[3]; }
             }
         }
-        SV_GTS(n, 2);
         {   /* the working warps' partial sums are whole; and a vote: a warp whose wait gave up takes every warp out */
             uint32_t any;
             asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.or.pred p, 1, 512, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                          : "=r"(any) : "r"(failed ? 1u : 0u) : "memory");
             if (any) { failed = true; break; }
         }
-        SV_GTS(n, 3);
         if (o_live) {                                                        /* sixteen warps' parts of one answer, in warp order */
             const float* from = part + (size_t)buf * ts * tile_floats + (size_t)o_tile * tile_floats + ((o / pi) % 16u) * pi + o_in;
             float sum = 0.f;
@@ -329,10 +294,6 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
      * (bounded) for every slot's barrier to settle before the memory is given back. */
     if (failed && tid == 0)
         for (uint32_t st = 0; st < S; ++st) for (uint32_t i = 0; i < 4096u && !mbar_try_wait(&full[st], 0u) && !mbar_try_wait(&full[st], 1u); ++i) { }
-    SV_GTR(31);
-#ifdef SV_GEMV_TRACE
-    if (tid == 0 && blockIdx.x < 256) { g_gv_trace[blockIdx.x * 32 + 28] = (unsigned long long)waited; g_gv_trace[blockIdx.x * 32 + 29] = (unsigned long long)worked; g_gv_trace[blockIdx.x * 32 + 30] = m; }
-#endif
     if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
 }
 
@@ -405,27 +366,27 @@ cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_
     a.x_wide = ((uintptr_t)x % 16 == 0 && cols % 8 == 0) ? 1u : 0u;
     a.ts = ts; a.pi = pi; a.stage_bytes = stage_bytes; a.smem_bytes = smem_bytes;
     a.status = device_status_word();
-    {   /* the table's image, once a device */
-        static bool made[64] = {};
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-        if (!made[dev]) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    {   /* the table's image, once a device; making it twice (two threads' first calls at once) writes the same bytes */
+        static std::atomic<bool> made[64];
+        if (!made[dev].load(std::memory_order_acquire)) {
             gv_lut_image_kernel<<<16, 256, 0, st>>>();
             const cudaError_t e = cudaGetLastError();
             if (e != cudaSuccess) return e;
             note_launch(1);
-            made[dev] = true;
+            made[dev].store(true, std::memory_order_release);
         }
     }
     const size_t smem = smem_bytes;
     const unsigned grid = steps < 148u ? steps : 148u;
 #define SV_GV2(N, WW)                                                                                                               \
     do {                                                                                                                             \
-        static bool ready = false;                                                                                                   \
-        if (!ready) {                                                                                                                \
+        static std::atomic<bool> ready[64];      /* a function's attribute is a device's: once a device, at the kernel's ceiling */ \
+        if (!ready[dev].load(std::memory_order_acquire)) {                                                                           \
             const cudaError_t e = cudaFuncSetAttribute(tq_gemv_fast_kernel<N, WW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return e;                                                                                          \
-            ready = true;                                                                                                            \
+            ready[dev].store(true, std::memory_order_release);                                                                       \
         }                                                                                                                            \
         tq_gemv_fast_kernel<N, WW><<<grid, GV_THREADS + 32, smem, st>>>(out, a, x, over);                                            \
     } while (0)

@@ -17,7 +17,10 @@ EXPORTS = (
     "silvann_b200_decode", "silvann_b200_decode_noalloc", "silvann_b200_merge", "silvann_b200_finish", "silvann_b200_plan_create",
     "silvann_b200_plan_destroy", "silvann_b200_plan_decode", "silvann_b200_plan_info", "silvann_b200_paged_decode", "silvann_b200_paged_append",
     "silvann_b200_prefill", "silvann_b200_deltanet", "silvann_b200_tier_create", "silvann_b200_tier_destroy",
-    "silvann_b200_tier_decode", "silvann_b200_tier_stats",
+    "silvann_b200_tier_decode", "silvann_b200_tier_stats", "silvann_b200_tier_decode_exchange",
+    "silvann_b200_exchange_create", "silvann_b200_exchange_destroy", "silvann_b200_exchange_local", "silvann_b200_exchange_handle",
+    "silvann_b200_exchange_connect_handles", "silvann_b200_exchange_connect_addresses", "silvann_b200_exchange_merge_finish",
+    "silvann_b200_exchange_vector_sum", "silvann_b200_exchange_deposit",
 )
 
 
@@ -56,13 +59,23 @@ def lib():
             "silvann_b200_plan_decode": [vp, vp, u32, u32, u32, u32, u32, vp],
             "silvann_b200_plan_info": [vp, vp, vp, vp],
             "silvann_b200_paged_decode": [vp, vp, vp, vp, vp, vp, u64, u32, vp, u32, i32, vp, vp],
-            "silvann_b200_paged_append": [vp, vp, vp, vp, vp, u32, vp, u32, vp],
+            "silvann_b200_paged_append": [vp, vp, vp, vp, vp, u64, u32, vp, u32, vp],
             "silvann_b200_tier_create": [vp, u32, u32, u32, i32, u32, u32],
             "silvann_b200_tier_destroy": [vp],
             "silvann_b200_tier_decode": [vp, vp, vp, vp, vp, vp, u64, vp, vp, u64, vp, vp],
             "silvann_b200_tier_stats": [vp, vp, vp],
+            "silvann_b200_tier_decode_exchange": [vp, vp, vp, vp, vp, vp, vp, u64, vp, vp, u64, vp, u32, vp],
+            "silvann_b200_exchange_create": [vp, u32, u32, u64],
+            "silvann_b200_exchange_destroy": [vp],
+            "silvann_b200_exchange_local": [vp, vp, vp],
+            "silvann_b200_exchange_handle": [vp, vp, u32],
+            "silvann_b200_exchange_connect_handles": [vp, vp, u32],
+            "silvann_b200_exchange_connect_addresses": [vp, vp],
+            "silvann_b200_exchange_merge_finish": [vp, vp, vp, vp, u64, u64, i32, vp, u32, vp],
+            "silvann_b200_exchange_vector_sum": [vp, vp, vp, u64, i32, vp, u32, vp],
+            "silvann_b200_exchange_deposit": [vp, u32, vp, u64, vp],
             "silvann_b200_prefill": [vp, vp, vp, vp, vp, u64, u64, u64, u64, u64, i32, vp, vp],
-            "silvann_b200_deltanet": [vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u32, u32, i32, vp, vp],
+            "silvann_b200_deltanet": [vp, vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u32, u32, i32, vp, vp],
         }
         for name, args in sigs.items():
             fn = getattr(L, name)
@@ -143,15 +156,15 @@ class Plan:
                                                page_positions, addr(page_table), table_stride, dtype, addr(over), stream))
 
 
-    def append(self, k_pool, v_pool, k_rows, v_rows, page_positions, page_table, table_stride, stream=None):
-        _check(lib().silvann_b200_paged_append(self.handle, addr(k_pool), addr(v_pool), addr(k_rows), addr(v_rows), page_positions,
+    def append(self, k_pool, v_pool, k_rows, v_rows, pool_pages, page_positions, page_table, table_stride, stream=None):
+        _check(lib().silvann_b200_paged_append(self.handle, addr(k_pool), addr(v_pool), addr(k_rows), addr(v_rows), pool_pages, page_positions,
                                                addr(page_table), table_stride, stream))
 
 
 class Tier:
     """Decode over a cache whose oldest positions live in pinned host RAM (see silvann_b200_tier_decode)."""
 
-    def __init__(self, q_heads, kv_heads, head_dim, dtype=FP16, chunk_positions=8192, stages=3):
+    def __init__(self, q_heads, kv_heads, head_dim, dtype=FP16, chunk_positions=0, stages=3):
         self.handle = C.c_void_p()
         _check(lib().silvann_b200_tier_create(C.byref(self.handle), q_heads, kv_heads, head_dim, dtype, chunk_positions, stages))
 
@@ -170,16 +183,73 @@ class Tier:
         _check(lib().silvann_b200_tier_decode(self.handle, addr(o), addr(res), addr(q), addr(k_host), addr(v_host), host_len,
                                               addr(k_dev), addr(v_dev), dev_len, addr(over), stream))
 
+    def decode_exchange(self, exchange, o, res, q, k_host, v_host, host_len, k_dev, v_dev, dev_len, over=None, wait_ms=0, stream=None):
+        """This member's residual over its two tiers, then the exchange with the members that hold the rest of the range."""
+        _check(lib().silvann_b200_tier_decode_exchange(self.handle, exchange.handle, addr(o), addr(res), addr(q), addr(k_host), addr(v_host), host_len,
+                                                       addr(k_dev), addr(v_dev), dev_len, addr(over), wait_ms, stream))
+
     def stats(self) -> dict:
         b, c = C.c_uint64(), C.c_uint64()
         _check(lib().silvann_b200_tier_stats(self.handle, C.byref(b), C.byref(c)))
         return {"h2d_bytes": b.value, "chunks": c.value}
 
 
+HANDLE_BYTES = 64
+
+
+class Exchange:
+    """One member's end of an exchange among the cards that share a piece of work (see silvann_b200_exchange_create)."""
+
+    def __init__(self, members, index, slot_bytes):
+        self.handle = C.c_void_p()
+        self.members, self.index = members, index
+        _check(lib().silvann_b200_exchange_create(C.byref(self.handle), members, index, slot_bytes))
+
+    def close(self):
+        if self.handle:
+            lib().silvann_b200_exchange_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def local(self) -> tuple:
+        a, b = C.c_uint64(), C.c_uint64()
+        _check(lib().silvann_b200_exchange_local(self.handle, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def ipc_handle(self) -> bytes:
+        buf = C.create_string_buffer(HANDLE_BYTES)
+        _check(lib().silvann_b200_exchange_handle(self.handle, buf, HANDLE_BYTES))
+        return buf.raw
+
+    def connect_handles(self, handles):
+        """handles: every member's ipc_handle() in member order (this member's own entry is ignored)."""
+        blob = b"".join(bytes(h) for h in handles)
+        assert len(blob) == HANDLE_BYTES * self.members
+        _check(lib().silvann_b200_exchange_connect_handles(self.handle, blob, HANDLE_BYTES))
+
+    def connect_addresses(self, addresses):
+        arr = (C.c_uint64 * self.members)(*[int(a) for a in addresses])
+        _check(lib().silvann_b200_exchange_connect_addresses(self.handle, arr))
+
+    def merge_finish(self, o, res, res_local, q_heads, head_dim, dtype=FP16, over=None, wait_ms=0, stream=None):
+        _check(lib().silvann_b200_exchange_merge_finish(self.handle, addr(o), addr(res), addr(res_local), q_heads, head_dim, dtype, addr(over), wait_ms, stream))
+
+    def vector_sum(self, out, partial, n, dtype=FP16, over=None, wait_ms=0, stream=None):
+        _check(lib().silvann_b200_exchange_vector_sum(self.handle, addr(out), addr(partial), n, dtype, addr(over), wait_ms, stream))
+
+    def deposit(self, member, data, nbytes, stream=None):
+        _check(lib().silvann_b200_exchange_deposit(self.handle, member, addr(data), nbytes, stream))
+
+
 def prefill(o, q, k, v, q_heads, kv_heads, head_dim, first, rows, dtype=FP16, over=None, stream=None, res=None):
     _check(lib().silvann_b200_prefill(addr(o), addr(res), addr(q), addr(k), addr(v), q_heads, kv_heads, head_dim, first, rows, dtype, addr(over), stream))
 
 
-def deltanet(S, conved, z, beta, g, w, out, k_heads, v_heads, head_dim, rows, seqs=1, gate=0, dtype=FP16, over=None, stream=None):
-    _check(lib().silvann_b200_deltanet(addr(S), addr(conved), addr(z), addr(beta), addr(g), addr(w), addr(out), k_heads, v_heads,
+def deltanet(S, conved, z, beta, g, w, out, k_heads, v_heads, head_dim, rows, seqs=1, gate=0, dtype=FP16, over=None, stream=None, readout=None):
+    _check(lib().silvann_b200_deltanet(addr(S), addr(conved), addr(z), addr(beta), addr(g), addr(w), addr(out), addr(readout), k_heads, v_heads,
                                        head_dim, rows, seqs, gate, dtype, addr(over), stream))

@@ -95,6 +95,24 @@ def gather_and_fold(residual, shard: Shard, dist, merge, process_group=None, emp
     return fold(pieces, merge)
 
 
+def connect_exchange(torch, ext, dist, members, rank, slot_bytes, device=None):
+    """This rank's end of an exchange among the ranks `members` (world ranks, in fold / sum order), connected.
+
+    Every rank of the WORLD must call this together (with its own `members`; a rank that belongs to no group of more than
+    one passes [rank]): the 64-byte buffer handles travel by one all_gather over the whole world — once, at set-up — so
+    no sub-group communicator is ever made.  `device`: where the gathered bytes live ("cuda" under NCCL, "cpu" under gloo).
+    """
+    x = ext.Exchange(len(members), members.index(rank), slot_bytes)
+    device = device or ("cuda" if dist.get_backend() == "nccl" else "cpu")
+    mine = torch.frombuffer(bytearray(x.ipc_handle()), dtype=torch.uint8).to(device)
+    world = dist.get_world_size()
+    every = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    if len(members) > 1:
+        x.connect_handles([bytes(every[r].cpu().numpy().tobytes()) for r in members])
+    return x
+
+
 class LongContextRank:
     """A rank's share of the long-context decode (configuration 4): its heads, its range, its two tiers.
 
@@ -104,10 +122,10 @@ class LongContextRank:
     """
 
     def __init__(self, torch, ext, shard: Shard, head_dim, dtype, k_host, v_host, host_len, k_dev, v_dev, dev_len,
-                 dist=None, process_group=None, chunk_positions=8192, stages=3):
+                 dist=None, process_group=None, chunk_positions=0, stages=3, exchange=None):
         self.torch, self.ext, self.shard, self.d, self.dtype = torch, ext, shard, head_dim, dtype
         self.k_host, self.v_host, self.host_len, self.k_dev, self.v_dev, self.dev_len = k_host, v_host, host_len, k_dev, v_dev, dev_len
-        self.dist, self.pg = dist, process_group
+        self.dist, self.pg, self.exchange = dist, process_group, exchange
         self.tier = ext.Tier(shard.q_heads, shard.kv_heads, head_dim, dtype, chunk_positions, stages)
         self.res = torch.zeros((shard.q_heads, head_dim + 2), dtype=torch.float32, device="cuda")
         self.out = torch.zeros((shard.q_heads, head_dim), dtype=torch.int16, device="cuda")
@@ -117,16 +135,41 @@ class LongContextRank:
         return a
 
     def step(self, q_local):
-        alone = len(self.shard.group) == 1
-        self.tier.decode(self.out if alone else None, None if alone else self.res, q_local, self.k_host, self.v_host, self.host_len,
-                         self.k_dev, self.v_dev, self.dev_len)
-        if not alone:
+        """One query position.  Alone on its heads: one call, and one launch when every position is on the card.  In a
+        range split with an exchange object (connect_exchange): one call — the rank's residual, then the library's
+        push-wait-fold kernel.  Without one (gloo on CPU, or by choice): the residuals are all-gathered and folded here."""
+        if len(self.shard.group) == 1:
+            self.tier.decode(self.out, None, q_local, self.k_host, self.v_host, self.host_len, self.k_dev, self.v_dev, self.dev_len)
+        elif self.exchange is not None:
+            self.tier.decode_exchange(self.exchange, self.out, None, q_local, self.k_host, self.v_host, self.host_len, self.k_dev, self.v_dev, self.dev_len)
+        else:
+            self.tier.decode(None, self.res, q_local, self.k_host, self.v_host, self.host_len, self.k_dev, self.v_dev, self.dev_len)
             merged = gather_and_fold(self.res, self.shard, self.dist, self._merge, self.pg)
             self.ext.finish(self.out, merged, self.shard.q_heads, self.d, self.dtype)
         return self.out
 
     def close(self):
         self.tier.close()
+
+
+class PeerSum:
+    """The tensor-parallel sum that follows head-sharded attention as ONE launch a rank: every rank pushes its 16-bit
+    partial into the others' memory, and each adds the pieces in rank order in fp32 and rounds once — the reference's
+    vector_sum over the cards' partials (engine/src/packages/nn/gpu/kernels/kernels.cuh:117-126, the fan-in of
+    nn/cpu/opcodes/partials__abi.cuh:110-163), so every rank holds the same bits.  `n`: the longest vector to be summed."""
+
+    def __init__(self, torch, ext, dist, n, dtype=0):
+        self.torch, self.ext, self.dtype = torch, ext, dtype
+        world, rank = dist.get_world_size(), dist.get_rank()
+        self.exchange = connect_exchange(torch, ext, dist, list(range(world)), rank, 2 * n)
+
+    def sum(self, partial, out=None, wait_ms=0):
+        out = self.torch.empty_like(partial) if out is None else out
+        self.exchange.vector_sum(out, partial, partial.numel(), self.dtype, wait_ms=wait_ms)
+        return out
+
+    def close(self):
+        self.exchange.close()
 
 
 def sum_over_ranks(partial, dist, vector_sum, process_group=None, world=None, empty_like=None):

@@ -18,7 +18,7 @@ def run_paged(cuda, layout, q, k_pool, v_pool, blocks_target=0):
     seqs = len(L.seq_lens)
     o = cuda.zeros((seqs, L.q_heads, L.head_dim), dtype=cuda.int16, device="cuda")
     res = cuda.zeros((seqs, L.q_heads, L.head_dim + 2), dtype=cuda.float32, device="cuda")
-    table = dev(cuda, np.maximum(L.page_table, 0))
+    table = dev(cuda, L.page_table)                  # the -1 padding goes to the card as it is
     plan.decode(o, res, dev(cuda, q), dev(cuda, k_pool), dev(cuda, v_pool), L.pool_pages, workloads.PAGE_POSITIONS,
                 table, L.page_table.shape[1], L.dtype)
     cuda.cuda.synchronize()
@@ -90,4 +90,60 @@ def test_plan_refusals(cuda):
     t = cuda.zeros(16 * 256, dtype=cuda.int16, device="cuda")
     with pytest.raises(ext.B200Error):
         plan.decode(t, None, t, t, t, 1, 100, t, 1, 1)     # page size not a multiple of 64
+    plan.close()
+
+
+def test_append_writes_each_sequences_newest_row_and_nothing_else(cuda):
+    L = workloads.config3_layout(seqs=5, lo=1, hi=900)
+    L.seq_lens[0] = 1; L.seq_lens[1] = 256; L.seq_lens[2] = 257
+    q, k_pool, v_pool = workloads.config3_fill(L)
+    row = L.kv_heads * L.head_dim
+    rng = np.random.default_rng(8)
+    k_rows = oracle.to_bits(rng.standard_normal((5, row), dtype=np.float32), 1)
+    v_rows = oracle.to_bits(rng.standard_normal((5, row), dtype=np.float32), 1)
+    plan = ext.Plan()
+    plan.plan(L.seq_lens, L.q_heads, L.kv_heads, L.head_dim)
+    tk, tv = dev(cuda, k_pool), dev(cuda, v_pool)
+    plan.append(tk, tv, dev(cuda, k_rows), dev(cuda, v_rows), L.pool_pages, workloads.PAGE_POSITIONS, dev(cuda, L.page_table), L.page_table.shape[1])
+    cuda.cuda.synchronize()
+    assert ext.device_status() == 0
+    want_k, want_v = k_pool.copy(), v_pool.copy()
+    for s, n in enumerate(L.seq_lens):
+        page, at = L.page_table[s, (int(n) - 1) // 256], (int(n) - 1) % 256
+        want_k[page, at] = k_rows[s].reshape(L.kv_heads, L.head_dim)
+        want_v[page, at] = v_rows[s].reshape(L.kv_heads, L.head_dim)
+    assert np.array_equal(host_bits(tk).reshape(want_k.shape), want_k) and np.array_equal(host_bits(tv).reshape(want_v.shape), want_v)
+    plan.close()
+
+
+def test_a_table_that_names_no_page_is_never_made_into_an_address(cuda):
+    """A short table is refused on the host; an entry outside the pool is skipped on the card and the status word says so."""
+    L = workloads.config3_layout(seqs=3, lo=300, hi=900)
+    q, k_pool, v_pool = workloads.config3_fill(L)
+    plan = ext.Plan()
+    plan.plan(L.seq_lens, L.q_heads, L.kv_heads, L.head_dim)
+    seqs, stride = 3, L.page_table.shape[1]
+    o = cuda.zeros((seqs, L.q_heads, L.head_dim), dtype=cuda.int16, device="cuda")
+    tq, tk, tv, tt = dev(cuda, q), dev(cuda, k_pool), dev(cuda, v_pool), dev(cuda, L.page_table)
+    with pytest.raises(ext.B200Error) as e:
+        plan.decode(o, None, tq, tk, tv, L.pool_pages, 256, tt, 1, 1)                         # rows of one column for sequences of several pages
+    assert e.value.code == ext.E_ARGUMENT
+    rows = cuda.zeros((2, seqs, L.kv_heads * L.head_dim), dtype=cuda.int16, device="cuda")
+    with pytest.raises(ext.B200Error):
+        plan.append(tk, tv, rows[0], rows[1], L.pool_pages, 256, tt, 1)
+    bad = L.page_table.copy()
+    last = (int(L.seq_lens[1]) - 1) // 256
+    bad[1, last] = L.pool_pages + 7                                                              # sequence 1's newest page: outside the pool
+    before = host_bits(tk).copy()
+    plan.append(tk, tv, rows[0], rows[1], L.pool_pages, 256, dev(cuda, bad), stride)
+    cuda.cuda.synchronize()
+    assert ext.device_status() == 0x80000000
+    after = host_bits(tk).reshape(k_pool.shape)
+    changed = np.flatnonzero((after != before.reshape(k_pool.shape)).any(axis=(1, 2, 3)))
+    assert set(changed) <= {int(L.page_table[0, (int(L.seq_lens[0]) - 1) // 256]), int(L.page_table[2, (int(L.seq_lens[2]) - 1) // 256])}
+    bad[1, last] = -1
+    plan.decode(o, None, tq, tk, tv, L.pool_pages, 256, dev(cuda, bad), stride, 1)              # read as zeros, flagged, no fault
+    cuda.cuda.synchronize()
+    assert ext.device_status() == 0x80000000
+    assert ext.device_status() == 0
     plan.close()

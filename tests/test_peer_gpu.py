@@ -80,3 +80,57 @@ def test_one_cache_split_by_position_over_two_cards(cuda, two, reference, port):
     assert fam.sys.compute_completed()
     want = impl.decode(q, k, v, qh, kvh, d, n)
     assert_close16(o.cpu().numpy().view(np.uint16), from_bits(want, FP16), FP16, "two ranges on two cards, merged over the link")
+
+
+def test_exchange_between_two_cards_of_one_process(cuda, two, port):
+    """The exchange kernels with both members REAL: one process, a card each, the members wired by address (peer access is
+    granted by the fixture).  Both launches are queued before either is waited for; each card waits on the device for the
+    other's push.  Range residuals are folded, then partial sums added — the same object, consecutive generations."""
+    from silvann_b200 import ext
+    fam = two
+    qh, kvh, d, n, cut = 16, 4, 128, 6000, 3072
+    rng = np.random.default_rng(33)
+    q = to_bits(rng.standard_normal((qh, d)).astype(np.float32) * 0.5, FP16)
+    k = to_bits(rng.standard_normal((n, kvh, d)).astype(np.float32) * 0.5, FP16)
+    v = to_bits(rng.standard_normal((n, kvh, d)).astype(np.float32) * 0.5, FP16)
+    hidden = 5120
+    parts = [to_bits(rng.standard_normal(hidden).astype(np.float32), FP16) for _ in range(2)]
+    xs, res, outs, sums, tparts = [], [], [], [], []
+    for i, (lo, hi) in enumerate([(0, cut), (cut, n)]):
+        tq, tk, tv = on(cuda, fam, i, q), on(cuda, fam, i, k[lo:hi]), on(cuda, fam, i, v[lo:hi])
+        r = cuda.zeros((qh, d + 2), dtype=cuda.float32, device=f"cuda:{i}")
+        ext.decode(None, r, tq, tk, tv, qh, kvh, d, hi - lo, 0)
+        cuda.cuda.synchronize()
+        res.append(r)
+        outs.append(cuda.zeros((qh, d), dtype=cuda.int16, device=f"cuda:{i}"))
+        sums.append(cuda.zeros(hidden, dtype=cuda.int16, device=f"cuda:{i}"))
+        tparts.append(on(cuda, fam, i, parts[i]))
+        xs.append(ext.Exchange(2, i, max(qh * (d + 2) * 4, 2 * hidden)))
+    addresses = [x.local()[0] for x in xs]
+    for i in range(2):
+        assert fam.sys.bind_device(i) == 1
+        cuda.cuda.set_device(i)
+        xs[i].connect_addresses(addresses)
+    for step in ("fold", "sum"):
+        for i in range(2):
+            assert fam.sys.bind_device(i) == 1
+            cuda.cuda.set_device(i)
+            if step == "fold":
+                xs[i].merge_finish(outs[i], None, res[i], qh, d, 0, wait_ms=2000)
+            else:
+                xs[i].vector_sum(sums[i], tparts[i], hidden, 0, wait_ms=2000)
+        for i in range(2):
+            cuda.cuda.synchronize(i)
+    for i in range(2):
+        assert fam.sys.bind_device(i) == 1
+        cuda.cuda.set_device(i)
+        assert ext.device_status() == 0
+    want = port.residual(q, k, v, qh, kvh, d, n, 0)
+    assert cuda.equal(outs[0].cpu(), outs[1].cpu())
+    assert_close16(outs[0].cpu().numpy().view(np.uint16), want[:, 2:] / want[:, 1:2], FP16, "two ranges folded by the exchange kernel")
+    total = to_bits(from_bits(parts[0], FP16) + from_bits(parts[1], FP16), FP16)
+    assert np.array_equal(sums[0].cpu().numpy().view(np.uint16), total) and np.array_equal(sums[1].cpu().numpy().view(np.uint16), total)
+    for i in range(2):
+        assert fam.sys.bind_device(i) == 1
+        cuda.cuda.set_device(i)
+        xs[i].close()

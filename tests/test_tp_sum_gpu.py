@@ -30,6 +30,33 @@ def _rank(rank, world, port, tmp):
     total = sharded.sum_over_ranks(mine, dist, sharded.family_vector_sum(torch, fam))
     assert fam.sys.compute_completed()
     np.save(Path(tmp) / f"s{rank}.npy", total.cpu().numpy().view(np.uint16))
+    # the same sum as one launch a rank over peer memory, twice (both parities of the exchange)
+    from silvann_b200 import ext
+    peer = sharded.PeerSum(torch, ext, dist, n, 0)
+    for _ in range(2):
+        pushed = peer.sum(mine, wait_ms=5000)
+    torch.cuda.synchronize()
+    assert ext.device_status() == 0
+    np.save(Path(tmp) / f"p{rank}.npy", pushed.cpu().numpy().view(np.uint16))
+    # and a KV range split over the two ranks: each attends its half, the exchange kernel folds
+    qh, kvh, d, L = 8, 1, 128, 4096
+    rng = np.random.default_rng(70)
+    q, k, v = (oracle.to_bits(rng.standard_normal(s, dtype=np.float32), 0) for s in ((qh, d), (L, kvh, d), (L, kvh, d)))
+    shard = sharded.shard_plan(qh, kvh, L, world)[rank]
+    x = sharded.connect_exchange(torch, ext, dist, shard.group, rank, qh * (d + 2) * 4)
+    up = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).cuda()
+    runner = sharded.LongContextRank(torch, ext, shard, d, 0, None, None, 0, up(k[shard.pos_lo:shard.pos_hi]), up(v[shard.pos_lo:shard.pos_hi]), shard.positions,
+                                     dist, None, exchange=x)
+    for _ in range(2):
+        o = runner.step(up(q))
+    torch.cuda.synchronize()
+    assert ext.device_status() == 0
+    np.save(Path(tmp) / f"o{rank}.npy", o.cpu().numpy().view(np.uint16))
+    if rank == 0:
+        r = oracle.port().residual(q, k, v, qh, kvh, d, L, 0)
+        np.save(Path(tmp) / "o_want.npy", r[:, 2:] / r[:, 1:2])
+    dist.barrier()
+    runner.close(); x.close(); peer.close()
     if rank == 0:
         s = np.zeros(n, np.float32)
         for p in parts:
@@ -47,3 +74,8 @@ def test_partial_sums_over_two_processes(cuda, tmp_path):
     mp.spawn(_rank, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     s0, s1, want = (np.load(tmp_path / f) for f in ("s0.npy", "s1.npy", "want.npy"))
     assert np.array_equal(s0, s1) and np.array_equal(s0, want)
+    p0, p1 = np.load(tmp_path / "p0.npy"), np.load(tmp_path / "p1.npy")
+    assert np.array_equal(p0, want) and np.array_equal(p1, want)
+    import oracle
+    o0, o1, o_want = np.load(tmp_path / "o0.npy"), np.load(tmp_path / "o1.npy"), np.load(tmp_path / "o_want.npy")
+    assert np.array_equal(o0, o1) and np.abs(oracle.from_bits(o0, 0) - o_want).max() <= 2e-3

@@ -39,27 +39,4 @@ def assert_close16(got_bits, want_f32, dtype, what, tol=2e-3):
     return float(err.max())
 
 
-class OnCard:
-    """This family on a card, worded as oracle/__init__.py's helpers word an implementation: `ptr(array)` is the address
-    of the array's copy in device memory (made at first sight), `nn` the family's doors, `wait()` the family's
-    compute_completed followed by every copy read back into its array — so a helper written for host pointers drives the
-    card's doors unchanged."""
-
-    def __init__(self, torch, fam):
-        self.torch, self.fam, self.nn, self.over = torch, fam, fam.nn, None
-        self.held = {}
-
-    def ptr(self, a):
-        if a is None:
-            return None
-        key = id(a)
-        if key not in self.held:
-            assert a.flags["C_CONTIGUOUS"]
-            self.held[key] = (a, self.torch.from_numpy(a.view(np.uint8).reshape(-1)).cuda())
-        return self.held[key][1].data_ptr()
-
-    def wait(self):
-        assert self.fam.sys.compute_completed(), "a door refused its launch"
-        for a, t in self.held.values():
-            if a.flags["WRITEABLE"] and a.size:
-                a.view(np.uint8).reshape(-1)[:] = t.cpu().numpy()
+OnCard = oracle.OnCard
