@@ -236,6 +236,11 @@ class Exchange:
         arr = (C.c_uint64 * self.members)(*[int(a) for a in addresses])
         _check(lib().silvann_b200_exchange_connect_addresses(self.handle, arr))
 
+    def connect_alone(self):
+        """For a one-card walk of a many-card plan: this member's own buffer stands in for every absent member's, so the
+        kernel's pushes and flags land somewhere real; the absent members' pieces arrive by deposit()."""
+        self.connect_addresses([self.local()[0]] * self.members)
+
     def merge_finish(self, o, res, res_local, q_heads, head_dim, dtype=FP16, over=None, wait_ms=0, stream=None):
         _check(lib().silvann_b200_exchange_merge_finish(self.handle, addr(o), addr(res), addr(res_local), q_heads, head_dim, dtype, addr(over), wait_ms, stream))
 

@@ -33,6 +33,8 @@ def residuals(rng, members, qh, d):
 def test_fold_equals_the_merge_door_in_member_order(cuda, port, members, index, qh, d, dtype):
     rng = np.random.default_rng(members * 100 + index)
     x = ext.Exchange(members, index, qh * (d + 2) * 4)
+    if members > 1:
+        x.connect_alone()
     for call in range(3):                                                  # three in a row: both parities, and one reused
         parts = residuals(rng, members, qh, d)
         t = [dev(cuda, p) for p in parts]
@@ -65,6 +67,7 @@ def test_fold_equals_the_merge_door_in_member_order(cuda, port, members, index, 
 def test_sum_is_fp32_in_member_order_rounded_once(cuda, members, index, n, dtype):
     rng = np.random.default_rng(n + members)
     x = ext.Exchange(members, index, 2 * n)
+    x.connect_alone()
     for call in range(2):
         parts = [to_bits(rng.standard_normal(n, dtype=np.float32), dtype) for _ in range(members)]
         t = [dev(cuda, p) for p in parts]
@@ -88,6 +91,7 @@ def test_a_member_that_never_arrives_ends_the_wait_with_a_status(cuda):
     qh, d = 8, 128
     rng = np.random.default_rng(5)
     x = ext.Exchange(2, 0, qh * (d + 2) * 4)
+    x.connect_alone()
     mine, theirs = (dev(cuda, r) for r in residuals(rng, 2, qh, d))
     o = cuda.full((qh, d), 0x1234, dtype=cuda.int16, device="cuda")
     assert ext.device_status() == 0

@@ -123,6 +123,7 @@ def test_config4_full_size_two_tiers_and_every_rank_plan(cuda, ref):
                 continue
             me = s.group.index(s.rank)
             x = ext.Exchange(len(s.group), me, s.q_heads * (d + 2) * 4)
+            x.connect_alone()
             for m, r in enumerate(s.group):
                 if r != s.rank:
                     x.deposit(m, piece[r], s.q_heads * (d + 2) * 4)
