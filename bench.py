@@ -16,11 +16,13 @@ process N batches: weak scaling.
                (queries and each sequence's newest K/V row, from pinned host memory through the family's memory_write
                door) and the read-back of the outputs (memory_read door)
   roofline     algorithmic KV bytes per launch / mean launch duration, against the measured HBM copy bandwidth
-  cpu_baseline the reference's own CPU family (oracle/_ref) on this host's cores, on a stated sample of the workload
+  cpu_baseline the reference's own CPU family (compiled unmodified by the checker's build recipe) on this host's cores, over the same batch
   others       the remaining configurations (1, 2, 4, 5), each with its own roofline fraction, single GPU
 
 The KV pool of a step is 3.3 GB, far larger than the 126 MB L2, so no L2 flush is needed between iterations.
-Synthetic data: pools are filled on the device with seeded N(0,1) values (there is no dataset for this path).
+Synthetic data (there is no dataset for this path): numpy PCG64, fixed seeds a configuration; the headline's pools are
+made on the host and uploaded before any timing, so the reference arm (`--impl reference`, which times the reference's
+CPU family on the host's cores) reads the very same values.  `--only long_context` runs configuration 4 alone at any N.
 """
 from __future__ import annotations
 
@@ -124,20 +126,47 @@ def time_loop(torch, fn, steps, warmup):
     return a.elapsed_time(b) / steps
 
 
+def paged_inputs(rank=0):
+    """Configuration 3's layout (seed 1003) and, for `rank`, its queries and the two pools as numpy bit arrays — PCG64,
+    seed 1004 + 1000 * rank.  Both arms of the benchmark read these same arrays: this arm as bf16, the reference arm as
+    the fp16 values that are the same real numbers."""
+    from silvann_b200 import workloads
+    L = workloads.config3_layout()
+    q, k_pool, v_pool = workloads.config3_fill(L, seed=1003 + 1000 * rank)
+    return L, q, k_pool, v_pool
+
+
+def config_of(L):
+    """The `config` object of the JSON line: what the workload is, identical for both arms."""
+    return {"workload": WORKLOAD, "seqs": int(len(L.seq_lens)), "positions": int(L.positions), "kv_bytes_per_step": int(L.kv_bytes),
+            "page_positions": 256, "pool_pages": int(L.pool_pages), "data": "numpy PCG64: layout seed 1003, values seed 1004 (+1000 a rank), fp16-exact bf16 N(0,1)"}
+
+
+def reference_planes(L, q, k_pool, v_pool, which=None):
+    """Every sequence (or those in `which`) gathered from the pools to the contiguous [len][kv_heads][head_dim] planes the
+    reference's doors take, as fp16 bits of the same real numbers (the reference has neither paging nor bf16).  Outside any
+    timed region."""
+    from silvann_b200 import workloads
+    to16 = lambda b: (b.astype(np.uint32) << 16).view(np.float32).astype(np.float16).view(np.uint16)
+    from concurrent.futures import ThreadPoolExecutor
+
+    def one(s):
+        return (to16(q[s]), to16(workloads.gather_sequence(L, k_pool, s)), to16(workloads.gather_sequence(L, v_pool, s)), int(L.seq_lens[s]))
+    with ThreadPoolExecutor(max_workers=max(1, min(8, os.cpu_count() or 1))) as pool:
+        return list(pool.map(one, range(len(L.seq_lens)) if which is None else which))
+
+
 class PagedWorkload:
     """Configuration 3 resident on the current device."""
 
-    def __init__(self, torch, seed_shift=0):
+    def __init__(self, torch, rank=0):
         from silvann_b200 import ext, workloads
         self.torch, self.ext = torch, ext
-        L = self.layout = workloads.config3_layout()
+        L, q, k_pool, v_pool = paged_inputs(rank)
+        self.layout, self.host = L, (q, k_pool, v_pool)
         self.seqs = len(L.seq_lens)
-        gen = torch.Generator(device="cuda")
-        gen.manual_seed(1003 + seed_shift)
-        shape = (L.pool_pages, workloads.PAGE_POSITIONS, L.kv_heads, L.head_dim)
-        self.k_pool = torch.randn(shape, generator=gen, device="cuda", dtype=torch.bfloat16)
-        self.v_pool = torch.randn(shape, generator=gen, device="cuda", dtype=torch.bfloat16)
-        self.q = torch.randn((self.seqs, L.q_heads, L.head_dim), generator=gen, device="cuda", dtype=torch.bfloat16)
+        up = lambda a: torch.from_numpy(a.view(np.int16)).cuda().view(torch.bfloat16)
+        self.k_pool, self.v_pool, self.q = up(k_pool), up(v_pool), up(q)
         self.table = torch.from_numpy(L.page_table).cuda()
         self.out = torch.zeros((self.seqs, L.q_heads, L.head_dim), device="cuda", dtype=torch.bfloat16)
         self.plan = ext.Plan()
@@ -189,50 +218,117 @@ class EndToEnd:
         self.fam.sys.memory_free_host_ram(self.host)
 
 
-def cpu_baseline_paged(wl: PagedWorkload, budget_s=20.0):
-    """The reference's CPU family over a bounded sample of configuration 3: whole sequences, gathered from the pools
-    to the contiguous planes its doors take, attention_scores + attention_mix each.  Answers (GB/s, cores, sample)."""
+def cpu_cores(R):
+    """(threads the reference family used, its own report): its pool beside the caller, plus the caller, who works too."""
+    threads, line = R.pool()
+    return (threads + 1 if threads is not None else (os.cpu_count() or 1)), line
+
+
+def cpu_baseline_paged(wl: PagedWorkload, budget_s=25.0):
+    """The reference's CPU family over configuration 3 — every sequence of the same batch, gathered to the contiguous fp16
+    planes its doors take, attention_scores + attention_mix each — or, where only the restatement is at hand, one short
+    sequence through it."""
     import oracle
     R = oracle.reference()
-    kind = "reference" if R is not None else "port"
-    P = None if R is not None else oracle.port()
     L = wl.layout
-    torch = wl.torch
-    order = np.argsort(L.seq_lens)[::-1]
-    picked, positions = [], 0
-    for s in order[:8]:
-        picked.append(int(s)); positions += int(L.seq_lens[s])
-        if kind == "port" and positions > 20000:
-            break
-    planes = []
-    for s in picked:
-        n = int(L.seq_lens[s])
-        pages = torch.from_numpy(L.page_table[s, :(n + wl.page_positions - 1) // wl.page_positions].astype(np.int64)).cuda()
-        ks = wl.k_pool[pages].reshape(-1, L.kv_heads, L.head_dim)[:n].to(torch.float16).cpu().numpy().view(np.uint16)
-        vs = wl.v_pool[pages].reshape(-1, L.kv_heads, L.head_dim)[:n].to(torch.float16).cpu().numpy().view(np.uint16)
-        qs = wl.q[s].to(torch.float16).cpu().numpy().view(np.uint16)
-        planes.append((qs, ks, vs, n))
+    q, k_pool, v_pool = wl.host
+    if R is None:
+        P = oracle.port()
+        s = int(np.argmin(L.seq_lens))
+        qs, ks, vs, n = reference_planes(L, q, k_pool, v_pool, [s])[0]
+        t0 = time.perf_counter(); P.decode(qs, ks, vs, L.q_heads, L.kv_heads, L.head_dim, n, 0); dt = time.perf_counter() - t0
+        nbytes = n * 2 * L.kv_heads * L.head_dim * 2
+        return {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": 1, "kind": "port", "sample": f"the shortest sequence of the batch ({n} positions), the C restatement, one pass"}
+    planes = reference_planes(L, q, k_pool, v_pool)
     pbuf = np.empty(L.q_heads * int(L.seq_lens.max()), np.float32)
-    best, t_all = None, time.time()
-    for _ in range(5):
+    best, t_all, passes = None, time.time(), 0
+    while passes < 3 and (passes == 0 or time.time() - t_all < budget_s):
         t0 = time.perf_counter()
         for qs, ks, vs, n in planes:
-            if R is not None:
-                R.decode(qs, ks, vs, L.q_heads, L.kv_heads, L.head_dim, n, pbuf[:L.q_heads * n].reshape(L.q_heads, n))
-            else:
-                P.decode(qs, ks, vs, L.q_heads, L.kv_heads, L.head_dim, n, 0)
+            R.decode(qs, ks, vs, L.q_heads, L.kv_heads, L.head_dim, n, pbuf[:L.q_heads * n].reshape(L.q_heads, n))
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
-        if time.time() - t_all > budget_s:
-            break
-    nbytes = positions * 2 * L.kv_heads * L.head_dim * 2
-    cores = (os.cpu_count() or 1) if R is not None else 1
-    return {"value": nbytes / best / 1e9, "unit": UNIT, "cores": cores, "kind": kind,
-            "sample": f"{len(picked)} longest sequences of the batch ({positions} positions, {nbytes / 1e6:.0f} MB of KV), fp16 copies, best of <=5 passes; SILVANN_CPU_AVX512=0"}
+        passes += 1
+    cores, line = cpu_cores(R)
+    return {"value": L.kv_bytes / best / 1e9, "unit": UNIT, "cores": cores, "kind": "reference", "ms_per_step": best * 1e3, "pool_report": line,
+            "sample": f"the whole batch: {len(planes)} sequences, {L.positions} positions, {L.kv_bytes / 1e6:.0f} MB of KV, as fp16 copies of the same values; best of {passes} pass(es); SILVANN_CPU_AVX512=0"}
+
+
+def cpu_baselines_others():
+    """The reference's CPU family timed beside configurations 1, 2, 4 and 5 on this host's cores — the same seeded inputs
+    the parity tests use (numpy PCG64 seeds 1001, 1002, 1004, 1005), one warm-up pass and the best of a few timed ones each
+    (about fifteen seconds in all).  Reported baselines, not targets."""
+    import oracle
+    from silvann_b200 import workloads
+    R = oracle.reference()
+    if R is None:
+        return {}
+    cores, line = cpu_cores(R)
+    to16 = lambda b: (b.astype(np.uint32) << 16).view(np.float32).astype(np.float16).view(np.uint16)
+    out = {}
+
+    def best_of(fn, passes):
+        fn()
+        best = None
+        for _ in range(passes):
+            t0 = time.perf_counter(); fn(); dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        return best
+
+    def entry(value, unit, secs, sample):
+        return {"value": value, "unit": unit, "cores": cores, "kind": "reference", "ms": secs * 1e3, "pool_report": line, "sample": sample}
+
+    w = workloads.config1()
+    p = np.empty((16, 8192), np.float32)
+    t = best_of(lambda: R.decode(w.q, w.k, w.v, 16, 4, 128, 8192, p), 20)
+    out["config1"] = entry(w.kv_bytes / t / 1e9, UNIT, t, "configuration 1 whole: attention_scores + attention_mix, fp16, 8,192 positions; best of 20")
+    w = workloads.config2()
+    q2, k2, v2 = to16(w.q), to16(w.k), to16(w.v)
+    t = best_of(lambda: R.prefill(q2, k2, v2, 16, 2, 256, 4096), 1)
+    out["config2"] = entry(w.flops / t / 1e12, "TFLOP/s", t, "configuration 2 whole: the three causal doors in 256-row chunks as the reference's runtime drives them, 4,096 rows; one timed pass")
+    w = workloads.config4()
+    q4, k4, v4 = to16(w.q), to16(w.k), to16(w.v)
+    p4 = np.empty((32, 262144), np.float32)
+    t = best_of(lambda: R.residual(q4, k4, v4, 32, 4, 128, 262144, p4), 3)
+    out["config4"] = entry(w.kv_bytes / t / 1e9, UNIT, t, "configuration 4 whole, every position in host RAM: attention_weights + attention_residual_mix, 262,144 positions; best of 3")
+    w = workloads.config5()
+    c5, z5, b5, g5, w5 = (to16(x) for x in (w.conved, w.z, w.beta, w.g, w.w))
+    T = 8192
+
+    def prompt():
+        S = np.zeros((32, 128, 128), np.float32)
+        R.deltanet(S, c5[:T], z5[:T], b5[:T], g5[:T], w5, 32, 32, 128, T)
+    t = best_of(prompt, 1)
+    out["config5_prefill"] = entry(T / t, "positions/s", t, "configuration 5's prompt: deltanet_steps_gate over 8,192 positions (the reference has no chunked form); one timed pass")
+    S = np.zeros((32, 128, 128), np.float32)
+
+    def steps():
+        for i in range(T, T + 512):
+            R.deltanet(S, c5[i:i + 1], z5[i:i + 1], b5[i:i + 1], g5[i:i + 1], w5, 32, 32, 128, 1)
+    t = best_of(steps, 1)
+    nbytes = 512 * (2 * 32 * 128 * 128 * 4 + 3 * 32 * 128 * 2 + 2 * 32 * 128 * 2 + 2 * 32 * 2 + 128 * 2)
+    out["config5_decode"] = entry(nbytes / t / 1e9, UNIT, t, "configuration 5's 512 decode steps: deltanet_step a position, one sequence; one timed pass")
+    return out
+
+
+def roofline(bound, work, ms, pk, kernel, traffic=None, how=None):
+    """The roofline object of one kernel: algorithmic bytes (bound "hbm") or flops ("tensor") a launch over the measured time,
+    against the measured peak; `traffic` = DRAM bytes a launch from the kernel's profiler capture (scaled where `how` says)."""
+    if bound == "hbm":
+        achieved, peak, unit, key = work / ms / 1e6, pk["hbm_gbs"], "GB/s", "algorithmic_bytes_per_launch"
+    else:
+        achieved, peak, unit, key = work / ms / 1e9, pk["bf16_tflops"], "TFLOP/s", "algorithmic_flops_per_launch"
+    r = {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak, "traffic": None if traffic is None else int(traffic),
+         "kernel": kernel, key: int(work), "peak_source": pk["source"]}
+    if bound == "hbm":
+        r["peak_note"] = "the measured peak is a copy (read + write); a read-only stream can exceed it slightly"
+    if how:
+        r["traffic_from"] = how
+    return r
 
 
 def gpu_baseline(torch, wl: PagedWorkload, pk, steps):
-    """The reference's own CUDA family (nvidia_cuda12, built unmodified for sm_100 into oracle/_ref) on the same card, door
+    """The reference's own CUDA family (nvidia_cuda12, built unmodified for sm_100 by the checker's build recipe) on the same card, door
     for door: a reported baseline beside the CPU one.  Configuration 3 has no paged form there, so — as for the CPU
     baseline — whole sequences are gathered to the contiguous planes its doors take (outside the timed region) and each is
     attended with attention_scores + attention_mix; configurations 1, 2 and 5 are the door sequences the reference's
@@ -240,7 +336,7 @@ def gpu_baseline(torch, wl: PagedWorkload, pk, steps):
     import oracle
     R = oracle.reference_cuda()
     if R is None:
-        return {"unavailable": "oracle/_ref holds no nvidia_cuda12 family, or it counts no card here"}
+        return {"unavailable": "the reference's nvidia_cuda12 family was not built here, or it counts no card"}
     out = {"kind": "reference nvidia_cuda12 family (sm_100 build), same card, CUDA events"}
     L = wl.layout
     order = np.argsort(L.seq_lens)[::-1][:8]
@@ -632,55 +728,174 @@ def other_workloads(torch, fam, pk, steps, warmup):
     return out
 
 
+# DRAM bytes a launch (dram__bytes_read.sum + dram__bytes_write.sum) over algorithmic bytes, from each kernel's profiler
+# capture on a small case of the same kernel (one summary a kernel and workload is kept with the sources).  A
+# ratio is scaled to the full launch by the launch's algorithmic bytes — each of these kernels passes over its input once,
+# so traffic grows in proportion — and an absolute figure is a capture of the very workload timed here.
+ROOFLINES = {
+    # entry: (bound, kernel, traffic ratio or absolute bytes or None, where the traffic figure comes from)
+    "config1_decode_doors": ("hbm", "sv::decode_kernel<128, fp16, 1>", 1.016, "ratio of the capture of this kernel on a 65,536-position cache, scaled by bytes"),
+    "config1_decode_kernel": ("hbm", "sv::decode_kernel<128, fp16, 1>", 1.016, "ratio of the capture of this kernel on a 65,536-position cache, scaled by bytes"),
+    "config4_long_context_1gpu_resident": ("hbm", "sv::decode_kernel<128, bf16, 1>", 1.016, "ratio of the capture of this kernel on a 65,536-position cache, scaled by bytes"),
+    "tq8_tier_d128": ("hbm", "sv::tq_attend_kernel<128, 8, 1>", 276.6e6, "capture of this workload"),
+    "tq4_tier_d128": ("hbm", "sv::tq_attend_kernel<128, 4, 1>", 142.0e6, "capture of this workload"),
+    "tq8_tier_d256": ("hbm", "sv::tq_attend_kernel<256, 8, 1>", 1.015, "ratio of the head_dim-128 capture, scaled by bytes"),
+    "tq4_tier_d256": ("hbm", "sv::tq_attend_kernel<256, 4, 1>", 1.026, "ratio of the head_dim-128 capture, scaled by bytes"),
+    "tq4_gemv_16384x4096": ("hbm", "sv::tq_gemv_fast_kernel<1, 4>", 33.69e6, "capture of this workload"),
+    "tq8_gemv_16384x4096": ("hbm", "sv::tq_gemv_fast_kernel<1, 8>", 67.43e6, "capture of this workload"),
+    "kda_decode_64heads": ("hbm", "sv::kda_steps_kernel<128, false>", 4.31e6, "capture of this workload (the 8.4 MB state stays in L2 between steps)"),
+    "mla_absorb_64heads": ("hbm", "sv::absorb_kernel", None, None),
+    "mla_expand_64heads": ("hbm", "sv::expand_kernel", None, None),
+    "mla_decode_64heads": ("hbm", "sv::mla_decode_kernel", None, None),
+    "config5_deltanet_decode_1seq": ("hbm", "sv::deltanet_steps_kernel<128, bf16, false, true> (one cluster a head)", None, None),
+    "config5_deltanet_decode_1seq_graph": ("hbm", "sv::deltanet_steps_kernel<128, bf16, false, true> (one cluster a head)", None, None),
+    "config5_deltanet_decode_64seq": ("hbm", "sv::deltanet_steps_kernel<128, bf16, false, false> + deltanet_norm_kernel", 213.3e6, "capture of this workload (part of the written state is still in L2 when the kernel ends)"),
+    "config5_deltanet_prefill_8192": ("hbm", "sv::deltanet_prep_kernel + deltanet_chunk_kernel + deltanet_norm_kernel", 1.921, "ratio of the capture of the three kernels on 2,048 positions (163.3 MB for 85.0 MB), scaled by bytes"),
+    "config2_causal_prefill": ("tensor", "sv::prefill_kernel<256, bf16>", 41.9e6 * 1.001, "the capture on 2,048 rows read its inputs once (21.02 MB for 21.0 MB); scaled by input bytes"),
+}
+
+
+def attach_rooflines(others, pk, cpu):
+    """Gives every entry of `others` its roofline object and, for configurations 1, 2, 4 and 5, the reference CPU family's
+    figure on the same configuration."""
+    beside = {"config1_decode_doors": "config1", "config1_decode_kernel": "config1", "config2_causal_prefill": "config2",
+              "config4_long_context_1gpu_resident": "config4", "config5_deltanet_decode_1seq": "config5_decode",
+              "config5_deltanet_decode_1seq_graph": "config5_decode", "config5_deltanet_prefill_8192": "config5_prefill"}
+    for name, e in others.items():
+        ms = e.get("ms_per_call", e.get("ms_per_step", e.get("ms")))
+        spec = ROOFLINES.get(name)
+        if spec and ms and e.get("value") is not None:
+            bound, kernel, traffic, how = spec
+            work = e.get("algorithmic_bytes") if bound == "hbm" else e.get("algorithmic_flops")
+            if work is None:
+                work = e["value"] * ms * (1e6 if e.get("unit") == UNIT else 1e9)
+            if traffic is not None and traffic < 100.0:
+                traffic = traffic * work
+            e["roofline"] = roofline(bound, work, ms, pk, kernel, traffic, how)
+        if name in beside and beside[name] in cpu:
+            e["cpu_baseline"] = cpu[beside[name]]
+
+
+def pinned_h2d_peak(torch):
+    """This box's pinned host-to-device copy rate: one 1 GiB cudaMemcpyAsync from pinned memory, best of 3, CUDA events."""
+    n = 1 << 30
+    host = torch.empty(n, dtype=torch.uint8).pin_memory()
+    card = torch.empty(n, dtype=torch.uint8, device="cuda")
+    best = None
+    for _ in range(4):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); card.copy_(host, non_blocking=True); b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        best = ms if best is None else min(best, ms)
+    del host, card
+    return n / best / 1e6
+
+
 def long_context(torch, dist, rank, world, steps, pk):
     """Configuration 4 on `world` GPUs: one sequence of 262,144 positions, 32 q heads on 4 kv heads, head_dim 128, bf16;
     kv heads sharded over the ranks (and the range halved among the two ranks of a kv head at 8), the first 65,536
     positions in pinned host RAM and streamed on a side stream.  Timed twice: as specified, and with every position
-    already on the card.  Answers whole-job KV GB/s from the slowest rank's device time."""
-    from silvann_b200 import ext, sharded
+    already on the card.  Strong scaling: the whole job's bytes over the slowest rank's device time, with rank 0's own
+    one-GPU time of the whole problem measured in the same run beside it."""
+    from silvann_b200 import ext, sharded, workloads
     qh, kvh, d, L, HOST = 32, 4, 128, 262144, 65536
     if world not in (1, 2, 4, 8):
         return {"note": f"not run at {world} GPUs"}
+    nbytes = 2 * L * kvh * d * 2
     shard = sharded.shard_plan(qh, kvh, L, world)[rank]
-    gen = torch.Generator(device="cuda"); gen.manual_seed(1004 + rank)
-    n, heads = shard.positions, shard.kv_heads
-    k = torch.randn((n, heads, d), generator=gen, device="cuda", dtype=torch.bfloat16)
-    v = torch.randn((n, heads, d), generator=gen, device="cuda", dtype=torch.bfloat16)
-    q = torch.randn((shard.q_heads, d), generator=gen, device="cuda", dtype=torch.bfloat16)
-    h_len = max(0, min(HOST, shard.pos_hi) - shard.pos_lo)
-    k_host = k[:h_len].cpu().pin_memory() if h_len else None
-    v_host = v[:h_len].cpu().pin_memory() if h_len else None
-    # the ranks that split a kv head's range exchange residuals through the library's own kernel over peer memory; the
-    # buffers' handles travel once, here
-    exchange = sharded.connect_exchange(torch, ext, dist, shard.group, rank, shard.q_heads * (d + 2) * 4) if world > 1 else None
-    if len(shard.group) == 1:
-        exchange = None
+    w = workloads.config4()                                   # numpy PCG64 seed 1004: the same sequence on every rank, each keeps its share
+    up = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).cuda()
     out = {}
-    for tag, (kh, vh, hl, kd, vd, dl) in {"tiered": (k_host, v_host, h_len, k[h_len:] if n > h_len else None, v[h_len:] if n > h_len else None, n - h_len),
-                                           "resident": (None, None, 0, k, v, n)}.items():
-        runner = sharded.LongContextRank(torch, ext, shard, d, ext.BF16, kh, vh, hl, kd, vd, dl, dist, None, chunk_positions=0, stages=3, exchange=exchange)
+
+    def timed(fn, n):
         for _ in range(3):
-            runner.step(q)
+            fn()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for _ in range(steps):
-            runner.step(q)
+        for _ in range(n):
+            fn()
         b.record()
         torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b) / steps], device="cuda", dtype=torch.float64)
+        t = torch.tensor([a.elapsed_time(b) / n], device="cuda", dtype=torch.float64)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-        nbytes = 2 * L * kvh * d * 2
+        return float(t.item())
+
+    # the whole problem on rank 0 alone, every position on the card: the t_1 of this run's strong-scaling figure
+    t1 = torch.zeros(1, device="cuda", dtype=torch.float64)
+    if rank == 0:
+        k1, v1, q1 = up(w.k), up(w.v), up(w.q)
+        o1 = torch.zeros((qh, d), dtype=torch.int16, device="cuda")
+        for _ in range(3):
+            ext.decode(o1, None, q1, k1, v1, qh, kvh, d, L, ext.BF16)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            ext.decode(o1, None, q1, k1, v1, qh, kvh, d, L, ext.BF16)
+        b.record()
+        torch.cuda.synchronize()
+        t1[0] = a.elapsed_time(b) / steps
+        del k1, v1, q1
+    if world > 1:
+        dist.broadcast(t1, 0)
+    t1 = float(t1.item())
+
+    n, heads = shard.positions, shard.kv_heads
+    k = up(w.k[shard.pos_lo:shard.pos_hi, shard.kv_head_lo:shard.kv_head_hi])
+    v = up(w.v[shard.pos_lo:shard.pos_hi, shard.kv_head_lo:shard.kv_head_hi])
+    q = up(w.q[shard.q_head_lo:shard.q_head_hi])
+    del w
+    h_len = max(0, min(HOST, shard.pos_hi) - shard.pos_lo)
+    k_host = k[:h_len].cpu().pin_memory() if h_len else None
+    v_host = v[:h_len].cpu().pin_memory() if h_len else None
+    h2d_peak = pinned_h2d_peak(torch)
+    # the ranks that split a kv head's range exchange residuals through the library's own kernel over peer memory; the
+    # buffers' handles travel once, here
+    exchange = sharded.connect_exchange(torch, ext, dist, shard.group, rank, shard.q_heads * (d + 2) * 4) if world > 1 else None
+    if len(shard.group) == 1:
+        exchange = None
+    for tag, (kh, vh, hl, kd, vd, dl) in {"tiered": (k_host, v_host, h_len, k[h_len:] if n > h_len else None, v[h_len:] if n > h_len else None, n - h_len),
+                                           "resident": (None, None, 0, k, v, n)}.items():
+        runner = sharded.LongContextRank(torch, ext, shard, d, ext.BF16, kh, vh, hl, kd, vd, dl, dist, None, chunk_positions=0, stages=3, exchange=exchange)
+        ms = timed(lambda: runner.step(q), steps)
         out[tag] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_step": ms, "frac_hbm_of_n_gpus": nbytes / ms / 1e6 / (pk["hbm_gbs"] * world)}
         runner.close()
-    out["tiered"]["host_tier_bytes"] = 2 * HOST * kvh * d * 2
-    out["tiered"]["host_tier_gbs"] = out["tiered"]["host_tier_bytes"] / out["tiered"]["ms_per_step"] / 1e6
-    out["note"] = ("kv heads sharded over ranks" + (", each kv head's range halved over two ranks, residuals pushed into the partner's memory and folded by one kernel a rank (no NCCL on the data path)" if world > kvh else ", no collective")
-                   + "; tiered: first 65,536 positions streamed from pinned host RAM each step (PCIe-bound); resident: all positions in HBM")
+    out["resident"]["one_gpu_ms_same_run"] = t1
+    out["resident"]["strong_scaling_efficiency"] = t1 / (world * out["resident"]["ms_per_step"])
+    out["resident"]["roofline"] = roofline("hbm", nbytes / world, out["resident"]["ms_per_step"], pk, "sv::decode_kernel<128, bf16, 1>" + (" + sv::exchange_merge_kernel" if exchange else ""),
+                                           1.016, "ratio of the capture of this kernel on a 65,536-position cache, scaled by bytes; per GPU")
+    host_bytes = 2 * HOST * kvh * d * 2
+    gbs = host_bytes / out["tiered"]["ms_per_step"] / 1e6
+    holders = min(world, kvh)                                 # ranks that hold a share of the host tier (the first range half of every kv head)
+    out["tiered"].update({"host_tier_bytes": host_bytes, "host_tier_gbs": gbs, "host_tier_gbs_per_holding_gpu": gbs / holders,
+                          "pinned_h2d_peak_gbs_measured": h2d_peak, "host_tier_frac_of_h2d_peak": gbs / holders / h2d_peak,
+                          "lower_bound_ms": max(host_bytes / holders / h2d_peak / 1e6, (nbytes - host_bytes) / world / pk["hbm_gbs"] / 1e6)})
+    if exchange is not None:
+        # the exchange alone: a residual each, pushed, waited for and folded — the merge latency of the range split
+        res = torch.zeros((shard.q_heads, d + 2), dtype=torch.float32, device="cuda"); res[:, 1] = 1.0
+        o = torch.zeros((shard.q_heads, d), dtype=torch.int16, device="cuda")
+        out["merge_latency_us"] = timed(lambda: exchange.merge_finish(o, None, res, shard.q_heads, d, ext.BF16), 200) * 1e3
+        exchange.close()
+    if world > 1:
+        # the tensor-parallel sum that follows head-sharded attention, HIDDEN = 5,120 halves: one launch a rank over peer memory,
+        # and the all-gather + vector_sum form beside it
+        hidden = 5120
+        part = torch.from_numpy(np.random.default_rng(50 + rank).standard_normal(hidden).astype(np.float16).view(np.int16)).cuda()
+        peer = sharded.PeerSum(torch, ext, dist, hidden, ext.FP16)
+        total = torch.empty_like(part)
+        out["tp_sum_us"] = timed(lambda: peer.sum(part, total), 200) * 1e3
+        import silvann_b200
+        vsum = sharded.family_vector_sum(torch, silvann_b200.family())
+        out["tp_sum_allgather_us"] = timed(lambda: sharded.sum_over_ranks(part, dist, vsum), 50) * 1e3
+        peer.close()
+    out["note"] = ("kv heads sharded over ranks" + (", each kv head's range halved over two ranks, residuals pushed into the partner's memory and folded by one kernel a rank (no NCCL on the data path)" if world > kvh else ", no exchange")
+                   + "; tiered: first 65,536 positions streamed from pinned host RAM each step (PCIe-bound); resident: all positions in HBM; strong scaling: whole-job bytes over the slowest rank's time")
+    assert ext.device_status() == 0, "a bounded device-side wait ran out during the long-context runs"
     return out
 
 
@@ -699,14 +914,23 @@ def run_ours(args):
     fam = silvann_b200.family()
     assert fam.sys.bind_device(local) == 1, "the family does not take this device (needs sm_100)"
     pk = peaks()
-
-    wl = PagedWorkload(torch, seed_shift=rank)
     steps, warmup = args.steps, max(args.warmup, 3)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.only == "long_context":
+        lc = long_context(torch, dist, rank, world, max(steps, 10), pk)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        if rank == 0:
+            print(json.dumps({"only": "long_context_config4", "n_gpus": world, "long_context_config4": lc}))
+        return
+
+    wl = PagedWorkload(torch, rank)
 
     # ---- value: K steps, inputs resident ----
     for _ in range(warmup):
@@ -751,8 +975,9 @@ def run_ours(args):
     line = {
         "metric": METRIC, "value": kv_all / ms_step / 1e6, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "positions_per_gpu": wl.layout.positions, "kv_bytes_per_gpu_step": wl.kv_bytes,
-                   "l2": "inputs (3.3 GB a step) larger than L2; no flush needed", "sharding": "one independent batch per GPU, no collective"},
+        "config": config_of(wl.layout),
+        "sharding": "one independent batch per GPU (sequences are independent: no collective); the sharded path with an exchange is configuration 4, under long_context_config4",
+        "l2": "inputs (3.3 GB a step) larger than L2; no flush needed",
         "e2e": {"value": kv_all / e2e_ms / 1e6, "unit": UNIT, "h2d_bytes_per_step": e2e.h2d, "d2h_bytes_per_step": e2e.d2h, "ms_per_step": e2e_ms,
                 "note": "plan + upload of queries and each sequence's newest K/V row (pinned host memory, memory_write door) + row append into the pool + decode + memory_read of outputs; the KV pool is the path's resident state"},
         "gpu_launches": int(launches),
@@ -760,16 +985,15 @@ def run_ours(args):
         "device_status": status,
     }
     if rank == 0:
-        achieved = wl.kv_bytes / per_launch_ms / 1e6
-        line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
-                            "traffic": int(wl.kv_bytes * TRAFFIC_PER_ALGORITHMIC_BYTE), "peak_source": pk["source"], "kernel": "sv::decode_kernel<256, bf16, 1>",
-                            "algorithmic_bytes_per_launch": wl.kv_bytes}
+        line["roofline"] = roofline("hbm", wl.kv_bytes, per_launch_ms, pk, "sv::decode_kernel<256, bf16, 1>", 1.016,
+                                    "ratio of the capture of this kernel on a batch of 180,181 positions (374.9 MB for 369.0 MB), scaled by positions")
         if world == 1:
             line["cpu_baseline"] = cpu_baseline_paged(wl)
             if not args.no_others:
                 line["gpu_baseline"] = gpu_baseline(torch, wl, pk, steps)
-            if not args.no_others:
-                line["others"] = other_workloads(torch, fam, pk, steps, warmup)
+                others = other_workloads(torch, fam, pk, steps, warmup)
+                attach_rooflines(others, pk, cpu_baselines_others())
+                line["others"] = others
     e2e.close()
     if not args.no_others:
         del wl, e2e
@@ -784,58 +1008,55 @@ def run_ours(args):
         print(json.dumps(line))
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel: the ncu capture of the same kernel on
-# a smaller batch (profiles/decode_kernel_paged_small.md: 374.9 MB of traffic for 369.0 MB of algorithmic bytes, ratio
-# 1.016) scaled to the full launch by positions — traffic is one pass over K and V, so it grows in proportion.
-TRAFFIC_PER_ALGORITHMIC_BYTE = 1.016
-
-
 # ---------------------------------------------------------------------------------------------------------------------
 # reference arm: the reference's own CPU implementation of the path on this host's cores
 # ---------------------------------------------------------------------------------------------------------------------
 
 def run_reference(args):
+    """The reference's CPU family (compiled unmodified by the checker's build recipe; the C restatement where that is absent) on rank 0's batch of configuration 3:
+    the same layout and the same values this arm reads (numpy PCG64), every sequence gathered to the contiguous fp16 planes
+    the reference's doors take — it has neither paging nor bf16 — outside the timed region.  A step attends the whole batch,
+    attention_scores + attention_mix a sequence, with every host thread the family's pool takes."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     import oracle
-    from silvann_b200 import workloads
     R = oracle.reference()
-    kind = "reference" if R is not None else "port"
-    P = None if R is not None else oracle.port()
-    L = workloads.config3_layout()
-    order = np.argsort(L.seq_lens)[::-1][: (8 if R is not None else 1)]
-    rng = np.random.default_rng(1003)
-    planes, positions = [], 0
-    for s in order:
-        n = int(L.seq_lens[s]) if R is not None else 4096
-        positions += n
-        mk = lambda shape: rng.standard_normal(shape, dtype=np.float32).astype(np.float16).view(np.uint16)
-        planes.append((mk((L.q_heads, L.head_dim)), mk((n, L.kv_heads, L.head_dim)), mk((n, L.kv_heads, L.head_dim)), n))
-    pbuf = np.empty(L.q_heads * max(p[3] for p in planes), np.float32)
-
-    def step():
-        for qs, ks, vs, n in planes:
-            if R is not None:
-                R.decode(qs, ks, vs, L.q_heads, L.kv_heads, L.head_dim, n, pbuf[:L.q_heads * n].reshape(L.q_heads, n))
-            else:
-                P.decode(qs, ks, vs, L.q_heads, L.kv_heads, L.head_dim, n, 0)
+    L, q, k_pool, v_pool = paged_inputs(0)
     steps, warmup = args.steps, max(args.warmup, 3)
+    if R is not None:
+        planes = reference_planes(L, q, k_pool, v_pool)
+        del k_pool, v_pool
+        pbuf = np.empty(L.q_heads * int(L.seq_lens.max()), np.float32)
+        nbytes, kind = L.kv_bytes, "reference"
+        cores, pool_line = cpu_cores(R)
+        sample = f"the whole batch every step: {len(planes)} sequences, {L.positions} positions, {nbytes / 1e6:.0f} MB of KV, fp16 copies of the same values, attention_scores + attention_mix a sequence"
+
+        def step():
+            for qs, ks, vs, n in planes:
+                R.decode(qs, ks, vs, L.q_heads, L.kv_heads, L.head_dim, n, pbuf[:L.q_heads * n].reshape(L.q_heads, n))
+    else:
+        P = oracle.port()
+        s = int(np.argmin(L.seq_lens))
+        planes = reference_planes(L, q, k_pool, v_pool, [s])
+        nbytes, kind, cores, pool_line = planes[0][3] * 2 * L.kv_heads * L.head_dim * 2, "port", 1, None
+        sample = f"the shortest sequence of the batch ({planes[0][3]} positions) through the scalar C restatement every step"
+
+        def step():
+            qs, ks, vs, n = planes[0]
+            P.decode(qs, ks, vs, L.q_heads, L.kv_heads, L.head_dim, n, 0)
     for _ in range(warmup):
         step()
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
     ms = (time.perf_counter() - t0) * 1e3 / steps
-    nbytes = positions * 2 * L.kv_heads * L.head_dim * 2
-    cores = (os.cpu_count() or 1) if R is not None else 1
     value = nbytes / ms / 1e6
-    sample = f"{len(planes)} sequences of the batch ({positions} positions, {nbytes / 1e6:.0f} MB of KV a step), fp16, attention_scores + attention_mix per sequence on the host's cores"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps, "warmup": warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate over fp16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "config": config_of(L),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample, "pool_report": pool_line},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
@@ -994,6 +1215,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the secondary configurations (faster; used under profilers)")
+    ap.add_argument("--only", default=None, choices=["long_context"], help="run configuration 4 alone (any N) and print its object")
     ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, decode_cfg1, decode_cfg1_graph, tq8_small, tq4_small, deltanet_64, deltanet_prefill, prefill_small)")
     args = ap.parse_args()
     if args.case:

@@ -236,11 +236,36 @@ class Reference:
         os.environ.setdefault("SILVANN_CPU_AVX512", "0")     # pin the AVX2 bodies so runs are comparable across hosts
         self.family = Family(path)
         self.nn = self.family.nn
-        self.family.sys.bind_device(0)
         self.over = np.zeros(4, np.uint32)
+        # How many threads the family's pool takes beside the caller is decided from the machine's load when the pool starts
+        # (at binding or on the first launch) and is only ever told through SILVANN_CPU_POOL_REPORT=1 on stderr
+        # (x86_avx2/primitives/pool.cuh:282-289 of the reference tree): bind and make a first launch with stderr caught.
+        import re
+        import tempfile
+        os.environ["SILVANN_CPU_POOL_REPORT"] = "1"
+        q = np.zeros((16, 128), np.uint16); k = np.zeros((512, 4, 128), np.uint16); p = np.zeros((16, 512), np.float32)
+        with tempfile.TemporaryFile() as tmp:
+            keep = os.dup(2)
+            os.dup2(tmp.fileno(), 2)
+            try:
+                self.family.sys.bind_device(0)
+                self.nn.attention_scores(_p(p), _p(q), _p(k), 16, 4, 128, 512)
+                self.nn.attention_mix(_p(np.zeros((16, 128), np.uint16)), _p(p), _p(k), 16, 4, 128, 512, _p(self.over))
+                self.family.sys.compute_completed()
+            finally:
+                os.dup2(keep, 2)
+                os.close(keep)
+            tmp.seek(0)
+            self.pool_line = tmp.read().decode(errors="replace").strip()
+        m = re.search(r"a pool of (\d+) thread", self.pool_line)
+        self.pool_threads = int(m.group(1)) if m else None      # threads beside the caller, who works too
 
     def wait(self):
         self.family.sys.compute_completed()
+
+    def pool(self):
+        """(threads the pool took beside the caller, or None when the family did not say; the family's own line)."""
+        return self.pool_threads, self.pool_line
 
     def scores(self, q, k, qh, kvh, d, length):
         p = np.empty((qh, length), np.float32)

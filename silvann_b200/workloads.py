@@ -23,7 +23,7 @@ def _bits(x: np.ndarray, dtype: int) -> np.ndarray:
         return x.astype(np.float16).view(np.uint16)
     u = x.view(np.uint32)
     b = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
-    small = np.abs((b.astype(np.uint32) << 16).view(np.float32)) < 2.0 ** -17
+    small = (b & 0x7F80) < ((127 - 17) << 7)          # |value| < 2^-17, read off the exponent field
     b[small] &= 0x8000
     return b
 
@@ -115,16 +115,37 @@ def config3_layout(seqs: int = 32, lo: int = 1024, hi: int = 100000) -> PagedLay
     return PagedLayout(lens, table, total, 16, 2, 256, BF16)
 
 
+FILL_CHUNK = 1 << 24
+
+
+def normal_bits_into(seed: int, stream: int, out: np.ndarray, dtype: int) -> None:
+    """Fills `out` (uint16, C order) with N(0,1) bit patterns, FILL_CHUNK elements at a time on a few threads: chunk c is
+    drawn from PCG64(seed) jumped (stream * 4096 + c + 1) times, so the values depend on nothing but (seed, stream, index)
+    and a 1.6-billion-element pool takes seconds, not minutes."""
+    from concurrent.futures import ThreadPoolExecutor
+    import os
+    flat = out.reshape(-1)
+
+    def one(c):
+        rng = np.random.Generator(np.random.PCG64(seed).jumped(stream * 4096 + c + 1))
+        at = c * FILL_CHUNK
+        n = min(FILL_CHUNK, flat.size - at)
+        flat[at:at + n] = _bits(rng.standard_normal(n, dtype=np.float32), dtype)
+    chunks = (flat.size + FILL_CHUNK - 1) // FILL_CHUNK
+    with ThreadPoolExecutor(max_workers=max(1, min(8, os.cpu_count() or 1))) as pool:
+        list(pool.map(one, range(chunks)))
+
+
 def config3_fill(layout: PagedLayout, seed: int = 1003):
-    """q and the two pools for a layout, on the host (use only at test scale: the benchmark fills its pools on the
-    device).  Pool rows past a sequence's end are filled with NaN bit patterns on purpose: a kernel must not let them
-    reach its output."""
+    """q and the two pools for a layout, on the host.  Pool rows past a sequence's end are filled with NaN bit patterns
+    on purpose: a kernel must not let them reach its output."""
     rng = np.random.default_rng(seed + 1)
     L = layout
     q = normal_bits(rng, (len(L.seq_lens), L.q_heads, L.head_dim), L.dtype)
     shape = (L.pool_pages, PAGE_POSITIONS, L.kv_heads, L.head_dim)
-    k_pool = normal_bits(rng, shape, L.dtype)
-    v_pool = normal_bits(rng, shape, L.dtype)
+    k_pool, v_pool = np.empty(shape, np.uint16), np.empty(shape, np.uint16)
+    normal_bits_into(seed + 1, 1, k_pool, L.dtype)
+    normal_bits_into(seed + 1, 2, v_pool, L.dtype)
     for s, n in enumerate(L.seq_lens):
         tail = int(n) % PAGE_POSITIONS
         if tail:
