@@ -318,6 +318,8 @@ def roofline(bound, work, ms, pk, kernel, traffic=None, how=None):
         achieved, peak, unit, key = work / ms / 1e6, pk["hbm_gbs"], "GB/s", "algorithmic_bytes_per_launch"
     else:
         achieved, peak, unit, key = work / ms / 1e9, pk["bf16_tflops"], "TFLOP/s", "algorithmic_flops_per_launch"
+    if traffic is not None and traffic < 100.0:            # a ratio of DRAM bytes to algorithmic bytes, from a capture of a smaller case
+        traffic = traffic * work if bound == "hbm" else None
     r = {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak, "traffic": None if traffic is None else int(traffic),
          "kernel": kernel, key: int(work), "peak_source": pk["source"]}
     if bound == "hbm":
@@ -591,7 +593,7 @@ def other_workloads(torch, fam, pk, steps, warmup):
                 ms = time_loop(torch, tq_rows, max(steps // 2, 10), 3)
                 assert ext.counters()["fused_residual"] > before, "the coded rows pair did not take the fused kernel"
                 flops = 4.0 * rows16 * tqh * dh * Lt
-                out["tq8_tier_d128_rows16"] = {"value": rows16 * Lt / ms * 1e3, "unit": "row-positions/s", "ms_per_call": ms, "tflops": flops / ms / 1e9,
+                out["tq8_tier_d128_rows16"] = {"value": rows16 * Lt / ms * 1e3, "unit": "row-positions/s", "ms_per_call": ms, "tflops": flops / ms / 1e9, "algorithmic_bytes": nbytes,
                                                "note": "16 rows of a prompt chunk x 32q/4kv heads of 128 over 262,144 positions coded at 8 bits, one launch"}
             del kc, vc, ks, vs
     torch.cuda.empty_cache()
@@ -663,7 +665,7 @@ def other_workloads(torch, fam, pk, steps, warmup):
         fam.nn.index_scores(iscores.data_ptr(), iq.data_ptr(), iw.data_ptr(), pooled.data_ptr(), ih, idim, pools, C.c_float(0.088))
         fam.nn.index_select(iindex.data_ptr(), icount.data_ptr(), iscores.data_ptr(), pools, topk, kpool, pools * kpool, 3)
     ms = time_loop(torch, indexer, max(steps * 5, 50), 5)
-    out["glm_indexer_8192pools"] = {"value": pools / ms * 1e3, "unit": "pools/s", "ms_per_call": ms,
+    out["glm_indexer_8192pools"] = {"value": pools / ms * 1e3, "unit": "pools/s", "ms_per_call": ms, "algorithmic_bytes": pools * idim * 2 + ih * idim * 2 + pools * 4 * 2 + topk * kpool * 4,
                                     "note": "index_scores + index_select: 32 heads of 128 over 8,192 pooled keys, the top 512 pools as positions (two launches)"}
 
     # configuration 5: recurrent decode steps (batched so that state traffic is real) and the prompt
@@ -708,7 +710,7 @@ def other_workloads(torch, fam, pk, steps, warmup):
     o = torch.zeros((T, heads * d), device="cuda", dtype=torch.bfloat16)
     ms = time_loop(torch, lambda: ext.deltanet(S, conved, z, beta, g, w, o, heads, heads, d, T, 1, 0, ext.BF16), 3, 1)
     nbytes = T * (3 * heads * d * 2 + 2 * heads * d * 2 + 4 * heads) + 2 * heads * d * d * 4
-    out["config5_deltanet_prefill_8192"] = {"value": T / ms * 1e3, "unit": "positions/s", "ms": ms, "frac_hbm": nbytes / ms / 1e6 / hbm,
+    out["config5_deltanet_prefill_8192"] = {"value": T / ms * 1e3, "unit": "positions/s", "ms": ms, "frac_hbm": nbytes / ms / 1e6 / hbm, "algorithmic_bytes": nbytes,
                                             "tflops": 7.0 * d * d * heads * T / ms / 1e9,
                                             "note": "one sequence, 8,192 positions, 64 at a time (chunked form), fp32 FMA"}
 
@@ -739,6 +741,8 @@ ROOFLINES = {
     "config4_long_context_1gpu_resident": ("hbm", "sv::decode_kernel<128, bf16, 1>", 1.016, "ratio of the capture of this kernel on a 65,536-position cache, scaled by bytes"),
     "tq8_tier_d128": ("hbm", "sv::tq_attend_kernel<128, 8, 1>", 276.6e6, "capture of this workload"),
     "tq4_tier_d128": ("hbm", "sv::tq_attend_kernel<128, 4, 1>", 142.0e6, "capture of this workload"),
+    "tq8_tier_d128_rows16": ("hbm", "sv::tq_attend_kernel<128, 8, 2> (16 rows a launch: latency- and issue-bound, far from either roof)", None, None),
+    "glm_indexer_8192pools": ("hbm", "sv::index_scores_kernel + sv::index_select_kernel (two launches, 2 MB: launch-bound)", None, None),
     "tq8_tier_d256": ("hbm", "sv::tq_attend_kernel<256, 8, 1>", 1.015, "ratio of the head_dim-128 capture, scaled by bytes"),
     "tq4_tier_d256": ("hbm", "sv::tq_attend_kernel<256, 4, 1>", 1.026, "ratio of the head_dim-128 capture, scaled by bytes"),
     "tq4_gemv_16384x4096": ("hbm", "sv::tq_gemv_fast_kernel<1, 4>", 33.69e6, "capture of this workload"),
@@ -769,8 +773,6 @@ def attach_rooflines(others, pk, cpu):
             work = e.get("algorithmic_bytes") if bound == "hbm" else e.get("algorithmic_flops")
             if work is None:
                 work = e["value"] * ms * (1e6 if e.get("unit") == UNIT else 1e9)
-            if traffic is not None and traffic < 100.0:
-                traffic = traffic * work
             e["roofline"] = roofline(bound, work, ms, pk, kernel, traffic, how)
         if name in beside and beside[name] in cpu:
             e["cpu_baseline"] = cpu[beside[name]]
