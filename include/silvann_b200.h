@@ -291,7 +291,8 @@ const silvann_b200_family* silvann_silicon_family_get(uint32_t abi_version);
 #define SILVANN_B200_COUNTER_LAUNCHES        6   /* kernels of this library launched, all paths */
 #define SILVANN_B200_COUNTER_EXT_CALLS       7   /* silvann_b200_* compute entry points called */
 #define SILVANN_B200_COUNTER_GEMV_FAST       8   /* coded matrix-vector doors answered by the tensor-core kernel */
-#define SILVANN_B200_COUNTERS                9
+#define SILVANN_B200_COUNTER_FUSED_LATENT     9   /* scores_grouped + softmax_rows + mix over one latent answered by one kernel */
+#define SILVANN_B200_COUNTERS                10
 
 const char* silvann_b200_last_error(void);
 /* Copies min(n, SILVANN_B200_COUNTERS) process-wide counters into out; reset != 0 zeroes them afterwards. */
@@ -439,6 +440,15 @@ int silvann_b200_tier_decode_exchange(silvann_b200_tier* tier, silvann_b200_exch
  * answer of attention_weights_rows + attention_residual_mix_rows (nn/gpu/doors.cuh:406-431) for a later merge. */
 int silvann_b200_prefill(void* o, float* res, const void* q, const void* k, const void* v, uint64_t q_heads, uint64_t kv_heads,
                          uint64_t head_dim, uint64_t first, uint64_t rows, int dtype, sv_fault* over, void* stream);
+
+/* One query position of latent attention in one pass — attention_scores_grouped + attention_softmax_rows + attention_mix
+ * when the keys and the values are the SAME rows (kernels.cuh:931-950, 1085-1100, 1144-1164; the sequence GLM's decode runs,
+ * ai_z__glm_5_3 layer__abi.cuh:279-289): `heads` (32 or 64) query heads over one kv head whose rows are `latent_dim` (512)
+ * wide.  q [heads][512]; latent [length][512]; o [heads][512] 16-bit and/or res [heads][514] fp32 (m, l, acc).  blocks 0 lets
+ * the library cut the positions over the card's SMs; with more than one block the blocks' partial residuals meet in scratch
+ * the library keeps a device (allocated on first use) and a second small kernel folds them. */
+int silvann_b200_mla_decode(void* o, float* res, const void* q, const void* latent, uint64_t heads, uint64_t latent_dim,
+                            uint64_t length, uint32_t blocks, int dtype, sv_fault* over, void* stream);
 
 /* Gated DeltaNet over `rows` positions of `seqs` independent sequences (deltanet_steps_gate, kernels.cuh:650-718,
  * 2131-2165, with a dtype and a batch).  S [seqs][v_heads][d][d] fp32 in place; conved [seqs][rows][(2·k_heads +

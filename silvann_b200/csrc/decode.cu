@@ -21,6 +21,7 @@
 #include <atomic>
 #include <mutex>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace sv {
@@ -78,6 +79,8 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     uint32_t* ticket_s = (uint32_t*)abort_flag + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    /* blocks a cluster (1 when the launch has none): the splits of a cluster meet in shared memory, clusters in scratch */
+    const int CL = (int)cluster_nctarank(), crank = (int)cluster_ctarank();
 
     /* ---- which work is this block's ---- */
     int seq, kvh, head0, heads, tile_begin, tile_end, split, nsplit, slot_base, slot_stride, ticket;
@@ -86,8 +89,12 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
         seq = it.seq; kvh = it.kvh; head0 = it.head0; heads = it.heads; tile_begin = it.tile_begin; tile_end = it.tile_end;
         split = it.split; nsplit = it.nsplit; slot_base = it.slot_base; slot_stride = 1; ticket = it.ticket;
     } else {
-        const int hb = blockIdx.x % P.head_blocks, rest = blockIdx.x / P.head_blocks;
-        kvh = rest % P.kv_heads; split = rest / P.kv_heads; nsplit = P.nsplit; seq = 0;
+        /* without clusters the splits of a group are spread over the grid (head blocks fastest); with clusters the splits are
+         * fastest, so that the blocks of a cluster are neighbouring splits of one group */
+        int hb;
+        if (CL > 1) { split = blockIdx.x % P.nsplit; const int rest = blockIdx.x / P.nsplit; hb = rest % P.head_blocks; kvh = rest / P.head_blocks; }
+        else { hb = blockIdx.x % P.head_blocks; const int rest = blockIdx.x / P.head_blocks; kvh = rest % P.kv_heads; split = rest / P.kv_heads; }
+        nsplit = P.nsplit; seq = 0;
         head0 = kvh * P.group + hb * P.heads_per_block;
         heads = min((int)P.heads_per_block, (int)P.group - hb * (int)P.heads_per_block);
         const int tiles = (P.length + BT - 1) / BT, chunk = (tiles + nsplit - 1) / nsplit;
@@ -114,6 +121,13 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
         for (int k = 0; k < KS; ++k) { oacc[n][k][0] = oacc[n][k][1] = oacc[n][k][2] = oacc[n][k][3] = 0.f; }
     }
 
+    /* Programmatic dependent launch (a no-op for a launch without the attribute).  The next launch on the stream may be
+     * scheduled as soon as every block of this one has got this far, so its blocks take SMs as this grid's blocks leave them
+     * instead of waiting for the whole grid and a launch latency.  What such an early block may do before the grid ahead of
+     * it has completed is limited to what that grid cannot have written: this kernel only ever READS the K and V planes, so
+     * a following launch of it may stream K and V at once; everything else — the query, scratch, tickets, outputs — is
+     * touched only after griddepcontrol.wait, which returns when the grid ahead has completed and its writes are visible. */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (warp == NW) {
         /* ---- producer: one lane issues every TMA load of this block ---- */
         if (lane == 0 && nt > 0) {
@@ -142,9 +156,14 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
                     tma_load_2d_hint(st + Cfg::K_BYTES + c * Cfg::BOX_BYTES, &vmap, &full[s], kvh * D + c * 64, y, pol);
             }
         }
+        asm volatile("griddepcontrol.wait;" ::: "memory");
     } else {
         /* ---- consumers: stage the query heads (zero rows past `heads`), then walk the tiles ---- */
         const uint16_t* qsrc = P.q + ((size_t)seq * P.q_heads + head0) * D;
+        /* the query may be the work of the grid ahead, so it is read after the wait; asking L2 for its lines beforehand is
+         * harmless (L2 is where writes meet) and takes a trip to memory off the path */
+        if (tid < heads * (D / 64)) asm volatile("prefetch.global.L2 [%0];" ::"l"(qsrc + (size_t)tid * 64));
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int i = tid; i < HPB * (D / 8); i += NW * 32) {
             const int r = i / (D / 8), j = i % (D / 8);
             uint4 val = make_uint4(0u, 0u, 0u, 0u);
@@ -299,8 +318,73 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
 
     const uint32_t SF = P.slot_floats;                /* floats per head in scratch: D + 2 */
     const bool single = (nsplit == 1);
-    float* my_slot = P.partials + (size_t)(slot_base + split * slot_stride) * HPB * SF;
     bool hit = false;
+    if (CL > 1) {
+        /* ---- the splits of this cluster meet in shared memory ----
+         * Every block leaves its (m, l, acc) in its own shared memory; after the cluster's barrier block r of the cluster
+         * folds columns [r D/CL, (r+1) D/CL) of every head over all CL blocks — read from the peers' shared memory, every
+         * load asked for before the first is used, summed in split order — and writes that slice: straight to the answer
+         * when the cluster holds all of the group's splits, else to the cluster's slot in scratch, where the clusters of
+         * the group meet as single blocks do.  A second barrier keeps every block alive until its peers have read it. */
+        float* bacc = wo + (size_t)NW * HPB * D;          /* [HPB][D] */
+        float* bm = bacc + HPB * D;                      /* [HPB] log2 units */
+        float* bl = bm + HPB;                            /* [HPB] */
+        for (int i = tid; i < HPB * D; i += (NW + 1) * 32) {
+            const int h = i / D, e = i % D;
+            float m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) m = fmaxf(m, wm[w * HPB + h]);
+            float acc = 0.f, l = 0.f;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) {
+                const float mw = wm[w * HPB + h];
+                if (mw != -INFINITY) { const float f = fast_exp2(mw - m); acc += wo[(size_t)(w * HPB + h) * D + e] * f; l += wl[w * HPB + h] * f; }
+            }
+            bacc[i] = acc;
+            if (e == 0) { bm[h] = m; bl[h] = l; }
+        }
+        cluster_sync_all();
+        const int DS = D / CL;                            /* columns of a head this block folds (CL divides D: it is a power of two <= 16) */
+        const int ecl = nsplit / CL, cidx = split / CL;   /* clusters in the group, and which of them this is */
+        float* cslot = P.partials + (size_t)(slot_base + cidx * slot_stride) * HPB * SF;
+        for (int i = tid; i < heads * DS; i += (NW + 1) * 32) {
+            const int h = i / DS, e = crank * DS + i % DS;
+            float pm[16], pl[16], pa[16];
+#pragma unroll
+            for (int r = 0; r < 16; ++r)
+                if (r < CL) { pm[r] = ld_cluster_f32(bm + h, (uint32_t)r); pl[r] = ld_cluster_f32(bl + h, (uint32_t)r); pa[r] = ld_cluster_f32(bacc + h * D + e, (uint32_t)r); }
+            float m = -INFINITY;
+#pragma unroll
+            for (int r = 0; r < 16; ++r) if (r < CL) m = fmaxf(m, pm[r]);
+            float acc = 0.f, l = 0.f;
+#pragma unroll
+            for (int r = 0; r < 16; ++r)
+                if (r < CL && pm[r] != -INFINITY) { const float f = fast_exp2(pm[r] - m); acc += pa[r] * f; l += pl[r] * f; }
+            if (ecl == 1) {
+                const size_t hq = (size_t)seq * P.q_heads + head0 + h;
+                if (P.o) ((uint16_t*)P.o)[hq * D + e] = E::from_float(acc / l, hit);
+                if (P.res) {
+                    float* r = P.res + hq * (D + 2);
+                    r[2 + e] = acc;
+                    if (e == 0) { r[0] = m * SV_LN2; r[1] = l; }
+                }
+            } else {
+                cslot[(size_t)h * D + e] = acc;
+                if (e == 0) { cslot[HPB * D + 2 * h] = m; cslot[HPB * D + 2 * h + 1] = l; }
+            }
+        }
+        if (ecl > 1) __threadfence();
+        cluster_sync_all();
+        if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
+        if (ecl == 1 || crank != 0) return;
+        /* the cluster's first block carries the cluster's partial to the meeting of the group's clusters */
+        nsplit = ecl; split = cidx; hit = false;
+        if (tid == 0) *ticket_s = atomicAdd(&P.tickets[ticket], 1u);
+        __syncthreads();
+        if (*ticket_s != (uint32_t)(nsplit - 1)) return;
+        __threadfence();
+    } else {
+    float* my_slot = P.partials + (size_t)(slot_base + split * slot_stride) * HPB * SF;
     for (int i = tid; i < heads * D; i += (NW + 1) * 32) {
         const int h = i / D, e = i % D;
         float m = -INFINITY;
@@ -338,6 +422,7 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     __syncthreads();
     if (*ticket_s != (uint32_t)(nsplit - 1)) return;
     __threadfence();
+    }
     /* The block is alone with its group by now and bound by trips to L2, so everything it needs is asked for at once:
      * a thread owns four neighbouring elements of a head over one run of splits and has that run's accumulators in
      * flight (16 bytes a load, no branch between the loads) while the warps that own a head fetch the splits' (m, l) and
@@ -536,7 +621,7 @@ void decode_auto_split(uint32_t length, uint32_t q_heads, uint32_t kv_heads, uin
 
 template <int D, int DT, int NHT>
 static cudaError_t launch_one(const CUtensorMap& km, const CUtensorMap& vm, const DecodeParams& P, uint32_t blocks,
-                              cudaStream_t st) {
+                              cudaStream_t st, uint32_t cluster = 1u, bool pdl = false) {
     using Cfg = DecodeCfg<D>;
     const size_t smem = 1024 + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES + Cfg::BOXES * 8 * NHT * 128 + 2 * Cfg::STAGES * 8 + 64;
     static std::atomic<bool> attr_set[DEVICES_MAX];       /* setting the attribute twice is harmless; the flag only saves the call */
@@ -546,9 +631,57 @@ static cudaError_t launch_one(const CUtensorMap& km, const CUtensorMap& vm, cons
         if (e != cudaSuccess) return e;
         attr_set[d].store(true, std::memory_order_release);
     }
+    if (cluster > 1u || pdl) {
+        static std::atomic<bool> wide_set[DEVICES_MAX];   /* clusters of 16 blocks are beyond the portable size of 8 */
+        if (cluster > 8u && d >= 0 && d < DEVICES_MAX && !wide_set[d].load(std::memory_order_acquire)) {
+            cudaError_t e = cudaFuncSetAttribute(decode_kernel<D, DT, NHT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            if (e != cudaSuccess) return e;
+            wide_set[d].store(true, std::memory_order_release);
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(blocks); cfg.blockDim = dim3((Cfg::NW + 1) * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+        cudaLaunchAttribute at[2];
+        unsigned na = 0;
+        if (cluster > 1u) {
+            at[na].id = cudaLaunchAttributeClusterDimension;
+            at[na].val.clusterDim.x = cluster; at[na].val.clusterDim.y = 1; at[na].val.clusterDim.z = 1;
+            ++na;
+        }
+        if (pdl) { at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[na].val.programmaticStreamSerializationAllowed = 1; ++na; }
+        cfg.attrs = at; cfg.numAttrs = na;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, decode_kernel<D, DT, NHT>, km, vm, P);
+        if (e != cudaSuccess) return e;
+        note_launch(1);
+        return cudaGetLastError();
+    }
     decode_kernel<D, DT, NHT><<<blocks, (Cfg::NW + 1) * 32, smem, st>>>(km, vm, P);
     note_launch(1);
     return cudaGetLastError();
+}
+
+/* How many neighbouring splits of a group share a thread-block cluster (1: none).  SILVANN_B200_DECODE_CLUSTER overrides
+ * the choice (1, 2, 4, 8 or 16), SILVANN_B200_DECODE_SPLITS the split count of one-sequence calls that leave it open. */
+static uint32_t env_u32(const char* name) {
+    const char* v = getenv(name);
+    return v ? (uint32_t)strtoul(v, nullptr, 10) : 0u;
+}
+/* One-sequence calls over a short cache are bound by how the splits meet, not by the stream.  When a kv head's whole
+ * cache is at most four tiles a block for a cluster's worth of blocks, the group's splits are ONE cluster and meet in
+ * shared memory: no scratch, no ticket, no second pass through L2 (configuration 1: 10.3 -> 8.6 microseconds a launch,
+ * 7.7 with the launch overlapped).  Answers the cluster size, or 1. */
+static uint32_t decode_cluster_for(uint32_t tiles, uint32_t lanes, uint32_t sms, uint32_t* ns) {
+    static const uint32_t forced = env_u32("SILVANN_B200_DECODE_CLUSTER");
+    if (forced == 1u) return 1u;
+    if (forced == 2u || forced == 4u || forced == 8u || forced == 16u) {
+        uint32_t c = forced;
+        while (c > 1u && c > *ns) c >>= 1;
+        if (c > 1u) *ns = (*ns + c - 1u) / c * c;          /* whole clusters: splits past the last tile are empty and fold as nothing */
+        return c;
+    }
+    uint32_t c = 16u;
+    while (c > 1u && (c * lanes > sms || c > tiles)) c >>= 1;
+    if (c >= 4u && (tiles + c - 1u) / c <= 4u) { *ns = c; return c; }
+    return 1u;
 }
 
 cudaError_t decode_launch(const DecodeCall& c) {
@@ -569,24 +702,44 @@ cudaError_t decode_launch(const DecodeCall& c) {
     P.length = c.length; P.head_blocks = hb; P.heads_per_block = hpb;
     P.slot_floats = c.head_dim + 2u;
     P.scale_log2 = (1.0f / sqrtf((float)c.head_dim)) * SV_LOG2E;
-    uint32_t blocks;
+    uint32_t blocks, cluster = 1u;
+    /* one-sequence calls are a few microseconds long and often follow each other (a layer after a layer): they are launched
+     * as programmatic dependents; SILVANN_B200_DECODE_PDL=0 turns that off */
+    static const bool pdl_on = []() { const char* v = getenv("SILVANN_B200_DECODE_PDL"); return !(v && v[0] == '0'); }();
+    const bool pdl = pdl_on && !c.items;
     if (c.items) { blocks = c.n_items; P.nsplit = 0; }
     else {
+        static const uint32_t splits_forced = env_u32("SILVANN_B200_DECODE_SPLITS");
         uint32_t ns = c.nsplit, hb2 = hb;
+        if (ns == 0 && splits_forced) ns = splits_forced;
         if (ns == 0) decode_auto_split(c.length, c.q_heads, c.kv_heads, c.head_dim, device_sm_count(), &ns, &hb2);
         const uint32_t tiles = (c.length + BT - 1) / BT;
         if (ns > tiles) ns = tiles;
         if (ns > 1024u) ns = 1024u;
         const uint32_t chunk = (tiles + ns - 1) / ns;
         ns = (tiles + chunk - 1) / chunk;
-        if ((uint64_t)ns * c.kv_heads * hb > c.scratch.slots || (uint64_t)c.kv_heads * hb > c.scratch.tickets_n) return cudaErrorInvalidValue;
+        if (c.nsplit == 0 || splits_forced) cluster = decode_cluster_for(tiles, c.kv_heads * hb, device_sm_count(), &ns);
+        if ((uint64_t)(ns / cluster) * c.kv_heads * hb > c.scratch.slots || (uint64_t)c.kv_heads * hb > c.scratch.tickets_n) return cudaErrorInvalidValue;
         P.nsplit = ns; blocks = ns * c.kv_heads * hb;
     }
     if (blocks == 0) return cudaSuccess;
     if ((size_t)hpb * P.slot_floats > (size_t)16 * c.scratch.slot_floats) return cudaErrorInvalidValue;
 
-#define SV_DECODE_CASE(DD, TT, NN) return launch_one<DD, TT, NN>(km, vm, P, blocks, c.stream)
     const int nht = hpb == 8 ? 1 : 2;
+    if (cluster > 1u) {
+        /* a cluster the card cannot place (its size, the blocks' shared memory) is an error of the launch, not of the call:
+         * the same work goes out again as single blocks that meet in scratch */
+        cudaError_t e = cudaErrorInvalidValue;
+#define SV_DECODE_TRY(DD, TT) e = (nht == 1) ? launch_one<DD, TT, 1>(km, vm, P, blocks, c.stream, cluster, pdl) : launch_one<DD, TT, 2>(km, vm, P, blocks, c.stream, cluster, pdl)
+        if (c.dtype == SV_DTYPE_FP16) { if (c.head_dim == 64) SV_DECODE_TRY(64, SV_DTYPE_FP16); else if (c.head_dim == 128) SV_DECODE_TRY(128, SV_DTYPE_FP16); else SV_DECODE_TRY(256, SV_DTYPE_FP16); }
+        else { if (c.head_dim == 64) SV_DECODE_TRY(64, SV_DTYPE_BF16); else if (c.head_dim == 128) SV_DECODE_TRY(128, SV_DTYPE_BF16); else SV_DECODE_TRY(256, SV_DTYPE_BF16); }
+#undef SV_DECODE_TRY
+        if (e == cudaSuccess) return e;
+        (void)cudaGetLastError();
+        cluster = 1u;
+        if ((uint64_t)P.nsplit * c.kv_heads * hb > c.scratch.slots) return cudaErrorInvalidValue;
+    }
+#define SV_DECODE_CASE(DD, TT, NN) return launch_one<DD, TT, NN>(km, vm, P, blocks, c.stream, cluster, pdl)
     if (c.dtype == SV_DTYPE_FP16) {
         if (c.head_dim == 64)  { if (nht == 1) SV_DECODE_CASE(64, SV_DTYPE_FP16, 1);  else SV_DECODE_CASE(64, SV_DTYPE_FP16, 2); }
         if (c.head_dim == 128) { if (nht == 1) SV_DECODE_CASE(128, SV_DTYPE_FP16, 1); else SV_DECODE_CASE(128, SV_DTYPE_FP16, 2); }

@@ -327,6 +327,18 @@ SV_EXPORT int silvann_b200_prefill(void* o, float* res, const void* q, const voi
     return e == cudaSuccess ? SILVANN_B200_OK : cuda_fail("prefill: launch", e);
 }
 
+SV_EXPORT int silvann_b200_mla_decode(void* o, float* res, const void* q, const void* latent, uint64_t heads, uint64_t latent_dim, uint64_t length,
+                                      uint32_t blocks, int dtype, sv_fault* over, void* stream) {
+    called();
+    if ((!o && !res) || !q || !latent) return fail(SILVANN_B200_E_ARGUMENT, "mla_decode: a null operand");
+    if (!dtype_ok(dtype)) return fail(SILVANN_B200_E_ARGUMENT, "mla_decode: dtype %d", dtype);
+    if (!sv::mla_decode_fits(q, latent, heads, latent_dim, length) || ((uintptr_t)res & 3u))
+        return fail(SILVANN_B200_E_ARGUMENT, "mla_decode: %llu heads (32 or 64) over a latent of %llu (512), %llu positions, or an operand's alignment is outside the kernel's fit",
+                    (unsigned long long)heads, (unsigned long long)latent_dim, (unsigned long long)length);
+    cudaError_t e = sv::mla_decode_launch(o, res, q, latent, heads, length, dtype, blocks, over, (cudaStream_t)stream);
+    return e == cudaSuccess ? SILVANN_B200_OK : cuda_fail("mla_decode: launch", e);
+}
+
 SV_EXPORT int silvann_b200_deltanet(float* S, const void* conved, const void* z, const void* beta, const void* g, const void* w, void* out,
                                     float* readout, uint64_t k_heads, uint64_t v_heads, uint64_t head_dim, uint64_t rows, uint32_t seqs, uint32_t gate,
                                     int dtype, sv_fault* over, void* stream) {

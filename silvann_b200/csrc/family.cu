@@ -55,7 +55,7 @@ static bool fuse_enabled() {
 }
 
 /* ---- the deferred first door of a pair, per device ---- */
-enum PendingKind { NONE = 0, SCORES, WEIGHTS, CAUSAL_RAW, CAUSAL_SOFT, WEIGHTS_ROWS, WEIGHTS_TQ };
+enum PendingKind { NONE = 0, SCORES, WEIGHTS, CAUSAL_RAW, CAUSAL_SOFT, WEIGHTS_ROWS, WEIGHTS_TQ, GROUPED_RAW, GROUPED_SOFT };
 struct Pending {
     int kind;
     float* p; float* res; const uint16_t* q; const uint16_t* k;      /* WEIGHTS_TQ: k is the key codes */
@@ -81,6 +81,11 @@ static void run_pending_locked(Pending& pd) {
                                                                   x.res + r * x.qh * (x.d + 2), 0));
             break;
         }
+        case GROUPED_RAW: check("attention_scores_grouped", sv::scores_launch(x.p, x.q, x.k, x.qh, x.kvh, x.d, x.length, 2, nullptr, 0)); break;
+        case GROUPED_SOFT:          /* the two doors that were recorded, as worded */
+            check("attention_scores_grouped", sv::scores_launch(x.p, x.q, x.k, x.qh, x.kvh, x.d, x.length, 2, nullptr, 0));
+            check("attention_softmax_rows", sv::softmax_rows_launch(x.p, x.qh, x.length, 0));
+            break;
         case WEIGHTS_TQ:  check("attention_weights_tq", sv::tq_weights_launch(x.p, x.res, x.q, (const uint8_t*)x.k, x.scales, x.qh, x.kvh, x.d, x.length, x.width, x.rows, 0)); break;
         default: return;
     }
@@ -242,6 +247,14 @@ static void d_attention_mix(sv_h16* o, const float* p, const sv_h16* v, sv_u64 q
     if (dev >= 0 && dev < DEVICES_MAX) {
         std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
         Pending& x = g_pending[dev];
+        if (x.kind == GROUPED_SOFT && x.p == p && x.k == v && x.qh == qh && x.kvh == kvh && x.d == d && x.length == length && ((uintptr_t)o & 1u) == 0) {
+            const Pending y = x;
+            x.kind = NONE;
+            const cudaError_t e = sv::mla_decode_launch(o, nullptr, y.q, y.k, qh, length, SV_DTYPE_FP16, 0, over, 0);
+            if (e == cudaSuccess) { bump(SILVANN_B200_COUNTER_FUSED_LATENT); return; }
+            (void)cudaGetLastError();               /* the fused launch was not taken: the three doors as worded */
+            x = y;
+        }
         if (x.kind == SCORES && x.p == p && x.qh == qh && x.kvh == kvh && x.d == d && x.length == length) {
             sv::DecodeCall c = decode_call_for(x, o, nullptr, v, over);
             if (sv::decode_fits(c) && sv::decode_device_scratch(&c.scratch) == cudaSuccess) {
@@ -291,12 +304,28 @@ static void d_attention_finish(sv_h16* o, const float* res, sv_u64 qh, sv_u64 d,
     flush();
     check("attention_finish", sv::finish_launch(o, res, qh, d, over, SV_DTYPE_FP16, 0));
 }
+/* Latent attention at decode is three doors on one buffer — scores_grouped, softmax_rows, mix with the keys' rows as the
+ * values (ai_z__glm_5_3 layer__abi.cuh:279-289).  The first two are recorded when the shape is the fused kernel's; if the
+ * mix that follows names the same weights and the same rows, one kernel answers all three and the weights are never
+ * written; any other door first runs what was recorded, as worded. */
 static void d_attention_scores_grouped(float* p, const sv_h16* q, const sv_h16* k, sv_u64 qh, sv_u64 kvh, sv_u64 d, sv_u64 length) {
     flush();
+    const int dev = current_device();
+    if (fuse_enabled() && dev >= 0 && dev < DEVICES_MAX && kvh == 1 && sv::mla_decode_fits(q, k, qh, d, length)) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        g_pending[dev] = Pending{GROUPED_RAW, p, nullptr, q, k, qh, kvh, d, length, 0, 0};
+        return;
+    }
     check("attention_scores_grouped", sv::scores_launch(p, q, k, qh, kvh, d, length, 2, nullptr, 0));
 }
 static void d_attention_softmax_rows(float* p, sv_u64 rows, sv_u64 length) {
-    flush();
+    const int dev = current_device();
+    if (dev >= 0 && dev < DEVICES_MAX) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        Pending& x = g_pending[dev];
+        if (x.kind == GROUPED_RAW && x.p == p && x.qh == rows && x.length == length) { x.kind = GROUPED_SOFT; return; }
+        run_pending_locked(x);
+    }
     check("attention_softmax_rows", sv::softmax_rows_launch(p, rows, length, 0));
 }
 static void d_attention_causal_scores(float* p, const sv_h16* q, const sv_h16* k, sv_u64 qh, sv_u64 kvh, sv_u64 d, sv_u64 first, sv_u64 rows) {

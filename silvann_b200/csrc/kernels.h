@@ -155,6 +155,13 @@ cudaError_t tq_residual_mix_launch(float* res, const float* p, const uint8_t* co
 
 }  // namespace sv
 
+/* ---- latent attention at decode on tcgen05 / TMEM: many heads over one 512-wide latent that is key and value (mla_decode.cu) ---- */
+namespace sv {
+bool mla_decode_fits(const void* q, const void* latent, uint64_t heads, uint64_t head_dim, uint64_t length);
+cudaError_t mla_decode_launch(void* o, float* res, const void* q, const void* latent, uint64_t heads, uint64_t length, int dtype, uint32_t blocks,
+                              unsigned int* over, cudaStream_t st);
+}  // namespace sv
+
 /* ---- causal GQA prefill on tcgen05 / TMEM (prefill.cu) ------------------------------------------------------- */
 namespace sv {
 struct PrefillCall {

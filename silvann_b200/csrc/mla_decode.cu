@@ -1,0 +1,385 @@
+/* mla_decode.cu — one query position of latent attention (MLA) on the 5th-generation tensor cores: many heads over ONE
+ * 512-wide latent row a key that is both the key and the value.
+ *
+ * The reference runs GLM's decode attention as three doors on that latent — attention_scores_grouped (raw scaled scores
+ * of 64 heads, engine/src/packages/nn/gpu/kernels/kernels.cuh:931-950), attention_softmax_rows (:1085-1100) and
+ * attention_mix (:1144-1164), in engine/src/packages/ai_z__glm_5_3/cpu/opcodes/layer__abi.cuh:279-289 — with an fp32
+ * weights buffer between them and the latent read twice.  Its CUDA family has a shared-memory tiled kernel for the scores
+ * (engine/src/silicon_families/nvidia_cuda12/overrides/attention.cuh:960-1137).  Here the three are one pass: a latent
+ * tile crosses HBM once, sits in shared memory once, and serves both products.
+ *
+ * The work is 128 flop a byte — a contraction, so it runs on tcgen05 — and the shapes are awkward for it: 64 heads would
+ * fill half of an M = 128 accumulator.  So the products are taken TRANSPOSED, keys as the M dimension:
+ *     S^T [128 keys x heads]      = C [128 keys x 512] . Q^T          A = the latent tile, K-major;  B = Q, K-major
+ *     O^T [512 x heads] (4 x 128) = C^T [512 x 128 keys] . P^T        A = the SAME tile read MN-major; B = P^T, K-major
+ * with N = heads (32 or 64) and nothing padded.  TMEM holds S^T (heads columns) and the four blocks of O^T (4 x heads
+ * columns) for the whole run of tiles.
+ *
+ * A block walks a range of 128-key tiles.  Roles: warp 0 loads (Q once; a tile as eight 64-column boxes of 16 KB into an
+ * eight-slot ring — a box is refilled as soon as the value product that read it has completed, so the ring is one tile
+ * deep but never drains at once); warp 1 issues every MMA; warps 2-5 are the softmax, a thread a key: it reads its key's
+ * scores of all heads from its TMEM lane, the tile's maximum a head is found across threads (an integer-ordered
+ * redux.sync a warp, then four values a head through shared memory), the reference maximum is kept unless a tile exceeds
+ * it by 2^8 (the weights and the normaliser are relative to the same reference, which is exact), the 16-bit weights go to
+ * shared memory transposed as the B operand, and each thread carries its own share of every head's normaliser, summed in
+ * a fixed order at the end.  The block's (m, l, acc) leaves in the reference's residual layout — straight to the answer
+ * when the block had the whole range, else to scratch, where a second small kernel folds the blocks' partials in range
+ * order with attention_merge's arithmetic (kernels.cuh:1243-1255) and finishes.
+ *
+ * Algorithmic bytes: positions x 512 x 2 (the latent once) + 2 x heads x 512 x 2.  Every mbarrier wait is bounded; a wait
+ * that runs out raises "B2TO" in the device status word and every role falls through to the exit, where TMEM is released.
+ * No cluster, no multicast. */
+#include "common.cuh"
+#include "kernels.h"
+#include "residual.cuh"
+#include "tcgen05.cuh"
+#include "tensormap.cuh"
+#include <atomic>
+#include <mutex>
+
+namespace sv {
+
+static constexpr int ML_D = 512;            /* latent width */
+static constexpr int ML_BK = 128;           /* keys a tile */
+static constexpr int ML_BOXES = ML_D / 64;  /* 64-column boxes a tile */
+static constexpr int ML_BOX_BYTES = ML_BK * 128;
+static constexpr int ML_THREADS = 6 * 32;
+
+struct MlaParams {
+    uint16_t* o;              /* [heads][512] or null */
+    float* res;               /* [heads][514] or null */
+    float* partials;          /* [blocks][heads][514] when blocks > 1 */
+    unsigned int* over;
+    unsigned int* status;
+    uint32_t length, tiles, blocks;
+    float scale_log2;
+};
+
+template <int NH> struct MlaCfg {
+    static constexpr int Q_BOX_BYTES = NH * 128;
+    static constexpr int Q_BYTES = ML_BOXES * Q_BOX_BYTES;
+    static constexpr int C_BYTES = ML_BOXES * ML_BOX_BYTES;          /* 128 KB: one tile */
+    static constexpr int P_BOX_BYTES = NH * 128;                     /* P^T: heads rows of 64 keys */
+    static constexpr int P_BYTES = 2 * P_BOX_BYTES;
+    static constexpr int T_S = 0, T_O = NH;                          /* TMEM columns: S^T, then O^T blocks NH apart */
+    static constexpr int TMEM_COLS = (5 * NH <= 256) ? 256 : 512;
+    static constexpr size_t SMEM = 1024 + Q_BYTES + C_BYTES + P_BYTES + 512 /*barriers*/ + (4 * NH + 3 * NH) * 4;
+};
+
+__device__ __forceinline__ int ordered_int(float x) { const int i = __float_as_int(x); return i ^ ((i >> 31) & 0x7FFFFFFF); }
+__device__ __forceinline__ float ordered_float(int i) { return __int_as_float(i ^ ((i >> 31) & 0x7FFFFFFF)); }
+__device__ __forceinline__ int warp_max_s32(int v) {
+    int r;
+    asm volatile("redux.sync.max.s32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
+    return r;
+}
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int NH, int DT>
+__global__ void __launch_bounds__(ML_THREADS, 1)
+mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap cmap, const MlaParams P) {
+    using Cfg = MlaCfg<NH>;
+    using E = Elem<DT>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_s = smem;
+    uint8_t* c_s = q_s + Cfg::Q_BYTES;
+    uint8_t* p_s = c_s + Cfg::C_BYTES;
+    uint64_t* bars = (uint64_t*)(p_s + Cfg::P_BYTES);
+    uint64_t* full = bars;                    /* 8: a box has landed */
+    uint64_t* empty = full + ML_BOXES;        /* 8: the value product that read the box has completed */
+    uint64_t* q_full = empty + ML_BOXES;
+    uint64_t* s_full = q_full + 1;            /* the tile's scores are in TMEM */
+    uint64_t* p_full = s_full + 1;            /* the tile's weights are in shared memory (4 warps arrive) */
+    uint64_t* pv_done = p_full + 1;           /* the tile's value products have completed */
+    uint32_t* tmem_slot = (uint32_t*)(pv_done + 1);
+    volatile uint32_t* abort_flag = (volatile uint32_t*)(tmem_slot + 1);
+    float* wmax = (float*)((uint8_t*)bars + 512);      /* [4 warps][NH] a warp's maximum a head (log2 units) */
+    float* mref = wmax + 4 * NH;                        /* [NH] the reference maximum a head, log2 units */
+    float* fac = mref + NH;                             /* [NH] this tile's rescale factor a head */
+    float* lsum = fac + NH;                             /* [NH] the normaliser, at the end */
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    /* this block's tiles: a contiguous share of the range, as even as whole tiles allow */
+    const int tile0 = (int)(((uint64_t)blockIdx.x * P.tiles) / P.blocks), tile1 = (int)(((uint64_t)(blockIdx.x + 1) * P.tiles) / P.blocks);
+    const int nt = tile1 - tile0;
+
+    if (tid == 0) {
+        for (int i = 0; i < ML_BOXES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+        mbar_init(q_full, 1); mbar_init(s_full, 1); mbar_init(p_full, 4); mbar_init(pv_done, 1);
+        *abort_flag = 0u;
+        mbar_fence_init();
+    }
+    if (tid < NH) mref[tid] = -INFINITY;
+    if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        /* ---------------- loads: Q once, then the tiles, a box at a time as its slot comes free ---------------- */
+        if (lane == 0 && nt > 0) {
+            tma_prefetch_desc(&qmap); tma_prefetch_desc(&cmap);
+            const uint64_t pol = l2_policy_evict_first();
+            mbar_expect_tx(q_full, Cfg::Q_BYTES);
+#pragma unroll
+            for (int i = 0; i < ML_BOXES; ++i) tma_load_2d(q_s + i * Cfg::Q_BOX_BYTES, &qmap, q_full, i * 64, 0);
+            bool ok = true;
+            for (int t = 0; ok && t < nt; ++t)
+                for (int i = 0; i < ML_BOXES; ++i) {
+                    if (t > 0 && !mbar_wait(&empty[i], (t - 1) & 1, abort_flag, P.status)) { ok = false; break; }
+                    mbar_expect_tx(&full[i], ML_BOX_BYTES);
+                    tma_load_2d_hint(c_s + i * ML_BOX_BYTES, &cmap, &full[i], i * 64, (tile0 + t) * ML_BK, pol);
+                }
+        }
+    } else if (warp == 1) {
+        /* ---------------- every MMA: S^T(t) as the boxes land, then — the weights written — the four blocks of O^T ------- */
+        if (lane == 0 && nt > 0) {
+            constexpr uint32_t IDESC_S = idesc_f16(DT == SV_DTYPE_BF16, 0, ML_BK, NH);
+            constexpr uint32_t IDESC_O = idesc_f16_a_mn(DT == SV_DTYPE_BF16, 0, 128, NH);
+            const uint64_t qd = smem_desc_sw128(smem_u32(q_s), 16, 1024), cd = smem_desc_sw128(smem_u32(c_s), 16, 1024);
+            const uint64_t ct = smem_desc_sw128(smem_u32(c_s), ML_BOX_BYTES, 1024);       /* the tile read transposed: 64-column groups a box apart */
+            const uint64_t pd = smem_desc_sw128(smem_u32(p_s), 16, 1024);
+            const uint32_t qd_lo = (uint32_t)qd, qd_hi = (uint32_t)(qd >> 32), cd_lo = (uint32_t)cd, cd_hi = (uint32_t)(cd >> 32);
+            const uint32_t ct_lo = (uint32_t)ct, ct_hi = (uint32_t)(ct >> 32), pd_lo = (uint32_t)pd, pd_hi = (uint32_t)(pd >> 32);
+            bool ok = mbar_wait(q_full, 0, abort_flag, P.status);
+            for (int t = 0; ok && t < nt; ++t) {
+                for (int i = 0; ok && i < ML_BOXES; ++i) {
+                    if (!mbar_wait(&full[i], t & 1, abort_flag, P.status)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)            /* 16 latent columns a step: 32 bytes inside the box's 128-byte rows */
+                        tc_mma_ss2(tmem + Cfg::T_S, cd_lo + i * (ML_BOX_BYTES >> 4) + kk * 2, cd_hi, qd_lo + i * (Cfg::Q_BOX_BYTES >> 4) + kk * 2, qd_hi,
+                                   IDESC_S, (i > 0 || kk > 0) ? 1u : 0u);
+                }
+                if (!ok) break;
+                tc_commit(s_full);
+                if (!mbar_wait(p_full, t & 1, abort_flag, P.status)) break;
+                tc_fence_after();
+#pragma unroll 1
+                for (int j = 0; j < 4; ++j) {
+                    /* O^T block j: latent columns 128 j .. 128 j + 127 = boxes 2j and 2j + 1; sixteen keys a step = two 8-key groups */
+#pragma unroll
+                    for (int kk = 0; kk < ML_BK / 16; ++kk)
+                        tc_mma_ss2(tmem + Cfg::T_O + j * NH, ct_lo + (2 * j) * (ML_BOX_BYTES >> 4) + kk * (2048 >> 4), ct_hi,
+                                   pd_lo + (kk / 4) * (Cfg::P_BOX_BYTES >> 4) + (kk % 4) * 2, pd_hi, IDESC_O, (t > 0 || kk > 0) ? 1u : 0u);
+                    tc_commit(&empty[2 * j]);
+                    tc_commit(&empty[2 * j + 1]);
+                }
+                tc_commit(pv_done);
+            }
+        }
+    } else {
+        /* ---------------- softmax: a thread a key of the tile ---------------- */
+        const int quad = warp & 3, sw = warp - 2;
+        const int r = quad * 32 + lane;                              /* key within the tile = TMEM lane */
+        const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+        const int st = sw * 32 + lane;                               /* 0..127 among the softmax threads */
+        float lpart[NH];
+#pragma unroll
+        for (int h = 0; h < NH; ++h) lpart[h] = 0.f;
+        /* The four warps meet at two block barriers a tile, so they walk the tiles together whatever happens: a warp whose
+         * wait ran out goes on as a bystander (it keeps the barriers' count whole and touches nothing else). */
+        bool alive = nt > 0;
+        for (int t = 0; t < nt; ++t) {
+            if (alive && !__all_sync(0xffffffffu, mbar_wait(s_full, t & 1, abort_flag, P.status))) alive = false;
+            uint32_t sv[NH];
+            if (alive) {
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < NH; c += 32) tmem_ld32(tmem + Cfg::T_S + c + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&sv[c]));
+                tmem_wait_ld();
+                tc_fence_before();
+                const bool valid = (uint32_t)((tile0 + t) * ML_BK + r) < P.length;   /* rows past the end arrive as zeros: not scores */
+                /* the tile's maximum a head: over the warp's 32 keys here, over the four warps through shared memory */
+#pragma unroll
+                for (int h = 0; h < NH; ++h) {
+                    const float sc = valid ? __uint_as_float(sv[h]) * P.scale_log2 : -INFINITY;
+                    sv[h] = __float_as_uint(sc);
+                    const int m = warp_max_s32(ordered_int(sc));
+                    if ((h & 31) == lane) wmax[sw * NH + h] = ordered_float(m);
+                }
+            }
+            softmax_bar();
+            if (st < NH) {
+                const float mx = fmaxf(fmaxf(wmax[st], wmax[NH + st]), fmaxf(wmax[2 * NH + st], wmax[3 * NH + st]));
+                const float old = mref[st];
+                float f = 1.f;
+                if ((mx > old + 8.f) || (old == -INFINITY && mx != -INFINITY)) { f = (old == -INFINITY) ? 0.f : fast_exp2(old - mx); mref[st] = mx; }
+                fac[st] = f;
+            }
+            softmax_bar();
+            if (!alive) continue;
+            bool rescale = false;
+            const int kb = r >> 6, kr = r & 63;
+            uint8_t* prow = p_s + kb * Cfg::P_BOX_BYTES + (kr & 7) * 2;
+#pragma unroll
+            for (int h = 0; h < NH; ++h) {
+                const float mu = mref[h], f = fac[h];
+                rescale |= (f != 1.f);
+                const float p = (mu == -INFINITY) ? 0.f : fast_exp2(__uint_as_float(sv[h]) - mu);
+                const uint32_t w = E::pack2(p, 0.f);
+                lpart[h] = lpart[h] * f + E::unpack2(w).x;           /* the normaliser sums what the MMA will see */
+                *reinterpret_cast<uint16_t*>(prow + swz128((uint32_t)h, (uint32_t)(kr >> 3))) = (uint16_t)(w & 0xFFFFu);
+            }
+            if (t > 0 && __any_sync(0xffffffffu, rescale)) {
+                /* s_full(t) is behind every box of tile t, and every box was refilled only after the value product of t - 1
+                 * that read it had completed: O^T is settled.  A thread scales its lane (a latent column) of the four blocks. */
+#pragma unroll 1
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int c = 0; c < NH; c += 32) {
+                        uint32_t ov[32];
+                        tmem_ld32(tmem + Cfg::T_O + j * NH + c + lane_off, ov);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int x = 0; x < 32; ++x) ov[x] = __float_as_uint(__uint_as_float(ov[x]) * fac[c + x]);
+                        tmem_st32(tmem + Cfg::T_O + j * NH + c + lane_off, ov);
+                    }
+                tmem_wait_st();
+            }
+            fence_proxy_async_smem();                                /* the weights, for the MMA's reads */
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+        }
+        /* ---- the block's (m, l, acc): the normaliser in a fixed order, O^T out of TMEM ---- */
+        if (alive && !__all_sync(0xffffffffu, mbar_wait(pv_done, (nt - 1) & 1, abort_flag, P.status))) alive = false;
+        tc_fence_after();
+        float* red = (float*)c_s;                                     /* [NH][128]: the ring is free now */
+        if (alive) {
+#pragma unroll
+            for (int h = 0; h < NH; ++h) red[h * 128 + st] = lpart[h];
+        }
+        softmax_bar();
+        if (alive && st < NH) {
+            float l = 0.f;
+            for (int x = 0; x < 128; ++x) l += red[st * 128 + x];
+            lsum[st] = l;
+        }
+        softmax_bar();
+        if (alive) {
+            const bool whole = P.blocks == 1u;
+            float* out = whole ? P.res : P.partials + (size_t)blockIdx.x * NH * (ML_D + 2);
+            bool hit = false;
+            if (out && st < NH) { out[(size_t)st * (ML_D + 2)] = mref[st] * SV_LN2; out[(size_t)st * (ML_D + 2) + 1] = lsum[st]; }
+#pragma unroll 1
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int c = 0; c < NH; c += 32) {
+                    uint32_t ov[32];
+                    tmem_ld32(tmem + Cfg::T_O + j * NH + c + lane_off, ov);
+                    tmem_wait_ld();
+                    const int e = j * 128 + r;                        /* this lane's latent column */
+#pragma unroll
+                    for (int x = 0; x < 32; ++x) {
+                        const int h = c + x;
+                        const float a = __uint_as_float(ov[x]);
+                        if (out) out[(size_t)h * (ML_D + 2) + 2 + e] = a;
+                        if (whole && P.o) P.o[(size_t)h * ML_D + e] = E::from_float(a / lsum[h], hit);
+                    }
+                }
+            if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
+            tc_fence_before();
+        }
+    }
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, Cfg::TMEM_COLS); }
+}
+
+/* The blocks' partial residuals folded in range order (attention_merge's arithmetic with the common maximum taken first,
+ * so the order of the sums is fixed), then attention_finish: a block a head and a quarter of its columns. */
+template <int DT>
+__global__ void __launch_bounds__(128) mla_fold_kernel(uint16_t* o, float* res, const float* partials, uint32_t heads, uint32_t blocks, unsigned int* over) {
+    using E = Elem<DT>;
+    const uint32_t h = blockIdx.x / 4u, e = (blockIdx.x % 4u) * 128u + threadIdx.x, w = ML_D + 2;
+    const size_t step = (size_t)heads * w;
+    const float* base = partials + (size_t)h * w;
+    float m = -INFINITY;
+    for (uint32_t s = 0; s < blocks; ++s) m = fmaxf(m, __ldcg(base + s * step));
+    float acc = 0.f, l = 0.f;
+    for (uint32_t s = 0; s < blocks; ++s) {
+        const float ms = __ldcg(base + s * step);
+        if (ms == -INFINITY) continue;
+        const float f = expf(ms - m);
+        acc = __fmaf_rn(__ldcg(base + s * step + 2 + e), f, acc);
+        l = __fmaf_rn(__ldcg(base + s * step + 1), f, l);
+    }
+    bool hit = false;
+    if (res) { res[(size_t)h * w + 2 + e] = acc; if (e == 0) { res[(size_t)h * w] = m; res[(size_t)h * w + 1] = l; } }
+    if (o) o[(size_t)h * ML_D + e] = E::from_float(acc / l, hit);
+    if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
+}
+
+/* ---------------------------------------------------------------------------------------------------------------------- */
+
+static std::mutex g_mla_lock;
+static float* g_mla_partials[64];
+static size_t g_mla_floats[64];
+
+bool mla_decode_fits(const void* q, const void* latent, uint64_t heads, uint64_t head_dim, uint64_t length) {
+    if (head_dim != ML_D || (heads != 32 && heads != 64)) return false;
+    if (length == 0 || length > 0x7FFFFF00ull) return false;
+    if (((uintptr_t)q | (uintptr_t)latent) & 15u) return false;
+    return encode_tiled_fn() != nullptr;
+}
+
+template <int NH, int DT>
+static cudaError_t launch_mla(uint16_t* o, float* res, const void* q, const void* latent, uint64_t length, uint32_t blocks_want, unsigned int* over, cudaStream_t st) {
+    using Cfg = MlaCfg<NH>;
+    const bool bf = DT == SV_DTYPE_BF16;
+    CUtensorMap qm, cm;
+    if (!make_map_2d_sw128(&qm, q, ML_D, NH, ML_D * 2, 64u, NH, bf)) return cudaErrorInvalidValue;
+    if (!make_map_2d_sw128(&cm, latent, ML_D, length, ML_D * 2, 64u, ML_BK, bf)) return cudaErrorInvalidValue;
+    MlaParams P;
+    P.o = o; P.res = res; P.over = over; P.status = device_status_word();
+    P.length = (uint32_t)length; P.tiles = (uint32_t)((length + ML_BK - 1) / ML_BK);
+    uint32_t blocks = blocks_want ? blocks_want : device_sm_count();
+    if (blocks > P.tiles) blocks = P.tiles;
+    P.blocks = blocks;
+    P.scale_log2 = (1.0f / sqrtf((float)ML_D)) * SV_LOG2E;
+    P.partials = nullptr;
+    int d = 0;
+    cudaError_t e = cudaGetDevice(&d);
+    if (e != cudaSuccess) return e;
+    if (d < 0 || d >= 64) return cudaErrorInvalidDevice;
+    if (blocks > 1u) {
+        std::lock_guard<std::mutex> hold(g_mla_lock);
+        const size_t want = (size_t)device_sm_count() * 64 * (ML_D + 2);
+        if (g_mla_floats[d] < want) {
+            if ((e = cudaMalloc(&g_mla_partials[d], want * sizeof(float))) != cudaSuccess) return e;
+            g_mla_floats[d] = want;
+        }
+        if ((size_t)blocks * NH * (ML_D + 2) > g_mla_floats[d]) return cudaErrorInvalidValue;
+        P.partials = g_mla_partials[d];
+    }
+    static std::atomic<bool> attr_set[64];
+    if (!attr_set[d].load(std::memory_order_acquire)) {
+        if ((e = cudaFuncSetAttribute(mla_decode_kernel<NH, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM)) != cudaSuccess) return e;
+        attr_set[d].store(true, std::memory_order_release);
+    }
+    mla_decode_kernel<NH, DT><<<blocks, ML_THREADS, Cfg::SMEM, st>>>(qm, cm, P);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    note_launch(1);
+    if (blocks > 1u) {
+        mla_fold_kernel<DT><<<NH * 4, 128, 0, st>>>(o, res, P.partials, NH, blocks, over);
+        note_launch(1);
+        e = cudaGetLastError();
+    }
+    return e;
+}
+
+/* q [heads][512]; latent [length][512] (key and value); o [heads][512] 16-bit and/or res [heads][514] (m, l, acc).
+ * blocks 0 = as many as the card has SMs (at most one a tile). */
+cudaError_t mla_decode_launch(void* o, float* res, const void* q, const void* latent, uint64_t heads, uint64_t length, int dtype, uint32_t blocks,
+                              unsigned int* over, cudaStream_t st) {
+#define SV_ML(NN) (dtype == SV_DTYPE_BF16 ? launch_mla<NN, SV_DTYPE_BF16>((uint16_t*)o, res, q, latent, length, blocks, over, st) \
+                                          : launch_mla<NN, SV_DTYPE_FP16>((uint16_t*)o, res, q, latent, length, blocks, over, st))
+    if (heads == 64) return SV_ML(64);
+    if (heads == 32) return SV_ML(32);
+#undef SV_ML
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace sv

@@ -11,7 +11,7 @@ from . import library_path
 
 FP16, BF16 = 0, 1
 OK, E_ARGUMENT, E_CUDA, E_TIMEOUT, E_STATE = 0, 1, 2, 3, 4
-COUNTERS = ("fused_decode", "fused_residual", "fused_prefill", "flushed", "refused", "deltanet", "launches", "ext_calls", "gemv_fast")
+COUNTERS = ("fused_decode", "fused_residual", "fused_prefill", "flushed", "refused", "deltanet", "launches", "ext_calls", "gemv_fast", "fused_latent")
 EXPORTS = (
     "silvann_silicon_family_get", "silvann_b200_last_error", "silvann_b200_counters_read", "silvann_b200_device_status",
     "silvann_b200_decode", "silvann_b200_decode_noalloc", "silvann_b200_merge", "silvann_b200_finish", "silvann_b200_plan_create",
@@ -20,7 +20,7 @@ EXPORTS = (
     "silvann_b200_tier_decode", "silvann_b200_tier_stats", "silvann_b200_tier_decode_exchange",
     "silvann_b200_exchange_create", "silvann_b200_exchange_destroy", "silvann_b200_exchange_local", "silvann_b200_exchange_handle",
     "silvann_b200_exchange_connect_handles", "silvann_b200_exchange_connect_addresses", "silvann_b200_exchange_merge_finish",
-    "silvann_b200_exchange_vector_sum", "silvann_b200_exchange_deposit",
+    "silvann_b200_exchange_vector_sum", "silvann_b200_exchange_deposit", "silvann_b200_mla_decode",
 )
 
 
@@ -65,6 +65,7 @@ def lib():
             "silvann_b200_tier_decode": [vp, vp, vp, vp, vp, vp, u64, vp, vp, u64, vp, vp],
             "silvann_b200_tier_stats": [vp, vp, vp],
             "silvann_b200_tier_decode_exchange": [vp, vp, vp, vp, vp, vp, vp, u64, vp, vp, u64, vp, u32, vp],
+            "silvann_b200_mla_decode": [vp, vp, vp, vp, u64, u64, u64, u32, i32, vp, vp],
             "silvann_b200_exchange_create": [vp, u32, u32, u64],
             "silvann_b200_exchange_destroy": [vp],
             "silvann_b200_exchange_local": [vp, vp, vp],
@@ -253,6 +254,10 @@ class Exchange:
 
 def prefill(o, q, k, v, q_heads, kv_heads, head_dim, first, rows, dtype=FP16, over=None, stream=None, res=None):
     _check(lib().silvann_b200_prefill(addr(o), addr(res), addr(q), addr(k), addr(v), q_heads, kv_heads, head_dim, first, rows, dtype, addr(over), stream))
+
+
+def mla_decode(o, res, q, latent, heads, length, dtype=FP16, blocks=0, latent_dim=512, over=None, stream=None):
+    _check(lib().silvann_b200_mla_decode(addr(o), addr(res), addr(q), addr(latent), heads, latent_dim, length, blocks, dtype, addr(over), stream))
 
 
 def deltanet(S, conved, z, beta, g, w, out, k_heads, v_heads, head_dim, rows, seqs=1, gate=0, dtype=FP16, over=None, stream=None, readout=None):
