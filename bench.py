@@ -451,6 +451,24 @@ def gpu_baseline(torch, wl: PagedWorkload, pk, steps):
         nbytes = 2 * Lt * tkvh * (rb + 2)
         out[f"tq{width}_tier_d128"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms}
         del kc, vc, ks, vs, tp
+    # latent attention at decode through the reference's own kernels for the three doors (its shared-memory tiled scores kernel)
+    for Lm, copies in ((2048, 16), (65536, 4)):
+        lat = torch.randn((copies, Lm, 512), generator=gen, device="cuda", dtype=torch.float16)
+        qm = torch.randn((64, 512), generator=gen, device="cuda", dtype=torch.float16) * 2.0
+        pm = torch.zeros((64, Lm), device="cuda", dtype=torch.float32)
+        om = torch.zeros((64, 512), device="cuda", dtype=torch.float16)
+        lstate = {"i": 0}
+
+        def latent():
+            i = lstate["i"] = (lstate["i"] + 1) % copies
+            R.nn.attention_scores_grouped(pm.data_ptr(), qm.data_ptr(), lat[i].data_ptr(), 64, 1, 512, Lm)
+            R.nn.attention_softmax_rows(pm.data_ptr(), 64, Lm)
+            R.nn.attention_mix(om.data_ptr(), pm.data_ptr(), lat[i].data_ptr(), 64, 1, 512, Lm, over.data_ptr())
+        ms = time_loop(torch, latent, 30, 5)
+        nbytes = Lm * 512 * 2 + 2 * 64 * 512 * 2
+        out[f"mla_decode_64heads_{Lm}"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms}
+        del lat, pm
+    torch.cuda.empty_cache()
     # Kimi Delta Attention, one decode step of 64 heads of 128, through the reference's kda_step
     import ctypes as C
     S, conved, f, b, dt, a_log, gate, w, o = kda_workload(torch, gen, 64, 128, 1)
@@ -652,6 +670,30 @@ def other_workloads(torch, fam, pk, steps, warmup):
     del Wl
     torch.cuda.empty_cache()
 
+    # latent attention at decode (GLM's shape: 64 heads over one 512-wide latent that is key and value) through the three doors
+    # scores_grouped + softmax_rows + mix — one fused launch (two when the positions are cut over blocks): 2,048 positions (what
+    # the sparse attention gathers) with 16 latents cycled, and 65,536 (dense) with 4
+    for Lm, copies in ((2048, 16), (65536, 4)):
+        lat = torch.randn((copies, Lm, 512), generator=gen, device="cuda", dtype=torch.float16)
+        qm = torch.randn((64, 512), generator=gen, device="cuda", dtype=torch.float16) * 2.0
+        pm = torch.zeros((64, 8), device="cuda", dtype=torch.float32)          # never written by the fused triple
+        om = torch.zeros((64, 512), device="cuda", dtype=torch.float16)
+        lstate = {"i": 0}
+
+        def latent():
+            i = lstate["i"] = (lstate["i"] + 1) % copies
+            fam.nn.attention_scores_grouped(pm.data_ptr(), qm.data_ptr(), lat[i].data_ptr(), 64, 1, 512, Lm)
+            fam.nn.attention_softmax_rows(pm.data_ptr(), 64, Lm)
+            fam.nn.attention_mix(om.data_ptr(), pm.data_ptr(), lat[i].data_ptr(), 64, 1, 512, Lm, None)
+        before = ext.counters()["fused_latent"]
+        ms = time_loop(torch, latent, max(steps * 5, 100), 10)
+        assert ext.counters()["fused_latent"] > before, "the latent triple did not take the fused kernel"
+        nbytes = Lm * 512 * 2 + 2 * 64 * 512 * 2
+        out[f"mla_decode_64heads_{Lm}"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms, "frac_hbm": nbytes / ms / 1e6 / hbm, "tflops": 4.0 * 64 * 512 * Lm / ms / 1e9,
+                                            "note": f"scores_grouped + softmax_rows + mix doors, 64 heads over {Lm} latents of 512: {nbytes / 1e6:.1f} MB a call, {copies} latents cycled"}
+        del lat
+    torch.cuda.empty_cache()
+
     # the sparse attention's indexer at decode: 32 index heads of 128 score 8,192 pooled keys, the top 512 pools chosen
     ih, idim, pools, topk, kpool = 32, 128, 8192, 512, 4
     iq = torch.randn((ih * idim,), generator=gen, device="cuda", dtype=torch.float16)
@@ -750,7 +792,8 @@ ROOFLINES = {
     "kda_decode_64heads": ("hbm", "sv::kda_steps_kernel<128, false>", 4.31e6, "capture of this workload (the 8.4 MB state stays in L2 between steps)"),
     "mla_absorb_64heads": ("hbm", "sv::absorb_kernel", None, None),
     "mla_expand_64heads": ("hbm", "sv::expand_kernel", None, None),
-    "mla_decode_64heads": ("hbm", "sv::mla_decode_kernel", None, None),
+    "mla_decode_64heads_2048": ("hbm", "sv::mla_decode_kernel<64, fp16> + sv::mla_fold_kernel (2 MB: latency-bound)", None, None),
+    "mla_decode_64heads_65536": ("hbm", "sv::mla_decode_kernel<64, fp16> + sv::mla_fold_kernel", None, None),
     "config5_deltanet_decode_1seq": ("hbm", "sv::deltanet_steps_kernel<128, bf16, false, true> (one cluster a head)", None, None),
     "config5_deltanet_decode_1seq_graph": ("hbm", "sv::deltanet_steps_kernel<128, bf16, false, true> (one cluster a head)", None, None),
     "config5_deltanet_decode_64seq": ("hbm", "sv::deltanet_steps_kernel<128, bf16, false, false> + deltanet_norm_kernel", 213.3e6, "capture of this workload (part of the written state is still in L2 when the kernel ends)"),
@@ -1195,6 +1238,18 @@ def run_case(args):
         o = torch.zeros((T, heads * d), device="cuda", dtype=torch.bfloat16)
         fn = lambda: ext.deltanet(S, conved, z, beta, g, w, o, heads, heads, d, T, 1, 0, ext.BF16)
         work, unit = 7.0 * d * d * heads * T, "flop"
+    elif name in ("mla_2048", "mla_65536"):
+        # latent attention at decode through the extension entry: 64 heads over 2,048 / 65,536 latents of 512, 8 / 4 latents cycled
+        Lm, copies = (2048, 8) if name == "mla_2048" else (65536, 4)
+        lat = torch.randn((copies, Lm, 512), generator=gen, device="cuda", dtype=torch.float16)
+        qm = torch.randn((64, 512), generator=gen, device="cuda", dtype=torch.float16) * 2.0
+        om = torch.zeros((64, 512), device="cuda", dtype=torch.float16)
+        lstate = {"i": 0}
+
+        def fn():
+            i = lstate["i"] = (lstate["i"] + 1) % copies
+            ext.mla_decode(om, None, qm, lat[i], 64, Lm, ext.FP16, int(os.environ.get("MLA_BLOCKS", "0")))
+        work, unit = Lm * 512 * 2 + 2 * 64 * 512 * 2, "bytes"
     elif name == "prefill_small":
         qh, kvh, d, T = 16, 2, 256, 2048
         q = torch.randn((T, qh, d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.5
@@ -1218,7 +1273,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the secondary configurations (faster; used under profilers)")
     ap.add_argument("--only", default=None, choices=["long_context"], help="run configuration 4 alone (any N) and print its object")
-    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, decode_cfg1, decode_cfg1_graph, tq8_small, tq4_small, deltanet_64, deltanet_prefill, prefill_small)")
+    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, decode_cfg1, decode_cfg1_graph, tq8_small, tq4_small, deltanet_64, deltanet_prefill, prefill_small, mla_2048, mla_65536)")
     args = ap.parse_args()
     if args.case:
         run_case(args)

@@ -17,8 +17,8 @@
  *
  * A block walks a range of 128-key tiles.  Roles: warp 0 loads (Q once; a tile as eight 64-column boxes of 16 KB into an
  * eight-slot ring — a box is refilled as soon as the value product that read it has completed, so the ring is one tile
- * deep but never drains at once); warp 1 issues every MMA; warps 2-5 are the softmax, a thread a key: it reads its key's
- * scores of all heads from its TMEM lane, the tile's maximum a head is found across threads (an integer-ordered
+ * deep but never drains at once); warp 1 issues every MMA; warps 2-9 are the softmax, a thread a key and 32 of the heads: it reads
+ * its key's scores from its TMEM lane, the tile's maximum a head is found across threads (an integer-ordered
  * redux.sync a warp, then four values a head through shared memory), the reference maximum is kept unless a tile exceeds
  * it by 2^8 (the weights and the normaliser are relative to the same reference, which is exact), the 16-bit weights go to
  * shared memory transposed as the B operand, and each thread carries its own share of every head's normaliser, summed in
@@ -43,12 +43,12 @@ static constexpr int ML_D = 512;            /* latent width */
 static constexpr int ML_BK = 128;           /* keys a tile */
 static constexpr int ML_BOXES = ML_D / 64;  /* 64-column boxes a tile */
 static constexpr int ML_BOX_BYTES = ML_BK * 128;
-static constexpr int ML_THREADS = 6 * 32;
 
 struct MlaParams {
     uint16_t* o;              /* [heads][512] or null */
     float* res;               /* [heads][514] or null */
     float* partials;          /* [blocks][heads][514] when blocks > 1 */
+    const void* latent;       /* the rows themselves, for L2 prefetches */
     unsigned int* over;
     unsigned int* status;
     uint32_t length, tiles, blocks;
@@ -61,9 +61,12 @@ template <int NH> struct MlaCfg {
     static constexpr int C_BYTES = ML_BOXES * ML_BOX_BYTES;          /* 128 KB: one tile */
     static constexpr int P_BOX_BYTES = NH * 128;                     /* P^T: heads rows of 64 keys */
     static constexpr int P_BYTES = 2 * P_BOX_BYTES;
+    static constexpr int HALVES = NH / 32;                           /* softmax warps a TMEM lane quadrant: a thread owns 32 heads of its key */
+    static constexpr int SOFT = 128 * HALVES;                        /* softmax threads */
+    static constexpr int THREADS = 64 + SOFT;                        /* warp 0 loads, warp 1 issues the MMAs */
     static constexpr int T_S = 0, T_O = NH;                          /* TMEM columns: S^T, then O^T blocks NH apart */
     static constexpr int TMEM_COLS = (5 * NH <= 256) ? 256 : 512;
-    static constexpr size_t SMEM = 1024 + Q_BYTES + C_BYTES + P_BYTES + 512 /*barriers*/ + (4 * NH + 3 * NH) * 4;
+    static constexpr size_t SMEM = 1024 + Q_BYTES + C_BYTES + P_BYTES + 512 /*barriers*/ + (4 * NH + 5 * NH) * 4;
 };
 
 __device__ __forceinline__ int ordered_int(float x) { const int i = __float_as_int(x); return i ^ ((i >> 31) & 0x7FFFFFFF); }
@@ -73,10 +76,20 @@ __device__ __forceinline__ int warp_max_s32(int v) {
     asm volatile("redux.sync.max.s32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
     return r;
 }
-__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, %0;" ::"n"(N) : "memory"); }
+/* the same barrier, answering whether any thread brought a true */
+template <int N> __device__ __forceinline__ bool softmax_bar_or(bool mine) {
+    uint32_t r;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %1, 0;\n\tbar.red.or.pred p, 1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(r) : "r"((uint32_t)mine), "n"(N) : "memory");
+    return r != 0u;
+}
+/* asks L2 for a box ahead of its load, so that the load that refills a ring slot is a trip to L2 and not to memory */
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
+}
 
 template <int NH, int DT>
-__global__ void __launch_bounds__(ML_THREADS, 1)
+__global__ void __launch_bounds__(MlaCfg<NH>::THREADS, 1)
 mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap cmap, const MlaParams P) {
     using Cfg = MlaCfg<NH>;
     using E = Elem<DT>;
@@ -94,10 +107,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     uint64_t* pv_done = p_full + 1;           /* the tile's value products have completed */
     uint32_t* tmem_slot = (uint32_t*)(pv_done + 1);
     volatile uint32_t* abort_flag = (volatile uint32_t*)(tmem_slot + 1);
-    float* wmax = (float*)((uint8_t*)bars + 512);      /* [4 warps][NH] a warp's maximum a head (log2 units) */
+    float* wmax = (float*)((uint8_t*)bars + 512);      /* [4 quadrants][NH] a warp's maximum a head (log2 units) */
     float* mref = wmax + 4 * NH;                        /* [NH] the reference maximum a head, log2 units */
     float* fac = mref + NH;                             /* [NH] this tile's rescale factor a head */
     float* lsum = fac + NH;                             /* [NH] the normaliser, at the end */
+    float* lhalf = lsum + NH;                           /* [2][NH] its two halves */
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     /* this block's tiles: a contiguous share of the range, as even as whole tiles allow */
@@ -106,7 +120,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 
     if (tid == 0) {
         for (int i = 0; i < ML_BOXES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-        mbar_init(q_full, 1); mbar_init(s_full, 1); mbar_init(p_full, 4); mbar_init(pv_done, 1);
+        mbar_init(q_full, 1); mbar_init(s_full, 1); mbar_init(p_full, 4 * Cfg::HALVES); mbar_init(pv_done, 1);
         *abort_flag = 0u;
         mbar_fence_init();
     }
@@ -116,22 +130,37 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-
     if (warp == 0) {
-        /* ---------------- loads: Q once, then the tiles, a box at a time as its slot comes free ---------------- */
+        /* ---------------- loads: Q once, then the tiles, a box at a time as its slot comes free ----------------
+         * One lane drives the copies.  After a tile's copies are on their way the whole warp asks L2 for the NEXT tile with
+         * plain prefetches (a tile is 128 KB of consecutive memory: 1,024 lines, 32 a lane), so that the copies that refill the
+         * ring later are trips to L2, not to memory — and cost the copy engine nothing, which a tensor prefetch would. */
+        bool ok = true;
+        const uint8_t* base = (const uint8_t*)P.latent;
+        const uint64_t end = (uint64_t)P.length * (ML_D * 2);
         if (lane == 0 && nt > 0) {
             tma_prefetch_desc(&qmap); tma_prefetch_desc(&cmap);
-            const uint64_t pol = l2_policy_evict_first();
             mbar_expect_tx(q_full, Cfg::Q_BYTES);
 #pragma unroll
             for (int i = 0; i < ML_BOXES; ++i) tma_load_2d(q_s + i * Cfg::Q_BOX_BYTES, &qmap, q_full, i * 64, 0);
-            bool ok = true;
-            for (int t = 0; ok && t < nt; ++t)
+        }
+        const uint64_t pol = l2_policy_evict_first();
+        for (int t = 0; t < nt; ++t) {
+            if (lane == 0 && ok)
                 for (int i = 0; i < ML_BOXES; ++i) {
                     if (t > 0 && !mbar_wait(&empty[i], (t - 1) & 1, abort_flag, P.status)) { ok = false; break; }
                     mbar_expect_tx(&full[i], ML_BOX_BYTES);
                     tma_load_2d_hint(c_s + i * ML_BOX_BYTES, &cmap, &full[i], i * 64, (tile0 + t) * ML_BK, pol);
                 }
+            __syncwarp();
+            if (t + 1 < nt) {
+                const uint64_t at = (uint64_t)(tile0 + t + 1) * (ML_BK * ML_D * 2);
+#pragma unroll 4
+                for (int i = 0; i < 32; ++i) {
+                    const uint64_t off = at + ((uint64_t)(i * 32 + lane) << 7);
+                    if (off < end) asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
+                }
+            }
         }
     } else if (warp == 1) {
         /* ---------------- every MMA: S^T(t) as the boxes land, then — the weights written — the four blocks of O^T ------- */
@@ -171,72 +200,105 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             }
         }
     } else {
-        /* ---------------- softmax: a thread a key of the tile ---------------- */
-        const int quad = warp & 3, sw = warp - 2;
+        /* ---------------- softmax: a thread a key of the tile and 32 of the heads ---------------- */
+        constexpr int SOFT = Cfg::SOFT;
+        const int quad = warp & 3, half = (warp - 2) >> 2;           /* TMEM lane quadrant; which 32 heads */
         const int r = quad * 32 + lane;                              /* key within the tile = TMEM lane */
         const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-        const int st = sw * 32 + lane;                               /* 0..127 among the softmax threads */
-        float lpart[NH];
+        const int st = (warp - 2) * 32 + lane;                       /* 0..SOFT-1 among the softmax threads */
+        const int h0 = half * 32;
+        float lpart[32];
 #pragma unroll
-        for (int h = 0; h < NH; ++h) lpart[h] = 0.f;
-        /* The four warps meet at two block barriers a tile, so they walk the tiles together whatever happens: a warp whose
+        for (int x = 0; x < 32; ++x) lpart[x] = 0.f;
+        /* The softmax warps meet at two block barriers a tile, so they walk the tiles together whatever happens: a warp whose
          * wait ran out goes on as a bystander (it keeps the barriers' count whole and touches nothing else). */
         bool alive = nt > 0;
         for (int t = 0; t < nt; ++t) {
             if (alive && !__all_sync(0xffffffffu, mbar_wait(s_full, t & 1, abort_flag, P.status))) alive = false;
-            uint32_t sv[NH];
+            uint32_t sv[32];
             if (alive) {
                 tc_fence_after();
-#pragma unroll
-                for (int c = 0; c < NH; c += 32) tmem_ld32(tmem + Cfg::T_S + c + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&sv[c]));
+                tmem_ld32(tmem + Cfg::T_S + h0 + lane_off, sv);
                 tmem_wait_ld();
                 tc_fence_before();
                 const bool valid = (uint32_t)((tile0 + t) * ML_BK + r) < P.length;   /* rows past the end arrive as zeros: not scores */
-                /* the tile's maximum a head: over the warp's 32 keys here, over the four warps through shared memory */
+                /* the tile's maximum a head: over the warp's 32 keys here, over the four quadrants through shared memory */
+                /* (all 32 reductions are asked for before any answer is used: they pipeline, a dependent chain would not) */
+                int mine = 0;
 #pragma unroll
-                for (int h = 0; h < NH; ++h) {
-                    const float sc = valid ? __uint_as_float(sv[h]) * P.scale_log2 : -INFINITY;
-                    sv[h] = __float_as_uint(sc);
-                    const int m = warp_max_s32(ordered_int(sc));
-                    if ((h & 31) == lane) wmax[sw * NH + h] = ordered_float(m);
+                for (int x = 0; x < 32; ++x) {
+                    const float sc = valid ? __uint_as_float(sv[x]) * P.scale_log2 : -INFINITY;
+                    sv[x] = __float_as_uint(sc);
                 }
+                int wm[32];
+#pragma unroll
+                for (int x = 0; x < 32; ++x) wm[x] = warp_max_s32(ordered_int(__uint_as_float(sv[x])));
+#pragma unroll
+                for (int x = 0; x < 32; ++x) mine = (x == lane) ? wm[x] : mine;
+                wmax[quad * NH + h0 + lane] = ordered_float(mine);
             }
-            softmax_bar();
+            softmax_bar<SOFT>();
+            bool grew = false;
             if (st < NH) {
                 const float mx = fmaxf(fmaxf(wmax[st], wmax[NH + st]), fmaxf(wmax[2 * NH + st], wmax[3 * NH + st]));
                 const float old = mref[st];
                 float f = 1.f;
-                if ((mx > old + 8.f) || (old == -INFINITY && mx != -INFINITY)) { f = (old == -INFINITY) ? 0.f : fast_exp2(old - mx); mref[st] = mx; }
+                if ((mx > old + 8.f) || (old == -INFINITY && mx != -INFINITY)) { f = (old == -INFINITY) ? 0.f : fast_exp2(old - mx); mref[st] = mx; grew = true; }
                 fac[st] = f;
             }
-            softmax_bar();
+            const bool rescale = softmax_bar_or<SOFT>(grew);          /* any head's reference moved: the rare path below */
             if (!alive) continue;
-            bool rescale = false;
             const int kb = r >> 6, kr = r & 63;
             uint8_t* prow = p_s + kb * Cfg::P_BOX_BYTES + (kr & 7) * 2;
+            if (rescale) {
 #pragma unroll
-            for (int h = 0; h < NH; ++h) {
-                const float mu = mref[h], f = fac[h];
-                rescale |= (f != 1.f);
-                const float p = (mu == -INFINITY) ? 0.f : fast_exp2(__uint_as_float(sv[h]) - mu);
-                const uint32_t w = E::pack2(p, 0.f);
-                lpart[h] = lpart[h] * f + E::unpack2(w).x;           /* the normaliser sums what the MMA will see */
-                *reinterpret_cast<uint16_t*>(prow + swz128((uint32_t)h, (uint32_t)(kr >> 3))) = (uint16_t)(w & 0xFFFFu);
+                for (int x = 0; x < 32; ++x) lpart[x] *= fac[h0 + x];
             }
-            if (t > 0 && __any_sync(0xffffffffu, rescale)) {
+            /* eight heads at a time, every stage of the eight before the next stage: loads, exponentials, roundings and stores
+             * of different heads overlap instead of forming one chain a head (two warps a scheduler hide little on their own) */
+            /* A head's row of P^T is 128 bytes whose 16-byte chunks are XORed with the row number mod 8: with c16 = chunk * 16,
+             * row h's chunk sits at h * 128 + (c16 ^ ((h & 7) * 16)) — eight XORs serve all 32 rows. */
+            const uint32_t c16 = (uint32_t)(kr >> 3) << 4;
+            uint32_t cx[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) cx[u] = c16 ^ ((uint32_t)u << 4);
+            /* (a head's reference is finite here: the first tile of a block has a key inside the range, and the reference
+             * was brought up to date above)  Eight heads at a time, each stage of the eight before the next. */
+#pragma unroll
+            for (int x0 = 0; x0 < 32; x0 += 8) {
+                float pv[8];
+                const float4 m0 = *reinterpret_cast<const float4*>(mref + h0 + x0), m1 = *reinterpret_cast<const float4*>(mref + h0 + x0 + 4);
+                const float mu[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+#pragma unroll
+                for (int u = 0; u < 8; ++u) pv[u] = fast_exp2(__uint_as_float(sv[x0 + u]) - mu[u]);
+                uint32_t w[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) w[u] = E::pack2(pv[2 * u], pv[2 * u + 1]);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float2 back = E::unpack2(w[u]);            /* the normaliser sums what the MMA will see */
+                    lpart[x0 + 2 * u] += back.x;
+                    lpart[x0 + 2 * u + 1] += back.y;
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {                        /* (h0 + x0 is a multiple of 8, so row h's low bits are 2u and 2u + 1) */
+                    *reinterpret_cast<uint16_t*>(prow + (h0 + x0 + 2 * u) * 128 + cx[2 * u]) = (uint16_t)(w[u] & 0xFFFFu);
+                    *reinterpret_cast<uint16_t*>(prow + (h0 + x0 + 2 * u + 1) * 128 + cx[2 * u + 1]) = (uint16_t)(w[u] >> 16);
+                }
+            }
+            if (t > 0 && rescale) {
                 /* s_full(t) is behind every box of tile t, and every box was refilled only after the value product of t - 1
-                 * that read it had completed: O^T is settled.  A thread scales its lane (a latent column) of the four blocks. */
+                 * that read it had completed: O^T is settled.  A thread scales its lane (a latent column) and its 32 heads of
+                 * the four blocks. */
 #pragma unroll 1
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t ov[32];
+                    tmem_ld32(tmem + Cfg::T_O + j * NH + h0 + lane_off, ov);
+                    tmem_wait_ld();
 #pragma unroll
-                    for (int c = 0; c < NH; c += 32) {
-                        uint32_t ov[32];
-                        tmem_ld32(tmem + Cfg::T_O + j * NH + c + lane_off, ov);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int x = 0; x < 32; ++x) ov[x] = __float_as_uint(__uint_as_float(ov[x]) * fac[c + x]);
-                        tmem_st32(tmem + Cfg::T_O + j * NH + c + lane_off, ov);
-                    }
+                    for (int x = 0; x < 32; ++x) ov[x] = __float_as_uint(__uint_as_float(ov[x]) * fac[h0 + x]);
+                    tmem_st32(tmem + Cfg::T_O + j * NH + h0 + lane_off, ov);
+                }
                 tmem_wait_st();
             }
             fence_proxy_async_smem();                                /* the weights, for the MMA's reads */
@@ -247,39 +309,47 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         /* ---- the block's (m, l, acc): the normaliser in a fixed order, O^T out of TMEM ---- */
         if (alive && !__all_sync(0xffffffffu, mbar_wait(pv_done, (nt - 1) & 1, abort_flag, P.status))) alive = false;
         tc_fence_after();
+        /* the fold that follows is launched as a programmatic dependent: once every block has streamed its tiles it may be
+         * scheduled — its launch then overlaps the blocks' write-out — and it waits, at its first instruction, for this grid to
+         * have completed (a no-op when nothing of the kind follows) */
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         float* red = (float*)c_s;                                     /* [NH][128]: the ring is free now */
         if (alive) {
 #pragma unroll
-            for (int h = 0; h < NH; ++h) red[h * 128 + st] = lpart[h];
+            for (int x = 0; x < 32; ++x) red[(h0 + x) * 128 + r] = lpart[x];
         }
-        softmax_bar();
-        if (alive && st < NH) {
-            float l = 0.f;
-            for (int x = 0; x < 128; ++x) l += red[st * 128 + x];
-            lsum[st] = l;
+        softmax_bar<SOFT>();
+        if (st < 2 * NH) {
+            /* a head's 128 shares: two threads take 64 each, four running sums apiece (the order is fixed, the chain short) */
+            const int h = st % NH, part = st / NH;
+            const float* src = red + h * 128 + part * 64;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+            for (int x = 0; x < 64; x += 4) { a0 += src[x]; a1 += src[x + 1]; a2 += src[x + 2]; a3 += src[x + 3]; }
+            lhalf[part * NH + h] = (a0 + a1) + (a2 + a3);
         }
-        softmax_bar();
+        softmax_bar<SOFT>();
+        if (st < NH) lsum[st] = lhalf[st] + lhalf[NH + st];
+        softmax_bar<SOFT>();
         if (alive) {
             const bool whole = P.blocks == 1u;
             float* out = whole ? P.res : P.partials + (size_t)blockIdx.x * NH * (ML_D + 2);
             bool hit = false;
             if (out && st < NH) { out[(size_t)st * (ML_D + 2)] = mref[st] * SV_LN2; out[(size_t)st * (ML_D + 2) + 1] = lsum[st]; }
 #pragma unroll 1
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < 4; ++j) {
+                uint32_t ov[32];
+                tmem_ld32(tmem + Cfg::T_O + j * NH + h0 + lane_off, ov);
+                tmem_wait_ld();
+                const int e = j * 128 + r;                            /* this lane's latent column */
 #pragma unroll
-                for (int c = 0; c < NH; c += 32) {
-                    uint32_t ov[32];
-                    tmem_ld32(tmem + Cfg::T_O + j * NH + c + lane_off, ov);
-                    tmem_wait_ld();
-                    const int e = j * 128 + r;                        /* this lane's latent column */
-#pragma unroll
-                    for (int x = 0; x < 32; ++x) {
-                        const int h = c + x;
-                        const float a = __uint_as_float(ov[x]);
-                        if (out) out[(size_t)h * (ML_D + 2) + 2 + e] = a;
-                        if (whole && P.o) P.o[(size_t)h * ML_D + e] = E::from_float(a / lsum[h], hit);
-                    }
+                for (int x = 0; x < 32; ++x) {
+                    const int h = h0 + x;
+                    const float a = __uint_as_float(ov[x]);
+                    if (out) out[(size_t)h * (ML_D + 2) + 2 + e] = a;
+                    if (whole && P.o) P.o[(size_t)h * ML_D + e] = E::from_float(a / lsum[h], hit);
                 }
+            }
             if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
             tc_fence_before();
         }
@@ -293,18 +363,29 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 template <int DT>
 __global__ void __launch_bounds__(128) mla_fold_kernel(uint16_t* o, float* res, const float* partials, uint32_t heads, uint32_t blocks, unsigned int* over) {
     using E = Elem<DT>;
+    __shared__ float ms_s[160], ls_s[160];
+    asm volatile("griddepcontrol.wait;" ::: "memory");          /* the partials are the grid ahead's */
     const uint32_t h = blockIdx.x / 4u, e = (blockIdx.x % 4u) * 128u + threadIdx.x, w = ML_D + 2;
     const size_t step = (size_t)heads * w;
     const float* base = partials + (size_t)h * w;
+    /* the blocks' (m, l) a thread each, all asked for at once; then the accumulators eight at a time, so that no load waits for
+     * the one before it */
+    for (uint32_t s = threadIdx.x; s < blocks; s += 128u) { ms_s[s] = __ldcg(base + s * step); ls_s[s] = __ldcg(base + s * step + 1); }
+    __syncthreads();
     float m = -INFINITY;
-    for (uint32_t s = 0; s < blocks; ++s) m = fmaxf(m, __ldcg(base + s * step));
+    for (uint32_t s = 0; s < blocks; ++s) m = fmaxf(m, ms_s[s]);
     float acc = 0.f, l = 0.f;
-    for (uint32_t s = 0; s < blocks; ++s) {
-        const float ms = __ldcg(base + s * step);
-        if (ms == -INFINITY) continue;
-        const float f = expf(ms - m);
-        acc = __fmaf_rn(__ldcg(base + s * step + 2 + e), f, acc);
-        l = __fmaf_rn(__ldcg(base + s * step + 1), f, l);
+    for (uint32_t s0 = 0; s0 < blocks; s0 += 8u) {
+        float a[8];
+#pragma unroll
+        for (uint32_t u = 0; u < 8u; ++u) a[u] = (s0 + u < blocks) ? __ldcg(base + (s0 + u) * step + 2 + e) : 0.f;
+#pragma unroll
+        for (uint32_t u = 0; u < 8u; ++u) {
+            if (s0 + u >= blocks || ms_s[s0 + u] == -INFINITY) continue;
+            const float f = expf(ms_s[s0 + u] - m);
+            acc = __fmaf_rn(a[u], f, acc);
+            l = __fmaf_rn(ls_s[s0 + u], f, l);
+        }
     }
     bool hit = false;
     if (res) { res[(size_t)h * w + 2 + e] = acc; if (e == 0) { res[(size_t)h * w] = m; res[(size_t)h * w + 1] = l; } }
@@ -333,10 +414,11 @@ static cudaError_t launch_mla(uint16_t* o, float* res, const void* q, const void
     if (!make_map_2d_sw128(&qm, q, ML_D, NH, ML_D * 2, 64u, NH, bf)) return cudaErrorInvalidValue;
     if (!make_map_2d_sw128(&cm, latent, ML_D, length, ML_D * 2, 64u, ML_BK, bf)) return cudaErrorInvalidValue;
     MlaParams P;
-    P.o = o; P.res = res; P.over = over; P.status = device_status_word();
+    P.o = o; P.res = res; P.over = over; P.status = device_status_word(); P.latent = latent;
     P.length = (uint32_t)length; P.tiles = (uint32_t)((length + ML_BK - 1) / ML_BK);
     uint32_t blocks = blocks_want ? blocks_want : device_sm_count();
     if (blocks > P.tiles) blocks = P.tiles;
+    if (blocks > 160u) blocks = 160u;                  /* the fold keeps the blocks' (m, l) in shared memory */
     P.blocks = blocks;
     P.scale_log2 = (1.0f / sqrtf((float)ML_D)) * SV_LOG2E;
     P.partials = nullptr;
@@ -359,11 +441,17 @@ static cudaError_t launch_mla(uint16_t* o, float* res, const void* q, const void
         if ((e = cudaFuncSetAttribute(mla_decode_kernel<NH, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM)) != cudaSuccess) return e;
         attr_set[d].store(true, std::memory_order_release);
     }
-    mla_decode_kernel<NH, DT><<<blocks, ML_THREADS, Cfg::SMEM, st>>>(qm, cm, P);
+    mla_decode_kernel<NH, DT><<<blocks, Cfg::THREADS, Cfg::SMEM, st>>>(qm, cm, P);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     note_launch(1);
     if (blocks > 1u) {
-        mla_fold_kernel<DT><<<NH * 4, 128, 0, st>>>(o, res, P.partials, NH, blocks, over);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(NH * 4); cfg.blockDim = dim3(128); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, mla_fold_kernel<DT>, o, res, (const float*)P.partials, (uint32_t)NH, blocks, over);
+        if (e != cudaSuccess) return e;
         note_launch(1);
         e = cudaGetLastError();
     }
