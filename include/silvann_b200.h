@@ -424,6 +424,13 @@ int silvann_b200_exchange_merge_finish(silvann_b200_exchange* exchange, void* o,
 /* out[i] = round16(sum over members, in member order, of fp32(partial_member[i])) — vector_sum (kernels.cuh:117-126). */
 int silvann_b200_exchange_vector_sum(silvann_b200_exchange* exchange, void* out, const void* partial, uint64_t n, int dtype,
                                      sv_fault* over, uint32_t wait_ms, void* stream);
+/* The output projection of a head-sharded mixer and the sum over the cards that follows it, in one launch a card: `codes`
+ * [rows][cols·width/8] and `scales` [rows] are this card's share of a TurboQuant-coded matrix (width 4 or 8; turboquant_gemv's
+ * operands, kernels.cuh:1405-1447), vec [cols] its share of the input; every member's 16-bit partial out_m[r] is pushed from
+ * the kernel's epilogue and out[r] = round16(sum over members, in member order, of fp32(out_m[r])) — what turboquant_gemv
+ * followed by nn__partials__reduce_onto leaves (nn partials__abi.cuh:110-163).  fp16; rows * 2 bytes must fit a slot. */
+int silvann_b200_exchange_gemv_sum(silvann_b200_exchange* exchange, void* out, const void* codes, const void* scales, const void* vec,
+                                   uint64_t width, uint64_t rows, uint64_t cols, sv_fault* over, uint32_t wait_ms, void* stream);
 /* Stands in for an absent member where there are fewer cards than members (a one-card walk of a many-card plan): puts
  * `data` where that member's push of the NEXT exchange would land and sets its flags.  Same stream as the exchange. */
 int silvann_b200_exchange_deposit(silvann_b200_exchange* exchange, uint32_t member, const void* data, uint64_t bytes, void* stream);

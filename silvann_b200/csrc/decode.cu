@@ -53,6 +53,7 @@ struct DecodeParams {
     uint32_t q_heads, kv_heads, group;
     uint32_t length, nsplit, head_blocks, heads_per_block;
     uint32_t slot_floats;
+    uint32_t l1, l1_groups, l2_slot0, l1_ticket0;   /* one-sequence calls with many splits meet in two levels: l1 splits a first-level group (0: one level) */
     float scale_log2;
 };
 
@@ -319,6 +320,7 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     const uint32_t SF = P.slot_floats;                /* floats per head in scratch: D + 2 */
     const bool single = (nsplit == 1);
     bool hit = false;
+    const bool two_level = CL == 1 && P.l1 != 0u && !P.items && nsplit > (int)P.l1;
     if (CL > 1) {
         /* ---- the splits of this cluster meet in shared memory ----
          * Every block leaves its (m, l, acc) in its own shared memory; after the cluster's barrier block r of the cluster
@@ -415,12 +417,21 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
         return;
     }
 
-    /* ---- arrive; the last block of the group merges all splits in split order ---- */
+    /* ---- arrive; the last block of the group merges all splits in split order ----
+     * With many splits a group meets in two levels: the splits in first-level groups of P.l1, whose last arrivals each merge
+     * their group into one partial (side by side, on different SMs), and those partials at the group's own ticket. */
     __threadfence();
     __syncthreads();
-    if (tid == 0) *ticket_s = atomicAdd(&P.tickets[ticket], 1u);
-    __syncthreads();
-    if (*ticket_s != (uint32_t)(nsplit - 1)) return;
+    if (two_level) {
+        const int g1 = split / (int)P.l1, n1 = min((int)P.l1, nsplit - g1 * (int)P.l1);
+        if (tid == 0) *ticket_s = atomicAdd(&P.tickets[P.l1_ticket0 + ticket * P.l1_groups + g1], 1u);
+        __syncthreads();
+        if (*ticket_s != (uint32_t)(n1 - 1)) return;
+    } else {
+        if (tid == 0) *ticket_s = atomicAdd(&P.tickets[ticket], 1u);
+        __syncthreads();
+        if (*ticket_s != (uint32_t)(nsplit - 1)) return;
+    }
     __threadfence();
     }
     /* The block is alone with its group by now and bound by trips to L2, so everything it needs is asked for at once:
@@ -429,6 +440,20 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
      * make the factors e^(m_s - m); then the run is summed in split order, the runs in run order — a fixed order, so
      * results repeat bit for bit. */
     constexpr int THREADS = (NW + 1) * 32, RUN_MAX = 16;
+    const size_t slot_f = (size_t)HPB * SF;
+    const int g1 = two_level ? split / (int)P.l1 : 0;
+    const int nsplit_all = nsplit;
+    /* what this pass merges and where its answer goes: a first-level group into its second-level slot, or everything into
+     * the answer */
+    const float* base = P.partials + (size_t)slot_base * slot_f;
+    size_t step = (size_t)slot_stride * slot_f;
+    float* to_slot = nullptr;
+    if (two_level) {
+        base += (size_t)g1 * P.l1 * step;
+        nsplit = min((int)P.l1, nsplit_all - g1 * (int)P.l1);
+        to_slot = P.partials + (size_t)(P.l2_slot0 + ticket * P.l1_groups + g1) * slot_f;
+    }
+  for (int level = 0;; ++level) {
     float* fac = (float*)stage_base;                  /* [heads][nsplit] */
     float* mh = fac + HPB * nsplit;                   /* [heads] merged m (log2 units), then merged l */
     float* lh = mh + HPB;
@@ -438,8 +463,6 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     if (runs < 1) runs = 1;
     if (runs > nsplit) runs = nsplit;
     int run_len = (nsplit + runs - 1) / runs;
-    const size_t slot_f = (size_t)HPB * SF, step = (size_t)slot_stride * slot_f;
-    const float* base = P.partials + (size_t)slot_base * slot_f;
     const bool one_pass = run_len <= RUN_MAX && runs * e4n <= THREADS;
     /* the (m, l) of a split a lane, asked for ahead of the accumulators so that they are back first */
     const bool ml_lanes = nsplit <= 32 && warp < heads;
@@ -516,6 +539,11 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
             }
         }
         const float m = mh[h], l = lh[h];
+        if (to_slot) {                                   /* a first-level group's partial, in a slot's layout (m in log2 units) */
+            *reinterpret_cast<float4*>(to_slot + (size_t)h * D + e) = acc;
+            if (e == 0) { to_slot[HPB * D + 2 * h] = m; to_slot[HPB * D + 2 * h + 1] = l; }
+            continue;
+        }
         const size_t hq = (size_t)seq * P.q_heads + head0 + h;
         if (P.o) {
             uint16_t* op = (uint16_t*)P.o + hq * D + e;
@@ -528,6 +556,18 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
             if (e == 0) { ro[0] = m * SV_LN2; ro[1] = l; }
         }
     }
+    if (!to_slot) break;
+    /* the first-level group is one partial now: its ticket is cleared for the next launch, and it goes to the meeting of the
+     * group's first-level groups */
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) { P.tickets[P.l1_ticket0 + ticket * P.l1_groups + g1] = 0u; *ticket_s = atomicAdd(&P.tickets[ticket], 1u); }
+    __syncthreads();
+    if (*ticket_s != P.l1_groups - 1u) return;
+    __threadfence();
+    base = P.partials + (size_t)(P.l2_slot0 + ticket * P.l1_groups) * slot_f; step = slot_f; nsplit = (int)P.l1_groups; to_slot = nullptr;
+    __syncthreads();                                  /* the shared arrays of the pass above are free */
+  }
     if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
     if (tid == 0) P.tickets[ticket] = 0u;             /* ready for the next launch */
 }
@@ -701,6 +741,7 @@ cudaError_t decode_launch(const DecodeCall& c) {
     P.q_heads = c.q_heads; P.kv_heads = c.kv_heads; P.group = group;
     P.length = c.length; P.head_blocks = hb; P.heads_per_block = hpb;
     P.slot_floats = c.head_dim + 2u;
+    P.l1 = 0; P.l1_groups = 0; P.l2_slot0 = 0; P.l1_ticket0 = 0;
     P.scale_log2 = (1.0f / sqrtf((float)c.head_dim)) * SV_LOG2E;
     uint32_t blocks, cluster = 1u;
     /* one-sequence calls are a few microseconds long and often follow each other (a layer after a layer): they are launched
@@ -721,6 +762,17 @@ cudaError_t decode_launch(const DecodeCall& c) {
         if (c.nsplit == 0 || splits_forced) cluster = decode_cluster_for(tiles, c.kv_heads * hb, device_sm_count(), &ns);
         if ((uint64_t)(ns / cluster) * c.kv_heads * hb > c.scratch.slots || (uint64_t)c.kv_heads * hb > c.scratch.tickets_n) return cudaErrorInvalidValue;
         P.nsplit = ns; blocks = ns * c.kv_heads * hb;
+        /* many splits of few groups (one long sequence, a kv head or two a card): the last arrival would merge them all on one
+         * SM through L2 — in two levels the first is done side by side */
+        const uint32_t lanes = c.kv_heads * hb;
+        if (cluster == 1u && ns > 48u && c.nsplit == 0u) {       /* (a caller that names its split count gets exactly that meeting) */
+            uint32_t g1 = 8u;
+            while (g1 * g1 < ns) ++g1;
+            const uint32_t groups = (ns + g1 - 1u) / g1;
+            if ((uint64_t)ns * lanes + (uint64_t)groups * lanes <= c.scratch.slots && (uint64_t)lanes + (uint64_t)groups * lanes <= c.scratch.tickets_n) {
+                P.l1 = g1; P.l1_groups = groups; P.l2_slot0 = ns * lanes; P.l1_ticket0 = lanes;
+            }
+        }
     }
     if (blocks == 0) return cudaSuccess;
     if ((size_t)hpb * P.slot_floats > (size_t)16 * c.scratch.slot_floats) return cudaErrorInvalidValue;
@@ -866,6 +918,7 @@ int decode_launch_static(const DecodeCall& c0, uint32_t* detail) {
     P.q_heads = c.q_heads; P.kv_heads = c.kv_heads; P.group = group;
     P.length = c.length; P.nsplit = ns; P.head_blocks = hb; P.heads_per_block = hpb;
     P.slot_floats = c.head_dim + 2u;
+    P.l1 = 0; P.l1_groups = 0; P.l2_slot0 = 0; P.l1_ticket0 = 0;
     P.scale_log2 = (1.0f / sqrtf((float)c.head_dim)) * SV_LOG2E;
     const uint32_t blocks = ns * lanes;
     const int nht = hpb == 8 ? 1 : 2;

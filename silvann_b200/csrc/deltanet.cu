@@ -214,6 +214,101 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_steps_kernel(const DeltaP
     if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
 }
 
+/* One position of MANY sequences in one launch: a block a (sequence, head) with the head's whole state in its registers —
+ * 4 row groups x D columns of threads, the same slice a thread and the same order of every sum as the cluster form above, so
+ * a sequence's answer has the same bits whether it is stepped alone or in a batch — and, because the block holds all D
+ * read-outs of the head, the RMS norm, weight and gate are finished here: no second launch, no scratch.  The state crosses
+ * HBM once in and once out; 64 KB of loads a block are in flight before the first sum. */
+template <int D, int DT>
+__global__ void __launch_bounds__(4 * D, 2) deltanet_step_head_kernel(const DeltaParams P) {
+    using E = Elem<DT>;
+    constexpr int CB = D / DN_COLS, R = D / DN_RG;
+    const int tid = threadIdx.x, rg = tid / D, j = tid % D, c = j % DN_COLS, cb = j / DN_COLS;
+    const int h = blockIdx.x % P.v_heads, b = blockIdx.x / P.v_heads;
+    const int rep = P.v_heads / P.k_heads, kh = h / rep;
+    const uint64_t ch = (uint64_t)(2 * P.k_heads + P.v_heads) * D, vd = (uint64_t)P.v_heads * D;
+
+    __shared__ __align__(16) float qk[2][D];
+    __shared__ float red1[DN_RG][D], red2[DN_RG][D], nq[DN_RG], nk[DN_RG], ssq[CB];
+
+    float* Sh = P.S + ((uint64_t)b * P.v_heads + h) * D * D;
+    float s[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) s[i] = Sh[(uint64_t)(rg * R + i) * D + j];
+    const uint16_t* cv = P.conved + (uint64_t)b * ch;
+    if (tid < 2 * D) {
+        const int which = tid / D, e = tid % D;
+        (&qk[0][0])[tid] = E::to_float(cv[(which == 0 ? kh * D : (P.k_heads + kh) * D) + e]);
+    }
+    const float vj = E::to_float(cv[(uint64_t)2 * P.k_heads * D + (uint64_t)h * D + j]);
+    const float beta = E::to_float(P.beta[(uint64_t)b * P.v_heads + h]), decay = expf(E::to_float(P.g[(uint64_t)b * P.v_heads + h]));
+    const uint16_t z_bits = rg == 0 ? P.z[(uint64_t)b * vd + (uint64_t)h * D + j] : (uint16_t)0;
+    const uint16_t w_bits = rg == 0 ? P.w[j] : (uint16_t)0;
+    __syncthreads();
+
+    const float inv_sqrt_d = 1.0f / sqrtf((float)D);
+    const float* qv = qk[0] + rg * R;
+    const float* kv_ = qk[1] + rg * R;
+    float qq = 0.f, kk = 0.f;
+    float kv4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < R; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kv_ + i);
+        const float4 q4 = *reinterpret_cast<const float4*>(qv + i);
+        kv4[(i >> 2) & 3] += s[i] * k4.x + s[i + 1] * k4.y + s[i + 2] * k4.z + s[i + 3] * k4.w;
+        kk += k4.x * k4.x + k4.y * k4.y + k4.z * k4.z + k4.w * k4.w;
+        qq += q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w;
+    }
+    red1[rg][j] = (kv4[0] + kv4[1]) + (kv4[2] + kv4[3]);
+    if (j == 0) { nq[rg] = qq; nk[rg] = kk; }
+    __syncthreads();
+    float kvsum = 0.f, qsum = 0.f, ksum = 0.f;
+#pragma unroll
+    for (int r = 0; r < DN_RG; ++r) { kvsum += red1[r][j]; qsum += nq[r]; ksum += nk[r]; }
+    const float inv_k = 1.0f / sqrtf(ksum + 1e-6f);
+    const float inv_q = 1.0f / sqrtf(qsum + 1e-6f) * inv_sqrt_d;
+    const float delta = (vj - decay * kvsum * inv_k) * beta;
+    const float kd = inv_k * delta;
+    float op4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < R; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kv_ + i);
+        const float4 q4 = *reinterpret_cast<const float4*>(qv + i);
+        s[i]     = decay * s[i]     + k4.x * kd; op4[0] += s[i]     * q4.x;
+        s[i + 1] = decay * s[i + 1] + k4.y * kd; op4[1] += s[i + 1] * q4.y;
+        s[i + 2] = decay * s[i + 2] + k4.z * kd; op4[2] += s[i + 2] * q4.z;
+        s[i + 3] = decay * s[i + 3] + k4.w * kd; op4[3] += s[i + 3] * q4.w;
+    }
+    red2[rg][j] = (op4[0] + op4[1]) + (op4[2] + op4[3]);
+    /* the state goes home while the read-out is folded */
+#pragma unroll
+    for (int i = 0; i < R; ++i) Sh[(uint64_t)(rg * R + i) * D + j] = s[i];
+    __syncthreads();
+    bool hit = false;
+    uint16_t oh = 0;
+    if (rg == 0) {
+        const float o = (red2[0][j] + red2[1][j] + red2[2][j] + red2[3][j]) * inv_q;
+        oh = E::from_float(o, hit);
+        if (P.readout) P.readout[(uint64_t)b * vd + (uint64_t)h * D + j] = o;
+        float sq = E::to_float(oh); sq *= sq;
+        for (int x = 16; x > 0; x >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, x);
+        if (c == 0) ssq[cb] = sq;
+    }
+    __syncthreads();
+    if (rg == 0) {
+        float sum = 0.f;
+#pragma unroll
+        for (int r = 0; r < CB; ++r) sum += ssq[r];
+        const float scale = 1.0f / sqrtf(sum / (float)D + 1e-6f);
+        const float zr = E::to_float(z_bits);
+        const float zc = zr < -88.0f ? -88.0f : (zr > 88.0f ? 88.0f : zr);
+        const float sg = 1.0f / (1.0f + expf(-zc));
+        const float gz = P.gate == 1 ? sg : zc * sg;
+        P.out[(uint64_t)b * vd + (uint64_t)h * D + j] = E::from_float(E::to_float(oh) * scale * E::to_float(w_bits) * gz, hit);
+    }
+    if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
+}
+
 /* The per-position scalars of a run of positions, off the serial path: a warp a (sequence, position, key head) folds
  * |q|^2 and |k|^2 and writes {1/sqrt(|q|^2 + 1e-6)/sqrt(d), 1/sqrt(|k|^2 + 1e-6), e^g, beta} for each of its value heads. */
 template <int D, int DT>
@@ -335,6 +430,12 @@ static cudaError_t launch_dn(const DeltaCall& c, float* ss) {
         note_launch(1);
         P.sc = sc;
         deltanet_steps_kernel<D, DT, true, false><<<blocks, DN_THREADS, 0, c.stream>>>(P);
+    } else if (blocks > fuse_blocks_max() && D <= 128) {
+        /* one position of many sequences: a block a (sequence, head), the read-out finished in the same launch */
+        P.sc = nullptr;
+        deltanet_step_head_kernel<(D <= 128 ? D : 128), DT><<<c.seqs * c.v_heads, 4 * (D <= 128 ? D : 128), 0, c.stream>>>(P);
+        note_launch(1);
+        return cudaGetLastError();
     } else if (blocks > fuse_blocks_max()) {
         P.sc = nullptr;
         deltanet_steps_kernel<D, DT, false, false><<<blocks, DN_THREADS, 0, c.stream>>>(P);

@@ -27,13 +27,11 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "residual.cuh"
+#include "exchange.cuh"
 #include <new>
 #include <string.h>
 
 #define SV_EXPORT extern "C" __attribute__((visibility("default")))
-#define XF_MEMBERS_MAX 8
-#define XF_BLOCKS 256u                      /* flags a member and parity: one a thread block of an exchange kernel */
-#define XF_FLAG_BYTES (2u * XF_MEMBERS_MAX * XF_BLOCKS * 4u)
 #define XF_HEADS_PER_BLOCK 8u
 #define XF_SUM_PIECE 4096u                  /* bytes of a partial a block of the sum kernel moves: 16 bytes a thread */
 
@@ -50,34 +48,6 @@ struct silvann_b200_exchange {
 };
 
 namespace sv {
-
-struct XfParams {
-    uint8_t* peer[XF_MEMBERS_MAX];
-    uint32_t members, index, gen;
-    uint64_t slot_bytes;
-    unsigned long long wait_ns;
-    unsigned int* status;
-};
-
-__device__ __forceinline__ unsigned int* xf_flag(uint8_t* base, uint32_t parity, uint32_t member, uint32_t block) {
-    return reinterpret_cast<unsigned int*>(base) + ((size_t)parity * XF_MEMBERS_MAX + member) * XF_BLOCKS + block;
-}
-__device__ __forceinline__ uint8_t* xf_slot(uint8_t* base, uint32_t parity, uint32_t member, uint64_t slot_bytes, uint32_t members) {
-    return base + XF_FLAG_BYTES + ((size_t)parity * members + member) * slot_bytes;
-}
-__device__ __forceinline__ void st_release_sys(unsigned int* at, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(at), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* at) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(at) : "memory");
-    return v;
-}
-__device__ __forceinline__ unsigned long long wall_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 
 /* After the block's pushes: publish this block's flag on every member, then wait until every member's flag for this block
  * shows the generation.  Answers false (to every thread of the block) when a wait ran out. */
@@ -333,6 +303,29 @@ SV_EXPORT int silvann_b200_exchange_vector_sum(silvann_b200_exchange* x, void* o
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return sv_ext_fail(SILVANN_B200_E_CUDA, "exchange_vector_sum: %s", cudaGetErrorString(e));
     sv::note_launch(1);
+    x->gen += 1u;
+    return SILVANN_B200_OK;
+}
+
+/* A coded matrix times a vector on every member, the members' answers added in member order, in ONE launch a member: the
+ * output projection of a head-sharded mixer (turboquant_gemv over the card's share of the columns) and the sum the reference
+ * makes afterwards with nn__partials__reduce_onto (ai_qwen_3 mixer__abi.cuh:254-257, nn partials__abi.cuh:110-163).  The
+ * kernel's epilogue rounds a row's answer to 16 bits — the partial the reference would have written — and pushes it to the
+ * members; each block then adds its own rows over the members in fp32 and rounds once, which is vector_sum's arithmetic. */
+SV_EXPORT int silvann_b200_exchange_gemv_sum(silvann_b200_exchange* x, void* out, const void* codes, const void* scales, const void* vec, uint64_t width,
+                                             uint64_t rows, uint64_t cols, sv_fault* over, uint32_t wait_ms, void* stream) {
+    if (!x || !out || !codes || !scales || !vec || rows == 0) return sv_ext_fail(SILVANN_B200_E_ARGUMENT, "exchange_gemv_sum: a null or empty operand");
+    struct { uint64_t codes[12], luts[12], rows[12], d[12], out_at[12], count; } g;
+    memset(&g, 0, sizeof g);
+    g.codes[0] = (uint64_t)(uintptr_t)codes; g.luts[0] = (uint64_t)(uintptr_t)scales; g.rows[0] = rows; g.d[0] = width; g.count = 1;
+    if (!sv::tq_gemv_fast_fits(&g, cols, 1) || rows * 2u > x->slot_bytes)
+        return sv_ext_fail(SILVANN_B200_E_ARGUMENT, "exchange_gemv_sum: %llu rows of %llu codes at %llu bits are outside the kernel's fit, or more than a slot of %llu bytes holds",
+                           (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)width, (unsigned long long)x->slot_bytes);
+    sv::XfParams P;
+    int rc = xf_params(x, "exchange_gemv_sum", wait_ms, &P);
+    if (rc != SILVANN_B200_OK) return rc;
+    const cudaError_t e = sv::tq_gemv_fast_launch((uint16_t*)out, &g, nullptr, (const uint16_t*)vec, cols, 1, 0, over, (cudaStream_t)stream, &P);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return sv_ext_fail(SILVANN_B200_E_CUDA, "exchange_gemv_sum: %s", cudaGetErrorString(e)); }
     x->gen += 1u;
     return SILVANN_B200_OK;
 }

@@ -108,8 +108,9 @@ cudaError_t attention_gate_rows_launch(uint16_t* o, const uint16_t* att, const u
 /* ---- a coded matrix times up to eight vectors on the tensor cores, codes expanded in flight (tq_gemv.cu) ---- */
 bool tq_gemv_fast_fits(const void* groups /*the door's by-value groups struct*/, uint64_t cols, uint64_t inputs);
 /* rows_cap: null, or a group's rows trimmed to what its rooms hold */
+struct XfParams;    /* exchange.cuh: with one, the answers are exchanged among the cards and added in member order in the same launch */
 cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_t* rows_cap, const uint16_t* x, uint64_t cols, uint64_t inputs,
-                                uint64_t out_stride, unsigned int* over, cudaStream_t st);
+                                uint64_t out_stride, unsigned int* over, cudaStream_t st, const XfParams* xf = nullptr);
 /* ---- the GLM mixer's doors: Kimi Delta Attention, latent absorb / expand, the sparse attention's indexer (glm_doors.cu) ---- */
 cudaError_t kda_decays_launch(float* eg, const uint16_t* f, const uint16_t* dt, const uint16_t* a_log, uint64_t heads, uint64_t head_dim, float lower,
                               uint64_t rows, cudaStream_t st);

@@ -32,6 +32,7 @@
  * lookups and 256 fetch wavefronts, after 2.7 us of prologue and first landing (every SM's first three slots, 14 MB over the
  * card, are asked for at once). */
 #include "common.cuh"
+#include "exchange.cuh"
 #include <atomic>
 #include "kernels.h"
 #include <string.h>
@@ -61,7 +62,7 @@ __global__ void __launch_bounds__(256) gv_lut_image_kernel() {
 }
 
 cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_t* rows_cap, const uint16_t* x, uint64_t cols, uint64_t inputs,
-                                uint64_t out_stride, unsigned int* over, cudaStream_t st);
+                                uint64_t out_stride, unsigned int* over, cudaStream_t st, const XfParams* xf);
 
 struct GemvFast {
     const uint8_t* codes[12];
@@ -72,6 +73,9 @@ struct GemvFast {
     uint32_t ts, pi, stage_bytes, smem_bytes;  /* tiles a step at most; inputs rounded up to a power of two; bytes a slot; the block's shared memory */
     uint64_t out_stride;
     unsigned int* status;
+    /* with an exchange (xf.members > 0; one group, one input): the rounded answers are pushed to the members' slots instead
+     * of `out`, and the block then adds every member's answers of its own rows in member order (exchange.cuh) */
+    XfParams xf;
 };
 
 /* The table entry of byte `idx` of word `w` for this lane.  The table starts on a 64 KB boundary of the shared window and
@@ -286,7 +290,11 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
             float sum = 0.f;
 #pragma unroll
             for (uint32_t w = 0; w < (uint32_t)GV_WARPS; ++w) sum += from[w * 16u * pi];
-            out[out_row + o_row + o_in * out_input] = H::from_float(sum * H::to_float(scale), hit);
+            const uint16_t y = H::from_float(sum * H::to_float(scale), hit);
+            if (a.xf.members == 0u) out[out_row + o_row + o_in * out_input] = y;
+            else
+                for (uint32_t mm = 0; mm < a.xf.members; ++mm)                   /* this card's partial of the row, to every member */
+                    reinterpret_cast<uint16_t*>(xf_slot(a.xf.peer[mm], a.xf.gen & 1u, a.xf.index, a.xf.slot_bytes, a.xf.members))[o_row] = y;
         }
         tile += nt;
     }
@@ -294,6 +302,40 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
      * (bounded) for every slot's barrier to settle before the memory is given back. */
     if (failed && tid == 0)
         for (uint32_t st = 0; st < S; ++st) for (uint32_t i = 0; i < 4096u && !mbar_try_wait(&full[st], 0u) && !mbar_try_wait(&full[st], 1u); ++i) { }
+    if (a.xf.members != 0u) {
+        /* ---- the exchange: the block's rows are on every member; say so, wait (bounded) for the members' same rows, add ----
+         * Every member runs this kernel over a matrix of the same shape, so block b owns the same rows everywhere and the
+         * flags are a block's own: no block waits for another block of its own card. */
+        const uint32_t parity = a.xf.gen & 1u;
+        volatile uint32_t* gave_up = abort_flag + 1;
+        __threadfence_system();                                               /* this thread's pushes before the flag below */
+        if (tid == 0) *gave_up = failed ? 1u : 0u;
+        asm volatile("barrier.cta.sync 1, 512;" ::: "memory");
+        if ((uint32_t)tid < a.xf.members && !failed) {
+            st_release_sys(xf_flag(a.xf.peer[tid], parity, a.xf.index, blockIdx.x), a.xf.gen);
+            const unsigned int* flag = xf_flag(a.xf.peer[a.xf.index], parity, (uint32_t)tid, blockIdx.x);
+            if (ld_acquire_sys(flag) != a.xf.gen) {
+                const unsigned long long t0 = wall_ns();
+                bool ok = false;
+                while (!ok) {
+                    for (int i = 0; i < 64 && !ok; ++i) ok = ld_acquire_sys(flag) == a.xf.gen;
+                    if (!ok && wall_ns() - t0 > a.xf.wait_ns) break;
+                }
+                if (!ok) { *gave_up = 1u; if (a.status) atomicOr(a.status, SV_STATUS_TIMEOUT); }
+            }
+        }
+        asm volatile("barrier.cta.sync 1, 512;" ::: "memory");
+        if (*gave_up == 0u) {
+            const uint32_t r_lo = run_lo * 16u, r_hi = min(run_hi * 16u, a.rows[0]);
+            uint8_t* local = a.xf.peer[a.xf.index];
+            for (uint32_t r = r_lo + (uint32_t)tid; r < r_hi; r += GV_THREADS) {
+                float sum = 0.f;
+                for (uint32_t mm = 0; mm < a.xf.members; ++mm)
+                    sum += H::to_float(__ldcg(reinterpret_cast<const uint16_t*>(xf_slot(local, parity, mm, a.xf.slot_bytes, a.xf.members)) + r));
+                out[a.out_at[0] + r] = H::from_float(sum, hit);
+            }
+        }
+    }
     if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
 }
 
@@ -311,7 +353,7 @@ bool tq_gemv_fast_fits(const void* groups, uint64_t cols, uint64_t inputs) {
 }
 
 cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_t* rows_cap, const uint16_t* x, uint64_t cols, uint64_t inputs,
-                                uint64_t out_stride, unsigned int* over, cudaStream_t st) {
+                                uint64_t out_stride, unsigned int* over, cudaStream_t st, const XfParams* xf) {
     struct G { uint64_t codes[12], luts[12], rows[12], d[12], out_at[12], count; } g;
     memcpy(&g, groups, sizeof g);
     if ((uintptr_t)x % 4 != 0 || (inputs > 1 && cols % 2 != 0)) return cudaErrorInvalidValue;
@@ -365,6 +407,10 @@ cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_
     a.count = n; a.cols = (uint32_t)cols; a.inputs = (uint32_t)inputs; a.out_stride = out_stride;
     a.x_wide = ((uintptr_t)x % 16 == 0 && cols % 8 == 0) ? 1u : 0u;
     a.ts = ts; a.pi = pi; a.stage_bytes = stage_bytes; a.smem_bytes = smem_bytes;
+    if (xf) {
+        if (n != 1 || inputs != 1 || rows_cap || (uint64_t)a.rows[0] * 2u > xf->slot_bytes) return cudaErrorInvalidValue;      /* (the grid is at most 148 blocks: a flag each) */
+        a.xf = *xf;
+    }
     a.status = device_status_word();
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;

@@ -20,7 +20,7 @@ EXPORTS = (
     "silvann_b200_tier_decode", "silvann_b200_tier_stats", "silvann_b200_tier_decode_exchange",
     "silvann_b200_exchange_create", "silvann_b200_exchange_destroy", "silvann_b200_exchange_local", "silvann_b200_exchange_handle",
     "silvann_b200_exchange_connect_handles", "silvann_b200_exchange_connect_addresses", "silvann_b200_exchange_merge_finish",
-    "silvann_b200_exchange_vector_sum", "silvann_b200_exchange_deposit", "silvann_b200_mla_decode",
+    "silvann_b200_exchange_vector_sum", "silvann_b200_exchange_deposit", "silvann_b200_mla_decode", "silvann_b200_exchange_gemv_sum",
 )
 
 
@@ -75,6 +75,7 @@ def lib():
             "silvann_b200_exchange_merge_finish": [vp, vp, vp, vp, u64, u64, i32, vp, u32, vp],
             "silvann_b200_exchange_vector_sum": [vp, vp, vp, u64, i32, vp, u32, vp],
             "silvann_b200_exchange_deposit": [vp, u32, vp, u64, vp],
+            "silvann_b200_exchange_gemv_sum": [vp, vp, vp, vp, vp, u64, u64, u64, vp, u32, vp],
             "silvann_b200_prefill": [vp, vp, vp, vp, vp, u64, u64, u64, u64, u64, i32, vp, vp],
             "silvann_b200_deltanet": [vp, vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u32, u32, i32, vp, vp],
         }
@@ -247,6 +248,10 @@ class Exchange:
 
     def vector_sum(self, out, partial, n, dtype=FP16, over=None, wait_ms=0, stream=None):
         _check(lib().silvann_b200_exchange_vector_sum(self.handle, addr(out), addr(partial), n, dtype, addr(over), wait_ms, stream))
+
+    def gemv_sum(self, out, codes, scales, vec, width, rows, cols, over=None, wait_ms=0, stream=None):
+        """This card's share of a coded matrix times its share of the input, the cards' answers added in member order: one launch."""
+        _check(lib().silvann_b200_exchange_gemv_sum(self.handle, addr(out), addr(codes), addr(scales), addr(vec), width, rows, cols, addr(over), wait_ms, stream))
 
     def deposit(self, member, data, nbytes, stream=None):
         _check(lib().silvann_b200_exchange_deposit(self.handle, member, addr(data), nbytes, stream))

@@ -105,3 +105,35 @@ def test_chunked_runs_match_the_recurrence(cuda, port, kh, vh, d, rows, seqs, dt
     ext.deltanet(S, dev(cuda, conved), dev(cuda, w.z), dev(cuda, w.beta), dev(cuda, w.g), dev(cuda, w.w), out, kh, vh, d, rows, seqs, 1, dtype)
     cuda.cuda.synchronize()
     check(S.cpu().numpy(), S_want, host_bits(out), o_want, dtype, f"chunked {rows} rows")
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_a_large_batch_steps_in_one_launch_with_the_same_bits(cuda, port, dtype):
+    """Sixteen sequences of 32 heads of 128, one position: enough blocks that the launcher takes the block-a-head kernel
+    (the read-out finished in the same launch).  Against the checker, against the fp32 read-out, and bit for bit against
+    each sequence stepped alone (which takes the cluster form)."""
+    kh = vh = 32; d = 128; B = 16
+    w = workloads.config5(rows=B, heads=vh, d=d, dtype=dtype)
+    rng = np.random.default_rng(21 + dtype)
+    S0 = (rng.standard_normal((B, vh, d, d), dtype=np.float32) * 0.05).astype(np.float32)
+    S_want = S0.copy()
+    ro_want = np.zeros((B, vh * d), np.float32)
+    o_want = np.concatenate([port.deltanet(S_want[b], w.conved[b:b + 1], w.z[b:b + 1], w.beta[b:b + 1], w.g[b:b + 1], w.w, kh, vh, d, 1, 0, dtype,
+                                           readout=ro_want[b:b + 1]) for b in range(B)])
+    tc, tz, tb, tg, tw = (dev(cuda, x) for x in (w.conved, w.z, w.beta, w.g, w.w))
+    S = dev(cuda, S0)
+    out = cuda.zeros((B, vh * d), dtype=cuda.int16, device="cuda")
+    ro = cuda.zeros((B, vh * d), dtype=cuda.float32, device="cuda")
+    before = ext.counters()["launches"]
+    ext.deltanet(S, tc, tz, tb, tg, tw, out, kh, vh, d, 1, B, 0, dtype, readout=ro)
+    cuda.cuda.synchronize()
+    assert ext.counters()["launches"] == before + 1
+    check(S.cpu().numpy(), S_want, host_bits(out), o_want, dtype, "batched step")
+    assert np.abs(ro.cpu().numpy() - ro_want).max() <= 1e-4
+    ch = (2 * kh + vh) * d
+    for b in (0, 7, 15):
+        S1 = dev(cuda, S0[b])
+        o1 = cuda.zeros((1, vh * d), dtype=cuda.int16, device="cuda")
+        ext.deltanet(S1, tc.data_ptr() + 2 * b * ch, tz.data_ptr() + 2 * b * vh * d, tb.data_ptr() + 2 * b * vh, tg.data_ptr() + 2 * b * vh, tw, o1, kh, vh, d, 1, 1, 0, dtype)
+        cuda.cuda.synchronize()
+        assert cuda.equal(S1, S[b]) and cuda.equal(o1[0], out[b]), f"sequence {b} alone"

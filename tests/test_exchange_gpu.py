@@ -130,3 +130,43 @@ def test_refusals(cuda):
     with pytest.raises(ext.B200Error):
         x.deposit(0, t, 16)                                                 # a member does not deposit for itself
     x.close()
+
+
+@pytest.mark.parametrize("members,index,width,rows,cols", [(2, 0, 4, 5120, 2048), (2, 1, 8, 5120, 1024), (4, 2, 4, 1000, 4096), (8, 7, 8, 2048, 512)])
+def test_coded_projection_and_sum_in_one_launch(cuda, fam, port, members, index, width, rows, cols):
+    """The output projection of a head-sharded mixer with the sum over the cards in its epilogue: this card's share of a coded
+    matrix times its share of the input, pushed as the 16-bit partial the reference's turboquant_gemv would have written, the
+    absent members' partials deposited; the bits must be those of the door followed by the exchange's vector_sum."""
+    rng = np.random.default_rng(members * 10 + index + width)
+    w = to_bits((rng.standard_normal((rows, cols)) / np.sqrt(cols * members)).astype(np.float32), 0)
+    codes, scales = oracle.tq_encode_rows(port, w, width)
+    vec = to_bits(rng.standard_normal(cols).astype(np.float32), 0)
+    tc, ts, tv = dev(cuda, codes), dev(cuda, scales), dev(cuda, vec)
+    others = {m: to_bits(rng.standard_normal(rows).astype(np.float32) * 0.5, 0) for m in range(members) if m != index}
+    x = ext.Exchange(members, index, 2 * rows)
+    x.connect_alone()
+    # the unfused pair: the door, then the exchange's sum
+    mine = cuda.zeros(rows, dtype=cuda.int16, device="cuda")
+    fam.nn.turboquant_gemv(mine.data_ptr(), tc.data_ptr(), codes.nbytes, ts.data_ptr(), scales.nbytes, tv.data_ptr(), width, rows, cols, None)
+    assert fam.sys.compute_completed()
+    t_others = {m: dev(cuda, p) for m, p in others.items()}
+    for m, t in t_others.items():
+        x.deposit(m, t, 2 * rows)
+    want = cuda.zeros(rows, dtype=cuda.int16, device="cuda")
+    x.vector_sum(want, mine, rows, 0, wait_ms=200)
+    for call in range(2):
+        for m, t in t_others.items():
+            x.deposit(m, t, 2 * rows)
+        got = cuda.full((rows,), 0x1234, dtype=cuda.int16, device="cuda")
+        x.gemv_sum(got, tc, ts, tv, width, rows, cols, wait_ms=200)
+        cuda.cuda.synchronize()
+        assert ext.device_status() == 0
+        assert cuda.equal(got, want), f"call {call}"
+    # and against the checker: the restatement's gemv for this card, the members added in order
+    s = np.zeros(rows, np.float32)
+    part = {index: oracle.tq_gemv(port, codes, scales.view(np.uint8).copy(), vec, width, rows, cols), **others}
+    for m in range(members):
+        s += from_bits(part[m], 0)
+    diff = np.abs(from_bits(host_bits(want), 0) - from_bits(to_bits(s, 0), 0))
+    assert diff.max() <= 4e-3, diff.max()
+    x.close()

@@ -38,6 +38,25 @@ def _rank(rank, world, port, tmp):
     torch.cuda.synchronize()
     assert ext.device_status() == 0
     np.save(Path(tmp) / f"p{rank}.npy", pushed.cpu().numpy().view(np.uint16))
+    # the same sum with its producer: each rank's share of a coded output projection, the partials exchanged in the epilogue
+    rows, cols, width = 5120, 1024, 4
+    P = oracle.port()
+    grng = np.random.default_rng(80 + rank)
+    codes, scales = oracle.tq_encode_rows(P, oracle.to_bits((grng.standard_normal((rows, cols)) / np.sqrt(cols * world)).astype(np.float32), 0), width)
+    vec = oracle.to_bits(grng.standard_normal(cols).astype(np.float32), 0)
+    up16 = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16 if a.dtype == np.uint16 else np.uint8)).cuda()
+    tc, ts, tv = up16(codes), up16(scales), up16(vec)
+    fused = torch.zeros(rows, dtype=torch.int16, device="cuda")
+    for _ in range(2):
+        peer.exchange.gemv_sum(fused, tc, ts, tv, width, rows, cols, wait_ms=5000)
+    part = torch.zeros(rows, dtype=torch.int16, device="cuda")
+    fam.nn.turboquant_gemv(part.data_ptr(), tc.data_ptr(), codes.nbytes, ts.data_ptr(), scales.nbytes, tv.data_ptr(), width, rows, cols, None)
+    assert fam.sys.compute_completed()
+    unfused = peer.sum(part, wait_ms=5000)
+    torch.cuda.synchronize()
+    assert ext.device_status() == 0
+    assert torch.equal(fused, unfused), "the fused projection + sum differs from the door followed by the sum"
+    np.save(Path(tmp) / f"g{rank}.npy", fused.cpu().numpy().view(np.uint16))
     # and a KV range split over the two ranks: each attends its half, the exchange kernel folds
     qh, kvh, d, L = 8, 1, 128, 4096
     rng = np.random.default_rng(70)
@@ -74,6 +93,7 @@ def test_partial_sums_over_two_processes(cuda, tmp_path):
     mp.spawn(_rank, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     s0, s1, want = (np.load(tmp_path / f) for f in ("s0.npy", "s1.npy", "want.npy"))
     assert np.array_equal(s0, s1) and np.array_equal(s0, want)
+    assert np.array_equal(np.load(tmp_path / "g0.npy"), np.load(tmp_path / "g1.npy"))
     p0, p1 = np.load(tmp_path / "p0.npy"), np.load(tmp_path / "p1.npy")
     assert np.array_equal(p0, want) and np.array_equal(p1, want)
     import oracle
