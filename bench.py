@@ -937,6 +937,21 @@ def long_context(torch, dist, rank, world, steps, pk):
         import silvann_b200
         vsum = sharded.family_vector_sum(torch, silvann_b200.family())
         out["tp_sum_allgather_us"] = timed(lambda: sharded.sum_over_ranks(part, dist, vsum), 50) * 1e3
+        # the same sum with its producer: each rank's share (4,096 / N columns) of a 4-bit coded 5,120-row output projection, the partials
+        # exchanged and added in the kernel's epilogue — against the door followed by the sum above
+        cols = 4096 // world
+        gen = torch.Generator(device="cuda"); gen.manual_seed(90 + rank)
+        codes = torch.randint(0, 256, (hidden, cols // 2), generator=gen, device="cuda", dtype=torch.uint8)
+        scales = ((torch.rand((hidden,), generator=gen, device="cuda") * 0.5 + 0.75) * (3.0 / 4096 ** 0.5)).to(torch.float16)
+        vec = torch.randn((cols,), generator=gen, device="cuda", dtype=torch.float16)
+        fused = torch.empty_like(part)
+        out["o_projection_and_tp_sum_fused_us"] = timed(lambda: peer.exchange.gemv_sum(fused, codes, scales, vec, 4, hidden, cols), 200) * 1e3
+        fam = silvann_b200.family()
+
+        def unfused():
+            fam.nn.turboquant_gemv(part.data_ptr(), codes.data_ptr(), codes.numel(), scales.data_ptr(), scales.numel() * 2, vec.data_ptr(), 4, hidden, cols, None)
+            peer.sum(part, total)
+        out["o_projection_then_tp_sum_us"] = timed(unfused, 200) * 1e3
         peer.close()
     out["note"] = ("kv heads sharded over ranks" + (", each kv head's range halved over two ranks, residuals pushed into the partner's memory and folded by one kernel a rank (no NCCL on the data path)" if world > kvh else ", no exchange")
                    + "; tiered: first 65,536 positions streamed from pinned host RAM each step (PCIe-bound); resident: all positions in HBM; strong scaling: whole-job bytes over the slowest rank's time")

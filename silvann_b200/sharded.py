@@ -5,8 +5,9 @@ attention doors never know (runtime/silvann_runtime/qwen3_5.py:112-134) — and 
 cards than kv heads.  Here a replicated kv head is put to work instead: the ranks that share it split its KV RANGE, each
 produces the residual (m, l, acc) of its range with the same decode kernel, and the residuals are folded with the
 reference's merge arithmetic (engine/src/packages/nn/gpu/kernels/kernels.cuh:1243-1255).  The residual is the wire
-format: q_heads_local * (head_dim + 2) floats a rank, so the exchange is one small all-gather among the ranks of a kv
-head (NCCL over NVLink on the GPUs, gloo in the CPU tests) and there is no collective at all while ranks <= kv heads.
+format: q_heads_local * (head_dim + 2) floats a rank.  On GPUs the exchange is the library's own kernel over peer memory
+(push, signal, bounded wait, fold in range order: one launch a rank, connect_exchange wires the ranks once); under gloo in
+the CPU tests it is one small all-gather and a fold here.  There is no exchange at all while ranks <= kv heads.
 
 This module is host logic only: it decides shards and drives the exchange; arithmetic is the library's (ext.merge,
 ext.finish), injected so that the plumbing can be exercised without a GPU.
