@@ -1265,6 +1265,18 @@ def run_case(args):
             i = lstate["i"] = (lstate["i"] + 1) % copies
             ext.mla_decode(om, None, qm, lat[i], 64, Lm, ext.FP16, int(os.environ.get("MLA_BLOCKS", "0")))
         work, unit = Lm * 512 * 2 + 2 * 64 * 512 * 2, "bytes"
+    elif name == "exchange_small":
+        # the exchange's fold alone on one card: 8 heads of 128 (configuration 4's share at 8 GPUs), the partner's push deposited
+        x = ext.Exchange(2, 0, 8 * 130 * 4)
+        x.connect_alone()
+        mine = torch.randn((8, 130), generator=gen, device="cuda", dtype=torch.float32).abs() + 0.5
+        theirs = torch.randn((8, 130), generator=gen, device="cuda", dtype=torch.float32).abs() + 0.5
+        om = torch.zeros((8, 128), device="cuda", dtype=torch.bfloat16)
+
+        def fn():
+            x.deposit(1, theirs, 8 * 130 * 4)
+            x.merge_finish(om, None, mine, 8, 128, ext.BF16, wait_ms=200)
+        work, unit = 2 * 8 * 130 * 4, "bytes"
     elif name == "prefill_small":
         qh, kvh, d, T = 16, 2, 256, 2048
         q = torch.randn((T, qh, d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.5
@@ -1288,7 +1300,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the secondary configurations (faster; used under profilers)")
     ap.add_argument("--only", default=None, choices=["long_context"], help="run configuration 4 alone (any N) and print its object")
-    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, decode_cfg1, decode_cfg1_graph, tq8_small, tq4_small, deltanet_64, deltanet_prefill, prefill_small, mla_2048, mla_65536)")
+    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, decode_cfg1, decode_cfg1_graph, tq8_small, tq4_small, deltanet_64, deltanet_prefill, prefill_small, mla_2048, mla_65536, exchange_small)")
     args = ap.parse_args()
     if args.case:
         run_case(args)

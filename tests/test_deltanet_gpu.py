@@ -107,12 +107,13 @@ def test_chunked_runs_match_the_recurrence(cuda, port, kh, vh, d, rows, seqs, dt
     check(S.cpu().numpy(), S_want, host_bits(out), o_want, dtype, f"chunked {rows} rows")
 
 
+@pytest.mark.parametrize("B", [16, 24])
 @pytest.mark.parametrize("dtype", [0, 1])
-def test_a_large_batch_steps_in_one_launch_with_the_same_bits(cuda, port, dtype):
-    """Sixteen sequences of 32 heads of 128, one position: enough blocks that the launcher takes the block-a-head kernel
-    (the read-out finished in the same launch).  Against the checker, against the fp32 read-out, and bit for bit against
-    each sequence stepped alone (which takes the cluster form)."""
-    kh = vh = 32; d = 128; B = 16
+def test_a_large_batch_steps_in_one_launch_with_the_same_bits(cuda, port, dtype, B):
+    """Sixteen / twenty-four sequences of 32 heads of 128, one position: enough blocks that the launcher takes the
+    block-a-head kernel (the read-out finished in the same launch).  Against the checker, against the fp32 read-out, and bit
+    for bit against each sequence stepped alone (which takes the cluster form)."""
+    kh = vh = 32; d = 128
     w = workloads.config5(rows=B, heads=vh, d=d, dtype=dtype)
     rng = np.random.default_rng(21 + dtype)
     S0 = (rng.standard_normal((B, vh, d, d), dtype=np.float32) * 0.05).astype(np.float32)
@@ -131,7 +132,7 @@ def test_a_large_batch_steps_in_one_launch_with_the_same_bits(cuda, port, dtype)
     check(S.cpu().numpy(), S_want, host_bits(out), o_want, dtype, "batched step")
     assert np.abs(ro.cpu().numpy() - ro_want).max() <= 1e-4
     ch = (2 * kh + vh) * d
-    for b in (0, 7, 15):
+    for b in (0, 7, B - 1):
         S1 = dev(cuda, S0[b])
         o1 = cuda.zeros((1, vh * d), dtype=cuda.int16, device="cuda")
         ext.deltanet(S1, tc.data_ptr() + 2 * b * ch, tz.data_ptr() + 2 * b * vh * d, tb.data_ptr() + 2 * b * vh, tg.data_ptr() + 2 * b * vh, tw, o1, kh, vh, d, 1, 1, 0, dtype)

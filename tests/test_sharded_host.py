@@ -108,3 +108,68 @@ def test_partial_sums_over_two_ranks_are_the_same_bits_everywhere(tmp_path):
     mp.spawn(_sum_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     s0, s1, want = (np.load(tmp_path / f) for f in ("s0.npy", "s1.npy", "want.npy"))
     assert np.array_equal(s0, s1) and np.array_equal(s0, want)
+
+
+class _FakeExchange:
+    """Stands in for ext.Exchange on a machine without a GPU: a handle that says whose it is, and a record of the wiring."""
+    def __init__(self, members, index, slot_bytes):
+        self.members, self.index, self.slot_bytes, self.wired = members, index, slot_bytes, None
+        self.me = int(os.environ["RANK_FOR_FAKE"])
+
+    def ipc_handle(self):
+        return bytes([self.me]) * 64
+
+    def connect_handles(self, handles):
+        self.wired = [h[0] for h in handles]
+
+
+class _FakeExt:
+    Exchange = _FakeExchange
+
+
+def _wire_main(rank, world, port, tmp):
+    sys.path.insert(0, str(ROOT))
+    import torch
+    import torch.distributed as dist
+    from silvann_b200 import sharded as sh
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK_FOR_FAKE=str(rank))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    shard = sh.shard_plan(8, 1, 1000, world)[rank]                 # one kv head over two ranks: a range split, group [0, 1]
+    x = sh.connect_exchange(torch, _FakeExt, dist, shard.group, rank, 8 * 66 * 4)
+    alone = sh.connect_exchange(torch, _FakeExt, dist, [rank], rank, 64)       # a rank without partners still takes part in the gather
+    np.save(Path(tmp) / f"w{rank}.npy", np.array([x.members, x.index] + x.wired + [alone.members, -1 if alone.wired is None else 1]))
+
+    calls = []
+
+    class Tier:
+        def __init__(self, *a): pass
+        def decode(self, *a): calls.append("decode")
+        def decode_exchange(self, ex, *a): calls.append(("decode_exchange", ex is x))
+        def close(self): pass
+
+    class Ext:
+        pass
+    Ext.Tier = Tier
+
+    class Torch:
+        float32, int16 = None, None
+        @staticmethod
+        def zeros(*a, **k): return None
+    runner = sh.LongContextRank(Torch, Ext, shard, 64, 0, None, None, 0, None, None, shard.positions, dist, None, exchange=x)
+    runner.step(None)
+    lone = sh.LongContextRank(Torch, Ext, sh.shard_plan(8, 2, 1000, world)[rank], 64, 0, None, None, 0, None, None, 1000, dist, None, exchange=None)
+    lone.step(None)
+    assert calls == [("decode_exchange", True), "decode"], calls
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_exchange_handles_reach_the_members_of_a_group_over_gloo(tmp_path):
+    """The one-time wiring of the exchange: every rank's buffer handle gathered over the world, each rank connecting the
+    handles of ITS group in group order; and the step's dispatch — a rank in a range split makes one decode_exchange call, a
+    rank alone on its heads one decode call."""
+    import torch.multiprocessing as mp
+    port = 33500 + os.getpid() % 2000
+    mp.spawn(_wire_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    w0, w1 = np.load(tmp_path / "w0.npy"), np.load(tmp_path / "w1.npy")
+    assert list(w0) == [2, 0, 0, 1, 1, -1] and list(w1) == [2, 1, 0, 1, 1, -1]
