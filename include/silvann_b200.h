@@ -432,8 +432,9 @@ int silvann_b200_exchange_vector_sum(silvann_b200_exchange* exchange, void* out,
 int silvann_b200_exchange_gemv_sum(silvann_b200_exchange* exchange, void* out, const void* codes, const void* scales, const void* vec,
                                    uint64_t width, uint64_t rows, uint64_t cols, sv_fault* over, uint32_t wait_ms, void* stream);
 /* Stands in for an absent member where there are fewer cards than members (a one-card walk of a many-card plan): puts
- * `data` where that member's push of the NEXT exchange would land and sets its flags.  Same stream as the exchange. */
-int silvann_b200_exchange_deposit(silvann_b200_exchange* exchange, uint32_t member, const void* data, uint64_t bytes, void* stream);
+ * `data` where that member's push of the NEXT exchange would land, in the form that exchange moves it: `unit_bytes` 4 for a
+ * residual (merge_finish) or a 16-bit vector (vector_sum), 2 for the rows of gemv_sum.  Same stream as the exchange. */
+int silvann_b200_exchange_deposit(silvann_b200_exchange* exchange, uint32_t member, const void* data, uint64_t bytes, uint32_t unit_bytes, void* stream);
 /* silvann_b200_tier_decode for a member of a range split: the member's residual over its two tiers, then the exchange,
  * as one call. */
 int silvann_b200_tier_decode_exchange(silvann_b200_tier* tier, silvann_b200_exchange* exchange, void* o, float* res, const void* q,

@@ -293,8 +293,8 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
             const uint16_t y = H::from_float(sum * H::to_float(scale), hit);
             if (a.xf.members == 0u) out[out_row + o_row + o_in * out_input] = y;
             else
-                for (uint32_t mm = 0; mm < a.xf.members; ++mm)                   /* this card's partial of the row, to every member */
-                    reinterpret_cast<uint16_t*>(xf_slot(a.xf.peer[mm], a.xf.gen & 1u, a.xf.index, a.xf.slot_bytes, a.xf.members))[o_row] = y;
+                for (uint32_t mm = 0; mm < a.xf.members; ++mm)                   /* this card's partial of the row, to every member: a tagged word */
+                    xf_store(xf_slot(a.xf.peer[mm], a.xf.gen & 1u, a.xf.index, a.xf.slot_words, a.xf.members) + o_row, (uint32_t)y, a.xf.gen);
         }
         tile += nt;
     }
@@ -303,35 +303,23 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
     if (failed && tid == 0)
         for (uint32_t st = 0; st < S; ++st) for (uint32_t i = 0; i < 4096u && !mbar_try_wait(&full[st], 0u) && !mbar_try_wait(&full[st], 1u); ++i) { }
     if (a.xf.members != 0u) {
-        /* ---- the exchange: the block's rows are on every member; say so, wait (bounded) for the members' same rows, add ----
-         * Every member runs this kernel over a matrix of the same shape, so block b owns the same rows everywhere and the
-         * flags are a block's own: no block waits for another block of its own card. */
+        /* ---- the exchange: the block's rows are on their way to every member; take the members' same rows as they come ----
+         * Every member runs this kernel over a matrix of the same shape, so block b owns the same rows everywhere: no block
+         * waits for another block of its own card.  A row is one tagged word, so nothing is fenced or flagged: a thread
+         * polls (bounded) the words of the row it adds. */
         const uint32_t parity = a.xf.gen & 1u;
-        volatile uint32_t* gave_up = abort_flag + 1;
-        __threadfence_system();                                               /* this thread's pushes before the flag below */
-        if (tid == 0) *gave_up = failed ? 1u : 0u;
-        asm volatile("barrier.cta.sync 1, 512;" ::: "memory");
-        if ((uint32_t)tid < a.xf.members && !failed) {
-            st_release_sys(xf_flag(a.xf.peer[tid], parity, a.xf.index, blockIdx.x), a.xf.gen);
-            const unsigned int* flag = xf_flag(a.xf.peer[a.xf.index], parity, (uint32_t)tid, blockIdx.x);
-            if (ld_acquire_sys(flag) != a.xf.gen) {
-                const unsigned long long t0 = wall_ns();
-                bool ok = false;
-                while (!ok) {
-                    for (int i = 0; i < 64 && !ok; ++i) ok = ld_acquire_sys(flag) == a.xf.gen;
-                    if (!ok && wall_ns() - t0 > a.xf.wait_ns) break;
-                }
-                if (!ok) { *gave_up = 1u; if (a.status) atomicOr(a.status, SV_STATUS_TIMEOUT); }
-            }
-        }
-        asm volatile("barrier.cta.sync 1, 512;" ::: "memory");
-        if (*gave_up == 0u) {
+        if (!failed) {
             const uint32_t r_lo = run_lo * 16u, r_hi = min(run_hi * 16u, a.rows[0]);
-            uint8_t* local = a.xf.peer[a.xf.index];
+            unsigned long long t0 = 0ull;
+            bool ok = true;
             for (uint32_t r = r_lo + (uint32_t)tid; r < r_hi; r += GV_THREADS) {
+                uint32_t part16[XF_MEMBERS_MAX];
+                xf_gather(a.xf, parity, r, part16, t0, ok);
+                if (!ok) { if (a.status) atomicOr(a.status, SV_STATUS_TIMEOUT); break; }
                 float sum = 0.f;
-                for (uint32_t mm = 0; mm < a.xf.members; ++mm)
-                    sum += H::to_float(__ldcg(reinterpret_cast<const uint16_t*>(xf_slot(local, parity, mm, a.xf.slot_bytes, a.xf.members)) + r));
+#pragma unroll
+                for (uint32_t mm = 0; mm < XF_MEMBERS_MAX; ++mm)
+                    if (mm < a.xf.members) sum += H::to_float((uint16_t)part16[mm]);
                 out[a.out_at[0] + r] = H::from_float(sum, hit);
             }
         }
@@ -408,7 +396,7 @@ cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_
     a.x_wide = ((uintptr_t)x % 16 == 0 && cols % 8 == 0) ? 1u : 0u;
     a.ts = ts; a.pi = pi; a.stage_bytes = stage_bytes; a.smem_bytes = smem_bytes;
     if (xf) {
-        if (n != 1 || inputs != 1 || rows_cap || (uint64_t)a.rows[0] * 2u > xf->slot_bytes) return cudaErrorInvalidValue;      /* (the grid is at most 148 blocks: a flag each) */
+        if (n != 1 || inputs != 1 || rows_cap || (uint64_t)a.rows[0] > xf->slot_words) return cudaErrorInvalidValue;
         a.xf = *xf;
     }
     a.status = device_status_word();

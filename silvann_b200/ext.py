@@ -74,7 +74,7 @@ def lib():
             "silvann_b200_exchange_connect_addresses": [vp, vp],
             "silvann_b200_exchange_merge_finish": [vp, vp, vp, vp, u64, u64, i32, vp, u32, vp],
             "silvann_b200_exchange_vector_sum": [vp, vp, vp, u64, i32, vp, u32, vp],
-            "silvann_b200_exchange_deposit": [vp, u32, vp, u64, vp],
+            "silvann_b200_exchange_deposit": [vp, u32, vp, u64, u32, vp],
             "silvann_b200_exchange_gemv_sum": [vp, vp, vp, vp, vp, u64, u64, u64, vp, u32, vp],
             "silvann_b200_prefill": [vp, vp, vp, vp, vp, u64, u64, u64, u64, u64, i32, vp, vp],
             "silvann_b200_deltanet": [vp, vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u32, u32, i32, vp, vp],
@@ -240,7 +240,7 @@ class Exchange:
 
     def connect_alone(self):
         """For a one-card walk of a many-card plan: this member's own buffer stands in for every absent member's, so the
-        kernel's pushes and flags land somewhere real; the absent members' pieces arrive by deposit()."""
+        kernel's pushes land somewhere real; the absent members' pieces arrive by deposit()."""
         self.connect_addresses([self.local()[0]] * self.members)
 
     def merge_finish(self, o, res, res_local, q_heads, head_dim, dtype=FP16, over=None, wait_ms=0, stream=None):
@@ -253,8 +253,9 @@ class Exchange:
         """This card's share of a coded matrix times its share of the input, the cards' answers added in member order: one launch."""
         _check(lib().silvann_b200_exchange_gemv_sum(self.handle, addr(out), addr(codes), addr(scales), addr(vec), width, rows, cols, addr(over), wait_ms, stream))
 
-    def deposit(self, member, data, nbytes, stream=None):
-        _check(lib().silvann_b200_exchange_deposit(self.handle, member, addr(data), nbytes, stream))
+    def deposit(self, member, data, nbytes, unit=4, stream=None):
+        """An absent member's piece of the next exchange; unit 4 for merge_finish and vector_sum, 2 for gemv_sum's rows."""
+        _check(lib().silvann_b200_exchange_deposit(self.handle, member, addr(data), nbytes, unit, stream))
 
 
 def prefill(o, q, k, v, q_heads, kv_heads, head_dim, first, rows, dtype=FP16, over=None, stream=None, res=None):

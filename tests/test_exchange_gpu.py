@@ -1,6 +1,6 @@
-"""The exchange kernels (push, signal, bounded wait, combine in member order) on ONE B200: the absent members' pushes are
-stood in for by `deposit`, which puts a piece where that member's store would have landed and sets its flags — the kernel
-under test then runs its own push, its flag protocol and its fold exactly as it does among real cards.
+"""The exchange kernels (push, bounded wait, combine in member order) on ONE B200: the absent members' pushes are stood in
+for by `deposit`, which puts a piece where that member's stores would have landed, as the same tagged words — the kernel
+under test then runs its own push, its polls and its fold exactly as it does among real cards.
 
 Bars: the fold equals attention_merge applied in member order and attention_finish (this library's own doors, which are
 checked against the reference elsewhere) bit for bit, and the checker's merge within fp32 rounding; the sum equals the
@@ -156,7 +156,7 @@ def test_coded_projection_and_sum_in_one_launch(cuda, fam, port, members, index,
     x.vector_sum(want, mine, rows, 0, wait_ms=200)
     for call in range(2):
         for m, t in t_others.items():
-            x.deposit(m, t, 2 * rows)
+            x.deposit(m, t, 2 * rows, unit=2)
         got = cuda.full((rows,), 0x1234, dtype=cuda.int16, device="cuda")
         x.gemv_sum(got, tc, ts, tv, width, rows, cols, wait_ms=200)
         cuda.cuda.synchronize()
