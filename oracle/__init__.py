@@ -428,6 +428,50 @@ def tq_gemv(impl, codes, luts, x, d, rows, cols):
     return out
 
 
+# ---- the expert-major GEMM doors (a coded matrix over rows of x named by pairs) through a family ---------------------
+
+def _address(p) -> int:
+    return int(p.value or 0) if isinstance(p, C.c_void_p) else int(p or 0)
+
+
+def expert_groups_struct(groups, ptr):
+    """groups: [(codes, luts, out_rows, d, out_at, pairs_at, pairs)] -> the by-value struct the door takes."""
+    from silvann_b200.abi import ExpertGroups
+    g = ExpertGroups()
+    for i, (codes, luts, out_rows, d, out_at, pairs_at, pairs) in enumerate(groups):
+        g.codes[i] = _address(ptr(codes))
+        g.luts[i] = _address(ptr(luts)) if luts is not None else 0
+        g.out_rows[i], g.d[i], g.out_at[i], g.pairs_at[i], g.pairs[i] = out_rows, d, out_at, pairs_at, pairs
+    g.count = len(groups)
+    return g
+
+
+def expert_rows(impl, out, codes, luts, x, pairs, count, d, out_rows, cols, w_room=None, l_room=None):
+    """expert_rows into `out` (a 16-bit array [out rows][out_rows], written in place): a family's door (the restatement has none)."""
+    P = getattr(impl, "ptr", _p)
+    over = impl.over if getattr(impl, "over", None) is not None else None
+    impl.nn.expert_rows(P(out), P(codes), codes.nbytes if w_room is None else w_room, P(luts) if luts is not None else None,
+                        (luts.nbytes if luts is not None else 0) if l_room is None else l_room,
+                        P(x), P(pairs), count, d, out_rows, cols, P(over) if over is not None else None)
+    impl.wait()
+    return out
+
+
+def expert_rows_sum(impl, acc, codes, luts, x, pairs, w, count, d, out_rows, cols):
+    P = getattr(impl, "ptr", _p)
+    impl.nn.expert_rows_sum(P(acc), P(codes), codes.nbytes, P(luts) if luts is not None else None, luts.nbytes if luts is not None else 0, P(x), P(pairs), P(w), count, d, out_rows, cols)
+    impl.wait()
+    return acc
+
+
+def expert_groups(impl, out, groups, x, pairs, cols):
+    P = getattr(impl, "ptr", _p)
+    over = impl.over if getattr(impl, "over", None) is not None else None
+    impl.nn.expert_groups(P(out), expert_groups_struct(groups, P), P(x), P(pairs), cols, P(over) if over is not None else None)
+    impl.wait()
+    return out
+
+
 # ---- the GLM mixer's doors through either implementation ------------------------------------------------------------
 
 def kda_steps(impl, S, conved, f, b, dt, a_log, gate, w, heads, d, lower, eps, rows, decayed=False):

@@ -1,0 +1,419 @@
+/* expert.cu — the expert-major GEMM: a coded matrix applied to several rows of `x` at once (a prompt chunk's projections).
+ *
+ * The reference's doors (engine/src/packages/nn/gpu/kernels/kernels.cuh:1513-1624 the shared body; expert_rows :1626-1633,
+ * expert_rows_sum :1640-1648, expert_groups :1650-1660, expert_rows_finish :1662-1672, expert_rows_reduce :1676-1692,
+ * expert_pairs_rows :3864-3871; declared in engine/src/packages/nn/contracts/abi/gpu.cuh) read a list of PAIRS: pair j is
+ * (row of x it reads, row of out it writes), and
+ *     out[pair's out row][r] = half(scale_r · sum_c level(code[r][c]) · x[pair's x row][c])
+ * for every row r of the matrix the rooms hold; at 16 bits the codes are the halves themselves and the scale is 1.  The
+ * levels are fp16 table entries and x is fp16, so every product is exact in fp32 and only the order of the sum is a family's
+ * own.  The prompt path of a mixer (engine/src/packages/ai_qwen_3/cpu/opcodes/prefill__abi.cuh:135-237) makes its q, k, v
+ * and o projections through these doors, up to 256 rows a call.
+ *
+ * Two kernels.  `expert_rows_kernel` is the door as worded — any width, any shape, a block a matrix row, eight pairs a pass.
+ * `expert_fast_kernel` is the one a prompt runs on: a block owns 128 matrix rows and up to 128 pairs and walks the columns 64
+ * at a time;
+ *   · eight producer warps expand the codes into fp16 in shared memory, K-major with the 128-byte swizzle, as the A operand
+ *     (a code byte is ONE shared-memory lookup in a table of 256 entries of 128 bytes — a lane reads its own bank, so no
+ *     lookup ever conflicts; at 4 bits an entry is the byte's two levels, at 8 bits the level twice), and gather the pairs'
+ *     rows of x as the B operand — both through cp.async three column blocks ahead, the raw codes through a small staging ring;
+ *   · one thread issues tcgen05.mma (M 128, N = the pairs rounded up to 16, K 16 a step), accumulating in tensor memory, and
+ *     gives a stage back to the producers by a commit on its mbarrier;
+ *   · the producers then read the accumulator out of tensor memory, scale a row by its fp16 scale, round once and store —
+ *     or, for expert_rows_sum, add weight · value onto the fp32 running sum.
+ * Shapes the fast kernel takes: widths 4, 8 and 16, columns a multiple of 64, codes and x on 16 bytes.  Every mbarrier wait
+ * is bounded; one that runs out ORs "B2TO" into the device's status word and the block leaves through the common exit
+ * (copies in flight waited for, tensor memory given back). */
+#include "common.cuh"
+#include "tcgen05.cuh"
+#include "kernels.h"
+#include <atomic>
+#include <string.h>
+
+namespace sv {
+
+using H = Elem<SV_DTYPE_FP16>;
+
+static __device__ const uint16_t g_tq_levels_expert[318] = {
+#include "tq_levels.inc"
+};
+
+struct ExpertGroups { uint64_t codes[12], luts[12], out_rows[12], d[12], out_at[12], pairs_at[12], pairs[12], count; };
+
+__host__ __device__ __forceinline__ bool ex_width_known(uint64_t d) { return d == 1 || d == 2 || d == 3 || d == 4 || d == 5 || d == 8 || d == 16; }
+__host__ __device__ __forceinline__ uint32_t ex_table_at(uint64_t d) { return d == 1 ? 0u : d == 2 ? 2u : d == 3 ? 6u : d == 4 ? 14u : d == 5 ? 30u : 62u; }
+__host__ __device__ __forceinline__ uint64_t ex_row_bytes(uint64_t d, uint64_t cols) { const uint64_t per = 16 / d; return ((cols + per - 1) / per) * 2; }
+__device__ __forceinline__ float ex_level(uint64_t d, uint32_t code) {
+    return d == 16 ? H::to_float((uint16_t)code) : H::to_float(g_tq_levels_expert[ex_table_at(d) + code]);
+}
+
+/* ---- the door as worded: a block a matrix row, eight pairs a pass ------------------------------------------------------ */
+__global__ void __launch_bounds__(128) expert_rows_kernel(uint16_t* out, float* acc, const uint8_t* weights, uint64_t held, const uint8_t* luts,
+                                                          const uint16_t* x, const uint32_t* pairs, const uint16_t* w, uint64_t count, uint64_t d,
+                                                          uint64_t out_rows, uint64_t cols, unsigned int* over) {
+    __shared__ float sh[4][8];
+    const uint64_t per = 16 / d, row_bytes = ex_row_bytes(d, cols), units = (cols + per - 1) / per;
+    const uint32_t mask = (uint32_t)((1ull << d) - 1ull);
+    bool hit = false;
+    for (uint64_t r = blockIdx.x; r < out_rows && r < held; r += gridDim.x) {
+        const uint8_t* row = weights + r * row_bytes;
+        const float scale = d == 16 ? 1.0f : H::to_float((uint16_t)((uint32_t)luts[r * 2] | ((uint32_t)luts[r * 2 + 1] << 8)));
+        for (uint64_t j0 = 0; j0 < count; j0 += 8) {
+            const uint16_t* xr[8];
+#pragma unroll
+            for (int b = 0; b < 8; ++b) xr[b] = j0 + b < count ? x + (uint64_t)pairs[2 * (j0 + b)] * cols : nullptr;
+            float part[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (uint64_t u = threadIdx.x; u < units; u += blockDim.x) {
+                const uint32_t unit = (uint32_t)row[u * 2] | ((uint32_t)row[u * 2 + 1] << 8);
+                const uint64_t c0 = u * per;
+                for (uint64_t s = 0; s < per && c0 + s < cols; ++s) {
+                    const float lv = ex_level(d, (unit >> (uint32_t)(d * s)) & mask);
+#pragma unroll
+                    for (int b = 0; b < 8; ++b)
+                        if (xr[b]) part[b] += lv * H::to_float(xr[b][c0 + s]);
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < 8; ++b)
+                for (int o = 16; o > 0; o >>= 1) part[b] += __shfl_xor_sync(0xffffffffu, part[b], o);
+            if ((threadIdx.x & 31) == 0)
+#pragma unroll
+                for (int b = 0; b < 8; ++b) sh[threadIdx.x >> 5][b] = part[b];
+            __syncthreads();
+            if (threadIdx.x < 8 && j0 + threadIdx.x < count) {
+                const uint64_t j = j0 + threadIdx.x;
+                const float v = ((sh[0][threadIdx.x] + sh[1][threadIdx.x]) + (sh[2][threadIdx.x] + sh[3][threadIdx.x])) * scale;
+                const uint64_t at = (uint64_t)pairs[2 * j + 1] * out_rows + r;
+                if (out) out[at] = H::from_float(v, hit);
+                else acc[at] += v * H::to_float(w[pairs[2 * j]]);
+            }
+            __syncthreads();
+        }
+    }
+    if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
+}
+
+/* expert_rows_finish: out[i] = half(residual[i] + acc[i]), acc[i] back to zero (residual may be out) */
+__global__ void __launch_bounds__(256) expert_rows_finish_kernel(uint16_t* out, float* acc, const uint16_t* residual, uint64_t n, unsigned int* over) {
+    bool hit = false;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        out[i] = H::from_float(H::to_float(residual[i]) + acc[i], hit);
+        acc[i] = 0.0f;
+    }
+    if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
+}
+/* expert_rows_reduce: acc is n rows of k picks of cols floats; out[t][c] = half(residual[t][c] + the picks added in their order) */
+__global__ void __launch_bounds__(256) expert_rows_reduce_kernel(uint16_t* out, float* acc, const uint16_t* residual, uint64_t n, uint64_t k, uint64_t cols,
+                                                                 unsigned int* over) {
+    bool hit = false;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n * cols; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t t = i / cols, c = i - t * cols;
+        float s = 0.0f;
+        for (uint64_t j = 0; j < k; ++j) {
+            float* a = acc + (t * k + j) * cols + c;
+            s += *a;
+            *a = 0.0f;
+        }
+        out[i] = H::from_float(H::to_float(residual[i]) + s, hit);
+    }
+    if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
+}
+/* expert_pairs_rows: pair t = (x_step · t + x_at, out_step · t + out_at), written on the card */
+__global__ void __launch_bounds__(256) expert_pairs_rows_kernel(uint32_t* pairs, uint64_t n, uint64_t x_step, uint64_t x_at, uint64_t out_step, uint64_t out_at) {
+    for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (uint64_t)gridDim.x * blockDim.x) {
+        pairs[2 * t] = (uint32_t)(x_step * t + x_at);
+        pairs[2 * t + 1] = (uint32_t)(out_step * t + out_at);
+    }
+}
+
+/* ---- the fast kernel ---------------------------------------------------------------------------------------------------- */
+
+constexpr int EX_THREADS = 288, EX_PRODUCERS = 256, EX_BM = 128, EX_BN = 128, EX_KC = 64;
+constexpr int EX_STAGES = 4, EX_LOOK = 3, EX_RAWS = 4;
+constexpr uint32_t EX_A_BYTES = EX_BM * 128, EX_B_BYTES = EX_BN * 128, EX_STAGE_BYTES = EX_A_BYTES + EX_B_BYTES;
+constexpr uint32_t EX_RAW_BYTES = EX_PRODUCERS * 32, EX_LUT_BYTES = 256 * 128;
+constexpr uint32_t EX_SMEM_BYTES = 1024 + EX_LUT_BYTES + EX_STAGES * EX_STAGE_BYTES + EX_RAWS * EX_RAW_BYTES + 2 * EX_BN * 4 + 256;
+
+struct ExpertFast {
+    const uint8_t* codes[12];
+    const uint16_t* scales[12];
+    uint32_t out_rows[12], held[12], d[12], pairs_at[12], pairs[12], tile0[13];   /* group i's blocks of 128 rows are [tile0[i], tile0[i+1]) */
+    uint64_t out_at[12];
+    uint32_t count, cols;
+    const uint16_t* x;
+    const uint32_t* rows;
+    const uint16_t* w;
+    uint16_t* out;
+    float* acc;
+    unsigned int* status;
+    unsigned int* over;
+};
+
+__device__ __forceinline__ void ex_cp16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void ex_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void ex_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint32_t ex_lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 ex_lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void ex_sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+
+__global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const ExpertFast a) {
+    extern __shared__ uint8_t ex_smem_raw[];
+    const uint32_t base = (smem_u32(ex_smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem = ex_smem_raw + (base - smem_u32(ex_smem_raw));
+    const uint32_t lut_at = base, stage_at = lut_at + EX_LUT_BYTES, raw_at = stage_at + EX_STAGES * EX_STAGE_BYTES;
+    uint32_t* xrow_s = reinterpret_cast<uint32_t*>(smem + EX_LUT_BYTES + EX_STAGES * EX_STAGE_BYTES + EX_RAWS * EX_RAW_BYTES);
+    uint32_t* orow_s = xrow_s + EX_BN;
+    uint64_t* full = reinterpret_cast<uint64_t*>(orow_s + EX_BN);
+    uint64_t* empty = full + EX_STAGES;
+    uint64_t* acc_full = empty + EX_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint32_t g = 0;
+    while (g + 1 < a.count && blockIdx.x >= a.tile0[g + 1]) ++g;
+    const uint32_t r0 = (blockIdx.x - a.tile0[g]) * EX_BM, j0 = blockIdx.y * EX_BN;
+    if (j0 >= a.pairs[g]) return;                                           /* the whole block: this group has fewer pairs than the widest */
+    const uint32_t nb = min((uint32_t)EX_BN, a.pairs[g] - j0), N = (nb + 15u) & ~15u;
+    const uint32_t d = a.d[g], cols = a.cols, nk = cols / EX_KC, out_rows = a.out_rows[g], held = a.held[g];
+    const uint64_t row_bytes = (uint64_t)cols * d / 8u;
+
+    if (tid == 0) {
+        for (int s = 0; s < EX_STAGES; ++s) { mbar_init(&full[s], EX_PRODUCERS / 32); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0u;
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(tmem_slot, 128);
+    else {
+        const int p = tid - 32;
+        for (int j = p; j < EX_BN; j += EX_PRODUCERS) {
+            const uint32_t* pr = a.rows + 2ull * (a.pairs_at[g] + j0 + min((uint32_t)j, nb - 1u));
+            xrow_s[j] = pr[0]; orow_s[j] = pr[1];
+        }
+        if (d != 16u)
+            for (int i = p; i < 256 * 32; i += EX_PRODUCERS) {
+                const uint32_t e = (uint32_t)i >> 5;
+                const uint32_t l8 = g_tq_levels_expert[62 + e];
+                const uint32_t v = d == 4u ? ((uint32_t)g_tq_levels_expert[14 + (e & 15u)] | ((uint32_t)g_tq_levels_expert[14 + (e >> 4)] << 16)) : (l8 | (l8 << 16));
+                reinterpret_cast<uint32_t*>(smem)[i] = v;
+            }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        /* ---------------- every MMA ---------------- */
+        if (lane == 0) {
+            const uint32_t idesc = idesc_f16(0, 0, EX_BM, (int)N);
+            for (uint32_t k = 0; k < nk; ++k) {
+                const uint32_t s = k % EX_STAGES;
+                if (!mbar_wait(&full[s], (k / EX_STAGES) & 1u, abort_flag, a.status)) break;
+                tc_fence_after();
+                const uint64_t ad = smem_desc_sw128(stage_at + s * EX_STAGE_BYTES, 16, 1024), bd = smem_desc_sw128(stage_at + s * EX_STAGE_BYTES + EX_A_BYTES, 16, 1024);
+#pragma unroll
+                for (uint32_t kk = 0; kk < 4; ++kk) tc_mma(tmem, ad + kk * 2u, bd + kk * 2u, idesc, (k | kk) != 0u ? 1u : 0u);
+                tc_commit(&empty[s]);
+            }
+            tc_commit(acc_full);
+        }
+    } else {
+        /* ---------------- producers: codes -> fp16 A tiles, the pairs' rows of x -> B tiles; then the read-out ---------------- */
+        const int p = tid - 32, row = p >> 1, half = p & 1;
+        const uint32_t grow = r0 + (uint32_t)row;
+        const bool row_ok = grow < held && grow < out_rows;
+        const uint8_t* my_codes = a.codes[g] + (row_ok ? (uint64_t)grow * row_bytes : 0ull);
+        const uint32_t lane_lut = lut_at + (uint32_t)lane * 4u;
+        const uint32_t my_raw = (uint32_t)p * 32u;
+        bool ok = true;
+
+        auto issue = [&](uint32_t k) {
+            const uint32_t s = k % EX_STAGES;
+            if (k >= (uint32_t)EX_STAGES && ok) ok = mbar_wait(&empty[s], ((k / EX_STAGES) - 1u) & 1u, abort_flag, a.status);
+            if (!ok) return;
+            const uint32_t a_at = stage_at + s * EX_STAGE_BYTES, b_at = a_at + EX_A_BYTES;
+            for (uint32_t q = (uint32_t)p; q < N * 8u; q += EX_PRODUCERS) {
+                const uint32_t j = q >> 3, c = q & 7u;
+                ex_cp16(b_at + swz128(j, c), a.x + (uint64_t)xrow_s[j] * cols + (uint64_t)k * EX_KC + c * 8u, j < nb ? 16u : 0u);
+            }
+            const uint32_t bytes = row_ok ? 16u : 0u;
+            if (d == 4u) ex_cp16(raw_at + (k % EX_RAWS) * EX_RAW_BYTES + my_raw, my_codes + (uint64_t)k * 32u + (uint32_t)half * 16u, bytes);
+            else if (d == 8u) {
+                ex_cp16(raw_at + (k % EX_RAWS) * EX_RAW_BYTES + my_raw, my_codes + (uint64_t)k * 64u + (uint32_t)half * 32u, bytes);
+                ex_cp16(raw_at + (k % EX_RAWS) * EX_RAW_BYTES + my_raw + 16u, my_codes + (uint64_t)k * 64u + (uint32_t)half * 32u + 16u, bytes);
+            } else {
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i)
+                    ex_cp16(a_at + swz128((uint32_t)row, (uint32_t)half * 4u + i), my_codes + (uint64_t)k * 128u + (uint32_t)half * 64u + i * 16u, bytes);
+            }
+        };
+
+        for (uint32_t k = 0; k < (uint32_t)EX_LOOK; ++k) { if (k < nk) issue(k); ex_cp_commit(); }
+        for (uint32_t k = 0; k < nk; ++k) {
+            if (k + EX_LOOK < nk) issue(k + EX_LOOK);
+            ex_cp_commit();                                                  /* (an empty group past the end keeps the count below uniform) */
+            ex_cp_wait<EX_LOOK>();                                           /* block k's copies of this thread have landed */
+            if (!ok) break;
+            const uint32_t s = k % EX_STAGES, a_at = stage_at + s * EX_STAGE_BYTES, raw = raw_at + (k % EX_RAWS) * EX_RAW_BYTES + my_raw;
+            if (d == 4u) {
+                const uint4 cw = ex_lds128(raw);
+                const uint32_t ws[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) {                           /* a word: four bytes, eight codes, one 16-byte chunk of the row */
+                    const uint32_t v0 = ex_lds32(lane_lut + ((ws[i] << 7) & 0x7F80u)), v1 = ex_lds32(lane_lut + ((ws[i] >> 1) & 0x7F80u));
+                    const uint32_t v2 = ex_lds32(lane_lut + ((ws[i] >> 9) & 0x7F80u)), v3 = ex_lds32(lane_lut + ((ws[i] >> 17) & 0x7F80u));
+                    ex_sts128(a_at + swz128((uint32_t)row, (uint32_t)half * 4u + i), v0, v1, v2, v3);
+                }
+            } else if (d == 8u) {
+                const uint4 c0 = ex_lds128(raw), c1 = ex_lds128(raw + 16u);
+                const uint32_t ws[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) {                           /* two words: eight bytes, eight codes, one chunk */
+                    uint32_t v[8];
+#pragma unroll
+                    for (uint32_t u = 0; u < 2; ++u) {
+                        const uint32_t wv = ws[2 * i + u];
+                        v[4 * u] = ex_lds32(lane_lut + ((wv << 7) & 0x7F80u)); v[4 * u + 1] = ex_lds32(lane_lut + ((wv >> 1) & 0x7F80u));
+                        v[4 * u + 2] = ex_lds32(lane_lut + ((wv >> 9) & 0x7F80u)); v[4 * u + 3] = ex_lds32(lane_lut + ((wv >> 17) & 0x7F80u));
+                    }
+                    ex_sts128(a_at + swz128((uint32_t)row, (uint32_t)half * 4u + i), __byte_perm(v[0], v[1], 0x5410), __byte_perm(v[2], v[3], 0x5410),
+                              __byte_perm(v[4], v[5], 0x5410), __byte_perm(v[6], v[7], 0x5410));
+                }
+            }
+            fence_proxy_async_smem();                                        /* this thread's stores and landed copies, for the MMA's reads */
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[s]);
+        }
+        ex_cp_wait<0>();
+
+        /* the read-out: a thread a matrix row (its lane of tensor memory), two warps a quadrant splitting the pairs 32 at a time */
+        if (ok) ok = mbar_wait(acc_full, 0u, abort_flag, a.status);
+        tc_fence_after();
+        if (ok) {
+            const uint32_t quad = (uint32_t)warp & 3u, grp = (uint32_t)(warp - 1) >> 2;
+            const uint32_t orow = r0 + quad * 32u + (uint32_t)lane;
+            const bool live = orow < held && orow < out_rows;
+            const float scale = d == 16u || !live ? 1.0f : H::to_float(a.scales[g][orow]);
+            bool hit = false;
+            for (uint32_t cb = grp; cb * 32u < N; cb += 2u) {
+                uint32_t v[32];
+                tmem_ld32(tmem + ((quad * 32u) << 16) + cb * 32u, v);
+                tmem_wait_ld();
+                if (!live) continue;
+#pragma unroll
+                for (uint32_t c = 0; c < 32; ++c) {
+                    const uint32_t j = cb * 32u + c;
+                    if (j >= nb) break;
+                    const float val = __uint_as_float(v[c]) * scale;
+                    const uint64_t at = (uint64_t)orow_s[j] * out_rows + orow;
+                    if (a.out) a.out[a.out_at[g] + at] = H::from_float(val, hit);
+                    else a.acc[at] += val * H::to_float(a.w[xrow_s[j]]);
+                }
+            }
+            if (hit && a.over) atomicOr(a.over, SV_FAULT_OVERFLOW);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 128);
+}
+
+/* ---------------------------------------------------------------------------------------------------------------------------- */
+
+static inline unsigned ex_grid(uint64_t items, unsigned cap = 4096u) { return (unsigned)(items < 1 ? 1 : (items > cap ? cap : items)); }
+
+bool expert_width_ok(uint64_t d) { return ex_width_known(d); }
+
+cudaError_t expert_rows_launch(uint16_t* out, float* acc, const uint8_t* weights, uint64_t w_room, const uint8_t* luts, uint64_t l_room, const uint16_t* x,
+                               const uint32_t* pairs, const uint16_t* w, uint64_t count, uint64_t d, uint64_t out_rows, uint64_t cols, unsigned int* over,
+                               cudaStream_t st) {
+    const uint64_t row_bytes = ex_row_bytes(d, cols);
+    uint64_t held = row_bytes == 0 ? 0 : w_room / row_bytes;
+    if (d != 16 && l_room / 2 < held) held = l_room / 2;
+    if (held == 0 || count == 0 || out_rows == 0) return cudaSuccess;
+    expert_rows_kernel<<<ex_grid(out_rows < held ? out_rows : held), 128, 0, st>>>(out, acc, weights, held, luts, x, pairs, w, count, d, out_rows, cols, over);
+    note_launch(1);
+    return cudaGetLastError();
+}
+cudaError_t expert_rows_finish_launch(uint16_t* out, float* acc, const uint16_t* residual, uint64_t n, unsigned int* over, cudaStream_t st) {
+    expert_rows_finish_kernel<<<ex_grid((n + 255) / 256), 256, 0, st>>>(out, acc, residual, n, over);
+    note_launch(1);
+    return cudaGetLastError();
+}
+cudaError_t expert_rows_reduce_launch(uint16_t* out, float* acc, const uint16_t* residual, uint64_t n, uint64_t k, uint64_t cols, unsigned int* over,
+                                      cudaStream_t st) {
+    expert_rows_reduce_kernel<<<ex_grid((n * cols + 255) / 256), 256, 0, st>>>(out, acc, residual, n, k, cols, over);
+    note_launch(1);
+    return cudaGetLastError();
+}
+cudaError_t expert_pairs_rows_launch(uint32_t* pairs, uint64_t n, uint64_t x_step, uint64_t x_at, uint64_t out_step, uint64_t out_at, cudaStream_t st) {
+    expert_pairs_rows_kernel<<<ex_grid((n + 255) / 256, 64u), 256, 0, st>>>(pairs, n, x_step, x_at, out_step, out_at);
+    note_launch(1);
+    return cudaGetLastError();
+}
+
+/* Whether the fast kernel takes these groups (an sv_expert_groups by address) over rows of `cols` columns. */
+bool expert_fast_fits(const void* groups, const void* x, uint64_t cols) {
+    ExpertGroups g;
+    memcpy(&g, groups, sizeof g);
+    if (g.count == 0 || g.count > 12 || cols == 0 || cols % EX_KC != 0 || cols > (1ull << 20) || ((uintptr_t)x & 15u)) return false;
+    uint64_t tiles = 0;
+    for (uint64_t i = 0; i < g.count; ++i) {
+        if (g.d[i] != 4 && g.d[i] != 8 && g.d[i] != 16) return false;
+        if (g.codes[i] % 16 != 0 || g.luts[i] % 2 != 0 || g.out_rows[i] == 0 || g.out_rows[i] > 0x0fffffffu || g.pairs[i] == 0 || g.pairs[i] > 0x0fffffffu) return false;
+        tiles += (g.out_rows[i] + EX_BM - 1) / EX_BM;
+    }
+    return tiles <= 0x7fffffffu;
+}
+
+/* `held`: for a single group, the rows its rooms hold (null: every row).  `out` or `acc` (with `w`), as the door has them. */
+cudaError_t expert_fast_launch(uint16_t* out, float* acc, const void* groups, const uint64_t* held, const uint16_t* x, const uint32_t* rows,
+                               const uint16_t* w, uint64_t cols, unsigned int* over, cudaStream_t st) {
+    ExpertGroups g;
+    memcpy(&g, groups, sizeof g);
+    ExpertFast a;
+    memset(&a, 0, sizeof a);
+    uint32_t tiles = 0, widest = 0;
+    for (uint64_t i = 0; i < g.count; ++i) {
+        a.codes[i] = (const uint8_t*)(uintptr_t)g.codes[i]; a.scales[i] = (const uint16_t*)(uintptr_t)g.luts[i];
+        a.out_rows[i] = (uint32_t)g.out_rows[i]; a.d[i] = (uint32_t)g.d[i]; a.pairs_at[i] = (uint32_t)g.pairs_at[i]; a.pairs[i] = (uint32_t)g.pairs[i];
+        a.held[i] = held && *held < g.out_rows[i] ? (uint32_t)*held : (uint32_t)g.out_rows[i];
+        a.out_at[i] = g.out_at[i];
+        a.tile0[i] = tiles;
+        tiles += (uint32_t)((g.out_rows[i] + EX_BM - 1) / EX_BM);
+        if (a.pairs[i] > widest) widest = a.pairs[i];
+    }
+    a.tile0[g.count] = tiles;
+    a.count = (uint32_t)g.count; a.cols = (uint32_t)cols; a.x = x; a.rows = rows; a.w = w; a.out = out; a.acc = acc; a.over = over;
+    a.status = device_status_word();
+    static std::atomic<bool> ready[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!ready[dev].load(std::memory_order_acquire)) {
+        e = cudaFuncSetAttribute(expert_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)EX_SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        ready[dev].store(true, std::memory_order_release);
+    }
+    const dim3 grid(tiles, (widest + EX_BN - 1) / EX_BN);
+    expert_fast_kernel<<<grid, EX_THREADS, EX_SMEM_BYTES, st>>>(a);
+    note_launch(1);
+    return cudaGetLastError();
+}
+
+}  // namespace sv

@@ -655,6 +655,91 @@ static void d_turboquant_gemv_groups(sv_h16* out, sv_tq_groups g, const sv_h16* 
     d_turboquant_gemv_groups_n(out, g, x, cols, 1, 0, over);
 }
 
+/* ---- the expert-major GEMM doors a prompt's projections go through (expert.cu) ---- */
+static bool expert_fast_off() {
+    static const bool off = [] { const char* e = getenv("SILVANN_B200_EXPERT_AS_WORDED"); return e && e[0] == '1'; }();
+    return off;
+}
+static void expert_rows_any(const char* door, sv_h16* out, float* acc, const sv_u8* weights, sv_u64 w_room, const sv_u8* luts, sv_u64 l_room, const sv_h16* x,
+                            const sv_u32* rows, const sv_h16* w, sv_u64 count, sv_u64 d, sv_u64 out_rows, sv_u64 cols, sv_fault* over) {
+    flush();
+    if (!sv::expert_width_ok(d)) { launch_refused(door, cudaSuccess); return; }
+    if (count == 0 || out_rows == 0 || cols == 0) return;
+    sv_expert_groups g;
+    memset(&g, 0, sizeof g);
+    g.codes[0] = (sv_u64)(uintptr_t)weights; g.luts[0] = (sv_u64)(uintptr_t)luts; g.out_rows[0] = out_rows; g.d[0] = d; g.pairs[0] = count; g.count = 1;
+    if (!expert_fast_off() && sv::expert_fast_fits(&g, x, cols)) {
+        const sv_u64 row_bytes = cols * d / 8;
+        sv_u64 held = w_room / row_bytes;                                   /* a row its rooms do not hold is computed and not written */
+        if (d != 16 && l_room / 2 < held) held = l_room / 2;
+        if (held == 0) return;
+        const cudaError_t e = sv::expert_fast_launch(out, acc, &g, &held, x, rows, w, cols, over, 0);
+        if (e == cudaSuccess) bump(SILVANN_B200_COUNTER_EXPERT_FAST);
+        check(door, e);
+        return;
+    }
+    check(door, sv::expert_rows_launch(out, acc, weights, w_room, luts, l_room, x, rows, w, count, d, out_rows, cols, over, 0));
+}
+static void d_expert_rows(sv_h16* out, const sv_u8* weights, sv_u64 w_room, const sv_u8* luts, sv_u64 l_room, const sv_h16* x, const sv_u32* rows, sv_u64 count,
+                          sv_u64 d, sv_u64 out_rows, sv_u64 cols, sv_fault* over) {
+    expert_rows_any("expert_rows", out, nullptr, weights, w_room, luts, l_room, x, rows, nullptr, count, d, out_rows, cols, over);
+}
+static void d_expert_rows_sum(float* acc, const sv_u8* weights, sv_u64 w_room, const sv_u8* luts, sv_u64 l_room, const sv_h16* x, const sv_u32* rows,
+                              const sv_h16* w, sv_u64 count, sv_u64 d, sv_u64 out_rows, sv_u64 cols) {
+    expert_rows_any("expert_rows_sum", nullptr, acc, weights, w_room, luts, l_room, x, rows, w, count, d, out_rows, cols, nullptr);
+}
+static void d_expert_groups(sv_h16* out, sv_expert_groups g, const sv_h16* x, const sv_u32* rows, sv_u64 cols, sv_fault* over) {
+    flush();
+    if (g.count == 0 || cols == 0) return;
+    if (g.count > 12) { launch_refused("expert_groups", cudaSuccess); return; }
+    for (sv_u64 i = 0; i < g.count; ++i)
+        if (!sv::expert_width_ok(g.d[i])) { launch_refused("expert_groups", cudaSuccess); return; }
+    sv_expert_groups live = g;                                              /* groups with rows and pairs */
+    live.count = 0;
+    for (sv_u64 i = 0; i < g.count; ++i)
+        if (g.out_rows[i] != 0 && g.pairs[i] != 0) {
+            const sv_u64 k = live.count++;
+            live.codes[k] = g.codes[i]; live.luts[k] = g.luts[i]; live.out_rows[k] = g.out_rows[i]; live.d[k] = g.d[i]; live.out_at[k] = g.out_at[i];
+            live.pairs_at[k] = g.pairs_at[i]; live.pairs[k] = g.pairs[i];
+        }
+    if (live.count == 0) return;
+    if (!expert_fast_off() && sv::expert_fast_fits(&live, x, cols)) {
+        const cudaError_t e = sv::expert_fast_launch(out, nullptr, &live, nullptr, x, rows, nullptr, cols, over, 0);
+        if (e == cudaSuccess) bump(SILVANN_B200_COUNTER_EXPERT_FAST);
+        check("expert_groups", e);
+        return;
+    }
+    for (sv_u64 i = 0; i < live.count; ++i) {                               /* as worded: the one-matrix door a group at a time */
+        const sv_u64 row_bytes = ((cols + 16 / live.d[i] - 1) / (16 / live.d[i])) * 2;
+        check("expert_groups", sv::expert_rows_launch(out + live.out_at[i], nullptr, (const sv_u8*)(uintptr_t)live.codes[i], live.out_rows[i] * row_bytes,
+                                                      (const sv_u8*)(uintptr_t)live.luts[i], live.out_rows[i] * 2, x, rows + 2 * live.pairs_at[i], nullptr,
+                                                      live.pairs[i], live.d[i], live.out_rows[i], cols, over, 0));
+    }
+}
+static void d_expert_rows_finish(sv_h16* out, float* acc, const sv_h16* residual, sv_u64 n, sv_fault* over) {
+    flush();
+    if (n) check("expert_rows_finish", sv::expert_rows_finish_launch(out, acc, residual, n, over, 0));
+}
+static void d_expert_rows_reduce(sv_h16* out, float* acc, const sv_h16* residual, sv_u64 n, sv_u64 k, sv_u64 cols, sv_fault* over) {
+    flush();
+    if (n * cols) check("expert_rows_reduce", sv::expert_rows_reduce_launch(out, acc, residual, n, k, cols, over, 0));
+}
+static void d_expert_pairs_rows(sv_u32* pairs, sv_u64 n, sv_u64 x_step, sv_u64 x_at, sv_u64 out_step, sv_u64 out_at) {
+    flush();
+    if (n) check("expert_pairs_rows", sv::expert_pairs_rows_launch(pairs, n, x_step, x_at, out_step, out_at, 0));
+}
+/* A 16-bit matrix times one vector, or n of them, is the coded door at width 16: the codes are the halves, the scale is 1. */
+static void d_expert_multiply_fp16_rows(sv_h16* out, const sv_h16* W, const sv_h16* x, sv_u64 rows, sv_u64 cols, sv_u64 n, sv_fault* over) {
+    if (rows == 0 || cols == 0 || n == 0) { flush(); return; }
+    sv_tq_groups g;
+    memset(&g, 0, sizeof g);
+    g.codes[0] = (sv_u64)(uintptr_t)W; g.luts[0] = 0; g.rows[0] = rows; g.d[0] = 16; g.out_at[0] = 0; g.count = 1;
+    d_turboquant_gemv_groups_n(out, g, x, cols, n, 0, over);
+}
+static void d_expert_multiply_fp16(sv_h16* out, const sv_h16* W, const sv_h16* x, sv_u64 rows, sv_u64 cols, sv_fault* over) {
+    d_expert_multiply_fp16_rows(out, W, x, rows, cols, 1, over);
+}
+
 /* ---- the GLM mixer's doors (glm_doors.cu): KDA, the latent's absorb and expand, the indexer ---- */
 static void d_kda_steps(float* S, const sv_h16* conved, const sv_h16* f, const sv_h16* b, const sv_h16* dt, const sv_h16* a_log, const sv_h16* gate,
                         const sv_h16* w, sv_h16* out, sv_u64 heads, sv_u64 head_dim, float lower, float eps, sv_u64 rows, sv_fault* over) {
@@ -824,6 +909,14 @@ static void install_doors() {
     g_nn.hadamard_rotate = d_hadamard_rotate;
     g_nn.rmsnorm_rotate = d_rmsnorm_rotate;
     g_nn.turboquant_gemv = d_turboquant_gemv;
+    g_nn.expert_rows = d_expert_rows;
+    g_nn.expert_rows_sum = d_expert_rows_sum;
+    g_nn.expert_groups = d_expert_groups;
+    g_nn.expert_rows_finish = d_expert_rows_finish;
+    g_nn.expert_rows_reduce = d_expert_rows_reduce;
+    g_nn.expert_pairs_rows = d_expert_pairs_rows;
+    g_nn.expert_multiply_fp16 = d_expert_multiply_fp16;
+    g_nn.expert_multiply_fp16_rows = d_expert_multiply_fp16_rows;
     g_nn.turboquant_gemv_groups = d_turboquant_gemv_groups;
     g_nn.turboquant_gemv_groups_n = d_turboquant_gemv_groups_n;
     g_nn.turboquant_decode = d_turboquant_decode;

@@ -146,6 +146,18 @@ cudaError_t tq_weights_launch(float* p, float* res, const uint16_t* q, const uin
 cudaError_t hadamard_rotate_launch(uint16_t* out, const uint16_t* in, const uint16_t* sign, uint64_t n, unsigned int* over, cudaStream_t st);
 cudaError_t tq_gemv_groups_launch(uint16_t* out, const void* groups /* sv_tq_groups */, uint64_t w_room, uint64_t l_room, const uint16_t* x,
                                   uint64_t cols, unsigned int* over, cudaStream_t st);
+/* ---- the expert-major GEMM: a coded matrix over several rows of x named by pairs (expert.cu) ---------------------- */
+bool expert_width_ok(uint64_t d);
+cudaError_t expert_rows_launch(uint16_t* out, float* acc, const uint8_t* weights, uint64_t w_room, const uint8_t* luts, uint64_t l_room, const uint16_t* x,
+                               const uint32_t* pairs, const uint16_t* w, uint64_t count, uint64_t d, uint64_t out_rows, uint64_t cols, unsigned int* over,
+                               cudaStream_t st);
+cudaError_t expert_rows_finish_launch(uint16_t* out, float* acc, const uint16_t* residual, uint64_t n, unsigned int* over, cudaStream_t st);
+cudaError_t expert_rows_reduce_launch(uint16_t* out, float* acc, const uint16_t* residual, uint64_t n, uint64_t k, uint64_t cols, unsigned int* over,
+                                      cudaStream_t st);
+cudaError_t expert_pairs_rows_launch(uint32_t* pairs, uint64_t n, uint64_t x_step, uint64_t x_at, uint64_t out_step, uint64_t out_at, cudaStream_t st);
+bool expert_fast_fits(const void* groups /* sv_expert_groups */, const void* x, uint64_t cols);
+cudaError_t expert_fast_launch(uint16_t* out, float* acc, const void* groups, const uint64_t* held /*one group: rows its rooms hold; null: all*/, const uint16_t* x,
+                               const uint32_t* rows, const uint16_t* w, uint64_t cols, unsigned int* over, cudaStream_t st);
 /* the pair weights_tq + residual_mix_tq as one kernel, codes expanded in flight (tq_decode.cu) */
 bool tq_attend_fits(const void* q, const void* kcodes, const void* kscales, const void* vcodes, const void* vscales, uint64_t qh, uint64_t kvh,
                     uint64_t dh, uint64_t length, uint64_t d);

@@ -225,6 +225,58 @@ def _tiered_mixer(s, reference):
     return h1, state
 
 
+ROWS_MIX = dict(H=512, QH=4, KVH=2, HD=128, ROT=64, D_Q=4, D_K=4, D_V=8, D_O=8, THETA=10000, CHUNKS=(64, 40, 1))
+
+
+def _rows_mixer(s, reference):
+    """`(ai_qwen_3__attention_rows x planes first h1 rows)` (engine/src/packages/ai_qwen_3/cpu/opcodes/prefill__abi.cuh:135-237): a
+    prompt through the attention mixer a chunk of rows at a time — norm and rotation of every row, q and k through
+    `expert_groups`, v and o through `expert_rows`, head norms and RoPE over the rows, the keys and values written into the
+    cache, the three causal doors, the gate, the residual add.  Answers h1 of every row and the caches at the end."""
+    m = ROWS_MIX
+    H, qh, kvh, hd, rot = m["H"], m["QH"], m["KVH"], m["HD"], m["ROT"]
+    qw, kvw = qh * hd, kvh * hd
+    total, most = sum(m["CHUNKS"]), max(m["CHUNKS"])
+    rng = np.random.default_rng(61)
+    mats = [_coded(reference, rng, 2 * qw, H, m["D_Q"]), _coded(reference, rng, kvw, H, m["D_K"]),
+            _coded(reference, rng, kvw, H, m["D_V"]), _coded(reference, rng, H, qw, m["D_O"])]
+    norms = [to_bits((1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32), FP16) for n in (H, hd, hd)]
+    signs = to_bits(np.where(rng.random(512) < 0.5, -1.0, 1.0).astype(np.float32), FP16)
+    xs = to_bits(rng.standard_normal((total, H)).astype(np.float32), FP16)
+
+    def filled(a):
+        return s.buffer(a.nbytes, a.tobytes())
+
+    def room(nbytes):
+        return s.buffer(nbytes, bytes(nbytes))
+
+    planes = [filled(norms[0]),
+              filled(mats[0][0]), filled(mats[0][1]), filled(mats[1][0]), filled(mats[1][1]),
+              filled(mats[2][0]), filled(mats[2][1]), filled(mats[3][0]), filled(mats[3][1]),
+              filled(norms[1]), filled(norms[2]),
+              room(2 * total * kvw), room(2 * total * kvw),                                    # the caches
+              room(4 * most * rot),                                                            # the rows' angles
+              room(4 * most * qh * total),                                                     # the rows' scores
+              filled(signs),
+              room(2 * most * (3 * H + 7 * qw + kvw) + 16 * 256 + 4096)]                        # pairs, then the rows' scratch
+    numbers = [H, qh, kvh, hd, rot, m["D_Q"], m["D_K"], m["D_V"], m["D_O"], m["THETA"], 0]
+    table = s.table(planes + numbers)
+    h1 = np.zeros((total, H), np.uint16)
+    seconds, first = [], 0
+    for T in m["CHUNKS"]:
+        xb, hb = filled(xs[first:first + T]), room(2 * T * H)
+        t0 = time.perf_counter()
+        kind, _ = s.run_cells("ai_qwen_3__attention_rows", [s.buf(xb.ref), s.buf(table), s.integer(first), s.buf(hb.ref), s.integer(T)])
+        assert kind == s.OBJ, f"rows {first}..{first + T}: the verb answers h1"
+        h1[first:first + T] = _u16(hb.read(), (T, H))
+        seconds.append(time.perf_counter() - t0)
+        first += T
+    state = {"x": xs, "k": _u16(planes[11].read(), (total, kvw)), "v": _u16(planes[12].read(), (total, kvw)), "seconds": seconds}
+    s.release(table)
+    s.release_buffers()
+    return h1, state
+
+
 DN_MIX = dict(H=512, KH=2, VH=4, HD=128, D_QKV=4, D_Z=8, D_A=8, D_B=8, D_OUT=4, STEPS=12)
 
 
@@ -309,7 +361,7 @@ def mixer_on_reference_family(cuda, reference):
         pytest.fail("oracle/_ref holds no reference engine and family: build them where the reference tree is mounted")
     s = engine_driver.Session(oracle.build.REF, "x86_avx2")
     try:
-        return _tiered_mixer(s, reference), _deltanet_mixer(s, reference)
+        return _tiered_mixer(s, reference), _deltanet_mixer(s, reference), _rows_mixer(s, reference)
     finally:
         s.close()
 
@@ -391,3 +443,27 @@ def test_engine_runs_the_deltanet_mixer_on_this_family(gpu_session, mixer_on_ref
     assert err.max() <= 2e-3 * max(1.0, float(np.abs(oracle.from_bits(want, FP16)).max())), f"h1 differs by {err.max()}"
     np.testing.assert_allclose(end["state"], want_end["state"], rtol=0, atol=1e-3 * np.abs(want_end["state"]).max())
     assert np.abs(oracle.from_bits(end["window"], FP16) - oracle.from_bits(want_end["window"], FP16)).max() <= 2e-3
+
+
+@pytest.mark.gpu
+def test_engine_runs_a_prompt_through_the_rows_mixer_on_this_family(gpu_session, mixer_on_reference_family, reference):
+    """The reference's prompt path of the attention mixer, three chunks of rows (the second and third over a cache the earlier
+    ones filled), on this family against the same program on the reference's CPU family: the projections are the expert-major
+    GEMM doors and the attention is the three causal doors, which this family answers with one tcgen05 kernel each."""
+    from silvann_b200 import ext
+    want, want_state = mixer_on_reference_family[2]
+    before = ext.counters()
+    got, state = _rows_mixer(gpu_session, reference)
+    after = ext.counters()
+    chunks = len(ROWS_MIX["CHUNKS"])
+    print(f"rows mixer through the engine: {[round(1e6 * t) for t in state['seconds']]} us a chunk of {list(ROWS_MIX['CHUNKS'])} rows on this family "
+          f"({(after['launches'] - before['launches']) / chunks:.1f} launches a chunk), {[round(1e6 * t) for t in want_state['seconds']]} us on the reference's CPU family")
+    assert after["refused"] == before["refused"] and ext.device_status() == 0
+    assert after["expert_fast"] - before["expert_fast"] == 3 * chunks, "q and k in one launch, v, o: the projections ran on the tcgen05 kernel"
+    assert after["fused_prefill"] - before["fused_prefill"] == chunks, "the three causal doors ran as one kernel a chunk"
+    err = np.abs(oracle.from_bits(got, FP16) - oracle.from_bits(want, FP16))
+    print("rows mixer: max |h1 - reference| a chunk:", [float(np.round(err[a:b].max(), 5)) for a, b in zip(np.cumsum((0,) + ROWS_MIX["CHUNKS"][:-1]), np.cumsum(ROWS_MIX["CHUNKS"]))])
+    assert err.max() <= 2e-3 * max(1.0, float(np.abs(oracle.from_bits(want, FP16)).max())), f"h1 differs by {err.max()}"
+    for name in ("k", "v"):
+        d = np.abs(oracle.from_bits(state[name], FP16) - oracle.from_bits(want_state[name], FP16))
+        assert d.max() <= 4e-3, f"the {name} cache differs by {d.max()}"
