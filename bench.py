@@ -468,6 +468,17 @@ def gpu_baseline(torch, wl: PagedWorkload, pk, steps):
         nbytes = Lm * 512 * 2 + 2 * 64 * 512 * 2
         out[f"mla_decode_64heads_{Lm}"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms}
         del lat, pm
+    # a prompt chunk's projection through the reference's expert_rows (its own tiled kernel): 256 rows through 8,192 x 5,120 at 4 bits
+    T, er, ec = 256, 8192, 5120
+    ecodes = torch.randint(0, 256, (er, ec // 2), generator=gen, device="cuda", dtype=torch.uint8)
+    escales = ((torch.rand((er,), generator=gen, device="cuda") * 0.5 + 0.75) * (3.0 / ec ** 0.5)).to(torch.float16)
+    ex = torch.randn((T, ec), generator=gen, device="cuda", dtype=torch.float16)
+    epairs = torch.arange(T, device="cuda", dtype=torch.int32).repeat_interleave(2).contiguous()
+    eout = torch.zeros((T, er), device="cuda", dtype=torch.float16)
+    ms = time_loop(torch, lambda: R.nn.expert_rows(eout.data_ptr(), ecodes.data_ptr(), ecodes.numel(), escales.data_ptr(), escales.numel() * 2, ex.data_ptr(),
+                                                   epairs.data_ptr(), T, 4, er, ec, over.data_ptr()), 5, 2)
+    out["prompt_projection_256rows_q4"] = {"value": 2.0 * T * er * ec / ms / 1e9, "unit": "TFLOP/s", "ms_per_call": ms}
+    del ecodes, ex, eout
     torch.cuda.empty_cache()
     # Kimi Delta Attention, one decode step of 64 heads of 128, through the reference's kda_step
     import ctypes as C
@@ -694,6 +705,31 @@ def other_workloads(torch, fam, pk, steps, warmup):
         del lat
     torch.cuda.empty_cache()
 
+    # a prompt chunk's projections through the expert-major GEMM door: 256 rows of 5,120 through a q projection of 8,192 rows at 4 bits,
+    # and 256 rows of 4,096 through an o projection of 5,120 rows at 8 bits (4 coded matrices cycled: the weights come from HBM)
+    for tag, er, ec, width in (("prompt_projection_256rows_q4", 8192, 5120, 4), ("prompt_projection_256rows_o8", 5120, 4096, 8)):
+        T, copies = 256, 4
+        ecodes = torch.randint(0, 256, (copies, er, ec * width // 8), generator=gen, device="cuda", dtype=torch.uint8)
+        escales = ((torch.rand((er,), generator=gen, device="cuda") * 0.5 + 0.75) * (3.0 / ec ** 0.5)).to(torch.float16)
+        ex = torch.randn((T, ec), generator=gen, device="cuda", dtype=torch.float16)
+        epairs = torch.arange(T, device="cuda", dtype=torch.int32).repeat_interleave(2).contiguous()
+        eout = torch.zeros((T, er), device="cuda", dtype=torch.float16)
+        estate = {"i": 0}
+
+        def project():
+            i = estate["i"] = (estate["i"] + 1) % copies
+            fam.nn.expert_rows(eout.data_ptr(), ecodes[i].data_ptr(), ecodes[i].numel(), escales.data_ptr(), escales.numel() * 2, ex.data_ptr(), epairs.data_ptr(),
+                               T, width, er, ec, None)
+        before = ext.counters()["expert_fast"]
+        ms = time_loop(torch, project, max(steps * 3, 40), 5)
+        assert ext.counters()["expert_fast"] > before, "the projection did not take the tcgen05 kernel"
+        flops = 2.0 * T * er * ec
+        out[tag] = {"value": flops / ms / 1e9, "unit": "TFLOP/s", "ms_per_call": ms, "frac_bf16_burst": flops / ms / 1e9 / pk["bf16_tflops"], "algorithmic_flops": flops,
+                    "weights_gbs": er * ec * width / 8 / ms / 1e6,
+                    "note": f"expert_rows door: {T} rows x {ec} through {er} coded rows at {width} bits ({er * ec * width / 8 / 1e6:.1f} MB of codes a call), one tcgen05 launch"}
+        del ecodes, ex, eout
+    torch.cuda.empty_cache()
+
     # the sparse attention's indexer at decode: 32 index heads of 128 score 8,192 pooled keys, the top 512 pools chosen
     ih, idim, pools, topk, kpool = 32, 128, 8192, 512, 4
     iq = torch.randn((ih * idim,), generator=gen, device="cuda", dtype=torch.float16)
@@ -792,11 +828,13 @@ ROOFLINES = {
     "kda_decode_64heads": ("hbm", "sv::kda_steps_kernel<128, false>", 4.31e6, "capture of this workload (the 8.4 MB state stays in L2 between steps)"),
     "mla_absorb_64heads": ("hbm", "sv::absorb_kernel", None, None),
     "mla_expand_64heads": ("hbm", "sv::expand_kernel", None, None),
-    "mla_decode_64heads_2048": ("hbm", "sv::mla_decode_kernel<64, fp16> + sv::mla_fold_kernel (2 MB: latency-bound)", None, None),
-    "mla_decode_64heads_65536": ("hbm", "sv::mla_decode_kernel<64, fp16> + sv::mla_fold_kernel", None, None),
+    "mla_decode_64heads_2048": ("hbm", "sv::mla_decode_kernel<64, fp16> + sv::mla_fold_kernel (2 MB: latency-bound)", 0.95, "ratio of the capture of this workload (2.23 MB for 2.36 MB)"),
+    "mla_decode_64heads_65536": ("hbm", "sv::mla_decode_kernel<64, fp16> + sv::mla_fold_kernel", 0.96, "ratio of the capture of this workload (72.3 MB for 75.5 MB: a tail of the latent is still in L2)"),
+    "prompt_projection_256rows_q4": ("tensor", "sv::expert_fast_kernel", None, None),
+    "prompt_projection_256rows_o8": ("tensor", "sv::expert_fast_kernel", None, None),
     "config5_deltanet_decode_1seq": ("hbm", "sv::deltanet_steps_kernel<128, bf16, false, true> (one cluster a head)", None, None),
     "config5_deltanet_decode_1seq_graph": ("hbm", "sv::deltanet_steps_kernel<128, bf16, false, true> (one cluster a head)", None, None),
-    "config5_deltanet_decode_64seq": ("hbm", "sv::deltanet_steps_kernel<128, bf16, false, false> + deltanet_norm_kernel", 213.3e6, "capture of this workload (part of the written state is still in L2 when the kernel ends)"),
+    "config5_deltanet_decode_64seq": ("hbm", "sv::deltanet_step_head_kernel<128, bf16> (one launch a step of the batch)", 215.8e6, "capture of this workload (part of the written state is still in L2 when the kernel ends)"),
     "config5_deltanet_prefill_8192": ("hbm", "sv::deltanet_prep_kernel + deltanet_chunk_kernel + deltanet_norm_kernel", 1.921, "ratio of the capture of the three kernels on 2,048 positions (163.3 MB for 85.0 MB), scaled by bytes"),
     "config2_causal_prefill": ("tensor", "sv::prefill_kernel<256, bf16>", 41.9e6 * 1.001, "the capture on 2,048 rows read its inputs once (21.02 MB for 21.0 MB); scaled by input bytes"),
 }
@@ -1277,6 +1315,23 @@ def run_case(args):
             x.deposit(1, theirs, 8 * 130 * 4)
             x.merge_finish(om, None, mine, 8, 128, ext.BF16, wait_ms=200)
         work, unit = 2 * 8 * 130 * 4, "bytes"
+    elif name in ("expert_q4", "expert_o8", "expert_q4_64rows"):
+        # a prompt chunk's projection through the expert_rows door: 256 (or 64) rows through 8,192 x 5,120 at 4 bits / 5,120 x 4,096 at 8
+        er, ec, width = (5120, 4096, 8) if name == "expert_o8" else (8192, 5120, 4)
+        ec = int(os.environ.get("EXPERT_COLS", ec))
+        T, copies = (64 if name.endswith("64rows") else 256), 4
+        ecodes = torch.randint(0, 256, (copies, er, ec * width // 8), generator=gen, device="cuda", dtype=torch.uint8)
+        escales = ((torch.rand((er,), generator=gen, device="cuda") * 0.5 + 0.75) * (3.0 / ec ** 0.5)).to(torch.float16)
+        ex = torch.randn((T, ec), generator=gen, device="cuda", dtype=torch.float16)
+        epairs = torch.arange(T, device="cuda", dtype=torch.int32).repeat_interleave(2).contiguous()
+        eout = torch.zeros((T, er), device="cuda", dtype=torch.float16)
+        estate = {"i": 0}
+
+        def fn():
+            i = estate["i"] = (estate["i"] + 1) % copies
+            fam.nn.expert_rows(eout.data_ptr(), ecodes[i].data_ptr(), ecodes[i].numel(), escales.data_ptr(), escales.numel() * 2, ex.data_ptr(), epairs.data_ptr(),
+                               T, width, er, ec, None)
+        work, unit = 2.0 * T * er * ec, "flop"
     elif name == "prefill_small":
         qh, kvh, d, T = 16, 2, 256, 2048
         q = torch.randn((T, qh, d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.5
@@ -1300,7 +1355,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the secondary configurations (faster; used under profilers)")
     ap.add_argument("--only", default=None, choices=["long_context"], help="run configuration 4 alone (any N) and print its object")
-    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, decode_cfg1, decode_cfg1_graph, tq8_small, tq4_small, deltanet_64, deltanet_prefill, prefill_small, mla_2048, mla_65536, exchange_small)")
+    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, decode_cfg1, decode_cfg1_graph, tq8_small, tq4_small, deltanet_64, deltanet_prefill, prefill_small, mla_2048, mla_65536, exchange_small, expert_q4, expert_o8, expert_q4_64rows)")
     args = ap.parse_args()
     if args.case:
         run_case(args)

@@ -13,7 +13,7 @@
  * Two kernels.  `expert_rows_kernel` is the door as worded — any width, any shape, a block a matrix row, eight pairs a pass.
  * `expert_fast_kernel` is the one a prompt runs on: a block owns 128 matrix rows and up to 128 pairs and walks the columns 64
  * at a time;
- *   · eight producer warps expand the codes into fp16 in shared memory, K-major with the 128-byte swizzle, as the A operand
+ *   · sixteen producer warps expand the codes into fp16 in shared memory, K-major with the 128-byte swizzle, as the A operand
  *     (a code byte is ONE shared-memory lookup in a table of 256 entries of 128 bytes — a lane reads its own bank, so no
  *     lookup ever conflicts; at 4 bits an entry is the byte's two levels, at 8 bits the level twice), and gather the pairs'
  *     rows of x as the B operand — both through cp.async three column blocks ahead, the raw codes through a small staging ring;
@@ -128,11 +128,12 @@ __global__ void __launch_bounds__(256) expert_pairs_rows_kernel(uint32_t* pairs,
 
 /* ---- the fast kernel ---------------------------------------------------------------------------------------------------- */
 
-constexpr int EX_THREADS = 288, EX_PRODUCERS = 256, EX_BM = 128, EX_BN = 128, EX_KC = 64;
-constexpr int EX_STAGES = 4, EX_LOOK = 3, EX_RAWS = 4;
-constexpr uint32_t EX_A_BYTES = EX_BM * 128, EX_B_BYTES = EX_BN * 128, EX_STAGE_BYTES = EX_A_BYTES + EX_B_BYTES;
-constexpr uint32_t EX_RAW_BYTES = EX_PRODUCERS * 32, EX_LUT_BYTES = 256 * 128;
-constexpr uint32_t EX_SMEM_BYTES = 1024 + EX_LUT_BYTES + EX_STAGES * EX_STAGE_BYTES + EX_RAWS * EX_RAW_BYTES + 2 * EX_BN * 4 + 256;
+constexpr int EX_THREADS = 544, EX_PRODUCERS = 512, EX_BM = 128, EX_BN = 128, EX_KC = 64;
+constexpr int EX_STAGES = 3, EX_LOOK = 1;                           /* stages of two column blocks; stages the copies of x run ahead */
+constexpr uint32_t EX_ATOM = 16384;                                   /* a tile of 128 rows x 64 columns of halves, 128-byte rows, swizzled */
+constexpr uint32_t EX_A_BYTES = 2 * EX_ATOM, EX_B_BYTES = 2 * EX_ATOM, EX_STAGE_BYTES = EX_A_BYTES + EX_B_BYTES;   /* two column blocks a stage */
+constexpr uint32_t EX_LUT_BYTES = 256 * 128;
+constexpr uint32_t EX_SMEM_BYTES = 1024 + EX_LUT_BYTES + EX_STAGES * EX_STAGE_BYTES + 2 * EX_BN * 4 + 256;
 
 struct ExpertFast {
     const uint8_t* codes[12];
@@ -152,16 +153,29 @@ struct ExpertFast {
 __device__ __forceinline__ void ex_cp16(uint32_t dst, const void* src, uint32_t src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+__device__ __forceinline__ uint4 ex_ldg128(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+/* A spinning wait (test_wait, no suspension) for the one thread whose wake-up latency is the whole pipeline's: bounded like mbar_wait. */
+__device__ __forceinline__ bool ex_spin_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, unsigned int* status) {
+    for (uint32_t i = 0; i < (SV_WAIT_TRIES << 4); ++i) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (done) return true;
+        if ((i & 1023u) == 1023u && *abort_flag != 0u) return false;
+    }
+    *abort_flag = 1u;
+    if (status) atomicOr(status, SV_STATUS_TIMEOUT);
+    return false;
+}
 __device__ __forceinline__ void ex_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void ex_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ uint32_t ex_lds32(uint32_t a) {
     uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint4 ex_lds128(uint32_t a) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));     /* (the table is written once, before the first lookup: not volatile, the compiler may move it) */
     return v;
 }
 __device__ __forceinline__ void ex_sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
@@ -172,8 +186,8 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
     extern __shared__ uint8_t ex_smem_raw[];
     const uint32_t base = (smem_u32(ex_smem_raw) + 1023u) & ~1023u;
     uint8_t* smem = ex_smem_raw + (base - smem_u32(ex_smem_raw));
-    const uint32_t lut_at = base, stage_at = lut_at + EX_LUT_BYTES, raw_at = stage_at + EX_STAGES * EX_STAGE_BYTES;
-    uint32_t* xrow_s = reinterpret_cast<uint32_t*>(smem + EX_LUT_BYTES + EX_STAGES * EX_STAGE_BYTES + EX_RAWS * EX_RAW_BYTES);
+    const uint32_t lut_at = base, stage_at = lut_at + EX_LUT_BYTES;
+    uint32_t* xrow_s = reinterpret_cast<uint32_t*>(smem + EX_LUT_BYTES + EX_STAGES * EX_STAGE_BYTES);
     uint32_t* orow_s = xrow_s + EX_BN;
     uint64_t* full = reinterpret_cast<uint64_t*>(orow_s + EX_BN);
     uint64_t* empty = full + EX_STAGES;
@@ -187,7 +201,7 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
     const uint32_t r0 = (blockIdx.x - a.tile0[g]) * EX_BM, j0 = blockIdx.y * EX_BN;
     if (j0 >= a.pairs[g]) return;                                           /* the whole block: this group has fewer pairs than the widest */
     const uint32_t nb = min((uint32_t)EX_BN, a.pairs[g] - j0), N = (nb + 15u) & ~15u;
-    const uint32_t d = a.d[g], cols = a.cols, nk = cols / EX_KC, out_rows = a.out_rows[g], held = a.held[g];
+    const uint32_t d = a.d[g], cols = a.cols, nk = cols / EX_KC, nst = (nk + 1u) / 2u, out_rows = a.out_rows[g], held = a.held[g];
     const uint64_t row_bytes = (uint64_t)cols * d / 8u;
 
     if (tid == 0) {
@@ -203,13 +217,12 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
             const uint32_t* pr = a.rows + 2ull * (a.pairs_at[g] + j0 + min((uint32_t)j, nb - 1u));
             xrow_s[j] = pr[0]; orow_s[j] = pr[1];
         }
-        if (d != 16u)
-            for (int i = p; i < 256 * 32; i += EX_PRODUCERS) {
-                const uint32_t e = (uint32_t)i >> 5;
-                const uint32_t l8 = g_tq_levels_expert[62 + e];
-                const uint32_t v = d == 4u ? ((uint32_t)g_tq_levels_expert[14 + (e & 15u)] | ((uint32_t)g_tq_levels_expert[14 + (e >> 4)] << 16)) : (l8 | (l8 << 16));
-                reinterpret_cast<uint32_t*>(smem)[i] = v;
-            }
+        if (d != 16u) {                                                      /* entry e, 32 copies: two threads an entry, half the copies each */
+            const uint32_t e = (uint32_t)p & 255u, l8 = g_tq_levels_expert[62 + e];
+            const uint32_t v = d == 4u ? ((uint32_t)g_tq_levels_expert[14 + (e & 15u)] | ((uint32_t)g_tq_levels_expert[14 + (e >> 4)] << 16)) : (l8 | (l8 << 16));
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) ex_sts128(lut_at + e * 128u + ((uint32_t)p >> 8) * 64u + i * 16u, v, v, v, v);
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -220,88 +233,140 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
         /* ---------------- every MMA ---------------- */
         if (lane == 0) {
             const uint32_t idesc = idesc_f16(0, 0, EX_BM, (int)N);
-            for (uint32_t k = 0; k < nk; ++k) {
-                const uint32_t s = k % EX_STAGES;
-                if (!mbar_wait(&full[s], (k / EX_STAGES) & 1u, abort_flag, a.status)) break;
+            uint32_t s = 0, ph = 0;
+            for (uint32_t st = 0; st < nst; ++st) {                          /* a stage: two column blocks (one at an odd end), eight MMAs a hand-over */
+                if (!ex_spin_wait(&full[s], ph, abort_flag, a.status)) break;
                 tc_fence_after();
-                const uint64_t ad = smem_desc_sw128(stage_at + s * EX_STAGE_BYTES, 16, 1024), bd = smem_desc_sw128(stage_at + s * EX_STAGE_BYTES + EX_A_BYTES, 16, 1024);
+                const uint32_t blocks = min(2u, nk - 2u * st);
+                for (uint32_t h = 0; h < blocks; ++h) {
+                    const uint64_t ad = smem_desc_sw128(stage_at + s * EX_STAGE_BYTES + h * EX_ATOM, 16, 1024);
+                    const uint64_t bd = smem_desc_sw128(stage_at + s * EX_STAGE_BYTES + EX_A_BYTES + h * EX_ATOM, 16, 1024);
 #pragma unroll
-                for (uint32_t kk = 0; kk < 4; ++kk) tc_mma(tmem, ad + kk * 2u, bd + kk * 2u, idesc, (k | kk) != 0u ? 1u : 0u);
+                    for (uint32_t kk = 0; kk < 4; ++kk) tc_mma(tmem, ad + kk * 2u, bd + kk * 2u, idesc, (st | h | kk) != 0u ? 1u : 0u);
+                }
                 tc_commit(&empty[s]);
+                if (++s == (uint32_t)EX_STAGES) { s = 0; ph ^= 1u; }
             }
             tc_commit(acc_full);
         }
     } else {
-        /* ---------------- producers: codes -> fp16 A tiles, the pairs' rows of x -> B tiles; then the read-out ---------------- */
-        const int p = tid - 32, row = p >> 1, half = p & 1;
+        /* ---------------- producers: codes -> fp16 A tiles, the pairs' rows of x -> B tiles; then the read-out ----------------
+         * A stage is TWO column blocks (128 columns): a hand-over between the producers and the issuing thread — the wait, the
+         * fence, the arrivals, the commit — costs a few hundred cycles on either side whatever hangs on it, so it is paid once a
+         * 128 columns.  A thread owns a quarter of a matrix row of the stage (32 columns: 16 bytes of 4-bit codes, 32 of 8-bit,
+         * 64 of halves — half of one 64-column tile) and up to four 16-byte pieces of the x tiles, the same chunk column of rows
+         * 32 apart — so every address of a stage is the one before plus a constant.  The codes are read two stages ahead into
+         * registers; x is copied one stage ahead by cp.async. */
+        const int p = tid - 32, row = p >> 2, quarter = p & 3;
         const uint32_t grow = r0 + (uint32_t)row;
         const bool row_ok = grow < held && grow < out_rows;
-        const uint8_t* my_codes = a.codes[g] + (row_ok ? (uint64_t)grow * row_bytes : 0ull);
+        const uint32_t code_step = d == 4u ? 64u : d == 8u ? 128u : 256u;    /* bytes of a row a stage covers */
+        const uint8_t* my_codes = a.codes[g] + (row_ok ? (uint64_t)grow * row_bytes : 0ull) + (uint32_t)quarter * (code_step / 4u);
         const uint32_t lane_lut = lut_at + (uint32_t)lane * 4u;
-        const uint32_t my_raw = (uint32_t)p * 32u;
-        bool ok = true;
-
-        auto issue = [&](uint32_t k) {
-            const uint32_t s = k % EX_STAGES;
-            if (k >= (uint32_t)EX_STAGES && ok) ok = mbar_wait(&empty[s], ((k / EX_STAGES) - 1u) & 1u, abort_flag, a.status);
-            if (!ok) return;
-            const uint32_t a_at = stage_at + s * EX_STAGE_BYTES, b_at = a_at + EX_A_BYTES;
-            for (uint32_t q = (uint32_t)p; q < N * 8u; q += EX_PRODUCERS) {
-                const uint32_t j = q >> 3, c = q & 7u;
-                ex_cp16(b_at + swz128(j, c), a.x + (uint64_t)xrow_s[j] * cols + (uint64_t)k * EX_KC + c * 8u, j < nb ? 16u : 0u);
-            }
-            const uint32_t bytes = row_ok ? 16u : 0u;
-            if (d == 4u) ex_cp16(raw_at + (k % EX_RAWS) * EX_RAW_BYTES + my_raw, my_codes + (uint64_t)k * 32u + (uint32_t)half * 16u, bytes);
-            else if (d == 8u) {
-                ex_cp16(raw_at + (k % EX_RAWS) * EX_RAW_BYTES + my_raw, my_codes + (uint64_t)k * 64u + (uint32_t)half * 32u, bytes);
-                ex_cp16(raw_at + (k % EX_RAWS) * EX_RAW_BYTES + my_raw + 16u, my_codes + (uint64_t)k * 64u + (uint32_t)half * 32u + 16u, bytes);
-            } else {
+        const uint32_t my_tile = (uint32_t)(quarter >> 1);                   /* which of the stage's two column blocks this thread's columns are in */
+        uint32_t a_off[4];
 #pragma unroll
-                for (uint32_t i = 0; i < 4; ++i)
-                    ex_cp16(a_at + swz128((uint32_t)row, (uint32_t)half * 4u + i), my_codes + (uint64_t)k * 128u + (uint32_t)half * 64u + i * 16u, bytes);
+        for (uint32_t i = 0; i < 4; ++i) a_off[i] = my_tile * EX_ATOM + swz128((uint32_t)row, (uint32_t)(quarter & 1) * 4u + i);
+        const uint32_t xc = (uint32_t)p & 15u, xj = (uint32_t)p >> 4;        /* this thread's chunk column of the stage's 16; its first row of the x tiles */
+        const uint32_t x_tile = xc >> 3;
+        const uint16_t* x_src[4];
+        uint32_t x_bytes[4];
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+            const uint32_t j = xj + 32u * i;
+            x_src[i] = a.x + (uint64_t)xrow_s[j] * cols + xc * 8u;
+            x_bytes[i] = j < nb ? 16u : 0u;
+        }
+        const uint32_t x_off = EX_A_BYTES + x_tile * EX_ATOM + swz128(xj, xc & 7u), x_count = N / 32u + ((N & 31u) > xj ? 1u : 0u);
+        bool ok = true;
+        uint32_t s_iss = 0, ph_iss = 1, st_iss = 0;                           /* the next stage to ask for: its slot, the parity of the slot's last release */
+        uint32_t s = 0;                                                       /* the slot of the stage being expanded */
+        /* whether column block `tile` of stage `st` exists (the last stage of an odd count of blocks has one) */
+        auto has = [&](uint32_t st, uint32_t tile) { return 2u * st + tile < nk; };
+
+        auto issue = [&]() {                                                  /* x (and a 16-bit matrix's own halves) of the next stage */
+            if (st_iss >= (uint32_t)EX_STAGES && ok) ok = mbar_wait(&empty[s_iss], ph_iss, abort_flag, a.status);
+            if (ok) {
+                const uint32_t at = stage_at + s_iss * EX_STAGE_BYTES;
+                if (has(st_iss, x_tile)) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i)
+                        if (i < x_count) ex_cp16(at + x_off + i * 4096u, x_src[i], x_bytes[i]);
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) x_src[i] += 2 * EX_KC;
+                if (d == 16u) {
+                    const uint32_t bytes = row_ok ? 16u : 0u;
+                    if (has(st_iss, my_tile)) {
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i) ex_cp16(at + a_off[i], my_codes + i * 16u, bytes);
+                    }
+                    my_codes += code_step;
+                }
             }
+            ++st_iss;
+            if (++s_iss == (uint32_t)EX_STAGES) { s_iss = 0; ph_iss ^= 1u; }
+        };
+        /* this thread's codes of stage st: four words at 4 bits, eight at 8 */
+        auto load_codes = [&](uint32_t st, uint32_t (&r)[8]) {
+#pragma unroll
+            for (uint32_t i = 0; i < 8; ++i) r[i] = 0u;
+            if (!row_ok || d == 16u || st >= nst || !has(st, my_tile)) return;
+            const uint4 v = ex_ldg128(my_codes + (uint64_t)st * code_step);
+            r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+            if (d == 8u) { const uint4 u = ex_ldg128(my_codes + (uint64_t)st * code_step + 16u); r[4] = u.x; r[5] = u.y; r[6] = u.z; r[7] = u.w; }
         };
 
-        for (uint32_t k = 0; k < (uint32_t)EX_LOOK; ++k) { if (k < nk) issue(k); ex_cp_commit(); }
-        for (uint32_t k = 0; k < nk; ++k) {
-            if (k + EX_LOOK < nk) issue(k + EX_LOOK);
+        uint32_t ra[8], rb[8], rc[8];
+        load_codes(0u, ra);
+        load_codes(1u, rb);
+        for (uint32_t st = 0; st < (uint32_t)EX_LOOK; ++st) { if (st < nst) issue(); ex_cp_commit(); }
+        for (uint32_t st = 0; st < nst && ok; ++st) {
+            load_codes(st + 2u, rc);                                         /* (past the end: zeros, nothing read) */
+            if (st + EX_LOOK < nst) issue();
             ex_cp_commit();                                                  /* (an empty group past the end keeps the count below uniform) */
-            ex_cp_wait<EX_LOOK>();                                           /* block k's copies of this thread have landed */
             if (!ok) break;
-            const uint32_t s = k % EX_STAGES, a_at = stage_at + s * EX_STAGE_BYTES, raw = raw_at + (k % EX_RAWS) * EX_RAW_BYTES + my_raw;
-            if (d == 4u) {
-                const uint4 cw = ex_lds128(raw);
-                const uint32_t ws[4] = {cw.x, cw.y, cw.z, cw.w};
+            const uint32_t a_at = stage_at + s * EX_STAGE_BYTES;
+            if (d == 4u) {                                                   /* a word: four bytes, eight codes, one 16-byte chunk of the row */
+                uint32_t v[16];                                              /* every lookup asked for before the first is used */
 #pragma unroll
-                for (uint32_t i = 0; i < 4; ++i) {                           /* a word: four bytes, eight codes, one 16-byte chunk of the row */
-                    const uint32_t v0 = ex_lds32(lane_lut + ((ws[i] << 7) & 0x7F80u)), v1 = ex_lds32(lane_lut + ((ws[i] >> 1) & 0x7F80u));
-                    const uint32_t v2 = ex_lds32(lane_lut + ((ws[i] >> 9) & 0x7F80u)), v3 = ex_lds32(lane_lut + ((ws[i] >> 17) & 0x7F80u));
-                    ex_sts128(a_at + swz128((uint32_t)row, (uint32_t)half * 4u + i), v0, v1, v2, v3);
+                for (uint32_t i = 0; i < 4; ++i) {
+                    const uint32_t w = ra[i];
+                    v[4 * i] = ex_lds32(lane_lut + ((w << 7) & 0x7F80u)); v[4 * i + 1] = ex_lds32(lane_lut + ((w >> 1) & 0x7F80u));
+                    v[4 * i + 2] = ex_lds32(lane_lut + ((w >> 9) & 0x7F80u)); v[4 * i + 3] = ex_lds32(lane_lut + ((w >> 17) & 0x7F80u));
                 }
-            } else if (d == 8u) {
-                const uint4 c0 = ex_lds128(raw), c1 = ex_lds128(raw + 16u);
-                const uint32_t ws[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
-                for (uint32_t i = 0; i < 4; ++i) {                           /* two words: eight bytes, eight codes, one chunk */
-                    uint32_t v[8];
+                for (uint32_t i = 0; i < 4; ++i) ex_sts128(a_at + a_off[i], v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            } else if (d == 8u) {                                            /* two words: eight codes, one chunk */
+                uint32_t v[32];
 #pragma unroll
-                    for (uint32_t u = 0; u < 2; ++u) {
-                        const uint32_t wv = ws[2 * i + u];
-                        v[4 * u] = ex_lds32(lane_lut + ((wv << 7) & 0x7F80u)); v[4 * u + 1] = ex_lds32(lane_lut + ((wv >> 1) & 0x7F80u));
-                        v[4 * u + 2] = ex_lds32(lane_lut + ((wv >> 9) & 0x7F80u)); v[4 * u + 3] = ex_lds32(lane_lut + ((wv >> 17) & 0x7F80u));
-                    }
-                    ex_sts128(a_at + swz128((uint32_t)row, (uint32_t)half * 4u + i), __byte_perm(v[0], v[1], 0x5410), __byte_perm(v[2], v[3], 0x5410),
-                              __byte_perm(v[4], v[5], 0x5410), __byte_perm(v[6], v[7], 0x5410));
+                for (uint32_t u = 0; u < 8; ++u) {
+                    const uint32_t w = ra[u];
+                    v[4 * u] = ex_lds32(lane_lut + ((w << 7) & 0x7F80u)); v[4 * u + 1] = ex_lds32(lane_lut + ((w >> 1) & 0x7F80u));
+                    v[4 * u + 2] = ex_lds32(lane_lut + ((w >> 9) & 0x7F80u)); v[4 * u + 3] = ex_lds32(lane_lut + ((w >> 17) & 0x7F80u));
                 }
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i)
+                    ex_sts128(a_at + a_off[i], __byte_perm(v[8 * i], v[8 * i + 1], 0x5410), __byte_perm(v[8 * i + 2], v[8 * i + 3], 0x5410),
+                              __byte_perm(v[8 * i + 4], v[8 * i + 5], 0x5410), __byte_perm(v[8 * i + 6], v[8 * i + 7], 0x5410));
             }
+            ex_cp_wait<EX_LOOK>();                                           /* this stage's copies of this thread have landed — waited for AFTER the
+                                                                                expansion, which does not need them */
             fence_proxy_async_smem();                                        /* this thread's stores and landed copies, for the MMA's reads */
             __syncwarp();
             if (lane == 0) mbar_arrive(&full[s]);
+            if (++s == (uint32_t)EX_STAGES) s = 0;
+#pragma unroll
+            for (uint32_t i = 0; i < 8; ++i) { ra[i] = rb[i]; rb[i] = rc[i]; }
         }
         ex_cp_wait<0>();
 
-        /* the read-out: a thread a matrix row (its lane of tensor memory), two warps a quadrant splitting the pairs 32 at a time */
-        if (ok) ok = mbar_wait(acc_full, 0u, abort_flag, a.status);
+        /* the read-out: a thread a matrix row (its lane of tensor memory), four warps a quadrant splitting the pairs 32 at a time */
+        if (ok) {
+            uint32_t got = 1u;
+            if (lane == 0) got = mbar_wait(acc_full, 0u, abort_flag, a.status) ? 1u : 0u;
+            ok = __shfl_sync(0xffffffffu, got, 0) != 0u;
+        }
         tc_fence_after();
         if (ok) {
             const uint32_t quad = (uint32_t)warp & 3u, grp = (uint32_t)(warp - 1) >> 2;
@@ -309,7 +374,7 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
             const bool live = orow < held && orow < out_rows;
             const float scale = d == 16u || !live ? 1.0f : H::to_float(a.scales[g][orow]);
             bool hit = false;
-            for (uint32_t cb = grp; cb * 32u < N; cb += 2u) {
+            for (uint32_t cb = grp; cb * 32u < N; cb += (uint32_t)EX_PRODUCERS / 128u) {
                 uint32_t v[32];
                 tmem_ld32(tmem + ((quad * 32u) << 16) + cb * 32u, v);
                 tmem_wait_ld();
