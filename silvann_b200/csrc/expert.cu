@@ -11,14 +11,16 @@
  * and o projections through these doors, up to 256 rows a call.
  *
  * Two kernels.  `expert_rows_kernel` is the door as worded — any width, any shape, a block a matrix row, eight pairs a pass.
- * `expert_fast_kernel` is the one a prompt runs on: a block owns 128 matrix rows and up to 128 pairs and walks the columns 64
- * at a time;
+ * `expert_fast_kernel` is the one a prompt runs on: a block owns 128 matrix rows and up to 128 pairs and walks the columns
+ * through a ring of three stages of TWO 64-column blocks each (a hand-over between the producers and the issuing thread
+ * costs a few hundred cycles on either side whatever hangs on it, so it is paid once a 128 columns);
  *   · sixteen producer warps expand the codes into fp16 in shared memory, K-major with the 128-byte swizzle, as the A operand
  *     (a code byte is ONE shared-memory lookup in a table of 256 entries of 128 bytes — a lane reads its own bank, so no
  *     lookup ever conflicts; at 4 bits an entry is the byte's two levels, at 8 bits the level twice), and gather the pairs'
- *     rows of x as the B operand — both through cp.async three column blocks ahead, the raw codes through a small staging ring;
- *   · one thread issues tcgen05.mma (M 128, N = the pairs rounded up to 16, K 16 a step), accumulating in tensor memory, and
- *     gives a stage back to the producers by a commit on its mbarrier;
+ *     rows of x as the B operand with cp.async one stage ahead; the codes themselves are read two stages ahead into registers,
+ *     so every byte of shared memory goes to the stages;
+ *   · one thread issues tcgen05.mma (M 128, N = the pairs rounded up to 16, K 16 a step, eight a stage), accumulating in
+ *     tensor memory, and gives a stage back to the producers by a commit on its mbarrier;
  *   · the producers then read the accumulator out of tensor memory, scale a row by its fp16 scale, round once and store —
  *     or, for expert_rows_sum, add weight · value onto the fp32 running sum.
  * Shapes the fast kernel takes: widths 4, 8 and 16, columns a multiple of 64, codes and x on 16 bytes.  Every mbarrier wait
