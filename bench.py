@@ -1096,7 +1096,10 @@ def run_ours(args):
     if not args.no_others:
         del wl, e2e
         torch.cuda.empty_cache()
-        lc = long_context(torch, dist, rank, world, max(steps, 10), pk)
+        try:
+            lc = long_context(torch, dist, rank, world, max(steps, 10), pk)
+        except Exception as e:                                   # the headline line is still printed; the failure is said in it
+            lc = {"error": f"{type(e).__name__}: {e}"}
         if rank == 0:
             line["long_context_config4"] = lc
     if world > 1:
