@@ -936,7 +936,20 @@ def long_context(torch, dist, rank, world, steps, pk):
     h_len = max(0, min(HOST, shard.pos_hi) - shard.pos_lo)
     k_host = k[:h_len].cpu().pin_memory() if h_len else None
     v_host = v[:h_len].cpu().pin_memory() if h_len else None
-    h2d_peak = pinned_h2d_peak(torch)
+    # the box's pinned host-to-device rate: rank 0 alone, and then every rank at once (the ranks' copies may share host links
+    # and memory channels: what a GPU can get while its neighbours stream too is the bound of the tiered step at N > 1)
+    h2d_alone = torch.zeros(1, device="cuda", dtype=torch.float64)
+    if rank == 0:
+        h2d_alone[0] = pinned_h2d_peak(torch)
+    if world > 1:
+        dist.broadcast(h2d_alone, 0)
+        dist.barrier()
+    h2d_alone = float(h2d_alone.item())
+    h2d_peak = h2d_alone
+    if world > 1:
+        together = torch.tensor([pinned_h2d_peak(torch)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(together, op=dist.ReduceOp.MIN)
+        h2d_peak = float(together.item())
     # the ranks that split a kv head's range exchange residuals through the library's own kernel over peer memory; the
     # buffers' handles travel once, here
     exchange = sharded.connect_exchange(torch, ext, dist, shard.group, rank, shard.q_heads * (d + 2) * 4) if world > 1 else None
@@ -956,7 +969,8 @@ def long_context(torch, dist, rank, world, steps, pk):
     gbs = host_bytes / out["tiered"]["ms_per_step"] / 1e6
     holders = min(world, kvh)                                 # ranks that hold a share of the host tier (the first range half of every kv head)
     out["tiered"].update({"host_tier_bytes": host_bytes, "host_tier_gbs": gbs, "host_tier_gbs_per_holding_gpu": gbs / holders,
-                          "pinned_h2d_peak_gbs_measured": h2d_peak, "host_tier_frac_of_h2d_peak": gbs / holders / h2d_peak,
+                          "pinned_h2d_peak_gbs_measured": h2d_alone, "pinned_h2d_peak_gbs_all_ranks_at_once": h2d_peak,
+                          "host_tier_frac_of_h2d_peak": gbs / holders / h2d_peak, "host_tier_frac_of_h2d_peak_one_gpu_alone": gbs / holders / h2d_alone,
                           "lower_bound_ms": max(host_bytes / holders / h2d_peak / 1e6, (nbytes - host_bytes) / world / pk["hbm_gbs"] / 1e6)})
     if exchange is not None:
         # the exchange alone: a residual each, pushed, waited for and folded — the merge latency of the range split
