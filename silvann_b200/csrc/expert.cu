@@ -14,13 +14,16 @@
  * `expert_fast_kernel` is the one a prompt runs on: a block owns 128 matrix rows and up to 128 pairs and walks the columns
  * through a ring of three stages of TWO 64-column blocks each (a hand-over between the producers and the issuing thread
  * costs a few hundred cycles on either side whatever hangs on it, so it is paid once a 128 columns);
- *   · sixteen producer warps expand the codes into fp16 in shared memory, K-major with the 128-byte swizzle, as the A operand
- *     (a code byte is ONE shared-memory lookup in a table of 256 entries of 128 bytes — a lane reads its own bank, so no
- *     lookup ever conflicts; at 4 bits an entry is the byte's two levels, at 8 bits the level twice), and gather the pairs'
- *     rows of x as the B operand with cp.async one stage ahead; the codes themselves are read two stages ahead into registers,
- *     so every byte of shared memory goes to the stages;
- *   · one thread issues tcgen05.mma (M 128, N = the pairs rounded up to 16, K 16 a step, eight a stage), accumulating in
- *     tensor memory, and gives a stage back to the producers by a commit on its mbarrier;
+ *   · sixteen producer warps expand the codes to fp16 straight into TENSOR MEMORY as the A operand — a thread owns one
+ *     matrix row (its lane) and 32 of the stage's columns, a code byte is ONE shared-memory lookup in a table of 256 entries
+ *     of 128 bytes (a lane reads its own bank, so no lookup ever conflicts; at 4 bits an entry is the byte's two levels,
+ *     packed as the MMA wants them; at 8 bits the level twice), and the 16 packed words go out with one tcgen05.st — so
+ *     the matrix's expanded rows never pass through the shared-memory pipe, which is what a block runs out of;
+ *   · the codes reach their row's owner through a small padded ring in shared memory, copied two stages ahead by cp.async
+ *     with the threads laid along a row (whole lines from DRAM); the pairs' rows of x are gathered as the B operand
+ *     (K-major, 128-byte swizzle) by cp.async one stage ahead;
+ *   · one thread issues tcgen05.mma with A in tensor memory (M 128, N = the pairs rounded up to 16, K 16 a step, eight a
+ *     stage), accumulating in tensor memory, and gives a stage back to the producers by a commit on its mbarrier;
  *   · the producers then read the accumulator out of tensor memory, scale a row by its fp16 scale, round once and store —
  *     or, for expert_rows_sum, add weight · value onto the fp32 running sum.
  * Shapes the fast kernel takes: widths 4, 8 and 16, columns a multiple of 64, codes and x on 16 bytes.  Every mbarrier wait
@@ -131,11 +134,13 @@ __global__ void __launch_bounds__(256) expert_pairs_rows_kernel(uint32_t* pairs,
 /* ---- the fast kernel ---------------------------------------------------------------------------------------------------- */
 
 constexpr int EX_THREADS = 544, EX_PRODUCERS = 512, EX_BM = 128, EX_BN = 128, EX_KC = 64;
-constexpr int EX_STAGES = 3, EX_LOOK = 1;                           /* stages of two column blocks; stages the copies of x run ahead */
+constexpr int EX_STAGES = 3;                                          /* stages of two column blocks; the copies of x run one ahead */
 constexpr uint32_t EX_ATOM = 16384;                                   /* a tile of 128 rows x 64 columns of halves, 128-byte rows, swizzled */
-constexpr uint32_t EX_A_BYTES = 2 * EX_ATOM, EX_B_BYTES = 2 * EX_ATOM, EX_STAGE_BYTES = EX_A_BYTES + EX_B_BYTES;   /* two column blocks a stage */
+constexpr uint32_t EX_STAGE_BYTES = 2 * EX_ATOM;                      /* a stage's x: two column blocks (the matrix's rows live in tensor memory) */
+constexpr uint32_t EX_RAWS = 4, EX_RAW_PITCH4 = 80, EX_RAW_PITCH8 = 144, EX_RAW_BYTES = 128 * EX_RAW_PITCH8;   /* a stage's codes as they lie in memory, rows padded apart */
+constexpr uint32_t EX_T_ACC = 0, EX_T_A = 128, EX_T_A_STAGE = 64, EX_T_COLS = 512;   /* tensor memory: the sums, then a stage's A operand, 64 packed columns each */
 constexpr uint32_t EX_LUT_BYTES = 256 * 128;
-constexpr uint32_t EX_SMEM_BYTES = 1024 + EX_LUT_BYTES + EX_STAGES * EX_STAGE_BYTES + 2 * EX_BN * 4 + 256;
+constexpr uint32_t EX_SMEM_BYTES = 1024 + EX_LUT_BYTES + EX_STAGES * EX_STAGE_BYTES + EX_RAWS * EX_RAW_BYTES + 2 * EX_BN * 4 + 256;
 
 struct ExpertFast {
     const uint8_t* codes[12];
@@ -180,6 +185,11 @@ __device__ __forceinline__ uint32_t ex_lds32(uint32_t a) {
     asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));     /* (the table is written once, before the first lookup: not volatile, the compiler may move it) */
     return v;
 }
+__device__ __forceinline__ uint4 ex_lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory");
+    return v;
+}
 __device__ __forceinline__ void ex_sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
@@ -188,8 +198,8 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
     extern __shared__ uint8_t ex_smem_raw[];
     const uint32_t base = (smem_u32(ex_smem_raw) + 1023u) & ~1023u;
     uint8_t* smem = ex_smem_raw + (base - smem_u32(ex_smem_raw));
-    const uint32_t lut_at = base, stage_at = lut_at + EX_LUT_BYTES;
-    uint32_t* xrow_s = reinterpret_cast<uint32_t*>(smem + EX_LUT_BYTES + EX_STAGES * EX_STAGE_BYTES);
+    const uint32_t lut_at = base, stage_at = lut_at + EX_LUT_BYTES, raw_at = stage_at + EX_STAGES * EX_STAGE_BYTES;
+    uint32_t* xrow_s = reinterpret_cast<uint32_t*>(smem + EX_LUT_BYTES + EX_STAGES * EX_STAGE_BYTES + EX_RAWS * EX_RAW_BYTES);
     uint32_t* orow_s = xrow_s + EX_BN;
     uint64_t* full = reinterpret_cast<uint64_t*>(orow_s + EX_BN);
     uint64_t* empty = full + EX_STAGES;
@@ -212,7 +222,7 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
         *abort_flag = 0u;
         mbar_fence_init();
     }
-    if (warp == 0) tmem_alloc(tmem_slot, 128);
+    if (warp == 0) tmem_alloc(tmem_slot, EX_T_COLS);
     else {
         const int p = tid - 32;
         for (int j = p; j < EX_BN; j += EX_PRODUCERS) {
@@ -240,11 +250,11 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
                 if (!ex_spin_wait(&full[s], ph, abort_flag, a.status)) break;
                 tc_fence_after();
                 const uint32_t blocks = min(2u, nk - 2u * st);
-                for (uint32_t h = 0; h < blocks; ++h) {
-                    const uint64_t ad = smem_desc_sw128(stage_at + s * EX_STAGE_BYTES + h * EX_ATOM, 16, 1024);
-                    const uint64_t bd = smem_desc_sw128(stage_at + s * EX_STAGE_BYTES + EX_A_BYTES + h * EX_ATOM, 16, 1024);
+                for (uint32_t h = 0; h < blocks; ++h) {                        /* A: this stage's rows in tensor memory, 8 packed columns a step of 16 */
+                    const uint64_t bd = smem_desc_sw128(stage_at + s * EX_STAGE_BYTES + h * EX_ATOM, 16, 1024);
+                    const uint32_t at = tmem + EX_T_A + s * EX_T_A_STAGE + h * 32u;
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 4; ++kk) tc_mma(tmem, ad + kk * 2u, bd + kk * 2u, idesc, (st | h | kk) != 0u ? 1u : 0u);
+                    for (uint32_t kk = 0; kk < 4; ++kk) tc_mma_ts(tmem + EX_T_ACC, at + kk * 8u, bd + kk * 2u, idesc, (st | h | kk) != 0u ? 1u : 0u);
                 }
                 tc_commit(&empty[s]);
                 if (++s == (uint32_t)EX_STAGES) { s = 0; ph ^= 1u; }
@@ -252,23 +262,34 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
             tc_commit(acc_full);
         }
     } else {
-        /* ---------------- producers: codes -> fp16 A tiles, the pairs' rows of x -> B tiles; then the read-out ----------------
+        /* ---------------- producers: codes -> the A operand in tensor memory, the pairs' rows of x -> B tiles; then the read-out ----
          * A stage is TWO column blocks (128 columns): a hand-over between the producers and the issuing thread — the wait, the
-         * fence, the arrivals, the commit — costs a few hundred cycles on either side whatever hangs on it, so it is paid once a
-         * 128 columns.  A thread owns a quarter of a matrix row of the stage (32 columns: 16 bytes of 4-bit codes, 32 of 8-bit,
-         * 64 of halves — half of one 64-column tile) and up to four 16-byte pieces of the x tiles, the same chunk column of rows
-         * 32 apart — so every address of a stage is the one before plus a constant.  The codes are read two stages ahead into
-         * registers; x is copied one stage ahead by cp.async. */
-        const int p = tid - 32, row = p >> 2, quarter = p & 3;
-        const uint32_t grow = r0 + (uint32_t)row;
-        const bool row_ok = grow < held && grow < out_rows;
+         * fences, the arrivals, the commit — costs a few hundred cycles on either side whatever hangs on it, so it is paid once a
+         * 128 columns.  The shared-memory pipe is what a block runs out of (tiles stored, copied and read by the MMA all pass
+         * through it), so the matrix's expanded rows never touch it: a thread owns ONE matrix row (its lane of tensor memory; a
+         * warp its quadrant's 32 rows) and 32 of the stage's columns (the four warps of a quadrant a quarter each), looks its
+         * codes up — a 4-bit byte's entry is already two neighbouring halves packed as the MMA wants them — and stores the 16
+         * packed words with one tcgen05.st; the MMA takes A from tensor memory and only x from shared memory.
+         * The codes come through a small ring as they lie in memory: copied two stages ahead by cp.async with the threads laid
+         * along a row (a row's 64 or 128 bytes of a stage in one go: whole lines from DRAM), read back by the row's owner
+         * (rows padded apart, so neither side meets a bank conflict).  A slot is written again four stages later, after a wait
+         * every thread makes first: for the release of the x slot of three stages ago, which every warp's hand-over preceded.
+         * A thread also copies up to four 16-byte pieces of the x tiles (one chunk column, rows 32 apart) one stage ahead. */
+        const int p = tid - 32;
+        const uint32_t quad = (uint32_t)warp & 3u, part = (uint32_t)(warp - 1) >> 2, row = quad * 32u + (uint32_t)lane;
+        const bool own_ok = r0 + row < held && r0 + row < out_rows;          /* the row this thread expands */
         const uint32_t code_step = d == 4u ? 64u : d == 8u ? 128u : 256u;    /* bytes of a row a stage covers */
-        const uint8_t* my_codes = a.codes[g] + (row_ok ? (uint64_t)grow * row_bytes : 0ull) + (uint32_t)quarter * (code_step / 4u);
+        const uint32_t pitch = d == 4u ? EX_RAW_PITCH4 : EX_RAW_PITCH8;
+        /* the copying side: thread p takes 16 bytes of row p / 4 (4 bits) or 32 bytes of it (8 bits) */
+        const uint32_t c_row = (uint32_t)p >> 2, c_q = (uint32_t)p & 3u, c_bytes = d == 4u ? 16u : 32u;
+        const bool c_ok = r0 + c_row < held && r0 + c_row < out_rows;
+        const uint8_t* c_src = a.codes[g] + (c_ok ? (uint64_t)(r0 + c_row) * row_bytes : 0ull) + c_q * c_bytes;
+        const uint32_t c_dst = raw_at + c_row * pitch + c_q * c_bytes;
+        const uint32_t my_raw = raw_at + row * pitch + part * (code_step / 4u);   /* the reading side: this thread's 32 columns of its row */
+        const uint8_t* my_halves = a.codes[g] + (own_ok ? (uint64_t)(r0 + row) * row_bytes : 0ull) + part * 64u;   /* (16 bits: read straight from memory) */
         const uint32_t lane_lut = lut_at + (uint32_t)lane * 4u;
-        const uint32_t my_tile = (uint32_t)(quarter >> 1);                   /* which of the stage's two column blocks this thread's columns are in */
-        uint32_t a_off[4];
-#pragma unroll
-        for (uint32_t i = 0; i < 4; ++i) a_off[i] = my_tile * EX_ATOM + swz128((uint32_t)row, (uint32_t)(quarter & 1) * 4u + i);
+        const uint32_t my_tile = part >> 1;                                  /* which of the stage's two column blocks this thread's columns are in */
+        const uint32_t a_at = tmem + EX_T_A + part * 16u + ((quad * 32u) << 16);   /* + the slot's 64 columns */
         const uint32_t xc = (uint32_t)p & 15u, xj = (uint32_t)p >> 4;        /* this thread's chunk column of the stage's 16; its first row of the x tiles */
         const uint32_t x_tile = xc >> 3;
         const uint16_t* x_src[4];
@@ -279,87 +300,105 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
             x_src[i] = a.x + (uint64_t)xrow_s[j] * cols + xc * 8u;
             x_bytes[i] = j < nb ? 16u : 0u;
         }
-        const uint32_t x_off = EX_A_BYTES + x_tile * EX_ATOM + swz128(xj, xc & 7u), x_count = N / 32u + ((N & 31u) > xj ? 1u : 0u);
+        const uint32_t x_off = x_tile * EX_ATOM + swz128(xj, xc & 7u), x_count = N / 32u + ((N & 31u) > xj ? 1u : 0u);
         bool ok = true;
-        uint32_t s_iss = 0, ph_iss = 1, st_iss = 0;                           /* the next stage to ask for: its slot, the parity of the slot's last release */
+        uint32_t s_iss = 0, ph_iss = 1, st_iss = 0;                           /* the next stage of x to ask for: its slot, the parity of the slot's last release */
         uint32_t s = 0;                                                       /* the slot of the stage being expanded */
         /* whether column block `tile` of stage `st` exists (the last stage of an odd count of blocks has one) */
         auto has = [&](uint32_t st, uint32_t tile) { return 2u * st + tile < nk; };
 
-        auto issue = [&]() {                                                  /* x (and a 16-bit matrix's own halves) of the next stage */
+        auto issue_x = [&]() {                                                /* x of the next stage, once the MMAs that read the slot have completed */
             if (st_iss >= (uint32_t)EX_STAGES && ok) ok = mbar_wait(&empty[s_iss], ph_iss, abort_flag, a.status);
-            if (ok) {
+            if (ok && has(st_iss, x_tile)) {
                 const uint32_t at = stage_at + s_iss * EX_STAGE_BYTES;
-                if (has(st_iss, x_tile)) {
 #pragma unroll
-                    for (uint32_t i = 0; i < 4; ++i)
-                        if (i < x_count) ex_cp16(at + x_off + i * 4096u, x_src[i], x_bytes[i]);
-                }
-#pragma unroll
-                for (uint32_t i = 0; i < 4; ++i) x_src[i] += 2 * EX_KC;
-                if (d == 16u) {
-                    const uint32_t bytes = row_ok ? 16u : 0u;
-                    if (has(st_iss, my_tile)) {
-#pragma unroll
-                        for (uint32_t i = 0; i < 4; ++i) ex_cp16(at + a_off[i], my_codes + i * 16u, bytes);
-                    }
-                    my_codes += code_step;
-                }
+                for (uint32_t i = 0; i < 4; ++i)
+                    if (i < x_count) ex_cp16(at + x_off + i * 4096u, x_src[i], x_bytes[i]);
             }
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) x_src[i] += 2 * EX_KC;
             ++st_iss;
             if (++s_iss == (uint32_t)EX_STAGES) { s_iss = 0; ph_iss ^= 1u; }
         };
-        /* this thread's codes of stage st: four words at 4 bits, eight at 8 */
-        auto load_codes = [&](uint32_t st, uint32_t (&r)[8]) {
-#pragma unroll
-            for (uint32_t i = 0; i < 8; ++i) r[i] = 0u;
-            if (!row_ok || d == 16u || st >= nst || !has(st, my_tile)) return;
-            const uint4 v = ex_ldg128(my_codes + (uint64_t)st * code_step);
-            r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
-            if (d == 8u) { const uint4 u = ex_ldg128(my_codes + (uint64_t)st * code_step + 16u); r[4] = u.x; r[5] = u.y; r[6] = u.z; r[7] = u.w; }
+        auto issue_codes = [&](uint32_t st) {                                 /* stage st's codes into the ring (nothing at 16 bits, nothing past the end) */
+            if (d == 16u || st >= nst || !ok) return;
+            const uint32_t to = c_dst + (st & (EX_RAWS - 1u)) * EX_RAW_BYTES, bytes = c_ok ? 16u : 0u;
+            const uint8_t* from = c_src + (uint64_t)st * code_step;
+            /* (the second column block of an odd last stage lies past the row's end: the upper half of the stage's bytes is not read) */
+            const bool second = has(st, 1u);
+            if (d == 4u) { if (second || c_q < 2u) ex_cp16(to, from, bytes); }
+            else if (second || c_q < 2u) { ex_cp16(to, from, bytes); ex_cp16(to + 16u, from + 16, bytes); }
         };
-
-        uint32_t ra[8], rb[8], rc[8];
-        load_codes(0u, ra);
-        load_codes(1u, rb);
-        for (uint32_t st = 0; st < (uint32_t)EX_LOOK; ++st) { if (st < nst) issue(); ex_cp_commit(); }
-        for (uint32_t st = 0; st < nst && ok; ++st) {
-            load_codes(st + 2u, rc);                                         /* (past the end: zeros, nothing read) */
-            if (st + EX_LOOK < nst) issue();
-            ex_cp_commit();                                                  /* (an empty group past the end keeps the count below uniform) */
-            if (!ok) break;
-            const uint32_t a_at = stage_at + s * EX_STAGE_BYTES;
-            if (d == 4u) {                                                   /* a word: four bytes, eight codes, one 16-byte chunk of the row */
-                uint32_t v[16];                                              /* every lookup asked for before the first is used */
-#pragma unroll
-                for (uint32_t i = 0; i < 4; ++i) {
-                    const uint32_t w = ra[i];
-                    v[4 * i] = ex_lds32(lane_lut + ((w << 7) & 0x7F80u)); v[4 * i + 1] = ex_lds32(lane_lut + ((w >> 1) & 0x7F80u));
-                    v[4 * i + 2] = ex_lds32(lane_lut + ((w >> 9) & 0x7F80u)); v[4 * i + 3] = ex_lds32(lane_lut + ((w >> 17) & 0x7F80u));
-                }
-#pragma unroll
-                for (uint32_t i = 0; i < 4; ++i) ex_sts128(a_at + a_off[i], v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            } else if (d == 8u) {                                            /* two words: eight codes, one chunk */
-                uint32_t v[32];
-#pragma unroll
-                for (uint32_t u = 0; u < 8; ++u) {
-                    const uint32_t w = ra[u];
-                    v[4 * u] = ex_lds32(lane_lut + ((w << 7) & 0x7F80u)); v[4 * u + 1] = ex_lds32(lane_lut + ((w >> 1) & 0x7F80u));
-                    v[4 * u + 2] = ex_lds32(lane_lut + ((w >> 9) & 0x7F80u)); v[4 * u + 3] = ex_lds32(lane_lut + ((w >> 17) & 0x7F80u));
-                }
-#pragma unroll
-                for (uint32_t i = 0; i < 4; ++i)
-                    ex_sts128(a_at + a_off[i], __byte_perm(v[8 * i], v[8 * i + 1], 0x5410), __byte_perm(v[8 * i + 2], v[8 * i + 3], 0x5410),
-                              __byte_perm(v[8 * i + 4], v[8 * i + 5], 0x5410), __byte_perm(v[8 * i + 6], v[8 * i + 7], 0x5410));
-            }
-            ex_cp_wait<EX_LOOK>();                                           /* this stage's copies of this thread have landed — waited for AFTER the
-                                                                                expansion, which does not need them */
-            fence_proxy_async_smem();                                        /* this thread's stores and landed copies, for the MMA's reads */
+        /* the stage's x of this thread has landed, its row of A is in tensor memory: the slot goes to the issuing thread */
+        auto hand_over = [&]() {
+            fence_proxy_async_smem();                                        /* the landed copies of x, for the MMA's reads */
+            tmem_wait_st();
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&full[s]);
             if (++s == (uint32_t)EX_STAGES) s = 0;
+        };
+
+        issue_codes(0u);
+        if (nst > 0u) issue_x();
+        ex_cp_commit();
+        issue_codes(1u);
+        ex_cp_commit();
+        for (uint32_t st = 0; st < nst && ok; ++st) {
+            if (st + 1u < nst) issue_x();                                    /* (waits for the release of stage st - 2's slot: every warp has handed st - 2 over) */
+            issue_codes(st + 2u);                                            /* over the codes of stage st - 2 */
+            ex_cp_commit();                                                  /* (an empty group past the end keeps the count below uniform) */
+            ex_cp_wait<1>();                                                 /* this thread's copies for stage st — its x, and its share of the codes — have landed */
+            /* the producers meet: every thread's share of the stage's codes has landed — and a thread whose wait ran out takes
+             * all of them out together, so nobody is left at this barrier */
+            {
+                uint32_t any;
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.or.pred p, 1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(any) : "r"(ok ? 0u : 1u), "n"(EX_PRODUCERS) : "memory");
+                if (any) { ok = false; break; }
+            }
+            uint32_t words[16];                                              /* 32 columns of this row: 16 words of two halves */
+            if (d == 16u) {
 #pragma unroll
-            for (uint32_t i = 0; i < 8; ++i) { ra[i] = rb[i]; rb[i] = rc[i]; }
+                for (uint32_t i = 0; i < 16; ++i) words[i] = 0u;
+                if (own_ok && has(st, my_tile)) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        const uint4 v = ex_ldg128(my_halves + (uint64_t)st * code_step + i * 16u);
+                        words[4 * i] = v.x; words[4 * i + 1] = v.y; words[4 * i + 2] = v.z; words[4 * i + 3] = v.w;
+                    }
+                }
+            } else {
+                const uint32_t raw = my_raw + (st & (EX_RAWS - 1u)) * EX_RAW_BYTES;
+                if (d == 4u) {                                               /* a byte: two codes, one word — every lookup asked for before the first is used */
+                    const uint4 cw = ex_lds128(raw);
+                    const uint32_t ws[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        const uint32_t w = ws[i];
+                        words[4 * i] = ex_lds32(lane_lut + ((w << 7) & 0x7F80u)); words[4 * i + 1] = ex_lds32(lane_lut + ((w >> 1) & 0x7F80u));
+                        words[4 * i + 2] = ex_lds32(lane_lut + ((w >> 9) & 0x7F80u)); words[4 * i + 3] = ex_lds32(lane_lut + ((w >> 17) & 0x7F80u));
+                    }
+                } else {                                                     /* a byte: one code; two lookups make a word */
+                    const uint4 c0 = ex_lds128(raw), c1 = ex_lds128(raw + 16u);
+                    const uint32_t ws[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                    uint32_t v[32];
+#pragma unroll
+                    for (uint32_t u = 0; u < 8; ++u) {
+                        const uint32_t w = ws[u];
+                        v[4 * u] = ex_lds32(lane_lut + ((w << 7) & 0x7F80u)); v[4 * u + 1] = ex_lds32(lane_lut + ((w >> 1) & 0x7F80u));
+                        v[4 * u + 2] = ex_lds32(lane_lut + ((w >> 9) & 0x7F80u)); v[4 * u + 3] = ex_lds32(lane_lut + ((w >> 17) & 0x7F80u));
+                    }
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) words[i] = __byte_perm(v[2 * i], v[2 * i + 1], 0x5410);
+                }
+                if (!own_ok) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) words[i] = 0u;
+                }
+            }
+            tmem_st16(a_at + s * EX_T_A_STAGE, words);
+            hand_over();
         }
         ex_cp_wait<0>();
 
@@ -396,7 +435,7 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, 128);
+    if (warp == 0) tmem_dealloc(tmem, EX_T_COLS);
 }
 
 /* ---------------------------------------------------------------------------------------------------------------------------- */
