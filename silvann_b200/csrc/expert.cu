@@ -12,20 +12,21 @@
  *
  * Two kernels.  `expert_rows_kernel` is the door as worded — any width, any shape, a block a matrix row, eight pairs a pass.
  * `expert_fast_kernel` is the one a prompt runs on: a block owns 128 matrix rows and up to 128 pairs and walks the columns
- * through a ring of three stages of TWO 64-column blocks each (a hand-over between the producers and the issuing thread
- * costs a few hundred cycles on either side whatever hangs on it, so it is paid once a 128 columns);
- *   · sixteen producer warps expand the codes to fp16 straight into TENSOR MEMORY as the A operand — a thread owns one
- *     matrix row (its lane) and 32 of the stage's columns, a code byte is ONE shared-memory lookup in a table of 256 entries
- *     of 128 bytes (a lane reads its own bank, so no lookup ever conflicts; at 4 bits an entry is the byte's two levels,
- *     packed as the MMA wants them; at 8 bits the level twice), and the 16 packed words go out with one tcgen05.st — so
- *     the matrix's expanded rows never pass through the shared-memory pipe, which is what a block runs out of;
- *   · the codes reach their row's owner through a small padded ring in shared memory, copied two stages ahead by cp.async
- *     with the threads laid along a row (whole lines from DRAM); the pairs' rows of x are gathered as the B operand
- *     (K-major, 128-byte swizzle) by cp.async one stage ahead;
+ * through a ring of stages of TWO 64-column blocks each (a hand-over between its roles costs a few hundred cycles on either
+ * side whatever hangs on it, so it is paid once a 128 columns).  Three roles, each a chain of its own:
+ *   · eight COPIER warps gather the pairs' rows of x as the B operand (K-major, 128-byte swizzle) and bring the codes, as
+ *     they lie in memory, into a small padded ring — cp.async, the threads laid along a row (whole lines from DRAM), as far
+ *     ahead as the slots allow (four stages where every group is 4 bits wide, three where one is 8);
+ *   · sixteen EXPANDER warps turn the codes into fp16 straight in TENSOR MEMORY as the A operand — a thread owns one matrix
+ *     row (its lane) and 32 of the stage's columns, a code byte is ONE shared-memory lookup in a table of 256 entries of 128
+ *     bytes (a lane reads its own bank, so no lookup ever conflicts; at 4 bits an entry is the byte's two levels, packed as
+ *     the MMA wants them; at 8 bits the level twice), and the 16 packed words go out with one tcgen05.st — so the matrix's
+ *     expanded rows never pass through the shared-memory pipe, which is what a block runs out of;
  *   · one thread issues tcgen05.mma with A in tensor memory (M 128, N = the pairs rounded up to 16, K 16 a step, eight a
- *     stage), accumulating in tensor memory, and gives a stage back to the producers by a commit on its mbarrier;
- *   · the producers then read the accumulator out of tensor memory, scale a row by its fp16 scale, round once and store —
- *     or, for expert_rows_sum, add weight · value onto the fp32 running sum.
+ *     stage), accumulating in tensor memory, and gives a stage back by a commit on its mbarrier.
+ * The expanders then read the accumulator out of tensor memory, scale a row by its fp16 scale, round once and store — or,
+ * for expert_rows_sum, add weight · value onto the fp32 running sum.  The roles meet only on mbarriers (no block barrier
+ * inside the loop), so a wait that runs out raises the block's flag and every role leaves by itself.
  * Shapes the fast kernel takes: widths 4, 8 and 16, columns a multiple of 64, codes and x on 16 bytes.  Every mbarrier wait
  * is bounded; one that runs out ORs "B2TO" into the device's status word and the block leaves through the common exit
  * (copies in flight waited for, tensor memory given back). */
@@ -133,21 +134,22 @@ __global__ void __launch_bounds__(256) expert_pairs_rows_kernel(uint32_t* pairs,
 
 /* ---- the fast kernel ---------------------------------------------------------------------------------------------------- */
 
-constexpr int EX_THREADS = 544, EX_PRODUCERS = 512, EX_BM = 128, EX_BN = 128, EX_KC = 64;
-constexpr int EX_STAGES = 3;                                          /* stages of two column blocks; the copies of x run one ahead */
+constexpr int EX_COPIERS = 256, EX_THREADS = 800, EX_PRODUCERS = 512, EX_BM = 128, EX_BN = 128, EX_KC = 64;
+constexpr int EX_STAGES_MAX = 4;                                      /* stages of two column blocks: four, or three where a group's codes are 8 bits wide (its ring slots are larger) */
 constexpr uint32_t EX_ATOM = 16384;                                   /* a tile of 128 rows x 64 columns of halves, 128-byte rows, swizzled */
 constexpr uint32_t EX_STAGE_BYTES = 2 * EX_ATOM;                      /* a stage's x: two column blocks (the matrix's rows live in tensor memory) */
-constexpr uint32_t EX_RAWS = 4, EX_RAW_PITCH4 = 80, EX_RAW_PITCH8 = 144, EX_RAW_BYTES = 128 * EX_RAW_PITCH8;   /* a stage's codes as they lie in memory, rows padded apart */
+constexpr uint32_t EX_RAW_PITCH4 = 80, EX_RAW_PITCH8 = 144;          /* a stage's codes as they lie in memory, rows padded apart: a ring slot is 128 rows of these */
 constexpr uint32_t EX_T_ACC = 0, EX_T_A = 128, EX_T_A_STAGE = 64, EX_T_COLS = 512;   /* tensor memory: the sums, then a stage's A operand, 64 packed columns each */
 constexpr uint32_t EX_LUT_BYTES = 256 * 128;
-constexpr uint32_t EX_SMEM_BYTES = 1024 + EX_LUT_BYTES + EX_STAGES * EX_STAGE_BYTES + EX_RAWS * EX_RAW_BYTES + 2 * EX_BN * 4 + 256;
+__host__ __device__ constexpr uint32_t ex_smem_bytes(uint32_t stages, uint32_t raw_bytes) { return 1024u + EX_LUT_BYTES + stages * (EX_STAGE_BYTES + raw_bytes) + 2u * EX_BN * 4u + 256u; }
+constexpr uint32_t EX_SMEM_MAX = ex_smem_bytes(4, 128 * EX_RAW_PITCH4) > ex_smem_bytes(3, 128 * EX_RAW_PITCH8) ? ex_smem_bytes(4, 128 * EX_RAW_PITCH4) : ex_smem_bytes(3, 128 * EX_RAW_PITCH8);
 
 struct ExpertFast {
     const uint8_t* codes[12];
     const uint16_t* scales[12];
     uint32_t out_rows[12], held[12], d[12], pairs_at[12], pairs[12], tile0[13];   /* group i's blocks of 128 rows are [tile0[i], tile0[i+1]) */
     uint64_t out_at[12];
-    uint32_t count, cols;
+    uint32_t count, cols, stages, raw_bytes;   /* stages: 3 or 4; raw_bytes: a ring slot */
     const uint16_t* x;
     const uint32_t* rows;
     const uint16_t* w;
@@ -164,19 +166,6 @@ __device__ __forceinline__ uint4 ex_ldg128(const void* p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
-}
-/* A spinning wait (test_wait, no suspension) for the one thread whose wake-up latency is the whole pipeline's: bounded like mbar_wait. */
-__device__ __forceinline__ bool ex_spin_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, unsigned int* status) {
-    for (uint32_t i = 0; i < (SV_WAIT_TRIES << 4); ++i) {
-        uint32_t done;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-        if (done) return true;
-        if ((i & 1023u) == 1023u && *abort_flag != 0u) return false;
-    }
-    *abort_flag = 1u;
-    if (status) atomicOr(status, SV_STATUS_TIMEOUT);
-    return false;
 }
 __device__ __forceinline__ void ex_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void ex_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -198,12 +187,14 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
     extern __shared__ uint8_t ex_smem_raw[];
     const uint32_t base = (smem_u32(ex_smem_raw) + 1023u) & ~1023u;
     uint8_t* smem = ex_smem_raw + (base - smem_u32(ex_smem_raw));
-    const uint32_t lut_at = base, stage_at = lut_at + EX_LUT_BYTES, raw_at = stage_at + EX_STAGES * EX_STAGE_BYTES;
-    uint32_t* xrow_s = reinterpret_cast<uint32_t*>(smem + EX_LUT_BYTES + EX_STAGES * EX_STAGE_BYTES + EX_RAWS * EX_RAW_BYTES);
+    const uint32_t S = a.stages, RAW = a.raw_bytes;                          /* stages (and ring slots); bytes a ring slot */
+    const uint32_t lut_at = base, stage_at = lut_at + EX_LUT_BYTES, raw_at = stage_at + S * EX_STAGE_BYTES;
+    uint32_t* xrow_s = reinterpret_cast<uint32_t*>(smem + EX_LUT_BYTES + S * (EX_STAGE_BYTES + RAW));
     uint32_t* orow_s = xrow_s + EX_BN;
     uint64_t* full = reinterpret_cast<uint64_t*>(orow_s + EX_BN);
-    uint64_t* empty = full + EX_STAGES;
-    uint64_t* acc_full = empty + EX_STAGES;
+    uint64_t* empty = full + EX_STAGES_MAX;
+    uint64_t* raw_full = empty + EX_STAGES_MAX;
+    uint64_t* acc_full = raw_full + EX_STAGES_MAX;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -217,13 +208,13 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
     const uint64_t row_bytes = (uint64_t)cols * d / 8u;
 
     if (tid == 0) {
-        for (int s = 0; s < EX_STAGES; ++s) { mbar_init(&full[s], EX_PRODUCERS / 32); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < EX_STAGES_MAX; ++s) { mbar_init(&full[s], (EX_PRODUCERS + EX_COPIERS) / 32); mbar_init(&empty[s], 1); mbar_init(&raw_full[s], EX_COPIERS / 32); }
         mbar_init(acc_full, 1);
         *abort_flag = 0u;
         mbar_fence_init();
     }
     if (warp == 0) tmem_alloc(tmem_slot, EX_T_COLS);
-    else {
+    else if (warp <= EX_PRODUCERS / 32) {
         const int p = tid - 32;
         for (int j = p; j < EX_BN; j += EX_PRODUCERS) {
             const uint32_t* pr = a.rows + 2ull * (a.pairs_at[g] + j0 + min((uint32_t)j, nb - 1u));
@@ -247,7 +238,7 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
             const uint32_t idesc = idesc_f16(0, 0, EX_BM, (int)N);
             uint32_t s = 0, ph = 0;
             for (uint32_t st = 0; st < nst; ++st) {                          /* a stage: two column blocks (one at an odd end), eight MMAs a hand-over */
-                if (!ex_spin_wait(&full[s], ph, abort_flag, a.status)) break;
+                if (!mbar_wait(&full[s], ph, abort_flag, a.status)) break;
                 tc_fence_after();
                 const uint32_t blocks = min(2u, nk - 2u * st);
                 for (uint32_t h = 0; h < blocks; ++h) {                        /* A: this stage's rows in tensor memory, 8 packed columns a step of 16 */
@@ -257,111 +248,105 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
                     for (uint32_t kk = 0; kk < 4; ++kk) tc_mma_ts(tmem + EX_T_ACC, at + kk * 8u, bd + kk * 2u, idesc, (st | h | kk) != 0u ? 1u : 0u);
                 }
                 tc_commit(&empty[s]);
-                if (++s == (uint32_t)EX_STAGES) { s = 0; ph ^= 1u; }
+                if (++s == S) { s = 0; ph ^= 1u; }
             }
             tc_commit(acc_full);
         }
+    } else if (warp > EX_PRODUCERS / 32) {
+        /* ---------------- copiers: the pairs' rows of x -> B tiles, the codes as they lie -> the ring ----------------
+         * Eight warps that only copy, two stages ahead: what a warp does for a stage is one chain of waits, so the copies have
+         * a chain of their own beside the expanders'.  A thread takes one chunk column of the stage's 16 and the rows 16 apart
+         * (N / 16 pieces of 16 bytes), and two or four 16-byte pieces of the codes, its addresses carried from stage to stage.  A slot of x is written again once the MMAs of
+         * three stages ago have completed (their commit); that also frees the ring slot of four stages ago, which the
+         * expanders had read before they handed that stage over. */
+        const uint32_t cp = (uint32_t)(tid - 32 - EX_PRODUCERS);              /* 0 .. 255 */
+        const uint32_t xc = cp & 15u, xj = cp >> 4;                            /* chunk column; first row (rows xj, xj + 16, ...) */
+        const uint32_t x_off = (xc >> 3) * EX_ATOM + swz128(xj, xc & 7u), x_count = N / 16u;
+        const uint16_t* x_src[8];
+        uint32_t x_bytes[8];
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i) {
+            const uint32_t j = xj + 16u * i;
+            x_src[i] = a.x + (uint64_t)xrow_s[j] * cols + xc * 8u;
+            x_bytes[i] = j < nb ? 16u : 0u;
+        }
+        const uint32_t code_step = d == 4u ? 64u : d == 8u ? 128u : 256u, pitch = d == 4u ? EX_RAW_PITCH4 : EX_RAW_PITCH8;
+        const uint32_t per_row = code_step / 16u, c_count = d == 16u ? 0u : 128u * per_row / EX_COPIERS;   /* 16-byte pieces of codes a row; a thread (2 or 4) */
+        const uint32_t c_q = cp & (per_row - 1u), c_row0 = cp / per_row, c_rows = EX_COPIERS / per_row;   /* its piece of a row; its rows c_row0, + c_rows, ... */
+        const uint8_t* c_src[4];
+        uint32_t c_dst[4], c_bytes[4];
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+            const uint32_t crow = c_row0 + c_rows * i;
+            const bool live = i < c_count && r0 + crow < held && r0 + crow < out_rows;
+            c_src[i] = a.codes[g] + (live ? (uint64_t)(r0 + crow) * row_bytes : 0ull) + c_q * 16u;
+            c_dst[i] = raw_at + crow * pitch + c_q * 16u;
+            c_bytes[i] = live ? 16u : 0u;
+        }
+        const uint32_t LAG = S - 2u;                                          /* stages its copies run ahead of their hand-over: the slots less the one the MMA reads and one to spare */
+        bool ok = true;
+        uint32_t sx = 0, phx = 1, sr = 0;                                      /* the slot of the stage asked for, the parity of its last release; the slot handed over next */
+        for (uint32_t c = 0; c < nst + LAG; ++c) {
+            if (c < nst) {
+                if (c >= S && ok) ok = mbar_wait(&empty[sx], phx, abort_flag, a.status);
+                if (ok) {
+                    const bool second = 2u * c + 1u < nk;                      /* the stage's second column block exists */
+                    if (second || xc < 8u) {
+                        const uint32_t at = stage_at + sx * EX_STAGE_BYTES + x_off;
+#pragma unroll
+                        for (uint32_t i = 0; i < 8; ++i)
+                            if (i < x_count) ex_cp16(at + i * 2048u, x_src[i], x_bytes[i]);
+                    }
+                    if (second || c_q * 2u < per_row) {
+                        const uint32_t to = sx * RAW;
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i)
+                            if (i < c_count) ex_cp16(c_dst[i] + to, c_src[i], c_bytes[i]);
+                    }
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < 8; ++i) x_src[i] += 2 * EX_KC;
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) c_src[i] += code_step;
+                if (++sx == S) { sx = 0; phx ^= 1u; }
+            }
+            ex_cp_commit();
+            if (c >= LAG) {                                                  /* stage c - LAG: this thread's copies have landed */
+                if (LAG == 2u) ex_cp_wait<2>(); else ex_cp_wait<1>();
+                fence_proxy_async_smem();                                    /* x, for the MMA's reads */
+                __syncwarp();
+                if (lane == 0 && ok) { mbar_arrive(&raw_full[sr]); mbar_arrive(&full[sr]); }
+                if (++sr == S) sr = 0;
+            }
+            if (!ok) break;
+        }
+        ex_cp_wait<0>();
     } else {
-        /* ---------------- producers: codes -> the A operand in tensor memory, the pairs' rows of x -> B tiles; then the read-out ----
-         * A stage is TWO column blocks (128 columns): a hand-over between the producers and the issuing thread — the wait, the
-         * fences, the arrivals, the commit — costs a few hundred cycles on either side whatever hangs on it, so it is paid once a
-         * 128 columns.  The shared-memory pipe is what a block runs out of (tiles stored, copied and read by the MMA all pass
-         * through it), so the matrix's expanded rows never touch it: a thread owns ONE matrix row (its lane of tensor memory; a
-         * warp its quadrant's 32 rows) and 32 of the stage's columns (the four warps of a quadrant a quarter each), looks its
-         * codes up — a 4-bit byte's entry is already two neighbouring halves packed as the MMA wants them — and stores the 16
-         * packed words with one tcgen05.st; the MMA takes A from tensor memory and only x from shared memory.
-         * The codes come through a small ring as they lie in memory: copied two stages ahead by cp.async with the threads laid
-         * along a row (a row's 64 or 128 bytes of a stage in one go: whole lines from DRAM), read back by the row's owner
-         * (rows padded apart, so neither side meets a bank conflict).  A slot is written again four stages later, after a wait
-         * every thread makes first: for the release of the x slot of three stages ago, which every warp's hand-over preceded.
-         * A thread also copies up to four 16-byte pieces of the x tiles (one chunk column, rows 32 apart) one stage ahead. */
-        const int p = tid - 32;
+        /* ---------------- expanders: codes -> the A operand in tensor memory; then the read-out ----------------
+         * A stage is TWO column blocks (128 columns): a hand-over between the producers and the issuing thread — the waits,
+         * the fences, the arrivals, the commit — costs a few hundred cycles on either side whatever hangs on it, so it is paid
+         * once a 128 columns.  The shared-memory pipe is what a block runs out of, so the matrix's expanded rows never touch
+         * it: a thread owns ONE matrix row (its lane of tensor memory; a warp its quadrant's 32 rows) and 32 of the stage's
+         * columns (the four warps of a quadrant a quarter each), reads its 16 or 32 bytes of codes from the ring (rows padded
+         * apart: no bank conflict), looks them up — a 4-bit byte's entry is already two neighbouring halves packed as the MMA
+         * wants them — and stores the 16 packed words with one tcgen05.st; the MMA takes A from tensor memory. */
         const uint32_t quad = (uint32_t)warp & 3u, part = (uint32_t)(warp - 1) >> 2, row = quad * 32u + (uint32_t)lane;
         const bool own_ok = r0 + row < held && r0 + row < out_rows;          /* the row this thread expands */
         const uint32_t code_step = d == 4u ? 64u : d == 8u ? 128u : 256u;    /* bytes of a row a stage covers */
         const uint32_t pitch = d == 4u ? EX_RAW_PITCH4 : EX_RAW_PITCH8;
-        /* the copying side: thread p takes 16 bytes of row p / 4 (4 bits) or 32 bytes of it (8 bits) */
-        const uint32_t c_row = (uint32_t)p >> 2, c_q = (uint32_t)p & 3u, c_bytes = d == 4u ? 16u : 32u;
-        const bool c_ok = r0 + c_row < held && r0 + c_row < out_rows;
-        const uint8_t* c_src = a.codes[g] + (c_ok ? (uint64_t)(r0 + c_row) * row_bytes : 0ull) + c_q * c_bytes;
-        const uint32_t c_dst = raw_at + c_row * pitch + c_q * c_bytes;
-        const uint32_t my_raw = raw_at + row * pitch + part * (code_step / 4u);   /* the reading side: this thread's 32 columns of its row */
+        const uint32_t my_raw = raw_at + row * pitch + part * (code_step / 4u);   /* this thread's 32 columns of its row */
         const uint8_t* my_halves = a.codes[g] + (own_ok ? (uint64_t)(r0 + row) * row_bytes : 0ull) + part * 64u;   /* (16 bits: read straight from memory) */
         const uint32_t lane_lut = lut_at + (uint32_t)lane * 4u;
         const uint32_t my_tile = part >> 1;                                  /* which of the stage's two column blocks this thread's columns are in */
         const uint32_t a_at = tmem + EX_T_A + part * 16u + ((quad * 32u) << 16);   /* + the slot's 64 columns */
-        const uint32_t xc = (uint32_t)p & 15u, xj = (uint32_t)p >> 4;        /* this thread's chunk column of the stage's 16; its first row of the x tiles */
-        const uint32_t x_tile = xc >> 3;
-        const uint16_t* x_src[4];
-        uint32_t x_bytes[4];
-#pragma unroll
-        for (uint32_t i = 0; i < 4; ++i) {
-            const uint32_t j = xj + 32u * i;
-            x_src[i] = a.x + (uint64_t)xrow_s[j] * cols + xc * 8u;
-            x_bytes[i] = j < nb ? 16u : 0u;
-        }
-        const uint32_t x_off = x_tile * EX_ATOM + swz128(xj, xc & 7u), x_count = N / 32u + ((N & 31u) > xj ? 1u : 0u);
         bool ok = true;
-        uint32_t s_iss = 0, ph_iss = 1, st_iss = 0;                           /* the next stage of x to ask for: its slot, the parity of the slot's last release */
-        uint32_t s = 0;                                                       /* the slot of the stage being expanded */
-        /* whether column block `tile` of stage `st` exists (the last stage of an odd count of blocks has one) */
-        auto has = [&](uint32_t st, uint32_t tile) { return 2u * st + tile < nk; };
-
-        auto issue_x = [&]() {                                                /* x of the next stage, once the MMAs that read the slot have completed */
-            if (st_iss >= (uint32_t)EX_STAGES && ok) ok = mbar_wait(&empty[s_iss], ph_iss, abort_flag, a.status);
-            if (ok && has(st_iss, x_tile)) {
-                const uint32_t at = stage_at + s_iss * EX_STAGE_BYTES;
-#pragma unroll
-                for (uint32_t i = 0; i < 4; ++i)
-                    if (i < x_count) ex_cp16(at + x_off + i * 4096u, x_src[i], x_bytes[i]);
-            }
-#pragma unroll
-            for (uint32_t i = 0; i < 4; ++i) x_src[i] += 2 * EX_KC;
-            ++st_iss;
-            if (++s_iss == (uint32_t)EX_STAGES) { s_iss = 0; ph_iss ^= 1u; }
-        };
-        auto issue_codes = [&](uint32_t st) {                                 /* stage st's codes into the ring (nothing at 16 bits, nothing past the end) */
-            if (d == 16u || st >= nst || !ok) return;
-            const uint32_t to = c_dst + (st & (EX_RAWS - 1u)) * EX_RAW_BYTES, bytes = c_ok ? 16u : 0u;
-            const uint8_t* from = c_src + (uint64_t)st * code_step;
-            /* (the second column block of an odd last stage lies past the row's end: the upper half of the stage's bytes is not read) */
-            const bool second = has(st, 1u);
-            if (d == 4u) { if (second || c_q < 2u) ex_cp16(to, from, bytes); }
-            else if (second || c_q < 2u) { ex_cp16(to, from, bytes); ex_cp16(to + 16u, from + 16, bytes); }
-        };
-        /* the stage's x of this thread has landed, its row of A is in tensor memory: the slot goes to the issuing thread */
-        auto hand_over = [&]() {
-            fence_proxy_async_smem();                                        /* the landed copies of x, for the MMA's reads */
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&full[s]);
-            if (++s == (uint32_t)EX_STAGES) s = 0;
-        };
-
-        issue_codes(0u);
-        if (nst > 0u) issue_x();
-        ex_cp_commit();
-        issue_codes(1u);
-        ex_cp_commit();
+        uint32_t s = 0, ph = 1;                                               /* the slot of the stage being expanded; the parity of its last release */
         for (uint32_t st = 0; st < nst && ok; ++st) {
-            if (st + 1u < nst) issue_x();                                    /* (waits for the release of stage st - 2's slot: every warp has handed st - 2 over) */
-            issue_codes(st + 2u);                                            /* over the codes of stage st - 2 */
-            ex_cp_commit();                                                  /* (an empty group past the end keeps the count below uniform) */
-            ex_cp_wait<1>();                                                 /* this thread's copies for stage st — its x, and its share of the codes — have landed */
-            /* the producers meet: every thread's share of the stage's codes has landed — and a thread whose wait ran out takes
-             * all of them out together, so nobody is left at this barrier */
-            {
-                uint32_t any;
-                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.or.pred p, 1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                             : "=r"(any) : "r"(ok ? 0u : 1u), "n"(EX_PRODUCERS) : "memory");
-                if (any) { ok = false; break; }
-            }
             uint32_t words[16];                                              /* 32 columns of this row: 16 words of two halves */
             if (d == 16u) {
 #pragma unroll
                 for (uint32_t i = 0; i < 16; ++i) words[i] = 0u;
-                if (own_ok && has(st, my_tile)) {
+                if (own_ok && 2u * st + my_tile < nk) {
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i) {
                         const uint4 v = ex_ldg128(my_halves + (uint64_t)st * code_step + i * 16u);
@@ -369,7 +354,8 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
                     }
                 }
             } else {
-                const uint32_t raw = my_raw + (st & (EX_RAWS - 1u)) * EX_RAW_BYTES;
+                if (!mbar_wait(&raw_full[s], ph ^ 1u, abort_flag, a.status)) { ok = false; break; }
+                const uint32_t raw = my_raw + s * RAW;
                 if (d == 4u) {                                               /* a byte: two codes, one word — every lookup asked for before the first is used */
                     const uint4 cw = ex_lds128(raw);
                     const uint32_t ws[4] = {cw.x, cw.y, cw.z, cw.w};
@@ -397,10 +383,15 @@ __global__ void __launch_bounds__(EX_THREADS, 1) expert_fast_kernel(const Expert
                     for (uint32_t i = 0; i < 16; ++i) words[i] = 0u;
                 }
             }
+            /* the slot of tensor memory is free once the MMAs of three stages ago have read it */
+            if (st >= S && !mbar_wait(&empty[s], ph, abort_flag, a.status)) { ok = false; break; }
             tmem_st16(a_at + s * EX_T_A_STAGE, words);
-            hand_over();
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[s]);
+            if (++s == S) { s = 0; ph ^= 1u; }
         }
-        ex_cp_wait<0>();
 
         /* the read-out: a thread a matrix row (its lane of tensor memory), four warps a quadrant splitting the pairs 32 at a time */
         if (ok) {
@@ -504,6 +495,10 @@ cudaError_t expert_fast_launch(uint16_t* out, float* acc, const void* groups, co
         if (a.pairs[i] > widest) widest = a.pairs[i];
     }
     a.tile0[g.count] = tiles;
+    bool wide = false;                                                      /* a group at 8 bits: larger ring slots, one stage fewer */
+    for (uint64_t i = 0; i < g.count; ++i) wide = wide || g.d[i] == 8;
+    a.stages = wide ? 3u : 4u;
+    a.raw_bytes = 128u * (wide ? EX_RAW_PITCH8 : EX_RAW_PITCH4);
     a.count = (uint32_t)g.count; a.cols = (uint32_t)cols; a.x = x; a.rows = rows; a.w = w; a.out = out; a.acc = acc; a.over = over;
     a.status = device_status_word();
     static std::atomic<bool> ready[64];
@@ -512,12 +507,12 @@ cudaError_t expert_fast_launch(uint16_t* out, float* acc, const void* groups, co
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!ready[dev].load(std::memory_order_acquire)) {
-        e = cudaFuncSetAttribute(expert_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)EX_SMEM_BYTES);
+        e = cudaFuncSetAttribute(expert_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)EX_SMEM_MAX);
         if (e != cudaSuccess) return e;
         ready[dev].store(true, std::memory_order_release);
     }
     const dim3 grid(tiles, (widest + EX_BN - 1) / EX_BN);
-    expert_fast_kernel<<<grid, EX_THREADS, EX_SMEM_BYTES, st>>>(a);
+    expert_fast_kernel<<<grid, EX_THREADS, ex_smem_bytes(a.stages, a.raw_bytes), st>>>(a);
     note_launch(1);
     return cudaGetLastError();
 }
