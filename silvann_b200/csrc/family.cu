@@ -55,12 +55,14 @@ static bool fuse_enabled() {
 }
 
 /* ---- the deferred first door of a pair, per device ---- */
-enum PendingKind { NONE = 0, SCORES, WEIGHTS, CAUSAL_RAW, CAUSAL_SOFT, WEIGHTS_ROWS, WEIGHTS_TQ, GROUPED_RAW, GROUPED_SOFT };
+enum PendingKind { NONE = 0, SCORES, WEIGHTS, CAUSAL_RAW, CAUSAL_SOFT, WEIGHTS_ROWS, WEIGHTS_TQ, GROUPED_RAW, GROUPED_SOFT, NORM_ROWS };
 struct Pending {
     int kind;
     float* p; float* res; const uint16_t* q; const uint16_t* k;      /* WEIGHTS_TQ: k is the key codes */
     uint64_t qh, kvh, d, length, first, rows;
     const uint16_t* scales; uint64_t width;                          /* WEIGHTS_TQ only: the key rows' scales and the code width */
+    /* NORM_ROWS (rmsnorm_rows recorded in case rope_rows over the same rows follows): q = x, k = w, d = n, rows, first = x_stride, length = o_stride */
+    uint16_t* o16; float eps; unsigned int* over;
 };
 static Pending g_pending[DEVICES_MAX];
 static std::mutex g_pending_lock[DEVICES_MAX];
@@ -86,6 +88,7 @@ static void run_pending_locked(Pending& pd) {
             check("attention_scores_grouped", sv::scores_launch(x.p, x.q, x.k, x.qh, x.kvh, x.d, x.length, 2, nullptr, 0));
             check("attention_softmax_rows", sv::softmax_rows_launch(x.p, x.qh, x.length, 0));
             break;
+        case NORM_ROWS:   check("rmsnorm_rows", sv::rmsnorm_rows_launch(x.o16, x.q, x.k, x.d, x.rows, x.first, x.length, x.eps, x.over, 0)); break;
         case WEIGHTS_TQ:  check("attention_weights_tq", sv::tq_weights_launch(x.p, x.res, x.q, (const uint8_t*)x.k, x.scales, x.qh, x.kvh, x.d, x.length, x.width, x.rows, 0)); break;
         default: return;
     }
@@ -490,14 +493,41 @@ static void d_rmsnorm(sv_h16* o, const sv_h16* x, const sv_h16* w, sv_u64 n, flo
 }
 static void d_rmsnorm_rows(sv_h16* o, const sv_h16* x, const sv_h16* w, sv_u64 n, sv_u64 rows, sv_u64 x_stride, sv_u64 o_stride, float eps, sv_fault* over) {
     flush();
-    if (n * rows) check("rmsnorm_rows", sv::rmsnorm_rows_launch(o, x, w, n, rows, x_stride, o_stride, eps, over, 0));
+    if (n * rows == 0) return;
+    /* A mixer norms every head's row and then turns it (rope_rows in place over the same rows): recorded, and one kernel
+     * answers both if that is what follows; any other door first runs this one as worded. */
+    const int dev = current_device();
+    if (fuse_enabled() && dev >= 0 && dev < DEVICES_MAX && n <= 16384) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        Pending pd;
+        memset(&pd, 0, sizeof pd);
+        pd.kind = NORM_ROWS; pd.q = x; pd.k = w; pd.d = n; pd.rows = rows; pd.first = x_stride; pd.length = o_stride; pd.o16 = o; pd.eps = eps; pd.over = over;
+        g_pending[dev] = pd;
+        return;
+    }
+    check("rmsnorm_rows", sv::rmsnorm_rows_launch(o, x, w, n, rows, x_stride, o_stride, eps, over, 0));
 }
 static void d_rope(sv_h16* o, const sv_h16* x, const float* cs, sv_u64 heads, sv_u64 head_dim, sv_fault* over) {
     flush();
     if (heads * (head_dim / 2)) check("rope", sv::rope_rows_launch(o, x, cs, 1, heads, head_dim, 0, head_dim, over, 0));
 }
 static void d_rope_rows(sv_h16* o, const sv_h16* x, const float* cs, sv_u64 rows, sv_u64 heads, sv_u64 head_stride, sv_u64 row_stride, sv_u64 rot, sv_fault* over) {
-    flush();
+    const int dev = current_device();
+    if (dev >= 0 && dev < DEVICES_MAX) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        Pending& pd = g_pending[dev];
+        /* the rows just normed, turned in place: norm row r is head r % heads of position r / heads, a head_stride apart, whole */
+        if (pd.kind == NORM_ROWS && x == o && o == pd.o16 && pd.rows == rows * heads && pd.length == head_stride && row_stride == heads * head_stride
+            && rot <= pd.d && rot % 2 == 0 && over == pd.over && rows * heads * (rot / 2) != 0) {
+            const Pending y = pd;
+            pd.kind = NONE;
+            const cudaError_t e = sv::rmsnorm_rope_rows_launch(o, y.q, y.k, cs, y.d, y.rows, heads, y.first, y.length, rot, y.eps, over, 0);
+            if (e == cudaSuccess) { bump(SILVANN_B200_COUNTER_FUSED_NORM_ROPE); return; }
+            (void)cudaGetLastError();                 /* the fused launch was not taken: the two doors as worded */
+            pd = y;
+        }
+        run_pending_locked(pd);
+    }
     if (rows * heads * (rot / 2)) check("rope_rows", sv::rope_rows_launch(o, x, cs, rows, heads, head_stride, row_stride, rot, over, 0));
 }
 static void d_rope_interleaved(sv_h16* o, const sv_h16* x, const float* cs, sv_u64 heads, sv_u64 head_stride, sv_u64 rot, sv_u64 inverse, sv_fault* over) {

@@ -97,6 +97,9 @@ cudaError_t vector_add_launch(uint16_t* z, const uint16_t* x, const uint16_t* y,
 cudaError_t vector_copy_rows_launch(uint16_t* out, uint64_t out_row, const uint16_t* in, uint64_t in_row, uint64_t width, uint64_t rows, cudaStream_t st);
 cudaError_t rmsnorm_rows_launch(uint16_t* o, const uint16_t* x, const uint16_t* w, uint64_t n, uint64_t rows, uint64_t x_stride, uint64_t o_stride,
                                 float eps, unsigned int* over, cudaStream_t st);
+/* rmsnorm_rows then rope_rows over the same rows as one kernel (rows = positions x heads; the bits of the two doors in turn) */
+cudaError_t rmsnorm_rope_rows_launch(uint16_t* o, const uint16_t* x, const uint16_t* w, const float* cs, uint64_t n, uint64_t rows, uint64_t heads,
+                                     uint64_t x_stride, uint64_t o_stride, uint64_t rot, float eps, unsigned int* over, cudaStream_t st);
 cudaError_t rope_rows_launch(uint16_t* o, const uint16_t* x, const float* cs, uint64_t rows, uint64_t heads, uint64_t head_stride, uint64_t row_stride,
                              uint64_t rot, unsigned int* over, cudaStream_t st);
 cudaError_t rope_interleaved_launch(uint16_t* o, const uint16_t* x, const float* cs, uint64_t heads, uint64_t head_stride, uint64_t rot, uint64_t inverse,

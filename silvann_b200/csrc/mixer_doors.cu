@@ -50,6 +50,43 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(uint16_t* o, const ui
     if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
 }
 
+/* rmsnorm_rows followed by rope_rows over the same rows, in one pass: a block a (position, head) row — its norm as the door
+ * above makes it, rounded to a half, kept in shared memory — and then the rotation of the row's first `rot` elements by the
+ * position's angles, reading those halves: the bits of the two doors one after the other.  Row r of the norm is head r %
+ * heads of position r / heads; the angles of a position are at cs + position·rot. */
+__global__ void __launch_bounds__(256) rmsnorm_rope_rows_kernel(uint16_t* o, const uint16_t* x, const uint16_t* w, const float* cs, uint64_t n, uint64_t rows,
+                                                                uint64_t heads, uint64_t x_stride, uint64_t o_stride, uint64_t rot, float eps,
+                                                                unsigned int* over) {
+    extern __shared__ uint16_t nr_row[];
+    __shared__ float sh[8];
+    const uint64_t pairs = rot / 2;
+    bool hit = false;
+    for (uint64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const uint16_t* xr = x + r * x_stride;
+        float part = 0.f;
+        for (uint64_t i = threadIdx.x; i < n; i += blockDim.x) { const float v = H::to_float(xr[i]); part += v * v; }
+        for (int s = 16; s > 0; s >>= 1) part += __shfl_xor_sync(0xffffffffu, part, s);
+        if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = part;
+        __syncthreads();
+        float sum = 0.f;
+        for (unsigned k = 0; k < blockDim.x / 32; ++k) sum += sh[k];
+        const float scale = 1.0f / sqrtf(sum / (float)n + eps);
+        for (uint64_t i = threadIdx.x; i < n; i += blockDim.x) nr_row[i] = H::from_float((H::to_float(xr[i]) * scale) * H::to_float(w[i]), hit);
+        __syncthreads();
+        const float* ang = cs + (r / heads) * rot;
+        uint16_t* orow = o + r * o_stride;
+        for (uint64_t k = threadIdx.x; k < pairs; k += blockDim.x) {         /* the turn, worded as rope_rows words it */
+            const float a = H::to_float(nr_row[k]), b = H::to_float(nr_row[k + pairs]);
+            const float c = ang[k], s = ang[pairs + k];
+            orow[k] = H::from_float(a * c - b * s, hit);
+            orow[k + pairs] = H::from_float(b * c + a * s, hit);
+        }
+        for (uint64_t i = rot + threadIdx.x; i < n; i += blockDim.x) orow[i] = nr_row[i];
+        __syncthreads();
+    }
+    if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
+}
+
 /* rotate_half on the first `rot` elements of every head of every row; row r's angles at cs + r·rot (cosines then sines) */
 __global__ void __launch_bounds__(256) rope_rows_kernel(uint16_t* o, const uint16_t* x, const float* cs, uint64_t rows, uint64_t heads,
                                                         uint64_t head_stride, uint64_t row_stride, uint64_t rot, unsigned int* over) {
@@ -141,6 +178,13 @@ cudaError_t rmsnorm_rows_launch(uint16_t* o, const uint16_t* x, const uint16_t* 
                                 float eps, unsigned int* over, cudaStream_t st) {
     const unsigned threads = n >= 2048 ? 256u : (n >= 512 ? 128u : 64u);
     rmsnorm_rows_kernel<<<(unsigned)(rows < 1 ? 1 : (rows > 65535 ? 65535 : rows)), threads, 0, st>>>(o, x, w, n, rows, x_stride, o_stride, eps, over); SV_DONE();
+}
+cudaError_t rmsnorm_rope_rows_launch(uint16_t* o, const uint16_t* x, const uint16_t* w, const float* cs, uint64_t n, uint64_t rows, uint64_t heads,
+                                     uint64_t x_stride, uint64_t o_stride, uint64_t rot, float eps, unsigned int* over, cudaStream_t st) {
+    if (n == 0 || n > 16384 || rot > n || rot % 2 != 0 || heads == 0) return cudaErrorInvalidValue;
+    const unsigned threads = n >= 2048 ? 256u : (n >= 512 ? 128u : 64u);    /* the norm door's own block: the same partial sums in the same order */
+    rmsnorm_rope_rows_kernel<<<(unsigned)(rows < 1 ? 1 : (rows > 65535 ? 65535 : rows)), threads, n * sizeof(uint16_t), st>>>(o, x, w, cs, n, rows, heads, x_stride,
+                                                                                                                         o_stride, rot, eps, over); SV_DONE();
 }
 cudaError_t rope_rows_launch(uint16_t* o, const uint16_t* x, const float* cs, uint64_t rows, uint64_t heads, uint64_t head_stride, uint64_t row_stride,
                              uint64_t rot, unsigned int* over, cudaStream_t st) {

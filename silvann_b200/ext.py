@@ -11,7 +11,7 @@ from . import library_path
 
 FP16, BF16 = 0, 1
 OK, E_ARGUMENT, E_CUDA, E_TIMEOUT, E_STATE = 0, 1, 2, 3, 4
-COUNTERS = ("fused_decode", "fused_residual", "fused_prefill", "flushed", "refused", "deltanet", "launches", "ext_calls", "gemv_fast", "fused_latent", "expert_fast")
+COUNTERS = ("fused_decode", "fused_residual", "fused_prefill", "flushed", "refused", "deltanet", "launches", "ext_calls", "gemv_fast", "fused_latent", "expert_fast", "fused_norm_rope")
 EXPORTS = (
     "silvann_silicon_family_get", "silvann_b200_last_error", "silvann_b200_counters_read", "silvann_b200_device_status",
     "silvann_b200_decode", "silvann_b200_decode_noalloc", "silvann_b200_merge", "silvann_b200_finish", "silvann_b200_plan_create",

@@ -139,3 +139,41 @@ def test_weight_path_doors(cuda, fam, golden):
     one_ulp(host_bits(h), g["wp_nr_h"], "the norm of rmsnorm_rotate")
     want = from_bits(g["wp_nr_hrot"], 0)
     assert np.abs(from_bits(host_bits(hrot), 0) - want).max() <= 2e-3 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("positions,heads,n,rot,x_stride", [(1, 16, 128, 64, 256), (1, 2, 256, 64, 256), (40, 4, 128, 128, 128), (7, 3, 64, 32, 80), (3, 2, 2048, 64, 2048)])
+def test_norm_then_rope_over_the_same_rows_is_one_kernel_with_the_two_doors_bits(cuda, fam, positions, heads, n, rot, x_stride):
+    """A mixer norms every head's row (rmsnorm_rows) and turns it in place (rope_rows): the pair is answered by one kernel,
+    and its bits are those of the two doors run one after the other (a wait between them makes each run as worded)."""
+    from silvann_b200 import ext
+    rng = np.random.default_rng(positions * 100 + heads)
+    rows = positions * heads
+    x = cuda.from_numpy(rng.standard_normal((rows, x_stride)).astype(np.float16).view(np.int16)).cuda()
+    w = cuda.from_numpy((1.0 + 0.1 * rng.standard_normal(n)).astype(np.float16).view(np.int16)).cuda()
+    ang = rng.uniform(0, 6.28, (positions, rot // 2))
+    cs = cuda.from_numpy(np.concatenate([np.cos(ang), np.sin(ang)], 1).astype(np.float32)).cuda()
+    eps = C.c_float(1e-6)
+    # as worded: a wait after the norm runs it alone
+    want = cuda.zeros((rows, n), dtype=cuda.int16, device="cuda")
+    fam.nn.rmsnorm_rows(want.data_ptr(), x.data_ptr(), w.data_ptr(), n, rows, x_stride, n, eps, None)
+    assert fam.sys.compute_completed()
+    normed = want.clone()
+    fam.nn.rope_rows(want.data_ptr(), want.data_ptr(), cs.data_ptr(), positions, heads, n, heads * n, rot, None)
+    assert fam.sys.compute_completed()
+    # the pair as a mixer issues it
+    before = ext.counters()
+    got = cuda.zeros((rows, n), dtype=cuda.int16, device="cuda")
+    fam.nn.rmsnorm_rows(got.data_ptr(), x.data_ptr(), w.data_ptr(), n, rows, x_stride, n, eps, None)
+    fam.nn.rope_rows(got.data_ptr(), got.data_ptr(), cs.data_ptr(), positions, heads, n, heads * n, rot, None)
+    assert fam.sys.compute_completed()
+    after = ext.counters()
+    assert after["fused_norm_rope"] - before["fused_norm_rope"] == 1 and after["refused"] == before["refused"]
+    assert cuda.equal(got, want), "the fused pair's bits differ from the two doors'"
+    assert not cuda.equal(got, normed), "the turn was applied"
+    # a norm that nothing turns still runs, when the next door asks
+    alone = cuda.zeros((rows, n), dtype=cuda.int16, device="cuda")
+    other = cuda.zeros((rows, n), dtype=cuda.int16, device="cuda")
+    fam.nn.rmsnorm_rows(alone.data_ptr(), x.data_ptr(), w.data_ptr(), n, rows, x_stride, n, eps, None)
+    fam.nn.rope_rows(other.data_ptr(), normed.data_ptr(), cs.data_ptr(), positions, heads, n, heads * n, rot, None)   # not in place over the normed rows
+    assert fam.sys.compute_completed()
+    assert cuda.equal(alone, normed) and cuda.equal(other[:, :rot], want[:, :rot])      # (rope_rows writes the turned elements only)
