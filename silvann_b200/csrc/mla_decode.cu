@@ -145,12 +145,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             for (int i = 0; i < ML_BOXES; ++i) tma_load_2d(q_s + i * Cfg::Q_BOX_BYTES, &qmap, q_full, i * 64, 0);
         }
         const uint64_t pol = l2_policy_evict_first();
+        int last_t = -1, last_i = -1;                        /* lane 0: the last box asked for (tile, box) */
         for (int t = 0; t < nt; ++t) {
             if (lane == 0 && ok)
                 for (int i = 0; i < ML_BOXES; ++i) {
                     if (t > 0 && !mbar_wait(&empty[i], (t - 1) & 1, abort_flag, P.status)) { ok = false; break; }
                     mbar_expect_tx(&full[i], ML_BOX_BYTES);
                     tma_load_2d_hint(c_s + i * ML_BOX_BYTES, &cmap, &full[i], i * 64, (tile0 + t) * ML_BK, pol);
+                    last_t = t; last_i = i;
                 }
             __syncwarp();
             if (t + 1 < nt) {
@@ -161,6 +163,16 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                     if (off < end) asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
                 }
             }
+        }
+        /* a wait gave up somewhere in the block: the copies already asked for get a bounded chance to land before the
+         * block's memory is given back (a box's barrier has one phase a tile) */
+        if (lane == 0 && *abort_flag != 0u) {
+            for (int i = 0; i < ML_BOXES; ++i) {
+                const int asked = i <= last_i ? last_t + 1 : last_t;         /* tiles whose box i has been asked for */
+                if (asked > 0)
+                    for (uint32_t k = 0; k < (1u << 16) && !mbar_try_wait(&full[i], (asked - 1) & 1); ++k) {}
+            }
+            if (nt > 0) for (uint32_t k = 0; k < (1u << 16) && !mbar_try_wait(q_full, 0); ++k) {}
         }
     } else if (warp == 1) {
         /* ---------------- every MMA: S^T(t) as the boxes land, then — the weights written — the four blocks of O^T ------- */

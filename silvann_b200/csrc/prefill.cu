@@ -137,6 +137,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 return true;
             };
             bool ok = true;
+            int jv = 0;                                      /* value tiles asked for */
             for (int i = 0; ok && i < KST - 1 && jk < nt; ++i) ok = load_k();
             for (int j = 0; ok && j < nt; ++j) {
                 if (jk < nt && !load_k()) break;
@@ -146,6 +147,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
 #pragma unroll
                 for (int c = 0; c < Cfg::BOXES; ++c)
                     tma_load_2d(v_s + s * Cfg::KV_TILE_BYTES + c * Cfg::KV_BOX_BYTES, &vmap, &v_full[s], g * D + c * 64, j * PF_BN);
+                jv = j + 1;
+            }
+            /* a wait gave up somewhere in the block: the copies already asked for get a bounded chance to land before the
+             * block's memory is given back */
+            if (*abort_flag != 0u) {
+                for (int t = jk > KST ? jk - KST : 0; t < jk; ++t)
+                    for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(&k_full[t % KST], (t / KST) & 1); ++i) {}
+                for (int t = jv > VST ? jv - VST : 0; t < jv; ++t)
+                    for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(&v_full[t % VST], (t / VST) & 1); ++i) {}
             }
         }
     } else if (warp == 1) {

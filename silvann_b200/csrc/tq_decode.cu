@@ -165,7 +165,8 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         if (lane == 0 && nt > 0) {
             tma_prefetch_desc(&kmap); tma_prefetch_desc(&vmap);
             const uint64_t pol = l2_policy_evict_first();
-            for (int it = 0; it < nt; ++it) {
+            int issued = 0;
+            for (int it = 0; it < nt; ++it, ++issued) {
                 const int s = it % Cfg::STAGES;
                 if (it >= Cfg::STAGES && !mbar_wait(&empty[s], ((it / Cfg::STAGES) - 1) & 1, abort_flag, P.status)) break;
                 const int pos0 = (tile_begin + it) * BT;
@@ -178,6 +179,11 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                 for (int c = 0; c < Cfg::BOXES; ++c)
                     tma_load_2d_hint(st + Cfg::TILE + c * (BT * Cfg::BOX), &vmap, &full[s], kvh * Cfg::RB + c * Cfg::BOX, pos0, pol);
             }
+            /* a wait gave up somewhere in the block: the copies already asked for get a bounded chance to land before the
+             * block's memory is given back */
+            if (*abort_flag != 0u)
+                for (int it = issued > Cfg::STAGES ? issued - Cfg::STAGES : 0; it < issued; ++it)
+                    for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(&full[it % Cfg::STAGES], (it / Cfg::STAGES) & 1); ++i) {}
         }
     } else {
         /* ---- consumers.  For k-step kk this lane's four contraction slots are elements t4·DH/4 + 4kk .. +3 of its head
