@@ -23,7 +23,8 @@ HERE = Path(__file__).resolve().parent
 PORT = HERE / "liboracle.so"
 REF_DIR = HERE / "_ref"
 REF = REF_DIR / "libsilvann_x86_avx2.so"
-REFERENCE_TREE = Path(os.environ.get("SILVANN_REFERENCE", "/root/reference"))
+# where the reference tree is mounted: SILVANN_REFERENCE, else a directory named "reference" beside this repository's own
+REFERENCE_TREE = Path(os.environ.get("SILVANN_REFERENCE") or HERE.parent.parent / "reference")
 
 
 def build_port(force: bool = False) -> Path:
