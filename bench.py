@@ -5,7 +5,7 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
            bench.py --gpus N --steps K --warmup W
 
-Headline (one JSON line on rank 0): `decode attn KV GB/s` on BASELINE configuration 3 — batched paged decode of 32
+Headline (one JSON line on rank 0): `decode attn KV GB/s` on configuration 3 of the path's five — batched paged decode of 32
 sequences with lengths uniform in [1,024, 100,000], 16 query heads on 2 kv heads, head_dim 256, bf16, 256-position
 pages in a randomly permuted pool, int32 page table.  A step is one pass of the fused paged-decode kernel over the
 whole batch.  Each GPU holds its own batch (sequences are independent: no collective on the data path), so N GPUs

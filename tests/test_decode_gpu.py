@@ -75,7 +75,7 @@ def test_decode_is_bit_repeatable(cuda):
 
 
 def test_config1_through_the_door_pair_against_the_reference(cuda, fam, port, reference):
-    """BASELINE configuration 1, driven exactly as (nn__attention__decode q k v scores out 16 4 128 0 8192)."""
+    """Configuration 1 (16 query heads on 4 kv heads of 128, 8,192 positions, fp16), driven exactly as (nn__attention__decode q k v scores out 16 4 128 0 8192)."""
     w = workloads.config1()
     want_bits = reference.decode(w.q, w.k, w.v, 16, 4, 128, 8192) if reference is not None else port.decode(w.q, w.k, w.v, 16, 4, 128, 8192, 0)[0]
     want = from_bits(want_bits, 0)
