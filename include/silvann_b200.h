@@ -293,7 +293,7 @@ const silvann_b200_family* silvann_silicon_family_get(uint32_t abi_version);
 #define SILVANN_B200_COUNTER_GEMV_FAST       8   /* coded matrix-vector doors answered by the tensor-core kernel */
 #define SILVANN_B200_COUNTER_FUSED_LATENT     9   /* scores_grouped + softmax_rows + mix over one latent answered by one kernel */
 #define SILVANN_B200_COUNTER_EXPERT_FAST     10   /* expert-major GEMM doors answered by the tcgen05 kernel */
-#define SILVANN_B200_COUNTER_FUSED_NORM_ROPE 11   /* rmsnorm_rows + rope_rows over the same rows answered by one kernel */
+#define SILVANN_B200_COUNTER_FUSED_NORM_ROPE 11   /* neighbours of attention answered two doors a kernel: rmsnorm_rows + rope_rows over the same rows, attention_gate_rows + hadamard_rotate */
 #define SILVANN_B200_COUNTERS                12
 
 const char* silvann_b200_last_error(void);

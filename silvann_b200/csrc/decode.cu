@@ -18,6 +18,8 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "tensormap.cuh"
+#include "exchange.cuh"
+#include "residual.cuh"
 #include <atomic>
 #include <mutex>
 #include <stdio.h>
@@ -55,6 +57,9 @@ struct DecodeParams {
     uint32_t slot_floats;
     uint32_t l1, l1_groups, l2_slot0, l1_ticket0;   /* one-sequence calls with many splits meet in two levels: l1 splits a first-level group (0: one level) */
     float scale_log2;
+    /* with an exchange (xf.members > 0; one sequence, its splits meeting through scratch): the block that holds a head block's
+     * whole residual pushes it to the members and folds theirs — this card's share of a KV range split, finished in the launch */
+    XfParams xf;
 };
 
 
@@ -545,6 +550,61 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
             continue;
         }
         const size_t hq = (size_t)seq * P.q_heads + head0 + h;
+        if (P.xf.members != 0u) {
+            /* ---- the exchange step in the same launch: this card's residual of the head (m, l, these four sums) goes to every
+             * member as tagged words, the members' words are polled (bounded) where they land in this card's own memory, and the
+             * ranges are folded in member order with the merge door's arithmetic and finished — the bits of the separate
+             * exchange kernel, without its launch ---- */
+            const XfParams& X = P.xf;
+            const uint32_t parity = X.gen & 1u;
+            const size_t wbase = hq * (size_t)(D + 2);
+            const float m_ln = m * SV_LN2;
+            for (uint32_t mm = 0; mm < X.members; ++mm) {
+                uint2* slot = xf_slot(X.peer[mm], parity, X.index, X.slot_words, X.members) + wbase;
+                xf_store2(slot + 2 + e, __float_as_uint(acc.x), __float_as_uint(acc.y), X.gen);
+                xf_store2(slot + 4 + e, __float_as_uint(acc.z), __float_as_uint(acc.w), X.gen);
+                if (e == 0) xf_store2(slot, __float_as_uint(m_ln), __float_as_uint(l), X.gen);
+            }
+            float tm = 0.f, tl = 0.f;
+            float4 ta = make_float4(0.f, 0.f, 0.f, 0.f);
+            unsigned long long t0 = 0ull;
+            bool ok = true;
+            for (uint32_t sm_ = 0; sm_ < X.members; ++sm_) {
+                float bm_ = m_ln, bl_ = l;
+                float4 ba = acc;
+                if (sm_ != X.index) {
+                    const uint2* from = xf_slot(X.peer[X.index], parity, sm_, X.slot_words, X.members) + wbase;
+                    const uint4 w0 = xf_load2(from), w1 = xf_load2(from + 2 + e), w2 = xf_load2(from + 4 + e);
+                    uint32_t pay[6] = {w0.x, w0.z, w1.x, w1.z, w2.x, w2.z};
+                    const uint32_t tag[6] = {w0.y, w0.w, w1.y, w1.w, w2.y, w2.w};
+                    const uint2* at[6] = {from, from + 1, from + 2 + e, from + 3 + e, from + 4 + e, from + 5 + e};
+#pragma unroll
+                    for (int u = 0; u < 6; ++u)
+                        if (tag[u] != X.gen && ok) ok = xf_await(at[u], X.gen, X.wait_ns, t0, pay[u]);
+                    bm_ = __uint_as_float(pay[0]); bl_ = __uint_as_float(pay[1]);
+                    ba = make_float4(__uint_as_float(pay[2]), __uint_as_float(pay[3]), __uint_as_float(pay[4]), __uint_as_float(pay[5]));
+                }
+                if (sm_ == 0u) { tm = bm_; tl = bl_; ta = ba; }
+                else {
+                    float fa, fb;
+                    merge_scalars(tm, tl, bm_, bl_, fa, fb);
+                    ta.x = merge_element(ta.x, fa, ba.x, fb); ta.y = merge_element(ta.y, fa, ba.y, fb);
+                    ta.z = merge_element(ta.z, fa, ba.z, fb); ta.w = merge_element(ta.w, fa, ba.w, fb);
+                }
+            }
+            if (!ok) { if (P.status) atomicOr(P.status, SV_STATUS_TIMEOUT); continue; }     /* a member never came: said, and nothing written */
+            if (P.o) {
+                uint16_t* op = (uint16_t*)P.o + hq * D + e;
+                op[0] = E::from_float(ta.x / tl, hit); op[1] = E::from_float(ta.y / tl, hit);
+                op[2] = E::from_float(ta.z / tl, hit); op[3] = E::from_float(ta.w / tl, hit);
+            }
+            if (P.res) {
+                float* ro = P.res + hq * (D + 2);
+                ro[2 + e] = ta.x; ro[3 + e] = ta.y; ro[4 + e] = ta.z; ro[5 + e] = ta.w;
+                if (e == 0) { ro[0] = tm; ro[1] = tl; }
+            }
+            continue;
+        }
         if (P.o) {
             uint16_t* op = (uint16_t*)P.o + hq * D + e;
             op[0] = E::from_float(acc.x / l, hit); op[1] = E::from_float(acc.y / l, hit);
@@ -743,6 +803,8 @@ cudaError_t decode_launch(const DecodeCall& c) {
     P.slot_floats = c.head_dim + 2u;
     P.l1 = 0; P.l1_groups = 0; P.l2_slot0 = 0; P.l1_ticket0 = 0;
     P.scale_log2 = (1.0f / sqrtf((float)c.head_dim)) * SV_LOG2E;
+    memset(&P.xf, 0, sizeof P.xf);
+    if (c.xf && (c.items || c.seqs != 1u || c.page_table)) return cudaErrorNotSupported;     /* the exchange step rides on one contiguous sequence's meeting of splits */
     uint32_t blocks, cluster = 1u;
     /* one-sequence calls are a few microseconds long and often follow each other (a layer after a layer): they are launched
      * as programmatic dependents; SILVANN_B200_DECODE_PDL=0 turns that off */
@@ -759,7 +821,11 @@ cudaError_t decode_launch(const DecodeCall& c) {
         if (ns > 1024u) ns = 1024u;
         const uint32_t chunk = (tiles + ns - 1) / ns;
         ns = (tiles + chunk - 1) / chunk;
-        if (c.nsplit == 0 || splits_forced) cluster = decode_cluster_for(tiles, c.kv_heads * hb, device_sm_count(), &ns);
+        if ((c.nsplit == 0 || splits_forced) && !c.xf) cluster = decode_cluster_for(tiles, c.kv_heads * hb, device_sm_count(), &ns);
+        if (c.xf) {                                              /* (a cache of one split has no meeting to ride on: the caller exchanges in a launch of its own) */
+            if (ns < 2u) return cudaErrorNotSupported;
+            P.xf = *static_cast<const XfParams*>(c.xf);
+        }
         if ((uint64_t)(ns / cluster) * c.kv_heads * hb > c.scratch.slots || (uint64_t)c.kv_heads * hb > c.scratch.tickets_n) return cudaErrorInvalidValue;
         P.nsplit = ns; blocks = ns * c.kv_heads * hb;
         /* many splits of few groups (one long sequence, a kv head or two a card): the last arrival would merge them all on one
@@ -920,6 +986,7 @@ int decode_launch_static(const DecodeCall& c0, uint32_t* detail) {
     P.slot_floats = c.head_dim + 2u;
     P.l1 = 0; P.l1_groups = 0; P.l2_slot0 = 0; P.l1_ticket0 = 0;
     P.scale_log2 = (1.0f / sqrtf((float)c.head_dim)) * SV_LOG2E;
+    memset(&P.xf, 0, sizeof P.xf);
     const uint32_t blocks = ns * lanes;
     const int nht = hpb == 8 ? 1 : 2;
     e = cudaErrorInvalidValue;

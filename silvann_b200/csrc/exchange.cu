@@ -363,6 +363,15 @@ SV_EXPORT int silvann_b200_exchange_deposit(silvann_b200_exchange* x, uint32_t m
     return SILVANN_B200_OK;
 }
 
+/* for tier.cu: a launch of another kernel that does the exchange step itself (the decode kernel's last block) — the members'
+ * buffers, this exchange's generation and the wait's limit; `advance` counts the exchange once that launch is queued */
+int sv_exchange_begin(silvann_b200_exchange* x, uint32_t wait_ms, uint64_t bytes, sv::XfParams* P) {
+    if (!x || !P) return sv_ext_fail(SILVANN_B200_E_ARGUMENT, "exchange: a null operand");
+    if (bytes > x->slot_bytes) return sv_ext_fail(SILVANN_B200_E_ARGUMENT, "exchange: a residual of %llu bytes and a slot holds %llu", (unsigned long long)bytes, (unsigned long long)x->slot_bytes);
+    return xf_params(x, "tier_decode_exchange", wait_ms, P);
+}
+void sv_exchange_advance(silvann_b200_exchange* x) { x->gen += 1u; }
+
 /* for tier.cu: the same launch from inside the library */
 int sv_exchange_merge_finish(silvann_b200_exchange* x, void* o, float* res, const float* res_local, uint64_t q_heads, uint64_t head_dim, int dtype,
                              sv_fault* over, uint32_t wait_ms, void* stream) {

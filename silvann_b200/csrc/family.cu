@@ -55,7 +55,7 @@ static bool fuse_enabled() {
 }
 
 /* ---- the deferred first door of a pair, per device ---- */
-enum PendingKind { NONE = 0, SCORES, WEIGHTS, CAUSAL_RAW, CAUSAL_SOFT, WEIGHTS_ROWS, WEIGHTS_TQ, GROUPED_RAW, GROUPED_SOFT, NORM_ROWS };
+enum PendingKind { NONE = 0, SCORES, WEIGHTS, CAUSAL_RAW, CAUSAL_SOFT, WEIGHTS_ROWS, WEIGHTS_TQ, GROUPED_RAW, GROUPED_SOFT, NORM_ROWS, GATE_ROWS };
 struct Pending {
     int kind;
     float* p; float* res; const uint16_t* q; const uint16_t* k;      /* WEIGHTS_TQ: k is the key codes */
@@ -63,6 +63,7 @@ struct Pending {
     const uint16_t* scales; uint64_t width;                          /* WEIGHTS_TQ only: the key rows' scales and the code width */
     /* NORM_ROWS (rmsnorm_rows recorded in case rope_rows over the same rows follows): q = x, k = w, d = n, rows, first = x_stride, length = o_stride */
     uint16_t* o16; float eps; unsigned int* over;
+    /* GATE_ROWS (attention_gate_rows recorded in case hadamard_rotate of its answers follows): o16 = o, q = att, k = qg, qh = heads, d = head_dim */
 };
 static Pending g_pending[DEVICES_MAX];
 static std::mutex g_pending_lock[DEVICES_MAX];
@@ -88,6 +89,7 @@ static void run_pending_locked(Pending& pd) {
             check("attention_scores_grouped", sv::scores_launch(x.p, x.q, x.k, x.qh, x.kvh, x.d, x.length, 2, nullptr, 0));
             check("attention_softmax_rows", sv::softmax_rows_launch(x.p, x.qh, x.length, 0));
             break;
+        case GATE_ROWS:   check("attention_gate_rows", sv::attention_gate_rows_launch(x.o16, x.q, x.k, x.qh, x.d, x.over, 0)); break;
         case NORM_ROWS:   check("rmsnorm_rows", sv::rmsnorm_rows_launch(x.o16, x.q, x.k, x.d, x.rows, x.first, x.length, x.eps, x.over, 0)); break;
         case WEIGHTS_TQ:  check("attention_weights_tq", sv::tq_weights_launch(x.p, x.res, x.q, (const uint8_t*)x.k, x.scales, x.qh, x.kvh, x.d, x.length, x.width, x.rows, 0)); break;
         default: return;
@@ -552,7 +554,19 @@ static void d_rope_angles_axial_rows(float* cs, const sv_u32* positions, float t
 }
 static void d_attention_gate_rows(sv_h16* o, const sv_h16* att, const sv_h16* qg, sv_u64 heads, sv_u64 head_dim, sv_fault* over) {
     flush();
-    if (heads * head_dim) check("attention_gate_rows", sv::attention_gate_rows_launch(o, att, qg, heads, head_dim, over, 0));
+    if (heads * head_dim == 0) return;
+    /* a mixer gates the answers and then rotates them for the output projection: recorded, and one kernel answers both if
+     * hadamard_rotate of these answers is what follows; any other door first runs this one as worded */
+    const int dev = current_device();
+    if (fuse_enabled() && dev >= 0 && dev < DEVICES_MAX) {
+        std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+        Pending pd;
+        memset(&pd, 0, sizeof pd);
+        pd.kind = GATE_ROWS; pd.o16 = o; pd.q = att; pd.k = qg; pd.qh = heads; pd.d = head_dim; pd.over = over;
+        g_pending[dev] = pd;
+        return;
+    }
+    check("attention_gate_rows", sv::attention_gate_rows_launch(o, att, qg, heads, head_dim, over, 0));
 }
 
 /* ---- the TurboQuant-coded tiers (tq.cu) ---- */
@@ -629,14 +643,41 @@ static void d_attention_residual_mix_tq(float* res, const float* p, const sv_u8*
 
 /* ---- the weight path's doors a mixer verb cannot run without, as worded (tq.cu) ---- */
 static void d_hadamard_rotate(sv_h16* out, const sv_h16* in, const sv_h16* sign, sv_u64 n, sv_fault* over) {
-    flush();
     const bool apart = !(out < in + n && in < out + n);           /* a lane reads the whole block it writes into */
     const bool shaped = n != 0 && (n < 512 || (n % 512) % 128 == 0);   /* past the whole blocks: a 256 and a 128, or a read past n */
+    {
+        const int dev = current_device();
+        if (dev >= 0 && dev < DEVICES_MAX) {
+            std::lock_guard<std::mutex> hold(g_pending_lock[dev]);
+            Pending& pd = g_pending[dev];
+            /* the answers just gated, rotated: one kernel (the rotated row must lie apart from everything the gate reads) */
+            if (pd.kind == GATE_ROWS && in == pd.o16 && n == pd.qh * pd.d && apart && shaped && over == pd.over
+                && !(out < pd.q + n && pd.q < out + n) && !(out < pd.k + 2 * n && pd.k < out + n)) {
+                const Pending y = pd;
+                pd.kind = NONE;
+                const cudaError_t e = sv::gate_rotate_launch(out, y.o16, y.q, y.k, sign, y.qh, y.d, over, 0);
+                if (e == cudaSuccess) { bump(SILVANN_B200_COUNTER_FUSED_NORM_ROPE); return; }
+                (void)cudaGetLastError();
+                pd = y;
+            }
+            run_pending_locked(pd);
+        }
+    }
     if (!apart || !shaped) { launch_refused("hadamard_rotate", cudaSuccess); return; }
     check("hadamard_rotate", sv::hadamard_rotate_launch(out, in, sign, n, over, 0));
 }
 static void d_rmsnorm_rotate(sv_h16* rot, sv_h16* o, const sv_h16* x, const sv_h16* w, const sv_h16* sign, sv_u64 n, float eps, sv_fault* over) {
-    d_rmsnorm(o, x, w, n, eps, over);                             /* nn's definition: the two doors, one after the other */
+    /* nn's definition: the two doors, one after the other.  One kernel with their bits where the row is the rotation door's
+     * shape and the three rows lie apart (every block reads all of x while others write o) */
+    const bool apart = !(rot < o + n && o < rot + n) && !(o < x + n && x < o + n) && !(rot < x + n && x < rot + n);
+    const bool shaped = n != 0 && (n < 512 || (n % 512) % 128 == 0);
+    if (fuse_enabled() && apart && shaped) {
+        flush();
+        const cudaError_t e = sv::rmsnorm_rotate_launch(rot, o, x, w, sign, n, eps, over, 0);
+        if (e == cudaSuccess) return;
+        (void)cudaGetLastError();
+    }
+    d_rmsnorm(o, x, w, n, eps, over);
     d_hadamard_rotate(rot, o, sign, n, over);
 }
 static bool gemv_fast_off() {

@@ -48,6 +48,8 @@ struct DecodeCall {
     unsigned int* over;         /* device fault word or null */
     DecodeScratch scratch;
     cudaStream_t stream;
+    const void* xf;             /* an XfParams (exchange.cuh) or null: the exchange step of a KV range split done in this launch — one contiguous
+                                   sequence of at least two splits, else cudaErrorNotSupported and the caller exchanges in a launch of its own */
 };
 
 /* Whether the TMA kernel can take these shapes and addresses (head_dim 64/128/256, 16-byte aligned q/k/v, rows a
@@ -147,6 +149,12 @@ cudaError_t tq_encode_rows_launch(uint8_t* codes, uint16_t* scales, const uint16
 cudaError_t tq_weights_launch(float* p, float* res, const uint16_t* q, const uint8_t* codes, const uint16_t* scales, uint64_t qh, uint64_t kvh,
                               uint64_t d_head, uint64_t length, uint64_t d, uint64_t rows, cudaStream_t st);
 cudaError_t hadamard_rotate_launch(uint16_t* out, const uint16_t* in, const uint16_t* sign, uint64_t n, unsigned int* over, cudaStream_t st);
+/* attention_gate_rows then hadamard_rotate over the gated answers in one kernel, the bits of the two doors in turn */
+cudaError_t gate_rotate_launch(uint16_t* rot, uint16_t* o, const uint16_t* att, const uint16_t* qg, const uint16_t* sign, uint64_t heads, uint64_t head_dim,
+                               unsigned int* over, cudaStream_t st);
+/* the norm of a row and its rotation in one kernel, the bits of the two doors in turn */
+cudaError_t rmsnorm_rotate_launch(uint16_t* rot, uint16_t* o, const uint16_t* x, const uint16_t* w, const uint16_t* sign, uint64_t n, float eps,
+                                  unsigned int* over, cudaStream_t st);
 cudaError_t tq_gemv_groups_launch(uint16_t* out, const void* groups /* sv_tq_groups */, uint64_t w_room, uint64_t l_room, const uint16_t* x,
                                   uint64_t cols, unsigned int* over, cudaStream_t st);
 /* ---- the expert-major GEMM: a coded matrix over several rows of x named by pairs (expert.cu) ---------------------- */

@@ -14,6 +14,7 @@
 #include "../../include/silvann_b200.h"
 #include "common.cuh"
 #include "kernels.h"
+#include "exchange.cuh"
 #include <new>
 #include <stdio.h>
 #include <string.h>
@@ -24,6 +25,8 @@
 
 int sv_ext_fail(int code, const char* fmt, ...);      /* ext.cu: records the message for silvann_b200_last_error */
 struct silvann_b200_exchange;
+int sv_exchange_begin(silvann_b200_exchange* x, uint32_t wait_ms, uint64_t bytes, sv::XfParams* P);     /* exchange.cu */
+void sv_exchange_advance(silvann_b200_exchange* x);
 int sv_exchange_merge_finish(silvann_b200_exchange* x, void* o, float* res, const float* res_local, uint64_t q_heads, uint64_t head_dim, int dtype,
                              sv_fault* over, uint32_t wait_ms, void* stream);      /* exchange.cu */
 
@@ -112,12 +115,12 @@ SV_EXPORT int silvann_b200_tier_stats(const silvann_b200_tier* t, uint64_t* h2d_
 
 /* One piece of the cache into `res` (m, l, acc per head), enqueued on `st`. */
 static cudaError_t piece(const silvann_b200_tier* t, void* o, float* res, const void* q, const void* k, const void* v, uint64_t length, sv_fault* over,
-                         cudaStream_t st) {
+                         cudaStream_t st, const sv::XfParams* xf = nullptr) {
     sv::DecodeCall c;
     memset(&c, 0, sizeof c);
     c.o = o; c.res = res; c.q = q; c.k = k; c.v = v; c.kv_rows = length; c.seqs = 1;
     c.q_heads = t->q_heads; c.kv_heads = t->kv_heads; c.head_dim = t->head_dim; c.length = (uint32_t)length;
-    c.dtype = t->dtype; c.over = over; c.stream = st;
+    c.dtype = t->dtype; c.over = over; c.stream = st; c.xf = xf;
     if (!sv::decode_fits(c)) return cudaErrorInvalidValue;
     cudaError_t e = sv::decode_device_scratch(&c.scratch);
     if (e != cudaSuccess) return e;
@@ -138,6 +141,18 @@ static int tier_decode(silvann_b200_tier* t, silvann_b200_exchange* x, uint32_t 
          * with no running residual and no finishing launch */
         SV_TRY(piece(t, o, res, q, k_dev, v_dev, dev_len, over, st), "card tier");
         return SILVANN_B200_OK;
+    }
+    if (host_len == 0 && x) {
+        /* everything is on the card and the other members hold the rest of the range: the decode kernel's last block of a head
+         * block pushes the residual to the members, folds theirs and writes the answer — the exchange step without a launch of
+         * its own.  A cache too short to be split has no such block: it takes the two launches below. */
+        sv::XfParams P;
+        const int rc = sv_exchange_begin(x, wait_ms, (uint64_t)t->q_heads * (t->head_dim + 2u) * sizeof(float), &P);
+        if (rc != SILVANN_B200_OK) return rc;
+        e = piece(t, o, res, q, k_dev, v_dev, dev_len, over, st, &P);
+        if (e == cudaSuccess) { sv_exchange_advance(x); return SILVANN_B200_OK; }
+        (void)cudaGetLastError();
+        if (e != cudaErrorNotSupported) return sv_ext_fail(SILVANN_B200_E_CUDA, "tier_decode: %s: %s", "card tier with the exchange", cudaGetErrorString(e));
     }
     const uint64_t nchunks = (host_len + t->chunk - 1) / t->chunk;
     /* queue the first copies before any compute so that they run under the card tier's kernel */

@@ -242,6 +242,89 @@ __global__ void __launch_bounds__(256) hadamard_rotate_kernel(uint16_t* out, con
     if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
 }
 
+/* rmsnorm_rotate (the norm of a row, then its rotation: nn's definition is the two doors one after the other) as ONE kernel: a
+ * block a rotation block of the row.  Every block folds the whole row's sum of squares itself, with the norm door's own block
+ * size and order (so the scale has the norm door's bits), norms its block into shared memory and `o`, and rotates it with the
+ * rotation door's four running sums. */
+__global__ void __launch_bounds__(256) rmsnorm_rotate_kernel(uint16_t* rot, uint16_t* o, const uint16_t* x, const uint16_t* w, const uint16_t* sign, uint64_t n,
+                                                             float eps, unsigned int* over) {
+    __shared__ float sh[8];
+    __shared__ uint16_t seg[512];
+    bool hit = false;
+    float part = 0.f;
+    for (uint64_t i = threadIdx.x; i < n; i += blockDim.x) { const float v = H::to_float(x[i]); part += v * v; }
+    for (int s = 16; s > 0; s >>= 1) part += __shfl_xor_sync(0xffffffffu, part, s);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = part;
+    __syncthreads();
+    float sum = 0.f;
+    for (unsigned k = 0; k < blockDim.x / 32; ++k) sum += sh[k];
+    const float scale = 1.0f / sqrtf(sum / (float)n + eps);
+    /* this block's rotation block [a, a + b): the whole 512s, then a 256 and a 128 of what is left; a row under 512 is one block */
+    const uint64_t whole = n < 512 ? 0 : (n / 512) * 512, rest = n - whole;
+    uint64_t a = 0, b = n;
+    if (n >= 512) {
+        if (blockIdx.x < whole / 512) { a = (uint64_t)blockIdx.x * 512; b = 512; }
+        else if (blockIdx.x == whole / 512 && rest >= 256) { a = whole; b = 256; }
+        else { a = whole + (rest >= 256 ? 256 : 0); b = 128; }
+    }
+    for (uint64_t i = threadIdx.x; i < b; i += blockDim.x) {
+        const uint16_t h = H::from_float((H::to_float(x[a + i]) * scale) * H::to_float(w[a + i]), hit);
+        seg[i] = h;
+        o[a + i] = h;
+    }
+    __syncthreads();
+    for (uint64_t r = threadIdx.x; r < b; r += blockDim.x) {
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        uint64_t c = 0;
+        for (; c + 4 <= b; c += 4)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float v = H::to_float(seg[c + q]) * H::to_float(sign[c + q]);
+                s[q] += (__popcll(r & (c + q)) & 1) ? -v : v;
+            }
+        for (; c < b; ++c) { const float v = H::to_float(seg[c]) * H::to_float(sign[c]); s[0] += (__popcll(r & c) & 1) ? -v : v; }
+        rot[a + r] = H::from_float(((s[0] + s[1]) + (s[2] + s[3])) / sqrtf((float)b), hit);
+    }
+    if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
+}
+
+/* attention_gate_rows followed by hadamard_rotate over the gated answers, as ONE kernel: a block a rotation block — the gate door's
+ * arithmetic element for element into shared memory and `o`, then the rotation door's four running sums over those halves. */
+__global__ void __launch_bounds__(256) gate_rotate_kernel(uint16_t* rot, uint16_t* o, const uint16_t* att, const uint16_t* qg, const uint16_t* sign,
+                                                          uint64_t heads, uint64_t head_dim, unsigned int* over) {
+    __shared__ uint16_t seg[512];
+    bool hit = false;
+    const uint64_t n = heads * head_dim, whole = n < 512 ? 0 : (n / 512) * 512, rest = n - whole;
+    uint64_t a = 0, b = n;
+    if (n >= 512) {
+        if (blockIdx.x < whole / 512) { a = (uint64_t)blockIdx.x * 512; b = 512; }
+        else if (blockIdx.x == whole / 512 && rest >= 256) { a = whole; b = 256; }
+        else { a = whole + (rest >= 256 ? 256 : 0); b = 128; }
+    }
+    for (uint64_t k = threadIdx.x; k < b; k += blockDim.x) {
+        const uint64_t i = a + k, h = i / head_dim, e = i - h * head_dim;
+        const float v = H::to_float(qg[h * 2 * head_dim + head_dim + e]);
+        const uint16_t gate = H::from_float(1.0f / (1.0f + expf(-v)), hit);
+        const uint16_t y = H::from_float(H::to_float(att[i]) * H::to_float(gate), hit);
+        seg[k] = y;
+        o[i] = y;
+    }
+    __syncthreads();
+    for (uint64_t r = threadIdx.x; r < b; r += blockDim.x) {
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        uint64_t c = 0;
+        for (; c + 4 <= b; c += 4)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float v = H::to_float(seg[c + q]) * H::to_float(sign[c + q]);
+                s[q] += (__popcll(r & (c + q)) & 1) ? -v : v;
+            }
+        for (; c < b; ++c) { const float v = H::to_float(seg[c]) * H::to_float(sign[c]); s[0] += (__popcll(r & c) & 1) ? -v : v; }
+        rot[a + r] = H::from_float(((s[0] + s[1]) + (s[2] + s[3])) / sqrtf((float)b), hit);
+    }
+    if (hit && over) atomicOr(over, SV_FAULT_OVERFLOW);
+}
+
 struct GemvGroups { uint64_t codes[12], luts[12], rows[12], d[12], out_at[12], count; };
 
 __global__ void __launch_bounds__(128) tq_gemv_groups_kernel(uint16_t* out, GemvGroups g, uint64_t w_room0, uint64_t l_room0, const uint16_t* x,
@@ -319,6 +402,27 @@ cudaError_t tq_residual_mix_launch(float* res, const float* p, const uint8_t* co
     return cudaGetLastError();
 }
 
+/* n as the rotation door takes it: under 512, or what is left after the whole 512s is 0, 128, 256 or 384 */
+cudaError_t rmsnorm_rotate_launch(uint16_t* rot, uint16_t* o, const uint16_t* x, const uint16_t* w, const uint16_t* sign, uint64_t n, float eps,
+                                  unsigned int* over, cudaStream_t st) {
+    if (n == 0 || (n >= 512 && (n % 512) % 128 != 0)) return cudaErrorInvalidValue;
+    const uint64_t rest = n % 512;
+    const unsigned blocks = n < 512 ? 1u : (unsigned)(n / 512 + (rest >= 256 ? 1 : 0) + ((rest % 256) >= 128 ? 1 : 0));
+    const unsigned threads = n >= 2048 ? 256u : (n >= 512 ? 128u : 64u);   /* the norm door's own block: the same partial sums in the same order */
+    rmsnorm_rotate_kernel<<<blocks, threads, 0, st>>>(rot, o, x, w, sign, n, eps, over);
+    note_launch(1);
+    return cudaGetLastError();
+}
+cudaError_t gate_rotate_launch(uint16_t* rot, uint16_t* o, const uint16_t* att, const uint16_t* qg, const uint16_t* sign, uint64_t heads, uint64_t head_dim,
+                               unsigned int* over, cudaStream_t st) {
+    const uint64_t n = heads * head_dim;
+    if (n == 0 || (n >= 512 && (n % 512) % 128 != 0)) return cudaErrorInvalidValue;
+    const uint64_t rest = n % 512;
+    const unsigned blocks = n < 512 ? 1u : (unsigned)(n / 512 + (rest >= 256 ? 1 : 0) + ((rest % 256) >= 128 ? 1 : 0));
+    gate_rotate_kernel<<<blocks, 256, 0, st>>>(rot, o, att, qg, sign, heads, head_dim, over);
+    note_launch(1);
+    return cudaGetLastError();
+}
 cudaError_t hadamard_rotate_launch(uint16_t* out, const uint16_t* in, const uint16_t* sign, uint64_t n, unsigned int* over, cudaStream_t st) {
     hadamard_rotate_kernel<<<tq_grid((n + 255) / 256), 256, 0, st>>>(out, in, sign, n, over);
     note_launch(1);

@@ -170,3 +170,56 @@ def test_coded_projection_and_sum_in_one_launch(cuda, fam, port, members, index,
     diff = np.abs(from_bits(host_bits(want), 0) - from_bits(to_bits(s, 0), 0))
     assert diff.max() <= 4e-3, diff.max()
     x.close()
+
+
+@pytest.mark.parametrize("members,index,length,dtype", [(2, 0, 40000, 1), (2, 1, 131072, 1), (4, 2, 9000, 0), (2, 0, 3000, 1), (2, 1, 100, 0)])
+def test_a_range_share_and_its_exchange_in_one_launch(cuda, members, index, length, dtype):
+    """A member's share of a KV range split with every position on the card: the decode kernel's last block does the exchange
+    step itself (one launch), and the answer has the bits of the decode followed by the exchange kernel wherever the two
+    meet their splits the same way (long shares; a short share's separate decode meets in a cluster, and a share of one split
+    has no meeting to ride on and takes the two launches)."""
+    qh, kvh, d = 8, 1, 128
+    rng = np.random.default_rng(length + index)
+    mk = lambda shape, s: to_bits((rng.standard_normal(shape) * s).astype(np.float32), dtype)
+    q, k, v = dev(cuda, mk((qh, d), 0.5)), dev(cuda, mk((length, kvh, d), 0.5)), dev(cuda, mk((length, kvh, d), 0.5))
+    parts = residuals(rng, members, qh, d)
+    t_parts = [dev(cuda, p) for p in parts]
+    tier = ext.Tier(qh, kvh, d, dtype)
+    # apart: the share's residual, then the exchange kernel
+    mine = cuda.zeros((qh, d + 2), dtype=cuda.float32, device="cuda")
+    tier.decode(None, mine, q, None, None, 0, k, v, length)
+    x1 = ext.Exchange(members, index, qh * (d + 2) * 4)
+    x1.connect_alone()
+    for m in range(members):
+        if m != index:
+            x1.deposit(m, t_parts[m], parts[m].nbytes)
+    o_want = cuda.zeros((qh, d), dtype=cuda.int16, device="cuda")
+    r_want = cuda.zeros((qh, d + 2), dtype=cuda.float32, device="cuda")
+    x1.merge_finish(o_want, r_want, mine, qh, d, dtype, wait_ms=200)
+    # together
+    x2 = ext.Exchange(members, index, qh * (d + 2) * 4)
+    x2.connect_alone()
+    for call in range(2):                                                  # twice: both parities of the slots
+        for m in range(members):
+            if m != index:
+                x2.deposit(m, t_parts[m], parts[m].nbytes)
+        o = cuda.full((qh, d), 0x1234, dtype=cuda.int16, device="cuda")
+        r = cuda.zeros((qh, d + 2), dtype=cuda.float32, device="cuda")
+        before = ext.counters()["launches"]
+        tier.decode_exchange(x2, o, r, q, None, None, 0, k, v, length, wait_ms=200)
+        cuda.cuda.synchronize()
+        launches = ext.counters()["launches"] - before
+        assert ext.device_status() == 0
+        assert launches == (2 if length <= 128 else 1), launches
+        if length >= 9000 or length <= 128:
+            assert cuda.equal(o, o_want) and cuda.equal(r, r_want), f"call {call}"
+        else:
+            got, want = from_bits(host_bits(o), dtype), from_bits(host_bits(o_want), dtype)
+            assert np.abs(got - want).max() <= 2e-3 * max(1.0, np.abs(want).max())
+    # a member that never comes: the wait runs out, nothing is written, the status says so
+    if length >= 9000:
+        o = cuda.full((qh, d), 0x1234, dtype=cuda.int16, device="cuda")
+        tier.decode_exchange(x2, o, None, q, None, None, 0, k, v, length, wait_ms=20)
+        cuda.cuda.synchronize()
+        assert ext.device_status() == B2TO and (o == 0x1234).all()
+    x1.close(); x2.close(); tier.close()

@@ -177,3 +177,58 @@ def test_norm_then_rope_over_the_same_rows_is_one_kernel_with_the_two_doors_bits
     fam.nn.rope_rows(other.data_ptr(), normed.data_ptr(), cs.data_ptr(), positions, heads, n, heads * n, rot, None)   # not in place over the normed rows
     assert fam.sys.compute_completed()
     assert cuda.equal(alone, normed) and cuda.equal(other[:, :rot], want[:, :rot])      # (rope_rows writes the turned elements only)
+
+
+@pytest.mark.parametrize("n", [128, 384, 512, 2048 + 384, 5120, 640])
+def test_rmsnorm_rotate_is_one_kernel_with_the_two_doors_bits(cuda, fam, n):
+    """rmsnorm_rotate is nn's rmsnorm followed by hadamard_rotate; here one kernel, and its two outputs must be the bits of the
+    two doors called one after the other."""
+    from silvann_b200 import ext
+    rng = np.random.default_rng(n)
+    x = cuda.from_numpy(rng.standard_normal(n).astype(np.float16).view(np.int16)).cuda()
+    w = cuda.from_numpy((1.0 + 0.1 * rng.standard_normal(n)).astype(np.float16).view(np.int16)).cuda()
+    sign = cuda.from_numpy(np.where(rng.random(512) < 0.5, -1.0, 1.0).astype(np.float16).view(np.int16)).cuda()
+    eps = C.c_float(1e-6)
+    o_want = cuda.zeros(n, dtype=cuda.int16, device="cuda")
+    r_want = cuda.zeros(n, dtype=cuda.int16, device="cuda")
+    fam.nn.rmsnorm(o_want.data_ptr(), x.data_ptr(), w.data_ptr(), n, eps, None)
+    fam.nn.hadamard_rotate(r_want.data_ptr(), o_want.data_ptr(), sign.data_ptr(), n, None)
+    assert fam.sys.compute_completed()
+    o = cuda.zeros(n, dtype=cuda.int16, device="cuda")
+    r = cuda.zeros(n, dtype=cuda.int16, device="cuda")
+    before = ext.counters()["launches"]
+    fam.nn.rmsnorm_rotate(r.data_ptr(), o.data_ptr(), x.data_ptr(), w.data_ptr(), sign.data_ptr(), n, eps, None)
+    assert fam.sys.compute_completed()
+    assert ext.counters()["launches"] == before + 1, "one kernel"
+    assert cuda.equal(o, o_want), "the normed row"
+    assert cuda.equal(r, r_want), "the rotated row"
+
+
+@pytest.mark.parametrize("heads,hd", [(4, 128), (16, 128), (3, 128), (2, 256), (1, 64)])
+def test_gate_then_rotation_is_one_kernel_with_the_two_doors_bits(cuda, fam, heads, hd):
+    """A mixer gates its answers (attention_gate_rows) and rotates them for the output projection (hadamard_rotate): the pair
+    is answered by one kernel with the bits of the two doors run apart."""
+    from silvann_b200 import ext
+    rng = np.random.default_rng(heads * 10 + hd)
+    n = heads * hd
+    att = cuda.from_numpy(rng.standard_normal(n).astype(np.float16).view(np.int16)).cuda()
+    qg = cuda.from_numpy((rng.standard_normal((heads, 2 * hd)) * 2).astype(np.float16).view(np.int16)).cuda()
+    sign = cuda.from_numpy(np.where(rng.random(512) < 0.5, -1.0, 1.0).astype(np.float16).view(np.int16)).cuda()
+    g_want = cuda.zeros(n, dtype=cuda.int16, device="cuda")
+    r_want = cuda.zeros(n, dtype=cuda.int16, device="cuda")
+    fam.nn.attention_gate_rows(g_want.data_ptr(), att.data_ptr(), qg.data_ptr(), heads, hd, None)
+    assert fam.sys.compute_completed()                                     # (a wait: the gate runs as worded)
+    fam.nn.hadamard_rotate(r_want.data_ptr(), g_want.data_ptr(), sign.data_ptr(), n, None)
+    assert fam.sys.compute_completed()
+    g = cuda.zeros(n, dtype=cuda.int16, device="cuda")
+    r = cuda.zeros(n, dtype=cuda.int16, device="cuda")
+    before = ext.counters()
+    fam.nn.attention_gate_rows(g.data_ptr(), att.data_ptr(), qg.data_ptr(), heads, hd, None)
+    fam.nn.hadamard_rotate(r.data_ptr(), g.data_ptr(), sign.data_ptr(), n, None)
+    assert fam.sys.compute_completed()
+    after = ext.counters()
+    shaped = n < 512 or (n % 512) % 128 == 0
+    assert after["launches"] - before["launches"] == (1 if shaped else 2) and after["refused"] == before["refused"] + (0 if shaped else 1)
+    assert cuda.equal(g, g_want), "the gated answers"
+    if shaped:
+        assert cuda.equal(r, r_want), "the rotated answers"
