@@ -936,8 +936,9 @@ def long_context(torch, dist, rank, world, steps, pk):
     h_len = max(0, min(HOST, shard.pos_hi) - shard.pos_lo)
     k_host = k[:h_len].cpu().pin_memory() if h_len else None
     v_host = v[:h_len].cpu().pin_memory() if h_len else None
-    # the box's pinned host-to-device rate: rank 0 alone, and then every rank at once (the ranks' copies may share host links
-    # and memory channels: what a GPU can get while its neighbours stream too is the bound of the tiered step at N > 1)
+    # the box's pinned host-to-device rate: rank 0 alone, and then every rank that holds a share of the host tier at once (the
+    # ranks' copies may share host links and memory channels: what a GPU can get while its neighbours stream too is the bound of
+    # the tiered step at N > 1)
     h2d_alone = torch.zeros(1, device="cuda", dtype=torch.float64)
     if rank == 0:
         h2d_alone[0] = pinned_h2d_peak(torch)
@@ -947,9 +948,11 @@ def long_context(torch, dist, rank, world, steps, pk):
     h2d_alone = float(h2d_alone.item())
     h2d_peak = h2d_alone
     if world > 1:
-        together = torch.tensor([pinned_h2d_peak(torch)], device="cuda", dtype=torch.float64)
+        # (only the ranks that hold a share of the host tier copy in the tiered step: only they copy here)
+        together = torch.tensor([pinned_h2d_peak(torch) if h_len else float("inf")], device="cuda", dtype=torch.float64)
         dist.all_reduce(together, op=dist.ReduceOp.MIN)
         h2d_peak = float(together.item())
+        dist.barrier()
     # the ranks that split a kv head's range exchange residuals through the library's own kernel over peer memory; the
     # buffers' handles travel once, here
     exchange = sharded.connect_exchange(torch, ext, dist, shard.group, rank, shard.q_heads * (d + 2) * 4) if world > 1 else None
@@ -969,7 +972,7 @@ def long_context(torch, dist, rank, world, steps, pk):
     gbs = host_bytes / out["tiered"]["ms_per_step"] / 1e6
     holders = min(world, kvh)                                 # ranks that hold a share of the host tier (the first range half of every kv head)
     out["tiered"].update({"host_tier_bytes": host_bytes, "host_tier_gbs": gbs, "host_tier_gbs_per_holding_gpu": gbs / holders,
-                          "pinned_h2d_peak_gbs_measured": h2d_alone, "pinned_h2d_peak_gbs_all_ranks_at_once": h2d_peak,
+                          "pinned_h2d_peak_gbs_measured": h2d_alone, "pinned_h2d_peak_gbs_holding_ranks_at_once": h2d_peak,
                           "host_tier_frac_of_h2d_peak": gbs / holders / h2d_peak, "host_tier_frac_of_h2d_peak_one_gpu_alone": gbs / holders / h2d_alone,
                           "lower_bound_ms": max(host_bytes / holders / h2d_peak / 1e6, (nbytes - host_bytes) / world / pk["hbm_gbs"] / 1e6)})
     if exchange is not None:
@@ -1349,6 +1352,28 @@ def run_case(args):
             fam.nn.expert_rows(eout.data_ptr(), ecodes[i].data_ptr(), ecodes[i].numel(), escales.data_ptr(), escales.numel() * 2, ex.data_ptr(), epairs.data_ptr(),
                                T, width, er, ec, None)
         work, unit = 2.0 * T * er * ec, "flop"
+    elif name in ("range_share_fused", "range_share_apart"):
+        # a rank's share of configuration 4 at 8 GPUs (131,072 positions of one kv head, 8 query heads) with its exchange step, the
+        # partner's push deposited: the exchange in the decode kernel's last block, or as a launch of its own after the decode
+        qh, kvh, d, Ls = 8, 1, 128, 131072
+        k = torch.randn((Ls, kvh, d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.5
+        v = torch.randn((Ls, kvh, d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.5
+        q = torch.randn((qh, d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.5
+        theirs = torch.randn((qh, d + 2), generator=gen, device="cuda", dtype=torch.float32).abs() + 0.5
+        x = ext.Exchange(2, 0, qh * (d + 2) * 4)
+        x.connect_alone()
+        tier = ext.Tier(qh, kvh, d, ext.BF16)
+        om = torch.zeros((qh, d), device="cuda", dtype=torch.bfloat16)
+        mine = torch.zeros((qh, d + 2), device="cuda", dtype=torch.float32)
+
+        def fn():
+            x.deposit(1, theirs, qh * (d + 2) * 4)
+            if name == "range_share_fused":
+                tier.decode_exchange(x, om, None, q, None, None, 0, k, v, Ls, wait_ms=200)
+            else:
+                tier.decode(None, mine, q, None, None, 0, k, v, Ls)
+                x.merge_finish(om, None, mine, qh, d, ext.BF16, wait_ms=200)
+        work, unit = 2 * Ls * kvh * d * 2, "bytes"
     elif name == "prefill_small":
         qh, kvh, d, T = 16, 2, 256, 2048
         q = torch.randn((T, qh, d), generator=gen, device="cuda", dtype=torch.bfloat16) * 0.5
@@ -1372,7 +1397,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the secondary configurations (faster; used under profilers)")
     ap.add_argument("--only", default=None, choices=["long_context"], help="run configuration 4 alone (any N) and print its object")
-    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, decode_cfg1, decode_cfg1_graph, tq8_small, tq4_small, deltanet_64, deltanet_prefill, prefill_small, mla_2048, mla_65536, exchange_small, expert_q4, expert_o8, expert_q4_64rows)")
+    ap.add_argument("--case", default=None, help="run one small single-kernel case instead (paged_small, long_small, decode_cfg1, decode_cfg1_graph, tq8_small, tq4_small, deltanet_64, deltanet_prefill, prefill_small, mla_2048, mla_65536, exchange_small, expert_q4, expert_o8, expert_q4_64rows, range_share_fused, range_share_apart)")
     args = ap.parse_args()
     if args.case:
         run_case(args)

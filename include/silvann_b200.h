@@ -438,7 +438,8 @@ int silvann_b200_exchange_gemv_sum(silvann_b200_exchange* exchange, void* out, c
  * residual (merge_finish) or a 16-bit vector (vector_sum), 2 for the rows of gemv_sum.  Same stream as the exchange. */
 int silvann_b200_exchange_deposit(silvann_b200_exchange* exchange, uint32_t member, const void* data, uint64_t bytes, uint32_t unit_bytes, void* stream);
 /* silvann_b200_tier_decode for a member of a range split: the member's residual over its two tiers, then the exchange,
- * as one call. */
+ * as one call — and as one launch when every position is on the card and the share is long enough to be split: the decode
+ * kernel's last block of a head block does the exchange step itself (the same bits). */
 int silvann_b200_tier_decode_exchange(silvann_b200_tier* tier, silvann_b200_exchange* exchange, void* o, float* res, const void* q,
                                       const void* k_host, const void* v_host, uint64_t host_len, const void* k_dev, const void* v_dev,
                                       uint64_t dev_len, sv_fault* over, uint32_t wait_ms, void* stream);
