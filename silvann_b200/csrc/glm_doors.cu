@@ -178,17 +178,20 @@ __global__ void __launch_bounds__(256) kda_steps_any_kernel(float* S, const uint
  * the block's threads past the columns split the nope rows between them; their sums meet in shared memory. */
 template <bool WIDE>
 __global__ void __launch_bounds__(512) absorb_kernel(uint16_t* out, const uint16_t* q, const uint16_t* W, uint64_t heads, uint64_t nope, uint64_t latent,
-                                                     uint64_t stride, float scale, uint64_t rows, unsigned int* over) {
-    extern __shared__ float acc[];                                         /* [slices][latent] */
+                                                     uint64_t stride, float scale, uint64_t rows, uint64_t parts, unsigned int* over) {
+    extern __shared__ float acc[];                                         /* [slices][columns of a part] */
     constexpr int PER = WIDE ? 8 : 1;
-    const uint64_t chunks = latent / PER;                                  /* WIDE only where 8 divides the latent's width */
+    const uint64_t chunks = latent / PER / parts;                          /* chunks of a part (WIDE only where 8 divides the latent's width; `parts` divides the chunks) */
+    const uint64_t pcols = chunks * PER;                                   /* columns of a part */
     const uint64_t across = chunks < blockDim.x ? chunks : blockDim.x;     /* threads side by side over the columns */
     const uint64_t slices = blockDim.x / across;                           /* and the rest of the block over the key rows */
     bool hit = false;
-    for (uint64_t bh = blockIdx.x; bh < rows * heads; bh += gridDim.x) {
+    /* a block a (row, head, part of the latent's columns): with few heads and one row, whole heads would leave most of the card idle */
+    for (uint64_t bhp = blockIdx.x; bhp < rows * heads * parts; bhp += gridDim.x) {
+        const uint64_t bh = bhp / parts, part = bhp - bh * parts;
         const uint64_t t = bh / heads, h = bh - t * heads;
         const uint16_t* qh = q + (t * heads + h) * nope;
-        const uint16_t* Wh = W + h * stride * latent;
+        const uint16_t* Wh = W + h * stride * latent + part * pcols;
         const uint64_t slice = threadIdx.x / across, first = threadIdx.x - slice * across;
         if (slice < slices)
             for (uint64_t chunk = first; chunk < chunks; chunk += across) {
@@ -221,13 +224,13 @@ __global__ void __launch_bounds__(512) absorb_kernel(uint16_t* out, const uint16
                     for (uint64_t i = slice; i < nope; i += slices) s[0] += H::to_float(Wh[i * latent + chunk]) * H::to_float(qh[i]);
                 }
 #pragma unroll
-                for (int e = 0; e < PER; ++e) acc[slice * latent + chunk * PER + e] = s[e];
+                for (int e = 0; e < PER; ++e) acc[slice * pcols + chunk * PER + e] = s[e];
             }
         __syncthreads();
-        for (uint64_t c = threadIdx.x; c < latent; c += blockDim.x) {
+        for (uint64_t c = threadIdx.x; c < pcols; c += blockDim.x) {
             float sum = 0.f;
-            for (uint64_t sl = 0; sl < slices; ++sl) sum += acc[sl * latent + c];
-            out[(t * heads + h) * latent + c] = H::from_float(sum * scale, hit);
+            for (uint64_t sl = 0; sl < slices; ++sl) sum += acc[sl * pcols + c];
+            out[(t * heads + h) * latent + part * pcols + c] = H::from_float(sum * scale, hit);
         }
         __syncthreads();
     }
@@ -524,12 +527,16 @@ cudaError_t kda_steps_launch(float* S, const uint16_t* conved, const uint16_t* f
 cudaError_t absorb_launch(uint16_t* out, const uint16_t* q, const uint16_t* W, uint64_t heads, uint64_t nope, uint64_t latent, uint64_t stride, float scale,
                           uint64_t rows, unsigned int* over, cudaStream_t st) {
     const bool wide = latent % 8 == 0 && (uintptr_t)W % 16 == 0;
-    const uint64_t chunks = wide ? latent / 8 : latent, across = chunks < 512 ? chunks : 512, slices = 512 / across;
-    const size_t smem = (size_t)slices * latent * sizeof(float);
+    const uint64_t all = wide ? latent / 8 : latent;
+    /* few (row, head) pairs: a head's columns are cut over up to four blocks so that the card has a block an SM or so */
+    uint64_t parts = 1;
+    while (parts < 4 && rows * heads * parts < 148 && all % (parts * 2) == 0 && all / (parts * 2) >= 8) parts *= 2;
+    const uint64_t chunks = all / parts, across = chunks < 512 ? chunks : 512, slices = 512 / across;
+    const size_t smem = (size_t)slices * (latent / parts) * sizeof(float);
     if (smem > 48 * 1024) return cudaErrorInvalidValue;
-    const unsigned g = glm_grid(rows * heads, 1, 148u * 16u);
-    if (wide) absorb_kernel<true><<<g, 512, smem, st>>>(out, q, W, heads, nope, latent, stride, scale, rows, over);
-    else absorb_kernel<false><<<g, 512, smem, st>>>(out, q, W, heads, nope, latent, stride, scale, rows, over);
+    const unsigned g = glm_grid(rows * heads * parts, 1, 148u * 16u);
+    if (wide) absorb_kernel<true><<<g, 512, smem, st>>>(out, q, W, heads, nope, latent, stride, scale, rows, parts, over);
+    else absorb_kernel<false><<<g, 512, smem, st>>>(out, q, W, heads, nope, latent, stride, scale, rows, parts, over);
     SV_GLM_DONE();
 }
 cudaError_t expand_launch(uint16_t* out, const uint16_t* o, const uint16_t* W, uint64_t heads, uint64_t width, uint64_t latent, uint64_t stride,
