@@ -173,3 +173,22 @@ def test_pairs_rows_and_the_16_bit_multiplies(cuda, fam, reference):
     close(outs[1][0], outs[0][0], "multiply_fp16")
     close(outs[1][1], outs[0][1], "multiply_fp16_rows")
     assert np.array_equal(outs[1][0], outs[1][1][0]), "the rows door's first row is the one-row door's answer"
+
+
+def test_empty_calls_write_nothing_and_an_unknown_width_is_refused(cuda, fam, reference):
+    rng = np.random.default_rng(3)
+    codes, luts = coded(reference, rng, 64, 128, 4)
+    x = cuda.from_numpy(rng.standard_normal((4, 128)).astype(np.float16).view(np.int16)).cuda()
+    pairs = cuda.from_numpy(np.array([[0, 0], [1, 1]], np.int32)).cuda()
+    tc = cuda.from_numpy(codes.copy()).cuda()
+    tl = cuda.from_numpy(luts.view(np.int16).copy()).cuda()
+    out = cuda.full((2, 64), 0x1234, dtype=cuda.int16, device="cuda")
+    before = ext.counters()
+    fam.nn.expert_rows(out.data_ptr(), tc.data_ptr(), codes.nbytes, tl.data_ptr(), luts.nbytes, x.data_ptr(), pairs.data_ptr(), 0, 4, 64, 128, None)     # no pairs
+    fam.nn.expert_rows(out.data_ptr(), tc.data_ptr(), 0, tl.data_ptr(), luts.nbytes, x.data_ptr(), pairs.data_ptr(), 2, 4, 64, 128, None)                # rooms that hold no row
+    assert fam.sys.compute_completed()
+    assert (out == 0x1234).all() and ext.counters()["launches"] == before["launches"]
+    fam.nn.expert_rows(out.data_ptr(), tc.data_ptr(), codes.nbytes, tl.data_ptr(), luts.nbytes, x.data_ptr(), pairs.data_ptr(), 2, 7, 64, 128, None)     # no such width
+    assert not fam.sys.compute_completed(), "a refused door makes the next wait answer false once"
+    assert fam.sys.compute_completed()
+    assert (out == 0x1234).all() and ext.counters()["refused"] == before["refused"] + 1
