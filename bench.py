@@ -308,6 +308,65 @@ def cpu_baselines_others():
     t = best_of(steps, 1)
     nbytes = 512 * (2 * 32 * 128 * 128 * 4 + 3 * 32 * 128 * 2 + 2 * 32 * 128 * 2 + 2 * 32 * 2 + 128 * 2)
     out["config5_decode"] = entry(nbytes / t / 1e9, UNIT, t, "configuration 5's 512 decode steps: deltanet_step a position, one sequence; one timed pass")
+
+    # the other entries of `others`, door for door on the same family (values drawn here: these are timings, the parity tests hold the checks)
+    P_, rng = oracle._p, np.random.default_rng(7)
+    f16 = lambda a: np.ascontiguousarray(a, dtype=np.float32).astype(np.float16).view(np.uint16)
+    S64 = (rng.standard_normal((64, 32, 128, 128)) * 0.05).astype(np.float32)
+
+    def steps64():
+        for b in range(64):
+            R.deltanet(S64[b], c5[b:b + 1], z5[b:b + 1], b5[b:b + 1], g5[b:b + 1], w5, 32, 32, 128, 1)
+    t = best_of(steps64, 2)
+    out["config5_decode_64seq"] = entry(64 * (2 * 32 * 128 * 128 * 4 + 3 * 32 * 128 * 2 + 2 * 32 * 128 * 2 + 2 * 32 * 2 + 128 * 2) / t / 1e9, UNIT, t,
+                                        "one decode step of 64 sequences: deltanet_step a sequence (the door takes one); best of 2")
+    qh_, kvh_, dh_, Lt = 32, 4, 128, 262144
+    for width in (8, 4):
+        rb = dh_ * width // 8
+        kc, vc = (rng.integers(0, 256, (Lt * kvh_, rb), dtype=np.uint8) for _ in range(2))
+        ks, vs = (f16(rng.random(Lt * kvh_) * 0.5 + 0.75) for _ in range(2))
+        tq_q = f16(rng.standard_normal((qh_, dh_)) * 0.25)
+        tp, tres = np.zeros((qh_, Lt), np.float32), np.zeros((qh_, dh_ + 2), np.float32)
+
+        def tier():
+            R.nn.attention_weights_tq(P_(tp), P_(tres), P_(tq_q), P_(kc), P_(ks), qh_, kvh_, dh_, Lt, width)
+            R.nn.attention_residual_mix_tq(P_(tres), P_(tp), P_(vc), P_(vs), qh_, kvh_, dh_, Lt, width)
+            R.wait()
+        t = best_of(tier, 2)
+        out[f"tq{width}_tier_d128"] = entry(2 * Lt * kvh_ * (rb + 2) / t / 1e9, UNIT, t, f"attention_weights_tq + attention_residual_mix_tq over 262,144 coded positions at {width} bits; best of 2")
+    for width in (4, 8):
+        rows_, cols_ = 16384, 4096
+        codes = rng.integers(0, 256, (rows_, cols_ * width // 8), dtype=np.uint8)
+        scales = f16((rng.random(rows_) * 0.5 + 0.75) * (3.0 / cols_ ** 0.5))
+        xv, ov = f16(rng.standard_normal(cols_)), np.zeros(rows_, np.uint16)
+
+        def gemv():
+            R.nn.turboquant_gemv(P_(ov), P_(codes), codes.nbytes, P_(scales), scales.nbytes, P_(xv), width, rows_, cols_, P_(R.over))
+            R.wait()
+        t = best_of(gemv, 5)
+        out[f"tq{width}_gemv_16384x4096"] = entry((codes.nbytes + scales.nbytes) / t / 1e9, UNIT, t, f"turboquant_gemv, 16,384 x 4,096 at {width} bits; best of 5")
+    for Lm in (2048, 65536):
+        lat, qm = f16(rng.standard_normal((Lm, 512))), f16(rng.standard_normal((64, 512)) * 2.0)
+        pm, om = np.zeros((64, Lm), np.float32), np.zeros((64, 512), np.uint16)
+
+        def latent():
+            R.nn.attention_scores_grouped(P_(pm), P_(qm), P_(lat), 64, 1, 512, Lm)
+            R.nn.attention_softmax_rows(P_(pm), 64, Lm)
+            R.nn.attention_mix(P_(om), P_(pm), P_(lat), 64, 1, 512, Lm, P_(R.over))
+            R.wait()
+        t = best_of(latent, 3)
+        out[f"mla_decode_64heads_{Lm}"] = entry((Lm * 512 * 2 + 2 * 64 * 512 * 2) / t / 1e9, UNIT, t, f"scores_grouped + softmax_rows + mix, 64 heads over {Lm} latents of 512; best of 3")
+    T_, er, ec = 256, 8192, 5120
+    ecodes = rng.integers(0, 256, (er, ec // 2), dtype=np.uint8)
+    escales = f16((rng.random(er) * 0.5 + 0.75) * (3.0 / ec ** 0.5))
+    ex, eout = f16(rng.standard_normal((T_, ec))), np.zeros((T_, er), np.uint16)
+    epairs = np.repeat(np.arange(T_, dtype=np.uint32), 2).copy()
+
+    def project():
+        R.nn.expert_rows(P_(eout), P_(ecodes), ecodes.nbytes, P_(escales), escales.nbytes, P_(ex), P_(epairs), T_, 4, er, ec, P_(R.over))
+        R.wait()
+    t = best_of(project, 2)
+    out["prompt_projection_256rows_q4"] = entry(2.0 * T_ * er * ec / t / 1e12, "TFLOP/s", t, "expert_rows, 256 rows x 5,120 through 8,192 coded rows at 4 bits; best of 2")
     return out
 
 
@@ -845,7 +904,10 @@ def attach_rooflines(others, pk, cpu):
     figure on the same configuration."""
     beside = {"config1_decode_doors": "config1", "config1_decode_kernel": "config1", "config2_causal_prefill": "config2",
               "config4_long_context_1gpu_resident": "config4", "config5_deltanet_decode_1seq": "config5_decode",
-              "config5_deltanet_decode_1seq_graph": "config5_decode", "config5_deltanet_prefill_8192": "config5_prefill"}
+              "config5_deltanet_decode_1seq_graph": "config5_decode", "config5_deltanet_prefill_8192": "config5_prefill",
+              "config5_deltanet_decode_64seq": "config5_decode_64seq", "tq8_tier_d128": "tq8_tier_d128", "tq4_tier_d128": "tq4_tier_d128",
+              "tq4_gemv_16384x4096": "tq4_gemv_16384x4096", "tq8_gemv_16384x4096": "tq8_gemv_16384x4096", "mla_decode_64heads_2048": "mla_decode_64heads_2048",
+              "mla_decode_64heads_65536": "mla_decode_64heads_65536", "prompt_projection_256rows_q4": "prompt_projection_256rows_q4"}
     for name, e in others.items():
         ms = e.get("ms_per_call", e.get("ms_per_step", e.get("ms")))
         spec = ROOFLINES.get(name)
