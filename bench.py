@@ -257,7 +257,8 @@ def cpu_baseline_paged(wl: PagedWorkload, budget_s=25.0):
 def cpu_baselines_others():
     """The reference's CPU family timed beside configurations 1, 2, 4 and 5 on this host's cores — the same seeded inputs
     the parity tests use (numpy PCG64 seeds 1001, 1002, 1004, 1005), one warm-up pass and the best of a few timed ones each
-    (about fifteen seconds in all).  Reported baselines, not targets."""
+    and, on drawn values, beside the other entries door for door (under a minute in all).  Reported baselines, not targets."""
+    import ctypes as C
     import oracle
     from silvann_b200 import workloads
     R = oracle.reference()
@@ -367,6 +368,68 @@ def cpu_baselines_others():
         R.wait()
     t = best_of(project, 2)
     out["prompt_projection_256rows_q4"] = entry(2.0 * T_ * er * ec / t / 1e12, "TFLOP/s", t, "expert_rows, 256 rows x 5,120 through 8,192 coded rows at 4 bits; best of 2")
+    er, ec = 5120, 4096
+    ecodes = rng.integers(0, 256, (er, ec), dtype=np.uint8)
+    escales = f16((rng.random(er) * 0.5 + 0.75) * (3.0 / ec ** 0.5))
+    ex, eout = f16(rng.standard_normal((T_, ec))), np.zeros((T_, er), np.uint16)
+    t = best_of(lambda: (R.nn.expert_rows(P_(eout), P_(ecodes), ecodes.nbytes, P_(escales), escales.nbytes, P_(ex), P_(epairs), T_, 8, er, ec, P_(R.over)), R.wait()), 2)
+    out["prompt_projection_256rows_o8"] = entry(2.0 * T_ * er * ec / t / 1e12, "TFLOP/s", t, "expert_rows, 256 rows x 4,096 through 5,120 coded rows at 8 bits; best of 2")
+
+    # the coded tiers at head_dim 256, and 16 rows of a prompt chunk over the 8-bit tier at 128 (a bounded sample: 65,536 positions)
+    qh_, kvh_, dh_ = 16, 2, 256
+    for width in (8, 4):
+        rb = dh_ * width // 8
+        kc, vc = (rng.integers(0, 256, (Lt * kvh_, rb), dtype=np.uint8) for _ in range(2))
+        ks, vs = (f16(rng.random(Lt * kvh_) * 0.5 + 0.75) for _ in range(2))
+        tq_q = f16(rng.standard_normal((qh_, dh_)) * 0.25)
+        tp, tres = np.zeros((qh_, Lt), np.float32), np.zeros((qh_, dh_ + 2), np.float32)
+
+        def tier256():
+            R.nn.attention_weights_tq(P_(tp), P_(tres), P_(tq_q), P_(kc), P_(ks), qh_, kvh_, dh_, Lt, width)
+            R.nn.attention_residual_mix_tq(P_(tres), P_(tp), P_(vc), P_(vs), qh_, kvh_, dh_, Lt, width)
+            R.wait()
+        t = best_of(tier256, 2)
+        out[f"tq{width}_tier_d256"] = entry(2 * Lt * kvh_ * (rb + 2) / t / 1e9, UNIT, t, f"attention_weights_tq + attention_residual_mix_tq over 262,144 coded positions at {width} bits, head_dim 256; best of 2")
+    qh_, kvh_, dh_, Ls, rows16 = 32, 4, 128, 65536, 16
+    kc, vc = (rng.integers(0, 256, (Ls * kvh_, dh_), dtype=np.uint8) for _ in range(2))
+    ks, vs = (f16(rng.random(Ls * kvh_) * 0.5 + 0.75) for _ in range(2))
+    q16 = f16(rng.standard_normal((rows16, qh_, dh_)) * 0.25)
+    tp16, res16 = np.zeros((rows16, qh_, Ls), np.float32), np.zeros((rows16, qh_, dh_ + 2), np.float32)
+
+    def rows_tier():
+        R.nn.attention_weights_tq_rows(P_(tp16), P_(res16), P_(q16), P_(kc), P_(ks), qh_, kvh_, dh_, Ls, 8, rows16)
+        R.nn.attention_residual_mix_tq_rows(P_(res16), P_(tp16), P_(vc), P_(vs), qh_, kvh_, dh_, Ls, 8, rows16)
+        R.wait()
+    t = best_of(rows_tier, 2)
+    out["tq8_tier_d128_rows16"] = entry(rows16 * Ls / t, "row-positions/s", t, "the _rows door pair, 16 rows over 65,536 of the 262,144 coded positions at 8 bits; best of 2")
+
+    # Kimi Delta Attention's decode step, the latent projections and the indexer, door for door
+    heads, d = 64, 128
+    W_ = heads * d
+    Sk = (rng.standard_normal((heads, d, d)) * 0.05).astype(np.float32)
+    kc3, kf, kg = f16(rng.standard_normal((3, 1, W_))), f16(rng.standard_normal((1, W_))), f16(rng.standard_normal((1, W_)))
+    kb, kdt, kal = f16(rng.standard_normal((1, heads))), f16(rng.standard_normal(W_)), f16(rng.standard_normal(heads) * 0.3)
+    kw, ko = f16(np.ones(d)), np.zeros((1, W_), np.uint16)
+    t = best_of(lambda: (R.nn.kda_step(P_(Sk), P_(kc3), P_(kf), P_(kb), P_(kdt), P_(kal), P_(kg), P_(kw), P_(ko), heads, d, C.c_float(-5.0), C.c_float(1e-5), P_(R.over)), R.wait()), 20)
+    out["kda_decode_64heads"] = entry((2 * heads * d * d * 4 + 6 * heads * d * 2) / t / 1e9, UNIT, t, "kda_step, 64 heads of 128; best of 20")
+    mh, nope, vd, lat_ = 64, 192, 256, 512
+    Wl = f16(rng.standard_normal((mh * (nope + vd), lat_)) * 0.05)
+    qa, oa = f16(rng.standard_normal(mh * nope)), f16(rng.standard_normal(mh * lat_))
+    absorbed, expanded = np.zeros(mh * lat_, np.uint16), np.zeros(mh * vd, np.uint16)
+    t = best_of(lambda: (R.nn.attention_absorb(P_(absorbed), P_(qa), P_(Wl), mh, nope, lat_, nope + vd, C.c_float(0.0722), P_(R.over)), R.wait()), 10)
+    out["mla_absorb_64heads"] = entry((mh * nope * lat_ * 2 + mh * nope * 2 + mh * lat_ * 2) / t / 1e9, UNIT, t, "attention_absorb, 64 heads; best of 10")
+    t = best_of(lambda: (R.nn.attention_expand(P_(expanded), P_(oa), P_(Wl), mh, vd, lat_, nope + vd, nope, P_(R.over)), R.wait()), 10)
+    out["mla_expand_64heads"] = entry((mh * vd * lat_ * 2 + mh * lat_ * 2 + mh * vd * 2) / t / 1e9, UNIT, t, "attention_expand, 64 heads; best of 10")
+    ih, idim, pools, topk, kpool = 32, 128, 8192, 512, 4
+    iq, iw, pooled = f16(rng.standard_normal(ih * idim)), f16(rng.standard_normal(ih)), f16(rng.standard_normal((pools, idim)))
+    iscores, iindex, icount = np.zeros(pools, np.float32), np.zeros(topk * kpool + kpool, np.int32), np.zeros(1, np.int32)
+
+    def indexer():
+        R.nn.index_scores(P_(iscores), P_(iq), P_(iw), P_(pooled), ih, idim, pools, C.c_float(0.088))
+        R.nn.index_select(P_(iindex), P_(icount), P_(iscores), pools, topk, kpool, pools * kpool, 3)
+        R.wait()
+    t = best_of(indexer, 10)
+    out["glm_indexer_8192pools"] = entry(pools / t, "pools/s", t, "index_scores + index_select, 32 heads of 128 over 8,192 pooled keys; best of 10")
     return out
 
 
@@ -907,7 +970,9 @@ def attach_rooflines(others, pk, cpu):
               "config5_deltanet_decode_1seq_graph": "config5_decode", "config5_deltanet_prefill_8192": "config5_prefill",
               "config5_deltanet_decode_64seq": "config5_decode_64seq", "tq8_tier_d128": "tq8_tier_d128", "tq4_tier_d128": "tq4_tier_d128",
               "tq4_gemv_16384x4096": "tq4_gemv_16384x4096", "tq8_gemv_16384x4096": "tq8_gemv_16384x4096", "mla_decode_64heads_2048": "mla_decode_64heads_2048",
-              "mla_decode_64heads_65536": "mla_decode_64heads_65536", "prompt_projection_256rows_q4": "prompt_projection_256rows_q4"}
+              "mla_decode_64heads_65536": "mla_decode_64heads_65536", "prompt_projection_256rows_q4": "prompt_projection_256rows_q4",
+              **{n: n for n in ("prompt_projection_256rows_o8", "tq8_tier_d256", "tq4_tier_d256", "tq8_tier_d128_rows16", "kda_decode_64heads",
+                                "mla_absorb_64heads", "mla_expand_64heads", "glm_indexer_8192pools")}}
     for name, e in others.items():
         ms = e.get("ms_per_call", e.get("ms_per_step", e.get("ms")))
         spec = ROOFLINES.get(name)
