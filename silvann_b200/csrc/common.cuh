@@ -37,6 +37,8 @@ template <> struct Elem<SV_DTYPE_FP16> {
         if ((h & 0x7FFFu) == 0x7C00u && !isinf(f)) over = true;
         return h;
     }
+    /* the smallest magnitude that rounds to infinity (half an ulp above the largest finite value, a tie that goes up) */
+    static __device__ __forceinline__ float over_from() { return 65520.0f; }
     static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
         const __half2 h = __floats2half2_rn(lo, hi);
         return *reinterpret_cast<const uint32_t*>(&h);
@@ -52,6 +54,7 @@ template <> struct Elem<SV_DTYPE_BF16> {
         if ((h & 0x7FFFu) == 0x7F80u && !isinf(f)) over = true;
         return h;
     }
+    static __device__ __forceinline__ float over_from() { return __uint_as_float(0x7F7F8000u); }
     static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
         const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
         return *reinterpret_cast<const uint32_t*>(&h);
@@ -100,6 +103,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     *abort_flag = 1u;
     if (status) atomicOr(status, SV_STATUS_TIMEOUT);
     return false;
+}
+
+/* One 2-D tile, shared -> global, as part of this thread's current bulk group; rows and columns past the tensor's extent
+ * are not written.  x (the innermost coordinate) times the element size must be a multiple of 16 bytes, and neither
+ * coordinate may be negative.  The writes to shared memory that the tile is made of must have been followed by
+ * tma_store_fence() in the threads that made them, before the synchronisation that lets this thread go. */
+__device__ __forceinline__ void tma_store_2d(const void* tmap, const void* src, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(tmap), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_store_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+/* closes the bulk group and waits until its tiles have been READ from shared memory (the memory may then be given back;
+ * the writes to global memory complete on their own) */
+__device__ __forceinline__ void tma_store_commit_and_wait_read() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 /* One 2-D tile, global -> shared, completion counted in bytes on `bar`.  x is the innermost (element) coordinate and

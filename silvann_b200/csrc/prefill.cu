@@ -6,7 +6,8 @@
  * cache rows 0 .. first + r; query head h reads kv head h / (q_heads / kv_heads).
  *
  * A block owns 128 query rows of one head; 11 warps in four roles.
- *   warp 0      TMA: Q once (128 x head_dim, kept in shared memory for the whole block), then rings of K tiles and V
+ *   warp 0      TMA: Q once (128 x head_dim, kept in shared memory for the whole block; asked for with the first K tile
+ *               by the thread that initialises the barriers, ahead of the block's first barrier), then rings of K tiles and V
  *               tiles of 64 keys (128-byte swizzle; 3 + 2 stages at head_dim 256, 4 + 4 below).
  *   warp 1      one thread issues the score MMAs S = Q.K^T (M 128, N 64, K = head_dim in steps of 16, both operands in
  *               shared memory) into one of THREE score buffers in TMEM, so scores run two tiles ahead of the softmax.
@@ -20,8 +21,9 @@
  *               shared memory) with O resident in TMEM for the whole row block.
  * Two issuing threads because the MMA queue is shallow and a satisfied mbarrier wait costs ~100 cycles: with one thread
  * every wait for the softmax was a bubble in the tensor pipe.  TMEM columns: O in [0, head_dim), score buffer b at
- * head_dim + 64 b.  The epilogue divides by the row sum and stores 16-bit rows, or leaves (m ln 2, l, acc) a row in the
- * reference's residual layout (the many-row residual doors).
+ * head_dim + 64 b.  The epilogue divides by the row sum and rounds; the 16-bit rows are staged in the K ring (free by then,
+ * in the swizzled box layout TMA reads) and leave as one TMA store a 64-column box — or (m ln 2, l, acc) a row is left in
+ * the reference's residual layout (the many-row residual doors).
  *
  * Every mbarrier wait is bounded; a wait that runs out raises the block's abort flag, ORs "B2TO" into the device status
  * word, and every role falls through to the common exit, where TMEM is released.  No multicast, no cluster.
@@ -56,19 +58,21 @@ template <int D> struct PrefillCfg {
 };
 
 struct PrefillParams {
+    const uint16_t* q;        /* the queries themselves, for L2 prefetches (the loads go through the tensor map) */
     uint16_t* o;
     float* res;
     unsigned int* over;
     unsigned int* status;
     uint32_t q_heads, kv_heads, group;
     uint32_t first, rows, q_tiles;
+    uint32_t ahead;           /* a block asks L2 for the queries of the block this many further on (the SM count) */
     float scale_log2;
 };
 
 template <int D, int DT>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
-               const __grid_constant__ CUtensorMap vmap, const PrefillParams P) {
+               const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap omap, const PrefillParams P) {
     using Cfg = PrefillCfg<D>;
     using E = Elem<DT>;
     constexpr int KST = Cfg::KST, VST = Cfg::VST, NSB = Cfg::NSB;
@@ -88,7 +92,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     uint64_t* s_free = p_full + NSB;         /* NSB: the PV MMA that read the buffer's weights has completed */
     uint64_t* q_full = s_free + NSB;         /* 1 */
     uint64_t* xbar = q_full + 1;             /* 4: the two softmax warps of a lane quadrant meet here once a tile */
-    uint32_t* tmem_slot = (uint32_t*)(xbar + 4);
+    uint64_t* o_staged = xbar + 4;           /* 1: the eight softmax warps have put their share of the output rows into shared memory */
+    uint32_t* tmem_slot = (uint32_t*)(o_staged + 1);
     volatile uint32_t* abort_flag = (volatile uint32_t*)(tmem_slot + 1);
     float* xch = (float*)((uint8_t*)bars + 256);             /* [2][128]: the halves' normalisers at the end */
 
@@ -107,8 +112,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         for (int b = 0; b < NSB; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 8); mbar_init(&s_free[b], 1); }
         mbar_init(q_full, 1);
         for (int x = 0; x < 4; ++x) mbar_init(&xbar[x], 2);
+        mbar_init(o_staged, 8);
         *abort_flag = 0u;
         mbar_fence_init();
+        /* Q and the first K tile are asked for here, ahead of the TMEM allocation and the block's first barrier: the
+         * first score MMA waits for nothing else */
+        tma_prefetch_desc(&qmap); tma_prefetch_desc(&kmap); tma_prefetch_desc(&vmap);
+        mbar_expect_tx(q_full, Cfg::Q_BYTES);
+#pragma unroll
+        for (int c = 0; c < Cfg::BOXES; ++c) tma_load_2d(q_s + c * Cfg::Q_BOX_BYTES, &qmap, q_full, h * D + c * 64, row0);
+        mbar_expect_tx(&k_full[0], Cfg::KV_TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < Cfg::BOXES; ++c) tma_load_2d(k_s + c * Cfg::KV_BOX_BYTES, &kmap, &k_full[0], g * D + c * 64, 0);
     }
     if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tc_fence_before();
@@ -118,14 +133,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     const uint32_t t_o = tmem, t_s0 = tmem + Cfg::T_S;
 
     if (warp == 0) {
-        /* ---------------- TMA producer: Q once, then a ring of K tiles and a ring of V tiles ---------------- */
+        /* ---------------- TMA producer: a ring of K tiles and a ring of V tiles (Q and K(0) are on their way) ---------------- */
+        {
+            /* the whole warp asks L2 for the queries of a block that starts about when this one ends, so that its first
+             * wait is a trip to L2 and not to memory: 128 rows of D elements, a row's share of this head contiguous */
+            const uint32_t nb = blockIdx.x + P.ahead;
+            if (P.ahead != 0u && nb < gridDim.x) {
+                const int nrow0 = ((int)P.q_tiles - 1 - (int)(nb / P.q_heads)) * PF_BM, nh = (int)(nb % P.q_heads);
+                constexpr int LINES = D * 2 / 128;                       /* 128-byte lines a row */
+                for (int i = lane; i < PF_BM * LINES; i += 32) {
+                    const int rr = nrow0 + i / LINES;
+                    if (rr < (int)P.rows)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(P.q + ((size_t)rr * P.q_heads + nh) * D + (i % LINES) * 64));
+                }
+            }
+        }
         if (lane == 0) {
-            tma_prefetch_desc(&qmap); tma_prefetch_desc(&kmap); tma_prefetch_desc(&vmap);
-            mbar_expect_tx(q_full, Cfg::Q_BYTES);
-#pragma unroll
-            for (int c = 0; c < Cfg::BOXES; ++c) tma_load_2d(q_s + c * Cfg::Q_BOX_BYTES, &qmap, q_full, h * D + c * 64, row0);
             /* K runs ahead of V by the depth of the score pipeline: K(j + KST - VST) is requested with V(j) */
-            int jk = 0;
+            int jk = 1;
             auto load_k = [&]() -> bool {
                 const int s = jk % KST, use = jk / KST;
                 if (use > 0 && !mbar_wait(&k_empty[s], (use - 1) & 1, abort_flag, P.status)) return false;
@@ -138,7 +163,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             };
             bool ok = true;
             int jv = 0;                                      /* value tiles asked for */
-            for (int i = 0; ok && i < KST - 1 && jk < nt; ++i) ok = load_k();
+            while (ok && jk < KST - 1 && jk < nt) ok = load_k();
             for (int j = 0; ok && j < nt; ++j) {
                 if (jk < nt && !load_k()) break;
                 const int s = j % VST, use = j / VST;
@@ -296,7 +321,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             const float l_row = met ? l + xch[(half ^ 1) * PF_BM + r] : 0.f;
             const float inv = met ? 1.0f / l_row : 0.f;
             bool hit = false;
-            uint16_t* orow = P.o + ((size_t)grow_ * P.q_heads + h) * D;
+            /* The 16-bit rows leave through shared memory and one TMA store a 64-column box: written straight from the
+             * registers, a warp's store would touch 32 rows (32 lines for 512 bytes) and the block's 4,096 such line visits
+             * took longer than three tiles of attention.  The K ring is free: every MMA has completed and every copy has
+             * landed.  The boxes are laid out as TMA reads them (128-byte rows, the 16-byte piece index XOR the row's low
+             * three bits), which also keeps the lanes of a warp, a row each, out of each other's banks. */
+            uint8_t* stage = k_s;
+            static_assert(Cfg::Q_BYTES <= KST * Cfg::KV_TILE_BYTES, "the staged output fits the K ring");
             /* the residual form of the answer: (m, l, acc) as attention_weights_rows + attention_residual_mix_rows leave
              * it — m is the reference the weights were taken against (natural-log units), acc is not divided */
             float* rrow = P.res ? P.res + ((size_t)grow_ * P.q_heads + h) * (D + 2) : nullptr;
@@ -311,21 +342,41 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                     for (int c = 0; c < 32; c += 2) *reinterpret_cast<float2*>(rrow + 2 + c0 + c) = make_float2(__uint_as_float(ov[c]), __uint_as_float(ov[c + 1]));
                 }
                 if (P.o && grow_ < (int)P.rows) {
+                    /* rounded two at a time; the overflow rule (a finite value that lands on infinity) is looked at a value
+                     * at a time only when the largest magnitude of the 32 says that it can have happened */
+                    float top = 0.f;
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
                         uint32_t w[4];
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
-                            const uint16_t lo = E::from_float(__uint_as_float(ov[c + 2 * u]) * inv, hit);
-                            const uint16_t hi = E::from_float(__uint_as_float(ov[c + 2 * u + 1]) * inv, hit);
-                            w[u] = (uint32_t)lo | ((uint32_t)hi << 16);
+                            const float x0 = __uint_as_float(ov[c + 2 * u]) * inv, x1 = __uint_as_float(ov[c + 2 * u + 1]) * inv;
+                            top = fmaxf(top, fmaxf(fabsf(x0), fabsf(x1)));
+                            w[u] = E::pack2(x0, x1);
                         }
-                        *reinterpret_cast<uint4*>(orow + c0 + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4*>(stage + ((c0 + c) >> 6) * Cfg::Q_BOX_BYTES + r * 128 + (((((c0 + c) & 63) >> 3) ^ (r & 7)) << 4)) =
+                            make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                    if (top >= E::over_from()) {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) (void)E::from_float(__uint_as_float(ov[c]) * inv, hit);
                     }
                 }
             }
             if (hit && P.over) atomicOr(P.over, SV_FAULT_OVERFLOW);
             tc_fence_before();
+            if (P.o) {
+                tma_store_fence();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(o_staged);
+                /* one thread sends the boxes once all eight warps have staged theirs; rows past the call's end are cut off
+                 * by the tensor map (they were not staged either) */
+                if (sw == 0 && lane == 0 && mbar_wait(o_staged, 0, abort_flag, P.status)) {
+#pragma unroll
+                    for (int c = 0; c < Cfg::BOXES; ++c) tma_store_2d(&omap, stage + c * Cfg::Q_BOX_BYTES, h * D + c * 64, row0);
+                    tma_store_commit_and_wait_read();
+                }
+            }
         }
     }
 
@@ -349,12 +400,15 @@ template <int D, int DT>
 static cudaError_t launch_prefill(const PrefillCall& c) {
     using Cfg = PrefillCfg<D>;
     const bool bf = DT == SV_DTYPE_BF16;
-    CUtensorMap qm, km, vm;
+    CUtensorMap qm, km, vm, om;
     const uint64_t qcols = (uint64_t)c.q_heads * D, kcols = (uint64_t)c.kv_heads * D;
     if (!make_map_2d_sw128(&qm, c.q, qcols, c.rows, qcols * 2, 64u, PF_BM, bf)) return cudaErrorInvalidValue;
     if (!make_map_2d_sw128(&km, c.k, kcols, c.first + c.rows, kcols * 2, 64u, PF_BN, bf)) return cudaErrorInvalidValue;
     if (!make_map_2d_sw128(&vm, c.v, kcols, c.first + c.rows, kcols * 2, 64u, PF_BN, bf)) return cudaErrorInvalidValue;
+    if (!c.o) om = qm;                                      /* not used then */
+    else if (!make_map_2d_sw128(&om, c.o, qcols, c.rows, qcols * 2, 64u, PF_BM, bf)) return cudaErrorInvalidValue;
     PrefillParams P;
+    P.q = (const uint16_t*)c.q; P.ahead = device_sm_count();
     P.o = (uint16_t*)c.o; P.res = c.res; P.over = c.over; P.status = device_status_word();
     P.q_heads = c.q_heads; P.kv_heads = c.kv_heads; P.group = c.q_heads / c.kv_heads;
     P.first = (uint32_t)c.first; P.rows = (uint32_t)c.rows; P.q_tiles = (uint32_t)((c.rows + PF_BM - 1) / PF_BM);
@@ -366,7 +420,7 @@ static cudaError_t launch_prefill(const PrefillCall& c) {
         if (e != cudaSuccess) return e;
         attr_set[d].store(true, std::memory_order_release);
     }
-    prefill_kernel<D, DT><<<P.q_tiles * c.q_heads, PF_THREADS, Cfg::SMEM, c.stream>>>(qm, km, vm, P);
+    prefill_kernel<D, DT><<<P.q_tiles * c.q_heads, PF_THREADS, Cfg::SMEM, c.stream>>>(qm, km, vm, om, P);
     note_launch(1);
     return cudaGetLastError();
 }
