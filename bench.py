@@ -634,6 +634,22 @@ def config1_graph(torch, ext, gen, copies=64):
     return replay, 2 * n * kvh * d * 2, "bytes"
 
 
+def mla_graph(torch, ext, lat, qm, om, Lm):
+    """One CUDA graph of a latent-attention call a latent of `lat`, captured on a side stream.  Answers the replay."""
+    side = torch.cuda.Stream()
+    ext.mla_decode(om, None, qm, lat[0], 64, Lm, ext.FP16)                  # scratch is allocated outside the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(lat.shape[0]):
+            ext.mla_decode(om, None, qm, lat[i], 64, Lm, ext.FP16, stream=side.cuda_stream)
+    keep = (lat, qm, om, side)
+
+    def replay(_keep=keep):
+        graph.replay()
+    return replay
+
+
 def coded_weights(torch, gen, copies, rows, cols, width):
     """`copies` distinct coded matrices (random codes, scales near 1/sqrt(cols)) and one input vector, on the card."""
     rb = cols * width // 8
@@ -824,6 +840,14 @@ def other_workloads(torch, fam, pk, steps, warmup):
         nbytes = Lm * 512 * 2 + 2 * 64 * 512 * 2
         out[f"mla_decode_64heads_{Lm}"] = {"value": nbytes / ms / 1e6, "unit": UNIT, "ms_per_call": ms, "frac_hbm": nbytes / ms / 1e6 / hbm, "tflops": 4.0 * 64 * 512 * Lm / ms / 1e9,
                                             "note": f"scores_grouped + softmax_rows + mix doors, 64 heads over {Lm} latents of 512: {nbytes / 1e6:.1f} MB a call, {copies} latents cycled"}
+        try:
+            # the same calls as the card sees them: one CUDA graph of `copies` launches (the three doors from Python cost the host
+            # about as much as a short call costs the card)
+            replay = mla_graph(torch, ext, lat, qm, om, Lm)
+            out[f"mla_decode_64heads_{Lm}"]["ms_per_call_in_a_graph"] = time_loop(torch, replay, 20, 3) / copies
+        except Exception as exc:                       # noqa: BLE001 - a capture the driver refuses is reported, not fatal
+            out[f"mla_decode_64heads_{Lm}"]["ms_per_call_in_a_graph"] = None
+            out[f"mla_decode_64heads_{Lm}"]["graph_note"] = str(exc)[:200]
         del lat
     torch.cuda.empty_cache()
 
@@ -1450,6 +1474,9 @@ def run_case(args):
             i = lstate["i"] = (lstate["i"] + 1) % copies
             ext.mla_decode(om, None, qm, lat[i], 64, Lm, ext.FP16, int(os.environ.get("MLA_BLOCKS", "0")))
         work, unit = Lm * 512 * 2 + 2 * 64 * 512 * 2, "bytes"
+        if os.environ.get("MLA_GRAPH"):
+            fn = mla_graph(torch, ext, lat, qm, om, Lm)
+            work *= copies
     elif name == "exchange_small":
         # the exchange's fold alone on one card: 8 heads of 128 (configuration 4's share at 8 GPUs), the partner's push deposited
         x = ext.Exchange(2, 0, 8 * 130 * 4)

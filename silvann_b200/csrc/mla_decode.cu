@@ -26,6 +26,12 @@
  * when the block had the whole range, else to scratch, where a second small kernel folds the blocks' partials in range
  * order with attention_merge's arithmetic (kernels.cuh:1243-1255) and finishes.
  *
+ * A short range (a few thousand keys: what the sparse attention gathers) gives the card fewer tiles than SMs, and a block's
+ * time is then one chain: copies, scores, softmax, value MMAs, the write-out of 131 KB at one SM's store rate.  Where SMs
+ * are to spare a share of the range is therefore given to four (or two) blocks, each answering for a quarter (a half) of
+ * O^T's columns: all take the scores and the softmax, each issues a quarter of the value MMAs and writes a quarter of the
+ * partial answer.
+ *
  * Algorithmic bytes: positions x 512 x 2 (the latent once) + 2 x heads x 512 x 2.  Every mbarrier wait is bounded; a wait
  * that runs out raises "B2TO" in the device status word and every role falls through to the exit, where TMEM is released.
  * No cluster, no multicast. */
@@ -51,7 +57,8 @@ struct MlaParams {
     const void* latent;       /* the rows themselves, for L2 prefetches */
     unsigned int* over;
     unsigned int* status;
-    uint32_t length, tiles, blocks;
+    uint32_t length, tiles, blocks;   /* blocks: the shares the key range is cut into */
+    uint32_t csplit;                  /* blocks a share of the range (1, 2 or 4): each takes 4 / csplit of the answer's four 128-column blocks */
     float scale_log2;
 };
 
@@ -115,7 +122,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     /* this block's tiles: a contiguous share of the range, as even as whole tiles allow */
-    const int tile0 = (int)(((uint64_t)blockIdx.x * P.tiles) / P.blocks), tile1 = (int)(((uint64_t)(blockIdx.x + 1) * P.tiles) / P.blocks);
+    const uint32_t share = blockIdx.x / P.csplit;
+    const int j0 = (int)(blockIdx.x % P.csplit) * (4 / (int)P.csplit), j1 = j0 + 4 / (int)P.csplit;   /* this block's column blocks of O^T */
+    const int tile0 = (int)(((uint64_t)share * P.tiles) / P.blocks), tile1 = (int)(((uint64_t)(share + 1) * P.tiles) / P.blocks);
     const int nt = tile1 - tile0;
 
     if (tid == 0) {
@@ -123,6 +132,20 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         mbar_init(q_full, 1); mbar_init(s_full, 1); mbar_init(p_full, 4 * Cfg::HALVES); mbar_init(pv_done, 1);
         *abort_flag = 0u;
         mbar_fence_init();
+        /* Q and the first tile are asked for here, ahead of the TMEM allocation and the block's first barrier: they head the
+         * block's chain of dependent steps */
+        if (nt > 0) {
+            tma_prefetch_desc(&qmap); tma_prefetch_desc(&cmap);
+            mbar_expect_tx(q_full, Cfg::Q_BYTES);
+#pragma unroll
+            for (int i = 0; i < ML_BOXES; ++i) tma_load_2d(q_s + i * Cfg::Q_BOX_BYTES, &qmap, q_full, i * 64, 0);
+            const uint64_t pol0 = l2_policy_evict_first();
+#pragma unroll
+            for (int i = 0; i < ML_BOXES; ++i) {
+                mbar_expect_tx(&full[i], ML_BOX_BYTES);
+                tma_load_2d_hint(c_s + i * ML_BOX_BYTES, &cmap, &full[i], i * 64, tile0 * ML_BK, pol0);
+            }
+        }
     }
     if (tid < NH) mref[tid] = -INFINITY;
     if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -138,18 +161,12 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         bool ok = true;
         const uint8_t* base = (const uint8_t*)P.latent;
         const uint64_t end = (uint64_t)P.length * (ML_D * 2);
-        if (lane == 0 && nt > 0) {
-            tma_prefetch_desc(&qmap); tma_prefetch_desc(&cmap);
-            mbar_expect_tx(q_full, Cfg::Q_BYTES);
-#pragma unroll
-            for (int i = 0; i < ML_BOXES; ++i) tma_load_2d(q_s + i * Cfg::Q_BOX_BYTES, &qmap, q_full, i * 64, 0);
-        }
         const uint64_t pol = l2_policy_evict_first();
-        int last_t = -1, last_i = -1;                        /* lane 0: the last box asked for (tile, box) */
+        int last_t = nt > 0 ? 0 : -1, last_i = nt > 0 ? ML_BOXES - 1 : -1;   /* lane 0: the last box asked for (tile, box); tile 0 is on its way */
         for (int t = 0; t < nt; ++t) {
-            if (lane == 0 && ok)
+            if (lane == 0 && ok && t > 0)
                 for (int i = 0; i < ML_BOXES; ++i) {
-                    if (t > 0 && !mbar_wait(&empty[i], (t - 1) & 1, abort_flag, P.status)) { ok = false; break; }
+                    if (!mbar_wait(&empty[i], (t - 1) & 1, abort_flag, P.status)) { ok = false; break; }
                     mbar_expect_tx(&full[i], ML_BOX_BYTES);
                     tma_load_2d_hint(c_s + i * ML_BOX_BYTES, &cmap, &full[i], i * 64, (tile0 + t) * ML_BK, pol);
                     last_t = t; last_i = i;
@@ -196,10 +213,15 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 }
                 if (!ok) break;
                 tc_commit(s_full);
+                /* the boxes whose columns another block of this share answers for are read by the score MMAs only: free now
+                 * (this block's own boxes stay until its value MMAs have read them, so a tile's scores still cannot complete
+                 * before the value products of the tile before it have) */
+                for (int i = 0; i < ML_BOXES; ++i)
+                    if (i < 2 * j0 || i >= 2 * j1) tc_commit(&empty[i]);
                 if (!mbar_wait(p_full, t & 1, abort_flag, P.status)) break;
                 tc_fence_after();
 #pragma unroll 1
-                for (int j = 0; j < 4; ++j) {
+                for (int j = j0; j < j1; ++j) {
                     /* O^T block j: latent columns 128 j .. 128 j + 127 = boxes 2j and 2j + 1; sixteen keys a step = two 8-key groups */
 #pragma unroll
                     for (int kk = 0; kk < ML_BK / 16; ++kk)
@@ -303,7 +325,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                  * that read it had completed: O^T is settled.  A thread scales its lane (a latent column) and its 32 heads of
                  * the four blocks. */
 #pragma unroll 1
-                for (int j = 0; j < 4; ++j) {
+                for (int j = j0; j < j1; ++j) {
                     uint32_t ov[32];
                     tmem_ld32(tmem + Cfg::T_O + j * NH + h0 + lane_off, ov);
                     tmem_wait_ld();
@@ -325,16 +347,18 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
          * scheduled — its launch then overlaps the blocks' write-out — and it waits, at its first instruction, for this grid to
          * have completed (a no-op when nothing of the kind follows) */
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-        float* red = (float*)c_s;                                     /* [NH][128]: the ring is free now */
+        float* red = (float*)c_s;                                     /* [NH][129]: the ring is free now; a head's row is one word
+                                                                         longer than its 128 shares so that the threads that sum
+                                                                         different heads below read different banks */
         if (alive) {
 #pragma unroll
-            for (int x = 0; x < 32; ++x) red[(h0 + x) * 128 + r] = lpart[x];
+            for (int x = 0; x < 32; ++x) red[(h0 + x) * 129 + r] = lpart[x];
         }
         softmax_bar<SOFT>();
         if (st < 2 * NH) {
             /* a head's 128 shares: two threads take 64 each, four running sums apiece (the order is fixed, the chain short) */
             const int h = st % NH, part = st / NH;
-            const float* src = red + h * 128 + part * 64;
+            const float* src = red + h * 129 + part * 64;
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
             for (int x = 0; x < 64; x += 4) { a0 += src[x]; a1 += src[x + 1]; a2 += src[x + 2]; a3 += src[x + 3]; }
@@ -345,11 +369,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         softmax_bar<SOFT>();
         if (alive) {
             const bool whole = P.blocks == 1u;
-            float* out = whole ? P.res : P.partials + (size_t)blockIdx.x * NH * (ML_D + 2);
+            float* out = whole ? P.res : P.partials + (size_t)share * NH * (ML_D + 2);
             bool hit = false;
-            if (out && st < NH) { out[(size_t)st * (ML_D + 2)] = mref[st] * SV_LN2; out[(size_t)st * (ML_D + 2) + 1] = lsum[st]; }
+            if (out && st < NH && j0 == 0) {                          /* every block of a share holds the same (m, l): the first writes them */ out[(size_t)st * (ML_D + 2)] = mref[st] * SV_LN2; out[(size_t)st * (ML_D + 2) + 1] = lsum[st]; }
 #pragma unroll 1
-            for (int j = 0; j < 4; ++j) {
+            for (int j = j0; j < j1; ++j) {
                 uint32_t ov[32];
                 tmem_ld32(tmem + Cfg::T_O + j * NH + h0 + lane_off, ov);
                 tmem_wait_ld();
@@ -375,26 +399,35 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 template <int DT>
 __global__ void __launch_bounds__(128) mla_fold_kernel(uint16_t* o, float* res, const float* partials, uint32_t heads, uint32_t blocks, unsigned int* over) {
     using E = Elem<DT>;
-    __shared__ float ms_s[160], ls_s[160];
+    __shared__ float ms_s[160], ls_s[160], fs_s[160];
     asm volatile("griddepcontrol.wait;" ::: "memory");          /* the partials are the grid ahead's */
     const uint32_t h = blockIdx.x / 4u, e = (blockIdx.x % 4u) * 128u + threadIdx.x, w = ML_D + 2;
     const size_t step = (size_t)heads * w;
     const float* base = partials + (size_t)h * w;
-    /* the blocks' (m, l) a thread each, all asked for at once; then the accumulators eight at a time, so that no load waits for
-     * the one before it */
+    /* a thread folds one element over the blocks in range order.  The first 32 blocks' accumulators are asked for before
+     * anything else and the blocks' (m, l) right behind them, so that a short range costs ONE trip to memory; a long one
+     * goes on 32 loads at a time (a trip's latency, not the bytes, is what a step of this loop costs) */
+    constexpr uint32_t FB = 32u;
+    float a[FB];
+#pragma unroll
+    for (uint32_t u = 0; u < FB; ++u) a[u] = (u < blocks) ? __ldcg(base + u * step + 2 + e) : 0.f;
     for (uint32_t s = threadIdx.x; s < blocks; s += 128u) { ms_s[s] = __ldcg(base + s * step); ls_s[s] = __ldcg(base + s * step + 1); }
     __syncthreads();
     float m = -INFINITY;
     for (uint32_t s = 0; s < blocks; ++s) m = fmaxf(m, ms_s[s]);
+    /* a block's weight is the same for every element of the head: taken once, not once a thread */
+    for (uint32_t s = threadIdx.x; s < blocks; s += 128u) fs_s[s] = ms_s[s] == -INFINITY ? 0.f : expf(ms_s[s] - m);
+    __syncthreads();
     float acc = 0.f, l = 0.f;
-    for (uint32_t s0 = 0; s0 < blocks; s0 += 8u) {
-        float a[8];
+    for (uint32_t s0 = 0; s0 < blocks; s0 += FB) {
+        if (s0 != 0u) {
 #pragma unroll
-        for (uint32_t u = 0; u < 8u; ++u) a[u] = (s0 + u < blocks) ? __ldcg(base + (s0 + u) * step + 2 + e) : 0.f;
+            for (uint32_t u = 0; u < FB; ++u) a[u] = (s0 + u < blocks) ? __ldcg(base + (s0 + u) * step + 2 + e) : 0.f;
+        }
 #pragma unroll
-        for (uint32_t u = 0; u < 8u; ++u) {
+        for (uint32_t u = 0; u < FB; ++u) {
             if (s0 + u >= blocks || ms_s[s0 + u] == -INFINITY) continue;
-            const float f = expf(ms_s[s0 + u] - m);
+            const float f = fs_s[s0 + u];
             acc = __fmaf_rn(a[u], f, acc);
             l = __fmaf_rn(ls_s[s0 + u], f, l);
         }
@@ -432,6 +465,12 @@ static cudaError_t launch_mla(uint16_t* o, float* res, const void* q, const void
     if (blocks > P.tiles) blocks = P.tiles;
     if (blocks > 160u) blocks = 160u;                  /* the fold keeps the blocks' (m, l) in shared memory */
     P.blocks = blocks;
+    /* A short range leaves most of the card idle, and a block's time is then its chain of one or two tiles: the value MMAs
+     * and the write-out of the partial answer (which goes at the one SM's store rate) are a third of it.  Two or four blocks
+     * a share, each with a half or a quarter of the answer's columns, cut both wherever every block still finds an SM of its
+     * own; the scores and the softmax are then taken two or four times, on SMs that had nothing to do. */
+    const uint32_t sms = device_sm_count();
+    P.csplit = blocks * 4u <= sms ? 4u : (blocks * 2u <= sms ? 2u : 1u);
     P.scale_log2 = (1.0f / sqrtf((float)ML_D)) * SV_LOG2E;
     P.partials = nullptr;
     int d = 0;
@@ -453,7 +492,7 @@ static cudaError_t launch_mla(uint16_t* o, float* res, const void* q, const void
         if ((e = cudaFuncSetAttribute(mla_decode_kernel<NH, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM)) != cudaSuccess) return e;
         attr_set[d].store(true, std::memory_order_release);
     }
-    mla_decode_kernel<NH, DT><<<blocks, Cfg::THREADS, Cfg::SMEM, st>>>(qm, cm, P);
+    mla_decode_kernel<NH, DT><<<blocks * P.csplit, Cfg::THREADS, Cfg::SMEM, st>>>(qm, cm, P);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     note_launch(1);
     if (blocks > 1u) {
