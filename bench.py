@@ -201,16 +201,22 @@ class EndToEnd:
         self.h_q = host.value
         self.h_rows = host.value + self.q_bytes
         self.h_out = self.h_rows + 2 * wl.seqs * self.row_bytes
-        self.rows_dev = torch.zeros((2, wl.seqs, row), device="cuda", dtype=torch.bfloat16)
+        # the step's inputs land in ONE device buffer, as they lie in the host buffer: queries, then the newest K rows, then the V rows
+        # — one upload a step instead of two (a synchronous copy costs about 12 us before its first byte moves)
+        q_elems = self.q_bytes // 2
+        self.in_dev = torch.zeros((q_elems + 2 * wl.seqs * row,), device="cuda", dtype=torch.bfloat16)
+        self.in_dev[:q_elems].copy_(wl.q.reshape(-1))
+        wl.q = self.in_dev[:q_elems].view(wl.q.shape)
+        self.rows_dev = self.in_dev[q_elems:].view(2, wl.seqs, row)
+        self.k_rows, self.v_rows = self.rows_dev[0], self.rows_dev[1]
         self.h2d = self.q_bytes + 2 * wl.seqs * self.row_bytes
         self.d2h = self.o_bytes
 
     def step(self):
         wl, sysd, L = self.wl, self.fam.sys, self.wl.layout
         wl.plan.plan(L.seq_lens, L.q_heads, L.kv_heads, L.head_dim)
-        sysd.memory_write(wl.q.data_ptr(), self.h_q, self.q_bytes)
-        sysd.memory_write(self.rows_dev.data_ptr(), self.h_rows, 2 * wl.seqs * self.row_bytes)
-        wl.plan.append(wl.k_pool, wl.v_pool, self.rows_dev[0], self.rows_dev[1], L.pool_pages, wl.page_positions, wl.table, L.page_table.shape[1])
+        sysd.memory_write(self.in_dev.data_ptr(), self.h_q, self.h2d)
+        wl.plan.append(wl.k_pool, wl.v_pool, self.k_rows, self.v_rows, L.pool_pages, wl.page_positions, wl.table, L.page_table.shape[1])
         wl.step()
         sysd.memory_read(self.h_out, wl.out.data_ptr(), self.o_bytes)
 
