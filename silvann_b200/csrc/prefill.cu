@@ -107,7 +107,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     const int nt = last_key / PF_BN + 1;                                     /* KV tiles this row block walks */
 
     if (tid == 0) {
-        for (int s = 0; s < KST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+        for (int s = 0; s < KST; ++s) { mbar_init(&k_full[s], KST == NSB ? 2 : 1); mbar_init(&k_empty[s], 1); }
         for (int s = 0; s < VST; ++s) { mbar_init(&v_full[s], 1); mbar_init(&pv_done[s], 1); }
         for (int b = 0; b < NSB; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 8); mbar_init(&s_free[b], 1); }
         mbar_init(q_full, 1);
@@ -122,6 +122,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
 #pragma unroll
         for (int c = 0; c < Cfg::BOXES; ++c) tma_load_2d(q_s + c * Cfg::Q_BOX_BYTES, &qmap, q_full, h * D + c * 64, row0);
         mbar_expect_tx(&k_full[0], Cfg::KV_TILE_BYTES);
+        if (KST == NSB) mbar_arrive(&k_full[0]);
 #pragma unroll
         for (int c = 0; c < Cfg::BOXES; ++c) tma_load_2d(k_s + c * Cfg::KV_BOX_BYTES, &kmap, &k_full[0], g * D + c * 64, 0);
     }
@@ -153,8 +154,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             int jk = 1;
             auto load_k = [&]() -> bool {
                 const int s = jk % KST, use = jk / KST;
-                if (use > 0 && !mbar_wait(&k_empty[s], (use - 1) & 1, abort_flag, P.status)) return false;
+                /* with as many K stages as score buffers the two rings turn together: the scores' own barrier says the stage is read */
+                if (use > 0 && !mbar_wait(KST == NSB ? &s_full[s] : &k_empty[s], (use - 1) & 1, abort_flag, P.status)) return false;
                 mbar_expect_tx(&k_full[s], Cfg::KV_TILE_BYTES);
+                if (KST == NSB && jk < NSB) mbar_arrive(&k_full[s]);       /* no value MMA three tiles back to say that the score buffer is free */
 #pragma unroll
                 for (int c = 0; c < Cfg::BOXES; ++c)
                     tma_load_2d(k_s + s * Cfg::KV_TILE_BYTES + c * Cfg::KV_BOX_BYTES, &kmap, &k_full[s], g * D + c * 64, jk * PF_BN);
@@ -198,14 +201,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             for (int j = 0; ok && j < nt; ++j) {
                 const int s = j % KST, b = j % NSB;
                 if (!mbar_wait(&k_full[s], (j / KST) & 1, abort_flag, P.status)) break;
-                if (j >= NSB && !mbar_wait(&s_free[b], (j / NSB - 1) & 1, abort_flag, P.status)) break;
+                if (KST != NSB && j >= NSB && !mbar_wait(&s_free[b], (j / NSB - 1) & 1, abort_flag, P.status)) break;
                 tc_fence_after();
                 const uint32_t lo = kd_lo + (uint32_t)s * (Cfg::KV_TILE_BYTES >> 4), d_s = t_s0 + b * PF_BN;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk)      /* 16 columns a step: box kk/4, 32 bytes a step inside the 128-byte row */
                     tc_mma_ss2(d_s, qd_lo + (kk / 4) * (Cfg::Q_BOX_BYTES >> 4) + (kk % 4) * 2, qd_hi,
                                lo + (kk / 4) * (Cfg::KV_BOX_BYTES >> 4) + (kk % 4) * 2, kd_hi, IDESC_S, kk > 0 ? 1u : 0u);
-                tc_commit(&k_empty[s]);
+                if (KST != NSB) tc_commit(&k_empty[s]);
                 tc_commit(&s_full[b]);
             }
         }
@@ -227,7 +230,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 for (int kk = 0; kk < PF_BN / 16; ++kk)
                     tc_mma_ts2(t_o, a_p + kk * 8, lo + kk * (2048 >> 4), vd_hi, IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
                 tc_commit(&pv_done[s]);
-                tc_commit(&s_free[b]);
+                /* the score buffer is free again.  With as many K stages as score buffers that is the second of the two arrivals the
+                 * K stage's barrier waits for (tile j + NSB lands in stage b), so the score thread has ONE wait a tile */
+                if (KST != NSB) tc_commit(&s_free[b]);
+                else if (j + NSB < nt) tc_commit(&k_full[b]);
             }
         }
     } else {
