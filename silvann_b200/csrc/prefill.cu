@@ -10,7 +10,10 @@
  *               by the thread that initialises the barriers, ahead of the block's first barrier), then rings of K tiles and V
  *               tiles of 64 keys (128-byte swizzle; 3 + 2 stages at head_dim 256, 4 + 4 below).
  *   warp 1      one thread issues the score MMAs S = Q.K^T (M 128, N 64, K = head_dim in steps of 16, both operands in
- *               shared memory) into one of THREE score buffers in TMEM, so scores run two tiles ahead of the softmax.
+ *               shared memory) into one of three (four below head_dim 256) score buffers in TMEM, so scores run tiles
+ *               ahead of the softmax.  There are as many K stages as score buffers and the two rings turn together: a K
+ *               stage's barrier takes two arrivals, the tile's bytes and the completion of the value MMAs that read the
+ *               score buffer of the same index, so this thread has ONE wait and ONE commit a tile.
  *   warps 2-9   the online softmax, two warps a TMEM lane quadrant: a thread owns half of one query row (32 of the
  *               tile's 64 scores, read with tcgen05.ld), the two halves exchange max and sum through shared memory.
  *               The weights go back INTO TMEM, 16-bit, over the scores they came from (tcgen05.st), and are the A
@@ -49,12 +52,12 @@ template <int D> struct PrefillCfg {
     static constexpr int KV_BOX_BYTES = PF_BN * 128;
     static constexpr int KST = (D >= 256) ? 3 : 4;                   /* K ring: scores run two tiles ahead of the values */
     static constexpr int VST = (D >= 256) ? 2 : 4;                   /* V ring */
-    static constexpr int NSB = 3;                                    /* score buffers in TMEM */
+    static constexpr int NSB = (D >= 256) ? 3 : 4;                   /* score buffers in TMEM: as many as K stages, so that the two rings turn together */
     /* TMEM columns: O [0, D) fp32, then NSB score buffers of PF_BN columns whose first PF_BN/2 columns are overwritten
      * in place by the 16-bit weights P */
     static constexpr int T_S = D;
     static constexpr int TMEM_COLS = (T_S + NSB * PF_BN <= 256) ? 256 : 512;
-    static constexpr size_t SMEM = 1024 + Q_BYTES + (KST + VST) * KV_TILE_BYTES + 256 + 2 * PF_BM * 4;
+    static constexpr size_t SMEM = 1024 + Q_BYTES + (KST + VST) * KV_TILE_BYTES + 320 + 2 * PF_BM * 4;
 };
 
 struct PrefillParams {
@@ -95,7 +98,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     uint64_t* o_staged = xbar + 4;           /* 1: the eight softmax warps have put their share of the output rows into shared memory */
     uint32_t* tmem_slot = (uint32_t*)(o_staged + 1);
     volatile uint32_t* abort_flag = (volatile uint32_t*)(tmem_slot + 1);
-    float* xch = (float*)((uint8_t*)bars + 256);             /* [2][128]: the halves' normalisers at the end */
+    float* xch = (float*)((uint8_t*)bars + 320);             /* [2][128]: the halves' normalisers at the end */
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int qt = (int)P.q_tiles - 1 - (int)(blockIdx.x / P.q_heads);       /* heaviest row blocks first */
@@ -157,7 +160,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 /* with as many K stages as score buffers the two rings turn together: the scores' own barrier says the stage is read */
                 if (use > 0 && !mbar_wait(KST == NSB ? &s_full[s] : &k_empty[s], (use - 1) & 1, abort_flag, P.status)) return false;
                 mbar_expect_tx(&k_full[s], Cfg::KV_TILE_BYTES);
-                if (KST == NSB && jk < NSB) mbar_arrive(&k_full[s]);       /* no value MMA three tiles back to say that the score buffer is free */
+                if (KST == NSB && jk < NSB) mbar_arrive(&k_full[s]);       /* no value MMA NSB tiles back to say that the score buffer is free */
 #pragma unroll
                 for (int c = 0; c < Cfg::BOXES; ++c)
                     tma_load_2d(k_s + s * Cfg::KV_TILE_BYTES + c * Cfg::KV_BOX_BYTES, &kmap, &k_full[s], g * D + c * 64, jk * PF_BN);
@@ -190,8 +193,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         /* ---------------- score MMAs: S(j) = Q · K(j)^T ----------------
          * Two threads issue MMAs, this one the scores and one of warp 10 the values, because a thread that waits on an
          * mbarrier (about a hundred cycles even when the phase is long complete) feeds the tensor pipe nothing meanwhile
-         * and the pipe's queue is short: with one issuer every wait is a bubble.  Scores run up to three tiles ahead
-         * (three TMEM buffers); a buffer is reused once the value MMA that read its weights has completed. */
+         * and the pipe's queue is short: with one issuer every wait is a bubble.  Scores run up to NSB tiles ahead; a
+         * buffer is reused once the value MMA that read its weights has completed, which the K stage's barrier also waits
+         * for (measured: each wait or commit taken off this thread's tile was worth 2-4 % of the whole kernel). */
         if (lane == 0) {
             constexpr uint32_t IDESC_S = idesc_f16(DT == SV_DTYPE_BF16, 0, PF_BM, PF_BN);
             /* descriptors of stage 0; a stage further is KV_TILE_BYTES >> 4 more in the start-address field */
