@@ -42,7 +42,7 @@ namespace sv {
 
 static constexpr int PF_BM = 128;      /* query rows per block */
 static constexpr int PF_BN = 64;       /* keys per tile */
-static constexpr int PF_THREADS = 352; /* warp 0 TMA, warp 1 score MMAs, warps 2-9 softmax (two per TMEM lane quadrant), warp 10 value MMAs */
+static constexpr int PF_THREADS = 384; /* warp 0 TMA, warp 1 score MMAs, warps 2-9 softmax (two per TMEM lane quadrant), warp 10 value MMAs, warp 11 the score thread's scout */
 
 template <int D> struct PrefillCfg {
     static constexpr int BOXES = D / 64;
@@ -57,6 +57,7 @@ template <int D> struct PrefillCfg {
      * in place by the 16-bit weights P */
     static constexpr int T_S = D;
     static constexpr int TMEM_COLS = (T_S + NSB * PF_BN <= 256) ? 256 : 512;
+    static_assert(KST == NSB, "the K ring and the score buffers turn together");
     static constexpr size_t SMEM = 1024 + Q_BYTES + (KST + VST) * KV_TILE_BYTES + 320 + 2 * PF_BM * 4;
 };
 
@@ -79,6 +80,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     using Cfg = PrefillCfg<D>;
     using E = Elem<DT>;
     constexpr int KST = Cfg::KST, VST = Cfg::VST, NSB = Cfg::NSB;
+    constexpr bool SCOUT = D >= 256;         /* the score thread's waits are taken by another warp (see warp 1) */
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -196,25 +198,47 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
          * and the pipe's queue is short: with one issuer every wait is a bubble.  Scores run up to NSB tiles ahead; a
          * buffer is reused once the value MMA that read its weights has completed, which the K stage's barrier also waits
          * for (measured: each wait or commit taken off this thread's tile was worth 2-4 % of the whole kernel). */
-        if (lane == 0) {
-            constexpr uint32_t IDESC_S = idesc_f16(DT == SV_DTYPE_BF16, 0, PF_BM, PF_BN);
-            /* descriptors of stage 0; a stage further is KV_TILE_BYTES >> 4 more in the start-address field */
-            const uint64_t qd0 = smem_desc_sw128(smem_u32(q_s), 16, 1024), kd0 = smem_desc_sw128(smem_u32(k_s), 16, 1024);
-            const uint32_t qd_lo = (uint32_t)qd0, qd_hi = (uint32_t)(qd0 >> 32), kd_lo = (uint32_t)kd0, kd_hi = (uint32_t)(kd0 >> 32);
-            bool ok = mbar_wait(q_full, 0, abort_flag, P.status);
-            for (int j = 0; ok && j < nt; ++j) {
-                const int s = j % KST, b = j % NSB;
-                if (!mbar_wait(&k_full[s], (j / KST) & 1, abort_flag, P.status)) break;
-                if (KST != NSB && j >= NSB && !mbar_wait(&s_free[b], (j / NSB - 1) & 1, abort_flag, P.status)) break;
+        /* This thread's own waits are not on mbarriers at all.  Any access of its to shared memory — an mbarrier try, a plain load
+         * — takes 100-200 cycles while the MMAs' operand reads own the port, and nothing is issued meanwhile.  The scout (warp 11)
+         * takes the tile's mbarrier waits a tile ahead and says so on a hardware barrier (bar 1: the scout arrives, this warp
+         * syncs); this warp says on bar 2 that it has taken the word, which lets the scout go on to the next tile.  A barrier's
+         * generation is the scout's 32 threads and this warp's 32, and neither side can be two generations ahead of the other.
+         * Should a wait of the scout's run out it still arrives, for every tile left, so that nothing here waits for ever: the
+         * status word says "B2TO" and the block's answer is void. */
+        constexpr uint32_t IDESC_S = idesc_f16(DT == SV_DTYPE_BF16, 0, PF_BM, PF_BN);
+        /* descriptors of stage 0; a stage further is KV_TILE_BYTES >> 4 more in the start-address field */
+        const uint64_t qd0 = smem_desc_sw128(smem_u32(q_s), 16, 1024), kd0 = smem_desc_sw128(smem_u32(k_s), 16, 1024);
+        const uint32_t qd_lo = (uint32_t)qd0, qd_hi = (uint32_t)(qd0 >> 32), kd_lo = (uint32_t)kd0, kd_hi = (uint32_t)(kd0 >> 32);
+        for (int j = 0; j < nt; ++j) {
+            const int s = j % KST, b = j % NSB;
+            if (SCOUT) {
+                asm volatile("bar.sync 1, 64;" ::: "memory");
+                asm volatile("bar.arrive 2, 64;" ::: "memory");
+            } else if (lane == 0) {
+                /* (below head_dim 256 the softmax, not this thread, paces the block, and the plain wait measured as fast) */
+                if (j == 0) (void)mbar_wait(q_full, 0, abort_flag, P.status);
+                (void)mbar_wait(&k_full[s], (j / KST) & 1, abort_flag, P.status);
+            }
+            if (lane == 0) {
                 tc_fence_after();
                 const uint32_t lo = kd_lo + (uint32_t)s * (Cfg::KV_TILE_BYTES >> 4), d_s = t_s0 + b * PF_BN;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk)      /* 16 columns a step: box kk/4, 32 bytes a step inside the 128-byte row */
                     tc_mma_ss2(d_s, qd_lo + (kk / 4) * (Cfg::Q_BOX_BYTES >> 4) + (kk % 4) * 2, qd_hi,
                                lo + (kk / 4) * (Cfg::KV_BOX_BYTES >> 4) + (kk % 4) * 2, kd_hi, IDESC_S, kk > 0 ? 1u : 0u);
-                if (KST != NSB) tc_commit(&k_empty[s]);
                 tc_commit(&s_full[b]);
             }
+            __syncwarp();
+        }
+    } else if (warp == 11) {
+        /* ---------------- the score thread's scout: Q, then a tile's K stage (its bytes, and the score buffer free) ---------------- */
+        bool ok = true;
+        if (SCOUT && lane == 0) ok = mbar_wait(q_full, 0, abort_flag, P.status);
+        for (int j = 0; SCOUT && j < nt; ++j) {
+            if (lane == 0 && ok) ok = mbar_wait(&k_full[j % KST], (j / KST) & 1, abort_flag, P.status);
+            __syncwarp();
+            asm volatile("bar.arrive 1, 64;" ::: "memory");
+            asm volatile("bar.sync 2, 64;" ::: "memory");
         }
     } else if (warp == 10) {
         /* ---------------- value MMAs: O += P(j) · V(j), P read from TMEM in place over the scores ---------------- */
