@@ -42,7 +42,7 @@ namespace sv {
 
 static constexpr int PF_BM = 128;      /* query rows per block */
 static constexpr int PF_BN = 64;       /* keys per tile */
-static constexpr int PF_THREADS = 384; /* warp 0 TMA, warp 1 score MMAs, warps 2-9 softmax (two per TMEM lane quadrant), warp 10 value MMAs, warp 11 the score thread's scout */
+static constexpr int PF_THREADS = 640; /* warp 0 TMA, warp 1 score MMAs, warp 2 value MMAs, warp 3 the score thread's scout, warps 4-19 softmax (four per TMEM lane quadrant) */
 
 template <int D> struct PrefillCfg {
     static constexpr int BOXES = D / 64;
@@ -58,6 +58,8 @@ template <int D> struct PrefillCfg {
     static constexpr int T_S = D;
     static constexpr int TMEM_COLS = (T_S + NSB * PF_BN <= 256) ? 256 : 512;
     static_assert(KST == NSB, "the K ring and the score buffers turn together");
+    static constexpr int T_X = T_S + NSB * PF_BN;                    /* 8 columns (two tiles' worth of 4) through which a row's four softmax threads exchange maxima and sums */
+    static_assert(T_X + 8 <= TMEM_COLS, "TMEM columns");
     static constexpr size_t SMEM = 1024 + Q_BYTES + (KST + VST) * KV_TILE_BYTES + 320 + 2 * PF_BM * 4;
 };
 
@@ -100,7 +102,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     uint64_t* o_staged = xbar + 4;           /* 1: the eight softmax warps have put their share of the output rows into shared memory */
     uint32_t* tmem_slot = (uint32_t*)(o_staged + 1);
     volatile uint32_t* abort_flag = (volatile uint32_t*)(tmem_slot + 1);
-    float* xch = (float*)((uint8_t*)bars + 320);             /* [2][128]: the halves' normalisers at the end */
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int qt = (int)P.q_tiles - 1 - (int)(blockIdx.x / P.q_heads);       /* heaviest row blocks first */
@@ -114,10 +115,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     if (tid == 0) {
         for (int s = 0; s < KST; ++s) { mbar_init(&k_full[s], KST == NSB ? 2 : 1); mbar_init(&k_empty[s], 1); }
         for (int s = 0; s < VST; ++s) { mbar_init(&v_full[s], 1); mbar_init(&pv_done[s], 1); }
-        for (int b = 0; b < NSB; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 8); mbar_init(&s_free[b], 1); }
+        for (int b = 0; b < NSB; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 16); mbar_init(&s_free[b], 1); }
         mbar_init(q_full, 1);
         for (int x = 0; x < 4; ++x) mbar_init(&xbar[x], 2);
-        mbar_init(o_staged, 8);
+        mbar_init(o_staged, 16);
         *abort_flag = 0u;
         mbar_fence_init();
         /* Q and the first K tile are asked for here, ahead of the TMEM allocation and the block's first barrier: the
@@ -230,7 +231,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             }
             __syncwarp();
         }
-    } else if (warp == 11) {
+    } else if (warp == 3) {
         /* ---------------- the score thread's scout: Q, then a tile's K stage (its bytes, and the score buffer free) ---------------- */
         bool ok = true;
         if (SCOUT && lane == 0) ok = mbar_wait(q_full, 0, abort_flag, P.status);
@@ -240,7 +241,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             asm volatile("bar.arrive 1, 64;" ::: "memory");
             asm volatile("bar.sync 2, 64;" ::: "memory");
         }
-    } else if (warp == 10) {
+    } else if (warp == 2) {
         /* ---------------- value MMAs: O += P(j) · V(j), P read from TMEM in place over the scores ---------------- */
         if (lane == 0) {
             constexpr uint32_t IDESC_O = idesc_f16(DT == SV_DTYPE_BF16, 1, PF_BM, D);
@@ -266,54 +267,68 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         }
     } else {
         /* ---------------- softmax, correction, epilogue ----------------
-         * Eight warps: a warp may touch only the 32 TMEM lanes of its quadrant (warp id mod 4), so two warps share each
-         * quadrant.  Both read a row's 64 scores (the row maximum needs them all, and reading twice is cheaper than
-         * exchanging), each turns its own 32 columns into weights, carries the normaliser of its half, and owns half of
-         * O's columns when a rescale or the final store is due. */
-        const int sw = warp - 2;                                    /* 0..7 */
-        const int quad = warp & 3, half = sw >> 2;
+         * Sixteen warps: a warp may touch only the 32 TMEM lanes of its quadrant (warp id mod 4), so four warps share each
+         * quadrant and a thread owns 16 of its row's 64 scores.  The row maximum needs all 64: each thread leaves the
+         * maximum of its 16 in a TMEM column of its own lane, the quadrant's four warps meet at a hardware barrier, and each
+         * reads the four (neither shared memory nor an mbarrier is touched: both cost 100-200 cycles a visit while the
+         * MMAs' operand reads own the shared-memory port).  The same barrier says that every warp has read its scores, so
+         * the weights may go over them.  The exponentials are what bounds this role (sixteen a cycle an SM), and four warps
+         * a scheduler keep that unit busy where two left it idle a third of the time.  A thread carries the normaliser of
+         * its 16 columns and owns a quarter of O's columns when a rescale or the final store is due.
+         * The quadrant's barrier is not bounded, so its four warps go through it together whatever happens: a warp whose
+         * wait ran out walks the remaining tiles as a bystander, touching nothing but the barrier. */
+        const int sw = warp - 4;                                    /* 0..15 */
+        const int quad = warp & 3, part = sw >> 2;
         const int r = quad * 32 + lane;                             /* row within the block */
         const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+        const uint32_t t_x = tmem + Cfg::T_X + lane_off;
         const int grow_ = row0 + r;                                 /* row of the call */
         const int pos = (int)P.first + grow_;                       /* this row's position: keys 0..pos */
+        const uint32_t qbar = 3u + (uint32_t)quad;                  /* bars 1 and 2 are the score thread's */
+        constexpr int OC = D / 4;                                   /* O's columns a thread */
+        constexpr int CH = OC >= 32 ? 32 : 16;                      /* ... read 32 (or 16) at a time */
 
         float m_ref = -INFINITY, l = 0.f;
         bool alive = true;
         for (int j = 0; j < nt; ++j) {
             const int b = j % NSB;
-            /* the TMEM accesses below are warp-collective: the warp leaves the loop together or not at all */
-            if (!__all_sync(0xffffffffu, mbar_wait(&s_full[b], (j / NSB) & 1, abort_flag, P.status))) { alive = false; break; }
-            tc_fence_after();
-            uint32_t sv[2][32];
-            tmem_ld32(t_s0 + b * PF_BN + lane_off, sv[0]);
-            tmem_ld32(t_s0 + b * PF_BN + 32 + lane_off, sv[1]);
-            tmem_wait_ld();
-            /* the partner warp may overwrite these columns with its weights once it knows they have been read */
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&xbar[quad]);
-
-            const int key0 = j * PF_BN;
-            if (key0 + PF_BN - 1 > pos) {                           /* keys of this tile lie past the row's position */
+            /* the TMEM accesses below are warp-collective: the warp goes on together or stands by together */
+            if (alive && !__all_sync(0xffffffffu, mbar_wait(&s_full[b], (j / NSB) & 1, abort_flag, P.status))) alive = false;
+            uint32_t sv[16];
+            if (alive) {
+                tc_fence_after();
+                tmem_ld16(t_s0 + b * PF_BN + part * 16 + lane_off, sv);
+                tmem_wait_ld();
+                const int key0 = j * PF_BN + part * 16;
+                if (key0 + 15 > pos) {                              /* keys of this tile lie past the row's position */
 #pragma unroll
-                for (int c = 0; c < 64; ++c) if (key0 + c > pos) sv[c >> 5][c & 31] = 0xFF800000u;   /* -inf */
+                    for (int c = 0; c < 16; ++c) if (key0 + c > pos) sv[c] = 0xFF800000u;   /* -inf */
+                }
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int c = 0; c < 16; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
+                tmem_st1(t_x + (j & 1) * 4 + part, __float_as_uint(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]))));
+                tmem_wait_st();
+                tc_fence_before();
             }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c >> 5][c & 31]));
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * P.scale_log2;
+            asm volatile("bar.sync %0, 128;" ::"r"(qbar) : "memory");
+            if (!alive) continue;
+            tc_fence_after();
+            uint32_t xm[4];
+            tmem_ld4(t_x + (j & 1) * 4, xm);
+            tmem_wait_ld();
+            const float mx = fmaxf(fmaxf(__uint_as_float(xm[0]), __uint_as_float(xm[1])), fmaxf(__uint_as_float(xm[2]), __uint_as_float(xm[3]))) * P.scale_log2;
             /* keep the reference maximum unless this tile's exceeds it by more than 8 (weights then stay <= 2^8) */
             float f = 1.f;
             const bool grow = (mx > m_ref + 8.f) || (m_ref == -INFINITY && mx != -INFINITY);
             if (grow) { f = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - mx); m_ref = mx; }
             const float mu = (m_ref == -INFINITY) ? 0.f : m_ref;
-            uint32_t pk[16];
+            uint32_t pk[8];
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < 32; c += 2) {
-                const float s0 = __uint_as_float(half ? sv[1][c] : sv[0][c]), s1 = __uint_as_float(half ? sv[1][c + 1] : sv[0][c + 1]);
-                const float p0 = fast_exp2(fmaf(s0, P.scale_log2, -mu));
-                const float p1 = fast_exp2(fmaf(s1, P.scale_log2, -mu));
+            for (int c = 0; c < 16; c += 2) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c]), P.scale_log2, -mu));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c + 1]), P.scale_log2, -mu));
                 const uint32_t w = E::pack2(p0, p1);
                 const float2 back = E::unpack2(w);                  /* the normaliser sums what the MMA will see */
                 sum4[(c >> 1) & 3] += back.x + back.y;
@@ -323,37 +338,44 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
 
             if (j > 0 && __any_sync(0xffffffffu, f != 1.f)) {
                 /* O may be rescaled only between PV MMAs: the previous one must have completed, the next waits for us */
-                if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) % VST], ((j - 1) / VST) & 1, abort_flag, P.status))) { alive = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) % VST], ((j - 1) / VST) & 1, abort_flag, P.status))) { alive = false; continue; }
                 tc_fence_after();
 #pragma unroll 1
-                for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {      /* each warp of the pair half of O's columns */
-                    uint32_t ov[32];
-                    tmem_ld32(t_o + c0 + lane_off, ov);
+                for (int c0 = part * OC; c0 < (part + 1) * OC; c0 += CH) {      /* each warp of the four a quarter of O's columns */
+                    uint32_t ov[CH];
+                    if (CH == 32) tmem_ld32(t_o + c0 + lane_off, *reinterpret_cast<uint32_t(*)[32]>(ov)); else tmem_ld16(t_o + c0 + lane_off, *reinterpret_cast<uint32_t(*)[16]>(ov));
                     tmem_wait_ld();
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * f);
-                    tmem_st32(t_o + c0 + lane_off, ov);
+                    for (int c = 0; c < CH; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * f);
+                    if (CH == 32) tmem_st32(t_o + c0 + lane_off, *reinterpret_cast<uint32_t(*)[32]>(ov)); else tmem_st16(t_o + c0 + lane_off, *reinterpret_cast<uint32_t(*)[16]>(ov));
                 }
                 tmem_wait_st();
             }
-            /* P over the scores, in place: 32 weights = 16 packed columns at this half's place, once the partner has read */
-            if (!__all_sync(0xffffffffu, mbar_wait(&xbar[quad], j & 1, abort_flag, P.status))) { alive = false; break; }
-            tmem_st16(t_s0 + b * PF_BN + half * 16 + lane_off, pk);
+            /* P over the scores, in place: 16 weights = 8 packed columns at this part's place (every warp of the quadrant has
+             * read its scores: the barrier above) */
+            tmem_st8(t_s0 + b * PF_BN + part * 8 + lane_off, pk);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full[b]);
         }
-        /* epilogue: the row's normaliser is the sum of its two halves'; O / l, rounded, to global — each warp of the pair
-         * writes half of the row, which is contiguous in the output */
-        if (alive && __all_sync(0xffffffffu, mbar_wait(&pv_done[(nt - 1) % VST], ((nt - 1) / VST) & 1, abort_flag, P.status))) {
+        /* epilogue: the row's normaliser is the sum of its four parts' (through the same TMEM columns, in a fixed order);
+         * O / l, rounded, to global — each warp of the four a quarter of the row */
+        const bool fin = alive && __all_sync(0xffffffffu, mbar_wait(&pv_done[(nt - 1) % VST], ((nt - 1) / VST) & 1, abort_flag, P.status));
+        if (fin) {
             tc_fence_after();
-            xch[half * PF_BM + r] = l;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&xbar[quad]);
-            const bool met = __all_sync(0xffffffffu, mbar_wait(&xbar[quad], nt & 1, abort_flag, P.status));
-            const float l_row = met ? l + xch[(half ^ 1) * PF_BM + r] : 0.f;
-            const float inv = met ? 1.0f / l_row : 0.f;
+            tmem_st1(t_x + (nt & 1) * 4 + part, __float_as_uint(l));
+            tmem_wait_st();
+            tc_fence_before();
+        }
+        asm volatile("bar.sync %0, 128;" ::"r"(qbar) : "memory");
+        if (fin) {
+            tc_fence_after();
+            uint32_t xl[4];
+            tmem_ld4(t_x + (nt & 1) * 4, xl);
+            tmem_wait_ld();
+            const float l_row = (__uint_as_float(xl[0]) + __uint_as_float(xl[1])) + (__uint_as_float(xl[2]) + __uint_as_float(xl[3]));
+            const float inv = 1.0f / l_row;
             bool hit = false;
             /* The 16-bit rows leave through shared memory and one TMA store a 64-column box: written straight from the
              * registers, a warp's store would touch 32 rows (32 lines for 512 bytes) and the block's 4,096 such line visits
@@ -365,22 +387,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             /* the residual form of the answer: (m, l, acc) as attention_weights_rows + attention_residual_mix_rows leave
              * it — m is the reference the weights were taken against (natural-log units), acc is not divided */
             float* rrow = P.res ? P.res + ((size_t)grow_ * P.q_heads + h) * (D + 2) : nullptr;
-            if (rrow && met && half == 0 && grow_ < (int)P.rows) { rrow[0] = m_ref * SV_LN2; rrow[1] = l_row; }
+            if (rrow && part == 0 && grow_ < (int)P.rows) { rrow[0] = m_ref * SV_LN2; rrow[1] = l_row; }
 #pragma unroll 1
-            for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
-                uint32_t ov[32];
-                tmem_ld32(t_o + c0 + lane_off, ov);
+            for (int c0 = part * OC; c0 < (part + 1) * OC; c0 += CH) {
+                uint32_t ov[CH];
+                if (CH == 32) tmem_ld32(t_o + c0 + lane_off, *reinterpret_cast<uint32_t(*)[32]>(ov)); else tmem_ld16(t_o + c0 + lane_off, *reinterpret_cast<uint32_t(*)[16]>(ov));
                 tmem_wait_ld();
                 if (rrow && grow_ < (int)P.rows) {
 #pragma unroll
-                    for (int c = 0; c < 32; c += 2) *reinterpret_cast<float2*>(rrow + 2 + c0 + c) = make_float2(__uint_as_float(ov[c]), __uint_as_float(ov[c + 1]));
+                    for (int c = 0; c < CH; c += 2) *reinterpret_cast<float2*>(rrow + 2 + c0 + c) = make_float2(__uint_as_float(ov[c]), __uint_as_float(ov[c + 1]));
                 }
                 if (P.o && grow_ < (int)P.rows) {
                     /* rounded two at a time; the overflow rule (a finite value that lands on infinity) is looked at a value
-                     * at a time only when the largest magnitude of the 32 says that it can have happened */
+                     * at a time only when the largest magnitude of the chunk says that it can have happened */
                     float top = 0.f;
 #pragma unroll
-                    for (int c = 0; c < 32; c += 8) {
+                    for (int c = 0; c < CH; c += 8) {
                         uint32_t w[4];
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
@@ -393,7 +415,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                     }
                     if (top >= E::over_from()) {
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) (void)E::from_float(__uint_as_float(ov[c]) * inv, hit);
+                        for (int c = 0; c < CH; ++c) (void)E::from_float(__uint_as_float(ov[c]) * inv, hit);
                     }
                 }
             }
@@ -403,7 +425,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 tma_store_fence();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(o_staged);
-                /* one thread sends the boxes once all eight warps have staged theirs; rows past the call's end are cut off
+                /* one thread sends the boxes once all sixteen warps have staged theirs; rows past the call's end are cut off
                  * by the tensor map (they were not staged either) */
                 if (sw == 0 && lane == 0 && mbar_wait(o_staged, 0, abort_flag, P.status)) {
 #pragma unroll
