@@ -5,7 +5,7 @@
  * rows x (first + rows) fp32 weights buffer they pass between them.  Row r of the call is position first + r and attends
  * cache rows 0 .. first + r; query head h reads kv head h / (q_heads / kv_heads).
  *
- * A block owns 128 query rows of one head; 11 warps in four roles.
+ * A block owns 128 query rows of one head; 20 warps in five roles.
  *   warp 0      TMA: Q once (128 x head_dim, kept in shared memory for the whole block; asked for with the first K tile
  *               by the thread that initialises the barriers, ahead of the block's first barrier), then rings of K tiles and V
  *               tiles of 64 keys (128-byte swizzle; 3 + 2 stages at head_dim 256, 4 + 4 below).
@@ -13,23 +13,28 @@
  *               shared memory) into one of three (four below head_dim 256) score buffers in TMEM, so scores run tiles
  *               ahead of the softmax.  There are as many K stages as score buffers and the two rings turn together: a K
  *               stage's barrier takes two arrivals, the tile's bytes and the completion of the value MMAs that read the
- *               score buffer of the same index, so this thread has ONE wait and ONE commit a tile.
- *   warps 2-9   the online softmax, two warps a TMEM lane quadrant: a thread owns half of one query row (32 of the
- *               tile's 64 scores, read with tcgen05.ld), the two halves exchange max and sum through shared memory.
- *               The weights go back INTO TMEM, 16-bit, over the scores they came from (tcgen05.st), and are the A
- *               operand of the value MMA there: P never touches shared memory.  O is rescaled in TMEM only when a
- *               row's maximum has grown by more than 2^8 (the reference maximum is otherwise kept, which is exact:
- *               every weight and the normaliser are relative to the same reference).
- *   warp 10     one thread issues the value MMAs O += P.V (M 128, N = head_dim, K 64; A from TMEM, B MN-major from
+ *               score buffer of the same index, so this thread has ONE wait and ONE commit a tile — and at head_dim 256
+ *               the wait is not its own either (warp 3).
+ *   warp 2      one thread issues the value MMAs O += P.V (M 128, N = head_dim, K 64; A from TMEM, B MN-major from
  *               shared memory) with O resident in TMEM for the whole row block.
- * Two issuing threads because the MMA queue is shallow and a satisfied mbarrier wait costs ~100 cycles: with one thread
- * every wait for the softmax was a bubble in the tensor pipe.  TMEM columns: O in [0, head_dim), score buffer b at
- * head_dim + 64 b.  The epilogue divides by the row sum and rounds; the 16-bit rows are staged in the K ring (free by then,
- * in the swizzled box layout TMA reads) and leave as one TMA store a 64-column box — or (m ln 2, l, acc) a row is left in
- * the reference's residual layout (the many-row residual doors).
+ *   warp 3      the score thread's scout: takes that thread's mbarrier waits a tile ahead and hands them over on a
+ *               hardware barrier (an mbarrier try costs the issuing thread 100-200 cycles while MMAs read their operands).
+ *   warps 4-19  the online softmax, four warps a TMEM lane quadrant: a thread owns 16 of its row's 64 scores (read with
+ *               tcgen05.ld); the four exchange their maxima, and at the end their sums, through spare TMEM columns and a
+ *               hardware barrier.  The weights go back INTO TMEM, 16-bit, over the scores they came from (tcgen05.st), and
+ *               are the A operand of the value MMA there: P never touches shared memory.  O is rescaled in TMEM only when
+ *               a row's maximum has grown by more than 2^8 (the reference maximum is otherwise kept, which is exact:
+ *               every weight and the normaliser are relative to the same reference).
+ * Two issuing threads because the MMA queue is shallow: with one thread every wait for the softmax was a bubble in the
+ * tensor pipe.  TMEM columns: O in [0, head_dim), score buffer b at head_dim + 64 b, then 8 columns for the softmax's
+ * exchanges.  The epilogue divides by the row sum and rounds; the 16-bit rows are staged in the K ring (free by then, in the
+ * swizzled box layout TMA reads) and leave as one TMA store a 64-column box — or (m ln 2, l, acc) a row is left in the
+ * reference's residual layout (the many-row residual doors).
  *
  * Every mbarrier wait is bounded; a wait that runs out raises the block's abort flag, ORs "B2TO" into the device status
- * word, and every role falls through to the common exit, where TMEM is released.  No multicast, no cluster.
+ * word, and the role goes on without touching anything else until the common exit, where TMEM is released.  The hardware
+ * barriers have no bound of their own: the warps that meet at one go through it the same number of times whatever
+ * happens.  No multicast, no cluster.
  *
  * Algorithmic flops: 4 · q_heads · head_dim · rows·(rows+1)/2 (+ first·rows terms) — QK^T and PV, 2 flop a MAC. */
 #include "common.cuh"
