@@ -181,7 +181,6 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
     if (warp == GV_WARPS) {
         /* ---- the fetching warp: the table, then slot after slot as the working warps hand them back ---- */
         const uint64_t policy = l2_policy_evict_first();
-        if (lane == 0) { mbar_expect_tx(table_bar, GV_LUT_BYTES); gv_bulk(lut, g_gv_lut_image, GV_LUT_BYTES, table_bar, l2_policy_evict_last()); }
         uint32_t m = 0;                                                      /* slots filled so far */
         int gi = -1;
         uint32_t hi = 0, lo = 0, row_bytes = 0, rows = 0, halves = 1, seg = 0;
@@ -205,11 +204,29 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
         return;                                                              /* nothing after this point waits for the fetching warp */
     }
 
-    /* ---- the sixteen working warps ---- */
+    /* ---- the sixteen working warps ----
+     * They make the table themselves while the first slots are on their way: eight 16-byte stores a thread, where a copy of
+     * the 64 KB image would take the block's first 1,150 cycles of copy-in (copies enter an SM at about 57 B/clk) ahead of
+     * the codes that the work waits for. */
+    {
+        static_assert(256 * 16 % GV_THREADS == 0, "a whole number of entries' pieces a thread");
+        constexpr int PER = 256 * 16 / GV_THREADS;
+        uint32_t e[PER];
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {                                      /* the levels first, all asked for at once */
+            const uint32_t i = (uint32_t)tid + (uint32_t)k * GV_THREADS, b = i >> 4, q = i & 15u;
+            const uint32_t lo16 = g_tq_levels_gemv[q < 8u ? 14u + (b & 15u) : 62u + b], hi16 = g_tq_levels_gemv[q < 8u ? 14u + (b >> 4) : 62u + b];
+            e[k] = lo16 | (hi16 << 16);
+        }
+#pragma unroll
+        for (int k = 0; k < PER; ++k)
+            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(lut + ((uint32_t)tid + (uint32_t)k * GV_THREADS) * 16u), "r"(e[k]) : "memory");
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(GV_THREADS) : "memory");
     const uint32_t at4 = lut | ((uint32_t)lane * 4u), at8 = at4 + 128u;     /* the 4-bit pair table, then the 8-bit one, in every entry */
     uint32_t xr[NIW][16];                                                    /* this lane's B fragments: input g, the columns of its bytes */
     uint32_t have_d = 0, n = 0, m = 0;
-    bool table_ready = false, failed = false;
+    bool failed = false;
     int buf = 0;
     bool hit = false;
     int gi = -1;
@@ -257,7 +274,6 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
             for (uint32_t h = 0; h < halves; ++h, ++m) {
                 const uint32_t slot = m % S;
                 bool landed = failed ? false : mbar_wait(&full[slot], (m / S) & 1u, abort_flag, a.status);
-                if (!table_ready && landed) { landed = mbar_wait(table_bar, 0u, abort_flag, a.status); table_ready = true; }
                 if (!landed) { failed = true; continue; }                    /* said at the step's barrier: every warp leaves there, or none */
                 const uint32_t stride = seg + GV_ROW_PAD, at_a = stage_at_s[slot] + (uint32_t)t * 16u + (uint32_t)g * stride, at_b = at_a + 8u * stride;
 #pragma unroll
