@@ -133,15 +133,38 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NW); }
         *abort_flag = 0u;
         mbar_fence_init();
+        /* the ring's first fill is asked for here, ahead of the table and the block's first barrier: the codes are what the
+         * work waits for, and nothing has to be free for them yet */
+        if (nt > 0) {
+            tma_prefetch_desc(&kmap); tma_prefetch_desc(&vmap);
+            const uint64_t pol = l2_policy_evict_first();
+            for (int it = 0; it < Cfg::STAGES && it < nt; ++it) {
+                const int pos0 = (tile_begin + it) * BT;
+                uint8_t* st = stage_base + it * Cfg::STAGE;
+                mbar_expect_tx(&full[it], Cfg::STAGE);
+#pragma unroll
+                for (int c = 0; c < Cfg::BOXES; ++c)
+                    tma_load_2d_hint(st + c * (BT * Cfg::BOX), &kmap, &full[it], kvh * Cfg::RB + c * Cfg::BOX, pos0, pol);
+#pragma unroll
+                for (int c = 0; c < Cfg::BOXES; ++c)
+                    tma_load_2d_hint(st + Cfg::TILE + c * (BT * Cfg::BOX), &vmap, &full[it], kvh * Cfg::RB + c * Cfg::BOX, pos0, pol);
+            }
+        }
     }
     /* the level table, every entry once a bank: [byte][bank], 256 bytes an entry.  8 bits: the byte's level in both halves.  4 bits: the
-     * low nibble's level in the low half, the high nibble's in the high half. */
-    for (int i = tid; i < 256 * 32; i += THREADS) {
-        const int b = i >> 5;
-        uint32_t e;
-        if (W == 8) { const uint32_t l = g_tq_levels_fused[62 + b]; e = l | (l << 16); }
-        else e = (uint32_t)g_tq_levels_fused[14 + (b & 15)] | ((uint32_t)g_tq_levels_fused[14 + (b >> 4)] << 16);
-        lut[b * 64 + (i & 31)] = e;
+     * low nibble's level in the low half, the high nibble's in the high half.  A thread's levels are all asked for before the
+     * first is stored: one trip to memory, not one a word. */
+    {
+        constexpr int PER = (256 * 32 + THREADS - 1) / THREADS;
+        uint32_t e[PER];
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int b = min((tid + k * THREADS) >> 5, 255);
+            if (W == 8) { const uint32_t l = g_tq_levels_fused[62 + b]; e[k] = l | (l << 16); }
+            else e[k] = (uint32_t)g_tq_levels_fused[14 + (b & 15)] | ((uint32_t)g_tq_levels_fused[14 + (b >> 4)] << 16);
+        }
+#pragma unroll
+        for (int k = 0; k < PER; ++k) { const int i = tid + k * THREADS; if (i < 256 * 32) lut[(i >> 5) * 64 + (i & 31)] = e[k]; }
     }
     for (int i = tid; i < HPB * (DH / 4); i += THREADS) {           /* 8 bytes a step */
         const int h = i / (DH / 4), e = (i % (DH / 4)) * 4;
@@ -163,10 +186,9 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     if (warp == NW) {
         /* ---- producer: one lane issues every TMA load of this block ---- */
         if (lane == 0 && nt > 0) {
-            tma_prefetch_desc(&kmap); tma_prefetch_desc(&vmap);
             const uint64_t pol = l2_policy_evict_first();
-            int issued = 0;
-            for (int it = 0; it < nt; ++it, ++issued) {
+            int issued = min((int)Cfg::STAGES, nt);                 /* the first fill is on its way */
+            for (int it = issued; it < nt; ++it, ++issued) {
                 const int s = it % Cfg::STAGES;
                 if (it >= Cfg::STAGES && !mbar_wait(&empty[s], ((it / Cfg::STAGES) - 1) & 1, abort_flag, P.status)) break;
                 const int pos0 = (tile_begin + it) * BT;
