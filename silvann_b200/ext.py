@@ -145,7 +145,12 @@ class Plan:
             pass
 
     def plan(self, seq_lens, q_heads, kv_heads, head_dim, blocks_target=0, stream=None):
-        arr = (C.c_int32 * len(seq_lens))(*[int(x) for x in seq_lens])
+        # a contiguous int32 numpy array is handed over as it lies (the planner copies what it keeps before it returns)
+        dt, fl = getattr(seq_lens, "dtype", None), getattr(seq_lens, "flags", None)
+        if dt is not None and fl is not None and str(dt) == "int32" and fl["C_CONTIGUOUS"] and getattr(seq_lens, "ndim", 0) == 1:
+            arr = seq_lens.ctypes.data
+        else:
+            arr = (C.c_int32 * len(seq_lens))(*[int(x) for x in seq_lens])
         _check(lib().silvann_b200_plan_decode(self.handle, arr, len(seq_lens), q_heads, kv_heads, head_dim, blocks_target, stream))
 
     def info(self) -> dict:
