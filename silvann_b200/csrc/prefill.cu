@@ -103,8 +103,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     uint64_t* p_full = s_full + NSB;         /* NSB */
     uint64_t* s_free = p_full + NSB;         /* NSB: the PV MMA that read the buffer's weights has completed */
     uint64_t* q_full = s_free + NSB;         /* 1 */
-    uint64_t* xbar = q_full + 1;             /* 4: the two softmax warps of a lane quadrant meet here once a tile */
-    uint64_t* o_staged = xbar + 4;           /* 1: the eight softmax warps have put their share of the output rows into shared memory */
+    uint64_t* o_staged = q_full + 1;           /* 1: the sixteen softmax warps have put their share of the output rows into shared memory */
     uint32_t* tmem_slot = (uint32_t*)(o_staged + 1);
     volatile uint32_t* abort_flag = (volatile uint32_t*)(tmem_slot + 1);
 
@@ -122,7 +121,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         for (int s = 0; s < VST; ++s) { mbar_init(&v_full[s], 1); mbar_init(&pv_done[s], 1); }
         for (int b = 0; b < NSB; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 16); mbar_init(&s_free[b], 1); }
         mbar_init(q_full, 1);
-        for (int x = 0; x < 4; ++x) mbar_init(&xbar[x], 2);
         mbar_init(o_staged, 16);
         *abort_flag = 0u;
         mbar_fence_init();
