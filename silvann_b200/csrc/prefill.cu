@@ -124,6 +124,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         mbar_init(o_staged, 16);
         *abort_flag = 0u;
         mbar_fence_init();
+        /* Programmatic dependent launch (a no-op for a launch without the attribute): this block may have been scheduled
+         * while the grid ahead of it on the stream was still running — its launch latency and this set-up are then off the
+         * path — and nothing of that grid's may be read or overwritten before the wait below has returned.  Everything
+         * else the block does follows from the copies asked for after it. */
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         /* Q and the first K tile are asked for here, ahead of the TMEM allocation and the block's first barrier: the
          * first score MMA waits for nothing else */
         tma_prefetch_desc(&qmap); tma_prefetch_desc(&kmap); tma_prefetch_desc(&vmap);
@@ -138,6 +143,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tc_fence_before();
     __syncthreads();
+    /* the launch behind this one on the stream may be scheduled once every block has got this far */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t t_o = tmem, t_s0 = tmem + Cfg::T_S;
@@ -479,7 +486,13 @@ static cudaError_t launch_prefill(const PrefillCall& c) {
         if (e != cudaSuccess) return e;
         attr_set[d].store(true, std::memory_order_release);
     }
-    prefill_kernel<D, DT><<<P.q_tiles * c.q_heads, PF_THREADS, Cfg::SMEM, c.stream>>>(qm, km, vm, om, P);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(P.q_tiles * c.q_heads); cfg.blockDim = dim3(PF_THREADS); cfg.dynamicSmemBytes = Cfg::SMEM; cfg.stream = c.stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, prefill_kernel<D, DT>, qm, km, vm, om, P);
+    if (e != cudaSuccess) return e;
     note_launch(1);
     return cudaGetLastError();
 }
