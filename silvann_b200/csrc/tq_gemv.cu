@@ -172,6 +172,12 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
         mbar_fence_init();
     }
     __syncthreads();
+    /* Programmatic dependent launch (no-ops for a launch without the attribute).  A decode step is a run of these calls
+     * back to back, each taking the answer of a kernel before it as its input: the launch behind this one may be scheduled
+     * as soon as every block has got this far, and a block scheduled early may stream its CODES and build its table at
+     * once — a layer's coded weights are not what the grid ahead writes — while everything that touches the input vector
+     * or the answers comes after the wait the working warps take below. */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t S = stages_s;
     if (S < 2) return;                                                       /* the launcher sized the block's memory so that two fit */
     /* this block's run of tiles: every block as many, to within one */
@@ -223,6 +229,7 @@ __global__ void __launch_bounds__(GV_THREADS + 32, 1) tq_gemv_fast_kernel(uint16
             asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(lut + ((uint32_t)tid + (uint32_t)k * GV_THREADS) * 16u), "r"(e[k]) : "memory");
     }
     asm volatile("bar.sync 1, %0;" ::"n"(GV_THREADS) : "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");                      /* the input vector may be the work of the grid ahead */
     const uint32_t at4 = lut | ((uint32_t)lane * 4u), at8 = at4 + 128u;     /* the 4-bit pair table, then the 8-bit one, in every entry */
     uint32_t xr[NIW][16];                                                    /* this lane's B fragments: input g, the columns of its bytes */
     uint32_t have_d = 0, n = 0, m = 0;
@@ -438,7 +445,13 @@ cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_
             if (e != cudaSuccess) return e;                                                                                          \
             ready[dev].store(true, std::memory_order_release);                                                                       \
         }                                                                                                                            \
-        tq_gemv_fast_kernel<N, WW><<<grid, GV_THREADS + 32, smem, st>>>(out, a, x, over);                                            \
+        cudaLaunchConfig_t cfg = {};                                                                                                 \
+        cfg.gridDim = dim3(grid); cfg.blockDim = dim3(GV_THREADS + 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;                \
+        cudaLaunchAttribute at[1];                                                                                                   \
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;         \
+        cfg.attrs = at; cfg.numAttrs = 1;                                                                                            \
+        const cudaError_t le = cudaLaunchKernelEx(&cfg, tq_gemv_fast_kernel<N, WW>, out, a, x, over);                                \
+        if (le != cudaSuccess) return le;                                                                                            \
     } while (0)
 #define SV_GV(N) do { if (one_width == 4) SV_GV2(N, 4); else if (one_width == 8) SV_GV2(N, 8); else SV_GV2(N, 0); } while (0)
     uint32_t one_width = a.d[0];
