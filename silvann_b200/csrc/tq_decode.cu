@@ -133,6 +133,10 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NW); }
         *abort_flag = 0u;
         mbar_fence_init();
+        /* Programmatic dependent launch (a no-op for a launch without the attribute): the block may have been scheduled while
+         * the grid ahead on the stream was still running — a tier's codes may be that grid's work (the mixer re-codes rows
+         * just before it attends), so nothing is read before this wait; the launch's latency and this set-up are off the path. */
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         /* the ring's first fill is asked for here, ahead of the table and the block's first barrier: the codes are what the
          * work waits for, and nothing has to be free for them yet */
         if (nt > 0) {
@@ -173,6 +177,7 @@ tq_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         *reinterpret_cast<uint2*>(q_s + h * Cfg::QROW + e * 2) = v;
     }
     __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   /* the launch behind this one may be scheduled once every block has got this far */
 
     float m_run[NHT][2], l_run[NHT][2];
     float oacc[NHT][KS][4];
@@ -507,7 +512,13 @@ static cudaError_t tq_launch_one(const CUtensorMap& km, const CUtensorMap& vm, c
         if (e != cudaSuccess) return e;
         attr_set[dev].store(true, std::memory_order_release);
     }
-    tq_attend_kernel<DH, W, NHT><<<blocks, (Cfg::NW + 1) * 32, smem, st>>>(km, vm, P);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks); cfg.blockDim = dim3((Cfg::NW + 1) * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    const cudaError_t ke = cudaLaunchKernelEx(&cfg, tq_attend_kernel<DH, W, NHT>, km, vm, P);
+    if (ke != cudaSuccess) return ke;
     note_launch(1);
     cudaError_t le = cudaGetLastError();           /* a refusal names what was asked for: the message the door prints has no room for it */
     if (le != cudaSuccess) {
