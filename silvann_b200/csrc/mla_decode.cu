@@ -132,6 +132,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         mbar_init(q_full, 1); mbar_init(s_full, 1); mbar_init(p_full, 4 * Cfg::HALVES); mbar_init(pv_done, 1);
         *abort_flag = 0u;
         mbar_fence_init();
+        /* Programmatic dependent launch (a no-op for a launch without the attribute): the block may have been scheduled while
+         * the grid ahead on the stream — the fold of the call before, or whatever gathered this latent — was still running;
+         * nothing of that grid's is read, and nothing it reads is overwritten, before this wait has returned. */
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         /* Q and the first tile are asked for here, ahead of the TMEM allocation and the block's first barrier: they head the
          * block's chain of dependent steps */
         if (nt > 0) {
@@ -400,6 +404,7 @@ template <int DT>
 __global__ void __launch_bounds__(128) mla_fold_kernel(uint16_t* o, float* res, const float* partials, uint32_t heads, uint32_t blocks, unsigned int* over) {
     using E = Elem<DT>;
     __shared__ float ms_s[160], ls_s[160], fs_s[160];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   /* a call behind this one may set up beside the fold; it reads nothing before its own wait */
     asm volatile("griddepcontrol.wait;" ::: "memory");          /* the partials are the grid ahead's */
     const uint32_t h = blockIdx.x / 4u, e = (blockIdx.x % 4u) * 128u + threadIdx.x, w = ML_D + 2;
     const size_t step = (size_t)heads * w;
@@ -492,7 +497,14 @@ static cudaError_t launch_mla(uint16_t* o, float* res, const void* q, const void
         if ((e = cudaFuncSetAttribute(mla_decode_kernel<NH, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM)) != cudaSuccess) return e;
         attr_set[d].store(true, std::memory_order_release);
     }
-    mla_decode_kernel<NH, DT><<<blocks * P.csplit, Cfg::THREADS, Cfg::SMEM, st>>>(qm, cm, P);
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(blocks * P.csplit); cfg.blockDim = dim3(Cfg::THREADS); cfg.dynamicSmemBytes = Cfg::SMEM; cfg.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        if ((e = cudaLaunchKernelEx(&cfg, mla_decode_kernel<NH, DT>, qm, cm, P)) != cudaSuccess) return e;
+    }
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     note_launch(1);
     if (blocks > 1u) {
