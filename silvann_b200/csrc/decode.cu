@@ -643,6 +643,11 @@ static DecodeScratch g_scratch[DEVICES_MAX];
 static unsigned int* g_status[DEVICES_MAX];
 static std::atomic<uint32_t> g_sms[DEVICES_MAX];
 
+bool pdl_allowed() {
+    static const bool on = []() { const char* v = getenv("SILVANN_B200_PDL"); return !(v && v[0] == '0'); }();
+    return on;
+}
+
 uint32_t device_sm_count() {
     int d = 0;
     if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= DEVICES_MAX) return 148u;
@@ -809,7 +814,7 @@ cudaError_t decode_launch(const DecodeCall& c) {
     /* one-sequence calls are a few microseconds long and often follow each other (a layer after a layer): they are launched
      * as programmatic dependents; SILVANN_B200_DECODE_PDL=0 turns that off */
     static const bool pdl_on = []() { const char* v = getenv("SILVANN_B200_DECODE_PDL"); return !(v && v[0] == '0'); }();
-    const bool pdl = pdl_on && !c.items;
+    const bool pdl = pdl_on && pdl_allowed() && !c.items;
     if (c.items) { blocks = c.n_items; P.nsplit = 0; }
     else {
         static const uint32_t splits_forced = env_u32("SILVANN_B200_DECODE_SPLITS");

@@ -62,6 +62,11 @@ cudaError_t decode_launch(const DecodeCall& c);
 /* Per-device scratch for calls that bring none (the doors): allocated once on first use, kept until exit. */
 cudaError_t decode_device_scratch(DecodeScratch* out);
 uint32_t device_sm_count();
+/* Whether kernels that follow each other closely are launched as programmatic dependents (the default);
+ * SILVANN_B200_PDL=0 turns it off for every kernel of the library, for a caller that cannot keep to what such a kernel
+ * reads before it waits for the grid ahead (the one-sequence decode: the K and V planes; the coded GEMV: the codes and
+ * their scales; every other kernel: nothing). */
+bool pdl_allowed();
 void note_launch(uint32_t kernels);    /* adds to the library's launch counter (family.cu) */
 unsigned int* device_status_word();   /* device address of the bound device's status word (allocated on first use) */
 cudaError_t static_status_take(unsigned int* word, int clear);   /* the allocation-free decode's own status word (decode.cu) */

@@ -502,7 +502,7 @@ static cudaError_t launch_mla(uint16_t* o, float* res, const void* q, const void
         cfg.gridDim = dim3(blocks * P.csplit); cfg.blockDim = dim3(Cfg::THREADS); cfg.dynamicSmemBytes = Cfg::SMEM; cfg.stream = st;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = at; cfg.numAttrs = 1;
+        cfg.attrs = at; cfg.numAttrs = pdl_allowed() ? 1u : 0u;
         if ((e = cudaLaunchKernelEx(&cfg, mla_decode_kernel<NH, DT>, qm, cm, P)) != cudaSuccess) return e;
     }
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
@@ -512,7 +512,7 @@ static cudaError_t launch_mla(uint16_t* o, float* res, const void* q, const void
         cfg.gridDim = dim3(NH * 4); cfg.blockDim = dim3(128); cfg.dynamicSmemBytes = 0; cfg.stream = st;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = at; cfg.numAttrs = 1;
+        cfg.attrs = at; cfg.numAttrs = pdl_allowed() ? 1u : 0u;
         e = cudaLaunchKernelEx(&cfg, mla_fold_kernel<DT>, o, res, (const float*)P.partials, (uint32_t)NH, blocks, over);
         if (e != cudaSuccess) return e;
         note_launch(1);

@@ -490,7 +490,7 @@ static cudaError_t launch_prefill(const PrefillCall& c) {
     cfg.gridDim = dim3(P.q_tiles * c.q_heads); cfg.blockDim = dim3(PF_THREADS); cfg.dynamicSmemBytes = Cfg::SMEM; cfg.stream = c.stream;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
+    cfg.attrs = at; cfg.numAttrs = pdl_allowed() ? 1u : 0u;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, prefill_kernel<D, DT>, qm, km, vm, om, P);
     if (e != cudaSuccess) return e;
     note_launch(1);

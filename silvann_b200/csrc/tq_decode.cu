@@ -516,7 +516,7 @@ static cudaError_t tq_launch_one(const CUtensorMap& km, const CUtensorMap& vm, c
     cfg.gridDim = dim3(blocks); cfg.blockDim = dim3((Cfg::NW + 1) * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
+    cfg.attrs = at; cfg.numAttrs = pdl_allowed() ? 1u : 0u;
     const cudaError_t ke = cudaLaunchKernelEx(&cfg, tq_attend_kernel<DH, W, NHT>, km, vm, P);
     if (ke != cudaSuccess) return ke;
     note_launch(1);

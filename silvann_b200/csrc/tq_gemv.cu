@@ -449,7 +449,7 @@ cudaError_t tq_gemv_fast_launch(uint16_t* out, const void* groups, const uint64_
         cfg.gridDim = dim3(grid); cfg.blockDim = dim3(GV_THREADS + 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;                \
         cudaLaunchAttribute at[1];                                                                                                   \
         at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;         \
-        cfg.attrs = at; cfg.numAttrs = 1;                                                                                            \
+        cfg.attrs = at; cfg.numAttrs = pdl_allowed() ? 1u : 0u;                                                                      \
         const cudaError_t le = cudaLaunchKernelEx(&cfg, tq_gemv_fast_kernel<N, WW>, out, a, x, over);                                \
         if (le != cudaSuccess) return le;                                                                                            \
     } while (0)
