@@ -204,13 +204,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         }
     } else if (warp == 1) {
         /* ---------------- score MMAs: S(j) = Q · K(j)^T ----------------
-         * Two threads issue MMAs, this one the scores and one of warp 10 the values, because a thread that waits on an
+         * Two threads issue MMAs, this one the scores and one of warp 2 the values, because a thread that waits on an
          * mbarrier (about a hundred cycles even when the phase is long complete) feeds the tensor pipe nothing meanwhile
          * and the pipe's queue is short: with one issuer every wait is a bubble.  Scores run up to NSB tiles ahead; a
          * buffer is reused once the value MMA that read its weights has completed, which the K stage's barrier also waits
          * for (measured: each wait or commit taken off this thread's tile was worth 2-4 % of the whole kernel). */
         /* This thread's own waits are not on mbarriers at all.  Any access of its to shared memory — an mbarrier try, a plain load
-         * — takes 100-200 cycles while the MMAs' operand reads own the port, and nothing is issued meanwhile.  The scout (warp 11)
+         * — takes 100-200 cycles while the MMAs' operand reads own the port, and nothing is issued meanwhile.  The scout (warp 3)
          * takes the tile's mbarrier waits a tile ahead and says so on a hardware barrier (bar 1: the scout arrives, this warp
          * syncs); this warp says on bar 2 that it has taken the word, which lets the scout go on to the next tile.  A barrier's
          * generation is the scout's 32 threads and this warp's 32, and neither side can be two generations ahead of the other.
